@@ -1,0 +1,600 @@
+// TEST INFRASTRUCTURE — CPU restatement of libkineto's trace post-processing path, used only as the
+// checker for the CUDA implementation (tests/, the smoke test, and bench.py's cpu_baseline leg).
+// The product library never calls into this file.
+//
+// Parity status: PINNED.  tests/test_oracle_vs_reference.py compares this restatement byte for byte
+// with the unmodified reference (oracle/_ref/ref_driver) on seeded traces, and tests/golden/ holds
+// reference outputs for machines where the reference is not built.
+//
+// What is restated (reference file:line, paths relative to the reference project):
+//   pass 1  correlation maps            libkineto/src/CuptiActivityProfiler.cpp:256-302
+//   pass 2  record dispatch             libkineto/src/CuptiActivityProfiler.cpp:532-588
+//           runtime / driver records    libkineto/src/CuptiActivityProfiler.cpp:304-358
+//           GPU records, window, spans  libkineto/src/GenericActivityProfiler.cpp:329-340, :397-435
+//   CPU ops                             libkineto/src/GenericActivityProfiler.cpp:234-275
+//   timestamps                          libkineto/src/CuptiTimestamp.h:29-51, src/ApproximateClock.cpp:83-90
+//   names                               libkineto/src/CuptiActivity.h:297-300, :586-602, :682-687
+//   args fragments                      libkineto/src/CuptiActivity.h:499-576, :604-622, :643-672,
+//                                       :694-712, :758-765;  include/TypedMetadataJson.h:38-205
+//   occupancy                           libkineto/src/DeviceProperties.cpp:161-222 (NVIDIA's
+//                                       cuda_occupancy.h from the CUDA toolkit, as the reference uses)
+//   JSON text                           libkineto/src/output_json.cpp:72-126, :144-153, :193-203,
+//                                       :237-259, :318-345, :837-1021
+//   user-annotation spans               libkineto/src/GenericActivityProfiler.cpp:277-327
+//
+// Output: the "activities" part of the trace file, i.e. every event written between the header /
+// metadata rows and the CPU trace span: CPU-op events, then GPU-side events in buffer order, then
+// gpu_user_annotation spans (ActivityTrace::save order, libkineto/src/output_membuf.h:91-107).
+#include <charconv>
+#include <cinttypes>
+#include <climits>
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include <cuda_occupancy.h>
+
+#include "trace_file.h"
+
+namespace {
+
+enum : uint32_t { K_MEMCPY = 1, K_MEMSET = 2, K_DRIVER = 4, K_RUNTIME = 5, K_KERNEL = 10, K_MEMCPY2 = 22, K_EXTCORR = 39 };
+enum : int { T_CPU_OP = 0, T_GPU_USER_ANNOTATION = 2, T_GPU_MEMCPY = 3, T_GPU_MEMSET = 4, T_KERNEL = 5, T_RUNTIME = 7,
+             T_DRIVER = 8, T_CPU_INSTANT = 9, T_MTIA_COUNTERS = 17, T_XPU_RUNTIME = 21, T_XPU_DRIVER = 22,
+             T_PU1_RUNTIME = 24, T_PU1_DRIVER = 25, T_XPU_SCOPE = 26, T_HW_COUNTERS = 28, T_COUNT = 29 };
+const char* kTypeNames[T_COUNT] = {  // libkineto/include/ActivityType.h:80-112
+    "cpu_op", "user_annotation", "gpu_user_annotation", "gpu_memcpy", "gpu_memset", "kernel",
+    "external_correlation", "cuda_runtime", "cuda_driver", "cpu_instant_event", "python_function",
+    "overhead", "mtia_runtime", "mtia_ccp_events", "mtia_insight", "cuda_sync", "cuda_event",
+    "mtia_counters", "glow_runtime", "cuda_profiler_range", "hpu_op", "xpu_runtime", "xpu_driver",
+    "collective_comm", "privateuse1_runtime", "privateuse1_driver", "xpu_scope_profiler", "xpu_sync",
+    "hardware_counters"};
+
+size_t recSize(uint32_t kind) {
+  switch (kind) {
+    case K_KERNEL: return 208;
+    case K_MEMCPY: return 88;
+    case K_MEMCPY2: return 96;
+    case K_MEMSET: return 88;
+    case K_RUNTIME: case K_DRIVER: return 40;
+    case K_EXTCORR: return 24;
+    default: return 0;
+  }
+}
+
+template <class T> T rd(const uint8_t* p, size_t off) { T v; memcpy(&v, p + off, sizeof(T)); return v; }
+
+struct Counters {  // GenericActivityProfiler::ErrorCounts, libkineto/src/GenericActivityProfiler.h:528-535
+  uint64_t out_of_range = 0, blocklisted_runtime = 0, invalid_external_correlation = 0, unexpected = 0;
+  uint64_t x_events = 0, flow_events = 0, records = 0;
+};
+
+// ---- runtime/driver callback classification: libkineto/src/CuptiCbidRegistry.cpp:53-258 ----
+bool rtFlow(uint32_t c) {
+  switch (c) { case 211: case 269: case 272: case 430: case 311: case 131: case 165: case 147: return true; }
+  return c >= 31 && c <= 52;
+}
+bool rtBlocked(uint32_t c) { return c == 17 || c == 16 || c == 10 || c == 133 || c == 134 || c == 136; }
+bool drRegistered(uint32_t c) { return c == 307 || c == 652 || c == 549 || c == 551 || c == 552 || c == 550 || c == 554 || c == 555; }
+bool drFlow(uint32_t c) { return c == 307 || c == 652; }
+
+const char* memcpyKindStr(uint8_t k) {  // libkineto/src/cupti_strings.cpp:15-41
+  static const char* n[] = {nullptr, "HtoD", "DtoH", "HtoA", "AtoH", "AtoA", "AtoD", "DtoA", "DtoD", "HtoH", "PtoP"};
+  return (k >= 1 && k <= 10) ? n[k] : "<unknown>";
+}
+const char* memoryKindStr(uint32_t k) {  // libkineto/src/cupti_strings.cpp:43-66
+  static const char* n[] = {"Unknown", "Pageable", "Pinned", "Device", "Array", "Managed", "Device Static", "Managed Static"};
+  if (k <= 7) return n[k];
+  if (k == 0x7fffffff) return "Force Int";
+  return "Unrecognized";
+}
+
+// ---- text helpers ----
+void appendI(std::string& s, int64_t v) { char b[24]; auto r = std::to_chars(b, b + 24, v); s.append(b, r.ptr); }
+void appendU(std::string& s, uint64_t v) { char b[24]; auto r = std::to_chars(b, b + 24, v); s.append(b, r.ptr); }
+
+// Default "{}" formatting of a double in {fmt}: shortest round-trip digits; fixed notation when the
+// decimal exponent is in [-4, 16), otherwise d[.ddd]e±XX with at least two exponent digits.
+void appendFmtDouble(std::string& s, double v) {
+  if (std::isnan(v)) { s += std::signbit(v) ? "-nan" : "nan"; return; }
+  if (std::isinf(v)) { s += v < 0 ? "-inf" : "inf"; return; }
+  if (std::signbit(v)) { s += '-'; v = -v; }
+  if (v == 0) { s += '0'; return; }
+  char b[64];
+  auto r = std::to_chars(b, b + 64, v, std::chars_format::scientific);
+  std::string t(b, r.ptr);  // d[.ddd]e[+-]XX
+  size_t epos = t.find('e');
+  int e10 = atoi(t.c_str() + epos + 1);
+  std::string digits;
+  for (size_t i = 0; i < epos; i++) if (t[i] != '.') digits += t[i];
+  int nd = (int)digits.size();
+  if (e10 < -4 || e10 >= 16) {
+    s += digits[0];
+    if (nd > 1) { s += '.'; s.append(digits, 1, std::string::npos); }
+    s += 'e';
+    s += e10 < 0 ? '-' : '+';
+    int a = e10 < 0 ? -e10 : e10;
+    if (a < 10) s += '0';
+    appendI(s, a);
+    return;
+  }
+  if (e10 >= nd - 1) {           // integer: digits then zeros
+    s += digits;
+    s.append(e10 - (nd - 1), '0');
+  } else if (e10 >= 0) {         // d.d with point inside
+    s.append(digits, 0, e10 + 1);
+    s += '.';
+    s.append(digits, e10 + 1, std::string::npos);
+  } else {                       // 0.000ddd
+    s += "0.";
+    s.append(-e10 - 1, '0');
+    s += digits;
+  }
+}
+void appendDoubleValue(std::string& s, double v) {  // TypedMetadataJson.h:172-178
+  if (std::isfinite(v)) { appendFmtDouble(s, v); return; }
+  s += '"'; appendFmtDouble(s, v); s += '"';
+}
+
+struct Frag {  // JsonTypedMetadataVisitor
+  std::string j; bool first = true;
+  void key(const char* k) { if (!first) j += ", "; first = false; j += '"'; j += k; j += "\": "; }
+  void key(const std::string& k) { key(k.c_str()); }
+  void i64(const char* k, int64_t v) { key(k); appendI(j, v); }
+  void u64(const char* k, uint64_t v) { key(k); appendU(j, v); }
+  void dbl(const char* k, double v) { key(k); appendDoubleValue(j, v); }
+  void str(const char* k, const char* v) { key(k); j += '"'; j += v; j += '"'; }
+  void beginDict(const char* k) { key(k); j += '{'; first = true; }
+  void endDict() { j += '}'; first = false; }
+};
+
+void sanitize(std::string& v) {  // output_json.cpp:72-78
+  std::string o; o.reserve(v.size());
+  for (char c : v) { if (c == '\n') continue; o += (c == '\\') ? '/' : c; }
+  v.swap(o);
+}
+std::string eventName(std::string n) {  // output_json.cpp:946-949
+  if (n == "kernel") n = "Kernel";
+  sanitize(n);
+  for (unsigned char c : n) if (c < 0x20 || c > 0x7e) { n = "unknown"; break; }
+  std::string o;
+  for (char c : n) { if (c == '"') o += '\\'; o += c; }
+  return o;
+}
+bool allSpace(const std::string& s) { for (unsigned char c : s) if (!isspace(c)) return false; return true; }
+
+void appendTs(std::string& s, int64_t ns) {  // fmtTs, output_json.cpp:124-126
+  appendI(s, ns / 1000);
+  s += '.';
+  int64_t r = ns % 1000;
+  char b[8];
+  snprintf(b, sizeof b, "%03" PRId64, r);  // "{:03}" pads to width 3 including a minus sign
+  s += b;
+}
+int64_t sanitizeTid(int64_t t) { return t == INT64_MIN ? 0 : (t < 0 ? -t : t); }
+
+struct Out {
+  std::string buf;
+  int64_t base;
+  Counters* c;
+  int64_t rel(int64_t t) const { int64_t r = t - base; return r < 0 ? 0 : r; }
+  void xEvent(const char* cat, const std::string& name, int64_t pid, int64_t tid, int64_t ts, int64_t dur, const std::string& args) {
+    buf += "\n  {\n    \"ph\": \"X\",\n    \"cat\": \""; buf += cat;
+    buf += "\",\n    \"name\": \""; buf += name;
+    buf += "\",\n    \"pid\": "; appendI(buf, pid);
+    buf += ",\n    \"tid\": "; appendI(buf, tid);
+    buf += ",\n    \"ts\": "; appendTs(buf, ts);
+    buf += ",\n    \"dur\": "; appendTs(buf, dur);
+    buf += "\n    ";
+    if (!args.empty()) { buf += ",\n    \"args\": {\n      "; buf += args; buf += "\n    }"; }
+    buf += "\n  },";
+    c->x_events++;
+  }
+  void flow(char ph, int64_t id, int64_t pid, int64_t tid, int64_t ts, const char* name) {
+    buf += "\n  {\n    \"ph\": \""; buf += ph;
+    buf += "\",\n    \"id\": "; appendI(buf, id);
+    buf += ",\n    \"pid\": "; appendI(buf, pid);
+    buf += ",\n    \"tid\": "; appendI(buf, tid);
+    buf += ",\n    \"ts\": "; appendTs(buf, ts);
+    buf += ",\n    \"cat\": \""; buf += name; buf += "\",\n    \"name\": \""; buf += name; buf += "\"\n    ";
+    if (ph == 'f') buf += ", \"bp\": \"e\"";
+    buf += "\n  },";
+    c->flow_events++;
+  }
+};
+
+// handleActivity, output_json.cpp:837-963, for the event shapes this path produces.
+struct Event {
+  int type; std::string name; int64_t ts, dur, device, resource; bool hasLinked; int64_t linkedId;
+  int64_t corrId; std::string md; int64_t flowId; int flowType; bool flowStart;
+};
+void emit(Out& o, const Event& e) {
+  int64_t ts = e.ts, dur = e.dur < 0 ? 0 : e.dur;
+  if (e.type == T_GPU_USER_ANNOTATION) { ts -= 1; dur += 2; }
+  int external = 0;
+  if (e.hasLinked) external = (int)e.linkedId;
+  else {
+    switch (e.type) {
+      case T_GPU_MEMCPY: case T_GPU_MEMSET: case T_KERNEL: case T_RUNTIME: case T_DRIVER:
+      case T_XPU_RUNTIME: case T_XPU_DRIVER: case T_PU1_RUNTIME: case T_PU1_DRIVER: break;
+      default: external = (int)e.corrId;
+    }
+  }
+  std::string args;
+  if (external != 0) { args += "\"External id\": "; appendI(args, external); }
+  std::string md = e.md;
+  sanitize(md);
+  if (!md.empty() && !allSpace(md)) { if (!args.empty()) args += ","; args += md; }
+  o.xEvent(kTypeNames[e.type], eventName(e.name), e.device, sanitizeTid(e.resource), o.rel(ts), dur, args);
+  if (e.flowId > 0) {
+    const char* fname = e.flowType == 1 ? "fwdbwd" : e.flowType == 2 ? "ac2g" : nullptr;
+    if (fname) o.flow(e.flowStart ? 's' : 'f', e.flowId, e.device, sanitizeTid(e.resource), o.rel(e.ts), fname);
+  }
+}
+
+struct Conv {  // the converter lambda of ApproximateClock.cpp:83-90 with fixed constants
+  int mode; int64_t t0; uint64_t t0a; long double scale;
+  int64_t operator()(uint64_t t) const {
+    if (mode == 0) return (int64_t)t;
+    return t > t0a ? static_cast<int64_t>(static_cast<double>(t - t0a) * scale) + t0 : 0;
+  }
+};
+
+struct Run {
+  const K2JTraceFile& tf;
+  k2jt_params p;
+  Counters c;
+  Out out;
+  Conv conv;
+  std::unordered_map<int64_t, int64_t> cpuCorr, userCorr;
+  std::unordered_map<int64_t, size_t> activityMap;  // op id -> op row (last writer wins)
+  std::map<int32_t, int32_t> tidMap;
+  struct Span { int64_t start, end; size_t op; int64_t device, resource; };
+  std::map<std::pair<int64_t, int64_t>, std::unordered_map<int64_t, Span>> userSpans;
+  size_t seg[3] = {0, 0, 0};
+
+  explicit Run(const K2JTraceFile& f) : tf(f), p(*f.ptr<k2jt_params>("PARAMS")) {
+    out.base = p.base_time_ns; out.c = &c;
+    conv = Conv{p.ts_mode, p.conv_t0, p.conv_t0_approx, ldexpl((long double)p.conv_scale_mant, p.conv_scale_exp - 63)};
+  }
+
+  std::string opMetadata(size_t i) {
+    const uint32_t* off = tf.ptr<uint32_t>("OPMDOFF");
+    const k2jt_md_entry* md = tf.ptr<k2jt_md_entry>("MDENT");
+    Frag f;
+    for (uint32_t e = off[i]; e < off[i + 1]; e++) {
+      f.key(tf.str(md[e].key));
+      switch (md[e].type) {
+        case 0: appendI(f.j, (int64_t)md[e].value); break;
+        case 1: appendU(f.j, md[e].value); break;
+        case 2: { double d; memcpy(&d, &md[e].value, 8); appendDoubleValue(f.j, d); break; }
+        case 3: f.j += md[e].value ? "true" : "false"; break;
+        case 4: f.j += '"'; f.j += tf.str((uint32_t)md[e].value); f.j += '"'; break;
+        case 5: f.j += tf.str((uint32_t)md[e].value); break;
+      }
+    }
+    return f.j;
+  }
+
+  void cpuOps() {
+    size_t n = tf.count<int64_t>("OPSTART");
+    for (size_t i = 0; i < n; i++) {
+      Event e;
+      e.type = tf.ptr<int32_t>("OPTYPE")[i];
+      e.name = tf.str(tf.ptr<uint32_t>("OPNAME")[i]);
+      e.ts = tf.ptr<int64_t>("OPSTART")[i];
+      e.dur = tf.ptr<int64_t>("OPEND")[i] - e.ts;
+      e.device = tf.ptr<int32_t>("OPDEV")[i];
+      e.resource = tf.ptr<int64_t>("OPRES")[i];
+      e.hasLinked = false; e.linkedId = 0;
+      e.corrId = tf.ptr<int32_t>("OPID")[i];
+      e.md = opMetadata(i);
+      e.flowId = tf.ptr<uint32_t>("OPFLOW")[i];
+      uint8_t ft = tf.ptr<uint8_t>("OPFLOWT")[i];
+      e.flowType = ft & 0xf; e.flowStart = (ft >> 4) & 1;
+      emit(out, e);
+      activityMap[e.corrId] = i;
+    }
+  }
+
+  bool linked(uint32_t corr, int64_t* id) {  // linkedActivity(int32_t, ...), GenericActivityProfiler.cpp:397-408
+    auto it = cpuCorr.find((int64_t)(int32_t)corr);
+    if (it == cpuCorr.end()) return false;
+    auto it2 = activityMap.find(it->second);
+    if (it2 == activityMap.end()) return false;
+    *id = tf.ptr<int32_t>("OPID")[it2->second];
+    return true;
+  }
+  bool outOfRange(int64_t ts, int64_t dur) {
+    bool oor = ts < p.window_start_ns || (ts + dur) > p.window_end_ns;
+    if (oor) c.out_of_range++;
+    return oor;
+  }
+
+  template <class F>
+  void forEachRecord(F f) {
+    const uint8_t* cu = tf.ptr<uint8_t>("CUPTI");
+    const uint64_t* bt = tf.ptr<uint64_t>("BUFTAB");
+    size_t nb = tf.count<uint64_t>("BUFTAB") / 2;
+    for (size_t b = 0; b < nb; b++) {
+      size_t pos = bt[2 * b], end = pos + bt[2 * b + 1];
+      while (pos < end) {
+        uint32_t kind = rd<uint32_t>(cu, pos);
+        size_t sz = recSize(kind);
+        f(cu + pos, kind);
+        if (!sz) break;  // unknown kind: length unknown, rest of the buffer cannot be walked
+        pos += sz;
+      }
+    }
+  }
+
+  void pass1() {
+    forEachRecord([&](const uint8_t* r, uint32_t kind) {
+      if (kind != K_EXTCORR) return;
+      uint32_t ek = rd<uint32_t>(r, 4);
+      int64_t ext = (int64_t)rd<uint64_t>(r, 8);
+      int64_t corr = rd<uint32_t>(r, 16);
+      if (ek == 3) cpuCorr[corr] = ext;
+      else if (ek == 4) userCorr[corr] = ext;
+      else c.invalid_external_correlation++;
+    });
+  }
+
+  void apiRecord(const uint8_t* r, bool driver) {
+    uint32_t cbid = rd<uint32_t>(r, 4);
+    if (!driver) { if (rtBlocked(cbid)) { c.blocklisted_runtime++; return; } }
+    else if (!drRegistered(cbid)) return;
+    Event e;
+    e.type = driver ? T_DRIVER : T_RUNTIME;
+    const uint32_t* nt = tf.ptr<uint32_t>(driver ? "DRNAME" : "RTNAME");
+    size_t nn = tf.count<uint32_t>(driver ? "DRNAME" : "RTNAME");
+    e.name = cbid < nn ? tf.str(nt[cbid]) : "INVALID";
+    uint64_t s = rd<uint64_t>(r, 8), en = rd<uint64_t>(r, 16);
+    e.ts = conv(s);
+    e.dur = p.ts_mode ? conv(en) - conv(s) : (int64_t)(en - s);
+    int32_t tid = (int32_t)rd<uint32_t>(r, 28);
+    auto it = tidMap.find(tid);
+    if (it != tidMap.end()) tid = it->second;
+    e.device = p.pid; e.resource = tid;
+    uint32_t corr = rd<uint32_t>(r, 32);
+    e.hasLinked = linked(corr, &e.linkedId);
+    e.corrId = corr;
+    if (outOfRange(e.ts, e.dur)) return;
+    Frag f;
+    f.u64("cbid", cbid); f.u64("correlation", corr);
+    e.md = f.j;
+    e.flowId = corr; e.flowType = 2; e.flowStart = driver ? drFlow(cbid) : rtFlow(cbid);
+    emit(out, e);
+  }
+
+  void gpuCommon(Event& e, uint32_t corr, uint64_t s, uint64_t en, int64_t device, int64_t stream) {
+    e.ts = conv(s);
+    e.dur = p.ts_mode ? conv(en) - conv(s) : (int64_t)(en - s);
+    e.device = device; e.resource = stream;
+    e.hasLinked = linked(corr, &e.linkedId);
+    e.corrId = corr; e.flowId = corr; e.flowType = 2; e.flowStart = false;
+  }
+  void afterGpu(const Event& e) {  // GenericActivityProfiler.cpp:424-434
+    if (!(p.flags & 1)) return;
+    auto it = userCorr.find(e.corrId);
+    if (it == userCorr.end()) return;
+    auto it2 = activityMap.find(it->second);
+    if (it2 == activityMap.end()) return;
+    int64_t opId = tf.ptr<int32_t>("OPID")[it2->second];
+    auto& m = userSpans[{e.device, e.resource}];
+    auto f = m.find(opId);
+    if (f == m.end()) f = m.insert({opId, Span{e.ts, e.ts + e.dur, it2->second, e.device, e.resource}}).first;
+    Span& sp = f->second;
+    if (e.ts < sp.start || sp.start == 0) sp.start = e.ts;
+    sp.end = std::max(e.ts + e.dur, sp.end);
+  }
+  void graphAndChannel(Frag& f, uint32_t graphId, uint64_t node, uint32_t ch, uint32_t chType) {
+    f.u64("graph id", graphId); f.u64("graph node id", node); f.u64("channel", ch); f.i64("channel_type", (int64_t)chType);
+  }
+
+  void kernelRecord(const uint8_t* r) {
+    Event e; e.type = T_KERNEL;
+    uint32_t dev = rd<uint32_t>(r, 40), ctx = rd<uint32_t>(r, 44), stream = rd<uint32_t>(r, 48), corr = rd<uint32_t>(r, 92);
+    gpuCommon(e, corr, rd<uint64_t>(r, 16), rd<uint64_t>(r, 24), dev, stream);
+    if (outOfRange(e.ts, e.dur)) return;
+    e.name = tf.str((uint32_t)rd<uint64_t>(r, 104));
+    int32_t gx = rd<int32_t>(r, 52), gy = rd<int32_t>(r, 56), gz = rd<int32_t>(r, 60);
+    int32_t bx = rd<int32_t>(r, 64), by = rd<int32_t>(r, 68), bz = rd<int32_t>(r, 72);
+    int32_t ssm = rd<int32_t>(r, 76), dsm = rd<int32_t>(r, 80);
+    uint16_t regs = rd<uint16_t>(r, 6);
+    const k2jt_device_props* dp = tf.ptr<k2jt_device_props>("DEVPROPS");
+    int smCount = dev < (uint32_t)p.n_devices ? dp[dev].num_sms : 0;
+    // blocksPerSm / warpsPerSm, DeviceProperties.cpp:161-174 (32-bit wrapping products, float math)
+    int32_t gridProd = (int32_t)((uint32_t)gx * (uint32_t)gy * (uint32_t)gz);
+    int32_t blockProd = (int32_t)((uint32_t)bx * (uint32_t)by * (uint32_t)bz);
+    float bps = smCount == 0 ? INFINITY : gridProd / static_cast<float>(smCount);
+    float wps = bps * blockProd / 32;
+    // computeOccupancyMetrics, DeviceProperties.cpp:176-222
+    cudaOccResult occ{};  // zero-initialised like OccupancyMetrics' default member
+    float occupancy = 0.0f;
+    if (dev < (uint32_t)p.n_devices) {
+      float blocksPerSm = -1.0f;
+      if (smCount != 0) blocksPerSm = gridProd / static_cast<float>(smCount);
+      cudaOccFuncAttributes fa;
+      fa.maxThreadsPerBlock = INT_MAX; fa.numRegs = regs; fa.sharedSizeBytes = ssm;
+      fa.partitionedGCConfig = PARTITIONED_GC_OFF; fa.shmemLimitConfig = FUNC_SHMEM_LIMIT_DEFAULT;
+      fa.maxDynamicSharedSizeBytes = 0;
+      fa.numBlockBarriers = 0;
+      const cudaOccDeviceState st = {};
+      cudaOccDeviceProp prop;
+      prop.computeMajor = dp[dev].major; prop.computeMinor = dp[dev].minor;
+      prop.maxThreadsPerBlock = dp[dev].max_threads_per_block;
+      prop.maxThreadsPerMultiprocessor = dp[dev].max_threads_per_sm;
+      prop.regsPerBlock = dp[dev].regs_per_block; prop.regsPerMultiprocessor = dp[dev].regs_per_sm;
+      prop.warpSize = dp[dev].warp_size; prop.sharedMemPerBlock = dp[dev].smem_per_block;
+      prop.sharedMemPerMultiprocessor = dp[dev].smem_per_sm; prop.numSms = dp[dev].num_sms;
+      prop.sharedMemPerBlockOptin = dp[dev].smem_per_block_optin;
+      prop.reservedSharedMemPerBlock = dp[dev].reserved_smem_per_block;
+      cudaOccError status = cudaOccMaxActiveBlocksPerMultiprocessor(&occ, &prop, &fa, &st, blockProd, (size_t)dsm);
+      if (status == CUDA_OCC_SUCCESS) {
+        float eff = std::min<float>((float)occ.activeBlocksPerMultiprocessor, blocksPerSm);
+        occupancy = eff * blockProd / static_cast<float>(dp[dev].max_threads_per_sm);
+      }
+    }
+    Frag f;
+    f.u64("queued", rd<uint64_t>(r, 120)); f.i64("device", dev); f.u64("context", ctx); f.i64("stream", stream);
+    f.u64("correlation", corr); f.u64("registers per thread", regs);
+    f.i64("shared memory", (int64_t)(int32_t)((uint32_t)ssm + (uint32_t)dsm));
+    f.dbl("blocks per SM", (double)bps); f.dbl("warps per SM", (double)wps);
+    f.key("grid"); f.j += '['; appendI(f.j, gx); f.j += ", "; appendI(f.j, gy); f.j += ", "; appendI(f.j, gz); f.j += ']';
+    f.key("block"); f.j += '['; appendI(f.j, bx); f.j += ", "; appendI(f.j, by); f.j += ", "; appendI(f.j, bz); f.j += ']';
+    f.i64("est. achieved occupancy %", (int64_t)std::lround(occupancy * 100.0));
+    f.beginDict("occupancy");
+    f.i64("activeBlocksPerMultiprocessor", occ.activeBlocksPerMultiprocessor);
+    {
+      std::string lf;
+      unsigned fac = occ.limitingFactors;
+      if (fac == 0) lf = "none";
+      else {
+        const std::pair<unsigned, const char*> k[] = {{OCC_LIMIT_WARPS, "WARPS"}, {OCC_LIMIT_REGISTERS, "REGS"},
+            {OCC_LIMIT_SHARED_MEMORY, "SMEM"}, {OCC_LIMIT_BLOCKS, "BLOCKS"}, {OCC_LIMIT_BARRIERS, "BARRIERS"}};
+        for (auto& [m, n] : k) if (fac & m) { if (!lf.empty()) lf += "|"; lf += n; }
+      }
+      f.str("limitingFactors", lf.c_str());
+    }
+    f.i64("blockLimitRegs", occ.blockLimitRegs); f.i64("blockLimitSharedMem", occ.blockLimitSharedMem);
+    f.i64("blockLimitWarps", occ.blockLimitWarps); f.i64("blockLimitBlocks", occ.blockLimitBlocks);
+    f.i64("blockLimitBarriers", occ.blockLimitBarriers);
+    f.i64("allocatedRegistersPerBlock", occ.allocatedRegistersPerBlock);
+    f.u64("allocatedSharedMemPerBlock", occ.allocatedSharedMemPerBlock);
+    f.endDict();
+    graphAndChannel(f, rd<uint32_t>(r, 156), rd<uint64_t>(r, 144), rd<uint32_t>(r, 168), rd<uint32_t>(r, 172));
+    e.md = f.j;
+    emit(out, e);
+    afterGpu(e);
+  }
+
+  void bandwidth(Frag& f, uint64_t bytes, int64_t dur) {  // CuptiActivity.h:460-470
+    if (dur == 0) return;
+    f.dbl("memory bandwidth (GB/s)", static_cast<double>(bytes) / static_cast<double>(dur));
+  }
+  std::string memcpyName(const uint8_t* r) {
+    return std::string("Memcpy ") + memcpyKindStr(r[4]) + " (" + memoryKindStr(r[5]) + " -> " + memoryKindStr(r[6]) + ")";
+  }
+  void memcpyRecord(const uint8_t* r) {
+    Event e; e.type = T_GPU_MEMCPY;
+    uint32_t dev = rd<uint32_t>(r, 32), ctx = rd<uint32_t>(r, 36), stream = rd<uint32_t>(r, 40), corr = rd<uint32_t>(r, 44);
+    gpuCommon(e, corr, rd<uint64_t>(r, 16), rd<uint64_t>(r, 24), dev, stream);
+    if (outOfRange(e.ts, e.dur)) return;
+    e.name = memcpyName(r);
+    uint64_t bytes = rd<uint64_t>(r, 8);
+    Frag f;
+    f.i64("device", dev); f.u64("context", ctx); f.i64("stream", stream); f.u64("correlation", corr); f.u64("bytes", bytes);
+    bandwidth(f, bytes, e.dur);
+    graphAndChannel(f, rd<uint32_t>(r, 72), rd<uint64_t>(r, 64), rd<uint32_t>(r, 76), rd<uint32_t>(r, 80));
+    e.md = f.j; emit(out, e); afterGpu(e);
+  }
+  void memcpy2Record(const uint8_t* r) {
+    Event e; e.type = T_GPU_MEMCPY;
+    uint32_t dev = rd<uint32_t>(r, 32), ctx = rd<uint32_t>(r, 36), stream = rd<uint32_t>(r, 40), corr = rd<uint32_t>(r, 60);
+    gpuCommon(e, corr, rd<uint64_t>(r, 16), rd<uint64_t>(r, 24), dev, stream);
+    if (outOfRange(e.ts, e.dur)) return;
+    e.name = memcpyName(r);
+    uint64_t bytes = rd<uint64_t>(r, 8);
+    Frag f;
+    f.u64("fromDevice", rd<uint32_t>(r, 44)); f.u64("inDevice", dev); f.u64("toDevice", rd<uint32_t>(r, 52));
+    f.u64("fromContext", rd<uint32_t>(r, 48)); f.u64("inContext", ctx); f.u64("toContext", rd<uint32_t>(r, 56));
+    f.i64("stream", stream); f.u64("correlation", corr); f.u64("bytes", bytes);
+    bandwidth(f, bytes, e.dur);
+    graphAndChannel(f, rd<uint32_t>(r, 80), rd<uint64_t>(r, 72), rd<uint32_t>(r, 84), rd<uint32_t>(r, 88));
+    e.md = f.j; emit(out, e); afterGpu(e);
+  }
+  void memsetRecord(const uint8_t* r) {
+    Event e; e.type = T_GPU_MEMSET;
+    uint32_t dev = rd<uint32_t>(r, 32), ctx = rd<uint32_t>(r, 36), stream = rd<uint32_t>(r, 40), corr = rd<uint32_t>(r, 44);
+    gpuCommon(e, corr, rd<uint64_t>(r, 16), rd<uint64_t>(r, 24), dev, stream);
+    if (outOfRange(e.ts, e.dur)) return;
+    e.name = std::string("Memset (") + memoryKindStr(rd<uint16_t>(r, 50)) + ")";
+    uint64_t bytes = rd<uint64_t>(r, 8);
+    Frag f;
+    f.i64("device", dev); f.u64("context", ctx); f.i64("stream", stream); f.u64("correlation", corr); f.u64("bytes", bytes);
+    bandwidth(f, bytes, e.dur);
+    graphAndChannel(f, rd<uint32_t>(r, 72), rd<uint64_t>(r, 64), rd<uint32_t>(r, 76), rd<uint32_t>(r, 80));
+    e.md = f.j; emit(out, e); afterGpu(e);
+  }
+
+  void pass2() {
+    forEachRecord([&](const uint8_t* r, uint32_t kind) {
+      c.records++;
+      switch (kind) {
+        case K_EXTCORR: break;
+        case K_RUNTIME: apiRecord(r, false); break;
+        case K_DRIVER: apiRecord(r, true); break;
+        case K_KERNEL: kernelRecord(r); break;
+        case K_MEMCPY: memcpyRecord(r); break;
+        case K_MEMCPY2: memcpy2Record(r); break;
+        case K_MEMSET: memsetRecord(r); break;
+        default: c.unexpected++; break;
+      }
+    });
+  }
+
+  void annotations() {  // GpuUserEventMap::logEvents, GenericActivityProfiler.cpp:320-327
+    for (auto& [key, m] : userSpans)
+      for (auto& [opId, sp] : m) {
+        Event e; e.type = T_GPU_USER_ANNOTATION;
+        e.name = tf.str(tf.ptr<uint32_t>("OPNAME")[sp.op]);
+        e.ts = sp.start; e.dur = sp.end - sp.start; e.device = sp.device; e.resource = sp.resource;
+        e.hasLinked = false; e.linkedId = 0; e.corrId = opId; e.flowId = 0; e.flowType = 0; e.flowStart = false;
+        emit(out, e);
+      }
+  }
+
+  void run() {
+    const int32_t* tm = tf.ptr<int32_t>("TIDMAP");
+    for (size_t i = 0; i < tf.count<int32_t>("TIDMAP") / 2; i++) tidMap.emplace(tm[2 * i], tm[2 * i + 1]);
+    cpuOps();
+    seg[0] = out.buf.size();
+    if (p.mode != 0) { pass1(); pass2(); }
+    seg[1] = out.buf.size();
+    if (p.mode != 0) annotations();
+    seg[2] = out.buf.size();
+  }
+};
+
+} // namespace
+
+extern "C" {
+
+// Runs the restatement over a trace container held in memory.  On success returns 0, stores a
+// malloc'd buffer with the activities text in *out (caller frees with k2j_oracle_free) and fills
+// stats[0..9] = {out bytes, cpu-op segment end, gpu segment end, X events, flow events, records,
+// out_of_range, blocklisted_runtime, invalid_external_correlation, unexpected kinds}.
+int k2j_oracle_run_file(const char* path, char** out, uint64_t* stats) {
+  try {
+    K2JTraceFile tf(path);
+    Run r(tf);
+    r.run();
+    *out = (char*)malloc(r.out.buf.size() + 1);
+    memcpy(*out, r.out.buf.data(), r.out.buf.size());
+    stats[0] = r.out.buf.size(); stats[1] = r.seg[0]; stats[2] = r.seg[1];
+    stats[3] = r.c.x_events; stats[4] = r.c.flow_events; stats[5] = r.c.records;
+    stats[6] = r.c.out_of_range; stats[7] = r.c.blocklisted_runtime; stats[8] = r.c.invalid_external_correlation;
+    stats[9] = r.c.unexpected;
+    return 0;
+  } catch (const std::exception& e) {
+    fprintf(stderr, "k2j_oracle: %s\n", e.what());
+    return 1;
+  }
+}
+void k2j_oracle_free(char* p) { free(p); }
+
+// "{}" formatting of doubles, exposed so the formatting rule can be checked in isolation.
+int k2j_oracle_fmt_double(double v, char* buf, int cap) {
+  std::string s;
+  appendFmtDouble(s, v);
+  if ((int)s.size() >= cap) return -1;
+  memcpy(buf, s.c_str(), s.size() + 1);
+  return (int)s.size();
+}
+}

@@ -1,0 +1,123 @@
+"""Shared test plumbing: run the CPU checkers (oracle/) on a synthetic trace and cut the
+"activities" part out of a Chrome-trace file."""
+from __future__ import annotations
+
+import ctypes
+import json
+import os
+import re
+import subprocess
+import tempfile
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF_DRIVER = os.path.join(ROOT, "oracle", "_ref", "ref_driver")
+PORT_LIB = os.path.join(ROOT, "oracle", "_build", "libk2j_oracle.so")
+GOLDEN = os.path.join(ROOT, "tests", "golden")
+
+_EVENT_START = b"\n  {\n"
+
+
+def have_ref() -> bool:
+    return os.path.exists(REF_DRIVER)
+
+
+def build_port():
+    if not os.path.exists(PORT_LIB) or os.path.getmtime(PORT_LIB) < os.path.getmtime(
+            os.path.join(ROOT, "oracle", "k2j_oracle.cpp")):
+        subprocess.run(["make", "-s", "-C", os.path.join(ROOT, "oracle"), "port"], check=True)
+    return PORT_LIB
+
+
+_port = None
+
+
+def port_lib():
+    global _port
+    if _port is None:
+        _port = ctypes.CDLL(build_port())
+        _port.k2j_oracle_run_file.argtypes = [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p),
+                                              ctypes.POINTER(ctypes.c_uint64)]
+        _port.k2j_oracle_free.argtypes = [ctypes.c_void_p]
+        _port.k2j_oracle_fmt_double.argtypes = [ctypes.c_double, ctypes.c_char_p, ctypes.c_int]
+    return _port
+
+
+STAT_NAMES = ["out_bytes", "ops_end", "gpu_end", "x_events", "flow_events", "records", "out_of_range",
+              "blocklisted_runtime", "invalid_external_correlation", "unexpected"]
+
+
+def run_port(trace, path=None):
+    """Runs the CPU restatement; returns (activities bytes, stats dict)."""
+    lib = port_lib()
+    with tempfile.TemporaryDirectory() as d:
+        p = path or os.path.join(d, "t.k2jt")
+        if path is None:
+            trace.write(p)
+        out = ctypes.c_void_p()
+        stats = (ctypes.c_uint64 * 10)()
+        rc = lib.k2j_oracle_run_file(p.encode(), ctypes.byref(out), stats)
+        assert rc == 0
+        data = ctypes.string_at(out, stats[0])
+        lib.k2j_oracle_free(out)
+    return data, dict(zip(STAT_NAMES, [int(x) for x in stats]))
+
+
+def port_fmt_double(v: float) -> str:
+    buf = ctypes.create_string_buffer(64)
+    n = port_lib().k2j_oracle_fmt_double(v, buf, 64)
+    assert n >= 0
+    return buf.value.decode()
+
+
+def run_ref(trace, repeat=1, path=None):
+    """Runs the unmodified reference; returns (full JSON bytes, timing dict)."""
+    with tempfile.TemporaryDirectory() as d:
+        p = path or os.path.join(d, "t.k2jt")
+        if path is None:
+            trace.write(p)
+        out = os.path.join(d, "out.json")
+        r = subprocess.run([REF_DRIVER, p, out, "--repeat", str(repeat)], capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
+        timing = json.loads(r.stdout.strip().splitlines()[-1])
+        return open(out, "rb").read(), timing
+
+
+def split_events(doc: bytes):
+    """Splits a Chrome-trace file written by the reference logger into (header, events, trailer).
+    Every event starts with "\\n  {\\n" (names and args have newlines stripped, so the marker cannot
+    occur inside an event)."""
+    first = doc.find(_EVENT_START)
+    end = doc.rfind(b"\n  ],")
+    body = doc[first:end]
+    parts = body.split(_EVENT_START)
+    assert parts[0] == b""
+    return doc[:first], [_EVENT_START + p for p in parts[1:]], doc[end:]
+
+
+_ACT = re.compile(rb'\n  \{\n    "ph": "(X|s|f)",\n    "(cat|id)": ')
+
+
+def activities_segment(doc: bytes) -> bytes:
+    """The events the device pipeline is responsible for: every X / flow event except the
+    host-written "Trace" spans."""
+    _, events, _ = split_events(doc)
+    keep = []
+    for e in events:
+        if not _ACT.match(e):
+            continue
+        if e.startswith(b'\n  {\n    "ph": "X",\n    "cat": "Trace",'):
+            continue
+        keep.append(e)
+    return b"".join(keep)
+
+
+def first_diff(a: bytes, b: bytes, ctx=120) -> str:
+    n = min(len(a), len(b))
+    aa = np.frombuffer(a[:n], np.uint8)
+    bb = np.frombuffer(b[:n], np.uint8)
+    d = np.nonzero(aa != bb)[0]
+    i = int(d[0]) if len(d) else n
+    return (f"len {len(a)} vs {len(b)}, first difference at {i}:\n--- a\n{a[max(0, i - ctx):i + ctx]!r}\n"
+            f"--- b\n{b[max(0, i - ctx):i + ctx]!r}")
