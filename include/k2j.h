@@ -1,0 +1,173 @@
+/* k2j — C ABI of the B200 trace post-processing library (libk2j.so).
+ *
+ * One context turns the raw inputs of libkineto's post-processing step into the Chrome-trace JSON
+ * text of every activity event, byte-identical to what the reference's ChromeTraceLogger writes for
+ * the same inputs.  Every entry point returns a k2j_status, never throws, never aborts.  A context
+ * is used by one thread at a time (the same contract as libkineto/src/output_json.h:62-63).
+ *
+ * Each declaration names the part of the reference it stands in for (paths relative to the
+ * reference project).  Array arguments may be host or device memory: device memory is used in
+ * place, host memory is copied to the GPU on the context's stream (asynchronously when it is
+ * pinned).  Either way the arrays must stay valid and unchanged until k2j_run returns.
+ */
+#ifndef K2J_H_
+#define K2J_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct k2j_ctx k2j_ctx;
+
+typedef enum {
+  K2J_OK = 0,
+  K2J_ERR_INVALID_ARGUMENT = 1, /* null pointer, misaligned or out-of-range table entry */
+  K2J_ERR_CUDA = 2,             /* a CUDA runtime call failed; see k2j_last_error */
+  K2J_ERR_UNSUPPORTED = 3,      /* input uses a feature this build does not implement */
+  K2J_ERR_STATE = 4,            /* call order violated (e.g. output requested before a run) */
+  K2J_ERR_DEVICE_CHECK = 5      /* a kernel's own bounds/consistency check tripped */
+} k2j_status;
+
+/* Scalars of one trace.
+ * base_time_ns        ChromeTraceBaseTime::get()             libkineto/src/output_json.h:265-279
+ * window_*            captureWindowStartTime_/EndTime_       libkineto/src/GenericActivityProfiler.cpp:329-340
+ * pid                 processId(), the "pid" of runtime rows libkineto/src/CuptiActivity.h:93-95
+ * ts_mode, conv_*     0: CUPTI timestamps are unix ns; 1: the affine TSC converter with a long-double
+ *                     scale = conv_scale_mant * 2^(conv_scale_exp-63)
+ *                                                            libkineto/src/ApproximateClock.cpp:83-90
+ * flags               K2J_FLAG_*                                                                  */
+typedef struct {
+  int64_t base_time_ns;
+  int64_t window_start_ns;
+  int64_t window_end_ns;
+  int32_t pid;
+  int32_t ts_mode;
+  int32_t flags;
+  int32_t n_devices;
+  int64_t conv_t0;
+  uint64_t conv_t0_approx;
+  uint64_t conv_scale_mant;
+  int32_t conv_scale_exp;
+  int32_t reserved;
+} k2j_params;
+
+#define K2J_FLAG_USER_ANNOTATIONS 1 /* GPU_USER_ANNOTATION selected (GenericActivityProfiler.cpp:424) */
+
+/* cudaDeviceProp fields read by blocksPerSm / warpsPerSm / computeOccupancyMetrics
+ * (libkineto/src/DeviceProperties.cpp:161-222). */
+typedef struct {
+  int32_t major, minor;
+  int32_t max_threads_per_block, max_threads_per_sm;
+  int32_t regs_per_block, regs_per_sm;
+  int32_t warp_size, num_sms;
+  uint64_t smem_per_block, smem_per_block_optin, smem_per_sm, reserved_smem_per_block;
+} k2j_device_props;
+
+/* One typed metadata entry of a CPU-side activity, in the order the activity visits them
+ * (GenericTraceActivity::visitTypedMetadata, libkineto/include/GenericTraceActivity.h:160-170). */
+typedef struct {
+  uint32_t key;   /* string id */
+  uint32_t type;  /* K2J_MD_* */
+  uint64_t value; /* int64 / uint64 / double bits / bool / string id */
+} k2j_md_entry;
+enum { K2J_MD_INT64 = 0, K2J_MD_UINT64 = 1, K2J_MD_DOUBLE = 2, K2J_MD_BOOL = 3, K2J_MD_STRING = 4, K2J_MD_RAWJSON = 5 };
+
+/* Columns of the CPU-side activities (libkineto::GenericTraceActivity fields,
+ * libkineto/include/GenericTraceActivity.h:173-192): all arrays have n_ops elements except
+ * md_off (n_ops + 1) and md (md_off[n_ops]). */
+typedef struct {
+  uint64_t n_ops;
+  const int64_t* start_ns;
+  const int64_t* end_ns;
+  const int32_t* id;        /* correlationId() */
+  const int32_t* device;    /* deviceId(): the pid column */
+  const int64_t* resource;  /* resourceId(): the tid column */
+  const int32_t* thread;    /* getThreadId() */
+  const int32_t* type;      /* libkineto::ActivityType value */
+  const uint32_t* name;     /* string id */
+  const uint32_t* flow_id;
+  const uint8_t* flow_info; /* flow.type | flow.start << 4 */
+  const uint32_t* md_off;
+  const k2j_md_entry* md;
+} k2j_ops;
+
+/* Result of a run.  The error counters mirror GenericActivityProfiler::ErrorCounts
+ * (libkineto/src/GenericActivityProfiler.h:528-535). */
+typedef struct {
+  uint64_t out_bytes;   /* total JSON bytes produced */
+  uint64_t ops_bytes;   /* bytes of the CPU-activity events (they come first) */
+  uint64_t n_records;   /* CUPTI records walked */
+  uint64_t x_events;    /* "ph": "X" events written */
+  uint64_t flow_events; /* "ph": "s"/"f" events written */
+  uint64_t out_of_range_events;
+  uint64_t blocklisted_runtime_events;
+  uint64_t invalid_external_correlation_events;
+  uint64_t unexpected_cuda_events;
+  uint64_t in_bytes;    /* CUPTI record bytes consumed */
+  uint64_t name_bytes;  /* escaped name bytes copied into events */
+  uint32_t kernel_launches; /* GPU kernels this run launched */
+  uint32_t reserved;
+  float ms_segment;     /* device time of each stage, CUDA events on the context's stream */
+  float ms_join;
+  float ms_size;
+  float ms_scan;
+  float ms_emit;
+  float ms_total;
+} k2j_result;
+
+/* Creates a context on CUDA device `device`.  `stream` is a cudaStream_t to run on, or NULL for a
+ * stream owned by the context.  No reference counterpart: the reference keeps this state in the
+ * profiler and logger objects. */
+k2j_status k2j_create(int device, void* stream, k2j_ctx** out);
+void k2j_destroy(k2j_ctx* ctx);
+/* Text of the last failure on this context. */
+const char* k2j_last_error(const k2j_ctx* ctx);
+
+/* Trace scalars and per-device properties (n_props = params->n_devices entries). */
+k2j_status k2j_set_params(k2j_ctx* ctx, const k2j_params* params, const k2j_device_props* props);
+
+/* The string pool every string id refers to: n_strings strings, string i = data[off[i], off[i+1]).
+ * Kernel names are the demangled names (libkineto/src/CuptiActivity.h:297-300); the library applies
+ * the JSON sanitising and escaping of libkineto/src/output_json.cpp:72-112 itself. */
+k2j_status k2j_set_strings(k2j_ctx* ctx, const uint64_t* off, const uint8_t* data, uint64_t n_strings);
+
+/* String ids of runtimeCbidName(cbid) / driverCbidName(cbid) per callback id
+ * (libkineto/src/cupti_strings.cpp:106-132); ids past the end render as "INVALID". */
+k2j_status k2j_set_cbid_names(k2j_ctx* ctx, const uint32_t* runtime, uint32_t n_runtime,
+                              const uint32_t* driver, uint32_t n_driver);
+
+/* (CUPTI thread id, system thread id) pairs: the resourceInfo_ lookup of
+ * CuptiActivityProfiler::handleRuntimeActivity (libkineto/src/CuptiActivityProfiler.cpp:315-319).
+ * For duplicate thread ids the first pair wins, as recordThreadInfo does. */
+k2j_status k2j_set_thread_map(k2j_ctx* ctx, const int32_t* pairs, uint32_t n_pairs);
+
+/* CPU-side activities: what GenericActivityProfiler::processCpuTrace iterates
+ * (libkineto/src/GenericActivityProfiler.cpp:234-275). */
+k2j_status k2j_set_ops(k2j_ctx* ctx, const k2j_ops* ops);
+
+/* The drained CUPTI activity buffers: what CuptiActivityApi::processActivities iterates
+ * (libkineto/src/CuptiActivityApi.cpp:235-246).  `buftab` holds (byte offset, valid bytes) per
+ * buffer, in processing order; records are packed back to back, 8-byte aligned, sized by kind.
+ * The `name` field of kernel records holds a string id. At most 32 GiB per call. */
+k2j_status k2j_set_cupti(k2j_ctx* ctx, const uint8_t* bytes, uint64_t n_bytes, const uint64_t* buftab,
+                         uint32_t n_buffers);
+
+/* Runs the pipeline: segment -> join tables -> size -> scan -> emit.  Replaces the per-record work
+ * of CuptiActivityProfiler::processGpuActivities (libkineto/src/CuptiActivityProfiler.cpp:189-220)
+ * plus ChromeTraceLogger::handleActivity (libkineto/src/output_json.cpp:837-963) for every event. */
+k2j_status k2j_run(k2j_ctx* ctx, k2j_result* result);
+
+/* Device pointer and size of the text produced by the last run (valid until the next run). */
+k2j_status k2j_output(k2j_ctx* ctx, const void** device_ptr, uint64_t* n_bytes);
+/* Copies the text to host memory (pinned memory makes the copy asynchronous up to its final wait). */
+k2j_status k2j_copy_output(k2j_ctx* ctx, void* host_dst, uint64_t capacity);
+
+/* Library version string. */
+const char* k2j_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* K2J_H_ */

@@ -1,0 +1,224 @@
+"""ctypes binding of libk2j.so (C ABI in include/k2j.h).
+
+There is no CPU implementation behind this module: if the CUDA library is missing or no GPU is
+present, constructing a `K2J` context raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+from . import tracefile as tf
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libk2j.so")
+
+STATUS = {0: "OK", 1: "INVALID_ARGUMENT", 2: "CUDA", 3: "UNSUPPORTED", 4: "STATE", 5: "DEVICE_CHECK"}
+
+
+class K2JError(RuntimeError):
+    def __init__(self, status: int, msg: str):
+        super().__init__(f"k2j: {STATUS.get(status, status)}: {msg}")
+        self.status = status
+
+
+class Params(C.Structure):
+    _fields_ = [("base_time_ns", C.c_int64), ("window_start_ns", C.c_int64), ("window_end_ns", C.c_int64),
+                ("pid", C.c_int32), ("ts_mode", C.c_int32), ("flags", C.c_int32), ("n_devices", C.c_int32),
+                ("conv_t0", C.c_int64), ("conv_t0_approx", C.c_uint64), ("conv_scale_mant", C.c_uint64),
+                ("conv_scale_exp", C.c_int32), ("reserved", C.c_int32)]
+
+
+class DeviceProps(C.Structure):
+    _fields_ = [("major", C.c_int32), ("minor", C.c_int32), ("max_threads_per_block", C.c_int32),
+                ("max_threads_per_sm", C.c_int32), ("regs_per_block", C.c_int32), ("regs_per_sm", C.c_int32),
+                ("warp_size", C.c_int32), ("num_sms", C.c_int32), ("smem_per_block", C.c_uint64),
+                ("smem_per_block_optin", C.c_uint64), ("smem_per_sm", C.c_uint64),
+                ("reserved_smem_per_block", C.c_uint64)]
+
+
+class Ops(C.Structure):
+    _fields_ = [("n_ops", C.c_uint64), ("start_ns", C.c_void_p), ("end_ns", C.c_void_p), ("id", C.c_void_p),
+                ("device", C.c_void_p), ("resource", C.c_void_p), ("thread", C.c_void_p), ("type", C.c_void_p),
+                ("name", C.c_void_p), ("flow_id", C.c_void_p), ("flow_info", C.c_void_p), ("md_off", C.c_void_p),
+                ("md", C.c_void_p)]
+
+
+class Result(C.Structure):
+    _fields_ = [("out_bytes", C.c_uint64), ("ops_bytes", C.c_uint64), ("n_records", C.c_uint64),
+                ("x_events", C.c_uint64), ("flow_events", C.c_uint64), ("out_of_range_events", C.c_uint64),
+                ("blocklisted_runtime_events", C.c_uint64), ("invalid_external_correlation_events", C.c_uint64),
+                ("unexpected_cuda_events", C.c_uint64), ("in_bytes", C.c_uint64), ("name_bytes", C.c_uint64),
+                ("kernel_launches", C.c_uint32), ("reserved", C.c_uint32), ("ms_segment", C.c_float),
+                ("ms_join", C.c_float), ("ms_size", C.c_float), ("ms_scan", C.c_float), ("ms_emit", C.c_float),
+                ("ms_total", C.c_float)]
+
+    def as_dict(self):
+        return {n: getattr(self, n) for n, _ in self._fields_ if n != "reserved"}
+
+
+EXPORTS = ["k2j_create", "k2j_destroy", "k2j_last_error", "k2j_set_params", "k2j_set_strings",
+           "k2j_set_cbid_names", "k2j_set_thread_map", "k2j_set_ops", "k2j_set_cupti", "k2j_run", "k2j_output",
+           "k2j_copy_output", "k2j_version"]
+
+_lib = None
+
+
+def load_library():
+    """Loads libk2j.so; raises if it has not been built (python -m kineto_b200.build)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(f"{LIB_PATH} is missing: build it with `python -m kineto_b200.build`")
+    lib = C.CDLL(LIB_PATH)
+    vp = C.c_void_p
+    lib.k2j_create.argtypes = [C.c_int, vp, C.POINTER(vp)]
+    lib.k2j_destroy.argtypes = [vp]
+    lib.k2j_destroy.restype = None
+    lib.k2j_last_error.argtypes = [vp]
+    lib.k2j_last_error.restype = C.c_char_p
+    lib.k2j_set_params.argtypes = [vp, C.POINTER(Params), C.POINTER(DeviceProps)]
+    lib.k2j_set_strings.argtypes = [vp, vp, vp, C.c_uint64]
+    lib.k2j_set_cbid_names.argtypes = [vp, vp, C.c_uint32, vp, C.c_uint32]
+    lib.k2j_set_thread_map.argtypes = [vp, vp, C.c_uint32]
+    lib.k2j_set_ops.argtypes = [vp, C.POINTER(Ops)]
+    lib.k2j_set_cupti.argtypes = [vp, vp, C.c_uint64, vp, C.c_uint32]
+    lib.k2j_run.argtypes = [vp, C.POINTER(Result)]
+    lib.k2j_output.argtypes = [vp, C.POINTER(vp), C.POINTER(C.c_uint64)]
+    lib.k2j_copy_output.argtypes = [vp, vp, C.c_uint64]
+    lib.k2j_version.restype = C.c_char_p
+    _lib = lib
+    return lib
+
+
+def _ptr(a):
+    """Address of a numpy array or a torch tensor (host or device)."""
+    if a is None:
+        return None
+    if isinstance(a, np.ndarray):
+        return a.ctypes.data if a.size else None
+    return a.data_ptr() if a.numel() else None  # torch tensor
+
+
+class K2J:
+    """One processing context on one GPU."""
+
+    def __init__(self, device: int = 0, stream: int | None = None):
+        self.lib = load_library()
+        h = C.c_void_p()
+        st = self.lib.k2j_create(device, C.c_void_p(stream) if stream else None, C.byref(h))
+        if st != 0:
+            raise K2JError(st, "k2j_create failed (is a CUDA device present?)")
+        self.h = h
+        self._keep = {}
+
+    def close(self):
+        if self.h:
+            self.lib.k2j_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, st):
+        if st != 0:
+            raise K2JError(st, self.lib.k2j_last_error(self.h).decode())
+
+    # -- inputs ------------------------------------------------------------------------------
+    def set_params(self, trace: tf.Trace):
+        p = trace.params[0]
+        cp = Params(int(p["base_time_ns"]), int(p["window_start_ns"]), int(p["window_end_ns"]), int(p["pid"]),
+                    int(p["ts_mode"]), int(p["flags"]), int(p["n_devices"]), int(p["conv_t0"]),
+                    int(p["conv_t0_approx"]), int(p["conv_scale_mant"]), int(p["conv_scale_exp"]), 0)
+        n = int(p["n_devices"])
+        props = (DeviceProps * max(n, 1))()
+        for i in range(n):
+            d = trace.devprops[i]
+            for name, _ in DeviceProps._fields_:
+                setattr(props[i], name, int(d[name]))
+        self._check(self.lib.k2j_set_params(self.h, C.byref(cp), props))
+
+    def set_arrays(self, a: dict, buftab: np.ndarray, tidmap: np.ndarray):
+        """`a` maps Trace attribute names to numpy arrays (host) or torch tensors (host or device)."""
+        self._keep = dict(a, buftab=buftab, tidmap=tidmap)
+        n_str = len(a["pool_off"]) - 1
+        self._check(self.lib.k2j_set_strings(self.h, _ptr(a["pool_off"]), _ptr(a["pool_data"]), n_str))
+        self._check(self.lib.k2j_set_cbid_names(self.h, _ptr(a["rt_names"]), len(a["rt_names"]), _ptr(a["dr_names"]),
+                                                len(a["dr_names"])))
+        self._check(self.lib.k2j_set_thread_map(self.h, _ptr(tidmap), len(tidmap) // 2))
+        n_ops = len(a["op_start"])
+        ops = Ops(n_ops, _ptr(a["op_start"]), _ptr(a["op_end"]), _ptr(a["op_id"]), _ptr(a["op_device"]),
+                  _ptr(a["op_resource"]), _ptr(a["op_thread"]), _ptr(a["op_type"]), _ptr(a["op_name"]),
+                  _ptr(a["op_flow"]), _ptr(a["op_flowt"]), _ptr(a["op_mdoff"]), _ptr(a["md"]))
+        self._check(self.lib.k2j_set_ops(self.h, C.byref(ops)))
+        nbytes = a["cupti"].nbytes if isinstance(a["cupti"], np.ndarray) else a["cupti"].numel()
+        self._check(self.lib.k2j_set_cupti(self.h, _ptr(a["cupti"]), nbytes, _ptr(buftab), len(buftab) // 2))
+
+    ARRAYS = ["pool_off", "pool_data", "rt_names", "dr_names", "op_start", "op_end", "op_id", "op_device",
+              "op_resource", "op_thread", "op_type", "op_name", "op_flow", "op_flowt", "op_mdoff", "md", "cupti"]
+
+    def load(self, trace: tf.Trace, arrays: dict | None = None):
+        """Stages a whole trace.  `arrays` overrides the numpy arrays of `trace` (e.g. device tensors)."""
+        self.set_params(trace)
+        a = {k: np.ascontiguousarray(getattr(trace, k)) for k in self.ARRAYS}
+        if arrays:
+            a.update(arrays)
+        self.set_arrays(a, np.ascontiguousarray(trace.buftab), np.ascontiguousarray(trace.tidmap))
+
+    # -- run ----------------------------------------------------------------------------------
+    def run(self) -> dict:
+        r = Result()
+        st = self.lib.k2j_run(self.h, C.byref(r))
+        self.result = r.as_dict()
+        self._check(st)
+        return self.result
+
+    def output_ptr(self):
+        p, n = C.c_void_p(), C.c_uint64()
+        self._check(self.lib.k2j_output(self.h, C.byref(p), C.byref(n)))
+        return p.value, n.value
+
+    def copy_output(self, dst=None) -> np.ndarray:
+        """Copies the produced text to host memory (`dst`: uint8 numpy array or pinned torch tensor)."""
+        n = self.result["out_bytes"]
+        if dst is None:
+            dst = np.empty(n, np.uint8)
+        cap = dst.nbytes if isinstance(dst, np.ndarray) else dst.numel()
+        self._check(self.lib.k2j_copy_output(self.h, _ptr(dst) or 0, cap))
+        return dst
+
+
+def device_arrays(trace: tf.Trace, device="cuda:0") -> dict:
+    """Uploads the large arrays of a trace with torch and returns them as device tensors, so a context
+    can use them in place (inputs resident in HBM)."""
+    import torch
+
+    out = {}
+    for k in K2J.ARRAYS:
+        a = np.ascontiguousarray(getattr(trace, k))
+        if a.dtype.fields is not None:  # structured (metadata entries): ship as bytes
+            a = a.view(np.uint8)
+        if a.dtype == np.uint64:
+            a = a.view(np.int64)
+        elif a.dtype == np.uint32:
+            a = a.view(np.int32)
+        out[k] = torch.from_numpy(a).to(device)
+    return out
+
+
+def process(trace: tf.Trace, device: int = 0) -> tuple[bytes, dict]:
+    """Convenience: run one trace from host arrays, return (activities text, result dict)."""
+    ctx = K2J(device)
+    try:
+        ctx.load(trace)
+        res = ctx.run()
+        out = ctx.copy_output().tobytes()
+    finally:
+        ctx.close()
+    return out, res

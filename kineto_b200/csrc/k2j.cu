@@ -1,0 +1,498 @@
+// Host side of libk2j: the C ABI of include/k2j.h over the kernels in k2j_kernels.cuh.
+// One context owns a stream, grow-only device workspaces and the staged inputs of one trace.
+#include "../../include/k2j.h"
+
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <algorithm>
+#include <string>
+#include <vector>
+
+#include "k2j_kernels.cuh"
+
+using namespace k2j;
+
+namespace {
+
+// Grow-only device allocation.
+struct DevBuf {
+  void* p = nullptr;
+  size_t cap = 0;
+  cudaError_t reserve(size_t bytes) {
+    if (bytes <= cap) return cudaSuccess;
+    if (p) cudaFree(p);
+    p = nullptr; cap = 0;
+    size_t want = bytes + bytes / 8 + 256;
+    cudaError_t e = cudaMalloc(&p, want);
+    if (e == cudaSuccess) cap = want;
+    return e;
+  }
+  void release() { if (p) cudaFree(p); p = nullptr; cap = 0; }
+  template <class T> T* as() const { return reinterpret_cast<T*>(p); }
+};
+
+// An input array: either caller-owned device memory used in place, or a staged copy of host memory.
+struct Input {
+  DevBuf own;
+  const void* dev = nullptr;
+  size_t bytes = 0;
+};
+
+}  // namespace
+
+struct k2j_ctx {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  bool own_stream = false;
+  std::string err;
+  k2j_params params{};
+  bool have_params = false;
+  std::vector<DevProps> props;
+  DevBuf d_props;
+  Input pool_off, pool_data, rt_names, dr_names, tid_keys, tid_vals, cupti;
+  Input op_start, op_end, op_id, op_device, op_resource, op_type, op_name, op_flow, op_flowt, op_mdoff, op_md;
+  uint64_t n_strings = 0, n_ops = 0, n_md = 0, cupti_bytes = 0;
+  uint32_t n_rt = 0, n_dr = 0, n_tid = 0, n_buf = 0, n_chunks = 0;
+  bool strings_dirty = true;
+  std::vector<uint64_t> h_buf_off, h_buf_valid;
+  std::vector<uint32_t> h_buf_chunk_base;
+  DevBuf d_buf_off, d_buf_valid, d_buf_chunk_base;
+  DevBuf esc_name, esc_md, esc_name_len, esc_md_len;
+  DevBuf slot_code, exit_map, chunk_entry, chunk_cnt, chunk_base, scan_sums, scan_totals;
+  DevBuf corr_tab, user_tab, op_tab, work_slot, work_ev, ev_size, ev_off, out, counters;
+  uint64_t* h_totals = nullptr;   // pinned: C_NCOL column totals, then the byte total
+  Counters* h_counters = nullptr; // pinned
+  cudaEvent_t ev[8]{};
+  uint64_t out_bytes = 0;
+  bool ran = false;
+};
+
+namespace {
+
+k2j_status fail(k2j_ctx* c, k2j_status st, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  if (c) c->err = buf;
+  return st;
+}
+#define K2J_CUDA(ctx, call)                                                                       \
+  do {                                                                                            \
+    cudaError_t _e = (call);                                                                      \
+    if (_e != cudaSuccess) return fail(ctx, K2J_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(_e)); \
+  } while (0)
+
+bool is_device_ptr(const void* p) {
+  cudaPointerAttributes a;
+  if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
+  return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+// Stages `bytes` of `src`: device memory is referenced, host memory is copied on the context stream.
+k2j_status stage(k2j_ctx* c, Input& in, const void* src, size_t bytes) {
+  in.bytes = bytes;
+  if (bytes == 0) { in.dev = nullptr; return K2J_OK; }
+  if (!src) return fail(c, K2J_ERR_INVALID_ARGUMENT, "null input array");
+  if (is_device_ptr(src)) { in.dev = src; return K2J_OK; }
+  K2J_CUDA(c, in.own.reserve(bytes));
+  K2J_CUDA(c, cudaMemcpyAsync(in.own.p, src, bytes, cudaMemcpyHostToDevice, c->stream));
+  in.dev = in.own.p;
+  return K2J_OK;
+}
+
+uint32_t pow2_at_least(uint64_t n) {
+  uint32_t p = 16;
+  while (p < n && p < (1u << 31)) p <<= 1;
+  return p;
+}
+
+struct Scan {
+  static uint32_t blocks(uint64_t n) { return (uint32_t)((n + kScanTile - 1) / kScanTile); }
+};
+
+// Exclusive scan of `cols` columns of n u32 each (column stride n) into u64; totals land in
+// totals[0..cols).  Three launches.
+k2j_status run_scan(k2j_ctx* c, const uint32_t* in, uint64_t n, uint32_t cols, uint64_t* out, uint64_t* totals, uint32_t* launches) {
+  const uint32_t nb = std::max<uint32_t>(1, Scan::blocks(n));
+  K2J_CUDA(c, c->scan_sums.reserve((size_t)nb * cols * 8));
+  uint64_t* sums = c->scan_sums.as<uint64_t>();
+  k_scan_reduce<<<dim3(nb, cols), kScanThreads, 0, c->stream>>>(in, n, n, sums, nb);
+  k_scan_sums<<<cols, kScanThreads, 0, c->stream>>>(sums, nb, totals);
+  k_scan_apply<<<dim3(nb, cols), kScanThreads, 0, c->stream>>>(in, n, n, sums, nb, out);
+  *launches += 3;
+  K2J_CUDA(c, cudaGetLastError());
+  return K2J_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* k2j_version(void) { return "k2j 0.1 (sm_100a)"; }
+
+k2j_status k2j_create(int device, void* stream, k2j_ctx** out) {
+  if (!out) return K2J_ERR_INVALID_ARGUMENT;
+  *out = nullptr;
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) { cudaGetLastError(); return K2J_ERR_CUDA; }
+  if (device < 0 || device >= n) return K2J_ERR_INVALID_ARGUMENT;
+  if (cudaSetDevice(device) != cudaSuccess) return K2J_ERR_CUDA;
+  k2j_ctx* c = new k2j_ctx();
+  c->device = device;
+  if (stream) c->stream = (cudaStream_t)stream;
+  else {
+    if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) { delete c; return K2J_ERR_CUDA; }
+    c->own_stream = true;
+  }
+  bool ok = cudaMallocHost((void**)&c->h_totals, 16 * sizeof(uint64_t)) == cudaSuccess &&
+            cudaMallocHost((void**)&c->h_counters, sizeof(Counters)) == cudaSuccess &&
+            c->counters.reserve(sizeof(Counters)) == cudaSuccess && c->scan_totals.reserve(16 * 8) == cudaSuccess;
+  for (auto& e : c->ev) ok = ok && cudaEventCreate(&e) == cudaSuccess;
+  if (!ok) { k2j_destroy(c); return K2J_ERR_CUDA; }
+  *out = c;
+  return K2J_OK;
+}
+
+void k2j_destroy(k2j_ctx* c) {
+  if (!c) return;
+  cudaSetDevice(c->device);
+  if (c->stream) cudaStreamSynchronize(c->stream);
+  for (Input* in : {&c->pool_off, &c->pool_data, &c->rt_names, &c->dr_names, &c->tid_keys, &c->tid_vals, &c->cupti,
+                    &c->op_start, &c->op_end, &c->op_id, &c->op_device, &c->op_resource, &c->op_type, &c->op_name,
+                    &c->op_flow, &c->op_flowt, &c->op_mdoff, &c->op_md})
+    in->own.release();
+  for (DevBuf* b : {&c->d_props, &c->d_buf_off, &c->d_buf_valid, &c->d_buf_chunk_base, &c->esc_name, &c->esc_md,
+                    &c->esc_name_len, &c->esc_md_len, &c->slot_code, &c->exit_map, &c->chunk_entry, &c->chunk_cnt,
+                    &c->chunk_base, &c->scan_sums, &c->scan_totals, &c->corr_tab, &c->user_tab, &c->op_tab,
+                    &c->work_slot, &c->work_ev, &c->ev_size, &c->ev_off, &c->out, &c->counters})
+    b->release();
+  if (c->h_totals) cudaFreeHost(c->h_totals);
+  if (c->h_counters) cudaFreeHost(c->h_counters);
+  for (auto& e : c->ev) if (e) cudaEventDestroy(e);
+  if (c->own_stream && c->stream) cudaStreamDestroy(c->stream);
+  delete c;
+}
+
+const char* k2j_last_error(const k2j_ctx* c) { return c ? c->err.c_str() : "null context"; }
+
+k2j_status k2j_set_params(k2j_ctx* c, const k2j_params* p, const k2j_device_props* props) {
+  if (!c) return K2J_ERR_INVALID_ARGUMENT;
+  if (!p || p->n_devices < 0 || p->n_devices > 4096 || (p->n_devices > 0 && !props))
+    return fail(c, K2J_ERR_INVALID_ARGUMENT, "bad params");
+  if (p->ts_mode != 0 && p->ts_mode != 1) return fail(c, K2J_ERR_INVALID_ARGUMENT, "ts_mode must be 0 or 1");
+  if (p->ts_mode == 1 && !(p->conv_scale_mant >> 63))
+    return fail(c, K2J_ERR_INVALID_ARGUMENT, "converter scale must be a normalised 64-bit significand");
+  K2J_CUDA(c, cudaSetDevice(c->device));
+  c->params = *p;
+  c->props.resize(p->n_devices);
+  for (int i = 0; i < p->n_devices; i++) {
+    DevProps& d = c->props[i];
+    d.major = props[i].major; d.minor = props[i].minor;
+    d.max_threads_per_block = props[i].max_threads_per_block; d.max_threads_per_sm = props[i].max_threads_per_sm;
+    d.regs_per_block = props[i].regs_per_block; d.regs_per_sm = props[i].regs_per_sm;
+    d.warp_size = props[i].warp_size; d.num_sms = props[i].num_sms;
+    d.smem_per_block = props[i].smem_per_block; d.smem_per_block_optin = props[i].smem_per_block_optin;
+    d.smem_per_sm = props[i].smem_per_sm; d.reserved_smem_per_block = props[i].reserved_smem_per_block;
+  }
+  K2J_CUDA(c, c->d_props.reserve(std::max<size_t>(1, c->props.size()) * sizeof(DevProps)));
+  if (!c->props.empty())
+    K2J_CUDA(c, cudaMemcpyAsync(c->d_props.p, c->props.data(), c->props.size() * sizeof(DevProps), cudaMemcpyHostToDevice, c->stream));
+  K2J_CUDA(c, cudaStreamSynchronize(c->stream));  // c->props may be resized by the next call
+  c->have_params = true;
+  return K2J_OK;
+}
+
+k2j_status k2j_set_strings(k2j_ctx* c, const uint64_t* off, const uint8_t* data, uint64_t n) {
+  if (!c) return K2J_ERR_INVALID_ARGUMENT;
+  if (n >= 0xFFFFFFF0ull) return fail(c, K2J_ERR_INVALID_ARGUMENT, "too many strings");
+  if (n > 0 && !off) return fail(c, K2J_ERR_INVALID_ARGUMENT, "null string offsets");
+  K2J_CUDA(c, cudaSetDevice(c->device));
+  c->n_strings = n;
+  c->strings_dirty = true;
+  uint64_t total = 0;
+  if (n > 0) {
+    if (is_device_ptr(off)) K2J_CUDA(c, cudaMemcpy(&total, off + n, 8, cudaMemcpyDeviceToHost));
+    else total = off[n];
+  }
+  k2j_status st = stage(c, c->pool_off, off, (n + 1) * 8);
+  if (st) return st;
+  st = stage(c, c->pool_data, data, total);
+  if (st) return st;
+  // closed-form capacities of the two sanitised flavours (see esc_name_pos / esc_md_pos)
+  K2J_CUDA(c, c->esc_name.reserve(2 * total + 16 * (n + 1) + 16));
+  K2J_CUDA(c, c->esc_md.reserve(total + 8 * (n + 1) + 16));
+  K2J_CUDA(c, c->esc_name_len.reserve((n + 1) * 4));
+  K2J_CUDA(c, c->esc_md_len.reserve((n + 1) * 4));
+  return K2J_OK;
+}
+
+k2j_status k2j_set_cbid_names(k2j_ctx* c, const uint32_t* rt, uint32_t n_rt, const uint32_t* dr, uint32_t n_dr) {
+  if (!c) return K2J_ERR_INVALID_ARGUMENT;
+  K2J_CUDA(c, cudaSetDevice(c->device));
+  c->n_rt = n_rt; c->n_dr = n_dr;
+  k2j_status st = stage(c, c->rt_names, rt, (size_t)n_rt * 4);
+  if (st) return st;
+  return stage(c, c->dr_names, dr, (size_t)n_dr * 4);
+}
+
+k2j_status k2j_set_thread_map(k2j_ctx* c, const int32_t* pairs, uint32_t n) {
+  if (!c) return K2J_ERR_INVALID_ARGUMENT;
+  if (n > 0 && !pairs) return fail(c, K2J_ERR_INVALID_ARGUMENT, "null thread map");
+  if (n > 0 && is_device_ptr(pairs)) return fail(c, K2J_ERR_INVALID_ARGUMENT, "thread map must be host memory");
+  K2J_CUDA(c, cudaSetDevice(c->device));
+  // first pair wins for duplicate thread ids; sorted by thread id for the device-side binary search
+  std::vector<std::pair<int32_t, int32_t>> v;
+  v.reserve(n);
+  for (uint32_t i = 0; i < n; i++) v.emplace_back(pairs[2 * i], pairs[2 * i + 1]);
+  std::stable_sort(v.begin(), v.end(), [](auto& a, auto& b) { return a.first < b.first; });
+  std::vector<int32_t> keys, vals;
+  for (auto& kv : v) if (keys.empty() || keys.back() != kv.first) { keys.push_back(kv.first); vals.push_back(kv.second); }
+  c->n_tid = (uint32_t)keys.size();
+  k2j_status st = stage(c, c->tid_keys, keys.data(), keys.size() * 4);
+  if (st) return st;
+  st = stage(c, c->tid_vals, vals.data(), vals.size() * 4);
+  if (st) return st;
+  K2J_CUDA(c, cudaStreamSynchronize(c->stream));  // the vectors above go out of scope
+  return K2J_OK;
+}
+
+k2j_status k2j_set_ops(k2j_ctx* c, const k2j_ops* o) {
+  if (!c) return K2J_ERR_INVALID_ARGUMENT;
+  if (!o) return fail(c, K2J_ERR_INVALID_ARGUMENT, "null ops");
+  if (o->n_ops >= 0x7FFFFFF0ull) return fail(c, K2J_ERR_INVALID_ARGUMENT, "too many CPU activities");
+  K2J_CUDA(c, cudaSetDevice(c->device));
+  const uint64_t n = o->n_ops;
+  c->n_ops = n;
+  uint64_t n_md = 0;
+  if (n > 0) {
+    if (!o->md_off) return fail(c, K2J_ERR_INVALID_ARGUMENT, "null md_off");
+    uint32_t last = 0;
+    if (is_device_ptr(o->md_off)) K2J_CUDA(c, cudaMemcpy(&last, o->md_off + n, 4, cudaMemcpyDeviceToHost));
+    else last = o->md_off[n];
+    n_md = last;
+  }
+  c->n_md = n_md;
+  k2j_status st;
+#define STAGE(field, src, bytes) if ((st = stage(c, c->field, src, bytes)) != K2J_OK) return st
+  STAGE(op_start, o->start_ns, n * 8); STAGE(op_end, o->end_ns, n * 8); STAGE(op_id, o->id, n * 4);
+  STAGE(op_device, o->device, n * 4); STAGE(op_resource, o->resource, n * 8); STAGE(op_type, o->type, n * 4);
+  STAGE(op_name, o->name, n * 4); STAGE(op_flow, o->flow_id, n * 4); STAGE(op_flowt, o->flow_info, n);
+  STAGE(op_mdoff, o->md_off, n ? (n + 1) * 4 : 0); STAGE(op_md, o->md, n_md * sizeof(k2j_md_entry));
+#undef STAGE
+  return K2J_OK;
+}
+
+k2j_status k2j_set_cupti(k2j_ctx* c, const uint8_t* bytes, uint64_t n_bytes, const uint64_t* buftab, uint32_t n_buf) {
+  if (!c) return K2J_ERR_INVALID_ARGUMENT;
+  if (n_bytes > (32ull << 30)) return fail(c, K2J_ERR_INVALID_ARGUMENT, "more than 32 GiB of CUPTI records in one call");
+  if (n_buf > 0 && (!buftab || !bytes)) return fail(c, K2J_ERR_INVALID_ARGUMENT, "null CUPTI buffers");
+  if (n_buf > 0 && is_device_ptr(buftab)) return fail(c, K2J_ERR_INVALID_ARGUMENT, "buffer table must be host memory");
+  K2J_CUDA(c, cudaSetDevice(c->device));
+  c->h_buf_off.clear(); c->h_buf_valid.clear(); c->h_buf_chunk_base.assign(1, 0);
+  uint64_t chunks = 0;
+  for (uint32_t b = 0; b < n_buf; b++) {
+    const uint64_t off = buftab[2 * b], valid = buftab[2 * b + 1];
+    if ((off & 7) || (valid & 7)) return fail(c, K2J_ERR_INVALID_ARGUMENT, "buffer %u: offset/size not 8-byte aligned", b);
+    if (off > n_bytes || valid > n_bytes - off) return fail(c, K2J_ERR_INVALID_ARGUMENT, "buffer %u: out of range", b);
+    if (valid == 0) continue;
+    c->h_buf_off.push_back(off); c->h_buf_valid.push_back(valid);
+    chunks += (valid + kChunkSlots * 8 - 1) / (kChunkSlots * 8);
+    if (chunks >= 0xFFFFFFF0ull) return fail(c, K2J_ERR_INVALID_ARGUMENT, "too many chunks");
+    c->h_buf_chunk_base.push_back((uint32_t)chunks);
+  }
+  c->n_buf = (uint32_t)c->h_buf_off.size();
+  c->n_chunks = (uint32_t)chunks;
+  c->cupti_bytes = n_bytes;
+  k2j_status st = stage(c, c->cupti, bytes, n_bytes);
+  if (st) return st;
+  K2J_CUDA(c, c->d_buf_off.reserve(std::max<size_t>(8, c->n_buf * 8)));
+  K2J_CUDA(c, c->d_buf_valid.reserve(std::max<size_t>(8, c->n_buf * 8)));
+  K2J_CUDA(c, c->d_buf_chunk_base.reserve((c->n_buf + 1) * 4));
+  if (c->n_buf) {
+    K2J_CUDA(c, cudaMemcpyAsync(c->d_buf_off.p, c->h_buf_off.data(), c->n_buf * 8, cudaMemcpyHostToDevice, c->stream));
+    K2J_CUDA(c, cudaMemcpyAsync(c->d_buf_valid.p, c->h_buf_valid.data(), c->n_buf * 8, cudaMemcpyHostToDevice, c->stream));
+  }
+  K2J_CUDA(c, cudaMemcpyAsync(c->d_buf_chunk_base.p, c->h_buf_chunk_base.data(), (c->n_buf + 1) * 4, cudaMemcpyHostToDevice, c->stream));
+  return K2J_OK;
+}
+
+k2j_status k2j_run(k2j_ctx* c, k2j_result* res) {
+  if (!c) return K2J_ERR_INVALID_ARGUMENT;
+  if (!res) return fail(c, K2J_ERR_INVALID_ARGUMENT, "null result");
+  if (!c->have_params) return fail(c, K2J_ERR_STATE, "k2j_set_params has not been called");
+  K2J_CUDA(c, cudaSetDevice(c->device));
+  memset(res, 0, sizeof *res);
+  c->ran = false;
+  cudaStream_t s = c->stream;
+  uint32_t launches = 0;
+
+  Dev d{};
+  d.base = c->params.base_time_ns; d.win_start = c->params.window_start_ns; d.win_end = c->params.window_end_ns;
+  d.pid = c->params.pid; d.ts_mode = c->params.ts_mode; d.flags = c->params.flags; d.n_devices = c->params.n_devices;
+  d.conv_t0 = c->params.conv_t0; d.conv_t0a = c->params.conv_t0_approx; d.conv_mant = c->params.conv_scale_mant;
+  d.conv_exp = c->params.conv_scale_exp;
+  d.props = c->d_props.as<DevProps>();
+  d.pool_off = (const uint64_t*)c->pool_off.dev; d.pool_data = (const uint8_t*)c->pool_data.dev; d.n_strings = (uint32_t)c->n_strings;
+  d.esc_name = c->esc_name.as<uint8_t>(); d.esc_md = c->esc_md.as<uint8_t>();
+  d.esc_name_len = c->esc_name_len.as<uint32_t>(); d.esc_md_len = c->esc_md_len.as<uint32_t>();
+  d.rt_names = (const uint32_t*)c->rt_names.dev; d.n_rt = c->n_rt; d.dr_names = (const uint32_t*)c->dr_names.dev; d.n_dr = c->n_dr;
+  d.tid_keys = (const int32_t*)c->tid_keys.dev; d.tid_vals = (const int32_t*)c->tid_vals.dev; d.n_tid = c->n_tid;
+  d.cupti = (const uint8_t*)c->cupti.dev; d.cupti_bytes = c->cupti_bytes;
+  d.buf_off = c->d_buf_off.as<uint64_t>(); d.buf_valid = c->d_buf_valid.as<uint64_t>();
+  d.buf_chunk_base = c->d_buf_chunk_base.as<uint32_t>(); d.n_buf = c->n_buf; d.n_chunks = c->n_chunks;
+  d.n_ops = c->n_ops;
+  d.op_start = (const int64_t*)c->op_start.dev; d.op_end = (const int64_t*)c->op_end.dev; d.op_id = (const int32_t*)c->op_id.dev;
+  d.op_device = (const int32_t*)c->op_device.dev; d.op_resource = (const int64_t*)c->op_resource.dev;
+  d.op_type = (const int32_t*)c->op_type.dev; d.op_name = (const uint32_t*)c->op_name.dev; d.op_flow = (const uint32_t*)c->op_flow.dev;
+  d.op_flowt = (const uint8_t*)c->op_flowt.dev; d.op_mdoff = (const uint32_t*)c->op_mdoff.dev; d.md = (const MdEntry*)c->op_md.dev;
+  d.counters = c->counters.as<Counters>();
+
+  K2J_CUDA(c, cudaMemsetAsync(c->counters.p, 0, sizeof(Counters), s));
+  K2J_CUDA(c, cudaEventRecord(c->ev[0], s));
+
+  // ---- string pool: sanitised copies (once per pool) ----
+  if (c->strings_dirty && c->n_strings) {
+    const uint32_t blocks = (uint32_t)((c->n_strings * 32 + 255) / 256);
+    k_escape_pool<<<blocks, 256, 0, s>>>(d);
+    launches++;
+    c->strings_dirty = false;
+  }
+
+  // ---- segmentation ----
+  const uint32_t nch = c->n_chunks;
+  const uint32_t seg_blocks = (nch + kSegWarps - 1) / kSegWarps;
+  uint64_t totals[C_NCOL] = {0};
+  if (nch) {
+    K2J_CUDA(c, c->slot_code.reserve(c->cupti_bytes / 8 + 64));
+    K2J_CUDA(c, c->exit_map.reserve((size_t)nch * 32));
+    K2J_CUDA(c, c->chunk_entry.reserve(nch));
+    K2J_CUDA(c, c->chunk_cnt.reserve((size_t)nch * C_NCOL * 4));
+    K2J_CUDA(c, c->chunk_base.reserve((size_t)nch * C_NCOL * 8));
+    d.slot_code = c->slot_code.as<uint8_t>(); d.exit_map = c->exit_map.as<uint8_t>();
+    d.chunk_entry = c->chunk_entry.as<uint8_t>(); d.chunk_cnt = c->chunk_cnt.as<uint32_t>();
+    d.chunk_base = c->chunk_base.as<uint64_t>();
+    k_seg_chunks<<<seg_blocks, kSegWarps * 32, 0, s>>>(d);
+    k_seg_compose<<<c->n_buf, 256, 0, s>>>(d);
+    k_seg_count<<<seg_blocks, kSegWarps * 32, 0, s>>>(d);
+    launches += 3;
+    K2J_CUDA(c, cudaGetLastError());
+    k2j_status st = run_scan(c, d.chunk_cnt, nch, C_NCOL, d.chunk_base, c->scan_totals.as<uint64_t>(), &launches);
+    if (st) return st;
+    K2J_CUDA(c, cudaMemcpyAsync(c->h_totals, c->scan_totals.p, C_NCOL * 8, cudaMemcpyDeviceToHost, s));
+    K2J_CUDA(c, cudaStreamSynchronize(s));
+    for (int i = 0; i < C_NCOL; i++) totals[i] = c->h_totals[i];
+  }
+  K2J_CUDA(c, cudaEventRecord(c->ev[1], s));
+
+  // ---- work lists and join tables ----
+  uint64_t pos = 0;
+  for (int cls = 0; cls < C_NCLASS; cls++) {
+    d.cls_begin[cls] = pos;
+    d.cls_count[cls] = cls == C_EXT ? 0 : totals[cls];
+    pos += (d.cls_count[cls] + 31) & ~31ull;
+  }
+  d.ops_begin = pos;
+  d.n_work = pos + c->n_ops;
+  const uint64_t n_gpu_events = totals[C_EVENTS];
+  d.n_events = c->n_ops + n_gpu_events;
+  if (d.n_events >= 0xFFFFFFF0ull) return fail(c, K2J_ERR_INVALID_ARGUMENT, "more than 2^32 events in one call");
+  K2J_CUDA(c, c->work_slot.reserve(std::max<uint64_t>(1, pos) * 4));
+  K2J_CUDA(c, c->work_ev.reserve(std::max<uint64_t>(1, pos) * 4));
+  K2J_CUDA(c, c->ev_size.reserve(std::max<uint64_t>(1, d.n_events) * 4));
+  K2J_CUDA(c, c->ev_off.reserve(std::max<uint64_t>(1, d.n_events) * 8));
+  d.work_slot = c->work_slot.as<uint32_t>(); d.work_ev = c->work_ev.as<uint32_t>();
+  d.ev_size = c->ev_size.as<uint32_t>(); d.ev_off = c->ev_off.as<uint64_t>();
+  const uint32_t corr_cap = pow2_at_least(2 * totals[C_EXT] + 2);
+  const uint32_t op_cap = pow2_at_least(2 * c->n_ops + 2);
+  K2J_CUDA(c, c->corr_tab.reserve((size_t)corr_cap * 8));
+  K2J_CUDA(c, c->user_tab.reserve((size_t)corr_cap * 8));
+  K2J_CUDA(c, c->op_tab.reserve((size_t)op_cap * 8));
+  d.corr_tab = c->corr_tab.as<unsigned long long>(); d.corr_mask = corr_cap - 1;
+  d.user_tab = c->user_tab.as<unsigned long long>(); d.user_mask = corr_cap - 1;
+  d.op_tab = c->op_tab.as<unsigned long long>(); d.op_mask = op_cap - 1;
+  K2J_CUDA(c, cudaMemsetAsync(d.corr_tab, 0, (size_t)corr_cap * 8, s));
+  K2J_CUDA(c, cudaMemsetAsync(d.user_tab, 0, (size_t)corr_cap * 8, s));
+  K2J_CUDA(c, cudaMemsetAsync(d.op_tab, 0, (size_t)op_cap * 8, s));
+  if (nch) { k_seg_write<<<seg_blocks, kSegWarps * 32, 0, s>>>(d); launches++; }
+  if (c->n_ops) { k_build_ops<<<(uint32_t)((c->n_ops + 255) / 256), 256, 0, s>>>(d); launches++; }
+  K2J_CUDA(c, cudaGetLastError());
+  K2J_CUDA(c, cudaEventRecord(c->ev[2], s));
+
+  // ---- size pass, scan, emit pass ----
+  uint64_t total_bytes = 0;
+  if (d.n_work) {
+    const uint32_t ev_blocks = (uint32_t)((d.n_work + kEventThreads - 1) / kEventThreads);
+    k_events<false><<<ev_blocks, kEventThreads, 0, s>>>(d);
+    launches++;
+    K2J_CUDA(c, cudaGetLastError());
+    K2J_CUDA(c, cudaEventRecord(c->ev[3], s));
+    k2j_status st = run_scan(c, d.ev_size, d.n_events, 1, c->ev_off.as<uint64_t>(), c->scan_totals.as<uint64_t>() + 8, &launches);
+    if (st) return st;
+    K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 8, c->scan_totals.as<uint64_t>() + 8, 8, cudaMemcpyDeviceToHost, s));
+    K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 9, c->ev_off.as<uint64_t>() + (c->n_ops ? c->n_ops : 0),
+                                n_gpu_events ? 8 : 0, cudaMemcpyDeviceToHost, s));
+    K2J_CUDA(c, cudaStreamSynchronize(s));
+    total_bytes = c->h_totals[8];
+    K2J_CUDA(c, cudaEventRecord(c->ev[4], s));
+    K2J_CUDA(c, c->out.reserve(total_bytes + 64));
+    d.out = c->out.as<uint8_t>(); d.out_cap = total_bytes;
+    if (total_bytes) { k_events<true><<<ev_blocks, kEventThreads, 0, s>>>(d); launches++; }
+    K2J_CUDA(c, cudaGetLastError());
+  } else {
+    K2J_CUDA(c, cudaEventRecord(c->ev[3], s));
+    K2J_CUDA(c, cudaEventRecord(c->ev[4], s));
+  }
+  K2J_CUDA(c, cudaEventRecord(c->ev[5], s));
+  K2J_CUDA(c, cudaMemcpyAsync(c->h_counters, c->counters.p, sizeof(Counters), cudaMemcpyDeviceToHost, s));
+  K2J_CUDA(c, cudaStreamSynchronize(s));
+
+  res->out_bytes = total_bytes;
+  res->ops_bytes = n_gpu_events ? c->h_totals[9] : total_bytes;
+  res->n_records = totals[C_EVENTS] + totals[C_EXT] + totals[C_UNEXPECTED];
+  res->x_events = c->h_counters->x_events;
+  res->flow_events = c->h_counters->flow_events;
+  res->out_of_range_events = c->h_counters->out_of_range;
+  res->blocklisted_runtime_events = c->h_counters->blocklisted_runtime;
+  res->invalid_external_correlation_events = c->h_counters->invalid_external_correlation;
+  res->unexpected_cuda_events = totals[C_UNEXPECTED];
+  res->in_bytes = 208 * totals[C_KERNEL] + 88 * totals[C_MEMCPY] + 96 * totals[C_MEMCPY2] + 88 * totals[C_MEMSET] +
+                  40 * totals[C_API] + 24 * totals[C_EXT];
+  res->name_bytes = c->h_counters->name_bytes;
+  res->kernel_launches = launches;
+  cudaEventElapsedTime(&res->ms_segment, c->ev[0], c->ev[1]);
+  cudaEventElapsedTime(&res->ms_join, c->ev[1], c->ev[2]);
+  cudaEventElapsedTime(&res->ms_size, c->ev[2], c->ev[3]);
+  cudaEventElapsedTime(&res->ms_scan, c->ev[3], c->ev[4]);
+  cudaEventElapsedTime(&res->ms_emit, c->ev[4], c->ev[5]);
+  cudaEventElapsedTime(&res->ms_total, c->ev[0], c->ev[5]);
+  c->out_bytes = total_bytes;
+  c->ran = true;
+  if (c->h_counters->device_check)
+    return fail(c, K2J_ERR_DEVICE_CHECK, "%llu device-side checks failed (string id, table or output bound)",
+                (unsigned long long)c->h_counters->device_check);
+  return K2J_OK;
+}
+
+k2j_status k2j_output(k2j_ctx* c, const void** p, uint64_t* n) {
+  if (!c || !p || !n) return K2J_ERR_INVALID_ARGUMENT;
+  if (!c->ran) return fail(c, K2J_ERR_STATE, "no completed run");
+  *p = c->out.p; *n = c->out_bytes;
+  return K2J_OK;
+}
+
+k2j_status k2j_copy_output(k2j_ctx* c, void* dst, uint64_t cap) {
+  if (!c) return K2J_ERR_INVALID_ARGUMENT;
+  if (!c->ran) return fail(c, K2J_ERR_STATE, "no completed run");
+  if (cap < c->out_bytes || (!dst && c->out_bytes)) return fail(c, K2J_ERR_INVALID_ARGUMENT, "destination too small");
+  K2J_CUDA(c, cudaSetDevice(c->device));
+  if (c->out_bytes) K2J_CUDA(c, cudaMemcpyAsync(dst, c->out.p, c->out_bytes, cudaMemcpyDeviceToHost, c->stream));
+  K2J_CUDA(c, cudaStreamSynchronize(c->stream));
+  return K2J_OK;
+}
+
+}  // extern "C"

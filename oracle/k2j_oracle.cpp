@@ -416,7 +416,7 @@ struct Run {
     float wps = bps * blockProd / 32;
     // computeOccupancyMetrics, DeviceProperties.cpp:176-222
     cudaOccResult occ{};  // zero-initialised like OccupancyMetrics' default member
-    float occupancy = 0.0f;
+    float occupancy = -1.0f;  // OccupancyMetrics default, DeviceProperties.h:54
     if (dev < (uint32_t)p.n_devices) {
       float blocksPerSm = -1.0f;
       if (smCount != 0) blocksPerSm = gridProd / static_cast<float>(smCount);
