@@ -37,7 +37,10 @@ typedef enum {
  * ts_mode, conv_*     0: CUPTI timestamps are unix ns; 1: the affine TSC converter with a long-double
  *                     scale = conv_scale_mant * 2^(conv_scale_exp-63)
  *                                                            libkineto/src/ApproximateClock.cpp:83-90
- * flags               K2J_FLAG_*                                                                  */
+ * flags               K2J_FLAG_*
+ * activity_type_mask  bit t set: CPU-side activities of libkineto::ActivityType t are logged
+ *                     (derivedConfig_->profileActivityTypes(), GenericActivityProfiler.cpp:248);
+ *                     unselected activities still take part in the join                              */
 typedef struct {
   int64_t base_time_ns;
   int64_t window_start_ns;
@@ -50,10 +53,13 @@ typedef struct {
   uint64_t conv_t0_approx;
   uint64_t conv_scale_mant;
   int32_t conv_scale_exp;
-  int32_t reserved;
+  uint32_t activity_type_mask;
 } k2j_params;
 
 #define K2J_FLAG_USER_ANNOTATIONS 1 /* GPU_USER_ANNOTATION selected (GenericActivityProfiler.cpp:424) */
+#define K2J_FLAG_PID0_OVERRIDE 4    /* CPU activities with device 0 are shown under params.pid: what
+                                       ActivityTrace::save() writes after the pid-0 override of
+                                       GenericActivityProfiler.cpp:263-271 */
 
 /* cudaDeviceProp fields read by blocksPerSm / warpsPerSm / computeOccupancyMetrics
  * (libkineto/src/DeviceProperties.cpp:161-222). */
@@ -140,7 +146,9 @@ k2j_status k2j_set_cbid_names(k2j_ctx* ctx, const uint32_t* runtime, uint32_t n_
 
 /* (CUPTI thread id, system thread id) pairs: the resourceInfo_ lookup of
  * CuptiActivityProfiler::handleRuntimeActivity (libkineto/src/CuptiActivityProfiler.cpp:315-319).
- * For duplicate thread ids the first pair wins, as recordThreadInfo does. */
+ * For duplicate thread ids the first pair wins, as recordThreadInfo does.  CPU-side activities whose
+ * device equals params.pid extend the map with (thread, resource) in order, after these pairs
+ * (libkineto/src/GenericActivityProfiler.cpp:272).  At most a few thousand distinct threads. */
 k2j_status k2j_set_thread_map(k2j_ctx* ctx, const int32_t* pairs, uint32_t n_pairs);
 
 /* CPU-side activities: what GenericActivityProfiler::processCpuTrace iterates
@@ -158,6 +166,32 @@ k2j_status k2j_set_cupti(k2j_ctx* ctx, const uint8_t* bytes, uint64_t n_bytes, c
  * of CuptiActivityProfiler::processGpuActivities (libkineto/src/CuptiActivityProfiler.cpp:189-220)
  * plus ChromeTraceLogger::handleActivity (libkineto/src/output_json.cpp:837-963) for every event. */
 k2j_status k2j_run(k2j_ctx* ctx, k2j_result* result);
+
+/* The same work in two steps, for traces sharded by contiguous record range over several GPUs (one
+ * context per GPU).  k2j_segment walks this shard's buffers and compacts its EXTERNAL_CORRELATION
+ * records (k2j_external_record, processing order).  The caller all-gathers those arrays and the CPU
+ * activity ids of all shards in shard order (NCCL) and hands the result to k2j_set_global_join, so
+ * that the correlation maps of CuptiActivityProfiler::buildProcessingState
+ * (libkineto/src/CuptiActivityProfiler.cpp:256-302) and activityMap_ cover the whole trace;
+ * `own_begin` is the index of this shard's first record in the gathered array.  k2j_emit then
+ * builds the tables and produces this shard's text.  Without k2j_set_global_join the join sees only
+ * the local shard (k2j_run = k2j_segment + k2j_emit). */
+typedef struct {
+  uint64_t external_id;
+  uint32_t correlation_id;
+  uint32_t external_kind;
+} k2j_external_record;
+typedef struct {
+  uint64_t n_records;
+  uint64_t n_external;
+  const k2j_external_record* external_records; /* device memory, n_external entries */
+  uint64_t n_ops;
+  const int32_t* op_ids;                       /* device memory, n_ops entries */
+} k2j_segment_info;
+k2j_status k2j_segment(k2j_ctx* ctx, k2j_segment_info* info);
+k2j_status k2j_set_global_join(k2j_ctx* ctx, const void* external_all, uint64_t n_external_all, uint64_t own_begin,
+                               const int32_t* op_ids_all, uint64_t n_ops_all);
+k2j_status k2j_emit(k2j_ctx* ctx, k2j_result* result);
 
 /* Device pointer and size of the text produced by the last run (valid until the next run). */
 k2j_status k2j_output(k2j_ctx* ctx, const void** device_ptr, uint64_t* n_bytes);

@@ -28,7 +28,7 @@ class Params(C.Structure):
     _fields_ = [("base_time_ns", C.c_int64), ("window_start_ns", C.c_int64), ("window_end_ns", C.c_int64),
                 ("pid", C.c_int32), ("ts_mode", C.c_int32), ("flags", C.c_int32), ("n_devices", C.c_int32),
                 ("conv_t0", C.c_int64), ("conv_t0_approx", C.c_uint64), ("conv_scale_mant", C.c_uint64),
-                ("conv_scale_exp", C.c_int32), ("reserved", C.c_int32)]
+                ("conv_scale_exp", C.c_int32), ("activity_type_mask", C.c_uint32)]
 
 
 class DeviceProps(C.Structure):
@@ -59,7 +59,12 @@ class Result(C.Structure):
         return {n: getattr(self, n) for n, _ in self._fields_ if n != "reserved"}
 
 
-EXPORTS = ["k2j_create", "k2j_destroy", "k2j_last_error", "k2j_set_params", "k2j_set_strings",
+class SegmentInfo(C.Structure):
+    _fields_ = [("n_records", C.c_uint64), ("n_external", C.c_uint64), ("external_records", C.c_void_p),
+                ("n_ops", C.c_uint64), ("op_ids", C.c_void_p)]
+
+
+EXPORTS = ["k2j_segment", "k2j_set_global_join", "k2j_emit", "k2j_create", "k2j_destroy", "k2j_last_error", "k2j_set_params", "k2j_set_strings",
            "k2j_set_cbid_names", "k2j_set_thread_map", "k2j_set_ops", "k2j_set_cupti", "k2j_run", "k2j_output",
            "k2j_copy_output", "k2j_version"]
 
@@ -87,11 +92,23 @@ def load_library():
     lib.k2j_set_ops.argtypes = [vp, C.POINTER(Ops)]
     lib.k2j_set_cupti.argtypes = [vp, vp, C.c_uint64, vp, C.c_uint32]
     lib.k2j_run.argtypes = [vp, C.POINTER(Result)]
+    lib.k2j_segment.argtypes = [vp, C.POINTER(SegmentInfo)]
+    lib.k2j_set_global_join.argtypes = [vp, vp, C.c_uint64, C.c_uint64, vp, C.c_uint64]
+    lib.k2j_emit.argtypes = [vp, C.POINTER(Result)]
     lib.k2j_output.argtypes = [vp, C.POINTER(vp), C.POINTER(C.c_uint64)]
     lib.k2j_copy_output.argtypes = [vp, vp, C.c_uint64]
     lib.k2j_version.restype = C.c_char_p
     _lib = lib
     return lib
+
+
+def activity_type_mask(mode: int, flags: int) -> int:
+    """Selected CPU-side activity types: everything when the logger is driven directly (mode 0);
+    otherwise libkineto's default selection (types 0..17), GPU_USER_ANNOTATION by flag bit 0."""
+    if mode == 0:
+        return 0xFFFFFFFF
+    m = (1 << 18) - 1
+    return m if flags & 1 else m & ~(1 << 2)
 
 
 def _ptr(a):
@@ -134,8 +151,9 @@ class K2J:
     def set_params(self, trace: tf.Trace):
         p = trace.params[0]
         cp = Params(int(p["base_time_ns"]), int(p["window_start_ns"]), int(p["window_end_ns"]), int(p["pid"]),
-                    int(p["ts_mode"]), int(p["flags"]), int(p["n_devices"]), int(p["conv_t0"]),
-                    int(p["conv_t0_approx"]), int(p["conv_scale_mant"]), int(p["conv_scale_exp"]), 0)
+                    int(p["ts_mode"]), int(p["flags"]) | (4 if int(p["mode"]) == 1 else 0), int(p["n_devices"]), int(p["conv_t0"]),
+                    int(p["conv_t0_approx"]), int(p["conv_scale_mant"]), int(p["conv_scale_exp"]),
+                    activity_type_mask(int(p["mode"]), int(p["flags"])))
         n = int(p["n_devices"])
         props = (DeviceProps * max(n, 1))()
         for i in range(n):
@@ -175,6 +193,25 @@ class K2J:
     def run(self) -> dict:
         r = Result()
         st = self.lib.k2j_run(self.h, C.byref(r))
+        self.result = r.as_dict()
+        self._check(st)
+        return self.result
+
+    def segment(self) -> SegmentInfo:
+        info = SegmentInfo()
+        self._check(self.lib.k2j_segment(self.h, C.byref(info)))
+        return info
+
+    def set_global_join(self, ext_all, n_ext_all: int, own_begin: int, op_ids_all, n_ops_all: int):
+        """`ext_all`: device tensor of 16-byte external-correlation records of all shards in shard
+        order; `op_ids_all`: device tensor of all shards' CPU-activity ids."""
+        self._keep["g_ext"], self._keep["g_ops"] = ext_all, op_ids_all
+        self._check(self.lib.k2j_set_global_join(self.h, _ptr(ext_all), n_ext_all, own_begin, _ptr(op_ids_all),
+                                                 n_ops_all))
+
+    def emit(self) -> dict:
+        r = Result()
+        st = self.lib.k2j_emit(self.h, C.byref(r))
         self.result = r.as_dict()
         self._check(st)
         return self.result

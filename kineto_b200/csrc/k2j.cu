@@ -52,8 +52,8 @@ struct k2j_ctx {
   bool have_params = false;
   std::vector<DevProps> props;
   DevBuf d_props;
-  Input pool_off, pool_data, rt_names, dr_names, tid_keys, tid_vals, cupti;
-  Input op_start, op_end, op_id, op_device, op_resource, op_type, op_name, op_flow, op_flowt, op_mdoff, op_md;
+  Input pool_off, pool_data, rt_names, dr_names, tid_pairs, cupti;
+  Input op_start, op_end, op_id, op_device, op_resource, op_thread, op_type, op_name, op_flow, op_flowt, op_mdoff, op_md;
   uint64_t n_strings = 0, n_ops = 0, n_md = 0, cupti_bytes = 0;
   uint32_t n_rt = 0, n_dr = 0, n_tid = 0, n_buf = 0, n_chunks = 0;
   bool strings_dirty = true;
@@ -62,12 +62,18 @@ struct k2j_ctx {
   DevBuf d_buf_off, d_buf_valid, d_buf_chunk_base;
   DevBuf esc_name, esc_md, esc_name_len, esc_md_len;
   DevBuf slot_code, exit_map, chunk_entry, chunk_cnt, chunk_base, scan_sums, scan_totals;
-  DevBuf corr_tab, user_tab, op_tab, work_slot, work_ev, ev_size, ev_off, out, counters;
+  DevBuf tid_tab, corr_tab, user_tab, op_tab, work_slot, work_ev, ev_size, ev_off, out, counters;
   uint64_t* h_totals = nullptr;   // pinned: C_NCOL column totals, then the byte total
   Counters* h_counters = nullptr; // pinned
   cudaEvent_t ev[8]{};
   uint64_t out_bytes = 0;
-  bool ran = false;
+  bool ran = false, segmented = false, have_global_join = false;
+  Dev d{};
+  uint64_t totals[C_NCOL] = {0};
+  uint32_t launches = 0;
+  DevBuf ext_local;
+  const void* g_ext = nullptr; uint64_t g_n_ext = 0, g_own_begin = 0;
+  const int32_t* g_op_ids = nullptr; uint64_t g_n_ops = 0;
 };
 
 namespace {
@@ -162,14 +168,14 @@ void k2j_destroy(k2j_ctx* c) {
   if (!c) return;
   cudaSetDevice(c->device);
   if (c->stream) cudaStreamSynchronize(c->stream);
-  for (Input* in : {&c->pool_off, &c->pool_data, &c->rt_names, &c->dr_names, &c->tid_keys, &c->tid_vals, &c->cupti,
+  for (Input* in : {&c->pool_off, &c->pool_data, &c->rt_names, &c->dr_names, &c->tid_pairs, &c->op_thread, &c->cupti,
                     &c->op_start, &c->op_end, &c->op_id, &c->op_device, &c->op_resource, &c->op_type, &c->op_name,
                     &c->op_flow, &c->op_flowt, &c->op_mdoff, &c->op_md})
     in->own.release();
   for (DevBuf* b : {&c->d_props, &c->d_buf_off, &c->d_buf_valid, &c->d_buf_chunk_base, &c->esc_name, &c->esc_md,
                     &c->esc_name_len, &c->esc_md_len, &c->slot_code, &c->exit_map, &c->chunk_entry, &c->chunk_cnt,
-                    &c->chunk_base, &c->scan_sums, &c->scan_totals, &c->corr_tab, &c->user_tab, &c->op_tab,
-                    &c->work_slot, &c->work_ev, &c->ev_size, &c->ev_off, &c->out, &c->counters})
+                    &c->chunk_base, &c->scan_sums, &c->scan_totals, &c->tid_tab, &c->corr_tab, &c->user_tab, &c->op_tab,
+                    &c->work_slot, &c->work_ev, &c->ev_size, &c->ev_off, &c->out, &c->counters, &c->ext_local})
     b->release();
   if (c->h_totals) cudaFreeHost(c->h_totals);
   if (c->h_counters) cudaFreeHost(c->h_counters);
@@ -245,19 +251,9 @@ k2j_status k2j_set_thread_map(k2j_ctx* c, const int32_t* pairs, uint32_t n) {
   if (n > 0 && !pairs) return fail(c, K2J_ERR_INVALID_ARGUMENT, "null thread map");
   if (n > 0 && is_device_ptr(pairs)) return fail(c, K2J_ERR_INVALID_ARGUMENT, "thread map must be host memory");
   K2J_CUDA(c, cudaSetDevice(c->device));
-  // first pair wins for duplicate thread ids; sorted by thread id for the device-side binary search
-  std::vector<std::pair<int32_t, int32_t>> v;
-  v.reserve(n);
-  for (uint32_t i = 0; i < n; i++) v.emplace_back(pairs[2 * i], pairs[2 * i + 1]);
-  std::stable_sort(v.begin(), v.end(), [](auto& a, auto& b) { return a.first < b.first; });
-  std::vector<int32_t> keys, vals;
-  for (auto& kv : v) if (keys.empty() || keys.back() != kv.first) { keys.push_back(kv.first); vals.push_back(kv.second); }
-  c->n_tid = (uint32_t)keys.size();
-  k2j_status st = stage(c, c->tid_keys, keys.data(), keys.size() * 4);
+  c->n_tid = n;
+  k2j_status st = stage(c, c->tid_pairs, pairs, (size_t)n * 8);
   if (st) return st;
-  st = stage(c, c->tid_vals, vals.data(), vals.size() * 4);
-  if (st) return st;
-  K2J_CUDA(c, cudaStreamSynchronize(c->stream));  // the vectors above go out of scope
   return K2J_OK;
 }
 
@@ -280,7 +276,8 @@ k2j_status k2j_set_ops(k2j_ctx* c, const k2j_ops* o) {
   k2j_status st;
 #define STAGE(field, src, bytes) if ((st = stage(c, c->field, src, bytes)) != K2J_OK) return st
   STAGE(op_start, o->start_ns, n * 8); STAGE(op_end, o->end_ns, n * 8); STAGE(op_id, o->id, n * 4);
-  STAGE(op_device, o->device, n * 4); STAGE(op_resource, o->resource, n * 8); STAGE(op_type, o->type, n * 4);
+  STAGE(op_device, o->device, n * 4); STAGE(op_resource, o->resource, n * 8); STAGE(op_thread, o->thread, n * 4);
+  STAGE(op_type, o->type, n * 4);
   STAGE(op_name, o->name, n * 4); STAGE(op_flow, o->flow_id, n * 4); STAGE(op_flowt, o->flow_info, n);
   STAGE(op_mdoff, o->md_off, n ? (n + 1) * 4 : 0); STAGE(op_md, o->md, n_md * sizeof(k2j_md_entry));
 #undef STAGE
@@ -321,19 +318,18 @@ k2j_status k2j_set_cupti(k2j_ctx* c, const uint8_t* bytes, uint64_t n_bytes, con
   return K2J_OK;
 }
 
-k2j_status k2j_run(k2j_ctx* c, k2j_result* res) {
+k2j_status k2j_segment(k2j_ctx* c, k2j_segment_info* info) {
   if (!c) return K2J_ERR_INVALID_ARGUMENT;
-  if (!res) return fail(c, K2J_ERR_INVALID_ARGUMENT, "null result");
   if (!c->have_params) return fail(c, K2J_ERR_STATE, "k2j_set_params has not been called");
   K2J_CUDA(c, cudaSetDevice(c->device));
-  memset(res, 0, sizeof *res);
-  c->ran = false;
+  c->ran = false; c->segmented = false; c->have_global_join = false;
   cudaStream_t s = c->stream;
-  uint32_t launches = 0;
+  c->launches = 0;
 
-  Dev d{};
+  Dev& d = c->d;
+  d = Dev{};
   d.base = c->params.base_time_ns; d.win_start = c->params.window_start_ns; d.win_end = c->params.window_end_ns;
-  d.pid = c->params.pid; d.ts_mode = c->params.ts_mode; d.flags = c->params.flags; d.n_devices = c->params.n_devices;
+  d.pid = c->params.pid; d.ts_mode = c->params.ts_mode; d.flags = c->params.flags; d.n_devices = c->params.n_devices; d.type_mask = c->params.activity_type_mask;
   d.conv_t0 = c->params.conv_t0; d.conv_t0a = c->params.conv_t0_approx; d.conv_mant = c->params.conv_scale_mant;
   d.conv_exp = c->params.conv_scale_exp;
   d.props = c->d_props.as<DevProps>();
@@ -341,13 +337,14 @@ k2j_status k2j_run(k2j_ctx* c, k2j_result* res) {
   d.esc_name = c->esc_name.as<uint8_t>(); d.esc_md = c->esc_md.as<uint8_t>();
   d.esc_name_len = c->esc_name_len.as<uint32_t>(); d.esc_md_len = c->esc_md_len.as<uint32_t>();
   d.rt_names = (const uint32_t*)c->rt_names.dev; d.n_rt = c->n_rt; d.dr_names = (const uint32_t*)c->dr_names.dev; d.n_dr = c->n_dr;
-  d.tid_keys = (const int32_t*)c->tid_keys.dev; d.tid_vals = (const int32_t*)c->tid_vals.dev; d.n_tid = c->n_tid;
+  d.tid_pairs = (const int32_t*)c->tid_pairs.dev; d.n_tid_pairs = c->n_tid;
   d.cupti = (const uint8_t*)c->cupti.dev; d.cupti_bytes = c->cupti_bytes;
   d.buf_off = c->d_buf_off.as<uint64_t>(); d.buf_valid = c->d_buf_valid.as<uint64_t>();
   d.buf_chunk_base = c->d_buf_chunk_base.as<uint32_t>(); d.n_buf = c->n_buf; d.n_chunks = c->n_chunks;
   d.n_ops = c->n_ops;
   d.op_start = (const int64_t*)c->op_start.dev; d.op_end = (const int64_t*)c->op_end.dev; d.op_id = (const int32_t*)c->op_id.dev;
   d.op_device = (const int32_t*)c->op_device.dev; d.op_resource = (const int64_t*)c->op_resource.dev;
+  d.op_thread = (const int32_t*)c->op_thread.dev;
   d.op_type = (const int32_t*)c->op_type.dev; d.op_name = (const uint32_t*)c->op_name.dev; d.op_flow = (const uint32_t*)c->op_flow.dev;
   d.op_flowt = (const uint8_t*)c->op_flowt.dev; d.op_mdoff = (const uint32_t*)c->op_mdoff.dev; d.md = (const MdEntry*)c->op_md.dev;
   d.counters = c->counters.as<Counters>();
@@ -359,14 +356,15 @@ k2j_status k2j_run(k2j_ctx* c, k2j_result* res) {
   if (c->strings_dirty && c->n_strings) {
     const uint32_t blocks = (uint32_t)((c->n_strings * 32 + 255) / 256);
     k_escape_pool<<<blocks, 256, 0, s>>>(d);
-    launches++;
+    c->launches++;
     c->strings_dirty = false;
   }
 
   // ---- segmentation ----
   const uint32_t nch = c->n_chunks;
   const uint32_t seg_blocks = (nch + kSegWarps - 1) / kSegWarps;
-  uint64_t totals[C_NCOL] = {0};
+  uint64_t* totals = c->totals;
+  for (int i = 0; i < C_NCOL; i++) totals[i] = 0;
   if (nch) {
     K2J_CUDA(c, c->slot_code.reserve(c->cupti_bytes / 8 + 64));
     K2J_CUDA(c, c->exit_map.reserve((size_t)nch * 32));
@@ -379,17 +377,16 @@ k2j_status k2j_run(k2j_ctx* c, k2j_result* res) {
     k_seg_chunks<<<seg_blocks, kSegWarps * 32, 0, s>>>(d);
     k_seg_compose<<<c->n_buf, 256, 0, s>>>(d);
     k_seg_count<<<seg_blocks, kSegWarps * 32, 0, s>>>(d);
-    launches += 3;
+    c->launches += 3;
     K2J_CUDA(c, cudaGetLastError());
-    k2j_status st = run_scan(c, d.chunk_cnt, nch, C_NCOL, d.chunk_base, c->scan_totals.as<uint64_t>(), &launches);
+    k2j_status st = run_scan(c, d.chunk_cnt, nch, C_NCOL, d.chunk_base, c->scan_totals.as<uint64_t>(), &c->launches);
     if (st) return st;
     K2J_CUDA(c, cudaMemcpyAsync(c->h_totals, c->scan_totals.p, C_NCOL * 8, cudaMemcpyDeviceToHost, s));
     K2J_CUDA(c, cudaStreamSynchronize(s));
     for (int i = 0; i < C_NCOL; i++) totals[i] = c->h_totals[i];
   }
-  K2J_CUDA(c, cudaEventRecord(c->ev[1], s));
 
-  // ---- work lists and join tables ----
+  // ---- class-sorted work lists, compacted EXTERNAL_CORRELATION records ----
   uint64_t pos = 0;
   for (int cls = 0; cls < C_NCLASS; cls++) {
     d.cls_begin[cls] = pos;
@@ -398,17 +395,70 @@ k2j_status k2j_run(k2j_ctx* c, k2j_result* res) {
   }
   d.ops_begin = pos;
   d.n_work = pos + c->n_ops;
-  const uint64_t n_gpu_events = totals[C_EVENTS];
-  d.n_events = c->n_ops + n_gpu_events;
+  d.n_events = c->n_ops + totals[C_EVENTS];
   if (d.n_events >= 0xFFFFFFF0ull) return fail(c, K2J_ERR_INVALID_ARGUMENT, "more than 2^32 events in one call");
   K2J_CUDA(c, c->work_slot.reserve(std::max<uint64_t>(1, pos) * 4));
   K2J_CUDA(c, c->work_ev.reserve(std::max<uint64_t>(1, pos) * 4));
+  K2J_CUDA(c, c->ext_local.reserve(std::max<uint64_t>(1, totals[C_EXT]) * sizeof(ExtRec)));
+  d.work_slot = c->work_slot.as<uint32_t>(); d.work_ev = c->work_ev.as<uint32_t>();
+  d.ext_local = c->ext_local.as<ExtRec>();
+  if (nch) { k_seg_write<<<seg_blocks, kSegWarps * 32, 0, s>>>(d); c->launches++; }
+  K2J_CUDA(c, cudaGetLastError());
+  K2J_CUDA(c, cudaEventRecord(c->ev[1], s));
+  c->segmented = true;
+  if (info) {
+    info->n_records = totals[C_EVENTS] + totals[C_EXT] + totals[C_UNEXPECTED];
+    info->n_external = totals[C_EXT];
+    info->external_records = reinterpret_cast<const k2j_external_record*>(d.ext_local);
+    info->n_ops = c->n_ops;
+    info->op_ids = d.op_id;
+    K2J_CUDA(c, cudaStreamSynchronize(s));  // the arrays above are complete when this returns
+  }
+  return K2J_OK;
+}
+
+k2j_status k2j_set_global_join(k2j_ctx* c, const void* ext_all, uint64_t n_ext_all, uint64_t own_begin,
+                               const int32_t* op_ids_all, uint64_t n_ops_all) {
+  if (!c) return K2J_ERR_INVALID_ARGUMENT;
+  if (!c->segmented) return fail(c, K2J_ERR_STATE, "k2j_segment has not run");
+  if ((n_ext_all && !ext_all) || (n_ops_all && !op_ids_all)) return fail(c, K2J_ERR_INVALID_ARGUMENT, "null join arrays");
+  if ((n_ext_all && !is_device_ptr(ext_all)) || (n_ops_all && !is_device_ptr(op_ids_all)))
+    return fail(c, K2J_ERR_INVALID_ARGUMENT, "gathered join arrays must be device memory");
+  if (n_ext_all >= 0xFFFFFFF0ull || n_ops_all >= 0xFFFFFFF0ull || own_begin + c->totals[C_EXT] > n_ext_all)
+    return fail(c, K2J_ERR_INVALID_ARGUMENT, "gathered join arrays out of range");
+  c->g_ext = ext_all; c->g_n_ext = n_ext_all; c->g_own_begin = own_begin;
+  c->g_op_ids = op_ids_all; c->g_n_ops = n_ops_all;
+  c->have_global_join = true;
+  return K2J_OK;
+}
+
+k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
+  if (!c) return K2J_ERR_INVALID_ARGUMENT;
+  if (!res) return fail(c, K2J_ERR_INVALID_ARGUMENT, "null result");
+  if (!c->segmented) return fail(c, K2J_ERR_STATE, "k2j_segment has not run");
+  K2J_CUDA(c, cudaSetDevice(c->device));
+  memset(res, 0, sizeof *res);
+  cudaStream_t s = c->stream;
+  Dev& d = c->d;
+  const uint64_t* totals = c->totals;
+  const uint64_t n_gpu_events = totals[C_EVENTS];
+  K2J_CUDA(c, cudaEventRecord(c->ev[6], s));
+
+  // ---- join tables ----
+  uint64_t own_begin = 0, own_end = totals[C_EXT];
+  if (c->have_global_join) {
+    d.ext_all = (const ExtRec*)c->g_ext; d.n_ext_all = c->g_n_ext;
+    d.join_op_ids = c->g_op_ids; d.n_join_ops = c->g_n_ops;
+    own_begin = c->g_own_begin; own_end = own_begin + totals[C_EXT];
+  } else {
+    d.ext_all = d.ext_local; d.n_ext_all = totals[C_EXT];
+    d.join_op_ids = d.op_id; d.n_join_ops = c->n_ops;
+  }
   K2J_CUDA(c, c->ev_size.reserve(std::max<uint64_t>(1, d.n_events) * 4));
   K2J_CUDA(c, c->ev_off.reserve(std::max<uint64_t>(1, d.n_events) * 8));
-  d.work_slot = c->work_slot.as<uint32_t>(); d.work_ev = c->work_ev.as<uint32_t>();
   d.ev_size = c->ev_size.as<uint32_t>(); d.ev_off = c->ev_off.as<uint64_t>();
-  const uint32_t corr_cap = pow2_at_least(2 * totals[C_EXT] + 2);
-  const uint32_t op_cap = pow2_at_least(2 * c->n_ops + 2);
+  const uint32_t corr_cap = pow2_at_least(2 * d.n_ext_all + 2);
+  const uint32_t op_cap = pow2_at_least(2 * d.n_join_ops + 2);
   K2J_CUDA(c, c->corr_tab.reserve((size_t)corr_cap * 8));
   K2J_CUDA(c, c->user_tab.reserve((size_t)corr_cap * 8));
   K2J_CUDA(c, c->op_tab.reserve((size_t)op_cap * 8));
@@ -418,8 +468,13 @@ k2j_status k2j_run(k2j_ctx* c, k2j_result* res) {
   K2J_CUDA(c, cudaMemsetAsync(d.corr_tab, 0, (size_t)corr_cap * 8, s));
   K2J_CUDA(c, cudaMemsetAsync(d.user_tab, 0, (size_t)corr_cap * 8, s));
   K2J_CUDA(c, cudaMemsetAsync(d.op_tab, 0, (size_t)op_cap * 8, s));
-  if (nch) { k_seg_write<<<seg_blocks, kSegWarps * 32, 0, s>>>(d); launches++; }
-  if (c->n_ops) { k_build_ops<<<(uint32_t)((c->n_ops + 255) / 256), 256, 0, s>>>(d); launches++; }
+  const uint32_t tid_cap = std::max<uint32_t>(16384, pow2_at_least(4ull * c->n_tid));
+  K2J_CUDA(c, c->tid_tab.reserve((size_t)tid_cap * 8));
+  d.tid_tab = c->tid_tab.as<unsigned long long>(); d.tid_mask = tid_cap - 1;
+  K2J_CUDA(c, cudaMemsetAsync(d.tid_tab, 0, (size_t)tid_cap * 8, s));
+  if (c->n_tid + c->n_ops) { k_build_tids<<<(uint32_t)((c->n_tid + c->n_ops + 255) / 256), 256, 0, s>>>(d); c->launches++; }
+  if (d.n_ext_all) { k_build_corr<<<(uint32_t)((d.n_ext_all + 255) / 256), 256, 0, s>>>(d, own_begin, own_end); c->launches++; }
+  if (d.n_join_ops) { k_build_ops<<<(uint32_t)((d.n_join_ops + 255) / 256), 256, 0, s>>>(d); c->launches++; }
   K2J_CUDA(c, cudaGetLastError());
   K2J_CUDA(c, cudaEventRecord(c->ev[2], s));
 
@@ -428,24 +483,26 @@ k2j_status k2j_run(k2j_ctx* c, k2j_result* res) {
   if (d.n_work) {
     const uint32_t ev_blocks = (uint32_t)((d.n_work + kEventThreads - 1) / kEventThreads);
     k_events<false><<<ev_blocks, kEventThreads, 0, s>>>(d);
-    launches++;
+    c->launches++;
     K2J_CUDA(c, cudaGetLastError());
     K2J_CUDA(c, cudaEventRecord(c->ev[3], s));
-    k2j_status st = run_scan(c, d.ev_size, d.n_events, 1, c->ev_off.as<uint64_t>(), c->scan_totals.as<uint64_t>() + 8, &launches);
+    k2j_status st = run_scan(c, d.ev_size, d.n_events, 1, c->ev_off.as<uint64_t>(), c->scan_totals.as<uint64_t>() + 8, &c->launches);
     if (st) return st;
     K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 8, c->scan_totals.as<uint64_t>() + 8, 8, cudaMemcpyDeviceToHost, s));
-    K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 9, c->ev_off.as<uint64_t>() + (c->n_ops ? c->n_ops : 0),
-                                n_gpu_events ? 8 : 0, cudaMemcpyDeviceToHost, s));
+    if (n_gpu_events)
+      K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 9, c->ev_off.as<uint64_t>() + c->n_ops, 8, cudaMemcpyDeviceToHost, s));
+    K2J_CUDA(c, cudaEventRecord(c->ev[4], s));
     K2J_CUDA(c, cudaStreamSynchronize(s));
     total_bytes = c->h_totals[8];
-    K2J_CUDA(c, cudaEventRecord(c->ev[4], s));
     K2J_CUDA(c, c->out.reserve(total_bytes + 64));
     d.out = c->out.as<uint8_t>(); d.out_cap = total_bytes;
-    if (total_bytes) { k_events<true><<<ev_blocks, kEventThreads, 0, s>>>(d); launches++; }
+    K2J_CUDA(c, cudaEventRecord(c->ev[7], s));
+    if (total_bytes) { k_events<true><<<ev_blocks, kEventThreads, 0, s>>>(d); c->launches++; }
     K2J_CUDA(c, cudaGetLastError());
   } else {
     K2J_CUDA(c, cudaEventRecord(c->ev[3], s));
     K2J_CUDA(c, cudaEventRecord(c->ev[4], s));
+    K2J_CUDA(c, cudaEventRecord(c->ev[7], s));
   }
   K2J_CUDA(c, cudaEventRecord(c->ev[5], s));
   K2J_CUDA(c, cudaMemcpyAsync(c->h_counters, c->counters.p, sizeof(Counters), cudaMemcpyDeviceToHost, s));
@@ -463,19 +520,27 @@ k2j_status k2j_run(k2j_ctx* c, k2j_result* res) {
   res->in_bytes = 208 * totals[C_KERNEL] + 88 * totals[C_MEMCPY] + 96 * totals[C_MEMCPY2] + 88 * totals[C_MEMSET] +
                   40 * totals[C_API] + 24 * totals[C_EXT];
   res->name_bytes = c->h_counters->name_bytes;
-  res->kernel_launches = launches;
+  res->kernel_launches = c->launches;
   cudaEventElapsedTime(&res->ms_segment, c->ev[0], c->ev[1]);
-  cudaEventElapsedTime(&res->ms_join, c->ev[1], c->ev[2]);
+  cudaEventElapsedTime(&res->ms_join, c->ev[6], c->ev[2]);
   cudaEventElapsedTime(&res->ms_size, c->ev[2], c->ev[3]);
   cudaEventElapsedTime(&res->ms_scan, c->ev[3], c->ev[4]);
-  cudaEventElapsedTime(&res->ms_emit, c->ev[4], c->ev[5]);
-  cudaEventElapsedTime(&res->ms_total, c->ev[0], c->ev[5]);
+  cudaEventElapsedTime(&res->ms_emit, c->ev[7], c->ev[5]);
+  res->ms_total = res->ms_segment + res->ms_join + res->ms_size + res->ms_scan + res->ms_emit;
   c->out_bytes = total_bytes;
   c->ran = true;
   if (c->h_counters->device_check)
     return fail(c, K2J_ERR_DEVICE_CHECK, "%llu device-side checks failed (string id, table or output bound)",
                 (unsigned long long)c->h_counters->device_check);
   return K2J_OK;
+}
+
+k2j_status k2j_run(k2j_ctx* c, k2j_result* res) {
+  if (!c) return K2J_ERR_INVALID_ARGUMENT;
+  if (!res) return fail(c, K2J_ERR_INVALID_ARGUMENT, "null result");
+  k2j_status st = k2j_segment(c, nullptr);
+  if (st) return st;
+  return k2j_emit(c, res);
 }
 
 k2j_status k2j_output(k2j_ctx* c, const void** p, uint64_t* n) {

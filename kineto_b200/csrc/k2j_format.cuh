@@ -348,9 +348,11 @@ K2J_HD int64_t tsc_to_ns(uint64_t t, uint64_t t0_approx, int64_t t0, uint64_t ma
   // value = sig * 2^(drop + e2 - 52 + exp - 63)
   int sh = drop + e2 - 52 + exp - 63;
   int64_t r;
-  if (sh >= 0) r = sh < 63 ? (int64_t)(sig << sh) : (int64_t)0x8000000000000000ull;
+  // sig has its top bit set, so any non-negative shift is >= 2^63: the x87 store yields the
+  // "integer indefinite" value 0x8000000000000000.
+  if (sh >= 0) r = (int64_t)0x8000000000000000ull;
   else r = (-sh) < 64 ? (int64_t)(sig >> (-sh)) : 0;
-  return r + t0;
+  return (int64_t)((uint64_t)r + (uint64_t)t0);
 }
 
 }  // namespace k2j

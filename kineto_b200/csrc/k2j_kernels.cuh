@@ -59,18 +59,19 @@ struct Counters {
 };
 
 struct MdEntry { uint32_t key, type; uint64_t value; };
+struct ExtRec { uint64_t external_id; uint32_t correlation_id; uint32_t external_kind; };
 
 struct Dev {
   // scalars
   int64_t base, win_start, win_end;
-  int32_t pid, ts_mode, flags, n_devices;
+  int32_t pid, ts_mode, flags, n_devices; uint32_t type_mask;
   int64_t conv_t0; uint64_t conv_t0a, conv_mant; int32_t conv_exp;
   const DevProps* props;
   // strings
   const uint64_t* pool_off; const uint8_t* pool_data; uint32_t n_strings;
   uint32_t* esc_name_len; uint32_t* esc_md_len; uint8_t* esc_name; uint8_t* esc_md;
   const uint32_t* rt_names; uint32_t n_rt; const uint32_t* dr_names; uint32_t n_dr;
-  const int32_t* tid_keys; const int32_t* tid_vals; uint32_t n_tid;
+  const int32_t* tid_pairs; uint32_t n_tid_pairs; unsigned long long* tid_tab; uint32_t tid_mask;
   // CUPTI bytes and segmentation
   const uint8_t* cupti; uint64_t cupti_bytes;
   const uint64_t* buf_off; const uint64_t* buf_valid; const uint32_t* buf_chunk_base; uint32_t n_buf, n_chunks;
@@ -82,8 +83,12 @@ struct Dev {
   // CPU ops
   uint64_t n_ops;
   const int64_t* op_start; const int64_t* op_end; const int32_t* op_id; const int32_t* op_device;
-  const int64_t* op_resource; const int32_t* op_type; const uint32_t* op_name; const uint32_t* op_flow;
+  const int64_t* op_resource; const int32_t* op_thread; const int32_t* op_type; const uint32_t* op_name; const uint32_t* op_flow;
   const uint8_t* op_flowt; const uint32_t* op_mdoff; const MdEntry* md;
+  // EXTERNAL_CORRELATION records in processing order, compacted: the local shard's (ext_local) and
+  // the array the tables are built from (ext_all: the same array, or all shards' arrays gathered)
+  ExtRec* ext_local; const ExtRec* ext_all; uint64_t n_ext_all;
+  const int32_t* join_op_ids; uint64_t n_join_ops;  // CPU-op ids the join sees (local or gathered)
   // join tables: 64-bit entries (key << 32 | value + 1), 0 = empty
   unsigned long long* corr_tab; uint32_t corr_mask;
   unsigned long long* user_tab; uint32_t user_mask;
@@ -96,6 +101,9 @@ struct Dev {
   Counters* counters;
 };
 
+// Flag bit 2: CPU-side activities with device 0 show under the process id (the pid-0 override of
+// GenericActivityProfiler.cpp:263-271 as seen through ActivityTrace::save()).
+__device__ __forceinline__ int32_t op_pid(const Dev& d, int32_t device) { return (device == 0 && (d.flags & 4)) ? d.pid : device; }
 __device__ __forceinline__ uint64_t esc_name_pos(const Dev& d, uint32_t id) { return ((2 * d.pool_off[id] + 7) & ~7ull) + 16ull * id; }
 __device__ __forceinline__ uint64_t esc_md_pos(const Dev& d, uint32_t id) { return ((d.pool_off[id] + 7) & ~7ull) + 8ull * id; }
 
@@ -117,6 +125,22 @@ __device__ __forceinline__ bool tab_insert(unsigned long long* tab, uint32_t mas
       if (old == 0) return true;
     }
     if ((uint32_t)(old >> 32) == key) { atomicMax(&tab[i], entry); return true; }
+    i = (i + 1) & mask;
+  }
+  return false;
+}
+// Same, but the smallest value stays (first writer wins: recordThreadInfo only inserts when the key is
+// absent, libkineto/src/GenericActivityProfiler.h:256-267).
+__device__ __forceinline__ bool tab_insert_min(unsigned long long* tab, uint32_t mask, uint32_t key, uint32_t value) {
+  const unsigned long long entry = ((unsigned long long)key << 32) | (unsigned long long)(value + 1u);
+  uint32_t i = hash32(key) & mask;
+  for (uint32_t probes = 0; probes <= mask; probes++) {
+    unsigned long long old = tab[i];
+    if (old == 0) {
+      old = atomicCAS(&tab[i], 0ull, entry);
+      if (old == 0) return true;
+    }
+    if ((uint32_t)(old >> 32) == key) { if (old > entry) atomicMin(&tab[i], entry); return true; }
     i = (i + 1) & mask;
   }
   return false;
@@ -362,13 +386,11 @@ __global__ void __launch_bounds__(kSegWarps * 32) k_seg_write(Dev d) {
     const uint64_t slot = g.slot0 + pos;
     if (cls == (uint32_t)C_EXT) {
       const uint8_t* r = d.cupti + slot * 8;
-      const uint32_t ek = *reinterpret_cast<const uint32_t*>(r + 4);
-      const uint32_t corr = *reinterpret_cast<const uint32_t*>(r + 16);
-      bool ok = true;
-      if (ek == 3u) ok = tab_insert(d.corr_tab, d.corr_mask, corr, (uint32_t)slot);
-      else if (ek == 4u) ok = tab_insert(d.user_tab, d.user_mask, corr, (uint32_t)slot);
-      else atomicAdd(&d.counters->invalid_external_correlation, 1ull);
-      if (!ok) atomicAdd(&d.counters->device_check, 1ull);
+      ExtRec e;
+      e.external_kind = *reinterpret_cast<const uint32_t*>(r + 4);
+      e.external_id = *reinterpret_cast<const uint64_t*>(r + 8);
+      e.correlation_id = *reinterpret_cast<const uint32_t*>(r + 16);
+      d.ext_local[d.chunk_base[(uint64_t)C_EXT * d.n_chunks + chunk] + s_rank[w][i]] = e;
     } else {
       const uint64_t dst = d.cls_begin[cls] + d.chunk_base[(uint64_t)cls * d.n_chunks + chunk] + s_rank[w][i];
       d.work_slot[dst] = (uint32_t)slot;
@@ -377,10 +399,38 @@ __global__ void __launch_bounds__(kSegWarps * 32) k_seg_write(Dev d) {
   }
 }
 
+// CUPTI thread id -> system thread id.  Priority order: the explicit pairs, then every CPU-side activity
+// of this process in order (processCpuTrace -> recordThreadInfo(resourceId, getThreadId, deviceId),
+// libkineto/src/GenericActivityProfiler.cpp:272); the first writer of a thread id wins.
+__global__ void k_build_tids(Dev d) {
+  const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (uint64_t)d.n_tid_pairs + d.n_ops) return;
+  uint32_t key;
+  if (i < d.n_tid_pairs) key = (uint32_t)d.tid_pairs[2 * i];
+  else {
+    const uint64_t j = i - d.n_tid_pairs;
+    if (op_pid(d, d.op_device[j]) != d.pid) return;
+    key = (uint32_t)d.op_thread[j];
+  }
+  if (!tab_insert_min(d.tid_tab, d.tid_mask, key, (uint32_t)i)) atomicAdd(&d.counters->device_check, 1ull);
+}
+// CPU-op id -> position (last writer wins): activityMap_[id] = op, GenericActivityProfiler.cpp:262.
 __global__ void k_build_ops(Dev d) {
   const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= d.n_ops) return;
-  if (!tab_insert(d.op_tab, d.op_mask, (uint32_t)d.op_id[i], (uint32_t)i)) atomicAdd(&d.counters->device_check, 1ull);
+  if (i >= d.n_join_ops) return;
+  if (!tab_insert(d.op_tab, d.op_mask, (uint32_t)d.join_op_ids[i], (uint32_t)i)) atomicAdd(&d.counters->device_check, 1ull);
+}
+// correlation id -> index of the winning EXTERNAL_CORRELATION record (handleCorrelationActivity,
+// CuptiActivityProfiler.cpp:290-302).  `count_invalid`: only the shard that owns a record counts it.
+__global__ void k_build_corr(Dev d, uint64_t own_begin, uint64_t own_end) {
+  const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= d.n_ext_all) return;
+  const ExtRec e = d.ext_all[i];
+  bool ok = true;
+  if (e.external_kind == 3u) ok = tab_insert(d.corr_tab, d.corr_mask, e.correlation_id, (uint32_t)i);
+  else if (e.external_kind == 4u) ok = tab_insert(d.user_tab, d.user_mask, e.correlation_id, (uint32_t)i);
+  else if (i >= own_begin && i < own_end) atomicAdd(&d.counters->invalid_external_correlation, 1ull);
+  if (!ok) atomicAdd(&d.counters->device_check, 1ull);
 }
 
 // ---- exclusive scan: u32 in -> u64 out, `gridDim.y` independent columns -----------------------------
@@ -545,13 +595,12 @@ __device__ __forceinline__ int64_t abs_tid(int64_t t) { return t == INT64_MIN ? 
 // never match; the external id must equal a CPU-op id exactly as a 64-bit value.
 __device__ __forceinline__ bool linked_op(const Dev& d, uint32_t corr, int32_t* op_id) {
   if (corr & 0x80000000u) return false;
-  const uint32_t slot = tab_find(d.corr_tab, d.corr_mask, corr);
-  if (slot == 0xFFFFFFFFu) return false;
-  const int64_t ext = *reinterpret_cast<const int64_t*>(d.cupti + (uint64_t)slot * 8 + 8);
+  const uint32_t idx = tab_find(d.corr_tab, d.corr_mask, corr);
+  if (idx == 0xFFFFFFFFu) return false;
+  const int64_t ext = (int64_t)d.ext_all[idx].external_id;
   if (ext != (int64_t)(int32_t)ext) return false;
-  const uint32_t row = tab_find(d.op_tab, d.op_mask, (uint32_t)(int32_t)ext);
-  if (row == 0xFFFFFFFFu) return false;
-  *op_id = d.op_id[row];
+  if (tab_find(d.op_tab, d.op_mask, (uint32_t)(int32_t)ext) == 0xFFFFFFFFu) return false;
+  *op_id = (int32_t)ext;  // the linked op's correlationId() is the key it was found under
   return true;
 }
 
@@ -619,9 +668,9 @@ template <class S> __device__ __forceinline__ bool ev_api(S& s, const Dev& d, co
   const int64_t ts = conv_ts(d, st), dur = conv_dur(d, st, en);
   if (out_of_range(d, ts, dur)) { *filt = 2; return false; }
   int32_t tid = (int32_t)b.y;
-  {  // resourceInfo_ lookup: sorted thread table
-    int lo = 0, hi = (int)d.n_tid - 1;
-    while (lo <= hi) { int mid = (lo + hi) >> 1; int32_t kx = d.tid_keys[mid]; if (kx == tid) { tid = d.tid_vals[mid]; break; } if (kx < tid) lo = mid + 1; else hi = mid - 1; }
+  {  // resourceInfo_.find({processId(), tid}), CuptiActivityProfiler.cpp:315-319
+    const uint32_t idx = tab_find(d.tid_tab, d.tid_mask, (uint32_t)tid);
+    if (idx != 0xFFFFFFFFu) tid = idx < d.n_tid_pairs ? d.tid_pairs[2 * idx + 1] : (int32_t)d.op_resource[idx - d.n_tid_pairs];
   }
   int32_t ext = 0;
   const bool has_ext = linked_op(d, corr, &ext) && ext != 0;
@@ -795,6 +844,12 @@ template <class S, int CLS> __device__ __forceinline__ bool ev_mem(S& s, const D
 // ---- CPU-side activity (ChromeTraceLogger::handleActivity for a GenericTraceActivity) ----
 template <class S> __device__ __forceinline__ bool ev_op(S& s, const Dev& d, uint64_t i, Tally& t) {
   const int32_t type = d.op_type[i];
+  if ((uint32_t)type >= 29u) { atomicAdd(&d.counters->device_check, 1ull); return false; }
+  if (!((d.type_mask >> type) & 1u)) return false;  // type not selected: joins, but is not logged
+  if (type == 9 || type == 17 || type == 26 || type == 28) {  // instant / counter events: not implemented
+    atomicAdd(&d.counters->device_check, 1ull);
+    return false;
+  }
   int64_t ts = d.op_start[i];
   int64_t dur = d.op_end[i] - ts;
   if (dur < 0) dur = 0;
@@ -806,10 +861,10 @@ template <class S> __device__ __forceinline__ bool ev_op(S& s, const Dev& d, uin
   if (!excluded) ext = d.op_id[i];
   const uint32_t m0 = d.op_mdoff[i], m1 = d.op_mdoff[i + 1];
   K2J_LIT(s, "\n  {\n    \"ph\": \"X\",\n    \"cat\": \"");
-  put_cstr(s, kTypeNames[(uint32_t)type < 29u ? type : 28]);
+  put_cstr(s, kTypeNames[type]);
   K2J_LIT(s, "\",\n    \"name\": \"");
   put_name(s, d, d.op_name[i], &t.name_bytes);
-  const int64_t pid = d.op_device[i], tid = abs_tid(d.op_resource[i]);
+  const int64_t pid = op_pid(d, d.op_device[i]), tid = abs_tid(d.op_resource[i]);
   x_mid(s, pid, tid, rel_ts(d, ts), dur);
   if (ext != 0 || m1 > m0) {
     K2J_LIT(s, ",\n    \"args\": {\n      ");

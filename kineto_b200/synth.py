@@ -312,12 +312,12 @@ _ATEN = ["aten::add", "aten::mul", "aten::mm", "aten::addmm", "aten::conv2d", "a
          "autograd::engine::evaluate_function: AddmmBackward0", "Optimizer.step#AdamW.step"]
 
 
-def _cpu_ops(rng, pool, n, starts, pid, n_threads=16, with_md=True):
-    """`n` cpu_op rows with ids 1..n on `n_threads` host threads."""
+def _cpu_ops(rng, pool, n, starts, pid, n_threads=16, with_md=True, id_base=0):
+    """`n` cpu_op rows with ids id_base+1..id_base+n on `n_threads` host threads."""
     t = tf.Trace()
     t.op_start = starts
     t.op_end = starts + rng.integers(2_000, 60_000, n)
-    t.op_id = np.arange(1, n + 1, dtype=np.int32)
+    t.op_id = np.arange(id_base + 1, id_base + n + 1, dtype=np.int32)
     t.op_device = np.full(n, pid, np.int32)
     thr = rng.integers(0, n_threads, n)
     t.op_resource = (50_000 + thr).astype(np.int64)  # system tid
@@ -332,7 +332,7 @@ def _cpu_ops(rng, pool, n, starts, pid, n_threads=16, with_md=True):
         order = md_visit_order(tuple(keys))
         dims = np.array([pool.add(s) for s in ["[[32, 64, 28, 28], [64, 64, 3, 3]]", "[[8, 1024], [1024, 4096]]",
                                                "[[], [128]]", "[[4, 16, 512, 64], [4, 16, 512, 64], []]"]], np.uint64)
-        cols = {"Sequence number": (tf.MD_INT64, np.arange(n).astype(np.uint64)),
+        cols = {"Sequence number": (tf.MD_INT64, (id_base + np.arange(n)).astype(np.uint64)),
                 "Fwd thread id": (tf.MD_INT64, (thr % 3).astype(np.uint64)),
                 "Input Dims": (tf.MD_RAWJSON, dims[rng.integers(0, len(dims), n)])}
         md = np.zeros(n * 3, tf.MD_ENTRY)
@@ -376,17 +376,30 @@ def _kernel_records(rng, n, names, starts, durs, corr, n_devices, n_streams):
 
 
 def gen_kernel_launches(n=1_000_000, seed=2, n_devices=8, n_streams=32, pool_size=4096, name_len=(20, 400),
-                        orphan_fraction=0.0, buffer_bytes=4 << 20, ts_mode=0) -> tf.Trace:
+                        orphan_fraction=0.0, buffer_bytes=4 << 20, ts_mode=0, shard=(0, 1)) -> tf.Trace:
     """`n` kernel launches: per launch one EXTERNAL_CORRELATION(CUSTOM0) record, one cudaLaunchKernel
     runtime record and one CUpti_ActivityKernel9, plus `n` CPU ops.  Kernel records carry the
-    correlation ids in a seeded permutation, so the join is not positional."""
-    rng = np.random.default_rng(seed)
+    correlation ids in a seeded permutation, so the join is not positional.
+
+    `shard=(r, w)`: the trace has w*n launches and this call returns the r-th contiguous record range
+    (n launches, n kernel records, n CPU ops).  The permutation is global, so a kernel's
+    EXTERNAL_CORRELATION record and CPU op usually live in another shard."""
+    r, w = shard
+    total = n * w
+    g = np.random.default_rng(seed)  # global draws: identical in every shard
     pool = tf.StringPool()
-    names = np.array([pool.add(s) for s in name_pool(rng, pool_size, *name_len)], np.uint64)
+    names = np.array([pool.add(s) for s in name_pool(g, pool_size, *name_len)], np.uint64)
     t0 = DEFAULT_BASE_TIME + 1_000_000_000
-    op_starts = _monotone_starts(rng, n, t0, 3000.0)
-    ops, thr = _cpu_ops(rng, pool, n, op_starts, DEFAULT_PID)
-    corr = (np.arange(n, dtype=np.int64) + 1000).astype(np.uint32)
+    op_starts_all = _monotone_starts(g, total, t0, 3000.0)
+    api_start_all = op_starts_all + g.integers(200, 1500, total)
+    perm_all = g.permutation(total)
+    kdelay_all = g.integers(3000, 200_000, total)
+    window = (t0 - 1000, int(api_start_all.max()) + 200_000 + 10_000_000_000)
+    rng = np.random.default_rng([seed, r])  # shard-local draws
+    lo, hi = r * n, (r + 1) * n
+    ops, thr = _cpu_ops(rng, pool, n, op_starts_all[lo:hi], DEFAULT_PID, id_base=lo)
+    corr_all_base = 1000
+    corr = (np.arange(lo, hi, dtype=np.int64) + corr_all_base).astype(np.uint32)
 
     ext = np.zeros(n, tf.EXTCORR)
     ext["kind"], ext["externalKind"] = tf.KIND_EXTERNAL_CORRELATION, tf.EXTERNAL_KIND_CUSTOM0
@@ -397,29 +410,59 @@ def gen_kernel_launches(n=1_000_000, seed=2, n_devices=8, n_streams=32, pool_siz
 
     api = np.zeros(n, tf.API)
     api["kind"], api["cbid"] = tf.KIND_RUNTIME, CBID_cudaLaunchKernel
-    api["start"] = op_starts + rng.integers(200, 1500, n)
+    api["start"] = api_start_all[lo:hi]
     api["end"] = api["start"] + rng.integers(1500, 9000, n)
     api["processId"], api["threadId"] = DEFAULT_PID, ops.op_thread.astype(np.uint32)
     api["correlationId"] = corr
 
-    perm = rng.permutation(n)
-    kstart = api["start"][perm].astype(np.int64) + rng.integers(3000, 200_000, n)
-    kern = _kernel_records(rng, n, names, kstart, _lognormal_dur(rng, n), corr[perm], n_devices, n_streams)
+    perm = perm_all[lo:hi]
+    kstart = api_start_all[perm].astype(np.int64) + kdelay_all[lo:hi]
+    kcorr = (perm + corr_all_base).astype(np.uint32)
+    kern = _kernel_records(rng, n, names, kstart, _lognormal_dur(rng, n), kcorr, n_devices, n_streams)
 
+    conv = None
+    if ts_mode == 1:
+        conv = tsc_converter_for(window)
+        for rec in (api, kern):
+            rec["start"], rec["end"] = ns_to_ticks(rec["start"], conv), ns_to_ticks(rec["end"], conv)
     order = np.tile(np.array([0, 1, 2], np.int8), n)
     t = ops
     t.cupti, offs = tf.interleave([ext, api, kern], order)
     t.buftab = tf.make_buftab(offs, buffer_bytes)
-    window = (t0 - 1000, int(kern["end"].max()) + 1_000_000)
-    conv = None
-    if ts_mode == 1:
-        conv = tsc_converter_for(window)
     return _finish(t, pool, 1, window, n_devices, ts_mode=ts_mode, conv=conv)
+
+
+def scale_to_x87(scale: float) -> tuple[int, int]:
+    """(64-bit significand, unbiased exponent) of `scale` as an x87 extended value."""
+    from fractions import Fraction
+    f = Fraction(scale)
+    e = 0
+    while f >= 2:
+        f /= 2
+        e += 1
+    while f < 1:
+        f *= 2
+        e -= 1
+    mant = int(f * (1 << 63))
+    return mant | (1 << 63), e
+
+
+TSC_SCALE = 0.5208333134651184  # ns per tick of a 1.92 GHz counter (exactly representable in float32)
+TSC_T0_APPROX = 123_456_789_012
 
 
 def tsc_converter_for(window):
     """Fixed converter constants (t0, t0_approx, 64-bit significand, exponent) for ts_mode 1."""
-    raise NotImplementedError
+    mant, exp = scale_to_x87(TSC_SCALE)
+    mant |= 0x5A5  # use the low significand bits a double cannot hold
+    return (int(window[0]) - 5_000_000, TSC_T0_APPROX, mant, exp)
+
+
+def ns_to_ticks(ns, conv):
+    """Inverse of the converter (to within a tick) for building ts_mode 1 traces."""
+    t0, t0a, mant, exp = conv
+    scale = mant * 2.0 ** (exp - 63)
+    return (t0a + np.round((np.asarray(ns, np.float64) - t0) / scale)).astype(np.uint64)
 
 
 def gen_mixed(n=10_000_000, seed=3, n_devices=8, n_streams=32, pool_size=50_000, name_len=(20, 400),
@@ -522,11 +565,12 @@ def gen_mixed(n=10_000_000, seed=3, n_devices=8, n_streams=32, pool_size=50_000,
     g_sorted_idx = gpu_idx[gorder]
 
     def _reorder(recs, members):
-        pos = {int(v): i for i, v in enumerate(members)} if len(members) < 0 else None
         rank = np.full(n, -1, np.int64)
         rank[members] = np.arange(len(members))
         sel = g_sorted_idx[np.isin(g_sorted_idx, members)] if len(members) else np.zeros(0, np.int64)
-        return recs[rank[sel]]
+        # index the raw bytes: field-wise copies of a padded struct dtype leave the padding undefined
+        raw = np.ascontiguousarray(recs).view(np.uint8).reshape(len(recs), -1)
+        return raw[rank[sel]].reshape(-1).view(recs.dtype)
 
     kern = _reorder(kern, ik)
     mc = _reorder(mc, im[i1])

@@ -290,6 +290,10 @@ struct Run {
       e.ts = tf.ptr<int64_t>("OPSTART")[i];
       e.dur = tf.ptr<int64_t>("OPEND")[i] - e.ts;
       e.device = tf.ptr<int32_t>("OPDEV")[i];
+      // processCpuTrace rewrites device 0 to the process id right after handing the op to the logger
+      // (GenericActivityProfiler.cpp:263-271); the in-memory logger only holds a pointer, so the file
+      // written by ActivityTrace::save() shows the rewritten value.
+      if (p.mode == 1 && e.device == 0) e.device = p.pid;
       e.resource = tf.ptr<int64_t>("OPRES")[i];
       e.hasLinked = false; e.linkedId = 0;
       e.corrId = tf.ptr<int32_t>("OPID")[i];
@@ -297,8 +301,14 @@ struct Run {
       e.flowId = tf.ptr<uint32_t>("OPFLOW")[i];
       uint8_t ft = tf.ptr<uint8_t>("OPFLOWT")[i];
       e.flowType = ft & 0xf; e.flowStart = (ft >> 4) & 1;
-      emit(out, e);
+      // processCpuTrace logs an op only if its type is selected (GenericActivityProfiler.cpp:248);
+      // the default selection is types 0..17, GPU_USER_ANNOTATION being switchable by flags bit 0.
+      const bool selected = p.mode == 0 || (e.type < 18 && (e.type != T_GPU_USER_ANNOTATION || (p.flags & 1)));
+      if (selected) emit(out, e);
       activityMap[e.corrId] = i;
+      // recordThreadInfo(resourceId, getThreadId, deviceId), GenericActivityProfiler.cpp:272: only keys
+      // of this process are ever looked up; sysTid is an int32 parameter.
+      if (e.device == p.pid) tidMap.emplace(tf.ptr<int32_t>("OPTHR")[i], (int32_t)e.resource);
     }
   }
 

@@ -1,0 +1,137 @@
+"""Named parity cases shared by the CPU and GPU test suites."""
+from __future__ import annotations
+
+import numpy as np
+
+from kineto_b200 import synth
+from kineto_b200 import tracefile as tf
+
+I64_MIN = -(1 << 63)
+
+
+def edge_trace(flags=0) -> tf.Trace:
+    """Hand-built trace that walks the reference's special cases one by one."""
+    b = synth.TraceBuilder(n_devices=2, flags=flags, buffer_bytes=1 << 20)
+    t0 = b.t0
+    b.window = (t0, t0 + 1_000_000)
+    b.thread(1001, 5001)
+    b.thread(1001, 6001)          # duplicate thread id: the first pair wins
+    b.thread(-7, -5002)           # negative system tid prints as its absolute value
+    # ---- CPU-side activities ----
+    b.op(t0 + 100, t0 + 900, 1, "aten::add", md=[("Sequence number", tf.MD_INT64, 7),
+                                                 ("Input Dims", tf.MD_RAWJSON, "[[2, 3], []]")])
+    b.op(t0 + 1000, t0 + 1900, 2, 'aten::"mul"\\x', flow_id=5, flow_type=1, flow_start=1)
+    b.op(t0 + 2000, t0 + 2100, 3, "kernel", type=synth.USER_ANNOTATION, resource=-77)
+    b.op(t0 + 2200, t0 + 2300, 0, "no external id", resource=I64_MIN, flow_id=9, flow_type=2, flow_start=0)
+    b.op(t0 + 2400, t0 + 2500, -4, "negative\nid\ttab", type=synth.PYTHON_FUNCTION, flow_id=11, flow_type=3)
+    b.op(t0 + 2600, t0 + 2600, 5, "", md=[("d1", tf.MD_DOUBLE, 1.5), ("d2", tf.MD_DOUBLE, float("inf")),
+                                          ("d3", tf.MD_DOUBLE, -0.0), ("d4", tf.MD_DOUBLE, 1e22),
+                                          ("d5", tf.MD_DOUBLE, float("nan")), ("b", tf.MD_BOOL, 1),
+                                          ("s", tf.MD_STRING, 'C:\\path\n"q"'), ("u", tf.MD_UINT64, (1 << 64) - 1),
+                                          ("i", tf.MD_INT64, I64_MIN), ("k\\ey\n", tf.MD_BOOL, 0)])
+    b.op(t0 + 2700, t0 + 2800, 6, "gpu annotation", type=synth.GPU_USER_ANNOTATION, device=0, resource=7)
+    b.op(b.base - 50, t0 + 10, 7, "starts before base time")
+    b.op(t0 + 3000, t0 + 3100, 2, "duplicate id 2: last one wins")
+    b.op(t0 + 3200, t0 + 3300, 8, "é utf8 name", type=synth.CONCURRENT_KERNEL, device=1, resource=3)
+    # ---- first buffer ----
+    b.extcorr(100, 1)
+    b.runtime(t0 + 200, t0 + 300, 100)
+    b.kernel(t0 + 500, t0 + 1500, 100, "void foo<int>(float*)", device=1, stream=9, grid=(100, 2, 1),
+             block=(256, 1, 1), regs=40, ssmem=1024, dsmem=2048, queued=t0 + 400, graph=3, graph_node=77,
+             channel=4, channel_type=2)
+    b.extcorr(101, 99)             # first writer for correlation 101 ...
+    b.extcorr(101, 2)              # ... replaced by the last writer
+    b.runtime(t0 + 1200, t0 + 1300, 101, cbid=synth.CBID_cudaMemcpyAsync)
+    b.memcpy(t0 + 1500, t0 + 2500, 101, 1 << 20)
+    b.runtime(t0 + 1400, t0 + 1450, 102, cbid=synth.CBID_cudaMemsetAsync, tid=-7 & 0xFFFFFFFF)
+    b.memset(t0 + 2600, t0 + 2700, 102, 4096, value=7)
+    b.memcpy_p2p(t0 + 2800, t0 + 2900, 103, 12345)
+    b.runtime(t0 + 3000, t0 + 3100, 104, cbid=synth.CBID_cudaGetLastError)   # blocklisted
+    b.runtime(t0 + 3000, t0 + 3100, 104, cbid=16)                            # blocklisted
+    b.runtime(t0 + 3000, t0 + 3100, 104, cbid=20, tid=4242)                  # no flow start: "f" event
+    b.runtime(t0 + 3000, t0 + 3100, 0, cbid=200)                             # correlation 0: no flow
+    b.runtime(t0 + 3000, t0 + 3100, 106, cbid=5000)                          # past the name table
+    b.driver(t0 + 3200, t0 + 3300, 105)
+    b.driver(t0 + 3200, t0 + 3300, 105, cbid=549)                            # tracked, no flow start
+    b.driver(t0 + 3200, t0 + 3300, 105, cbid=1)                              # untracked driver call
+    b.kernel(t0 + 3500, t0 + 3600, 105, "k\tbad")                            # non-printable: "unknown"
+    b.kernel(t0 + 3500, t0 + 3600, 107, "kernel")                            # legacy rename
+    b.kernel(t0 + 3500, t0 + 3600, 108, 'quo"te\\back\nslash')
+    b.kernel(t0 + 3500, t0 + 3600, 109, "del\x7f")
+    b.kernel(t0 + 3500, t0 + 3600, 110, "")
+    b.new_buffer()
+    # ---- second buffer: join and window corner cases ----
+    b.extcorr(0x80000005, 1)
+    b.kernel(t0 + 4000, t0 + 4100, 0x80000005, "corr above 2^31 never links")
+    b.extcorr(120, (1 << 32) + 1)
+    b.kernel(t0 + 4000, t0 + 4100, 120, "external id does not fit an int")
+    b.extcorr(121, 55)
+    b.kernel(t0 + 4000, t0 + 4100, 121, "external id without a CPU op")
+    b.extcorr(122, 1, ext_kind=7)                                            # invalid external kind
+    b.extcorr(123, 0)
+    b.kernel(t0 + 4000, t0 + 4100, 123, "linked op with id 0")
+    b.extcorr(124, 0xFFFFFFFFFFFFFFFC)                                       # -4 as uint64
+    b.kernel(t0 + 4000, t0 + 4100, 124, "negative external id links to op -4")
+    b.kernel(t0 - 1, t0 + 50, 125, "starts before the window")
+    b.kernel(t0 + 999_000, t0 + 1_000_001, 126, "ends after the window")
+    b.kernel(t0 + 999_000, t0 + 1_000_000, 127, "ends exactly at the window end")
+    b.runtime(t0 - 5, t0 + 5, 128)
+    b.memcpy(t0 + 5000, t0 + 5000, 129, 100)                                 # zero duration: no bandwidth
+    b.memcpy(t0 + 5000, t0 + 4990, 130, 100)                                 # negative duration
+    b.memcpy(t0 + 5000, t0 + 5003, 131, (1 << 64) - 1, copy_kind=0, src_kind=9, dst_kind=0)
+    b.memcpy(t0 + 5000, t0 + 5007, 132, 1, copy_kind=9, src_kind=7, dst_kind=6)
+    b.memset(t0 + 5000, t0 + 5003, 133, 10, memory_kind=9)
+    b.memset(t0 + 5000, t0 + 5003, 134, 10, memory_kind=0, device=5, stream=0xFFFFFFFF)
+    b.kernel(t0 + 6000, t0 + 6100, 135, "device out of range", device=2)
+    b.kernel(t0 + 6000, t0 + 6100, 136, "zero block", block=(0, 1, 1))
+    b.kernel(t0 + 6000, t0 + 6100, 137, "grid product wraps", grid=(65536, 65536, 2), block=(1024, 1, 1))
+    b.kernel(t0 + 6000, t0 + 6100, 138, "negative grid", grid=(-3, 1, 1), block=(33, 3, 1), regs=255,
+             ssmem=0x7FFFFFFF, dsmem=1)
+    b.kernel(t0 + 6000, t0 + 6100, 139, "too much smem", block=(128, 1, 1), ssmem=100_000, dsmem=200_000)
+    b.kernel(t0 + 6000, t0 + 6100, 140, "regs limited", block=(1024, 1, 1), regs=128)
+    b.kernel(t0 + 6000, t0 + 6100, 141, "big ids", queued=(1 << 64) - 1, graph=0xFFFFFFFF, graph_node=(1 << 64) - 1,
+             channel=0xFFFFFFFF, channel_type=0x7FFFFFFF, context=0xFFFFFFFF, stream=0xFFFFFFFF)
+    b.new_buffer()
+    # ---- third buffer: an unknown kind ends the walk of this buffer ----
+    b.kernel(t0 + 7000, t0 + 7100, 150, "before the unknown record")
+    b.raw_record(77, 48)
+    b.kernel(t0 + 7000, t0 + 7100, 151, "never reached")
+    b.new_buffer()
+    # ---- fourth buffer ----
+    b.kernel(t0 + 8000, t0 + 8100, 152, "after the broken buffer")
+    return b.build()
+
+
+def annotation_trace() -> tf.Trace:
+    """User annotations: CUSTOM1 correlation records extend per-(device, stream) spans."""
+    b = synth.TraceBuilder(n_devices=2, flags=tf.FLAG_USER_ANNOTATIONS)
+    t0 = b.t0
+    b.op(t0 + 100, t0 + 5000, 1, "aten::add")
+    b.op(t0 + 50, t0 + 9000, 20, "ProfilerStep#3", type=synth.USER_ANNOTATION)
+    b.op(t0 + 60, t0 + 8000, 21, 'anno "two"', type=synth.USER_ANNOTATION)
+    for i in range(12):
+        corr = 300 + i
+        b.extcorr(corr, 1)
+        b.extcorr(corr, 20 + (i % 2), ext_kind=tf.EXTERNAL_KIND_CUSTOM1)
+        b.runtime(t0 + 200 + 10 * i, t0 + 205 + 10 * i, corr)
+        b.kernel(t0 + 1000 + 100 * i, t0 + 1050 + 100 * i, corr, "k%d" % i, device=i % 2, stream=7 + (i % 3))
+    b.extcorr(400, 999, ext_kind=tf.EXTERNAL_KIND_CUSTOM1)   # annotation op unknown
+    b.memcpy(t0 + 3000, t0 + 3100, 400, 64)
+    b.extcorr(401, 20, ext_kind=tf.EXTERNAL_KIND_CUSTOM1)
+    b.memset(t0 + 10, t0 + 20, 401, 64, stream=7)            # earliest start on (0, 7)
+    b.extcorr(402, 21, ext_kind=tf.EXTERNAL_KIND_CUSTOM1)
+    b.kernel(t0 - 100, t0 + 20, 402, "out of window, no span")
+    return b.build()
+
+
+def tsc_trace(n=3000) -> tf.Trace:
+    return synth.gen_kernel_launches(n, seed=21, pool_size=64, ts_mode=1)
+
+
+CASES = {
+    "edge": edge_trace,
+    "generic_300": lambda: synth.gen_generic_kernels(300, seed=31, pool_size=40),
+    "launches_150": lambda: synth.gen_kernel_launches(150, seed=32, pool_size=50),
+    "mixed_400": lambda: synth.gen_mixed(400, seed=33, pool_size=100, escape_fraction=0.2),
+    "tsc_100": lambda: tsc_trace(100),
+}

@@ -121,3 +121,11 @@ def first_diff(a: bytes, b: bytes, ctx=120) -> str:
     i = int(d[0]) if len(d) else n
     return (f"len {len(a)} vs {len(b)}, first difference at {i}:\n--- a\n{a[max(0, i - ctx):i + ctx]!r}\n"
             f"--- b\n{b[max(0, i - ctx):i + ctx]!r}")
+
+
+def activities_span(doc: bytes) -> bytes:
+    """Fast cut for large mode-1 files: the activities are one contiguous run between the metadata
+    rows and the CPU trace span."""
+    a = doc.find(b'\n  {\n    "ph": "X",')
+    b = doc.rfind(b'\n  {\n    "ph": "X",\n    "cat": "Trace",')
+    return doc[a:b]

@@ -1,0 +1,221 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU checkers, on a real GPU."""
+import hashlib
+import os
+
+import numpy as np
+import pytest
+
+import cases
+import helpers
+from kineto_b200 import synth
+from kineto_b200 import tracefile as tf
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = sorted(f[:-5] for f in os.listdir(helpers.GOLDEN) if f.endswith(".k2jt"))
+UNSUPPORTED_ON_GPU = {"annotations"}  # user-annotation spans are produced by a later pipeline stage
+
+
+def gpu_run(trace, **kw):
+    from kineto_b200 import api
+    return api.process(trace, **kw)
+
+
+def check_counters(res, stats, trace):
+    assert res["x_events"] == stats["x_events"]
+    assert res["flow_events"] == stats["flow_events"]
+    assert res["n_records"] == stats["records"]
+    assert res["out_of_range_events"] == stats["out_of_range"]
+    assert res["blocklisted_runtime_events"] == stats["blocklisted_runtime"]
+    assert res["invalid_external_correlation_events"] == stats["invalid_external_correlation"]
+    assert res["unexpected_cuda_events"] == stats["unexpected"]
+    assert res["ops_bytes"] == stats["ops_end"]
+    assert res["kernel_launches"] > 0
+
+
+@pytest.mark.parametrize("name", [g for g in GOLDEN if g not in UNSUPPORTED_ON_GPU])
+def test_gpu_matches_reference_golden(name):
+    trace = tf.Trace.read(os.path.join(helpers.GOLDEN, name + ".k2jt"))
+    want = open(os.path.join(helpers.GOLDEN, name + ".ref.json"), "rb").read()
+    got, res = gpu_run(trace)
+    assert got == want, helpers.first_diff(want, got)
+    _, stats = helpers.run_port(trace)
+    check_counters(res, stats, trace)
+
+
+@pytest.mark.parametrize("gen", [
+    lambda: synth.gen_generic_kernels(50_000, seed=201),
+    lambda: synth.gen_kernel_launches(100_000, seed=202, pool_size=1000, orphan_fraction=0.05),
+    lambda: synth.gen_kernel_launches(30_000, seed=203, pool_size=300, shard=(2, 4)),
+    lambda: synth.gen_mixed(200_000, seed=204, pool_size=5000, escape_fraction=0.05),
+    lambda: synth.gen_mixed(50_000, seed=205, pool_size=500, buffer_bytes=4096 + 64),
+    lambda: cases.tsc_trace(40_000),
+    cases.edge_trace,
+], ids=["generic", "launches", "shard", "mixed", "mixed_small_buffers", "tsc", "edge"])
+def test_gpu_matches_port(gen):
+    trace = gen()
+    want, stats = helpers.run_port(trace)
+    got, res = gpu_run(trace)
+    assert got == want, helpers.first_diff(want, got)
+    check_counters(res, stats, trace)
+
+
+def test_device_resident_inputs_and_context_reuse():
+    """Inputs already in HBM give the same bytes as host inputs; a context can be reused."""
+    from kineto_b200 import api
+    t1 = synth.gen_mixed(30_000, seed=301, pool_size=300)
+    t2 = synth.gen_kernel_launches(8_000, seed=302, pool_size=100)
+    want1, _ = helpers.run_port(t1)
+    want2, _ = helpers.run_port(t2)
+    ctx = api.K2J(0)
+    try:
+        ctx.load(t1)
+        ctx.run()
+        assert ctx.copy_output().tobytes() == want1
+        ctx.load(t2, api.device_arrays(t2, "cuda:0"))
+        for _ in range(2):
+            ctx.run()
+            assert ctx.copy_output().tobytes() == want2
+        ctx.load(t1, api.device_arrays(t1, "cuda:0"))
+        ctx.run()
+        assert ctx.copy_output().tobytes() == want1
+    finally:
+        ctx.close()
+
+
+def test_empty_and_degenerate_inputs():
+    from kineto_b200 import api
+    b = synth.TraceBuilder()
+    out, res = api.process(b.build())                      # nothing at all
+    assert out == b"" and res["out_bytes"] == 0
+    b = synth.TraceBuilder()
+    b.op(b.t0 + 1, b.t0 + 2, 1, "only an op")
+    t = b.build()
+    assert api.process(t)[0] == helpers.run_port(t)[0]
+    b = synth.TraceBuilder()
+    b.extcorr(1, 1)                                        # records that emit nothing
+    b.runtime(b.t0 + 1, b.t0 + 2, 1, cbid=synth.CBID_cudaGetLastError)
+    t = b.build()
+    out, res = api.process(t)
+    assert out == b"" and res["blocklisted_runtime_events"] == 1
+    b = synth.TraceBuilder()
+    b.raw_record(99, 64)                                   # a buffer that starts with an unknown kind
+    t = b.build()
+    out, res = api.process(t)
+    assert out == b"" and res["unexpected_cuda_events"] == 1
+
+
+def test_error_behaviour():
+    from kineto_b200 import api
+    ctx = api.K2J(0)
+    try:
+        with pytest.raises(api.K2JError) as e:
+            ctx.run()
+        assert e.value.status == 4                         # STATE: no params yet
+        t = synth.gen_kernel_launches(100, seed=1, pool_size=10)
+        bad = t.buftab.copy()
+        bad[0] = 4                                         # misaligned buffer offset
+        ctx.set_params(t)
+        a = {k: np.ascontiguousarray(getattr(t, k)) for k in api.K2J.ARRAYS}
+        with pytest.raises(api.K2JError) as e:
+            ctx.set_arrays(a, bad, t.tidmap)
+        assert e.value.status == 1
+        bad = t.buftab.copy()
+        bad[1] = len(t.cupti) + 8                          # buffer past the end
+        with pytest.raises(api.K2JError) as e:
+            ctx.set_arrays(a, bad, t.tidmap)
+        assert e.value.status == 1
+        # string id out of range -> the kernels' own check trips, the context stays usable
+        k = t.cupti.copy()
+        k[48 + 104:48 + 112].view(np.uint64)[0] = 1 << 20  # name field of the first kernel record
+        a2 = dict(a, cupti=k)
+        ctx.set_arrays(a2, t.buftab, t.tidmap)
+        with pytest.raises(api.K2JError) as e:
+            ctx.run()
+        assert e.value.status == 5
+        # unsupported CPU activity type (instant event)
+        a3 = dict(a, op_type=np.full(len(t.op_type), 9, np.int32))
+        ctx.set_arrays(a3, t.buftab, t.tidmap)
+        with pytest.raises(api.K2JError) as e:
+            ctx.run()
+        assert e.value.status == 5
+        ctx.set_arrays(a, t.buftab, t.tidmap)
+        ctx.run()
+        assert ctx.copy_output().tobytes() == helpers.run_port(t)[0]
+    finally:
+        ctx.close()
+
+
+def test_sharded_runs_concatenate_to_the_whole():
+    """Size-independent property at the benchmark's full size: processing contiguous buffer ranges
+    separately, with the join arrays gathered from all of them, gives exactly the bytes of one run
+    over the whole trace (events are emitted in record order and depend only on the record and the
+    join)."""
+    import torch
+    from kineto_b200 import api
+    n = 1_000_000
+    t = synth.gen_kernel_launches(n, seed=2)
+    ctx = api.K2J(0)
+    try:
+        ctx.load(t, api.device_arrays(t, "cuda:0"))
+        res = ctx.run()
+        assert res["x_events"] == 3 * n and res["flow_events"] == 2 * n and res["n_records"] == 3 * n
+        whole = ctx.copy_output()
+        h_whole = hashlib.sha256(whole.tobytes()).hexdigest()
+        # closed-form check of the first events against the CPU checker on a prefix of the trace
+        nb = t.n_buffers
+        parts = []
+        bt = t.buftab.reshape(-1, 2)
+        cuts = [0, nb // 3, 2 * nb // 3, nb]
+        op_cuts = [0, n // 4, n // 2, n]
+        infos = []
+        ctxs = [api.K2J(0) for _ in range(3)]
+        try:
+            for i, c in enumerate(ctxs):
+                sub = tf.Trace(**{attr: getattr(t, attr) for _, attr, _ in tf._SECTIONS})
+                sub.buftab = bt[cuts[i]:cuts[i + 1]].reshape(-1).copy()
+                lo, hi = op_cuts[i], op_cuts[i + 1]
+                for col in ("op_start", "op_end", "op_id", "op_device", "op_resource", "op_thread", "op_type", "op_name",
+                            "op_flow", "op_flowt"):
+                    setattr(sub, col, getattr(t, col)[lo:hi].copy())
+                mo = t.op_mdoff[lo:hi + 1]
+                sub.md = t.md[mo[0]:mo[-1]].copy()
+                sub.op_mdoff = (mo - mo[0]).astype(np.uint32)
+                c.load(sub)
+                infos.append(c.segment())
+            def view(ptr, n_items, ts):
+                class M:
+                    pass
+                m = M()
+                m.__cuda_array_interface__ = {"shape": (n_items,), "typestr": ts, "data": (ptr, True), "version": 2}
+                return torch.as_tensor(m, device="cuda:0").clone()
+            ext = torch.cat([view(i.external_records, int(i.n_external) * 2, "<i8") for i in infos])
+            ops = torch.cat([view(i.op_ids, int(i.n_ops), "<i4") for i in infos])
+            begin = 0
+            for c, i in zip(ctxs, infos):
+                c.set_global_join(ext, ext.numel() // 2, begin, ops, ops.numel())
+                begin += int(i.n_external)
+                c.emit()
+                parts.append(c.copy_output().tobytes())
+        finally:
+            for c in ctxs:
+                c.close()
+        ops_parts = [p[:c_res] for p, c_res in zip(parts, [None] * 3)]
+        del ops_parts
+        # CPU-op events come first in every shard: reorder to [all ops][all gpu events]
+        ops_txt = b"".join(p[:c.result["ops_bytes"]] for p, c in zip(parts, ctxs))
+        gpu_txt = b"".join(p[c.result["ops_bytes"]:] for p, c in zip(parts, ctxs))
+        assert hashlib.sha256(ops_txt + gpu_txt).hexdigest() == h_whole
+    finally:
+        ctx.close()
+
+
+@pytest.mark.skipif(not helpers.have_ref(), reason="reference build (oracle/_ref) not present")
+def test_full_size_against_reference():
+    """The benchmark workload at a quarter of its size, byte for byte against the unmodified reference."""
+    t = synth.gen_kernel_launches(250_000, seed=2)
+    doc, _ = helpers.run_ref(t)
+    want = helpers.activities_span(doc)
+    got, res = gpu_run(t)
+    assert len(got) == len(want)
+    assert got == want, helpers.first_diff(want, got)

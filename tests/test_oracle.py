@@ -1,0 +1,76 @@
+"""CPU checks of the oracle itself: the restatement (oracle/k2j_oracle.cpp) against the committed
+reference outputs, and — where the reference build is present — against the live reference."""
+import os
+
+import pytest
+
+import cases
+import helpers
+from kineto_b200 import synth
+from kineto_b200 import tracefile as tf
+
+GOLDEN = sorted(f[:-5] for f in os.listdir(helpers.GOLDEN) if f.endswith(".k2jt"))
+
+
+@pytest.mark.parametrize("name", GOLDEN)
+def test_port_matches_golden(name):
+    path = os.path.join(helpers.GOLDEN, name + ".k2jt")
+    want = open(os.path.join(helpers.GOLDEN, name + ".ref.json"), "rb").read()
+    got, stats = helpers.run_port(None, path=path)
+    assert got == want, helpers.first_diff(want, got)
+    assert stats["out_bytes"] == len(want)
+
+
+@pytest.mark.parametrize("name", GOLDEN)
+def test_golden_container_is_reproducible(name):
+    """The committed containers are exactly what the seeded generators produce today."""
+    gen = dict(cases.CASES, annotations=cases.annotation_trace)[name]
+    want = tf.Trace.read(os.path.join(helpers.GOLDEN, name + ".k2jt"))
+    got = gen()
+    for _, attr, _ in tf._SECTIONS:
+        a, b = getattr(want, attr), getattr(got, attr)
+        assert a.tobytes() == b.tobytes(), attr
+
+
+@pytest.mark.skipif(not helpers.have_ref(), reason="reference build (oracle/_ref) not present")
+@pytest.mark.parametrize("gen", [
+    lambda: synth.gen_generic_kernels(4000, seed=101),
+    lambda: synth.gen_kernel_launches(3000, seed=102, pool_size=200, orphan_fraction=0.1),
+    lambda: synth.gen_kernel_launches(1500, seed=103, pool_size=80, shard=(1, 3)),
+    lambda: synth.gen_mixed(6000, seed=104, pool_size=400, escape_fraction=0.1),
+    lambda: cases.tsc_trace(2000),
+    cases.edge_trace,
+    lambda: cases.edge_trace(flags=1),
+    cases.annotation_trace,
+], ids=["generic", "launches", "shard", "mixed", "tsc", "edge", "edge_annot", "annotations"])
+def test_port_matches_live_reference(gen):
+    trace = gen()
+    doc, _ = helpers.run_ref(trace)
+    want = helpers.activities_segment(doc)
+    got, stats = helpers.run_port(trace)
+    assert got == want, helpers.first_diff(want, got)
+
+
+def test_reference_known_answers_in_port_output():
+    """Known-answer strings the reference's own tests pin (libkineto/test/CuptiActivityProfilerTest.cpp:564-582,
+    libkineto/test/OutputJsonTest.cpp:145-152, libkineto/test/TypedMetadataTest.cpp:164-178)."""
+    b = synth.TraceBuilder()
+    t0 = b.t0
+    b.op(t0 + 10, t0 + 20, 1, 'op "quoted"', md=[("count", tf.MD_INT64, 5), ("ratio", tf.MD_DOUBLE, 1.5),
+                                                 ("big", tf.MD_UINT64, 18446744073709551615)])
+    b.runtime(t0 + 30, t0 + 40, 7, cbid=synth.CBID_cudaMemcpy)
+    b.memcpy(t0 + 50, t0 + 60, 7, 128, copy_kind=1, src_kind=2, dst_kind=3)
+    b.kernel(t0 + 70, t0 + 80, 8, "kernel")
+    out, _ = helpers.run_port(b.build())
+    assert b'"name": "op \\"quoted\\""' in out
+    assert b'"count": 5' in out and b'"ratio": 1.5' in out and b'"big": 18446744073709551615' in out
+    assert b'"name": "Memcpy HtoD (Pinned -> Device)"' in out
+    assert b'"name": "cudaMemcpy"' in out
+    assert b'"name": "Kernel"' in out
+
+
+def test_port_double_formatting_known_answers():
+    for v, s in [(2.0, "2"), (1e16, "1e+16"), (1e-5, "1e-05"), (174.76266666666666, "174.76266666666666"),
+                 (1.5, "1.5"), (0.1, "0.1"), (1e15, "1000000000000000"), (1e-4, "0.0001"), (123456.789, "123456.789"),
+                 (5e-324, "5e-324"), (1.7976931348623157e308, "1.7976931348623157e+308"), (-0.0, "-0")]:
+        assert helpers.port_fmt_double(v) == s
