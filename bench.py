@@ -317,20 +317,13 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-class _DeviceMemory:
-    """Exposes a raw device address through __cuda_array_interface__ so torch can view it."""
-
-    def __init__(self, ptr, n, typestr):
-        self.__cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (ptr, True), "version": 2}
-
-
 def _wrap(ptr, n, dtype, dev, pad_to):
     """Copies `n` elements at device address `ptr` into a fresh tensor padded to `pad_to` elements."""
     import torch
+    from kineto_b200 import api
     out = torch.zeros(pad_to, dtype=dtype, device=dev)
     if n:
-        view = torch.as_tensor(_DeviceMemory(ptr, n, "<i8" if dtype == torch.int64 else "<i4"), device=dev)
-        out[:n].copy_(view)
+        out[:n].copy_(api.device_view(ptr, n, "<i8" if dtype == torch.int64 else "<i4", dev))
     return out
 
 

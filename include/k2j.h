@@ -113,6 +113,7 @@ typedef struct {
   uint64_t unexpected_cuda_events;
   uint64_t in_bytes;    /* CUPTI record bytes consumed */
   uint64_t name_bytes;  /* escaped name bytes copied into events */
+  uint64_t annotation_bytes; /* bytes of the gpu_user_annotation events (they come last) */
   uint32_t kernel_launches; /* GPU kernels this run launched */
   uint32_t reserved;
   float ms_segment;     /* device time of each stage, CUDA events on the context's stream */

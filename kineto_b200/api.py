@@ -50,7 +50,7 @@ class Result(C.Structure):
     _fields_ = [("out_bytes", C.c_uint64), ("ops_bytes", C.c_uint64), ("n_records", C.c_uint64),
                 ("x_events", C.c_uint64), ("flow_events", C.c_uint64), ("out_of_range_events", C.c_uint64),
                 ("blocklisted_runtime_events", C.c_uint64), ("invalid_external_correlation_events", C.c_uint64),
-                ("unexpected_cuda_events", C.c_uint64), ("in_bytes", C.c_uint64), ("name_bytes", C.c_uint64),
+                ("unexpected_cuda_events", C.c_uint64), ("in_bytes", C.c_uint64), ("name_bytes", C.c_uint64), ("annotation_bytes", C.c_uint64),
                 ("kernel_launches", C.c_uint32), ("reserved", C.c_uint32), ("ms_segment", C.c_float),
                 ("ms_join", C.c_float), ("ms_size", C.c_float), ("ms_scan", C.c_float), ("ms_emit", C.c_float),
                 ("ms_total", C.c_float)]
@@ -259,3 +259,18 @@ def process(trace: tf.Trace, device: int = 0) -> tuple[bytes, dict]:
     finally:
         ctx.close()
     return out, res
+
+
+class _DeviceMemory:
+    def __init__(self, ptr, n, typestr):
+        self.__cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (ptr, False), "version": 2}
+
+
+def device_view(ptr: int, n: int, typestr: str, device="cuda:0"):
+    """A torch tensor over `n` elements of device memory at address `ptr` (no copy).  The memory
+    belongs to the context that returned the address and is valid until its next call."""
+    import torch
+
+    if n == 0:
+        return torch.empty(0, dtype={"<i8": torch.int64, "<i4": torch.int32}[typestr], device=device)
+    return torch.as_tensor(_DeviceMemory(ptr, n, typestr), device=device)

@@ -8,7 +8,9 @@
 #include <string.h>
 
 #include <algorithm>
+#include <map>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 #include "k2j_kernels.cuh"
@@ -62,6 +64,7 @@ struct k2j_ctx {
   DevBuf d_buf_off, d_buf_valid, d_buf_chunk_base;
   DevBuf esc_name, esc_md, esc_name_len, esc_md_len;
   DevBuf slot_code, exit_map, chunk_entry, chunk_cnt, chunk_base, scan_sums, scan_totals;
+  DevBuf ds_tab, span_key, span_nstart, span_end, span_nfirst, span_row, span_out, span_cnt, ann_size, ann_off;
   DevBuf tid_tab, corr_tab, user_tab, op_tab, work_slot, work_ev, ev_size, ev_off, out, counters;
   uint64_t* h_totals = nullptr;   // pinned: C_NCOL column totals, then the byte total
   Counters* h_counters = nullptr; // pinned
@@ -135,6 +138,52 @@ k2j_status run_scan(k2j_ctx* c, const uint32_t* in, uint64_t n, uint32_t cols, u
   return K2J_OK;
 }
 
+// Collects the span table, puts the spans in the order GpuUserEventMap::logEvents walks them — a
+// std::map over (device, stream), and inside it a std::unordered_map<int64_t, ...> over the op id,
+// filled in order of first use (libkineto/src/GenericActivityProfiler.h:341-346, .cpp:320-327) — and
+// sizes their events.  Host work is O(distinct annotations).
+k2j_status order_annotations(k2j_ctx* c, uint32_t span_cap, uint32_t* n_out, uint64_t* bytes_out) {
+  cudaStream_t s = c->stream;
+  Dev& d = c->d;
+  K2J_CUDA(c, c->span_out.reserve((size_t)span_cap * sizeof(SpanRec)));
+  K2J_CUDA(c, c->span_cnt.reserve(16));
+  K2J_CUDA(c, cudaMemsetAsync(c->span_cnt.p, 0, 4, s));
+  k_span_collect<<<(span_cap + 255) / 256, 256, 0, s>>>(d, c->span_out.as<SpanRec>(), c->span_cnt.as<unsigned int>());
+  c->launches++;
+  unsigned int n = 0;
+  K2J_CUDA(c, cudaMemcpyAsync(&n, c->span_cnt.p, 4, cudaMemcpyDeviceToHost, s));
+  K2J_CUDA(c, cudaStreamSynchronize(s));
+  *n_out = n; *bytes_out = 0;
+  if (n == 0) return K2J_OK;
+  std::vector<SpanRec> spans(n);
+  K2J_CUDA(c, cudaMemcpyAsync(spans.data(), c->span_out.p, (size_t)n * sizeof(SpanRec), cudaMemcpyDeviceToHost, s));
+  K2J_CUDA(c, cudaStreamSynchronize(s));
+  std::map<std::pair<int64_t, int64_t>, std::vector<const SpanRec*>> by_stream;
+  for (const SpanRec& r : spans) by_stream[{(int64_t)r.device, (int64_t)r.stream}].push_back(&r);
+  std::vector<SpanRec> ordered;
+  ordered.reserve(n);
+  for (auto& kv : by_stream) {
+    auto& v = kv.second;
+    std::sort(v.begin(), v.end(), [](const SpanRec* a, const SpanRec* b) { return a->first_event < b->first_event; });
+    std::unordered_map<int64_t, const SpanRec*> m;
+    for (const SpanRec* r : v) m.insert({(int64_t)r->op_id, r});
+    for (auto& e : m) ordered.push_back(*e.second);
+  }
+  K2J_CUDA(c, cudaMemcpyAsync(c->span_out.p, ordered.data(), (size_t)n * sizeof(SpanRec), cudaMemcpyHostToDevice, s));
+  K2J_CUDA(c, c->ann_size.reserve((size_t)n * 4));
+  K2J_CUDA(c, c->ann_off.reserve((size_t)n * 8));
+  k_annotations<false><<<(n + kEventThreads - 1) / kEventThreads, kEventThreads, 0, s>>>(
+      d, c->span_out.as<SpanRec>(), n, c->ann_size.as<uint32_t>(), nullptr, 0);
+  c->launches++;
+  K2J_CUDA(c, cudaGetLastError());
+  k2j_status st = run_scan(c, c->ann_size.as<uint32_t>(), n, 1, c->ann_off.as<uint64_t>(), c->scan_totals.as<uint64_t>() + 10, &c->launches);
+  if (st) return st;
+  K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 10, c->scan_totals.as<uint64_t>() + 10, 8, cudaMemcpyDeviceToHost, s));
+  K2J_CUDA(c, cudaStreamSynchronize(s));  // also covers `ordered`, which goes out of scope
+  *bytes_out = c->h_totals[10];
+  return K2J_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -174,7 +223,8 @@ void k2j_destroy(k2j_ctx* c) {
     in->own.release();
   for (DevBuf* b : {&c->d_props, &c->d_buf_off, &c->d_buf_valid, &c->d_buf_chunk_base, &c->esc_name, &c->esc_md,
                     &c->esc_name_len, &c->esc_md_len, &c->slot_code, &c->exit_map, &c->chunk_entry, &c->chunk_cnt,
-                    &c->chunk_base, &c->scan_sums, &c->scan_totals, &c->tid_tab, &c->corr_tab, &c->user_tab, &c->op_tab,
+                    &c->chunk_base, &c->scan_sums, &c->scan_totals, &c->ds_tab, &c->span_key, &c->span_nstart, &c->span_end, &c->span_nfirst, &c->span_row,
+                    &c->span_out, &c->span_cnt, &c->ann_size, &c->ann_off, &c->tid_tab, &c->corr_tab, &c->user_tab, &c->op_tab,
                     &c->work_slot, &c->work_ev, &c->ev_size, &c->ev_off, &c->out, &c->counters, &c->ext_local})
     b->release();
   if (c->h_totals) cudaFreeHost(c->h_totals);
@@ -473,13 +523,37 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
   d.tid_tab = c->tid_tab.as<unsigned long long>(); d.tid_mask = tid_cap - 1;
   K2J_CUDA(c, cudaMemsetAsync(d.tid_tab, 0, (size_t)tid_cap * 8, s));
   if (c->n_tid + c->n_ops) { k_build_tids<<<(uint32_t)((c->n_tid + c->n_ops + 255) / 256), 256, 0, s>>>(d); c->launches++; }
+  // user-annotation span tables (single-shard runs only)
+  const bool spans_on = (c->params.flags & K2J_FLAG_USER_ANNOTATIONS) && !c->have_global_join && totals[C_USER] > 0;
+  d.span_key = nullptr;
+  uint32_t span_cap = 0;
+  if (spans_on) {
+    span_cap = pow2_at_least(2 * totals[C_USER] + 16);
+    const uint32_t ds_cap = 1u << 16;
+    K2J_CUDA(c, c->ds_tab.reserve((size_t)ds_cap * 8));
+    K2J_CUDA(c, c->span_key.reserve((size_t)span_cap * 8));
+    K2J_CUDA(c, c->span_nstart.reserve((size_t)span_cap * 8));
+    K2J_CUDA(c, c->span_end.reserve((size_t)span_cap * 8));
+    K2J_CUDA(c, c->span_nfirst.reserve((size_t)span_cap * 8));
+    K2J_CUDA(c, c->span_row.reserve((size_t)span_cap * 4));
+    d.ds_tab = c->ds_tab.as<unsigned long long>(); d.ds_mask = ds_cap - 1;
+    d.span_key = c->span_key.as<unsigned long long>(); d.span_nstart = c->span_nstart.as<unsigned long long>();
+    d.span_end = c->span_end.as<unsigned long long>(); d.span_nfirst = c->span_nfirst.as<unsigned long long>();
+    d.span_row = c->span_row.as<uint32_t>(); d.span_mask = span_cap - 1;
+    K2J_CUDA(c, cudaMemsetAsync(d.ds_tab, 0, (size_t)ds_cap * 8, s));
+    K2J_CUDA(c, cudaMemsetAsync(d.span_key, 0, (size_t)span_cap * 8, s));
+    K2J_CUDA(c, cudaMemsetAsync(d.span_nstart, 0, (size_t)span_cap * 8, s));
+    K2J_CUDA(c, cudaMemsetAsync(d.span_end, 0, (size_t)span_cap * 8, s));
+    K2J_CUDA(c, cudaMemsetAsync(d.span_nfirst, 0, (size_t)span_cap * 8, s));
+  }
   if (d.n_ext_all) { k_build_corr<<<(uint32_t)((d.n_ext_all + 255) / 256), 256, 0, s>>>(d, own_begin, own_end); c->launches++; }
   if (d.n_join_ops) { k_build_ops<<<(uint32_t)((d.n_join_ops + 255) / 256), 256, 0, s>>>(d); c->launches++; }
   K2J_CUDA(c, cudaGetLastError());
   K2J_CUDA(c, cudaEventRecord(c->ev[2], s));
 
   // ---- size pass, scan, emit pass ----
-  uint64_t total_bytes = 0;
+  uint64_t total_bytes = 0, ann_bytes = 0;
+  uint32_t n_spans = 0;
   if (d.n_work) {
     const uint32_t ev_blocks = (uint32_t)((d.n_work + kEventThreads - 1) / kEventThreads);
     k_events<false><<<ev_blocks, kEventThreads, 0, s>>>(d);
@@ -494,10 +568,19 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
     K2J_CUDA(c, cudaEventRecord(c->ev[4], s));
     K2J_CUDA(c, cudaStreamSynchronize(s));
     total_bytes = c->h_totals[8];
-    K2J_CUDA(c, c->out.reserve(total_bytes + 64));
-    d.out = c->out.as<uint8_t>(); d.out_cap = total_bytes;
+    if (spans_on) {
+      k2j_status st2 = order_annotations(c, span_cap, &n_spans, &ann_bytes);
+      if (st2) return st2;
+    }
+    K2J_CUDA(c, c->out.reserve(total_bytes + ann_bytes + 64));
+    d.out = c->out.as<uint8_t>(); d.out_cap = total_bytes + ann_bytes;
     K2J_CUDA(c, cudaEventRecord(c->ev[7], s));
     if (total_bytes) { k_events<true><<<ev_blocks, kEventThreads, 0, s>>>(d); c->launches++; }
+    if (ann_bytes) {
+      k_annotations<true><<<(n_spans + kEventThreads - 1) / kEventThreads, kEventThreads, 0, s>>>(
+          d, c->span_out.as<SpanRec>(), n_spans, nullptr, c->ann_off.as<uint64_t>(), total_bytes);
+      c->launches++;
+    }
     K2J_CUDA(c, cudaGetLastError());
   } else {
     K2J_CUDA(c, cudaEventRecord(c->ev[3], s));
@@ -508,10 +591,11 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
   K2J_CUDA(c, cudaMemcpyAsync(c->h_counters, c->counters.p, sizeof(Counters), cudaMemcpyDeviceToHost, s));
   K2J_CUDA(c, cudaStreamSynchronize(s));
 
-  res->out_bytes = total_bytes;
+  res->out_bytes = total_bytes + ann_bytes;
+  res->annotation_bytes = ann_bytes;
   res->ops_bytes = n_gpu_events ? c->h_totals[9] : total_bytes;
   res->n_records = totals[C_EVENTS] + totals[C_EXT] + totals[C_UNEXPECTED];
-  res->x_events = c->h_counters->x_events;
+  res->x_events = c->h_counters->x_events + (ann_bytes ? n_spans : 0);
   res->flow_events = c->h_counters->flow_events;
   res->out_of_range_events = c->h_counters->out_of_range;
   res->blocklisted_runtime_events = c->h_counters->blocklisted_runtime;
@@ -527,8 +611,10 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
   cudaEventElapsedTime(&res->ms_scan, c->ev[3], c->ev[4]);
   cudaEventElapsedTime(&res->ms_emit, c->ev[7], c->ev[5]);
   res->ms_total = res->ms_segment + res->ms_join + res->ms_size + res->ms_scan + res->ms_emit;
-  c->out_bytes = total_bytes;
+  c->out_bytes = total_bytes + ann_bytes;
   c->ran = true;
+  if ((c->params.flags & K2J_FLAG_USER_ANNOTATIONS) && c->have_global_join && c->h_counters->n_user)
+    return fail(c, K2J_ERR_UNSUPPORTED, "user-annotation spans across shards are not implemented");
   if (c->h_counters->device_check)
     return fail(c, K2J_ERR_DEVICE_CHECK, "%llu device-side checks failed (string id, table or output bound)",
                 (unsigned long long)c->h_counters->device_check);

@@ -25,9 +25,12 @@
 namespace k2j {
 
 // ---- record classes ---------------------------------------------------------------------------
-enum : int { C_API = 0, C_KERNEL = 1, C_MEMCPY = 2, C_MEMCPY2 = 3, C_MEMSET = 4, C_EXT = 5, C_NCLASS = 6,
+enum : int { C_API = 0, C_KERNEL = 1, C_MEMCPY = 2, C_MEMCPY2 = 3, C_MEMSET = 4, C_EXT = 5,
+             C_EXT_USER = 6 /* slot class only: EXTERNAL_CORRELATION of kind CUSTOM1; counted in C_EXT too */,
+             C_NCLASS = 6,
              C_EVENTS = 6 /* column 6 of the count matrix: records that own an event slot */,
-             C_UNEXPECTED = 7 /* column 7: records of unknown kind */, C_NCOL = 8, C_OP = 8 };
+             C_UNEXPECTED = 7 /* column 7: records of unknown kind */,
+             C_USER = 8 /* column 8: CUSTOM1 correlation records */, C_NCOL = 9, C_OP = 9 };
 enum : uint32_t { K_MEMCPY = 1, K_MEMSET = 2, K_DRIVER = 4, K_RUNTIME = 5, K_KERNEL = 10, K_MEMCPY2 = 22, K_EXTCORR = 39 };
 
 constexpr int kChunkSlots = 512;            // 4 KiB of 8-byte slots
@@ -36,14 +39,14 @@ constexpr uint8_t kExitTerminate = 254;     // the walk hit a record it cannot s
 constexpr uint8_t kEntryNone = 255;         // chunk is unreachable
 
 // size/8 | class<<5 for a record kind; 0 = unknown
-__device__ __forceinline__ uint32_t slot_code(uint32_t kind) {
+__device__ __forceinline__ uint32_t slot_code(uint32_t kind, uint32_t word1) {
   switch (kind) {
     case K_KERNEL: return 26u | (C_KERNEL << 5);
     case K_MEMCPY: return 11u | (C_MEMCPY << 5);
     case K_MEMCPY2: return 12u | (C_MEMCPY2 << 5);
     case K_MEMSET: return 11u | (C_MEMSET << 5);
     case K_RUNTIME: case K_DRIVER: return 5u | (C_API << 5);
-    case K_EXTCORR: return 3u | (C_EXT << 5);
+    case K_EXTCORR: return 3u | ((word1 == 4u ? C_EXT_USER : C_EXT) << 5);  // word1 = externalKind
     default: return 0u;
   }
 }
@@ -55,11 +58,12 @@ struct DevProps {
 
 struct Counters {
   unsigned long long x_events, flow_events, out_of_range, blocklisted_runtime, invalid_external_correlation,
-      unexpected, name_bytes, device_check;
+      unexpected, name_bytes, device_check, n_user;
 };
 
 struct MdEntry { uint32_t key, type; uint64_t value; };
 struct ExtRec { uint64_t external_id; uint32_t correlation_id; uint32_t external_kind; };
+struct SpanRec { int64_t start, end; uint64_t first_event; uint32_t device, stream; int32_t op_id; uint32_t op_row; };
 
 struct Dev {
   // scalars
@@ -93,6 +97,10 @@ struct Dev {
   unsigned long long* corr_tab; uint32_t corr_mask;
   unsigned long long* user_tab; uint32_t user_mask;
   unsigned long long* op_tab; uint32_t op_mask;
+  // user-annotation spans (GpuUserEventMap): (device, stream) set, then (set slot, op id) -> span
+  unsigned long long* ds_tab; uint32_t ds_mask;
+  unsigned long long* span_key; unsigned long long* span_nstart; unsigned long long* span_end;
+  unsigned long long* span_nfirst; uint32_t* span_row; uint32_t span_mask;  // span_key == nullptr: off
   // work lists (class-sorted) and per-event arrays
   uint32_t* work_slot; uint32_t* work_ev; uint64_t cls_begin[C_NCLASS]; uint64_t cls_count[C_NCLASS];
   uint64_t ops_begin; uint64_t n_work;
@@ -236,7 +244,7 @@ __global__ void __launch_bounds__(kSegWarps * 32) k_seg_chunks(Dev d) {
   const uint32_t chunk = blockIdx.x * kSegWarps + w;
   if (chunk >= d.n_chunks) return;
   const ChunkGeom g = chunk_geom(d, chunk);
-  const uint32_t* words = reinterpret_cast<const uint32_t*>(d.cupti);
+  const uint2* words = reinterpret_cast<const uint2*>(d.cupti);
 #pragma unroll
   for (int j = 0; j < kChunkSlots / 128; j++) {
     const uint32_t s = 4 * (lane + 32 * j);
@@ -244,7 +252,7 @@ __global__ void __launch_bounds__(kSegWarps * 32) k_seg_chunks(Dev d) {
 #pragma unroll
     for (int q = 0; q < 4; q++) {
       uint32_t code = 0;
-      if (s + q < g.nvalid) code = slot_code(words[(g.slot0 + s + q) * 2]);
+      if (s + q < g.nvalid) { const uint2 w2 = words[g.slot0 + s + q]; code = slot_code(w2.x, w2.y); }
       packed |= code << (8 * q);
     }
     *reinterpret_cast<uint32_t*>(&s_code[w][s]) = packed;
@@ -333,7 +341,9 @@ __global__ void __launch_bounds__(kSegWarps * 32) k_seg_count(Dev d) {
     if (lane == 0) {
       walk_chunk(s_code[w], entry, g, [&](uint32_t, uint32_t code) {
         if (code == 0) { cnt[C_UNEXPECTED]++; return; }
-        const uint32_t cls = code >> 5;
+        uint32_t cls = code >> 5;
+        cnt[C_USER] += (cls == (uint32_t)C_EXT_USER);
+        if (cls == (uint32_t)C_EXT_USER) cls = C_EXT;
 #pragma unroll
         for (int i = 0; i < C_NCLASS; i++) cnt[i] += (cls == (uint32_t)i);
         cnt[C_EVENTS] += (cls != (uint32_t)C_EXT);
@@ -366,7 +376,8 @@ __global__ void __launch_bounds__(kSegWarps * 32) k_seg_write(Dev d) {
     uint32_t n = 0, ev = 0;
     walk_chunk(s_code[w], entry, g, [&](uint32_t pos, uint32_t code) {
       if (code == 0) return;
-      const uint32_t cls = code >> 5;
+      uint32_t cls = code >> 5;
+      if (cls == (uint32_t)C_EXT_USER) cls = C_EXT;
       uint32_t r = 0;
 #pragma unroll
       for (int i = 0; i < C_NCLASS; i++) if (cls == (uint32_t)i) r = cnt[i]++;
@@ -428,7 +439,7 @@ __global__ void k_build_corr(Dev d, uint64_t own_begin, uint64_t own_end) {
   const ExtRec e = d.ext_all[i];
   bool ok = true;
   if (e.external_kind == 3u) ok = tab_insert(d.corr_tab, d.corr_mask, e.correlation_id, (uint32_t)i);
-  else if (e.external_kind == 4u) ok = tab_insert(d.user_tab, d.user_mask, e.correlation_id, (uint32_t)i);
+  else if (e.external_kind == 4u) { ok = tab_insert(d.user_tab, d.user_mask, e.correlation_id, (uint32_t)i); atomicAdd(&d.counters->n_user, 1ull); }
   else if (i >= own_begin && i < own_end) atomicAdd(&d.counters->invalid_external_correlation, 1ull);
   if (!ok) atomicAdd(&d.counters->device_check, 1ull);
 }
@@ -604,7 +615,46 @@ __device__ __forceinline__ bool linked_op(const Dev& d, uint32_t corr, int32_t* 
   return true;
 }
 
-struct Tally { uint32_t x, flow; unsigned long long name_bytes; };
+// GenericActivityProfiler::handleGpuActivity's user-annotation step (GenericActivityProfiler.cpp:424-434)
+// with GpuUserEventMap::insertOrExtendEvent (:292-311): per (device, stream) and annotation op the span
+// [min start, max end] over the GPU activities correlated to it.  Runs in the size pass only.
+__device__ __forceinline__ void span_update(const Dev& d, uint32_t corr, uint32_t dev, uint32_t stream, int64_t ts,
+                                            int64_t dur, uint64_t ev) {
+  if (d.span_key == nullptr) return;
+  const uint32_t idx = tab_find(d.user_tab, d.user_mask, corr);
+  if (idx == 0xFFFFFFFFu) return;
+  const int64_t ext = (int64_t)d.ext_all[idx].external_id;
+  if (ext != (int64_t)(int32_t)ext) return;
+  const uint32_t row = tab_find(d.op_tab, d.op_mask, (uint32_t)(int32_t)ext);
+  if (row == 0xFFFFFFFFu) return;
+  // (device, stream) -> slot
+  const unsigned long long dskey = (((unsigned long long)dev << 32) | stream) + 1ull;
+  uint32_t i = hash32(dev * 0x9E3779B1u ^ stream) & d.ds_mask;
+  uint32_t probes = 0;
+  for (; probes <= d.ds_mask; probes++) {
+    unsigned long long old = d.ds_tab[i];
+    if (old == 0) old = atomicCAS(&d.ds_tab[i], 0ull, dskey);
+    if (old == 0 || old == dskey) break;
+    i = (i + 1) & d.ds_mask;
+  }
+  if (probes > d.ds_mask) { atomicAdd(&d.counters->device_check, 1ull); return; }
+  const unsigned long long key = ((unsigned long long)(i + 1u) << 32) | (uint32_t)(int32_t)ext;
+  uint32_t j = hash32((i + 1u) * 0x85EBCA6Bu ^ (uint32_t)(int32_t)ext) & d.span_mask;
+  for (probes = 0; probes <= d.span_mask; probes++) {
+    unsigned long long old = d.span_key[j];
+    if (old == 0) old = atomicCAS(&d.span_key[j], 0ull, key);
+    if (old == 0 || old == key) break;
+    j = (j + 1) & d.span_mask;
+  }
+  if (probes > d.span_mask) { atomicAdd(&d.counters->device_check, 1ull); return; }
+  // min start / first event are kept as max of the complement so that zero-filled memory is "unset"
+  atomicMax(&d.span_nstart[j], ~(unsigned long long)ts);
+  atomicMax(&d.span_end[j], (unsigned long long)(ts + dur));
+  atomicMax(&d.span_nfirst[j], ~(unsigned long long)ev);
+  d.span_row[j] = row;
+}
+
+struct Tally { uint32_t x, flow; unsigned long long name_bytes; uint64_t ev; };
 
 // Shared tail of an "X" event after the name: pid, tid, ts, dur and the opening of args.
 template <class S> __device__ __forceinline__ void x_mid(S& s, int64_t pid, int64_t tid, int64_t ts_rel, int64_t dur) {
@@ -784,6 +834,7 @@ template <class S> __device__ __forceinline__ bool ev_kernel(S& s, const Dev& d,
   K2J_LIT(s, "\n    }\n  },");
   t.x++;
   if (corr > 0) { flow_event(s, false, false, corr, (int64_t)dev, (int64_t)stream, ts_rel); t.flow++; }
+  if (S::kCounting) span_update(d, corr, dev, stream, ts, dur, t.ev);
   return true;
 }
 
@@ -838,6 +889,7 @@ template <class S, int CLS> __device__ __forceinline__ bool ev_mem(S& s, const D
   K2J_LIT(s, "\n    }\n  },");
   t.x++;
   if (corr > 0) { flow_event(s, false, false, corr, (int64_t)dev, (int64_t)stream, ts_rel); t.flow++; }
+  if (S::kCounting) span_update(d, corr, dev, stream, ts, dur, t.ev);
   return true;
 }
 
@@ -907,7 +959,7 @@ __global__ void __launch_bounds__(kEventThreads) k_events(Dev d) {
   if (threadIdx.x < 8) s_cnt[threadIdx.x] = 0;
   __syncthreads();
   const uint64_t i = (uint64_t)blockIdx.x * kEventThreads + threadIdx.x;
-  Tally t; t.x = 0; t.flow = 0; t.name_bytes = 0;
+  Tally t; t.x = 0; t.flow = 0; t.name_bytes = 0; t.ev = 0;
   uint32_t filt = 0;
   if (i < d.n_work) {
     int cls;
@@ -923,6 +975,7 @@ __global__ void __launch_bounds__(kEventThreads) k_events(Dev d) {
     if (cls == C_OP && j >= d.n_ops) cls = -1;
     if (cls >= 0) {
       const uint64_t ev = cls == C_OP ? j : d.work_ev[i];
+      t.ev = ev;
       const uint8_t* r = cls == C_OP ? nullptr : d.cupti + (uint64_t)d.work_slot[i] * 8;
       if (!WRITE) {
         CountSink s;
@@ -971,6 +1024,51 @@ __global__ void __launch_bounds__(kEventThreads) k_events(Dev d) {
       if (s_cnt[3]) atomicAdd(&d.counters->blocklisted_runtime, s_cnt[3]);
       if (s_cnt[4]) atomicAdd(&d.counters->name_bytes, s_cnt[4]);
     }
+  }
+}
+
+// ---- user-annotation spans: collect, then format in the order the host determined ----
+__global__ void k_span_collect(Dev d, SpanRec* out, unsigned int* n_out) {
+  const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j > d.span_mask) return;
+  const unsigned long long key = d.span_key[j];
+  if (key == 0) return;
+  const unsigned long long ds = d.ds_tab[(uint32_t)(key >> 32) - 1u] - 1ull;
+  SpanRec r;
+  r.start = (int64_t)~d.span_nstart[j];
+  r.end = (int64_t)d.span_end[j];
+  r.first_event = ~d.span_nfirst[j];
+  r.device = (uint32_t)(ds >> 32); r.stream = (uint32_t)ds;
+  r.op_id = (int32_t)(uint32_t)key; r.op_row = d.span_row[j];
+  out[atomicAdd(n_out, 1u)] = r;
+}
+
+// One thread per span, in emission order: the gpu_user_annotation event that
+// GpuUserEventMap::logEvents hands to the logger (GenericActivityProfiler.cpp:277-290, :320-327;
+// output_json.cpp:862-895: starts 1 ns earlier, lasts 2 ns longer, "External id" is the op's id).
+template <bool WRITE>
+__global__ void __launch_bounds__(kEventThreads) k_annotations(Dev d, const SpanRec* spans, uint32_t n, uint32_t* sizes,
+                                                               const uint64_t* offs, uint64_t out_base) {
+  __shared__ uint32_t s_stage[kEventThreads * 4];
+  const uint32_t i = blockIdx.x * kEventThreads + threadIdx.x;
+  if (i >= n) return;
+  const SpanRec r = spans[i];
+  int64_t dur = r.end - r.start;
+  if (dur < 0) dur = 0;
+  unsigned long long nb = 0;
+  auto body = [&](auto& s) {
+    K2J_LIT(s, "\n  {\n    \"ph\": \"X\",\n    \"cat\": \"gpu_user_annotation\",\n    \"name\": \"");
+    if (r.op_row < d.n_ops) put_name(s, d, d.op_name[r.op_row], &nb);
+    x_mid(s, (int64_t)r.device, (int64_t)r.stream, rel_ts(d, r.start - 1), dur + 2);
+    if (r.op_id != 0) { K2J_LIT(s, ",\n    \"args\": {\n      \"External id\": "); put_i64(s, r.op_id); K2J_LIT(s, "\n    }"); }
+    K2J_LIT(s, "\n  },");
+  };
+  if (!WRITE) { CountSink s; body(s); sizes[i] = s.n; }
+  else {
+    GlobalSink s;
+    s.init(d.out + out_base + offs[i], &s_stage[(threadIdx.x >> 5) * 128 + (threadIdx.x & 31)]);
+    body(s);
+    s.finish();
   }
 }
 

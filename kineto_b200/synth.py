@@ -376,7 +376,7 @@ def _kernel_records(rng, n, names, starts, durs, corr, n_devices, n_streams):
 
 
 def gen_kernel_launches(n=1_000_000, seed=2, n_devices=8, n_streams=32, pool_size=4096, name_len=(20, 400),
-                        orphan_fraction=0.0, buffer_bytes=4 << 20, ts_mode=0, shard=(0, 1)) -> tf.Trace:
+                        orphan_fraction=0.0, buffer_bytes=4 << 20, ts_mode=0, shard=(0, 1), user_annotations=0) -> tf.Trace:
     """`n` kernel launches: per launch one EXTERNAL_CORRELATION(CUSTOM0) record, one cudaLaunchKernel
     runtime record and one CUpti_ActivityKernel9, plus `n` CPU ops.  Kernel records carry the
     correlation ids in a seeded permutation, so the join is not positional.
@@ -425,9 +425,31 @@ def gen_kernel_launches(n=1_000_000, seed=2, n_devices=8, n_streams=32, pool_siz
         conv = tsc_converter_for(window)
         for rec in (api, kern):
             rec["start"], rec["end"] = ns_to_ticks(rec["start"], conv), ns_to_ticks(rec["end"], conv)
-    order = np.tile(np.array([0, 1, 2], np.int8), n)
     t = ops
-    t.cupti, offs = tf.interleave([ext, api, kern], order)
+    if user_annotations:
+        # `user_annotations` user_annotation ops (ids above every cpu_op id), each covering a contiguous
+        # run of launches through a CUSTOM1 correlation record per launch
+        k = user_annotations
+        ann_id = (total + 1 + (np.arange(lo, hi) * k // total)).astype(np.int32)
+        extu = np.zeros(n, tf.EXTCORR)
+        extu["kind"], extu["externalKind"] = tf.KIND_EXTERNAL_CORRELATION, tf.EXTERNAL_KIND_CUSTOM1
+        extu["externalId"], extu["correlationId"] = ann_id.astype(np.uint64), corr
+        ids = np.unique(ann_id)
+        m = len(ids)
+        first = np.array([np.argmax(ann_id == i) for i in ids])
+        add = dict(op_start=op_starts_all[lo:hi][first] - 50, op_end=op_starts_all[lo:hi][first] + 5_000_000,
+                   op_id=ids, op_device=np.full(m, DEFAULT_PID, np.int32), op_resource=t.op_resource[first],
+                   op_thread=t.op_thread[first], op_type=np.full(m, USER_ANNOTATION, np.int32),
+                   op_name=np.array([pool.add("ProfilerStep#%d" % i) for i in ids], np.uint32),
+                   op_flow=np.zeros(m, np.uint32), op_flowt=np.zeros(m, np.uint8))
+        for col, v in add.items():
+            setattr(t, col, np.concatenate([getattr(t, col), v.astype(getattr(t, col).dtype)]))
+        t.op_mdoff = np.concatenate([t.op_mdoff, np.full(m, t.op_mdoff[-1], np.uint32)])
+        order = np.tile(np.array([0, 3, 1, 2], np.int8), n)
+        t.cupti, offs = tf.interleave([ext, api, kern, extu], order)
+    else:
+        order = np.tile(np.array([0, 1, 2], np.int8), n)
+        t.cupti, offs = tf.interleave([ext, api, kern], order)
     t.buftab = tf.make_buftab(offs, buffer_bytes)
     return _finish(t, pool, 1, window, n_devices, ts_mode=ts_mode, conv=conv)
 

@@ -13,7 +13,7 @@ from kineto_b200 import tracefile as tf
 pytestmark = pytest.mark.gpu
 
 GOLDEN = sorted(f[:-5] for f in os.listdir(helpers.GOLDEN) if f.endswith(".k2jt"))
-UNSUPPORTED_ON_GPU = {"annotations"}  # user-annotation spans are produced by a later pipeline stage
+UNSUPPORTED_ON_GPU = set()
 
 
 def gpu_run(trace, **kw):
@@ -30,6 +30,7 @@ def check_counters(res, stats, trace):
     assert res["invalid_external_correlation_events"] == stats["invalid_external_correlation"]
     assert res["unexpected_cuda_events"] == stats["unexpected"]
     assert res["ops_bytes"] == stats["ops_end"]
+    assert res["out_bytes"] - res["annotation_bytes"] == stats["gpu_end"]
     assert res["kernel_launches"] > 0
 
 
@@ -51,7 +52,11 @@ def test_gpu_matches_reference_golden(name):
     lambda: synth.gen_mixed(50_000, seed=205, pool_size=500, buffer_bytes=4096 + 64),
     lambda: cases.tsc_trace(40_000),
     cases.edge_trace,
-], ids=["generic", "launches", "shard", "mixed", "mixed_small_buffers", "tsc", "edge"])
+    lambda: cases.edge_trace(flags=1),
+    cases.annotation_trace,
+    lambda: synth.gen_kernel_launches(60_000, seed=206, pool_size=300, user_annotations=40),
+], ids=["generic", "launches", "shard", "mixed", "mixed_small_buffers", "tsc", "edge", "edge_annot", "annotations",
+        "launches_annot"])
 def test_gpu_matches_port(gen):
     trace = gen()
     want, stats = helpers.run_port(trace)
@@ -127,7 +132,7 @@ def test_error_behaviour():
         assert e.value.status == 1
         # string id out of range -> the kernels' own check trips, the context stays usable
         k = t.cupti.copy()
-        k[48 + 104:48 + 112].view(np.uint64)[0] = 1 << 20  # name field of the first kernel record
+        k[64 + 104:64 + 112].view(np.uint64)[0] = 1 << 20  # name field of the first kernel record (after 24 + 40 bytes)
         a2 = dict(a, cupti=k)
         ctx.set_arrays(a2, t.buftab, t.tidmap)
         with pytest.raises(api.K2JError) as e:
@@ -184,11 +189,7 @@ def test_sharded_runs_concatenate_to_the_whole():
                 c.load(sub)
                 infos.append(c.segment())
             def view(ptr, n_items, ts):
-                class M:
-                    pass
-                m = M()
-                m.__cuda_array_interface__ = {"shape": (n_items,), "typestr": ts, "data": (ptr, True), "version": 2}
-                return torch.as_tensor(m, device="cuda:0").clone()
+                return api.device_view(ptr, n_items, ts).clone()
             ext = torch.cat([view(i.external_records, int(i.n_external) * 2, "<i8") for i in infos])
             ops = torch.cat([view(i.op_ids, int(i.n_ops), "<i4") for i in infos])
             begin = 0

@@ -42,7 +42,8 @@ def test_golden_container_is_reproducible(name):
     cases.edge_trace,
     lambda: cases.edge_trace(flags=1),
     cases.annotation_trace,
-], ids=["generic", "launches", "shard", "mixed", "tsc", "edge", "edge_annot", "annotations"])
+    lambda: synth.gen_kernel_launches(4000, seed=105, pool_size=100, user_annotations=25),
+], ids=["generic", "launches", "shard", "mixed", "tsc", "edge", "edge_annot", "annotations", "launches_annot"])
 def test_port_matches_live_reference(gen):
     trace = gen()
     doc, _ = helpers.run_ref(trace)
