@@ -194,6 +194,14 @@ k2j_status k2j_set_global_join(k2j_ctx* ctx, const void* external_all, uint64_t 
                                const int32_t* op_ids_all, uint64_t n_ops_all);
 k2j_status k2j_emit(k2j_ctx* ctx, k2j_result* result);
 
+/* The device-wide exclusive scan of the pipeline on its own: offsets[i] = sizes[0] + ... + sizes[i-1]
+ * and *total = the sum, for n 32-bit sizes in device memory (offsets: n 64-bit values in device
+ * memory).  It is the step that turns per-event byte lengths into final output positions; callers
+ * that place several shards' text themselves use it for their own size tables.  The reference has no
+ * such step: its logger appends to one std::ofstream (libkineto/src/output_json.cpp:246-257).
+ * Scratch for the block sums comes from the context's grow-only workspace. */
+k2j_status k2j_exclusive_scan_u32(k2j_ctx* ctx, const uint32_t* sizes, uint64_t n, uint64_t* offsets, uint64_t* total);
+
 /* Device pointer and size of the text produced by the last run (valid until the next run). */
 k2j_status k2j_output(k2j_ctx* ctx, const void** device_ptr, uint64_t* n_bytes);
 /* Copies the text to host memory (pinned memory makes the copy asynchronous up to its final wait). */

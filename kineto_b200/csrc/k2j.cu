@@ -629,6 +629,22 @@ k2j_status k2j_run(k2j_ctx* c, k2j_result* res) {
   return k2j_emit(c, res);
 }
 
+k2j_status k2j_exclusive_scan_u32(k2j_ctx* c, const uint32_t* sizes, uint64_t n, uint64_t* offsets, uint64_t* total) {
+  if (!c) return K2J_ERR_INVALID_ARGUMENT;
+  if (!total || (n && (!sizes || !offsets))) return fail(c, K2J_ERR_INVALID_ARGUMENT, "null scan argument");
+  if (n && (!is_device_ptr(sizes) || !is_device_ptr(offsets))) return fail(c, K2J_ERR_INVALID_ARGUMENT, "scan arrays must be device memory");
+  K2J_CUDA(c, cudaSetDevice(c->device));
+  *total = 0;
+  if (n == 0) return K2J_OK;
+  uint32_t launches = 0;
+  k2j_status st = run_scan(c, sizes, n, 1, offsets, c->scan_totals.as<uint64_t>() + 12, &launches);
+  if (st) return st;
+  K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 12, c->scan_totals.as<uint64_t>() + 12, 8, cudaMemcpyDeviceToHost, c->stream));
+  K2J_CUDA(c, cudaStreamSynchronize(c->stream));
+  *total = c->h_totals[12];
+  return K2J_OK;
+}
+
 k2j_status k2j_output(k2j_ctx* c, const void** p, uint64_t* n) {
   if (!c || !p || !n) return K2J_ERR_INVALID_ARGUMENT;
   if (!c->ran) return fail(c, K2J_ERR_STATE, "no completed run");

@@ -151,6 +151,25 @@ def test_error_behaviour():
         ctx.close()
 
 
+@pytest.mark.parametrize("n", [1, 255, 2048, 2049, 1_000_003])
+def test_exclusive_scan_entry_point(n):
+    import torch
+    from kineto_b200 import api
+    rng = np.random.default_rng(n)
+    sizes = rng.integers(0, 5000, n).astype(np.int32)
+    sizes[rng.integers(0, n, max(1, n // 50))] = 0
+    ctx = api.K2J(0)
+    try:
+        d_sizes = torch.from_numpy(sizes).cuda()
+        d_off = torch.empty(n, dtype=torch.int64, device="cuda")
+        total = ctx.exclusive_scan(d_sizes, d_off)
+        want = np.concatenate([[0], np.cumsum(sizes.astype(np.int64))])
+        assert total == want[-1]
+        assert (d_off.cpu().numpy() == want[:-1]).all()
+    finally:
+        ctx.close()
+
+
 def test_sharded_runs_concatenate_to_the_whole():
     """Size-independent property at the benchmark's full size: processing contiguous buffer ranges
     separately, with the join arrays gathered from all of them, gives exactly the bytes of one run

@@ -82,7 +82,7 @@ def test_library_exports_every_declared_symbol():
     """The shared library loads without a GPU and exports exactly what include/k2j.h declares."""
     from kineto_b200 import api
     header = open(os.path.join(ROOT, "include", "k2j.h")).read()
-    declared = set(re.findall(r"\b(k2j_[a-z_]+)\s*\(", header))
+    declared = set(re.findall(r"\b(k2j_[a-z0-9_]+)\s*\(", header))
     lib = ctypes.CDLL(api.LIB_PATH)
     for name in declared:
         assert hasattr(lib, name), name
