@@ -202,6 +202,21 @@ k2j_status k2j_emit(k2j_ctx* ctx, k2j_result* result);
  * Scratch for the block sums comes from the context's grow-only workspace. */
 k2j_status k2j_exclusive_scan_u32(k2j_ctx* ctx, const uint32_t* sizes, uint64_t n, uint64_t* offsets, uint64_t* total);
 
+/* The same scan for callers that cannot allocate (no counterpart in the reference).  Profiler
+ * callbacks that run during context teardown or under the allocator's lock, and processes whose
+ * device memory is wholly owned by a framework's caching allocator, cannot let a library call
+ * cudaMalloc; this entry point never allocates or frees: its block-sum scratch is a fixed array inside
+ * the library image (about 64 KiB of device memory per GPU that loads the library, held until exit).
+ * `sizes`, `offsets` and `total` are DEVICE pointers (total: one uint64 written by the GPU); the work is
+ * queued on `stream` (a cudaStream_t, NULL = default stream) of `device` and is not waited for.
+ * n above K2J_NOALLOC_SCAN_MAX is rejected with K2J_ERR_INVALID_ARGUMENT.  The first call on a device
+ * looks up the scratch address and should come before any stream capture on that device.  All calls
+ * on a device share the scratch: calls whose kernels could overlap on the GPU race and must be
+ * ordered by the caller; nothing in the scratch needs clearing between calls. */
+#define K2J_NOALLOC_SCAN_MAX (1ull << 24)
+k2j_status k2j_exclusive_scan_u32_noalloc(int device, void* stream, const uint32_t* sizes, uint64_t n,
+                                          uint64_t* offsets, uint64_t* total);
+
 /* Device pointer and size of the text produced by the last run (valid until the next run). */
 k2j_status k2j_output(k2j_ctx* ctx, const void** device_ptr, uint64_t* n_bytes);
 /* Copies the text to host memory (pinned memory makes the copy asynchronous up to its final wait). */

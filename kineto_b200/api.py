@@ -64,7 +64,7 @@ class SegmentInfo(C.Structure):
                 ("n_ops", C.c_uint64), ("op_ids", C.c_void_p)]
 
 
-EXPORTS = ["k2j_exclusive_scan_u32", "k2j_segment", "k2j_set_global_join", "k2j_emit", "k2j_create", "k2j_destroy", "k2j_last_error", "k2j_set_params", "k2j_set_strings",
+EXPORTS = ["k2j_exclusive_scan_u32", "k2j_exclusive_scan_u32_noalloc", "k2j_segment", "k2j_set_global_join", "k2j_emit", "k2j_create", "k2j_destroy", "k2j_last_error", "k2j_set_params", "k2j_set_strings",
            "k2j_set_cbid_names", "k2j_set_thread_map", "k2j_set_ops", "k2j_set_cupti", "k2j_run", "k2j_output",
            "k2j_copy_output", "k2j_version"]
 
@@ -96,6 +96,7 @@ def load_library():
     lib.k2j_set_global_join.argtypes = [vp, vp, C.c_uint64, C.c_uint64, vp, C.c_uint64]
     lib.k2j_emit.argtypes = [vp, C.POINTER(Result)]
     lib.k2j_exclusive_scan_u32.argtypes = [vp, vp, C.c_uint64, vp, C.POINTER(C.c_uint64)]
+    lib.k2j_exclusive_scan_u32_noalloc.argtypes = [C.c_int, vp, vp, C.c_uint64, vp, vp]
     lib.k2j_output.argtypes = [vp, C.POINTER(vp), C.POINTER(C.c_uint64)]
     lib.k2j_copy_output.argtypes = [vp, vp, C.c_uint64]
     lib.k2j_version.restype = C.c_char_p
