@@ -37,7 +37,7 @@ UNIT = "records/s"
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one k_events<true> launch divided by the JSON bytes
 # it wrote, from the ncu capture summarised in profiles/ (None until a capture exists).
-EMIT_TRAFFIC_PER_OUT_BYTE = None
+EMIT_TRAFFIC_PER_OUT_BYTE = 1.353
 
 
 def parse():

@@ -508,98 +508,311 @@ __global__ void __launch_bounds__(kScanThreads) k_scan_apply(const uint32_t* in,
 }
 
 // ---- output sink: 16-byte vector stores straight to the final position ----------------------------------
-// Bytes are gathered in a 64-bit shift register, completed 32-bit words go to a 4-word staging slot
-// of this lane in shared memory (word k of lane l lives at index k*32+l: conflict free), and every
-// fourth word the slot leaves as one 16-byte store.  Only the first and last 16-byte block of an
-// event are written with narrower stores, so neighbouring events never overwrite each other.
+// Bytes are gathered in a 32-bit shift register, completed words go to a 4-word staging slot of this
+// lane in shared memory (word k of lane l lives at index k*32+l: conflict free), and every fourth word
+// the slot leaves as one 16-byte store.  Only the first and last 16-byte block of an event are
+// written with narrower stores, so neighbouring events never overwrite each other.
+__device__ __noinline__ void store_partial(uint8_t* b, const uint32_t* slot, int from, int to) {
+  int i = from;
+  while (i < to) {
+    const uint32_t w = slot[(i >> 2) * 32];
+    if ((i & 3) == 0 && i + 4 <= to) { *reinterpret_cast<uint32_t*>(b + i) = w; i += 4; }
+    else { b[i] = (uint8_t)(w >> ((i & 3) * 8)); i++; }
+  }
+}
+
 struct GlobalSink {
   static constexpr bool kCounting = false;
-  uint64_t acc; int n; int k; int head; uint32_t* slot; uint4* p;
+  uint32_t lo; int sh; int head; uint32_t* sp; uint32_t* sp_end; uint4* p;
   __device__ __forceinline__ void init(uint8_t* dst, uint32_t* lane_slot) {
     const uintptr_t a = reinterpret_cast<uintptr_t>(dst);
     const int phase = (int)(a & 15);
     p = reinterpret_cast<uint4*>(a - phase);
-    k = phase >> 2; n = phase & 3; acc = 0; head = phase; slot = lane_slot;
-  }
-  __device__ __forceinline__ void store_partial(int from, int to) {
-    uint8_t* b = reinterpret_cast<uint8_t*>(p);
-    int i = from;
-    while (i < to) {
-      const uint32_t w = slot[(i >> 2) * 32];
-      if ((i & 3) == 0 && i + 4 <= to) { *reinterpret_cast<uint32_t*>(b + i) = w; i += 4; }
-      else { b[i] = (uint8_t)(w >> ((i & 3) * 8)); i++; }
-    }
+    sp_end = lane_slot + 128; sp = lane_slot + 32 * (phase >> 2);
+    sh = 8 * (phase & 3); lo = 0; head = phase;
   }
   __device__ __forceinline__ void word(uint32_t x) {
-    slot[(k & 3) * 32] = x;
-    k++;
-    if ((k & 3) == 0) {
-      if (head) { store_partial(head, 16); head = 0; }
-      else *p = make_uint4(slot[0], slot[32], slot[64], slot[96]);
+    *sp = x;
+    sp += 32;
+    if (sp == sp_end) {
+      sp = sp_end - 128;
+      if (head) { store_partial(reinterpret_cast<uint8_t*>(p), sp, head, 16); head = 0; }
+      else *p = make_uint4(sp[0], sp[32], sp[64], sp[96]);
       p++;
     }
   }
+  __device__ __forceinline__ void put4(uint32_t w) {
+    word(lo | (w << sh));
+    lo = __funnelshift_l(w, 0u, sh);
+  }
   __device__ __forceinline__ void put(uint32_t w, int len) {
-    acc |= (uint64_t)w << (n * 8);
-    n += len;
-    if (n >= 4) { word((uint32_t)acc); acc >>= 32; n -= 4; }
+    const uint32_t t = lo | (w << sh);
+    const int s2 = sh + 8 * len;
+    if (s2 >= 32) { word(t); lo = __funnelshift_l(w, 0u, sh); sh = s2 - 32; }
+    else { lo = t; sh = s2; }
   }
   __device__ __forceinline__ void skip(uint32_t) {}
   template <int N> __device__ __forceinline__ void lit(const Lit<N>& l) {
 #pragma unroll
-    for (int i = 0; i < N / 4; i++) put(l.w[i], 4);
+    for (int i = 0; i < N / 4; i++) put4(l.w[i]);
     if (N % 4) put(l.w[N / 4], N % 4);
   }
+  // `len` bytes from a word array in constant or global memory (last word zero padded).
+  __device__ __forceinline__ void words(const uint32_t* w, uint32_t len) {
+    // four loads in flight per round: the loads do not depend on the shift register, the puts do
+    const uint32_t nw = len >> 2;
+    uint32_t i = 0;
+    for (; i + 4 <= nw; i += 4) {
+      const uint32_t a = w[i], b = w[i + 1], c = w[i + 2], e = w[i + 3];
+      put4(a); put4(b); put4(c); put4(e);
+    }
+    for (; i < nw; i++) put4(w[i]);
+    const uint32_t rem = len & 3u;
+    if (rem) put(w[nw] & (0xFFFFFFFFu >> (8 * (4 - rem))), (int)rem);
+  }
   __device__ __forceinline__ void finish() {
-    const int have = (k & 3) * 4 + n;
-    if (n) slot[(k & 3) * 32] = (uint32_t)acc;
-    if (have > head) store_partial(head, have);
+    uint32_t* base = sp_end - 128;
+    const int have = (int)((sp - base) >> 5) * 4 + (sh >> 3);
+    if (sh) *sp = lo;
+    if (have > head) store_partial(reinterpret_cast<uint8_t*>(p), base, head, have);
   }
 };
+struct CountSink2 : CountSink {
+  __device__ __forceinline__ void put4(uint32_t) { n += 4; }
+  __device__ __forceinline__ void words(const uint32_t*, uint32_t len) { n += len; }
+};
 
-// ---- event formatting ---------------------------------------------------------------------------------------
-K2J_CONST_TABLE char kTypeNames[29][24] = {  // libkineto/include/ActivityType.h:80-112
-    "cpu_op", "user_annotation", "gpu_user_annotation", "gpu_memcpy", "gpu_memset", "kernel",
-    "external_correlation", "cuda_runtime", "cuda_driver", "cpu_instant_event", "python_function",
-    "overhead", "mtia_runtime", "mtia_ccp_events", "mtia_insight", "cuda_sync", "cuda_event",
-    "mtia_counters", "glow_runtime", "cuda_profiler_range", "hpu_op", "xpu_runtime", "xpu_driver",
-    "collective_comm", "privateuse1_runtime", "privateuse1_driver", "xpu_scope_profiler", "xpu_sync",
-    "hardware_counters"};
-K2J_CONST_TABLE char kMemcpyKind[12][12] = {  // libkineto/src/cupti_strings.cpp:15-41
-    "<unknown>", "HtoD", "DtoH", "HtoA", "AtoH", "AtoA", "AtoD", "DtoA", "DtoD", "HtoH", "PtoP", "<unknown>"};
-K2J_CONST_TABLE char kMemoryKind[9][16] = {  // libkineto/src/cupti_strings.cpp:43-66
-    "Unknown", "Pageable", "Pinned", "Device", "Array", "Managed", "Device Static", "Managed Static", "Unrecognized"};
+// ---- event programs ------------------------------------------------------------------------------------
+// An event is a fixed sequence of fields, each a literal followed by a value.  The sequence of a
+// record class is data (a table in constant memory), so all classes share one small formatting loop:
+// the emit kernel stays a few tens of KiB of code, and the lanes of a warp, which format events of one
+// class, run the loop in lock step.  Per event the class-specific code only gathers the values.
+enum : uint8_t { T_NONE = 0, T_U64, T_I64, T_TS, T_DBL, T_NAME, T_CSTR, T_MD /* the metadata entries of a CPU-side activity */ };
+struct FieldSrc { const char* lit; uint8_t type; };
+struct FieldDesc { uint16_t off, len; uint8_t type, pad; };
 
-template <class S> __device__ __forceinline__ void put_cstr(S& s, const char* c) {
-  for (int i = 0; c[i]; i++) put_char(s, c[i]);
+constexpr int c_strlen(const char* s) { int n = 0; while (s[n]) n++; return n; }
+template <int NF> constexpr int prog_words(const FieldSrc (&src)[NF]) {
+  int w = 0;
+  for (int f = 0; f < NF; f++) w += (c_strlen(src[f].lit) + 3) / 4;
+  return w > 0 ? w : 1;
 }
-// Copies an escaped pool string (8-byte aligned, padded to a multiple of 4 readable bytes).
-template <class S> __device__ __forceinline__ void put_pool(S& s, const uint8_t* src, uint32_t len) {
-  if (S::kCounting) { s.skip(len); return; }
-  const uint32_t* w = reinterpret_cast<const uint32_t*>(src);
-  uint32_t i = 0;
-  for (; i + 4 <= len; i += 4) s.put(w[i >> 2], 4);
-  if (i < len) s.put(w[i >> 2] & (0xFFFFFFFFu >> (8 * (4 - (len - i)))), (int)(len - i));
+template <int NF, int NW> struct Prog {
+  FieldDesc f[NF];
+  uint32_t w[NW];
+};
+template <int NF, int NW> constexpr Prog<NF, NW> make_prog(const FieldSrc (&src)[NF]) {
+  Prog<NF, NW> p{};
+  int pos = 0;
+  for (int f = 0; f < NF; f++) {
+    const int n = c_strlen(src[f].lit);
+    p.f[f].off = (uint16_t)pos; p.f[f].len = (uint16_t)n; p.f[f].type = src[f].type; p.f[f].pad = 0;
+    for (int i = 0; i < n; i++) p.w[pos + i / 4] |= (uint32_t)(unsigned char)src[f].lit[i] << (8 * (i % 4));
+    pos += (n + 3) / 4;
+  }
+  return p;
+}
+#define XHEAD(cat) "\n  {\n    \"ph\": \"X\",\n    \"cat\": \"" cat "\",\n    \"name\": \""
+#define FLOW_TAIL "\n  },"
+
+// -- small constant strings: activity type names (libkineto/include/ActivityType.h:80-112), memcpy and
+// memory kinds (libkineto/src/cupti_strings.cpp:15-66), limiting factors (CuptiActivity.h:476-497) --
+// -- runtime / driver API record --
+enum : int { A_HEAD_RT, A_HEAD_DR, A_NAME, A_INVALID, A_PID, A_TID, A_TS, A_DUR, A_ARGS, A_EXT, A_EXTC, A_CBID, A_CORR, A_CLOSE,
+             A_FLOW_S, A_FLOW_F, A_FPID, A_FTID, A_FTS, A_FCAT, A_FBP, A_FEND, A_COUNT };
+#define K2J_API_FIELDS \
+    {XHEAD("cuda_runtime"), T_NONE}, {XHEAD("cuda_driver"), T_NONE}, {"", T_NAME}, {"INVALID", T_NONE}, \
+    {"\",\n    \"pid\": ", T_I64}, {",\n    \"tid\": ", T_I64}, {",\n    \"ts\": ", T_TS}, {",\n    \"dur\": ", T_TS}, \
+    {"\n    ,\n    \"args\": {\n      ", T_NONE}, {"\"External id\": ", T_I64}, {",", T_NONE}, \
+    {"\"cbid\": ", T_U64}, {", \"correlation\": ", T_U64}, {"\n    }\n  },", T_NONE}, \
+    {"\n  {\n    \"ph\": \"s\",\n    \"id\": ", T_U64}, {"\n  {\n    \"ph\": \"f\",\n    \"id\": ", T_U64}, \
+    {",\n    \"pid\": ", T_I64}, {",\n    \"tid\": ", T_I64}, {",\n    \"ts\": ", T_TS}, \
+    {",\n    \"cat\": \"ac2g\",\n    \"name\": \"ac2g\"\n    ", T_NONE}, {", \"bp\": \"e\"", T_NONE}, {FLOW_TAIL, T_NONE}
+
+// -- kernel record (GpuActivity<Kernel>, libkineto/src/CuptiActivity.h:499-576) --
+enum : int { K_HEAD, K_PID, K_TID, K_TS, K_DUR, K_ARGS, K_EXT, K_EXTC, K_QUEUED, K_DEV, K_CTX, K_STREAM, K_CORR, K_REGS, K_SMEM,
+             K_BPS, K_WPS, K_GX, K_GY, K_GZ, K_BX, K_BY, K_BZ, K_OCCPCT, K_ACTIVE, K_LIMIT, K_LREGS, K_LSMEM, K_LWARPS, K_LBLOCKS,
+             K_LBARR, K_AREGS, K_ASMEM, K_GRAPH, K_NODE, K_CHAN, K_CHTYPE, K_CLOSE, K_FLOW, K_FPID, K_FTID, K_FTS, K_FEND, K_COUNT };
+#define K2J_KERNEL_FIELDS \
+    {XHEAD("kernel"), T_NAME}, {"\",\n    \"pid\": ", T_U64}, {",\n    \"tid\": ", T_U64}, {",\n    \"ts\": ", T_TS}, \
+    {",\n    \"dur\": ", T_TS}, {"\n    ,\n    \"args\": {\n      ", T_NONE}, {"\"External id\": ", T_I64}, {",", T_NONE}, \
+    {"\"queued\": ", T_U64}, {", \"device\": ", T_U64}, {", \"context\": ", T_U64}, {", \"stream\": ", T_U64}, \
+    {", \"correlation\": ", T_U64}, {", \"registers per thread\": ", T_U64}, {", \"shared memory\": ", T_I64}, \
+    {", \"blocks per SM\": ", T_DBL}, {", \"warps per SM\": ", T_DBL}, {", \"grid\": [", T_I64}, {", ", T_I64}, {", ", T_I64}, \
+    {"], \"block\": [", T_I64}, {", ", T_I64}, {", ", T_I64}, {"], \"est. achieved occupancy %\": ", T_I64}, \
+    {", \"occupancy\": {\"activeBlocksPerMultiprocessor\": ", T_I64}, {", \"limitingFactors\": \"", T_CSTR}, \
+    {"\", \"blockLimitRegs\": ", T_I64}, {", \"blockLimitSharedMem\": ", T_I64}, {", \"blockLimitWarps\": ", T_I64}, \
+    {", \"blockLimitBlocks\": ", T_I64}, {", \"blockLimitBarriers\": ", T_I64}, {", \"allocatedRegistersPerBlock\": ", T_I64}, \
+    {", \"allocatedSharedMemPerBlock\": ", T_U64}, {"}, \"graph id\": ", T_U64}, {", \"graph node id\": ", T_U64}, \
+    {", \"channel\": ", T_U64}, {", \"channel_type\": ", T_U64}, {"\n    }\n  },", T_NONE}, \
+    {"\n  {\n    \"ph\": \"f\",\n    \"id\": ", T_U64}, {",\n    \"pid\": ", T_U64}, {",\n    \"tid\": ", T_U64}, {",\n    \"ts\": ", T_TS}, \
+    {",\n    \"cat\": \"ac2g\",\n    \"name\": \"ac2g\"\n    , \"bp\": \"e\"\n  },", T_NONE}
+
+// -- memcpy / memcpy2 / memset records (libkineto/src/CuptiActivity.h:586-712) --
+enum : int { M_CPY_KIND, M_CPY_SRC, M_CPY_DST, M_SET_KIND, M_PID, M_TID, M_TS, M_DUR, M_ARGS, M_EXT, M_EXTC, M_FROMDEV, M_INDEV,
+             M_TODEV, M_FROMCTX, M_INCTX, M_TOCTX, M_DEV, M_CTX, M_STREAM, M_CORR, M_BYTES, M_BW, M_GRAPH, M_NODE, M_CHAN, M_CHTYPE,
+             M_CLOSE, M_FLOW, M_FPID, M_FTID, M_FTS, M_FEND, M_COUNT };
+#define K2J_MEM_FIELDS \
+    {XHEAD("gpu_memcpy") "Memcpy ", T_CSTR}, {" (", T_CSTR}, {" -> ", T_CSTR}, {XHEAD("gpu_memset") "Memset (", T_CSTR}, \
+    {")\",\n    \"pid\": ", T_U64}, {",\n    \"tid\": ", T_U64}, {",\n    \"ts\": ", T_TS}, {",\n    \"dur\": ", T_TS}, \
+    {"\n    ,\n    \"args\": {\n      ", T_NONE}, {"\"External id\": ", T_I64}, {",", T_NONE}, \
+    {"\"fromDevice\": ", T_U64}, {", \"inDevice\": ", T_U64}, {", \"toDevice\": ", T_U64}, {", \"fromContext\": ", T_U64}, \
+    {", \"inContext\": ", T_U64}, {", \"toContext\": ", T_U64}, {"\"device\": ", T_U64}, {", \"context\": ", T_U64}, \
+    {", \"stream\": ", T_U64}, {", \"correlation\": ", T_U64}, {", \"bytes\": ", T_U64}, {", \"memory bandwidth (GB/s)\": ", T_DBL}, \
+    {", \"graph id\": ", T_U64}, {", \"graph node id\": ", T_U64}, {", \"channel\": ", T_U64}, {", \"channel_type\": ", T_U64}, \
+    {"\n    }\n  },", T_NONE}, \
+    {"\n  {\n    \"ph\": \"f\",\n    \"id\": ", T_U64}, {",\n    \"pid\": ", T_U64}, {",\n    \"tid\": ", T_U64}, {",\n    \"ts\": ", T_TS}, \
+    {",\n    \"cat\": \"ac2g\",\n    \"name\": \"ac2g\"\n    , \"bp\": \"e\"\n  },", T_NONE}
+
+// -- CPU-side activity: head, (metadata entries are formatted by ev_op itself), tail --
+enum : int { O_CAT, O_NAME, O_PID, O_TID, O_TS, O_DUR, O_PAD, O_ARGS, O_EXT, O_EXTC, O_MD,
+             P_ARGS_CLOSE, P_CLOSE, P_FLOW_S, P_FLOW_F, P_FPID, P_FTID, P_FTS, P_FWDBWD, P_AC2G, P_FBP, P_FEND, O_COUNT };
+#define K2J_OPHEAD_FIELDS \
+    {"\n  {\n    \"ph\": \"X\",\n    \"cat\": \"", T_CSTR}, {"\",\n    \"name\": \"", T_NAME}, {"\",\n    \"pid\": ", T_I64}, \
+    {",\n    \"tid\": ", T_I64}, {",\n    \"ts\": ", T_TS}, {",\n    \"dur\": ", T_TS}, {"\n    ", T_NONE}, \
+    {",\n    \"args\": {\n      ", T_NONE}, {"\"External id\": ", T_I64}, {",", T_NONE}
+#define K2J_OPTAIL_FIELDS \
+    {"\n    }", T_NONE}, {"\n  },", T_NONE}, {"\n  {\n    \"ph\": \"s\",\n    \"id\": ", T_U64}, \
+    {"\n  {\n    \"ph\": \"f\",\n    \"id\": ", T_U64}, {",\n    \"pid\": ", T_I64}, {",\n    \"tid\": ", T_I64}, {",\n    \"ts\": ", T_TS}, \
+    {",\n    \"cat\": \"fwdbwd\",\n    \"name\": \"fwdbwd\"\n    ", T_NONE}, {",\n    \"cat\": \"ac2g\",\n    \"name\": \"ac2g\"\n    ", T_NONE}, \
+    {", \"bp\": \"e\"", T_NONE}, {FLOW_TAIL, T_NONE}
+
+// -- gpu_user_annotation span --
+enum : int { N_HEAD, N_PID, N_TID, N_TS, N_DUR, N_PAD, N_EXT, N_ARGS_CLOSE, N_CLOSE, N_COUNT };
+#define K2J_ANN_FIELDS \
+    {XHEAD("gpu_user_annotation"), T_NAME}, {"\",\n    \"pid\": ", T_U64}, {",\n    \"tid\": ", T_U64}, {",\n    \"ts\": ", T_TS}, \
+    {",\n    \"dur\": ", T_TS}, {"\n    ", T_NONE}, {",\n    \"args\": {\n      \"External id\": ", T_I64}, {"\n    }", T_NONE}, \
+    {"\n  },", T_NONE}
+
+
+// One table for everything: [api][kernel][mem][op head, metadata marker, op tail][annotation][constant strings].
+enum : int { CS_TYPE = 0, CS_MEMCPY_KIND = 29, CS_MEMORY_KIND = 41, CS_LIMIT = 50, CS_COUNT = 82 };
+#define K2J_CSTR_FIELDS \
+    {"cpu_op", 0}, {"user_annotation", 0}, {"gpu_user_annotation", 0}, {"gpu_memcpy", 0}, {"gpu_memset", 0}, {"kernel", 0}, \
+    {"external_correlation", 0}, {"cuda_runtime", 0}, {"cuda_driver", 0}, {"cpu_instant_event", 0}, {"python_function", 0}, \
+    {"overhead", 0}, {"mtia_runtime", 0}, {"mtia_ccp_events", 0}, {"mtia_insight", 0}, {"cuda_sync", 0}, {"cuda_event", 0}, \
+    {"mtia_counters", 0}, {"glow_runtime", 0}, {"cuda_profiler_range", 0}, {"hpu_op", 0}, {"xpu_runtime", 0}, \
+    {"xpu_driver", 0}, {"collective_comm", 0}, {"privateuse1_runtime", 0}, {"privateuse1_driver", 0}, \
+    {"xpu_scope_profiler", 0}, {"xpu_sync", 0}, {"hardware_counters", 0}, \
+    {"<unknown>", 0}, {"HtoD", 0}, {"DtoH", 0}, {"HtoA", 0}, {"AtoH", 0}, {"AtoA", 0}, {"AtoD", 0}, {"DtoA", 0}, {"DtoD", 0}, \
+    {"HtoH", 0}, {"PtoP", 0}, {"<unknown>", 0}, \
+    {"Unknown", 0}, {"Pageable", 0}, {"Pinned", 0}, {"Device", 0}, {"Array", 0}, {"Managed", 0}, {"Device Static", 0}, \
+    {"Managed Static", 0}, {"Unrecognized", 0}, \
+    {"none", 0}, {"WARPS", 0}, {"REGS", 0}, {"WARPS|REGS", 0}, {"SMEM", 0}, {"WARPS|SMEM", 0}, {"REGS|SMEM", 0}, \
+    {"WARPS|REGS|SMEM", 0}, {"BLOCKS", 0}, {"WARPS|BLOCKS", 0}, {"REGS|BLOCKS", 0}, {"WARPS|REGS|BLOCKS", 0}, \
+    {"SMEM|BLOCKS", 0}, {"WARPS|SMEM|BLOCKS", 0}, {"REGS|SMEM|BLOCKS", 0}, {"WARPS|REGS|SMEM|BLOCKS", 0}, {"BARRIERS", 0}, \
+    {"WARPS|BARRIERS", 0}, {"REGS|BARRIERS", 0}, {"WARPS|REGS|BARRIERS", 0}, {"SMEM|BARRIERS", 0}, \
+    {"WARPS|SMEM|BARRIERS", 0}, {"REGS|SMEM|BARRIERS", 0}, {"WARPS|REGS|SMEM|BARRIERS", 0}, {"BLOCKS|BARRIERS", 0}, \
+    {"WARPS|BLOCKS|BARRIERS", 0}, {"REGS|BLOCKS|BARRIERS", 0}, {"WARPS|REGS|BLOCKS|BARRIERS", 0}, \
+    {"SMEM|BLOCKS|BARRIERS", 0}, {"WARPS|SMEM|BLOCKS|BARRIERS", 0}, {"REGS|SMEM|BLOCKS|BARRIERS", 0}, \
+    {"WARPS|REGS|SMEM|BLOCKS|BARRIERS", 0}
+
+
+constexpr int API_BASE = 0, KERNEL_BASE = API_BASE + A_COUNT, MEM_BASE = KERNEL_BASE + K_COUNT, OP_BASE = MEM_BASE + M_COUNT,
+              ANN_BASE = OP_BASE + O_COUNT, CSTR_BASE = ANN_BASE + N_COUNT, FIELD_COUNT = CSTR_BASE + CS_COUNT;
+constexpr FieldSrc kAllFields[] = {K2J_API_FIELDS, K2J_KERNEL_FIELDS, K2J_MEM_FIELDS, K2J_OPHEAD_FIELDS, {"", T_MD},
+                                   K2J_OPTAIL_FIELDS, K2J_ANN_FIELDS, K2J_CSTR_FIELDS};
+static_assert(sizeof(kAllFields) / sizeof(kAllFields[0]) == FIELD_COUNT, "field table and enums disagree");
+constexpr int kAllWords = prog_words(kAllFields);
+__constant__ Prog<FIELD_COUNT, kAllWords> g_fields = make_prog<FIELD_COUNT, kAllWords>(kAllFields);
+
+// ---- value formatting ----------------------------------------------------------------------------------------
+// Sink that writes bytes to a small local buffer; the slow formatters below run against it once and
+// hand the finished text to the real sink as words, which keeps them out of line and the emit kernel small.
+struct BufSink {
+  static constexpr bool kCounting = false;
+  uint8_t* b; int n;
+  __device__ __forceinline__ void put(uint32_t w, int len) { for (int i = 0; i < len; i++) b[n++] = (uint8_t)(w >> (8 * i)); }
+  __device__ __forceinline__ void skip(uint32_t) {}
+};
+// Text of v into buf (zero padded to whole words); returns the length.
+__device__ __noinline__ int fmt_u64_buf(uint64_t v, uint32_t* buf) {
+#pragma unroll
+  for (int i = 0; i < 6; i++) buf[i] = 0;
+  BufSink bs{reinterpret_cast<uint8_t*>(buf), 0};
+  put_u64(bs, v);
+  return bs.n;
+}
+__device__ __noinline__ int fmt_double_buf(double v, uint32_t* buf) {
+#pragma unroll
+  for (int i = 0; i < 8; i++) buf[i] = 0;
+  BufSink bs{reinterpret_cast<uint8_t*>(buf), 0};
+  put_double_value(bs, v);
+  return bs.n;
+}
+__device__ __noinline__ int len_double(double v) {
+  CountSink c;
+  put_double_value(c, v);
+  return (int)c.n;
+}
+
+// Four zero-padded ASCII digits of x < 10^4, most significant digit in the low byte (32-bit SWAR).
+__device__ __forceinline__ uint32_t ascii4(uint32_t x) {
+  const uint32_t q = (x * 5243u) >> 19, r = x - q * 100u;          // x / 100, x % 100
+  const uint32_t pk = q | (r << 16);
+  const uint32_t t = ((pk * 103u) >> 10) & 0x000F000Fu;            // tens of both pairs
+  return (t | ((pk - t * 10u) << 8)) | 0x30303030u;
+}
+// Decimal of v: inline paths below 10^4 and below 10^8 (nearly every field), out of line above.
+template <class S> __device__ __forceinline__ void put_dec(S& s, uint64_t v) {
+  if (S::kCounting) { s.skip((uint32_t)ndigits64(v)); return; }
+  if (v < 10000ull) {
+    const uint32_t x = (uint32_t)v;
+    const int d = 1 + (x >= 10u) + (x >= 100u) + (x >= 1000u);
+    s.put(ascii4(x) >> (8 * (4 - d)), d);
+    return;
+  }
+  if (v < 100000000ull) {
+    const uint32_t x = (uint32_t)v, hi = x / 10000u, lo = x - hi * 10000u;
+    const int d = 1 + (hi >= 10u) + (hi >= 100u) + (hi >= 1000u);  // digits of the upper part (hi >= 1)
+    s.put(ascii4(hi) >> (8 * (4 - d)), d);
+    s.put4(ascii4(lo));
+    return;
+  }
+  put_u64(s, v);
+}
+template <class S> __device__ __forceinline__ void put_dbl(S& s, double v) { put_double_value(s, v); }
+template <class S> __device__ __forceinline__ void put_sdec(S& s, int64_t v) {
+  if (v < 0) { put_char(s, '-'); put_dec(s, 0ull - (uint64_t)v); }
+  else put_dec(s, (uint64_t)v);
+}
+template <class S> __device__ __forceinline__ void put_ts2(S& s, int64_t ns) {  // "{}.{:03}" of ns/1000, ns%1000
+  const uint64_t us = (uint64_t)ns / 1000ull;
+  const uint32_t fr = (uint32_t)((uint64_t)ns - us * 1000ull);
+  put_dec(s, us);
+  if (S::kCounting) { s.skip(4); return; }
+  const uint32_t a = (fr * 41u) >> 12, r = fr - a * 100u, b = (r * 103u) >> 10, c = r - b * 10u;
+  s.put4(0x3030302Eu + (a << 8) + (b << 16) + (c << 24));
+}
+
+template <class S> __device__ __forceinline__ void put_pool_words(S& s, const uint8_t* src, uint32_t len) {
+  s.words(reinterpret_cast<const uint32_t*>(src), len);
 }
 template <class S> __device__ __forceinline__ void put_name(S& s, const Dev& d, uint32_t id, unsigned long long* name_bytes) {
   if (id >= d.n_strings) { atomicAdd(&d.counters->device_check, 1ull); return; }
   const uint32_t len = d.esc_name_len[id];
-  put_pool(s, d.esc_name + esc_name_pos(d, id), len);
+  put_pool_words(s, d.esc_name + esc_name_pos(d, id), len);
   *name_bytes += len;
 }
 template <class S> __device__ __forceinline__ void put_mdstr(S& s, const Dev& d, uint32_t id) {
   if (id >= d.n_strings) { atomicAdd(&d.counters->device_check, 1ull); return; }
-  put_pool(s, d.esc_md + esc_md_pos(d, id), d.esc_md_len[id]);
+  put_pool_words(s, d.esc_md + esc_md_pos(d, id), d.esc_md_len[id]);
 }
 
+__device__ __noinline__ int64_t tsc_convert(uint64_t t, uint64_t t0a, int64_t t0, uint64_t mant, int exp) {
+  return tsc_to_ns(t, t0a, t0, mant, exp);
+}
 __device__ __forceinline__ int64_t conv_ts(const Dev& d, uint64_t t) {
-  return d.ts_mode ? tsc_to_ns(t, d.conv_t0a, d.conv_t0, d.conv_mant, d.conv_exp) : (int64_t)t;
+  return d.ts_mode ? tsc_convert(t, d.conv_t0a, d.conv_t0, d.conv_mant, d.conv_exp) : (int64_t)t;
 }
 __device__ __forceinline__ int64_t conv_dur(const Dev& d, uint64_t s, uint64_t e) {
   return d.ts_mode ? conv_ts(d, e) - conv_ts(d, s) : (int64_t)(e - s);
 }
 __device__ __forceinline__ int64_t rel_ts(const Dev& d, int64_t t) { const int64_t r = t - d.base; return r < 0 ? 0 : r; }
 __device__ __forceinline__ int64_t abs_tid(int64_t t) { return t == INT64_MIN ? 0 : (t < 0 ? -t : t); }
+__device__ __forceinline__ bool out_of_range(const Dev& d, int64_t ts, int64_t dur) {
+  return ts < d.win_start || (ts + dur) > d.win_end;
+}
 
 // linkedActivity(int32_t correlationId, cpuCorrelationMap_) (GenericActivityProfiler.cpp:397-408):
 // the id is sign-extended before the lookup while keys were stored zero-extended, so ids >= 2^31
@@ -618,16 +831,14 @@ __device__ __forceinline__ bool linked_op(const Dev& d, uint32_t corr, int32_t* 
 // GenericActivityProfiler::handleGpuActivity's user-annotation step (GenericActivityProfiler.cpp:424-434)
 // with GpuUserEventMap::insertOrExtendEvent (:292-311): per (device, stream) and annotation op the span
 // [min start, max end] over the GPU activities correlated to it.  Runs in the size pass only.
-__device__ __forceinline__ void span_update(const Dev& d, uint32_t corr, uint32_t dev, uint32_t stream, int64_t ts,
-                                            int64_t dur, uint64_t ev) {
-  if (d.span_key == nullptr) return;
+__device__ __noinline__ void span_update(const Dev& d, uint32_t corr, uint32_t dev, uint32_t stream, int64_t ts,
+                                         int64_t dur, uint64_t ev) {
   const uint32_t idx = tab_find(d.user_tab, d.user_mask, corr);
   if (idx == 0xFFFFFFFFu) return;
   const int64_t ext = (int64_t)d.ext_all[idx].external_id;
   if (ext != (int64_t)(int32_t)ext) return;
   const uint32_t row = tab_find(d.op_tab, d.op_mask, (uint32_t)(int32_t)ext);
   if (row == 0xFFFFFFFFu) return;
-  // (device, stream) -> slot
   const unsigned long long dskey = (((unsigned long long)dev << 32) | stream) + 1ull;
   uint32_t i = hash32(dev * 0x9E3779B1u ^ stream) & d.ds_mask;
   uint32_t probes = 0;
@@ -656,49 +867,22 @@ __device__ __forceinline__ void span_update(const Dev& d, uint32_t corr, uint32_
 
 struct Tally { uint32_t x, flow; unsigned long long name_bytes; uint64_t ev; };
 
-// Shared tail of an "X" event after the name: pid, tid, ts, dur and the opening of args.
-template <class S> __device__ __forceinline__ void x_mid(S& s, int64_t pid, int64_t tid, int64_t ts_rel, int64_t dur) {
-  K2J_LIT(s, "\",\n    \"pid\": "); put_i64(s, pid);
-  K2J_LIT(s, ",\n    \"tid\": "); put_i64(s, tid);
-  K2J_LIT(s, ",\n    \"ts\": "); put_ts(s, ts_rel);
-  K2J_LIT(s, ",\n    \"dur\": "); put_ts(s, dur);
-  K2J_LIT(s, "\n    ");
-}
-template <class S> __device__ __forceinline__ void flow_event(S& s, bool start, bool fwdbwd, uint64_t id, int64_t pid, int64_t tid, int64_t ts_rel) {
-  if (start) K2J_LIT(s, "\n  {\n    \"ph\": \"s\",\n    \"id\": "); else K2J_LIT(s, "\n  {\n    \"ph\": \"f\",\n    \"id\": ");
-  put_u64(s, id);
-  K2J_LIT(s, ",\n    \"pid\": "); put_i64(s, pid);
-  K2J_LIT(s, ",\n    \"tid\": "); put_i64(s, tid);
-  K2J_LIT(s, ",\n    \"ts\": "); put_ts(s, ts_rel);
-  if (fwdbwd) K2J_LIT(s, ",\n    \"cat\": \"fwdbwd\",\n    \"name\": \"fwdbwd\"\n    ");
-  else K2J_LIT(s, ",\n    \"cat\": \"ac2g\",\n    \"name\": \"ac2g\"\n    ");
-  if (!start) K2J_LIT(s, ", \"bp\": \"e\"");
-  K2J_LIT(s, "\n  },");
-}
-template <class S> __device__ __forceinline__ void args_open_ext(S& s, bool has_ext, int32_t ext) {
-  K2J_LIT(s, ",\n    \"args\": {\n      ");
-  if (has_ext) { K2J_LIT(s, "\"External id\": "); put_i64(s, ext); put_char(s, ','); }
-}
-template <class S> __device__ __forceinline__ void graph_channel(S& s, uint32_t graph, uint64_t node, uint32_t ch, uint32_t cht) {
-  K2J_LIT(s, ", \"graph id\": "); put_u64(s, graph);
-  K2J_LIT(s, ", \"graph node id\": "); put_u64(s, node);
-  K2J_LIT(s, ", \"channel\": "); put_u64(s, ch);
-  K2J_LIT(s, ", \"channel_type\": "); put_u64(s, cht);
-}
-template <class S> __device__ __forceinline__ void bandwidth(S& s, uint64_t bytes, int64_t dur) {
-  if (dur == 0) return;  // addBandwidthTypedMetadata, CuptiActivity.h:460-470
-  K2J_LIT(s, ", \"memory bandwidth (GB/s)\": ");
-  put_double_value(s, __ddiv_rn(__ull2double_rn(bytes), __ll2double_rn(dur)));
-}
+// Per-event values that are computed rather than read straight from the record.  They stay in
+// registers; everything else is re-read from the record (an L1 hit) when its field comes up.
+struct EvCtx {
+  const uint8_t* r; uint64_t j;
+  int64_t ts_rel, dur, flow_ts_rel, pid, tid;
+  int32_t ext; uint32_t corr, name, aux;   // aux: cbid (api), activity type (op)
+  uint64_t d0, d1;                          // doubles as bits: blocks/warps per SM, or bandwidth
+  int32_t occ_pct, occ_active, occ_limit, occ_lregs, occ_lsmem, occ_lwarps, occ_lblocks, occ_lbarr, occ_aregs;
+  uint64_t occ_asmem;
+};
 
-__device__ __forceinline__ bool out_of_range(const Dev& d, int64_t ts, int64_t dur) {
-  return ts < d.win_start || (ts + dur) > d.win_end;
-}
+// Each gather returns false if the record produces no event (`*filt`: 1 blocklisted, 2 outside the window).
 
-// ---- runtime / driver API record (handleRuntimeActivity / handleDriverActivity) ----
-template <class S> __device__ __forceinline__ bool ev_api(S& s, const Dev& d, const uint8_t* r, Tally& t, uint32_t* filt) {
-  // 40-byte records are only 8-byte aligned: 64-bit loads
-  const uint2 a = *reinterpret_cast<const uint2*>(r);        // kind, cbid
+// handleRuntimeActivity / handleDriverActivity (libkineto/src/CuptiActivityProfiler.cpp:304-358)
+__device__ __forceinline__ bool gather_api(const Dev& d, const uint8_t* r, EvCtx& c, uint64_t* present, Tally& t, uint32_t* filt) {
+  const uint2 a = *reinterpret_cast<const uint2*>(r);        // kind, cbid (40-byte records are 8-byte aligned)
   const uint64_t st = *reinterpret_cast<const uint64_t*>(r + 8), en = *reinterpret_cast<const uint64_t*>(r + 16);
   const uint2 b = *reinterpret_cast<const uint2*>(r + 24);   // processId, threadId
   const uint32_t corr = *reinterpret_cast<const uint32_t*>(r + 32);
@@ -724,45 +908,43 @@ template <class S> __device__ __forceinline__ bool ev_api(S& s, const Dev& d, co
   }
   int32_t ext = 0;
   const bool has_ext = linked_op(d, corr, &ext) && ext != 0;
-  if (driver) K2J_LIT(s, "\n  {\n    \"ph\": \"X\",\n    \"cat\": \"cuda_driver\",\n    \"name\": \"");
-  else K2J_LIT(s, "\n  {\n    \"ph\": \"X\",\n    \"cat\": \"cuda_runtime\",\n    \"name\": \"");
   const uint32_t ntab = driver ? d.n_dr : d.n_rt;
-  if (cbid < ntab) put_name(s, d, (driver ? d.dr_names : d.rt_names)[cbid], &t.name_bytes);
-  else K2J_LIT(s, "INVALID");
-  const int64_t tid_out = abs_tid(tid), ts_rel = rel_ts(d, ts);
-  x_mid(s, d.pid, tid_out, ts_rel, dur < 0 ? 0 : dur);
-  args_open_ext(s, has_ext, ext);
-  K2J_LIT(s, "\"cbid\": "); put_u64(s, cbid);
-  K2J_LIT(s, ", \"correlation\": "); put_u64(s, corr);
-  K2J_LIT(s, "\n    }\n  },");
+  const bool named = cbid < ntab;
+  c.ts_rel = rel_ts(d, ts); c.dur = dur < 0 ? 0 : dur; c.pid = d.pid; c.tid = abs_tid(tid); c.ext = ext; c.corr = corr;
+  c.aux = cbid; c.name = named ? (driver ? d.dr_names : d.rt_names)[cbid] : 0u;
+  uint64_t p = 0;
+  auto on = [&](int f) { p |= 1ull << f; };
+  on(driver ? A_HEAD_DR : A_HEAD_RT); on(named ? A_NAME : A_INVALID);
+  on(A_PID); on(A_TID); on(A_TS); on(A_DUR); on(A_ARGS);
+  if (has_ext) { on(A_EXT); on(A_EXTC); }
+  on(A_CBID); on(A_CORR); on(A_CLOSE);
   t.x++;
-  if (corr > 0) { flow_event(s, flow_start, false, corr, d.pid, tid_out, ts_rel); t.flow++; }
+  if (corr > 0) {
+    on(flow_start ? A_FLOW_S : A_FLOW_F); on(A_FPID); on(A_FTID); on(A_FTS); on(A_FCAT);
+    if (!flow_start) on(A_FBP);
+    on(A_FEND);
+    t.flow++;
+  }
+  *present = p;
   return true;
 }
+__device__ __forceinline__ uint64_t value_api(int f, const EvCtx& c) {
+  switch (f) {
+    case A_NAME: return c.name;
+    case A_PID: case A_FPID: return (uint64_t)c.pid;
+    case A_TID: case A_FTID: return (uint64_t)c.tid;
+    case A_TS: case A_FTS: return (uint64_t)c.ts_rel;
+    case A_DUR: return (uint64_t)c.dur;
+    case A_EXT: return (uint64_t)(int64_t)c.ext;
+    case A_CBID: return c.aux;
+    default: return c.corr;  // A_CORR, A_FLOW_S, A_FLOW_F
+  }
+}
 
-// ---- kernel record (GpuActivity<Kernel>, CuptiActivity.h:499-576) ----
-template <class S> __device__ __forceinline__ bool ev_kernel(S& s, const Dev& d, const uint8_t* r, Tally& t, uint32_t* filt) {
-  const uint64_t st = *reinterpret_cast<const uint64_t*>(r + 16), en = *reinterpret_cast<const uint64_t*>(r + 24);
-  const int64_t ts = conv_ts(d, st), dur = conv_dur(d, st, en);
-  if (out_of_range(d, ts, dur)) { *filt = 2; return false; }
-  const uint32_t dev = *reinterpret_cast<const uint32_t*>(r + 40), ctx = *reinterpret_cast<const uint32_t*>(r + 44);
-  const uint32_t stream = *reinterpret_cast<const uint32_t*>(r + 48), corr = *reinterpret_cast<const uint32_t*>(r + 92);
-  const int32_t gx = *reinterpret_cast<const int32_t*>(r + 52), gy = *reinterpret_cast<const int32_t*>(r + 56), gz = *reinterpret_cast<const int32_t*>(r + 60);
-  const int32_t bx = *reinterpret_cast<const int32_t*>(r + 64), by = *reinterpret_cast<const int32_t*>(r + 68), bz = *reinterpret_cast<const int32_t*>(r + 72);
-  const int32_t ssm = *reinterpret_cast<const int32_t*>(r + 76), dsm = *reinterpret_cast<const int32_t*>(r + 80);
-  const uint32_t regs = *reinterpret_cast<const uint16_t*>(r + 6);
-  const uint32_t name_id = (uint32_t)*reinterpret_cast<const uint64_t*>(r + 104);
-  int32_t ext = 0;
-  const bool has_ext = linked_op(d, corr, &ext) && ext != 0;
-
-  // blocksPerSm / warpsPerSm / computeOccupancyMetrics (DeviceProperties.cpp:161-222): 32-bit wrapping
-  // products, single-precision arithmetic without contraction.
-  const int32_t grid_prod = (int32_t)((uint32_t)gx * (uint32_t)gy * (uint32_t)gz);
-  const int32_t block_prod = (int32_t)((uint32_t)bx * (uint32_t)by * (uint32_t)bz);
-  const bool have_dev = dev < (uint32_t)d.n_devices;
-  const int sm_count = have_dev ? d.props[dev].num_sms : 0;
-  const float bps = sm_count == 0 ? __int_as_float(0x7f800000) : __fdiv_rn(__int2float_rn(grid_prod), __int2float_rn(sm_count));
-  const float wps = __fdiv_rn(__fmul_rn(bps, __int2float_rn(block_prod)), 32.0f);
+// computeOccupancyMetrics (libkineto/src/DeviceProperties.cpp:176-222) with NVIDIA's occupancy calculator.
+__device__ __forceinline__ void occupancy_metrics(const Dev& d, uint32_t dev, bool have_dev, int sm_count, int32_t grid_prod,
+                                               int32_t block_prod, uint32_t regs, int32_t ssm, int32_t dsm, cudaOccResult* out,
+                                               float* occupancy_out) {
   cudaOccResult occ;
   occ.activeBlocksPerMultiprocessor = 0; occ.limitingFactors = 0; occ.blockLimitRegs = 0; occ.blockLimitWarps = 0;
   occ.blockLimitSharedMem = 0; occ.blockLimitBlocks = 0; occ.blockLimitBarriers = 0; occ.allocatedRegistersPerBlock = 0;
@@ -788,113 +970,149 @@ template <class S> __device__ __forceinline__ bool ev_kernel(S& s, const Dev& d,
       occupancy = __fdiv_rn(__fmul_rn(eff, __int2float_rn(block_prod)), __int2float_rn(dp.max_threads_per_sm));
     }
   }
-  const long long occ_pct = llround(__dmul_rn((double)occupancy, 100.0));
+  *out = occ;
+  *occupancy_out = occupancy;
+}
 
-  K2J_LIT(s, "\n  {\n    \"ph\": \"X\",\n    \"cat\": \"kernel\",\n    \"name\": \"");
-  put_name(s, d, name_id, &t.name_bytes);
-  const int64_t ts_rel = rel_ts(d, ts);
-  x_mid(s, (int64_t)dev, (int64_t)stream, ts_rel, dur < 0 ? 0 : dur);
-  args_open_ext(s, has_ext, ext);
-  K2J_LIT(s, "\"queued\": "); put_u64(s, *reinterpret_cast<const uint64_t*>(r + 120));
-  K2J_LIT(s, ", \"device\": "); put_u64(s, dev);
-  K2J_LIT(s, ", \"context\": "); put_u64(s, ctx);
-  K2J_LIT(s, ", \"stream\": "); put_u64(s, stream);
-  K2J_LIT(s, ", \"correlation\": "); put_u64(s, corr);
-  K2J_LIT(s, ", \"registers per thread\": "); put_u64(s, regs);
-  K2J_LIT(s, ", \"shared memory\": "); put_i64(s, (int64_t)(int32_t)((uint32_t)ssm + (uint32_t)dsm));
-  K2J_LIT(s, ", \"blocks per SM\": "); put_double_value(s, (double)bps);
-  K2J_LIT(s, ", \"warps per SM\": "); put_double_value(s, (double)wps);
-  K2J_LIT(s, ", \"grid\": ["); put_i64(s, gx); K2J_LIT(s, ", "); put_i64(s, gy); K2J_LIT(s, ", "); put_i64(s, gz);
-  K2J_LIT(s, "], \"block\": ["); put_i64(s, bx); K2J_LIT(s, ", "); put_i64(s, by); K2J_LIT(s, ", "); put_i64(s, bz);
-  K2J_LIT(s, "], \"est. achieved occupancy %\": "); put_i64(s, occ_pct);
-  K2J_LIT(s, ", \"occupancy\": {\"activeBlocksPerMultiprocessor\": "); put_i64(s, occ.activeBlocksPerMultiprocessor);
-  K2J_LIT(s, ", \"limitingFactors\": \"");
-  {  // limitingFactorsToString, CuptiActivity.h:476-497
-    const unsigned f = occ.limitingFactors;
-    if (f == 0) K2J_LIT(s, "none");
-    else {
-      bool first = true;
-      if (f & OCC_LIMIT_WARPS) { K2J_LIT(s, "WARPS"); first = false; }
-      if (f & OCC_LIMIT_REGISTERS) { if (!first) put_char(s, '|'); K2J_LIT(s, "REGS"); first = false; }
-      if (f & OCC_LIMIT_SHARED_MEMORY) { if (!first) put_char(s, '|'); K2J_LIT(s, "SMEM"); first = false; }
-      if (f & OCC_LIMIT_BLOCKS) { if (!first) put_char(s, '|'); K2J_LIT(s, "BLOCKS"); first = false; }
-      if (f & OCC_LIMIT_BARRIERS) { if (!first) put_char(s, '|'); K2J_LIT(s, "BARRIERS"); first = false; }
-    }
-  }
-  K2J_LIT(s, "\", \"blockLimitRegs\": "); put_i64(s, occ.blockLimitRegs);
-  K2J_LIT(s, ", \"blockLimitSharedMem\": "); put_i64(s, occ.blockLimitSharedMem);
-  K2J_LIT(s, ", \"blockLimitWarps\": "); put_i64(s, occ.blockLimitWarps);
-  K2J_LIT(s, ", \"blockLimitBlocks\": "); put_i64(s, occ.blockLimitBlocks);
-  K2J_LIT(s, ", \"blockLimitBarriers\": "); put_i64(s, occ.blockLimitBarriers);
-  K2J_LIT(s, ", \"allocatedRegistersPerBlock\": "); put_i64(s, occ.allocatedRegistersPerBlock);
-  K2J_LIT(s, ", \"allocatedSharedMemPerBlock\": "); put_u64(s, (uint64_t)occ.allocatedSharedMemPerBlock);
-  put_char(s, '}');
-  graph_channel(s, *reinterpret_cast<const uint32_t*>(r + 156), *reinterpret_cast<const uint64_t*>(r + 144),
-                *reinterpret_cast<const uint32_t*>(r + 168), *reinterpret_cast<const uint32_t*>(r + 172));
-  K2J_LIT(s, "\n    }\n  },");
+// GpuActivity<Kernel> (libkineto/src/CuptiActivity.h:499-576)
+__device__ __forceinline__ bool gather_kernel(const Dev& d, const uint8_t* r, EvCtx& c, uint64_t* present, Tally& t, uint32_t* filt,
+                                              bool counting) {
+  const uint64_t st = *reinterpret_cast<const uint64_t*>(r + 16), en = *reinterpret_cast<const uint64_t*>(r + 24);
+  const int64_t ts = conv_ts(d, st), dur = conv_dur(d, st, en);
+  if (out_of_range(d, ts, dur)) { *filt = 2; return false; }
+  const uint32_t dev = *reinterpret_cast<const uint32_t*>(r + 40);
+  const uint32_t stream = *reinterpret_cast<const uint32_t*>(r + 48), corr = *reinterpret_cast<const uint32_t*>(r + 92);
+  const int32_t gx = *reinterpret_cast<const int32_t*>(r + 52), gy = *reinterpret_cast<const int32_t*>(r + 56), gz = *reinterpret_cast<const int32_t*>(r + 60);
+  const int32_t bx = *reinterpret_cast<const int32_t*>(r + 64), by = *reinterpret_cast<const int32_t*>(r + 68), bz = *reinterpret_cast<const int32_t*>(r + 72);
+  const int32_t ssm = *reinterpret_cast<const int32_t*>(r + 76), dsm = *reinterpret_cast<const int32_t*>(r + 80);
+  const uint32_t regs = *reinterpret_cast<const uint16_t*>(r + 6);
+  int32_t ext = 0;
+  const bool has_ext = linked_op(d, corr, &ext) && ext != 0;
+  // blocksPerSm / warpsPerSm (DeviceProperties.cpp:161-174): 32-bit wrapping products, single-precision
+  // arithmetic without contraction.
+  const int32_t grid_prod = (int32_t)((uint32_t)gx * (uint32_t)gy * (uint32_t)gz);
+  const int32_t block_prod = (int32_t)((uint32_t)bx * (uint32_t)by * (uint32_t)bz);
+  const bool have_dev = dev < (uint32_t)d.n_devices;
+  const int sm_count = have_dev ? d.props[dev].num_sms : 0;
+  const float bps = sm_count == 0 ? __int_as_float(0x7f800000) : __fdiv_rn(__int2float_rn(grid_prod), __int2float_rn(sm_count));
+  const float wps = __fdiv_rn(__fmul_rn(bps, __int2float_rn(block_prod)), 32.0f);
+  cudaOccResult occ;
+  float occupancy;
+  occupancy_metrics(d, dev, have_dev, sm_count, grid_prod, block_prod, regs, ssm, dsm, &occ, &occupancy);
+  c.occ_pct = (int32_t)llround(__dmul_rn((double)occupancy, 100.0));
+  c.occ_active = occ.activeBlocksPerMultiprocessor; c.occ_limit = CS_LIMIT + (int)(occ.limitingFactors & 31u);
+  c.occ_lregs = occ.blockLimitRegs; c.occ_lsmem = occ.blockLimitSharedMem; c.occ_lwarps = occ.blockLimitWarps;
+  c.occ_lblocks = occ.blockLimitBlocks; c.occ_lbarr = occ.blockLimitBarriers; c.occ_aregs = occ.allocatedRegistersPerBlock;
+  c.occ_asmem = (uint64_t)occ.allocatedSharedMemPerBlock;
+  c.d0 = (uint64_t)__double_as_longlong((double)bps); c.d1 = (uint64_t)__double_as_longlong((double)wps);
+  c.ts_rel = rel_ts(d, ts); c.dur = dur < 0 ? 0 : dur; c.pid = dev; c.tid = stream; c.ext = ext; c.corr = corr;
+  uint64_t p = (1ull << K_COUNT) - 1ull;  // every field except the optional ones below
+  if (!has_ext) p &= ~((1ull << K_EXT) | (1ull << K_EXTC));
   t.x++;
-  if (corr > 0) { flow_event(s, false, false, corr, (int64_t)dev, (int64_t)stream, ts_rel); t.flow++; }
-  if (S::kCounting) span_update(d, corr, dev, stream, ts, dur, t.ev);
+  if (corr > 0) t.flow++;
+  else p &= ~((1ull << K_FLOW) | (1ull << K_FPID) | (1ull << K_FTID) | (1ull << K_FTS) | (1ull << K_FEND));
+  *present = p;
+  if (counting && d.span_key != nullptr) span_update(d, corr, dev, stream, ts, dur, t.ev);
   return true;
 }
-
-template <class S> __device__ __forceinline__ void memcpy_name(S& s, uint32_t kind, uint32_t src, uint32_t dst) {
-  K2J_LIT(s, "Memcpy "); put_cstr(s, kMemcpyKind[kind <= 10 ? kind : 11]);
-  K2J_LIT(s, " ("); put_cstr(s, kMemoryKind[src <= 7 ? src : 8]);
-  K2J_LIT(s, " -> "); put_cstr(s, kMemoryKind[dst <= 7 ? dst : 8]);
-  put_char(s, ')');
+__device__ __forceinline__ uint64_t value_kernel(int f, const EvCtx& c) {
+  const uint8_t* r = c.r;
+  switch (f) {
+    case K_HEAD: return (uint32_t)*reinterpret_cast<const uint64_t*>(r + 104);
+    case K_PID: case K_FPID: case K_DEV: return (uint64_t)c.pid;
+    case K_TID: case K_FTID: case K_STREAM: return (uint64_t)c.tid;
+    case K_TS: case K_FTS: return (uint64_t)c.ts_rel;
+    case K_DUR: return (uint64_t)c.dur;
+    case K_EXT: return (uint64_t)(int64_t)c.ext;
+    case K_QUEUED: return *reinterpret_cast<const uint64_t*>(r + 120);
+    case K_CTX: return *reinterpret_cast<const uint32_t*>(r + 44);
+    case K_CORR: case K_FLOW: return c.corr;
+    case K_REGS: return *reinterpret_cast<const uint16_t*>(r + 6);
+    case K_SMEM: return (uint64_t)(int64_t)(int32_t)(*reinterpret_cast<const uint32_t*>(r + 76) + *reinterpret_cast<const uint32_t*>(r + 80));
+    case K_BPS: return c.d0;
+    case K_WPS: return c.d1;
+    case K_GX: case K_GY: case K_GZ: return (uint64_t)(int64_t)*reinterpret_cast<const int32_t*>(r + 52 + 4 * (f - K_GX));
+    case K_BX: case K_BY: case K_BZ: return (uint64_t)(int64_t)*reinterpret_cast<const int32_t*>(r + 64 + 4 * (f - K_BX));
+    case K_OCCPCT: return (uint64_t)(int64_t)c.occ_pct;
+    case K_ACTIVE: return (uint64_t)(int64_t)c.occ_active;
+    case K_LIMIT: return (uint64_t)c.occ_limit;
+    case K_LREGS: return (uint64_t)(int64_t)c.occ_lregs;
+    case K_LSMEM: return (uint64_t)(int64_t)c.occ_lsmem;
+    case K_LWARPS: return (uint64_t)(int64_t)c.occ_lwarps;
+    case K_LBLOCKS: return (uint64_t)(int64_t)c.occ_lblocks;
+    case K_LBARR: return (uint64_t)(int64_t)c.occ_lbarr;
+    case K_AREGS: return (uint64_t)(int64_t)c.occ_aregs;
+    case K_ASMEM: return c.occ_asmem;
+    case K_GRAPH: return *reinterpret_cast<const uint32_t*>(r + 156);
+    case K_NODE: return *reinterpret_cast<const uint64_t*>(r + 144);
+    case K_CHAN: return *reinterpret_cast<const uint32_t*>(r + 168);
+    default: return *reinterpret_cast<const uint32_t*>(r + 172);  // K_CHTYPE
+  }
 }
 
-// ---- memcpy / memcpy2 / memset records (CuptiActivity.h:604-712) ----
-template <class S, int CLS> __device__ __forceinline__ bool ev_mem(S& s, const Dev& d, const uint8_t* r, Tally& t, uint32_t* filt) {
+// memcpy / memcpy2 / memset records (libkineto/src/CuptiActivity.h:586-712)
+template <int CLS>
+__device__ __forceinline__ bool gather_mem(const Dev& d, const uint8_t* r, EvCtx& c, uint64_t* present, Tally& t, uint32_t* filt,
+                                           bool counting) {
   const uint64_t st = *reinterpret_cast<const uint64_t*>(r + 16), en = *reinterpret_cast<const uint64_t*>(r + 24);
   const int64_t ts = conv_ts(d, st), dur = conv_dur(d, st, en);
   if (out_of_range(d, ts, dur)) { *filt = 2; return false; }
   const uint64_t bytes = *reinterpret_cast<const uint64_t*>(r + 8);
-  const uint32_t dev = *reinterpret_cast<const uint32_t*>(r + 32), ctx = *reinterpret_cast<const uint32_t*>(r + 36);
-  const uint32_t stream = *reinterpret_cast<const uint32_t*>(r + 40);
+  const uint32_t dev = *reinterpret_cast<const uint32_t*>(r + 32), stream = *reinterpret_cast<const uint32_t*>(r + 40);
   const uint32_t corr = *reinterpret_cast<const uint32_t*>(r + (CLS == C_MEMCPY2 ? 60 : 44));
   int32_t ext = 0;
   const bool has_ext = linked_op(d, corr, &ext) && ext != 0;
-  if (CLS == C_MEMSET) {
-    K2J_LIT(s, "\n  {\n    \"ph\": \"X\",\n    \"cat\": \"gpu_memset\",\n    \"name\": \"Memset (");
-    const uint32_t mk = *reinterpret_cast<const uint16_t*>(r + 50);
-    put_cstr(s, kMemoryKind[mk <= 7 ? mk : 8]);
-    put_char(s, ')');
-  } else {
-    K2J_LIT(s, "\n  {\n    \"ph\": \"X\",\n    \"cat\": \"gpu_memcpy\",\n    \"name\": \"");
-    memcpy_name(s, r[4], r[5], r[6]);
+  c.ts_rel = rel_ts(d, ts); c.dur = dur < 0 ? 0 : dur; c.pid = dev; c.tid = stream; c.ext = ext; c.corr = corr;
+  c.aux = CLS == C_MEMCPY2 ? 8u : 0u;  // byte shift of the trailing fields in the peer-to-peer layout
+  uint64_t p = 0;
+  auto on = [&](int f) { p |= 1ull << f; };
+  if (CLS == C_MEMSET) on(M_SET_KIND); else { on(M_CPY_KIND); on(M_CPY_SRC); on(M_CPY_DST); }
+  on(M_PID); on(M_TID); on(M_TS); on(M_DUR); on(M_ARGS);
+  if (has_ext) { on(M_EXT); on(M_EXTC); }
+  if (CLS == C_MEMCPY2) { on(M_FROMDEV); on(M_INDEV); on(M_TODEV); on(M_FROMCTX); on(M_INCTX); on(M_TOCTX); }
+  else { on(M_DEV); on(M_CTX); }
+  on(M_STREAM); on(M_CORR); on(M_BYTES);
+  if (dur != 0) {  // addBandwidthTypedMetadata, CuptiActivity.h:460-470
+    on(M_BW);
+    c.d0 = (uint64_t)__double_as_longlong(__ddiv_rn(__ull2double_rn(bytes), __ll2double_rn(dur)));
   }
-  const int64_t ts_rel = rel_ts(d, ts);
-  x_mid(s, (int64_t)dev, (int64_t)stream, ts_rel, dur < 0 ? 0 : dur);
-  args_open_ext(s, has_ext, ext);
-  if (CLS == C_MEMCPY2) {
-    K2J_LIT(s, "\"fromDevice\": "); put_u64(s, *reinterpret_cast<const uint32_t*>(r + 44));
-    K2J_LIT(s, ", \"inDevice\": "); put_u64(s, dev);
-    K2J_LIT(s, ", \"toDevice\": "); put_u64(s, *reinterpret_cast<const uint32_t*>(r + 52));
-    K2J_LIT(s, ", \"fromContext\": "); put_u64(s, *reinterpret_cast<const uint32_t*>(r + 48));
-    K2J_LIT(s, ", \"inContext\": "); put_u64(s, ctx);
-    K2J_LIT(s, ", \"toContext\": "); put_u64(s, *reinterpret_cast<const uint32_t*>(r + 56));
-  } else {
-    K2J_LIT(s, "\"device\": "); put_u64(s, dev);
-    K2J_LIT(s, ", \"context\": "); put_u64(s, ctx);
-  }
-  K2J_LIT(s, ", \"stream\": "); put_u64(s, stream);
-  K2J_LIT(s, ", \"correlation\": "); put_u64(s, corr);
-  K2J_LIT(s, ", \"bytes\": "); put_u64(s, bytes);
-  bandwidth(s, bytes, dur);
-  constexpr int g = CLS == C_MEMCPY2 ? 8 : 0;
-  graph_channel(s, *reinterpret_cast<const uint32_t*>(r + 72 + g), *reinterpret_cast<const uint64_t*>(r + 64 + g),
-                *reinterpret_cast<const uint32_t*>(r + 76 + g), *reinterpret_cast<const uint32_t*>(r + 80 + g));
-  K2J_LIT(s, "\n    }\n  },");
+  on(M_GRAPH); on(M_NODE); on(M_CHAN); on(M_CHTYPE); on(M_CLOSE);
   t.x++;
-  if (corr > 0) { flow_event(s, false, false, corr, (int64_t)dev, (int64_t)stream, ts_rel); t.flow++; }
-  if (S::kCounting) span_update(d, corr, dev, stream, ts, dur, t.ev);
+  if (corr > 0) { on(M_FLOW); on(M_FPID); on(M_FTID); on(M_FTS); on(M_FEND); t.flow++; }
+  *present = p;
+  if (counting && d.span_key != nullptr) span_update(d, corr, dev, stream, ts, dur, t.ev);
   return true;
 }
+__device__ __forceinline__ uint64_t value_mem(int f, const EvCtx& c) {
+  const uint8_t* r = c.r;
+  const uint32_t g = c.aux;
+  switch (f) {
+    case M_CPY_KIND: { const uint32_t k = r[4]; return CS_MEMCPY_KIND + (k <= 10 ? k : 11); }
+    case M_CPY_SRC: { const uint32_t k = r[5]; return CS_MEMORY_KIND + (k <= 7 ? k : 8); }
+    case M_CPY_DST: { const uint32_t k = r[6]; return CS_MEMORY_KIND + (k <= 7 ? k : 8); }
+    case M_SET_KIND: { const uint32_t k = *reinterpret_cast<const uint16_t*>(r + 50); return CS_MEMORY_KIND + (k <= 7 ? k : 8); }
+    case M_PID: case M_FPID: case M_DEV: case M_INDEV: return (uint64_t)c.pid;
+    case M_TID: case M_FTID: case M_STREAM: return (uint64_t)c.tid;
+    case M_TS: case M_FTS: return (uint64_t)c.ts_rel;
+    case M_DUR: return (uint64_t)c.dur;
+    case M_EXT: return (uint64_t)(int64_t)c.ext;
+    case M_FROMDEV: return *reinterpret_cast<const uint32_t*>(r + 44);
+    case M_TODEV: return *reinterpret_cast<const uint32_t*>(r + 52);
+    case M_FROMCTX: return *reinterpret_cast<const uint32_t*>(r + 48);
+    case M_INCTX: case M_CTX: return *reinterpret_cast<const uint32_t*>(r + 36);
+    case M_TOCTX: return *reinterpret_cast<const uint32_t*>(r + 56);
+    case M_CORR: case M_FLOW: return c.corr;
+    case M_BYTES: return *reinterpret_cast<const uint64_t*>(r + 8);
+    case M_BW: return c.d0;
+    case M_GRAPH: return *reinterpret_cast<const uint32_t*>(r + 72 + g);
+    case M_NODE: return *reinterpret_cast<const uint64_t*>(r + 64 + g);
+    case M_CHAN: return *reinterpret_cast<const uint32_t*>(r + 76 + g);
+    default: return *reinterpret_cast<const uint32_t*>(r + 80 + g);  // M_CHTYPE
+  }
+}
 
-// ---- CPU-side activity (ChromeTraceLogger::handleActivity for a GenericTraceActivity) ----
-template <class S> __device__ __forceinline__ bool ev_op(S& s, const Dev& d, uint64_t i, Tally& t) {
+// CPU-side activity: ChromeTraceLogger::handleActivity for a GenericTraceActivity (output_json.cpp:837-963)
+__device__ __forceinline__ bool gather_op(const Dev& d, uint64_t i, EvCtx& c, uint64_t* present, Tally& t) {
   const int32_t type = d.op_type[i];
   if ((uint32_t)type >= 29u) { atomicAdd(&d.counters->device_check, 1ull); return false; }
   if (!((d.type_mask >> type) & 1u)) return false;  // type not selected: joins, but is not logged
@@ -911,49 +1129,130 @@ template <class S> __device__ __forceinline__ bool ev_op(S& s, const Dev& d, uin
   int32_t ext = 0;
   const bool excluded = type == 3 || type == 4 || type == 5 || type == 7 || type == 8 || type == 21 || type == 22 || type == 24 || type == 25;
   if (!excluded) ext = d.op_id[i];
-  const uint32_t m0 = d.op_mdoff[i], m1 = d.op_mdoff[i + 1];
-  K2J_LIT(s, "\n  {\n    \"ph\": \"X\",\n    \"cat\": \"");
-  put_cstr(s, kTypeNames[type]);
-  K2J_LIT(s, "\",\n    \"name\": \"");
-  put_name(s, d, d.op_name[i], &t.name_bytes);
-  const int64_t pid = op_pid(d, d.op_device[i]), tid = abs_tid(d.op_resource[i]);
-  x_mid(s, pid, tid, rel_ts(d, ts), dur);
-  if (ext != 0 || m1 > m0) {
-    K2J_LIT(s, ",\n    \"args\": {\n      ");
-    if (ext != 0) { K2J_LIT(s, "\"External id\": "); put_i64(s, ext); if (m1 > m0) put_char(s, ','); }
-    for (uint32_t e = m0; e < m1; e++) {  // JsonTypedMetadataVisitor, TypedMetadataJson.h:72-158
-      const MdEntry md = d.md[e];
-      if (e > m0) K2J_LIT(s, ", ");
-      put_char(s, '"'); put_mdstr(s, d, md.key); K2J_LIT(s, "\": ");
-      switch (md.type) {
-        case 0: put_i64(s, (int64_t)md.value); break;
-        case 1: put_u64(s, md.value); break;
-        case 2: put_double_value(s, __longlong_as_double((long long)md.value)); break;
-        case 3: if (md.value) K2J_LIT(s, "true"); else K2J_LIT(s, "false"); break;
-        case 4: put_char(s, '"'); put_mdstr(s, d, (uint32_t)md.value); put_char(s, '"'); break;
-        default: put_mdstr(s, d, (uint32_t)md.value); break;
-      }
-    }
-    K2J_LIT(s, "\n    }");
-  }
-  K2J_LIT(s, "\n  },");
+  const bool has_md = d.op_mdoff[i + 1] > d.op_mdoff[i];
+  const bool has_args = ext != 0 || has_md;
+  c.ts_rel = rel_ts(d, ts); c.dur = dur; c.flow_ts_rel = rel_ts(d, flow_ts);
+  c.pid = op_pid(d, d.op_device[i]); c.tid = abs_tid(d.op_resource[i]); c.ext = ext; c.aux = (uint32_t)type;
+  c.name = d.op_name[i]; c.corr = d.op_flow[i];
+  uint64_t p = 0;
+  auto on = [&](int f) { p |= 1ull << f; };
+  on(O_CAT); on(O_NAME); on(O_PID); on(O_TID); on(O_TS); on(O_DUR); on(O_PAD);
+  if (has_args) on(O_ARGS);
+  if (ext != 0) { on(O_EXT); if (has_md) on(O_EXTC); }
+  if (has_md) on(O_MD);
+  if (has_args) on(P_ARGS_CLOSE);
+  on(P_CLOSE);
   t.x++;
-  const uint32_t fid = d.op_flow[i];
   const uint32_t ft = d.op_flowt[i] & 0xfu;
-  if (fid > 0 && (ft == 1u || ft == 2u)) {  // handleGenericLink, output_json.cpp:973-995
-    flow_event(s, (d.op_flowt[i] >> 4) & 1u, ft == 1u, fid, pid, tid, rel_ts(d, flow_ts));
+  if (c.corr > 0 && (ft == 1u || ft == 2u)) {  // handleGenericLink, output_json.cpp:973-995
+    const bool start = (d.op_flowt[i] >> 4) & 1u;
+    on(start ? P_FLOW_S : P_FLOW_F); on(P_FPID); on(P_FTID); on(P_FTS); on(ft == 1u ? P_FWDBWD : P_AC2G);
+    if (!start) on(P_FBP);
+    on(P_FEND);
     t.flow++;
   }
+  *present = p;
   return true;
+}
+__device__ __forceinline__ uint64_t value_op(int f, const EvCtx& c) {
+  switch (f) {
+    case O_CAT: return CS_TYPE + c.aux;
+    case O_NAME: return c.name;
+    case O_PID: case P_FPID: return (uint64_t)c.pid;
+    case O_TID: case P_FTID: return (uint64_t)c.tid;
+    case O_TS: return (uint64_t)c.ts_rel;
+    case O_DUR: return (uint64_t)c.dur;
+    case O_EXT: return (uint64_t)(int64_t)c.ext;
+    case O_MD: return c.j;
+    case P_FTS: return (uint64_t)c.flow_ts_rel;
+    default: return c.corr;  // P_FLOW_S, P_FLOW_F
+  }
+}
+__device__ __forceinline__ uint64_t value_ann(int f, const EvCtx& c) {
+  switch (f) {
+    case N_HEAD: return c.name;
+    case N_PID: return (uint64_t)c.pid;
+    case N_TID: return (uint64_t)c.tid;
+    case N_TS: return (uint64_t)c.ts_rel;
+    case N_DUR: return (uint64_t)c.dur;
+    default: return (uint64_t)(int64_t)c.ext;  // N_EXT
+  }
+}
+
+constexpr int C_ANN = 10;  // program selector for annotation spans (not a record class)
+
+// The formatting loop shared by every class: fields [base, base + nf) of the table.  `present` has one
+// bit per field.  T_MD (CPU-side activities only) formats the typed metadata entries of the op
+// (JsonTypedMetadataVisitor, libkineto/include/TypedMetadataJson.h:72-158).
+template <class S>
+__device__ __forceinline__ void run_fields(S& s, const Dev& d, int cls, int base, int nf, const EvCtx& c, uint64_t present,
+                                           unsigned long long* name_bytes) {
+  for (int f = 0; f < nf; f++) {
+    if (!((present >> f) & 1ull)) continue;
+    const FieldDesc fd = g_fields.f[base + f];
+    s.words(g_fields.w + fd.off, fd.len);
+    if (fd.type == T_NONE) continue;
+    uint64_t v;
+    switch (cls) {
+      case C_API: v = value_api(f, c); break;
+      case C_KERNEL: v = value_kernel(f, c); break;
+      case C_MEMCPY: case C_MEMCPY2: case C_MEMSET: v = value_mem(f, c); break;
+      case C_ANN: v = value_ann(f, c); break;
+      default: v = value_op(f, c); break;
+    }
+    switch (fd.type) {
+      case T_U64: put_dec(s, v); break;
+      case T_I64: put_sdec(s, (int64_t)v); break;
+      case T_TS: put_ts2(s, (int64_t)v); break;
+      case T_DBL: put_dbl(s, __longlong_as_double((long long)v)); break;
+      case T_NAME: put_name(s, d, (uint32_t)v, name_bytes); break;
+      case T_CSTR: { const FieldDesc cs = g_fields.f[CSTR_BASE + (uint32_t)v]; s.words(g_fields.w + cs.off, cs.len); break; }
+      default: {  // T_MD
+        const uint32_t m0 = d.op_mdoff[v], m1 = d.op_mdoff[v + 1];
+        for (uint32_t e = m0; e < m1; e++) {
+          const MdEntry md = d.md[e];
+          if (e > m0) s.put(0x202Cu, 2);  // ", "
+          put_char(s, '"'); put_mdstr(s, d, md.key); s.put(0x203A22u, 3);  // "\": "
+          switch (md.type) {
+            case 0: put_sdec(s, (int64_t)md.value); break;
+            case 1: put_dec(s, md.value); break;
+            case 2: put_dbl(s, __longlong_as_double((long long)md.value)); break;
+            case 3: if (md.value) s.put4(0x65757274u); else { s.put4(0x736C6166u); put_char(s, 'e'); } break;  // true / false
+            case 4: put_char(s, '"'); put_mdstr(s, d, (uint32_t)md.value); put_char(s, '"'); break;
+            default: put_mdstr(s, d, (uint32_t)md.value); break;
+          }
+        }
+        break;
+      }
+    }
+  }
 }
 
 constexpr int kEventThreads = 128;
+
+template <class S>
+__device__ __forceinline__ void format_event(S& s, const Dev& d, int cls, const uint8_t* r, uint64_t j, Tally& t, uint32_t* filt) {
+  EvCtx c;
+  c.r = r; c.j = j;
+  uint64_t present = 0;
+  int base = 0, nf = 0;
+  bool ok;
+  switch (cls) {
+    case C_API: ok = gather_api(d, r, c, &present, t, filt); base = API_BASE; nf = A_COUNT; break;
+    case C_KERNEL: ok = gather_kernel(d, r, c, &present, t, filt, S::kCounting); base = KERNEL_BASE; nf = K_COUNT; break;
+    case C_MEMCPY: ok = gather_mem<C_MEMCPY>(d, r, c, &present, t, filt, S::kCounting); base = MEM_BASE; nf = M_COUNT; break;
+    case C_MEMCPY2: ok = gather_mem<C_MEMCPY2>(d, r, c, &present, t, filt, S::kCounting); base = MEM_BASE; nf = M_COUNT; break;
+    case C_MEMSET: ok = gather_mem<C_MEMSET>(d, r, c, &present, t, filt, S::kCounting); base = MEM_BASE; nf = M_COUNT; break;
+    default: ok = gather_op(d, j, c, &present, t); base = OP_BASE; nf = O_COUNT; break;
+  }
+  if (ok) run_fields(s, d, cls, base, nf, c, present, &t.name_bytes);
+}
 
 // One thread per work item.  Work items are class-sorted (each class padded to a multiple of 32),
 // so a warp formats events of one shape.  WRITE = false: store the byte length; WRITE = true: write
 // the bytes at ev_off[event].
 template <bool WRITE>
-__global__ void __launch_bounds__(kEventThreads) k_events(Dev d) {
+__global__ void __launch_bounds__(kEventThreads, 6) k_events(Dev d) {
   __shared__ uint32_t s_stage[kEventThreads * 4];
   __shared__ unsigned long long s_cnt[8];
   if (threadIdx.x < 8) s_cnt[threadIdx.x] = 0;
@@ -978,15 +1277,8 @@ __global__ void __launch_bounds__(kEventThreads) k_events(Dev d) {
       t.ev = ev;
       const uint8_t* r = cls == C_OP ? nullptr : d.cupti + (uint64_t)d.work_slot[i] * 8;
       if (!WRITE) {
-        CountSink s;
-        switch (cls) {
-          case C_API: ev_api(s, d, r, t, &filt); break;
-          case C_KERNEL: ev_kernel(s, d, r, t, &filt); break;
-          case C_MEMCPY: ev_mem<CountSink, C_MEMCPY>(s, d, r, t, &filt); break;
-          case C_MEMCPY2: ev_mem<CountSink, C_MEMCPY2>(s, d, r, t, &filt); break;
-          case C_MEMSET: ev_mem<CountSink, C_MEMSET>(s, d, r, t, &filt); break;
-          default: ev_op(s, d, j, t); break;
-        }
+        CountSink2 s;
+        format_event(s, d, cls, r, j, t, &filt);
         d.ev_size[ev] = filt ? 0u : s.n;
       } else {
         const uint32_t size = d.ev_size[ev];
@@ -996,14 +1288,7 @@ __global__ void __launch_bounds__(kEventThreads) k_events(Dev d) {
           else {
             GlobalSink s;
             s.init(d.out + off, &s_stage[(threadIdx.x >> 5) * 128 + (threadIdx.x & 31)]);
-            switch (cls) {
-              case C_API: ev_api(s, d, r, t, &filt); break;
-              case C_KERNEL: ev_kernel(s, d, r, t, &filt); break;
-              case C_MEMCPY: ev_mem<GlobalSink, C_MEMCPY>(s, d, r, t, &filt); break;
-              case C_MEMCPY2: ev_mem<GlobalSink, C_MEMCPY2>(s, d, r, t, &filt); break;
-              case C_MEMSET: ev_mem<GlobalSink, C_MEMSET>(s, d, r, t, &filt); break;
-              default: ev_op(s, d, j, t); break;
-            }
+            format_event(s, d, cls, r, j, t, &filt);
             s.finish();
           }
         }
@@ -1056,18 +1341,17 @@ __global__ void __launch_bounds__(kEventThreads) k_annotations(Dev d, const Span
   int64_t dur = r.end - r.start;
   if (dur < 0) dur = 0;
   unsigned long long nb = 0;
-  auto body = [&](auto& s) {
-    K2J_LIT(s, "\n  {\n    \"ph\": \"X\",\n    \"cat\": \"gpu_user_annotation\",\n    \"name\": \"");
-    if (r.op_row < d.n_ops) put_name(s, d, d.op_name[r.op_row], &nb);
-    x_mid(s, (int64_t)r.device, (int64_t)r.stream, rel_ts(d, r.start - 1), dur + 2);
-    if (r.op_id != 0) { K2J_LIT(s, ",\n    \"args\": {\n      \"External id\": "); put_i64(s, r.op_id); K2J_LIT(s, "\n    }"); }
-    K2J_LIT(s, "\n  },");
-  };
-  if (!WRITE) { CountSink s; body(s); sizes[i] = s.n; }
+  EvCtx c;
+  c.r = nullptr; c.j = 0;
+  c.name = r.op_row < d.n_ops ? d.op_name[r.op_row] : 0xFFFFFFFFu; c.pid = r.device; c.tid = r.stream;
+  c.ts_rel = rel_ts(d, r.start - 1); c.dur = dur + 2; c.ext = r.op_id;
+  uint64_t p = (1ull << N_COUNT) - 1ull;
+  if (r.op_id == 0) p &= ~((1ull << N_EXT) | (1ull << N_ARGS_CLOSE));
+  if (!WRITE) { CountSink2 s; run_fields(s, d, C_ANN, ANN_BASE, N_COUNT, c, p, &nb); sizes[i] = s.n; }
   else {
     GlobalSink s;
     s.init(d.out + out_base + offs[i], &s_stage[(threadIdx.x >> 5) * 128 + (threadIdx.x & 31)]);
-    body(s);
+    run_fields(s, d, C_ANN, ANN_BASE, N_COUNT, c, p, &nb);
     s.finish();
   }
 }
