@@ -177,7 +177,7 @@ def run_reference(args):
 def run_ours(args):
     import torch
     import torch.distributed as dist
-    from kineto_b200 import api
+    from kineto_b200 import api, sharding
 
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -204,22 +204,10 @@ def run_ours(args):
             return ctx.run()
         info = ctx.segment()
         n_ext, n_ops = int(info.n_external), int(info.n_ops)
-        counts = torch.tensor([n_ext, n_ops], dtype=torch.int64, device=dev)
-        all_counts = torch.empty(world * 2, dtype=torch.int64, device=dev)
-        dist.all_gather_into_tensor(all_counts, counts)
-        all_counts = all_counts.view(world, 2).cpu()
-        max_ext, max_ops = int(all_counts[:, 0].max()), int(all_counts[:, 1].max())
-        ext_local = _wrap(info.external_records, n_ext * 2, torch.int64, dev, max_ext * 2)
-        ops_local = _wrap(info.op_ids, n_ops, torch.int32, dev, max_ops)
-        ext_all = torch.empty(world * max_ext * 2, dtype=torch.int64, device=dev)
-        ops_all = torch.empty(world * max_ops, dtype=torch.int32, device=dev)
-        dist.all_gather_into_tensor(ext_all, ext_local)
-        dist.all_gather_into_tensor(ops_all, ops_local)
-        # compact the padded gathers into shard order
-        ext_c = torch.cat([ext_all[r * max_ext * 2: r * max_ext * 2 + int(all_counts[r, 0]) * 2] for r in range(world)])
-        ops_c = torch.cat([ops_all[r * max_ops: r * max_ops + int(all_counts[r, 1])] for r in range(world)])
-        own_begin = int(all_counts[:rank, 0].sum())
-        ctx.set_global_join(ext_c, ext_c.numel() // 2, own_begin, ops_c, ops_c.numel())
+        ext_local = api.device_view(info.external_records, n_ext * 2, "<i8", dev)
+        ops_local = api.device_view(info.op_ids, n_ops, "<i4", dev)
+        ext_all, ops_all, own_begin = sharding.gather_join_keys(ext_local, ops_local, rank, world, dist)
+        ctx.set_global_join(ext_all, ext_all.numel() // 2, own_begin, ops_all, ops_all.numel())
         return ctx.emit()
 
     # ---- resident: inputs already in HBM ----
@@ -327,16 +315,6 @@ def run_ours(args):
     ctx.close()
     if world > 1:
         dist.destroy_process_group()
-
-
-def _wrap(ptr, n, dtype, dev, pad_to):
-    """Copies `n` elements at device address `ptr` into a fresh tensor padded to `pad_to` elements."""
-    import torch
-    from kineto_b200 import api
-    out = torch.zeros(pad_to, dtype=dtype, device=dev)
-    if n:
-        out[:n].copy_(api.device_view(ptr, n, "<i8" if dtype == torch.int64 else "<i4", dev))
-    return out
 
 
 if __name__ == "__main__":

@@ -171,6 +171,8 @@ _SECTIONS = [  # (tag, attribute, dtype)
     ("OPNAME", "op_name", np.uint32), ("OPFLOW", "op_flow", np.uint32),
     ("OPFLOWT", "op_flowt", np.uint8), ("OPMDOFF", "op_mdoff", np.uint32),
     ("MDENT", "md", MD_ENTRY),
+    # optional: join keys gathered from all shards of a sharded trace (see kineto_b200/sharding.py)
+    ("GEXT", "g_ext", np.uint64), ("GOPS", "g_ops", np.int32),
 ]
 
 
@@ -201,6 +203,8 @@ class Trace:
     op_flowt: np.ndarray = field(default_factory=lambda: _empty(np.uint8))
     op_mdoff: np.ndarray = field(default_factory=lambda: np.zeros(1, np.uint32))
     md: np.ndarray = field(default_factory=lambda: _empty(MD_ENTRY))
+    g_ext: np.ndarray = field(default_factory=lambda: _empty(np.uint64))
+    g_ops: np.ndarray = field(default_factory=lambda: _empty(np.int32))
 
     @property
     def n_ops(self) -> int:
@@ -220,6 +224,8 @@ class Trace:
         secs = []
         for tag, attr, dt in _SECTIONS:
             a = np.ascontiguousarray(getattr(self, attr), dtype=dt)
+            if tag in ("GEXT", "GOPS") and a.size == 0:
+                continue
             secs.append((tag, a.tobytes()))
         table_end = 16 + 24 * len(secs)
         pos = (table_end + 63) // 64 * 64

@@ -253,6 +253,7 @@ struct Run {
   Conv conv;
   std::unordered_map<int64_t, int64_t> cpuCorr, userCorr;
   std::unordered_map<int64_t, size_t> activityMap;  // op id -> op row (last writer wins)
+  std::unordered_map<int64_t, bool> globalOps;        // sharded traces: ids of all shards' ops
   std::map<int32_t, int32_t> tidMap;
   struct Span { int64_t start, end; size_t op; int64_t device, resource; };
   std::map<std::pair<int64_t, int64_t>, std::unordered_map<int64_t, Span>> userSpans;
@@ -315,6 +316,11 @@ struct Run {
   bool linked(uint32_t corr, int64_t* id) {  // linkedActivity(int32_t, ...), GenericActivityProfiler.cpp:397-408
     auto it = cpuCorr.find((int64_t)(int32_t)corr);
     if (it == cpuCorr.end()) return false;
+    if (globalJoin()) {
+      if (!globalOps.count(it->second)) return false;
+      *id = it->second;
+      return true;
+    }
     auto it2 = activityMap.find(it->second);
     if (it2 == activityMap.end()) return false;
     *id = tf.ptr<int32_t>("OPID")[it2->second];
@@ -343,6 +349,25 @@ struct Run {
     }
   }
 
+  // Sharded traces: the correlation maps and the CPU-op id set come from the arrays gathered from all
+  // shards (sections GEXT: {external id, correlation id | external kind << 32} pairs; GOPS: op ids).
+  bool globalJoin() const { return tf.has("GEXT") || tf.has("GOPS"); }
+  void pass1Global() {
+    const uint64_t* g = tf.ptr<uint64_t>("GEXT");
+    for (size_t i = 0; i < tf.count<uint64_t>("GEXT") / 2; i++) {
+      int64_t ext = (int64_t)g[2 * i];
+      int64_t corr = (uint32_t)g[2 * i + 1];
+      uint32_t ek = (uint32_t)(g[2 * i + 1] >> 32);
+      if (ek == 3) cpuCorr[corr] = ext;
+      else if (ek == 4) userCorr[corr] = ext;
+    }
+    const int32_t* ids = tf.ptr<int32_t>("GOPS");
+    for (size_t i = 0; i < tf.count<int32_t>("GOPS"); i++) globalOps[ids[i]] = true;
+    // invalid external kinds are counted by the shard that owns the record
+    forEachRecord([&](const uint8_t* r, uint32_t kind) {
+      if (kind == K_EXTCORR) { uint32_t ek = rd<uint32_t>(r, 4); if (ek != 3 && ek != 4) c.invalid_external_correlation++; }
+    });
+  }
   void pass1() {
     forEachRecord([&](const uint8_t* r, uint32_t kind) {
       if (kind != K_EXTCORR) return;
@@ -565,7 +590,7 @@ struct Run {
     for (size_t i = 0; i < tf.count<int32_t>("TIDMAP") / 2; i++) tidMap.emplace(tm[2 * i], tm[2 * i + 1]);
     cpuOps();
     seg[0] = out.buf.size();
-    if (p.mode != 0) { pass1(); pass2(); }
+    if (p.mode != 0) { if (globalJoin()) pass1Global(); else pass1(); pass2(); }
     seg[1] = out.buf.size();
     if (p.mode != 0) annotations();
     seg[2] = out.buf.size();

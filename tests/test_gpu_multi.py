@@ -1,0 +1,56 @@
+"""Two ranks on two GPUs: segment -> NCCL all-gather of the join keys -> emit, compared per shard with
+the CPU checker given the same gathered keys.  Skipped on boxes with one GPU."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+from kineto_b200 import synth
+
+pytestmark = pytest.mark.gpu
+WORLD = 2
+N = 40_000
+
+
+def _rank_main(rank, port, tmp):
+    import torch.distributed as dist
+    from kineto_b200 import api, sharding
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(WORLD),
+                      NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=WORLD, device_id=dev)
+    shard = synth.gen_kernel_launches(N, seed=91, pool_size=500, shard=(rank, WORLD))
+    ctx = api.K2J(rank, torch.cuda.current_stream().cuda_stream)
+    try:
+        ctx.load(shard)
+        info = ctx.segment()
+        ext_local = api.device_view(info.external_records, int(info.n_external) * 2, "<i8", dev)
+        ops_local = api.device_view(info.op_ids, int(info.n_ops), "<i4", dev)
+        ext_all, ops_all, own_begin = sharding.gather_join_keys(ext_local, ops_local, rank, WORLD, dist)
+        ctx.set_global_join(ext_all, ext_all.numel() // 2, own_begin, ops_all, ops_all.numel())
+        res = ctx.emit()
+        got = ctx.copy_output().tobytes()
+        shard.g_ext = ext_all.cpu().numpy().view(np.uint64)
+        shard.g_ops = ops_all.cpu().numpy()
+        want, stats = helpers.run_port(shard)
+        ok = got == want and res["x_events"] == stats["x_events"] and res["ops_bytes"] == stats["ops_end"]
+        alone, _ = helpers.run_port(synth.gen_kernel_launches(N, seed=91, pool_size=500, shard=(rank, WORLD)))
+        open(os.path.join(tmp, "ok%d" % rank), "w").write("%d %d" % (int(ok), int(alone != want)))
+        dist.barrier()
+    finally:
+        ctx.close()
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpu_ranks_match_checker(tmp_path):
+    import torch.multiprocessing as mp
+    port = 29700 + (os.getpid() % 2000)
+    mp.spawn(_rank_main, args=(port, str(tmp_path)), nprocs=WORLD, join=True)
+    for r in range(WORLD):
+        ok, crosses = open(str(tmp_path / ("ok%d" % r))).read().split()
+        assert ok == "1", "rank %d output differs from the checker" % r
+        assert crosses == "1"   # the join does reach into the other shard

@@ -1,0 +1,71 @@
+"""The N > 1 path on CPUs: two gloo ranks exchange their join keys with kineto_b200.sharding, each
+runs the CPU checker on its shard with the gathered keys, and the shard outputs must concatenate to
+the output of the whole trace processed at once."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import helpers
+from kineto_b200 import sharding, synth
+from kineto_b200 import tracefile as tf
+
+WORLD = 2
+N = 1500
+
+
+def ext_records(trace):
+    """The EXTERNAL_CORRELATION records of a launches trace as (external id, corr | kind << 32) pairs."""
+    group = trace.cupti.reshape(-1, 272)            # 24 (ext) + 40 (api) + 208 (kernel) bytes per launch
+    ext = np.ascontiguousarray(group[:, :24]).view(tf.EXTCORR).reshape(-1)
+    out = np.zeros((len(ext), 2), np.uint64)
+    out[:, 0] = ext["externalId"]
+    out[:, 1] = ext["correlationId"].astype(np.uint64) | (ext["externalKind"].astype(np.uint64) << np.uint64(32))
+    return out.reshape(-1)
+
+
+def _rank_main(rank, port, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(WORLD))
+    dist.init_process_group("gloo", rank=rank, world_size=WORLD)
+    shard = synth.gen_kernel_launches(N, seed=77, pool_size=60, shard=(rank, WORLD))
+    ext_local = torch.from_numpy(ext_records(shard).view(np.int64).copy())
+    ops_local = torch.from_numpy(shard.op_id.copy())
+    ext_all, ops_all, own_begin = sharding.gather_join_keys(ext_local, ops_local, rank, WORLD, dist)
+    assert own_begin == rank * N
+    shard.g_ext = ext_all.numpy().view(np.uint64)
+    shard.g_ops = ops_all.numpy()
+    out, stats = helpers.run_port(shard)
+    base, total = sharding.output_bases(len(out), rank, WORLD, dist, "cpu")
+    np.save(os.path.join(tmp, "out%d.npy" % rank), np.frombuffer(out, np.uint8))
+    np.save(os.path.join(tmp, "meta%d.npy" % rank), np.array([stats["ops_end"], base, total, len(out)]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_reproduce_the_whole_trace(tmp_path):
+    port = 29500 + (os.getpid() % 2000)
+    mp.spawn(_rank_main, args=(port, str(tmp_path)), nprocs=WORLD, join=True)
+    shards = [synth.gen_kernel_launches(N, seed=77, pool_size=60, shard=(r, WORLD)) for r in range(WORLD)]
+    whole = tf.Trace(**{attr: getattr(shards[0], attr) for _, attr, _ in tf._SECTIONS})
+    for col in ("op_start", "op_end", "op_id", "op_device", "op_resource", "op_thread", "op_type", "op_name", "op_flow",
+                "op_flowt", "md"):
+        setattr(whole, col, np.concatenate([getattr(s, col) for s in shards]))
+    whole.op_mdoff = np.concatenate([shards[0].op_mdoff, shards[1].op_mdoff[1:] + shards[0].op_mdoff[-1]]).astype(np.uint32)
+    whole.cupti = np.concatenate([s.cupti for s in shards])
+    bt1 = shards[1].buftab.copy()
+    bt1[0::2] += np.uint64(len(shards[0].cupti))
+    whole.buftab = np.concatenate([shards[0].buftab, bt1])
+    want, stats = helpers.run_port(whole)
+    outs = [np.load(str(tmp_path / ("out%d.npy" % r))).tobytes() for r in range(WORLD)]
+    metas = [np.load(str(tmp_path / ("meta%d.npy" % r))) for r in range(WORLD)]
+    ops_txt = b"".join(o[:int(m[0])] for o, m in zip(outs, metas))
+    gpu_txt = b"".join(o[int(m[0]):] for o, m in zip(outs, metas))
+    assert ops_txt + gpu_txt == want, helpers.first_diff(want, ops_txt + gpu_txt)
+    assert int(metas[1][1]) == len(outs[0]) and int(metas[0][2]) == len(outs[0]) + len(outs[1])
+    # the join really crosses shards: most kernels of shard 0 are linked to ops of shard 1 and vice versa
+    alone, _ = helpers.run_port(shards[0])
+    assert alone != outs[0]
