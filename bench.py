@@ -198,6 +198,8 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    exchange_events = []
+
     def exchange_and_emit():
         """segment -> (all-gather join keys) -> emit; returns the result dict."""
         if world == 1:
@@ -206,7 +208,11 @@ def run_ours(args):
         n_ext, n_ops = int(info.n_external), int(info.n_ops)
         ext_local = api.device_view(info.external_records, n_ext * 2, "<i8", dev)
         ops_local = api.device_view(info.op_ids, n_ops, "<i4", dev)
+        x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        x0.record(stream)
         ext_all, ops_all, own_begin = sharding.gather_join_keys(ext_local, ops_local, rank, world, dist)
+        x1.record(stream)
+        exchange_events.append((x0, x1))
         ctx.set_global_join(ext_all, ext_all.numel() // 2, own_begin, ops_all, ops_all.numel())
         return ctx.emit()
 
@@ -232,6 +238,7 @@ def run_ours(args):
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     ms = e0.elapsed_time(e1)
+    ms_exchange = sum(a.elapsed_time(b) for a, b in exchange_events[-args.steps:]) / args.steps if world > 1 else 0.0
     n_records = res["n_records"] + len(trace.op_start)
 
     # ---- end to end: pinned host buffers in, pinned host buffer out ----
@@ -303,7 +310,7 @@ def run_ours(args):
                          "algorithmic_bytes_per_launch": alg_emit, "ms_per_launch": emit_ms,
                          "traffic": (EMIT_TRAFFIC_PER_OUT_BYTE * res["out_bytes"]) if EMIT_TRAFFIC_PER_OUT_BYTE else None,
                          "pipeline_frac": alg_all / (sum(stage.values()) / args.steps * 1e-3) / 1e9 / peak},
-            "stage_ms_per_step": {k: v / args.steps for k, v in stage.items()},
+            "stage_ms_per_step": dict({k: v / args.steps for k, v in stage.items()}, ms_exchange=ms_exchange),
         }
         if world == 1 and not args.no_cpu_baseline:
             v, secs, n_rec, kind = reference_records_per_sec(min(args.cpu_sample, args.launches), 1)

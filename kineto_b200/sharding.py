@@ -14,28 +14,37 @@ from __future__ import annotations
 def gather_join_keys(ext_local, ops_local, rank: int, world: int, dist):
     """ext_local: int64 tensor with 2 words per record; ops_local: int32 tensor.
     Returns (ext_all, ops_all, own_begin): the gathered arrays in rank order and the index of this
-    rank's first EXTERNAL_CORRELATION record in ext_all."""
+    rank's first EXTERNAL_CORRELATION record in ext_all.  Two collectives: the counts, then one
+    packed payload (records and ids in one buffer, padded to the largest shard)."""
     import torch
 
     dev = ext_local.device
-    counts = torch.tensor([ext_local.numel() // 2, ops_local.numel()], dtype=torch.int64, device=dev)
+    n_ext, n_ops = ext_local.numel() // 2, ops_local.numel()
+    counts = torch.tensor([n_ext, n_ops], dtype=torch.int64, device=dev)
     all_counts = torch.empty(world * 2, dtype=torch.int64, device=dev)
     dist.all_gather_into_tensor(all_counts, counts)
-    all_counts = all_counts.view(world, 2).cpu()
-    max_ext, max_ops = int(all_counts[:, 0].max()), int(all_counts[:, 1].max())
-    ext_pad = torch.zeros(max(1, max_ext) * 2, dtype=torch.int64, device=dev)
-    ext_pad[:ext_local.numel()] = ext_local
-    ops_pad = torch.zeros(max(1, max_ops), dtype=torch.int32, device=dev)
-    ops_pad[:ops_local.numel()] = ops_local
-    ext_g = torch.empty(world * ext_pad.numel(), dtype=torch.int64, device=dev)
-    ops_g = torch.empty(world * ops_pad.numel(), dtype=torch.int32, device=dev)
-    dist.all_gather_into_tensor(ext_g, ext_pad)
-    dist.all_gather_into_tensor(ops_g, ops_pad)
-    # drop the padding: rank order is processing order
-    ext_all = torch.cat([ext_g[r * ext_pad.numel(): r * ext_pad.numel() + int(all_counts[r, 0]) * 2] for r in range(world)])
-    ops_all = torch.cat([ops_g[r * ops_pad.numel(): r * ops_pad.numel() + int(all_counts[r, 1])] for r in range(world)])
-    own_begin = int(all_counts[:rank, 0].sum())
-    return ext_all, ops_all, own_begin
+    all_counts = all_counts.view(world, 2).tolist()
+    max_ext = max(1, max(c[0] for c in all_counts))
+    max_ops = max(1, max(c[1] for c in all_counts))
+    ops_words = (max_ops + 1) // 2                       # op ids packed two per 64-bit word
+    stride = max_ext * 2 + ops_words
+    pack = torch.empty(stride, dtype=torch.int64, device=dev)
+    pack[:n_ext * 2] = ext_local
+    pack[max_ext * 2:].view(torch.int32)[:n_ops] = ops_local
+    gathered = torch.empty(world * stride, dtype=torch.int64, device=dev)
+    dist.all_gather_into_tensor(gathered, pack)
+    g = gathered.view(world, stride)
+    if all(c[0] == max_ext for c in all_counts):
+        ext_all = g[:, :max_ext * 2].reshape(-1)
+    else:
+        ext_all = torch.cat([g[r, :all_counts[r][0] * 2] for r in range(world)])
+    gi = g[:, max_ext * 2:].view(torch.int32)
+    if all(c[1] == max_ops for c in all_counts) and max_ops % 2 == 0:
+        ops_all = gi.reshape(-1)
+    else:
+        ops_all = torch.cat([gi[r, :all_counts[r][1]] for r in range(world)])
+    own_begin = sum(c[0] for c in all_counts[:rank])
+    return ext_all.contiguous(), ops_all.contiguous(), own_begin
 
 
 def output_bases(out_bytes: int, rank: int, world: int, dist, device):
