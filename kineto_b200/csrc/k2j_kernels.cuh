@@ -508,78 +508,86 @@ __global__ void __launch_bounds__(kScanThreads) k_scan_apply(const uint32_t* in,
 }
 
 // ---- output sink: 16-byte vector stores straight to the final position ----------------------------------
-// Bytes are gathered in a 32-bit shift register, completed words go to a 4-word staging slot of this
-// lane in shared memory (word k of lane l lives at index k*32+l: conflict free), and every fourth word
-// the slot leaves as one 16-byte store.  Only the first and last 16-byte block of an event are
-// written with narrower stores, so neighbouring events never overwrite each other.
-__device__ __noinline__ void store_partial(uint8_t* b, const uint32_t* slot, int from, int to) {
-  int i = from;
-  while (i < to) {
-    const uint32_t w = slot[(i >> 2) * 32];
-    if ((i & 3) == 0 && i + 4 <= to) { *reinterpret_cast<uint32_t*>(b + i) = w; i += 4; }
-    else { b[i] = (uint8_t)(w >> ((i & 3) * 8)); i++; }
+// Bytes are gathered in a 64-bit shift register; a completed 8-byte word is either parked in a register
+// (first half of a 16-byte block) or leaves together with the parked one as one 16-byte store (second
+// half).  Only the first and last 16-byte block of an event are written with narrower stores, so
+// neighbouring events never overwrite each other.  No shared or local memory is involved.
+__device__ __noinline__ void store_partial(uint8_t* b, uint64_t w0, uint64_t w1, int from, int to) {
+  for (int i = from; i < to; i++) {
+    const uint64_t w = i < 8 ? w0 : w1;
+    b[i] = (uint8_t)(w >> ((i & 7) * 8));
   }
 }
 
 struct GlobalSink {
   static constexpr bool kCounting = false;
-  uint32_t lo; int sh; int head; uint32_t* sp; uint32_t* sp_end; uint4* p;
-  __device__ __forceinline__ void init(uint8_t* dst, uint32_t* lane_slot) {
+  uint64_t lo, w0; int sh, k, head; uint4* p;
+  __device__ __forceinline__ void init(uint8_t* dst) {
     const uintptr_t a = reinterpret_cast<uintptr_t>(dst);
     const int phase = (int)(a & 15);
     p = reinterpret_cast<uint4*>(a - phase);
-    sp_end = lane_slot + 128; sp = lane_slot + 32 * (phase >> 2);
-    sh = 8 * (phase & 3); lo = 0; head = phase;
+    k = phase >> 3; sh = 8 * (phase & 7); lo = 0; w0 = 0; head = phase;
   }
-  __device__ __forceinline__ void word(uint32_t x) {
-    *sp = x;
-    sp += 32;
-    if (sp == sp_end) {
-      sp = sp_end - 128;
-      if (head) { store_partial(reinterpret_cast<uint8_t*>(p), sp, head, 16); head = 0; }
-      else *p = make_uint4(sp[0], sp[32], sp[64], sp[96]);
-      p++;
-    }
+  __device__ __forceinline__ void word(uint64_t x) {
+    if (k) {
+      if (head) { store_partial(reinterpret_cast<uint8_t*>(p), w0, x, head, 16); head = 0; }
+      else *p = make_uint4((uint32_t)w0, (uint32_t)(w0 >> 32), (uint32_t)x, (uint32_t)(x >> 32));
+      p++; k = 0;
+    } else { w0 = x; k = 1; }
   }
-  __device__ __forceinline__ void put4(uint32_t w) {
+  // append 8 bytes
+  __device__ __forceinline__ void put8w(uint64_t w) {
     word(lo | (w << sh));
-    lo = __funnelshift_l(w, 0u, sh);
+    lo = sh ? (w >> (64 - sh)) : 0ull;
   }
-  __device__ __forceinline__ void put(uint32_t w, int len) {
-    const uint32_t t = lo | (w << sh);
+  // append the low `len` (1..8) bytes of w; bytes above len must be zero
+  __device__ __forceinline__ void put64(uint64_t w, int len) {
+    const uint64_t t = lo | (w << sh);
     const int s2 = sh + 8 * len;
-    if (s2 >= 32) { word(t); lo = __funnelshift_l(w, 0u, sh); sh = s2 - 32; }
+    if (s2 >= 64) { word(t); lo = sh ? (w >> (64 - sh)) : 0ull; sh = s2 - 64; }
     else { lo = t; sh = s2; }
   }
+  __device__ __forceinline__ void put(uint32_t w, int len) { put64((uint64_t)w, len); }
+  __device__ __forceinline__ void put4(uint32_t w) { put64((uint64_t)w, 4); }
   __device__ __forceinline__ void skip(uint32_t) {}
   template <int N> __device__ __forceinline__ void lit(const Lit<N>& l) {
 #pragma unroll
     for (int i = 0; i < N / 4; i++) put4(l.w[i]);
     if (N % 4) put(l.w[N / 4], N % 4);
   }
-  // `len` bytes from a word array in constant or global memory (last word zero padded).
-  __device__ __forceinline__ void words(const uint32_t* w, uint32_t len) {
-    // four loads in flight per round: the loads do not depend on the shift register, the puts do
-    const uint32_t nw = len >> 2;
+  __device__ __forceinline__ void store16(uint64_t a, uint64_t b) {
+    if (head) { store_partial(reinterpret_cast<uint8_t*>(p), a, b, head, 16); head = 0; }
+    else *p = make_uint4((uint32_t)a, (uint32_t)(a >> 32), (uint32_t)b, (uint32_t)(b >> 32));
+    p++;
+  }
+  // `len` bytes from an 8-byte aligned word array (bytes past len in the last word are ignored).
+  // The byte phase does not change inside the run, so after aligning to a 16-byte block the body
+  // handles two words per round with no per-word branching.
+  __device__ __forceinline__ void words(const uint64_t* w, uint32_t len) {
+    const uint32_t nw = len >> 3;
     uint32_t i = 0;
-    for (; i + 4 <= nw; i += 4) {
-      const uint32_t a = w[i], b = w[i + 1], c = w[i + 2], e = w[i + 3];
-      put4(a); put4(b); put4(c); put4(e);
+    if (k && nw) { put8w(w[0]); i = 1; }
+    const int rs = 63 - sh;  // (x >> 1) >> rs == x >> (64 - sh), and 0 when sh == 0
+    for (; i + 2 <= nw; i += 2) {
+      const uint64_t a = w[i], b = w[i + 1];
+      const uint64_t t0 = lo | (a << sh);
+      const uint64_t t1 = ((a >> 1) >> rs) | (b << sh);
+      lo = (b >> 1) >> rs;
+      store16(t0, t1);
     }
-    for (; i < nw; i++) put4(w[i]);
-    const uint32_t rem = len & 3u;
-    if (rem) put(w[nw] & (0xFFFFFFFFu >> (8 * (4 - rem))), (int)rem);
+    if (i < nw) put8w(w[i]);
+    const uint32_t rem = len & 7u;
+    if (rem) put64(w[nw] & (~0ull >> (8 * (8 - rem))), (int)rem);
   }
   __device__ __forceinline__ void finish() {
-    uint32_t* base = sp_end - 128;
-    const int have = (int)((sp - base) >> 5) * 4 + (sh >> 3);
-    if (sh) *sp = lo;
-    if (have > head) store_partial(reinterpret_cast<uint8_t*>(p), base, head, have);
+    const int have = k * 8 + (sh >> 3);
+    if (have > head) store_partial(reinterpret_cast<uint8_t*>(p), k ? w0 : lo, lo, head, have);
   }
 };
 struct CountSink2 : CountSink {
   __device__ __forceinline__ void put4(uint32_t) { n += 4; }
-  __device__ __forceinline__ void words(const uint32_t*, uint32_t len) { n += len; }
+  __device__ __forceinline__ void put64(uint64_t, int len) { n += (uint32_t)len; }
+  __device__ __forceinline__ void words(const uint64_t*, uint32_t len) { n += len; }
 };
 
 // ---- event programs ------------------------------------------------------------------------------------
@@ -592,14 +600,14 @@ struct FieldSrc { const char* lit; uint8_t type; };
 struct FieldDesc { uint16_t off, len; uint8_t type, pad; };
 
 constexpr int c_strlen(const char* s) { int n = 0; while (s[n]) n++; return n; }
-template <int NF> constexpr int prog_words(const FieldSrc (&src)[NF]) {
+template <int NF> constexpr int prog_words(const FieldSrc (&src)[NF]) {  // 64-bit words
   int w = 0;
-  for (int f = 0; f < NF; f++) w += (c_strlen(src[f].lit) + 3) / 4;
+  for (int f = 0; f < NF; f++) w += (c_strlen(src[f].lit) + 7) / 8;
   return w > 0 ? w : 1;
 }
 template <int NF, int NW> struct Prog {
   FieldDesc f[NF];
-  uint32_t w[NW];
+  uint64_t w[NW];
 };
 template <int NF, int NW> constexpr Prog<NF, NW> make_prog(const FieldSrc (&src)[NF]) {
   Prog<NF, NW> p{};
@@ -607,8 +615,8 @@ template <int NF, int NW> constexpr Prog<NF, NW> make_prog(const FieldSrc (&src)
   for (int f = 0; f < NF; f++) {
     const int n = c_strlen(src[f].lit);
     p.f[f].off = (uint16_t)pos; p.f[f].len = (uint16_t)n; p.f[f].type = src[f].type; p.f[f].pad = 0;
-    for (int i = 0; i < n; i++) p.w[pos + i / 4] |= (uint32_t)(unsigned char)src[f].lit[i] << (8 * (i % 4));
-    pos += (n + 3) / 4;
+    for (int i = 0; i < n; i++) p.w[pos + i / 8] |= (uint64_t)(unsigned char)src[f].lit[i] << (8 * (i % 8));
+    pos += (n + 7) / 8;
   }
   return p;
 }
@@ -717,35 +725,6 @@ constexpr int kAllWords = prog_words(kAllFields);
 __constant__ Prog<FIELD_COUNT, kAllWords> g_fields = make_prog<FIELD_COUNT, kAllWords>(kAllFields);
 
 // ---- value formatting ----------------------------------------------------------------------------------------
-// Sink that writes bytes to a small local buffer; the slow formatters below run against it once and
-// hand the finished text to the real sink as words, which keeps them out of line and the emit kernel small.
-struct BufSink {
-  static constexpr bool kCounting = false;
-  uint8_t* b; int n;
-  __device__ __forceinline__ void put(uint32_t w, int len) { for (int i = 0; i < len; i++) b[n++] = (uint8_t)(w >> (8 * i)); }
-  __device__ __forceinline__ void skip(uint32_t) {}
-};
-// Text of v into buf (zero padded to whole words); returns the length.
-__device__ __noinline__ int fmt_u64_buf(uint64_t v, uint32_t* buf) {
-#pragma unroll
-  for (int i = 0; i < 6; i++) buf[i] = 0;
-  BufSink bs{reinterpret_cast<uint8_t*>(buf), 0};
-  put_u64(bs, v);
-  return bs.n;
-}
-__device__ __noinline__ int fmt_double_buf(double v, uint32_t* buf) {
-#pragma unroll
-  for (int i = 0; i < 8; i++) buf[i] = 0;
-  BufSink bs{reinterpret_cast<uint8_t*>(buf), 0};
-  put_double_value(bs, v);
-  return bs.n;
-}
-__device__ __noinline__ int len_double(double v) {
-  CountSink c;
-  put_double_value(c, v);
-  return (int)c.n;
-}
-
 // Four zero-padded ASCII digits of x < 10^4, most significant digit in the low byte (32-bit SWAR).
 __device__ __forceinline__ uint32_t ascii4(uint32_t x) {
   const uint32_t q = (x * 5243u) >> 19, r = x - q * 100u;          // x / 100, x % 100
@@ -765,8 +744,7 @@ template <class S> __device__ __forceinline__ void put_dec(S& s, uint64_t v) {
   if (v < 100000000ull) {
     const uint32_t x = (uint32_t)v, hi = x / 10000u, lo = x - hi * 10000u;
     const int d = 1 + (hi >= 10u) + (hi >= 100u) + (hi >= 1000u);  // digits of the upper part (hi >= 1)
-    s.put(ascii4(hi) >> (8 * (4 - d)), d);
-    s.put4(ascii4(lo));
+    s.put64((uint64_t)(ascii4(hi) >> (8 * (4 - d))) | ((uint64_t)ascii4(lo) << (8 * d)), d + 4);
     return;
   }
   put_u64(s, v);
@@ -786,7 +764,7 @@ template <class S> __device__ __forceinline__ void put_ts2(S& s, int64_t ns) {  
 }
 
 template <class S> __device__ __forceinline__ void put_pool_words(S& s, const uint8_t* src, uint32_t len) {
-  s.words(reinterpret_cast<const uint32_t*>(src), len);
+  s.words(reinterpret_cast<const uint64_t*>(src), len);  // sanitised pool strings start 8-byte aligned
 }
 template <class S> __device__ __forceinline__ void put_name(S& s, const Dev& d, uint32_t id, unsigned long long* name_bytes) {
   if (id >= d.n_strings) { atomicAdd(&d.counters->device_check, 1ull); return; }
@@ -871,12 +849,19 @@ struct Tally { uint32_t x, flow; unsigned long long name_bytes; uint64_t ev; };
 // registers; everything else is re-read from the record (an L1 hit) when its field comes up.
 struct EvCtx {
   const uint8_t* r; uint64_t j;
-  int64_t ts_rel, dur, flow_ts_rel, pid, tid;
-  int32_t ext; uint32_t corr, name, aux;   // aux: cbid (api), activity type (op)
-  uint64_t d0, d1;                          // doubles as bits: blocks/warps per SM, or bandwidth
-  int32_t occ_pct, occ_active, occ_limit, occ_lregs, occ_lsmem, occ_lwarps, occ_lblocks, occ_lbarr, occ_aregs;
-  uint64_t occ_asmem;
+  int64_t ts_rel, dur, pid, tid;
+  int32_t ext; uint32_t corr, name, aux;   // aux: cbid (api), activity type (op), layout shift (memcpy2)
+  uint32_t* sm;                             // this thread's column of the per-block scratch (see X_*)
 };
+// Rarely used per-event values live in shared memory (word i of thread t at [i * kEventThreads + t]),
+// which keeps the formatting loop's register footprint small.
+enum : int { X_D0_LO, X_D0_HI, X_D1_LO, X_D1_HI, X_OCC_PCT, X_OCC_ACTIVE, X_OCC_LIMIT, X_OCC_LREGS, X_OCC_LSMEM, X_OCC_LWARPS,
+             X_OCC_LBLOCKS, X_OCC_LBARR, X_OCC_AREGS, X_OCC_ASMEM_LO, X_OCC_ASMEM_HI, X_COUNT };
+constexpr int kCtxStride = 128;  // = kEventThreads
+__device__ __forceinline__ void xs(const EvCtx& c, int i, uint32_t v) { c.sm[i * kCtxStride] = v; }
+__device__ __forceinline__ uint32_t xl(const EvCtx& c, int i) { return c.sm[i * kCtxStride]; }
+__device__ __forceinline__ void xs64(const EvCtx& c, int i, uint64_t v) { xs(c, i, (uint32_t)v); xs(c, i + 1, (uint32_t)(v >> 32)); }
+__device__ __forceinline__ uint64_t xl64(const EvCtx& c, int i) { return (uint64_t)xl(c, i) | ((uint64_t)xl(c, i + 1) << 32); }
 
 // Each gather returns false if the record produces no event (`*filt`: 1 blocklisted, 2 outside the window).
 
@@ -999,12 +984,13 @@ __device__ __forceinline__ bool gather_kernel(const Dev& d, const uint8_t* r, Ev
   cudaOccResult occ;
   float occupancy;
   occupancy_metrics(d, dev, have_dev, sm_count, grid_prod, block_prod, regs, ssm, dsm, &occ, &occupancy);
-  c.occ_pct = (int32_t)llround(__dmul_rn((double)occupancy, 100.0));
-  c.occ_active = occ.activeBlocksPerMultiprocessor; c.occ_limit = CS_LIMIT + (int)(occ.limitingFactors & 31u);
-  c.occ_lregs = occ.blockLimitRegs; c.occ_lsmem = occ.blockLimitSharedMem; c.occ_lwarps = occ.blockLimitWarps;
-  c.occ_lblocks = occ.blockLimitBlocks; c.occ_lbarr = occ.blockLimitBarriers; c.occ_aregs = occ.allocatedRegistersPerBlock;
-  c.occ_asmem = (uint64_t)occ.allocatedSharedMemPerBlock;
-  c.d0 = (uint64_t)__double_as_longlong((double)bps); c.d1 = (uint64_t)__double_as_longlong((double)wps);
+  xs(c, X_OCC_PCT, (uint32_t)(int32_t)llround(__dmul_rn((double)occupancy, 100.0)));
+  xs(c, X_OCC_ACTIVE, (uint32_t)occ.activeBlocksPerMultiprocessor); xs(c, X_OCC_LIMIT, (uint32_t)(CS_LIMIT + (int)(occ.limitingFactors & 31u)));
+  xs(c, X_OCC_LREGS, (uint32_t)occ.blockLimitRegs); xs(c, X_OCC_LSMEM, (uint32_t)occ.blockLimitSharedMem);
+  xs(c, X_OCC_LWARPS, (uint32_t)occ.blockLimitWarps); xs(c, X_OCC_LBLOCKS, (uint32_t)occ.blockLimitBlocks);
+  xs(c, X_OCC_LBARR, (uint32_t)occ.blockLimitBarriers); xs(c, X_OCC_AREGS, (uint32_t)occ.allocatedRegistersPerBlock);
+  xs64(c, X_OCC_ASMEM_LO, (uint64_t)occ.allocatedSharedMemPerBlock);
+  xs64(c, X_D0_LO, (uint64_t)__double_as_longlong((double)bps)); xs64(c, X_D1_LO, (uint64_t)__double_as_longlong((double)wps));
   c.ts_rel = rel_ts(d, ts); c.dur = dur < 0 ? 0 : dur; c.pid = dev; c.tid = stream; c.ext = ext; c.corr = corr;
   uint64_t p = (1ull << K_COUNT) - 1ull;  // every field except the optional ones below
   if (!has_ext) p &= ~((1ull << K_EXT) | (1ull << K_EXTC));
@@ -1029,20 +1015,20 @@ __device__ __forceinline__ uint64_t value_kernel(int f, const EvCtx& c) {
     case K_CORR: case K_FLOW: return c.corr;
     case K_REGS: return *reinterpret_cast<const uint16_t*>(r + 6);
     case K_SMEM: return (uint64_t)(int64_t)(int32_t)(*reinterpret_cast<const uint32_t*>(r + 76) + *reinterpret_cast<const uint32_t*>(r + 80));
-    case K_BPS: return c.d0;
-    case K_WPS: return c.d1;
+    case K_BPS: return xl64(c, X_D0_LO);
+    case K_WPS: return xl64(c, X_D1_LO);
     case K_GX: case K_GY: case K_GZ: return (uint64_t)(int64_t)*reinterpret_cast<const int32_t*>(r + 52 + 4 * (f - K_GX));
     case K_BX: case K_BY: case K_BZ: return (uint64_t)(int64_t)*reinterpret_cast<const int32_t*>(r + 64 + 4 * (f - K_BX));
-    case K_OCCPCT: return (uint64_t)(int64_t)c.occ_pct;
-    case K_ACTIVE: return (uint64_t)(int64_t)c.occ_active;
-    case K_LIMIT: return (uint64_t)c.occ_limit;
-    case K_LREGS: return (uint64_t)(int64_t)c.occ_lregs;
-    case K_LSMEM: return (uint64_t)(int64_t)c.occ_lsmem;
-    case K_LWARPS: return (uint64_t)(int64_t)c.occ_lwarps;
-    case K_LBLOCKS: return (uint64_t)(int64_t)c.occ_lblocks;
-    case K_LBARR: return (uint64_t)(int64_t)c.occ_lbarr;
-    case K_AREGS: return (uint64_t)(int64_t)c.occ_aregs;
-    case K_ASMEM: return c.occ_asmem;
+    case K_OCCPCT: return (uint64_t)(int64_t)(int32_t)xl(c, X_OCC_PCT);
+    case K_ACTIVE: return (uint64_t)(int64_t)(int32_t)xl(c, X_OCC_ACTIVE);
+    case K_LIMIT: return xl(c, X_OCC_LIMIT);
+    case K_LREGS: return (uint64_t)(int64_t)(int32_t)xl(c, X_OCC_LREGS);
+    case K_LSMEM: return (uint64_t)(int64_t)(int32_t)xl(c, X_OCC_LSMEM);
+    case K_LWARPS: return (uint64_t)(int64_t)(int32_t)xl(c, X_OCC_LWARPS);
+    case K_LBLOCKS: return (uint64_t)(int64_t)(int32_t)xl(c, X_OCC_LBLOCKS);
+    case K_LBARR: return (uint64_t)(int64_t)(int32_t)xl(c, X_OCC_LBARR);
+    case K_AREGS: return (uint64_t)(int64_t)(int32_t)xl(c, X_OCC_AREGS);
+    case K_ASMEM: return xl64(c, X_OCC_ASMEM_LO);
     case K_GRAPH: return *reinterpret_cast<const uint32_t*>(r + 156);
     case K_NODE: return *reinterpret_cast<const uint64_t*>(r + 144);
     case K_CHAN: return *reinterpret_cast<const uint32_t*>(r + 168);
@@ -1074,7 +1060,7 @@ __device__ __forceinline__ bool gather_mem(const Dev& d, const uint8_t* r, EvCtx
   on(M_STREAM); on(M_CORR); on(M_BYTES);
   if (dur != 0) {  // addBandwidthTypedMetadata, CuptiActivity.h:460-470
     on(M_BW);
-    c.d0 = (uint64_t)__double_as_longlong(__ddiv_rn(__ull2double_rn(bytes), __ll2double_rn(dur)));
+    xs64(c, X_D0_LO, (uint64_t)__double_as_longlong(__ddiv_rn(__ull2double_rn(bytes), __ll2double_rn(dur))));
   }
   on(M_GRAPH); on(M_NODE); on(M_CHAN); on(M_CHTYPE); on(M_CLOSE);
   t.x++;
@@ -1103,7 +1089,7 @@ __device__ __forceinline__ uint64_t value_mem(int f, const EvCtx& c) {
     case M_TOCTX: return *reinterpret_cast<const uint32_t*>(r + 56);
     case M_CORR: case M_FLOW: return c.corr;
     case M_BYTES: return *reinterpret_cast<const uint64_t*>(r + 8);
-    case M_BW: return c.d0;
+    case M_BW: return xl64(c, X_D0_LO);
     case M_GRAPH: return *reinterpret_cast<const uint32_t*>(r + 72 + g);
     case M_NODE: return *reinterpret_cast<const uint64_t*>(r + 64 + g);
     case M_CHAN: return *reinterpret_cast<const uint32_t*>(r + 76 + g);
@@ -1131,7 +1117,7 @@ __device__ __forceinline__ bool gather_op(const Dev& d, uint64_t i, EvCtx& c, ui
   if (!excluded) ext = d.op_id[i];
   const bool has_md = d.op_mdoff[i + 1] > d.op_mdoff[i];
   const bool has_args = ext != 0 || has_md;
-  c.ts_rel = rel_ts(d, ts); c.dur = dur; c.flow_ts_rel = rel_ts(d, flow_ts);
+  c.ts_rel = rel_ts(d, ts); c.dur = dur; xs64(c, X_D0_LO, (uint64_t)rel_ts(d, flow_ts));
   c.pid = op_pid(d, d.op_device[i]); c.tid = abs_tid(d.op_resource[i]); c.ext = ext; c.aux = (uint32_t)type;
   c.name = d.op_name[i]; c.corr = d.op_flow[i];
   uint64_t p = 0;
@@ -1164,7 +1150,7 @@ __device__ __forceinline__ uint64_t value_op(int f, const EvCtx& c) {
     case O_DUR: return (uint64_t)c.dur;
     case O_EXT: return (uint64_t)(int64_t)c.ext;
     case O_MD: return c.j;
-    case P_FTS: return (uint64_t)c.flow_ts_rel;
+    case P_FTS: return xl64(c, X_D0_LO);
     default: return c.corr;  // P_FLOW_S, P_FLOW_F
   }
 }
@@ -1184,23 +1170,41 @@ constexpr int C_ANN = 10;  // program selector for annotation spans (not a recor
 // The formatting loop shared by every class: fields [base, base + nf) of the table.  `present` has one
 // bit per field.  T_MD (CPU-side activities only) formats the typed metadata entries of the op
 // (JsonTypedMetadataVisitor, libkineto/include/TypedMetadataJson.h:72-158).
+__device__ __forceinline__ uint64_t field_value(int cls, int f, const EvCtx& c) {
+  switch (cls) {
+    case C_API: return value_api(f, c);
+    case C_KERNEL: return value_kernel(f, c);
+    case C_MEMCPY: case C_MEMCPY2: case C_MEMSET: return value_mem(f, c);
+    case C_ANN: return value_ann(f, c);
+    default: return value_op(f, c);
+  }
+}
+
 template <class S>
 __device__ __forceinline__ void run_fields(S& s, const Dev& d, int cls, int base, int nf, const EvCtx& c, uint64_t present,
                                            unsigned long long* name_bytes) {
-  for (int f = 0; f < nf; f++) {
-    if (!((present >> f) & 1ull)) continue;
-    const FieldDesc fd = g_fields.f[base + f];
-    s.words(g_fields.w + fd.off, fd.len);
-    if (fd.type == T_NONE) continue;
-    uint64_t v;
-    switch (cls) {
-      case C_API: v = value_api(f, c); break;
-      case C_KERNEL: v = value_kernel(f, c); break;
-      case C_MEMCPY: case C_MEMCPY2: case C_MEMSET: v = value_mem(f, c); break;
-      case C_ANN: v = value_ann(f, c); break;
-      default: v = value_op(f, c); break;
+  // Walks the set bits of `present`.  Descriptor and value of the NEXT field are fetched before the
+  // current one is formatted, so their load latency hides behind the formatting work.
+  (void)nf;
+  if (!present) return;
+  int f = __ffsll((long long)present) - 1;
+  present &= present - 1;
+  FieldDesc fd = g_fields.f[base + f];
+  uint64_t v = fd.type != T_NONE ? field_value(cls, f, c) : 0ull;
+  while (true) {
+    const bool more = present != 0;
+    int fn = 0;
+    FieldDesc fdn = fd;
+    uint64_t vn = 0;
+    if (more) {
+      fn = __ffsll((long long)present) - 1;
+      present &= present - 1;
+      fdn = g_fields.f[base + fn];
+      vn = fdn.type != T_NONE ? field_value(cls, fn, c) : 0ull;
     }
+    s.words(g_fields.w + fd.off, fd.len);
     switch (fd.type) {
+      case T_NONE: break;
       case T_U64: put_dec(s, v); break;
       case T_I64: put_sdec(s, (int64_t)v); break;
       case T_TS: put_ts2(s, (int64_t)v); break;
@@ -1225,15 +1229,18 @@ __device__ __forceinline__ void run_fields(S& s, const Dev& d, int cls, int base
         break;
       }
     }
+    if (!more) break;
+    f = fn; fd = fdn; v = vn;
   }
 }
 
 constexpr int kEventThreads = 128;
 
 template <class S>
-__device__ __forceinline__ void format_event(S& s, const Dev& d, int cls, const uint8_t* r, uint64_t j, Tally& t, uint32_t* filt) {
+__device__ __forceinline__ void format_event(S& s, const Dev& d, int cls, const uint8_t* r, uint64_t j, Tally& t, uint32_t* filt,
+                                             uint32_t* scratch) {
   EvCtx c;
-  c.r = r; c.j = j;
+  c.r = r; c.j = j; c.sm = scratch;
   uint64_t present = 0;
   int base = 0, nf = 0;
   bool ok;
@@ -1253,7 +1260,7 @@ __device__ __forceinline__ void format_event(S& s, const Dev& d, int cls, const 
 // the bytes at ev_off[event].
 template <bool WRITE>
 __global__ void __launch_bounds__(kEventThreads, 6) k_events(Dev d) {
-  __shared__ uint32_t s_stage[kEventThreads * 4];
+  __shared__ uint32_t s_ctx[X_COUNT * kEventThreads];
   __shared__ unsigned long long s_cnt[8];
   if (threadIdx.x < 8) s_cnt[threadIdx.x] = 0;
   __syncthreads();
@@ -1278,7 +1285,7 @@ __global__ void __launch_bounds__(kEventThreads, 6) k_events(Dev d) {
       const uint8_t* r = cls == C_OP ? nullptr : d.cupti + (uint64_t)d.work_slot[i] * 8;
       if (!WRITE) {
         CountSink2 s;
-        format_event(s, d, cls, r, j, t, &filt);
+        format_event(s, d, cls, r, j, t, &filt, &s_ctx[threadIdx.x]);
         d.ev_size[ev] = filt ? 0u : s.n;
       } else {
         const uint32_t size = d.ev_size[ev];
@@ -1287,8 +1294,8 @@ __global__ void __launch_bounds__(kEventThreads, 6) k_events(Dev d) {
           if (off + size > d.out_cap) { atomicAdd(&d.counters->device_check, 1ull); }
           else {
             GlobalSink s;
-            s.init(d.out + off, &s_stage[(threadIdx.x >> 5) * 128 + (threadIdx.x & 31)]);
-            format_event(s, d, cls, r, j, t, &filt);
+            s.init(d.out + off);
+            format_event(s, d, cls, r, j, t, &filt, &s_ctx[threadIdx.x]);
             s.finish();
           }
         }
@@ -1334,15 +1341,15 @@ __global__ void k_span_collect(Dev d, SpanRec* out, unsigned int* n_out) {
 template <bool WRITE>
 __global__ void __launch_bounds__(kEventThreads) k_annotations(Dev d, const SpanRec* spans, uint32_t n, uint32_t* sizes,
                                                                const uint64_t* offs, uint64_t out_base) {
-  __shared__ uint32_t s_stage[kEventThreads * 4];
   const uint32_t i = blockIdx.x * kEventThreads + threadIdx.x;
   if (i >= n) return;
   const SpanRec r = spans[i];
   int64_t dur = r.end - r.start;
   if (dur < 0) dur = 0;
   unsigned long long nb = 0;
+  __shared__ uint32_t s_ctx[X_COUNT * kEventThreads];
   EvCtx c;
-  c.r = nullptr; c.j = 0;
+  c.r = nullptr; c.j = 0; c.sm = &s_ctx[threadIdx.x];
   c.name = r.op_row < d.n_ops ? d.op_name[r.op_row] : 0xFFFFFFFFu; c.pid = r.device; c.tid = r.stream;
   c.ts_rel = rel_ts(d, r.start - 1); c.dur = dur + 2; c.ext = r.op_id;
   uint64_t p = (1ull << N_COUNT) - 1ull;
@@ -1350,7 +1357,7 @@ __global__ void __launch_bounds__(kEventThreads) k_annotations(Dev d, const Span
   if (!WRITE) { CountSink2 s; run_fields(s, d, C_ANN, ANN_BASE, N_COUNT, c, p, &nb); sizes[i] = s.n; }
   else {
     GlobalSink s;
-    s.init(d.out + out_base + offs[i], &s_stage[(threadIdx.x >> 5) * 128 + (threadIdx.x & 31)]);
+    s.init(d.out + out_base + offs[i]);
     run_fields(s, d, C_ANN, ANN_BASE, N_COUNT, c, p, &nb);
     s.finish();
   }
