@@ -857,7 +857,7 @@ struct EvCtx {
 // which keeps the formatting loop's register footprint small.
 enum : int { X_D0_LO, X_D0_HI, X_D1_LO, X_D1_HI, X_OCC_PCT, X_OCC_ACTIVE, X_OCC_LIMIT, X_OCC_LREGS, X_OCC_LSMEM, X_OCC_LWARPS,
              X_OCC_LBLOCKS, X_OCC_LBARR, X_OCC_AREGS, X_OCC_ASMEM_LO, X_OCC_ASMEM_HI, X_COUNT };
-constexpr int kCtxStride = 128;  // = kEventThreads
+constexpr int kCtxStride = 128;  // must equal kEventThreads (checked below)
 __device__ __forceinline__ void xs(const EvCtx& c, int i, uint32_t v) { c.sm[i * kCtxStride] = v; }
 __device__ __forceinline__ uint32_t xl(const EvCtx& c, int i) { return c.sm[i * kCtxStride]; }
 __device__ __forceinline__ void xs64(const EvCtx& c, int i, uint64_t v) { xs(c, i, (uint32_t)v); xs(c, i + 1, (uint32_t)(v >> 32)); }
@@ -1235,6 +1235,7 @@ __device__ __forceinline__ void run_fields(S& s, const Dev& d, int cls, int base
 }
 
 constexpr int kEventThreads = 128;
+static_assert(kEventThreads == kCtxStride, "scratch column stride");
 
 template <class S>
 __device__ __forceinline__ void format_event(S& s, const Dev& d, int cls, const uint8_t* r, uint64_t j, Tally& t, uint32_t* filt,
@@ -1259,7 +1260,7 @@ __device__ __forceinline__ void format_event(S& s, const Dev& d, int cls, const 
 // so a warp formats events of one shape.  WRITE = false: store the byte length; WRITE = true: write
 // the bytes at ev_off[event].
 template <bool WRITE>
-__global__ void __launch_bounds__(kEventThreads, 6) k_events(Dev d) {
+__global__ void __launch_bounds__(kEventThreads, WRITE ? 6 : 8) k_events(Dev d) {
   __shared__ uint32_t s_ctx[X_COUNT * kEventThreads];
   __shared__ unsigned long long s_cnt[8];
   if (threadIdx.x < 8) s_cnt[threadIdx.x] = 0;
