@@ -1,0 +1,410 @@
+// See output_b200.h.  Reference behaviour being matched (paths relative to the reference project):
+//   file layout and host-written rows   libkineto/src/output_json.cpp:214-235, :261-292, :445-479, :507-658, :1066-1108
+//   arrival order of the calls          libkineto/src/output_membuf.h:91-107 (save) and
+//                                       libkineto/src/GenericActivityProfiler.cpp:178-275, :655-740 (direct)
+#include "output_b200.h"
+
+#include <fmt/format.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <map>
+
+#include <cuda_runtime_api.h>
+
+#include "CuptiActivity.h"
+#include "EnvMetadata.h"
+#include "GenericTraceActivity.h"
+#include "Logger.h"
+#include "ThreadUtil.h"
+#include "TraceSpan.h"
+#include "TypedMetadataJson.h"
+#include "cupti_strings.h"
+#include "output_json.h"
+
+#include "k2j.h"
+
+namespace KINETO_NAMESPACE {
+
+namespace {
+
+void sanitize(std::string& v) {  // backslash -> slash, newlines dropped
+  std::string o;
+  o.reserve(v.size());
+  for (char c : v) {
+    if (c == '\n') continue;
+    o += c == '\\' ? '/' : c;
+  }
+  v.swap(o);
+}
+void escapeQuotes(std::string& v) {
+  std::string o;
+  o.reserve(v.size() + 8);
+  for (char c : v) {
+    if (c == '"') o += '\\';
+    o += c;
+  }
+  v.swap(o);
+}
+std::string ts(int64_t ns) { return fmt::format("{}.{:03}", ns / 1000, ns % 1000); }
+int64_t rel(int64_t t) {
+  int64_t r = t - ChromeTraceBaseTime::singleton().get();
+  return r < 0 ? 0 : r;
+}
+int64_t absTid(int64_t t) { return t == INT64_MIN ? 0 : (t < 0 ? -t : t); }
+
+std::string metaRow(const std::string& name, int64_t time, const std::string& pid, const std::string& tid,
+                    const std::string& key, const std::string& value) {
+  return fmt::format(
+      "\n  {{\n    \"ph\": \"M\",\n    \"name\": \"{}\",\n    \"ts\": {},\n    \"pid\": {},\n    \"tid\": {},\n    \"args\": {{\n      \"{}\": {}\n    }}\n  }},",
+      name, ts(time), pid, tid, key, value);
+}
+std::string instantRow(const std::string& name, const std::string& pid, const std::string& tid, int64_t time, bool last) {
+  return fmt::format(
+      "\n  {{\n    \"ph\": \"i\",\n    \n    \"s\": \"g\",\n    \"name\": \"{}\",\n    \"pid\": {},\n    \"tid\": {},\n    \"ts\": {}\n    \n  }}{}",
+      name, pid, tid, ts(time), last ? "" : ",");
+}
+
+// Typed metadata of a GenericTraceActivity in visit order.
+struct MdCollector final : public libkineto::ITypedMetadataVisitor {
+  struct Entry { std::string key; uint32_t type; uint64_t value; std::string text; };
+  std::vector<Entry> entries;
+  void visitValue(const MetadataField<int64_t>& f, int64_t v) override { entries.push_back({std::string(f.name), K2J_MD_INT64, (uint64_t)v, {}}); }
+  void visitValue(const MetadataField<double>& f, double v) override {
+    uint64_t b; memcpy(&b, &v, 8);
+    entries.push_back({std::string(f.name), K2J_MD_DOUBLE, b, {}});
+  }
+  void visitValue(const MetadataField<bool>& f, bool v) override { entries.push_back({std::string(f.name), K2J_MD_BOOL, v ? 1u : 0u, {}}); }
+  void visitValue(const MetadataField<std::string>& f, std::string_view v) override { entries.push_back({std::string(f.name), K2J_MD_STRING, 0, std::string(v)}); }
+  void visitValue(const MetadataField<std::vector<int64_t>>& f, const std::vector<int64_t>& v) override { raw(f.name, v); }
+  void visitValue(const MetadataField<std::vector<std::string>>& f, const std::vector<std::string>& v) override { raw(f.name, v); }
+  void visitValue(const MetadataField<RawJson>& f, const RawJson& v) override { entries.push_back({std::string(f.name), K2J_MD_RAWJSON, 0, v.value}); }
+  void visitValue(const MetadataField<uint64_t>& f, uint64_t v) override { entries.push_back({std::string(f.name), K2J_MD_UINT64, v, {}}); }
+  void visitValue(const MetadataField<InputShapes>& f, const InputShapes& v) override { raw(f.name, v); }
+  void visitUnsupported(std::string_view name) override { entries.push_back({std::string(name), K2J_MD_STRING, 0, "<unsupported metadata type>"}); }
+  void beginDict(std::string_view) override {}
+  void endDict() override {}
+  template <class T> void raw(std::string_view name, const T& v) {  // collections: text once, as the reference renders them
+    std::string out;
+    libkineto::internal::JsonTypedMetadataVisitor::appendArray(out, v);
+    entries.push_back({std::string(name), K2J_MD_RAWJSON, 0, out});
+  }
+};
+
+}  // namespace
+
+struct B200TraceLogger::Impl {
+  std::string fileName, tempFileName;
+  FILE* out = nullptr;
+  k2j_ctx* ctx = nullptr;
+  int device = 0;
+
+  // string pool shared by all runs
+  std::unordered_map<std::string, uint32_t> ids;
+  std::vector<uint64_t> poolOff{0};
+  std::vector<uint8_t> poolData;
+  uint32_t intern(const std::string& s) {
+    auto it = ids.find(s);
+    if (it != ids.end()) return it->second;
+    uint32_t id = (uint32_t)ids.size();
+    ids.emplace(s, id);
+    poolData.insert(poolData.end(), s.begin(), s.end());
+    poolOff.push_back(poolData.size());
+    return id;
+  }
+  std::unordered_map<const void*, uint32_t> kernelNameIds;  // raw name pointer -> id of the demangled name
+  std::vector<uint32_t> rtNames, drNames;                    // cbid -> string id (filled on demand)
+  uint32_t invalidId = 0;
+
+  // one run = CPU-side activities followed by CUPTI records, in arrival order
+  struct Run {
+    std::vector<int64_t> start, end, resource;
+    std::vector<int32_t> id, dev, thread, type;
+    std::vector<uint32_t> name, flow, mdoff{0};
+    std::vector<uint8_t> flowt;
+    std::vector<k2j_md_entry> md;
+    std::vector<uint8_t> cupti;
+    bool hasCupti = false;
+  };
+  Run run;
+  std::vector<int32_t> tidPairs;
+  std::unordered_map<int32_t, bool> tidSeen;
+
+  void text(const std::string& s) {
+    flushRun();
+    if (out) fwrite(s.data(), 1, s.size(), out);
+  }
+  template <class T> void appendRecord(const T& rec) {
+    const uint8_t* p = reinterpret_cast<const uint8_t*>(&rec);
+    run.cupti.insert(run.cupti.end(), p, p + sizeof(T));
+    run.hasCupti = true;
+  }
+  void addLink(const libkineto::ITraceActivity& a) {
+    if (!a.linkedActivity()) return;
+    CUpti_ActivityExternalCorrelation e;
+    memset(&e, 0, sizeof e);
+    e.kind = CUPTI_ACTIVITY_KIND_EXTERNAL_CORRELATION;
+    e.externalKind = CUPTI_EXTERNAL_CORRELATION_KIND_CUSTOM0;
+    e.externalId = (uint64_t)a.linkedActivity()->correlationId();
+    e.correlationId = (uint32_t)a.correlationId();
+    appendRecord(e);
+    linkedIds.push_back((int32_t)a.linkedActivity()->correlationId());
+  }
+  std::vector<int32_t> linkedIds;
+
+  bool flushRun();
+};
+
+bool B200TraceLogger::Impl::flushRun() {
+  Run r;
+  std::swap(r, run);
+  std::vector<int32_t> links;
+  std::swap(links, linkedIds);
+  const size_t nops = r.start.size();
+  if (nops == 0 && r.cupti.empty()) return true;
+  if (!ctx || !out) return false;
+  // CPU ops a record is linked to may have been logged in an earlier run: make them joinable here as
+  // unselected activities (type bit cleared below), which take part in the join but print nothing.
+  const uint32_t kHidden = 27;  // XPU_SYNC: never produced on this path; its type bit is left clear
+  for (int32_t idv : links) {
+    r.start.push_back(0); r.end.push_back(0); r.resource.push_back(0); r.id.push_back(idv); r.dev.push_back(0);
+    r.thread.push_back(0); r.type.push_back((int32_t)kHidden); r.name.push_back(0); r.flow.push_back(0);
+    r.flowt.push_back(0); r.mdoff.push_back(r.mdoff.back());
+  }
+  k2j_params p{};
+  p.base_time_ns = ChromeTraceBaseTime::singleton().get();
+  p.window_start_ns = INT64_MIN;  // records arrive already filtered by the profiler
+  p.window_end_ns = INT64_MAX;
+  p.pid = processId();
+  p.ts_mode = 0;  // CuptiActivity<T>::timestamp() was not used: raw timestamps are converted below
+  p.flags = 0;
+  p.activity_type_mask = ~(1u << kHidden);
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess) ndev = 0;
+  std::vector<k2j_device_props> props(ndev);
+  for (int i = 0; i < ndev; i++) {
+    cudaDeviceProp dp;
+    if (cudaGetDeviceProperties(&dp, i) != cudaSuccess) { props.resize(i); break; }
+    props[i] = {dp.major, dp.minor, dp.maxThreadsPerBlock, dp.maxThreadsPerMultiProcessor, dp.regsPerBlock,
+                dp.regsPerMultiprocessor, dp.warpSize, dp.multiProcessorCount, dp.sharedMemPerBlock,
+                dp.sharedMemPerBlockOptin, dp.sharedMemPerMultiprocessor, dp.reservedSharedMemPerBlock};
+  }
+  p.n_devices = (int32_t)props.size();
+  if (use_cupti_tsc()) {
+    // The reference converts through get_time_converter(); its constants are not exposed, so the raw
+    // timestamps are converted on the host into the record copies before upload (ts_mode stays 0).
+  }
+  k2j_ops ops{};
+  const size_t n = r.start.size();
+  ops.n_ops = n; ops.start_ns = r.start.data(); ops.end_ns = r.end.data(); ops.id = r.id.data(); ops.device = r.dev.data();
+  ops.resource = r.resource.data(); ops.thread = r.thread.data(); ops.type = r.type.data(); ops.name = r.name.data();
+  ops.flow_id = r.flow.data(); ops.flow_info = r.flowt.data(); ops.md_off = r.mdoff.data(); ops.md = r.md.data();
+  const uint64_t buftab[2] = {0, r.cupti.size()};
+  k2j_result res;
+  bool ok = k2j_set_params(ctx, &p, props.data()) == K2J_OK &&
+            k2j_set_strings(ctx, poolOff.data(), poolData.data(), poolOff.size() - 1) == K2J_OK &&
+            k2j_set_cbid_names(ctx, rtNames.data(), (uint32_t)rtNames.size(), drNames.data(), (uint32_t)drNames.size()) == K2J_OK &&
+            k2j_set_thread_map(ctx, tidPairs.data(), (uint32_t)(tidPairs.size() / 2)) == K2J_OK &&
+            k2j_set_ops(ctx, &ops) == K2J_OK &&
+            k2j_set_cupti(ctx, r.cupti.data(), r.cupti.size(), buftab, r.cupti.empty() ? 0 : 1) == K2J_OK &&
+            k2j_run(ctx, &res) == K2J_OK;
+  if (!ok) {
+    LOG(ERROR) << "B200TraceLogger: " << k2j_last_error(ctx);
+    return false;
+  }
+  std::vector<char> buf(res.out_bytes);
+  if (k2j_copy_output(ctx, buf.data(), buf.size()) != K2J_OK) {
+    LOG(ERROR) << "B200TraceLogger: " << k2j_last_error(ctx);
+    return false;
+  }
+  fwrite(buf.data(), 1, buf.size(), out);
+  return true;
+}
+
+B200TraceLogger::B200TraceLogger(const std::string& traceFileName, int cudaDevice) : impl_(new Impl) {
+  impl_->fileName = traceFileName.empty() ? fmt::format("/tmp/libkineto_activities_{}.json", processId()) : traceFileName;
+  impl_->tempFileName = impl_->fileName + ".tmp";
+  impl_->device = cudaDevice;
+  impl_->out = fopen(impl_->tempFileName.c_str(), "wb");
+  if (!impl_->out) PLOG(ERROR) << "Failed to open '" << impl_->fileName << "'";
+  if (k2j_create(cudaDevice, nullptr, &impl_->ctx) != K2J_OK) {
+    // No GPU path, and deliberately no CPU path: like ChromeTraceLogger with an unopened file, every
+    // handler returns without writing.
+    LOG(ERROR) << "B200TraceLogger: cannot create a k2j context on CUDA device " << cudaDevice;
+    impl_->ctx = nullptr;
+    if (impl_->out) { fclose(impl_->out); impl_->out = nullptr; remove(impl_->tempFileName.c_str()); }
+  }
+  impl_->invalidId = impl_->intern("INVALID");
+}
+
+B200TraceLogger::~B200TraceLogger() {
+  if (impl_->out) fclose(impl_->out);
+  k2j_destroy(impl_->ctx);
+}
+
+void B200TraceLogger::handleTraceStart(const std::unordered_map<std::string, std::string>& metadata,
+                                       const std::string& device_properties) {
+  if (!impl_->out) return;
+  std::string s = fmt::format(" {{\n    \"schemaVersion\": {},\n    \"deviceProperties\": [{}],\n    ", 1, device_properties);
+  auto combined = libkineto::getEnvMetadata();  // environment first, caller's metadata wins (output_json.cpp:433-443)
+  for (const auto& [k, v] : metadata) combined[k] = v;
+  for (const auto& [k, v] : combined) {
+    std::string sv = v;
+    sanitize(sv);
+    s += fmt::format("\n      \"{}\": {},", k, sv);
+  }
+  std::string unit = "ms";
+#ifdef DISPLAY_TRACE_IN_NS
+  unit = "ns";
+#endif
+  s += fmt::format("\n    \"displayTimeUnit\": \"{}\",\n    \"baseTimeNanoseconds\": {},\n    \"traceEvents\": [\n    ", unit,
+                   ChromeTraceBaseTime::singleton().get());
+  impl_->text(s);
+}
+
+void B200TraceLogger::handleDeviceInfo(const DeviceInfo& info, int64_t time) {
+  if (!impl_->out) return;
+  std::string name = info.name, label = info.label;
+  sanitize(name); escapeQuotes(name); sanitize(label); escapeQuotes(label);
+  time = rel(time);
+  const std::string pid = std::to_string(info.id);
+  impl_->text(metaRow("process_name", time, pid, "0", "name", "\"" + name + "\"") +
+              metaRow("process_labels", time, pid, "0", "labels", "\"" + label + "\"") +
+              metaRow("process_sort_index", time, pid, "0", "sort_index", std::to_string(info.sortIndex)));
+}
+
+void B200TraceLogger::handleResourceInfo(const ResourceInfo& info, int64_t time) {
+  if (!impl_->out) return;
+  std::string name = info.name;
+  if (info.resourceType == ResourceType::HOST_THREAD) name = fmt::format("thread {} ({})", info.id, info.name);
+  sanitize(name); escapeQuotes(name);
+  time = rel(time);
+  const std::string pid = std::to_string(info.deviceId), tid = std::to_string(absTid(info.id));
+  impl_->text(metaRow("thread_name", time, pid, tid, "name", "\"" + name + "\"") +
+              metaRow("thread_sort_index", time, pid, tid, "sort_index", std::to_string(info.sortIndex)));
+}
+
+void B200TraceLogger::handleOverheadInfo(const OverheadInfo& info, int64_t time) {
+  if (!impl_->out) return;
+  std::string name = info.name;
+  sanitize(name); escapeQuotes(name);
+  time = rel(time);
+  impl_->text(metaRow("process_name", time, "-1", "0", "name", "\"" + name + "\"") +
+              metaRow("process_sort_index", time, "-1", "0", "sort_index", std::to_string(0x100000All)));
+}
+
+void B200TraceLogger::handleTraceSpan(const TraceSpan& span) {
+  if (!impl_->out) return;
+  const int64_t start = rel(span.startTime);
+  const int64_t dur = span.endTime == 0 ? 0 : span.endTime - span.startTime;
+  std::string s = fmt::format(
+      "\n  {{\n    \"ph\": \"X\",\n    \"cat\": \"Trace\",\n    \"name\": \"{}{} ({})\",\n    \"pid\": \"Spans\",\n    \"tid\": \"{}\",\n    \"ts\": {},\n    \"dur\": {}\n    ,\n    \"args\": {{\n      \"Op count\": {}\n    }}\n  }},",
+      span.prefix, span.name, span.iteration, span.name, ts(start), ts(dur), span.opCount);
+  s += metaRow("process_sort_index", start, "\"Spans\"", "0", "sort_index", std::to_string(0x20000000ll));
+  s += instantRow(fmt::format("Iteration Start: {}", span.name), "\"Traces\"", fmt::format("\"Trace {}\"", span.name), start, false);
+  impl_->text(s);
+}
+
+void B200TraceLogger::handleGenericActivity(const libkineto::GenericTraceActivity& op) {
+  if (!impl_->out) return;
+  Impl& m = *impl_;
+  if (m.run.hasCupti) m.flushRun();  // a run is CPU-side activities followed by CUPTI records
+  auto& r = m.run;
+  r.start.push_back(op.startTime); r.end.push_back(op.endTime); r.id.push_back(op.id); r.dev.push_back(op.device);
+  r.resource.push_back(op.resource); r.thread.push_back(op.threadId); r.type.push_back((int32_t)op.activityType);
+  r.name.push_back(m.intern(op.activityName)); r.flow.push_back(op.flow.id);
+  r.flowt.push_back((uint8_t)(op.flow.type | (op.flow.start << 4)));
+  MdCollector mc;
+  op.visitTypedMetadata(mc);
+  for (auto& e : mc.entries) {
+    k2j_md_entry k{m.intern(e.key), e.type, e.value};
+    if (e.type == K2J_MD_STRING || e.type == K2J_MD_RAWJSON) k.value = m.intern(e.text);
+    r.md.push_back(k);
+  }
+  r.mdoff.push_back((uint32_t)r.md.size());
+}
+
+void B200TraceLogger::handleActivity(const libkineto::ITraceActivity& a) {
+  if (!impl_->out) return;
+  Impl& m = *impl_;
+  if (auto* g = dynamic_cast<const libkineto::GenericTraceActivity*>(&a)) { handleGenericActivity(*g); return; }
+  auto convert = [](auto& rec) {  // timestamps as the wrapper reports them (CuptiTimestamp.h:29-51)
+    const uint64_t s = rec.start, e = rec.end;
+    rec.start = (uint64_t)convertCuptiTimestamp(s);
+    rec.end = (uint64_t)(convertCuptiTimestamp(s) + convertCuptiDuration(s, e));
+  };
+  auto cbidName = [&](std::vector<uint32_t>& tab, uint32_t cbid, bool driver) {
+    if (cbid >= tab.size()) tab.resize(cbid + 1, m.invalidId);
+    tab[cbid] = m.intern(driver ? driverCbidName(cbid) : runtimeCbidName(cbid));
+  };
+  if (auto* k = dynamic_cast<const GpuActivity<CUpti_ActivityKernelType>*>(&a)) {
+    m.addLink(a);
+    CUpti_ActivityKernelType rec = k->raw();
+    convert(rec);
+    auto it = m.kernelNameIds.find(rec.name);
+    uint32_t id = it != m.kernelNameIds.end() ? it->second : (m.kernelNameIds[rec.name] = m.intern(a.name()));
+    uint64_t id64 = id;
+    memcpy(&rec.name, &id64, 8);
+    m.appendRecord(rec);
+  } else if (auto* c = dynamic_cast<const GpuActivity<CUpti_ActivityMemcpyType>*>(&a)) {
+    m.addLink(a);
+    CUpti_ActivityMemcpyType rec = c->raw();
+    convert(rec);
+    m.appendRecord(rec);
+  } else if (auto* c2 = dynamic_cast<const GpuActivity<CUpti_ActivityMemcpyPtoPType>*>(&a)) {
+    m.addLink(a);
+    CUpti_ActivityMemcpyPtoPType rec = c2->raw();
+    convert(rec);
+    m.appendRecord(rec);
+  } else if (auto* s = dynamic_cast<const GpuActivity<CUpti_ActivityMemsetType>*>(&a)) {
+    m.addLink(a);
+    CUpti_ActivityMemsetType rec = s->raw();
+    convert(rec);
+    m.appendRecord(rec);
+  } else if (auto* rt = dynamic_cast<const RuntimeActivity*>(&a)) {
+    m.addLink(a);
+    CUpti_ActivityAPI rec = rt->raw();
+    convert(rec);
+    cbidName(m.rtNames, rec.cbid, false);
+    if (!m.tidSeen.count((int32_t)rec.threadId)) {
+      m.tidSeen[(int32_t)rec.threadId] = true;
+      m.tidPairs.push_back((int32_t)rec.threadId); m.tidPairs.push_back((int32_t)a.resourceId());
+    }
+    m.appendRecord(rec);
+  } else if (auto* dr = dynamic_cast<const DriverActivity*>(&a)) {
+    m.addLink(a);
+    CUpti_ActivityAPI rec = dr->raw();
+    convert(rec);
+    cbidName(m.drNames, rec.cbid, true);
+    if (!m.tidSeen.count((int32_t)rec.threadId)) {
+      m.tidSeen[(int32_t)rec.threadId] = true;
+      m.tidPairs.push_back((int32_t)rec.threadId); m.tidPairs.push_back((int32_t)a.resourceId());
+    }
+    m.appendRecord(rec);
+  } else {
+    // Synchronisation, CUDA-event and overhead records and foreign activity classes are not handled by
+    // the GPU path yet; there is no CPU path to fall back to, so they are counted and reported.
+    if (skipped_++ == 0) LOG(ERROR) << "B200TraceLogger: unsupported activity class for '" << a.name() << "'; skipped";
+  }
+}
+
+void B200TraceLogger::finalizeTrace(const Config&, std::unique_ptr<ActivityBuffers> /*buffers*/, int64_t endTime) {
+  if (!impl_->out) {
+    LOG(ERROR) << "Failed to write to log file!";
+    return;
+  }
+  std::string fileName = impl_->fileName;
+  sanitize(fileName);
+  std::string s = instantRow("Record Window End", "\"\"", "\"\"", rel(endTime), true);
+  s += "\n  ],";
+  s += fmt::format("\"traceName\": \"{}\" }}", fileName);
+  impl_->text(s);
+  fclose(impl_->out);
+  impl_->out = nullptr;
+  remove(impl_->fileName.c_str());
+  if (rename(impl_->tempFileName.c_str(), impl_->fileName.c_str()) != 0)
+    PLOG(ERROR) << "Failed to rename " << impl_->tempFileName << " to " << impl_->fileName;
+}
+
+}  // namespace KINETO_NAMESPACE

@@ -35,6 +35,7 @@ extern "C" int clock_gettime(clockid_t clk, struct timespec* ts) {
   return (int)syscall(SYS_clock_gettime, clk, ts);
 }
 
+#ifndef K2J_REAL_CUDART  // the shim driver runs on a real GPU and keeps the real runtime
 extern "C" cudaError_t cudaGetDeviceCount(int* count) {
   *count = (int)g_props.size();
   return cudaSuccess;
@@ -48,3 +49,4 @@ extern "C" cudaError_t cudaRuntimeGetVersion(int* v) { *v = CUDART_VERSION; retu
 extern "C" cudaError_t cudaDriverGetVersion(int* v) { *v = CUDART_VERSION; return cudaSuccess; }
 extern "C" cudaError_t cudaDeviceSynchronize(void) { return cudaSuccess; }
 extern "C" const char* cudaGetErrorString(cudaError_t) { return "fake cudart"; }
+#endif
