@@ -57,6 +57,9 @@ typedef struct {
 } k2j_params;
 
 #define K2J_FLAG_USER_ANNOTATIONS 1 /* GPU_USER_ANNOTATION selected (GenericActivityProfiler.cpp:424) */
+#define K2J_FLAG_SORT_BY_START 2     /* GPU-side events in stable order of their start timestamp (64-bit
+                                       radix sort).  The reference never sorts: the output equals the
+                                       reference's on buffers pre-sorted that way. */
 #define K2J_FLAG_PID0_OVERRIDE 4    /* CPU activities with device 0 are shown under params.pid: what
                                        ActivityTrace::save() writes after the pid-0 override of
                                        GenericActivityProfiler.cpp:263-271 */

@@ -14,6 +14,7 @@
 #include <vector>
 
 #include "k2j_kernels.cuh"
+#include "k2j_sort.cuh"
 
 using namespace k2j;
 
@@ -65,6 +66,7 @@ struct k2j_ctx {
   DevBuf esc_name, esc_md, esc_name_len, esc_md_len;
   DevBuf slot_code, exit_map, chunk_entry, chunk_cnt, chunk_base, scan_sums, scan_totals;
   DevBuf ds_tab, span_key, span_nstart, span_end, span_nfirst, span_row, span_out, span_cnt, ann_size, ann_off;
+  DevBuf sort_keys[2], sort_vals[2], sort_hist, sort_base, sort_rank;
   DevBuf tid_tab, corr_tab, user_tab, op_tab, work_slot, work_ev, ev_size, ev_off, out, counters;
   uint64_t* h_totals = nullptr;   // pinned: C_NCOL column totals, then the byte total
   Counters* h_counters = nullptr; // pinned
@@ -134,6 +136,45 @@ k2j_status run_scan(k2j_ctx* c, const uint32_t* in, uint64_t n, uint32_t cols, u
   k_scan_sums<<<cols, kScanThreads, 0, c->stream>>>(sums, nb, totals);
   k_scan_apply<<<dim3(nb, cols), kScanThreads, 0, c->stream>>>(in, n, n, sums, nb, out);
   *launches += 3;
+  K2J_CUDA(c, cudaGetLastError());
+  return K2J_OK;
+}
+
+// Stable LSD radix sort of the GPU-side events by start timestamp; afterwards work_ev holds sorted ranks.
+k2j_status sort_gpu_events(k2j_ctx* c, uint64_t n) {
+  cudaStream_t s = c->stream;
+  Dev& d = c->d;
+  const uint64_t span = (uint64_t)(c->params.window_end_ns - c->params.window_start_ns);
+  int bits = 1;
+  while (bits < 64 && ((span + 1) >> bits)) bits++;
+  const int passes = (bits + 7) / 8;
+  const uint32_t tiles = (uint32_t)((n + kSortTile - 1) / kSortTile);
+  for (int i = 0; i < 2; i++) {
+    K2J_CUDA(c, c->sort_keys[i].reserve(n * 8));
+    K2J_CUDA(c, c->sort_vals[i].reserve(n * 4));
+  }
+  K2J_CUDA(c, c->sort_hist.reserve((size_t)tiles * 256 * 4));
+  K2J_CUDA(c, c->sort_base.reserve((size_t)tiles * 256 * 8));
+  K2J_CUDA(c, c->sort_rank.reserve(n * 4));
+  const uint32_t wl_blocks = (uint32_t)((d.ops_begin + 255) / 256);
+  k_sort_keys<<<wl_blocks, 256, 0, s>>>(d, c->sort_keys[0].as<uint64_t>(), c->sort_vals[0].as<uint32_t>(), span);
+  c->launches++;
+  int cur = 0;
+  for (int pass = 0; pass < passes; pass++) {
+    k_rs_hist<<<tiles, kSortThreads, 0, s>>>(c->sort_keys[cur].as<uint64_t>(), n, 8 * pass, c->sort_hist.as<uint32_t>(), tiles);
+    c->launches++;
+    k2j_status st = run_scan(c, c->sort_hist.as<uint32_t>(), (uint64_t)tiles * 256, 1, c->sort_base.as<uint64_t>(),
+                             c->scan_totals.as<uint64_t>() + 13, &c->launches);
+    if (st) return st;
+    k_rs_scatter<<<tiles, kSortThreads, 0, s>>>(c->sort_keys[cur].as<uint64_t>(), c->sort_vals[cur].as<uint32_t>(), n, 8 * pass,
+                                                c->sort_base.as<uint64_t>(), tiles, c->sort_keys[cur ^ 1].as<uint64_t>(),
+                                                c->sort_vals[cur ^ 1].as<uint32_t>());
+    c->launches++;
+    cur ^= 1;
+  }
+  k_rs_invert<<<(uint32_t)((n + 255) / 256), 256, 0, s>>>(c->sort_vals[cur].as<uint32_t>(), n, c->sort_rank.as<uint32_t>());
+  k_sort_remap<<<wl_blocks, 256, 0, s>>>(d, c->sort_rank.as<uint32_t>());
+  c->launches += 2;
   K2J_CUDA(c, cudaGetLastError());
   return K2J_OK;
 }
@@ -224,7 +265,8 @@ void k2j_destroy(k2j_ctx* c) {
   for (DevBuf* b : {&c->d_props, &c->d_buf_off, &c->d_buf_valid, &c->d_buf_chunk_base, &c->esc_name, &c->esc_md,
                     &c->esc_name_len, &c->esc_md_len, &c->slot_code, &c->exit_map, &c->chunk_entry, &c->chunk_cnt,
                     &c->chunk_base, &c->scan_sums, &c->scan_totals, &c->ds_tab, &c->span_key, &c->span_nstart, &c->span_end, &c->span_nfirst, &c->span_row,
-                    &c->span_out, &c->span_cnt, &c->ann_size, &c->ann_off, &c->tid_tab, &c->corr_tab, &c->user_tab, &c->op_tab,
+                    &c->span_out, &c->span_cnt, &c->ann_size, &c->ann_off, &c->sort_keys[0], &c->sort_keys[1], &c->sort_vals[0],
+                    &c->sort_vals[1], &c->sort_hist, &c->sort_base, &c->sort_rank, &c->tid_tab, &c->corr_tab, &c->user_tab, &c->op_tab,
                     &c->work_slot, &c->work_ev, &c->ev_size, &c->ev_off, &c->out, &c->counters, &c->ext_local})
     b->release();
   if (c->h_totals) cudaFreeHost(c->h_totals);
@@ -550,6 +592,12 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
   if (d.n_join_ops) { k_build_ops<<<(uint32_t)((d.n_join_ops + 255) / 256), 256, 0, s>>>(d); c->launches++; }
   K2J_CUDA(c, cudaGetLastError());
   K2J_CUDA(c, cudaEventRecord(c->ev[2], s));
+
+  // ---- optional: GPU-side events in stable order of their start timestamp ----
+  if ((c->params.flags & K2J_FLAG_SORT_BY_START) && n_gpu_events > 1) {
+    k2j_status st = sort_gpu_events(c, n_gpu_events);
+    if (st) return st;
+  }
 
   // ---- size pass, scan, emit pass ----
   uint64_t total_bytes = 0, ann_bytes = 0;

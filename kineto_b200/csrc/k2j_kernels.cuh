@@ -1320,6 +1320,34 @@ __global__ void __launch_bounds__(kEventThreads, WRITE ? 6 : 8) k_events(Dev d) 
   }
 }
 
+// ---- optional ordering by start timestamp ----
+// Sort key of every GPU-side event: converted start time relative to the window start (records outside
+// the window emit nothing, their position does not matter).  Values are the buffer-order event numbers.
+__global__ void k_sort_keys(Dev d, uint64_t* keys, uint32_t* vals, uint64_t span) {
+  const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= d.ops_begin) return;
+  int cls = 0;
+#pragma unroll
+  for (int c = 1; c < C_EXT; c++) if (i >= d.cls_begin[c]) cls = c;
+  if (i - d.cls_begin[cls] >= d.cls_count[cls]) return;  // padding
+  const uint8_t* r = d.cupti + (uint64_t)d.work_slot[i] * 8;
+  const int64_t ts = conv_ts(d, *reinterpret_cast<const uint64_t*>(r + (cls == C_API ? 8 : 16)));
+  uint64_t key = 0;
+  if (ts >= d.win_start) { key = (uint64_t)(ts - d.win_start); if (key > span) key = span + 1; }
+  const uint32_t e = d.work_ev[i] - (uint32_t)d.n_ops;
+  keys[e] = key;
+  vals[e] = e;
+}
+__global__ void k_sort_remap(Dev d, const uint32_t* rank) {
+  const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= d.ops_begin) return;
+  int cls = 0;
+#pragma unroll
+  for (int c = 1; c < C_EXT; c++) if (i >= d.cls_begin[c]) cls = c;
+  if (i - d.cls_begin[cls] >= d.cls_count[cls]) return;
+  d.work_ev[i] = (uint32_t)d.n_ops + rank[d.work_ev[i] - (uint32_t)d.n_ops];
+}
+
 // ---- user-annotation spans: collect, then format in the order the host determined ----
 __global__ void k_span_collect(Dev d, SpanRec* out, unsigned int* n_out) {
   const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x;

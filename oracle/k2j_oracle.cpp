@@ -25,6 +25,7 @@
 // Output: the "activities" part of the trace file, i.e. every event written between the header /
 // metadata rows and the CPU trace span: CPU-op events, then GPU-side events in buffer order, then
 // gpu_user_annotation spans (ActivityTrace::save order, libkineto/src/output_membuf.h:91-107).
+#include <algorithm>
 #include <charconv>
 #include <cinttypes>
 #include <climits>
@@ -558,8 +559,24 @@ struct Run {
     e.md = f.j; emit(out, e); afterGpu(e);
   }
 
+  int64_t recordStart(const uint8_t* r, uint32_t kind) {
+    switch (kind) {
+      case K_RUNTIME: case K_DRIVER: return conv(rd<uint64_t>(r, 8));
+      case K_KERNEL: case K_MEMCPY: case K_MEMCPY2: case K_MEMSET: return conv(rd<uint64_t>(r, 16));
+      default: return INT64_MIN;
+    }
+  }
   void pass2() {
-    forEachRecord([&](const uint8_t* r, uint32_t kind) {
+    // flags bit 1: the records are first put in stable order of their converted start timestamp (the
+    // reference itself never sorts: this equals running it on pre-sorted buffers).
+    std::vector<std::pair<const uint8_t*, uint32_t>> recs;
+    forEachRecord([&](const uint8_t* r, uint32_t kind) { recs.push_back({r, kind}); });
+    if (p.flags & 2) {
+      std::stable_sort(recs.begin(), recs.end(), [&](const auto& a, const auto& b) {
+        return recordStart(a.first, a.second) < recordStart(b.first, b.second);
+      });
+    }
+    for (auto& [r, kind] : recs) {
       c.records++;
       switch (kind) {
         case K_EXTCORR: break;
@@ -571,7 +588,7 @@ struct Run {
         case K_MEMSET: memsetRecord(r); break;
         default: c.unexpected++; break;
       }
-    });
+    }
   }
 
   void annotations() {  // GpuUserEventMap::logEvents, GenericActivityProfiler.cpp:320-327

@@ -135,3 +135,36 @@ CASES = {
     "mixed_400": lambda: synth.gen_mixed(400, seed=33, pool_size=100, escape_fraction=0.2),
     "tsc_100": lambda: tsc_trace(100),
 }
+
+
+def with_flags(trace: tf.Trace, extra: int) -> tf.Trace:
+    """Copy of `trace` with extra flag bits set."""
+    import copy
+    t = copy.copy(trace)
+    t.params = trace.params.copy()
+    t.params["flags"] = int(trace.params["flags"][0]) | extra
+    return t
+
+
+def presorted_launches(trace: tf.Trace) -> tf.Trace:
+    """The same launches trace with its runtime and kernel records moved into stable order of their
+    start timestamps (EXTERNAL_CORRELATION records first): what the sort option must reproduce."""
+    import copy
+    g = trace.cupti.reshape(-1, 272)
+    ext = np.ascontiguousarray(g[:, :24]).view(tf.EXTCORR).reshape(-1)
+    api = np.ascontiguousarray(g[:, 24:64]).view(tf.API).reshape(-1)
+    ker = np.ascontiguousarray(g[:, 64:]).view(tf.KERNEL9).reshape(-1)
+    starts = np.concatenate([api["start"].astype(np.int64), ker["start"].astype(np.int64)])
+    kind = np.concatenate([np.zeros(len(api), np.int8), np.ones(len(ker), np.int8)])
+    orig = np.concatenate([np.arange(len(api)) * 3 + 1, np.arange(len(ker)) * 3 + 2])
+    o = np.lexsort((orig, starts))
+    order = np.concatenate([np.zeros(len(ext), np.int8), kind[o] + 1])
+
+    def by_start(a):
+        raw = np.ascontiguousarray(a).view(np.uint8).reshape(len(a), -1)
+        return raw[np.argsort(a["start"], kind="stable")].reshape(-1).view(a.dtype)
+
+    t = copy.copy(trace)
+    t.cupti, offs = tf.interleave([ext, by_start(api), by_start(ker)], order)
+    t.buftab = tf.make_buftab(offs)
+    return t

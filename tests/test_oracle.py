@@ -52,6 +52,19 @@ def test_port_matches_live_reference(gen):
     assert got == want, helpers.first_diff(want, got)
 
 
+@pytest.mark.skipif(not helpers.have_ref(), reason="reference build (oracle/_ref) not present")
+def test_sort_option_equals_reference_on_presorted_buffers():
+    """The reference never sorts; ordering by start timestamp is defined as what the reference writes
+    for buffers that were sorted beforehand."""
+    trace = synth.gen_kernel_launches(3000, seed=55, pool_size=100)
+    got, _ = helpers.run_port(cases.with_flags(trace, tf.FLAG_SORT_BY_START))
+    doc, _ = helpers.run_ref(cases.presorted_launches(trace))
+    want = helpers.activities_segment(doc)
+    assert got == want, helpers.first_diff(want, got)
+    plain, _ = helpers.run_port(trace)
+    assert plain != got
+
+
 def test_reference_known_answers_in_port_output():
     """Known-answer strings the reference's own tests pin (libkineto/test/CuptiActivityProfilerTest.cpp:564-582,
     libkineto/test/OutputJsonTest.cpp:145-152, libkineto/test/TypedMetadataTest.cpp:164-178)."""
