@@ -67,7 +67,7 @@ struct k2j_ctx {
   DevBuf slot_code, exit_map, chunk_entry, chunk_cnt, chunk_base, scan_sums, scan_totals;
   DevBuf ds_tab, span_key, span_nstart, span_end, span_nfirst, span_row, span_out, span_cnt, ann_size, ann_off;
   DevBuf sort_keys[2], sort_vals[2], sort_hist, sort_base, sort_rank;
-  DevBuf tid_tab, corr_tab, user_tab, op_tab, work_slot, work_ev, ev_size, ev_off, out, counters;
+  DevBuf tid_tab, corr_tab, user_tab, op_tab, work_slot, work_ev, ev_size, ev_off, ev_ext, out, counters;
   uint64_t* h_totals = nullptr;   // pinned: C_NCOL column totals, then the byte total
   Counters* h_counters = nullptr; // pinned
   cudaEvent_t ev[8]{};
@@ -548,7 +548,8 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
   }
   K2J_CUDA(c, c->ev_size.reserve(std::max<uint64_t>(1, d.n_events) * 4));
   K2J_CUDA(c, c->ev_off.reserve(std::max<uint64_t>(1, d.n_events) * 8));
-  d.ev_size = c->ev_size.as<uint32_t>(); d.ev_off = c->ev_off.as<uint64_t>();
+  K2J_CUDA(c, c->ev_ext.reserve(std::max<uint64_t>(1, d.n_events) * 4));
+  d.ev_size = c->ev_size.as<uint32_t>(); d.ev_off = c->ev_off.as<uint64_t>(); d.ev_ext = c->ev_ext.as<int32_t>();
   const uint32_t corr_cap = pow2_at_least(2 * d.n_ext_all + 2);
   const uint32_t op_cap = pow2_at_least(2 * d.n_join_ops + 2);
   K2J_CUDA(c, c->corr_tab.reserve((size_t)corr_cap * 8));

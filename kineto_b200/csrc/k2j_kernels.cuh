@@ -105,6 +105,7 @@ struct Dev {
   uint32_t* work_slot; uint32_t* work_ev; uint64_t cls_begin[C_NCLASS]; uint64_t cls_count[C_NCLASS];
   uint64_t ops_begin; uint64_t n_work;
   uint32_t* ev_size; const uint64_t* ev_off; uint64_t n_events;
+  int32_t* ev_ext;        // per event: id of the linked CPU op found by the size pass (0 = none)
   uint8_t* out; uint64_t out_cap;
   Counters* counters;
 };
@@ -866,7 +867,8 @@ __device__ __forceinline__ uint64_t xl64(const EvCtx& c, int i) { return (uint64
 // Each gather returns false if the record produces no event (`*filt`: 1 blocklisted, 2 outside the window).
 
 // handleRuntimeActivity / handleDriverActivity (libkineto/src/CuptiActivityProfiler.cpp:304-358)
-__device__ __forceinline__ bool gather_api(const Dev& d, const uint8_t* r, EvCtx& c, uint64_t* present, Tally& t, uint32_t* filt) {
+__device__ __forceinline__ bool gather_api(const Dev& d, const uint8_t* r, EvCtx& c, uint64_t* present, Tally& t, uint32_t* filt,
+                                           bool counting, int32_t ext_known) {
   const uint2 a = *reinterpret_cast<const uint2*>(r);        // kind, cbid (40-byte records are 8-byte aligned)
   const uint64_t st = *reinterpret_cast<const uint64_t*>(r + 8), en = *reinterpret_cast<const uint64_t*>(r + 16);
   const uint2 b = *reinterpret_cast<const uint2*>(r + 24);   // processId, threadId
@@ -891,8 +893,9 @@ __device__ __forceinline__ bool gather_api(const Dev& d, const uint8_t* r, EvCtx
     const uint32_t idx = tab_find(d.tid_tab, d.tid_mask, (uint32_t)tid);
     if (idx != 0xFFFFFFFFu) tid = idx < d.n_tid_pairs ? d.tid_pairs[2 * idx + 1] : (int32_t)d.op_resource[idx - d.n_tid_pairs];
   }
-  int32_t ext = 0;
-  const bool has_ext = linked_op(d, corr, &ext) && ext != 0;
+  int32_t ext = ext_known;
+  if (counting) linked_op(d, corr, &ext);
+  const bool has_ext = ext != 0;
   const uint32_t ntab = driver ? d.n_dr : d.n_rt;
   const bool named = cbid < ntab;
   c.ts_rel = rel_ts(d, ts); c.dur = dur < 0 ? 0 : dur; c.pid = d.pid; c.tid = abs_tid(tid); c.ext = ext; c.corr = corr;
@@ -961,7 +964,7 @@ __device__ __forceinline__ void occupancy_metrics(const Dev& d, uint32_t dev, bo
 
 // GpuActivity<Kernel> (libkineto/src/CuptiActivity.h:499-576)
 __device__ __forceinline__ bool gather_kernel(const Dev& d, const uint8_t* r, EvCtx& c, uint64_t* present, Tally& t, uint32_t* filt,
-                                              bool counting) {
+                                              bool counting, int32_t ext_known) {
   const uint64_t st = *reinterpret_cast<const uint64_t*>(r + 16), en = *reinterpret_cast<const uint64_t*>(r + 24);
   const int64_t ts = conv_ts(d, st), dur = conv_dur(d, st, en);
   if (out_of_range(d, ts, dur)) { *filt = 2; return false; }
@@ -971,8 +974,9 @@ __device__ __forceinline__ bool gather_kernel(const Dev& d, const uint8_t* r, Ev
   const int32_t bx = *reinterpret_cast<const int32_t*>(r + 64), by = *reinterpret_cast<const int32_t*>(r + 68), bz = *reinterpret_cast<const int32_t*>(r + 72);
   const int32_t ssm = *reinterpret_cast<const int32_t*>(r + 76), dsm = *reinterpret_cast<const int32_t*>(r + 80);
   const uint32_t regs = *reinterpret_cast<const uint16_t*>(r + 6);
-  int32_t ext = 0;
-  const bool has_ext = linked_op(d, corr, &ext) && ext != 0;
+  int32_t ext = ext_known;
+  if (counting) linked_op(d, corr, &ext);
+  const bool has_ext = ext != 0;
   // blocksPerSm / warpsPerSm (DeviceProperties.cpp:161-174): 32-bit wrapping products, single-precision
   // arithmetic without contraction.
   const int32_t grid_prod = (int32_t)((uint32_t)gx * (uint32_t)gy * (uint32_t)gz);
@@ -1039,15 +1043,16 @@ __device__ __forceinline__ uint64_t value_kernel(int f, const EvCtx& c) {
 // memcpy / memcpy2 / memset records (libkineto/src/CuptiActivity.h:586-712)
 template <int CLS>
 __device__ __forceinline__ bool gather_mem(const Dev& d, const uint8_t* r, EvCtx& c, uint64_t* present, Tally& t, uint32_t* filt,
-                                           bool counting) {
+                                           bool counting, int32_t ext_known) {
   const uint64_t st = *reinterpret_cast<const uint64_t*>(r + 16), en = *reinterpret_cast<const uint64_t*>(r + 24);
   const int64_t ts = conv_ts(d, st), dur = conv_dur(d, st, en);
   if (out_of_range(d, ts, dur)) { *filt = 2; return false; }
   const uint64_t bytes = *reinterpret_cast<const uint64_t*>(r + 8);
   const uint32_t dev = *reinterpret_cast<const uint32_t*>(r + 32), stream = *reinterpret_cast<const uint32_t*>(r + 40);
   const uint32_t corr = *reinterpret_cast<const uint32_t*>(r + (CLS == C_MEMCPY2 ? 60 : 44));
-  int32_t ext = 0;
-  const bool has_ext = linked_op(d, corr, &ext) && ext != 0;
+  int32_t ext = ext_known;
+  if (counting) linked_op(d, corr, &ext);
+  const bool has_ext = ext != 0;
   c.ts_rel = rel_ts(d, ts); c.dur = dur < 0 ? 0 : dur; c.pid = dev; c.tid = stream; c.ext = ext; c.corr = corr;
   c.aux = CLS == C_MEMCPY2 ? 8u : 0u;  // byte shift of the trailing fields in the peer-to-peer layout
   uint64_t p = 0;
@@ -1180,12 +1185,43 @@ __device__ __forceinline__ uint64_t field_value(int cls, int f, const EvCtx& c) 
   }
 }
 
+// The value that follows a field's literal.  T_MD (CPU-side activities only) formats the typed metadata
+// entries of the op (JsonTypedMetadataVisitor, libkineto/include/TypedMetadataJson.h:72-158).
 template <class S>
-__device__ __forceinline__ void run_fields(S& s, const Dev& d, int cls, int base, int nf, const EvCtx& c, uint64_t present,
+__device__ __forceinline__ void put_value(S& s, const Dev& d, int type, uint64_t v, unsigned long long* name_bytes) {
+  switch (type) {
+    case T_NONE: break;
+    case T_U64: put_dec(s, v); break;
+    case T_I64: put_sdec(s, (int64_t)v); break;
+    case T_TS: put_ts2(s, (int64_t)v); break;
+    case T_DBL: put_dbl(s, __longlong_as_double((long long)v)); break;
+    case T_NAME: put_name(s, d, (uint32_t)v, name_bytes); break;
+    case T_CSTR: { const FieldDesc cs = g_fields.f[CSTR_BASE + (uint32_t)v]; s.words(g_fields.w + cs.off, cs.len); break; }
+    default: {  // T_MD
+      const uint32_t m0 = d.op_mdoff[v], m1 = d.op_mdoff[v + 1];
+      for (uint32_t e = m0; e < m1; e++) {
+        const MdEntry md = d.md[e];
+        if (e > m0) s.put(0x202Cu, 2);  // ", "
+        put_char(s, '"'); put_mdstr(s, d, md.key); s.put(0x203A22u, 3);  // "\": "
+        switch (md.type) {
+          case 0: put_sdec(s, (int64_t)md.value); break;
+          case 1: put_dec(s, md.value); break;
+          case 2: put_dbl(s, __longlong_as_double((long long)md.value)); break;
+          case 3: if (md.value) s.put4(0x65757274u); else { s.put4(0x736C6166u); put_char(s, 'e'); } break;  // true / false
+          case 4: put_char(s, '"'); put_mdstr(s, d, (uint32_t)md.value); put_char(s, '"'); break;
+          default: put_mdstr(s, d, (uint32_t)md.value); break;
+        }
+      }
+      break;
+    }
+  }
+}
+
+// Emit pass: walks the set bits of `present`.  Descriptor and value of the NEXT field are fetched before
+// the current one is formatted, so their load latency hides behind the formatting work.
+template <class S>
+__device__ __forceinline__ void run_fields(S& s, const Dev& d, int cls, int base, const EvCtx& c, uint64_t present,
                                            unsigned long long* name_bytes) {
-  // Walks the set bits of `present`.  Descriptor and value of the NEXT field are fetched before the
-  // current one is formatted, so their load latency hides behind the formatting work.
-  (void)nf;
   if (!present) return;
   int f = __ffsll((long long)present) - 1;
   present &= present - 1;
@@ -1203,35 +1239,32 @@ __device__ __forceinline__ void run_fields(S& s, const Dev& d, int cls, int base
       vn = fdn.type != T_NONE ? field_value(cls, fn, c) : 0ull;
     }
     s.words(g_fields.w + fd.off, fd.len);
-    switch (fd.type) {
-      case T_NONE: break;
-      case T_U64: put_dec(s, v); break;
-      case T_I64: put_sdec(s, (int64_t)v); break;
-      case T_TS: put_ts2(s, (int64_t)v); break;
-      case T_DBL: put_dbl(s, __longlong_as_double((long long)v)); break;
-      case T_NAME: put_name(s, d, (uint32_t)v, name_bytes); break;
-      case T_CSTR: { const FieldDesc cs = g_fields.f[CSTR_BASE + (uint32_t)v]; s.words(g_fields.w + cs.off, cs.len); break; }
-      default: {  // T_MD
-        const uint32_t m0 = d.op_mdoff[v], m1 = d.op_mdoff[v + 1];
-        for (uint32_t e = m0; e < m1; e++) {
-          const MdEntry md = d.md[e];
-          if (e > m0) s.put(0x202Cu, 2);  // ", "
-          put_char(s, '"'); put_mdstr(s, d, md.key); s.put(0x203A22u, 3);  // "\": "
-          switch (md.type) {
-            case 0: put_sdec(s, (int64_t)md.value); break;
-            case 1: put_dec(s, md.value); break;
-            case 2: put_dbl(s, __longlong_as_double((long long)md.value)); break;
-            case 3: if (md.value) s.put4(0x65757274u); else { s.put4(0x736C6166u); put_char(s, 'e'); } break;  // true / false
-            case 4: put_char(s, '"'); put_mdstr(s, d, (uint32_t)md.value); put_char(s, '"'); break;
-            default: put_mdstr(s, d, (uint32_t)md.value); break;
-          }
-        }
-        break;
-      }
-    }
+    put_value(s, d, fd.type, v, name_bytes);
     if (!more) break;
     f = fn; fd = fdn; v = vn;
   }
+}
+
+// Size pass: the same fields as straight-line code.  Field types and literal lengths are compile-time
+// constants here, so each present field costs its value's digit count and one addition.
+template <int I> struct FieldInfo {
+  static constexpr int type = kAllFields[I].type;
+  static constexpr uint32_t len = (uint32_t)c_strlen(kAllFields[I].lit);
+};
+template <int CLS, int BASE, int F, int NF, class S>
+__device__ __forceinline__ void count_fields(S& s, const Dev& d, const EvCtx& c, uint64_t present, unsigned long long* name_bytes) {
+  if constexpr (F < NF) {
+    if ((present >> F) & 1ull) {
+      s.n += FieldInfo<BASE + F>::len;
+      if constexpr (FieldInfo<BASE + F>::type != T_NONE) put_value(s, d, FieldInfo<BASE + F>::type, field_value(CLS, F, c), name_bytes);
+    }
+    count_fields<CLS, BASE, F + 1, NF>(s, d, c, present, name_bytes);
+  }
+}
+template <int CLS, int BASE, int NF, class S>
+__device__ __forceinline__ void do_fields(S& s, const Dev& d, const EvCtx& c, uint64_t present, unsigned long long* name_bytes) {
+  if constexpr (S::kCounting) count_fields<CLS, BASE, 0, NF>(s, d, c, present, name_bytes);
+  else run_fields(s, d, CLS, BASE, c, present, name_bytes);
 }
 
 constexpr int kEventThreads = 128;
@@ -1239,38 +1272,61 @@ static_assert(kEventThreads == kCtxStride, "scratch column stride");
 
 template <class S>
 __device__ __forceinline__ void format_event(S& s, const Dev& d, int cls, const uint8_t* r, uint64_t j, Tally& t, uint32_t* filt,
-                                             uint32_t* scratch) {
+                                             uint32_t* scratch, int32_t* ext) {
   EvCtx c;
   c.r = r; c.j = j; c.sm = scratch;
   uint64_t present = 0;
-  int base = 0, nf = 0;
+  unsigned long long* nb = &t.name_bytes;
+  if (S::kCounting) {
+    // straight-line field code per class
+    switch (cls) {
+      case C_API: if (gather_api(d, r, c, &present, t, filt, true, 0)) { *ext = c.ext; do_fields<C_API, API_BASE, A_COUNT>(s, d, c, present, nb); } break;
+      case C_KERNEL: if (gather_kernel(d, r, c, &present, t, filt, true, 0)) { *ext = c.ext; do_fields<C_KERNEL, KERNEL_BASE, K_COUNT>(s, d, c, present, nb); } break;
+      case C_MEMCPY: if (gather_mem<C_MEMCPY>(d, r, c, &present, t, filt, true, 0)) { *ext = c.ext; do_fields<C_MEMCPY, MEM_BASE, M_COUNT>(s, d, c, present, nb); } break;
+      case C_MEMCPY2: if (gather_mem<C_MEMCPY2>(d, r, c, &present, t, filt, true, 0)) { *ext = c.ext; do_fields<C_MEMCPY2, MEM_BASE, M_COUNT>(s, d, c, present, nb); } break;
+      case C_MEMSET: if (gather_mem<C_MEMSET>(d, r, c, &present, t, filt, true, 0)) { *ext = c.ext; do_fields<C_MEMSET, MEM_BASE, M_COUNT>(s, d, c, present, nb); } break;
+      default: if (gather_op(d, j, c, &present, t)) do_fields<C_OP, OP_BASE, O_COUNT>(s, d, c, present, nb); break;
+    }
+    return;
+  }
+  int base = 0;
   bool ok;
   switch (cls) {
-    case C_API: ok = gather_api(d, r, c, &present, t, filt); base = API_BASE; nf = A_COUNT; break;
-    case C_KERNEL: ok = gather_kernel(d, r, c, &present, t, filt, S::kCounting); base = KERNEL_BASE; nf = K_COUNT; break;
-    case C_MEMCPY: ok = gather_mem<C_MEMCPY>(d, r, c, &present, t, filt, S::kCounting); base = MEM_BASE; nf = M_COUNT; break;
-    case C_MEMCPY2: ok = gather_mem<C_MEMCPY2>(d, r, c, &present, t, filt, S::kCounting); base = MEM_BASE; nf = M_COUNT; break;
-    case C_MEMSET: ok = gather_mem<C_MEMSET>(d, r, c, &present, t, filt, S::kCounting); base = MEM_BASE; nf = M_COUNT; break;
-    default: ok = gather_op(d, j, c, &present, t); base = OP_BASE; nf = O_COUNT; break;
+    case C_API: ok = gather_api(d, r, c, &present, t, filt, false, *ext); base = API_BASE; break;
+    case C_KERNEL: ok = gather_kernel(d, r, c, &present, t, filt, false, *ext); base = KERNEL_BASE; break;
+    case C_MEMCPY: ok = gather_mem<C_MEMCPY>(d, r, c, &present, t, filt, false, *ext); base = MEM_BASE; break;
+    case C_MEMCPY2: ok = gather_mem<C_MEMCPY2>(d, r, c, &present, t, filt, false, *ext); base = MEM_BASE; break;
+    case C_MEMSET: ok = gather_mem<C_MEMSET>(d, r, c, &present, t, filt, false, *ext); base = MEM_BASE; break;
+    default: ok = gather_op(d, j, c, &present, t); base = OP_BASE; break;
   }
-  if (ok) run_fields(s, d, cls, base, nf, c, present, &t.name_bytes);
+  if (ok) run_fields(s, d, cls, base, c, present, nb);
 }
+
+// 8-byte units of a record of each class (C_API .. C_MEMSET)
+__device__ __forceinline__ uint32_t class_units(int cls) {
+  return cls == C_KERNEL ? 26u : cls == C_MEMCPY2 ? 12u : cls == C_API ? 5u : 11u;
+}
+constexpr int kRecStride = 27;  // 8-byte units per staged record: 26 for the longest record, odd so that 64-bit reads of the
+                                // 32 lanes fall in distinct banks
 
 // One thread per work item.  Work items are class-sorted (each class padded to a multiple of 32),
 // so a warp formats events of one shape.  WRITE = false: store the byte length; WRITE = true: write
-// the bytes at ev_off[event].
+// the bytes at ev_off[event].  The emit pass first copies the 32 records of a warp into shared memory
+// with coalesced loads (lane = 8-byte unit of a record), so that the field loop reads record fields
+// at shared-memory latency instead of one cache line per lane.
 template <bool WRITE>
 __global__ void __launch_bounds__(kEventThreads, WRITE ? 6 : 8) k_events(Dev d) {
   __shared__ uint32_t s_ctx[X_COUNT * kEventThreads];
+  __shared__ uint64_t s_rec[WRITE ? kEventThreads * kRecStride : 1];
   __shared__ unsigned long long s_cnt[8];
   if (threadIdx.x < 8) s_cnt[threadIdx.x] = 0;
   __syncthreads();
   const uint64_t i = (uint64_t)blockIdx.x * kEventThreads + threadIdx.x;
   Tally t; t.x = 0; t.flow = 0; t.name_bytes = 0; t.ev = 0;
   uint32_t filt = 0;
+  int cls = -1;
+  uint64_t j = 0;
   if (i < d.n_work) {
-    int cls;
-    uint64_t j;
     if (i >= d.ops_begin) { cls = C_OP; j = i - d.ops_begin; }
     else {
       cls = 0;
@@ -1280,27 +1336,55 @@ __global__ void __launch_bounds__(kEventThreads, WRITE ? 6 : 8) k_events(Dev d) 
       if (j >= d.cls_count[cls]) cls = -1;  // padding
     }
     if (cls == C_OP && j >= d.n_ops) cls = -1;
-    if (cls >= 0) {
-      const uint64_t ev = cls == C_OP ? j : d.work_ev[i];
-      t.ev = ev;
-      const uint8_t* r = cls == C_OP ? nullptr : d.cupti + (uint64_t)d.work_slot[i] * 8;
-      if (!WRITE) {
-        CountSink2 s;
-        format_event(s, d, cls, r, j, t, &filt, &s_ctx[threadIdx.x]);
-        d.ev_size[ev] = filt ? 0u : s.n;
-      } else {
-        const uint32_t size = d.ev_size[ev];
-        if (size) {
-          const uint64_t off = d.ev_off[ev];
-          if (off + size > d.out_cap) { atomicAdd(&d.counters->device_check, 1ull); }
-          else {
-            GlobalSink s;
-            s.init(d.out + off);
-            format_event(s, d, cls, r, j, t, &filt, &s_ctx[threadIdx.x]);
-            s.finish();
-          }
-        }
+  }
+  uint64_t ev = 0;
+  const uint8_t* r = nullptr;
+  uint32_t size = 0;
+  uint64_t off = 0;
+  int32_t ext = 0;
+  if (cls >= 0) {
+    ev = cls == C_OP ? j : d.work_ev[i];
+    t.ev = ev;
+    if (cls != C_OP) r = d.cupti + (uint64_t)d.work_slot[i] * 8;
+    if (WRITE) {
+      size = d.ev_size[ev];
+      if (size) {
+        off = d.ev_off[ev];
+        if (cls != C_OP) ext = d.ev_ext[ev];
+        if (off + size > d.out_cap) { atomicAdd(&d.counters->device_check, 1ull); size = 0; }
       }
+      if (!size) r = nullptr;
+    }
+  }
+  if (WRITE) {
+    // stage this warp's records: every lane's class is the warp's class (or none)
+    const uint32_t lane = threadIdx.x & 31u, wbase = threadIdx.x & ~31u;
+    const int cls0 = __shfl_sync(0xffffffffu, cls, 0);
+    if (cls0 >= 0 && cls0 != C_OP) {
+      const uint32_t nu = class_units(cls0), rpi = 32u / nu;
+      const uint32_t sub = lane / nu, unit = lane - sub * nu;
+      const unsigned long long mine = (unsigned long long)reinterpret_cast<uintptr_t>(r);
+#pragma unroll 4
+      for (uint32_t k = 0; k < 32u; k += rpi) {
+        const uint32_t rec = k + sub;
+        const uint64_t* src = reinterpret_cast<const uint64_t*>((uintptr_t)__shfl_sync(0xffffffffu, mine, rec & 31u));
+        if (sub < rpi && rec < 32u && src != nullptr) s_rec[(wbase + rec) * kRecStride + unit] = src[unit];
+      }
+      __syncwarp();
+      r = reinterpret_cast<const uint8_t*>(&s_rec[threadIdx.x * kRecStride]);
+    }
+  }
+  if (cls >= 0) {
+    if (!WRITE) {
+      CountSink2 s;
+      format_event(s, d, cls, r, j, t, &filt, &s_ctx[threadIdx.x], &ext);
+      d.ev_size[ev] = filt ? 0u : s.n;
+      if (cls != C_OP) d.ev_ext[ev] = ext;
+    } else if (size) {
+      GlobalSink s;
+      s.init(d.out + off);
+      format_event(s, d, cls, r, j, t, &filt, &s_ctx[threadIdx.x], &ext);
+      s.finish();
     }
   }
   if (!WRITE) {  // counters are tallied once, in the size pass
@@ -1383,11 +1467,11 @@ __global__ void __launch_bounds__(kEventThreads) k_annotations(Dev d, const Span
   c.ts_rel = rel_ts(d, r.start - 1); c.dur = dur + 2; c.ext = r.op_id;
   uint64_t p = (1ull << N_COUNT) - 1ull;
   if (r.op_id == 0) p &= ~((1ull << N_EXT) | (1ull << N_ARGS_CLOSE));
-  if (!WRITE) { CountSink2 s; run_fields(s, d, C_ANN, ANN_BASE, N_COUNT, c, p, &nb); sizes[i] = s.n; }
+  if (!WRITE) { CountSink2 s; count_fields<C_ANN, ANN_BASE, 0, N_COUNT>(s, d, c, p, &nb); sizes[i] = s.n; }
   else {
     GlobalSink s;
     s.init(d.out + out_base + offs[i]);
-    run_fields(s, d, C_ANN, ANN_BASE, N_COUNT, c, p, &nb);
+    run_fields(s, d, C_ANN, ANN_BASE, c, p, &nb);
     s.finish();
   }
 }
