@@ -627,7 +627,7 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
     if (total_bytes) { k_events<true><<<ev_blocks, kEventThreads, 0, s>>>(d); c->launches++; }
     if (ann_bytes) {
       k_annotations<true><<<(n_spans + kEventThreads - 1) / kEventThreads, kEventThreads, 0, s>>>(
-          d, c->span_out.as<SpanRec>(), n_spans, nullptr, c->ann_off.as<uint64_t>(), total_bytes);
+          d, c->span_out.as<SpanRec>(), n_spans, c->ann_size.as<uint32_t>(), c->ann_off.as<uint64_t>(), total_bytes);
       c->launches++;
     }
     K2J_CUDA(c, cudaGetLastError());

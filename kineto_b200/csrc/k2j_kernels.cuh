@@ -508,103 +508,118 @@ __global__ void __launch_bounds__(kScanThreads) k_scan_apply(const uint32_t* in,
   for (int k = 0; k < kScanItems; k++) { const uint64_t i = base + k; if (i < n) dst[i] = ex; ex += v[k]; }
 }
 
-// ---- output sink: 16-byte vector stores straight to the final position ----------------------------------
-// Bytes are gathered in a 64-bit shift register; a completed 8-byte word is either parked in a register
-// (first half of a 16-byte block) or leaves together with the parked one as one 16-byte store (second
-// half).  Only the first and last 16-byte block of an event are written with narrower stores, so
-// neighbouring events never overwrite each other.  No shared or local memory is involved.
-__device__ __noinline__ void store_partial(uint8_t* b, uint64_t w0, uint64_t w1, int from, int to) {
-  for (int i = from; i < to; i++) {
-    const uint64_t w = i < 8 ? w0 : w1;
-    b[i] = (uint8_t)(w >> ((i & 7) * 8));
-  }
-}
+// ---- output sink: 32-byte stores straight to the final position, no branches ---------------------------
+// Bytes are gathered in a 64-bit shift register.  A completed 8-byte word that belongs to a 32-byte
+// block lying wholly inside the event is parked in shared memory; the block's fourth word leaves
+// together with the three parked ones as one 256-bit store (a full DRAM sector, so the L2 never has
+// to fetch the rest of a sector).  Words of the event's first and last (partial) block leave as 8-byte
+// stores.  Everything is predicated: lanes whose word is not complete simply skip the store.
+// The two 8-byte words an event may share with its neighbours are written without knowing the
+// neighbour's bytes: every event begins with "\n  {\n   " and ends with "\n  },", so the neighbour's (at
+// most three) bytes inside a shared 4-byte half are known constants, and a half that belongs wholly to
+// the neighbour is not touched.  Both owners write a shared half with the same bytes.
+constexpr uint64_t kEventHead8 = 0x2020200A7B20200Aull;  // "\n  {\n   "  first 8 bytes of every event
+constexpr uint64_t kEventTail8 = 0x2C7D20200A000000ull;  // "\n  },"      last 5 bytes of every event, in the top bytes
+constexpr uint32_t kMinEventBytes = 16;
 
 struct GlobalSink {
   static constexpr bool kCounting = false;
-  uint64_t lo, w0; int sh, k, head; uint4* p;
-  __device__ __forceinline__ void init(uint8_t* dst) {
-    const uintptr_t a = reinterpret_cast<uintptr_t>(dst);
-    const int phase = (int)(a & 15);
-    p = reinterpret_cast<uint4*>(a - phase);
-    k = phase >> 3; sh = 8 * (phase & 7); lo = 0; w0 = 0; head = phase;
+  uint64_t lo; uint32_t sh;
+  uint32_t wo;            // byte offset (from base) of the 8-byte word being filled
+  uint32_t c8, lim8;      // words stored singly: 0 <= wo - c8 < lim8 and outside the block range
+  uint32_t c32, lim32;    // words of whole blocks: 0 <= wo - c32 < lim32
+  uint8_t* base;          // 32-byte aligned
+  uint64_t* park;         // this thread's column of the parking area: word k at park[k * kParkStride]
+  static constexpr int kParkStride = 128;  // = threads per block of the kernels that use the sink
+  __device__ __forceinline__ void init(uint8_t* dst, uint32_t size, uint64_t* park_column) {
+    const uint32_t phase32 = (uint32_t)(reinterpret_cast<uintptr_t>(dst) & 31u), phase = phase32 & 7u;
+    base = dst - phase32; sh = 8u * phase; lo = 0; park = park_column;
+    wo = phase32 & ~7u;
+    const uint32_t end = phase32 + size;
+    c8 = wo + 8u; lim8 = (end & ~7u) - c8;           // strictly between the first word and the word holding the end
+    c32 = phase32 ? 32u : 0u;
+    const uint32_t last_blk = end & ~31u;
+    lim32 = last_blk > c32 ? last_blk - c32 : 0u;
+    const uint64_t w = ((kEventTail8 >> 1) >> (63u - sh)) | (kEventHead8 << sh);
+    if (phase < 4u) *reinterpret_cast<uint64_t*>(base + wo) = w;
+    else *reinterpret_cast<uint32_t*>(base + wo + 4) = (uint32_t)(w >> 32);
   }
-  __device__ __forceinline__ void word(uint64_t x) {
-    if (k) {
-      if (head) { store_partial(reinterpret_cast<uint8_t*>(p), w0, x, head, 16); head = 0; }
-      else *p = make_uint4((uint32_t)w0, (uint32_t)(w0 >> 32), (uint32_t)x, (uint32_t)(x >> 32));
-      p++; k = 0;
-    } else { w0 = x; k = 1; }
+  // a completed word `t` at offset `wo`; `on`: this lane really has one
+  __device__ __forceinline__ void word_out(uint64_t t, bool on) {
+    const bool blk = on && (wo - c32) < lim32;
+    const uint32_t k = (wo >> 3) & 3u;
+    if (blk && k != 3u) park[k * kParkStride] = t;
+    if (blk && k == 3u) {
+      const uint64_t w0 = park[0], w1 = park[kParkStride], w2 = park[2 * kParkStride];
+      asm volatile("st.global.v4.b64 [%0], {%1, %2, %3, %4};" ::"l"(base + (wo & ~31u)), "l"(w0), "l"(w1), "l"(w2), "l"(t) : "memory");
+    }
+    if (on && !blk && (wo - c8) < lim8) *reinterpret_cast<uint64_t*>(base + wo) = t;
   }
-  // append 8 bytes
-  __device__ __forceinline__ void put8w(uint64_t w) {
-    word(lo | (w << sh));
-    lo = sh ? (w >> (64 - sh)) : 0ull;
+  __device__ __forceinline__ void put8w(uint64_t w) {  // append 8 bytes
+    word_out(lo | (w << sh), true);
+    lo = (w >> 1) >> (63u - sh);
+    wo += 8u;
   }
-  // append the low `len` (1..8) bytes of w; bytes above len must be zero
-  __device__ __forceinline__ void put64(uint64_t w, int len) {
+  // append the low `len` (0..8) bytes of w; bytes above len must be zero
+  __device__ __forceinline__ void put64(uint64_t w, uint32_t len) {
     const uint64_t t = lo | (w << sh);
-    const int s2 = sh + 8 * len;
-    if (s2 >= 64) { word(t); lo = sh ? (w >> (64 - sh)) : 0ull; sh = s2 - 64; }
-    else { lo = t; sh = s2; }
+    const uint32_t s2 = sh + 8u * len;
+    const bool full = s2 >= 64u;
+    word_out(t, full);
+    lo = full ? ((w >> 1) >> (63u - sh)) : t;
+    wo += full ? 8u : 0u;
+    sh = s2 & 63u;
   }
-  __device__ __forceinline__ void put(uint32_t w, int len) { put64((uint64_t)w, len); }
-  __device__ __forceinline__ void put4(uint32_t w) { put64((uint64_t)w, 4); }
+  __device__ __forceinline__ void put(uint32_t w, int len) { put64((uint64_t)w, (uint32_t)len); }
+  __device__ __forceinline__ void put4(uint32_t w) { put64((uint64_t)w, 4u); }
   __device__ __forceinline__ void skip(uint32_t) {}
   template <int N> __device__ __forceinline__ void lit(const Lit<N>& l) {
 #pragma unroll
     for (int i = 0; i < N / 4; i++) put4(l.w[i]);
     if (N % 4) put(l.w[N / 4], N % 4);
   }
-  __device__ __forceinline__ void store16(uint64_t a, uint64_t b) {
-    if (head) { store_partial(reinterpret_cast<uint8_t*>(p), a, b, head, 16); head = 0; }
-    else *p = make_uint4((uint32_t)a, (uint32_t)(a >> 32), (uint32_t)b, (uint32_t)(b >> 32));
-    p++;
-  }
-  // `len` bytes from an 8-byte aligned word array (bytes past len in the last word are ignored).
-  // The byte phase does not change inside the run, so after aligning to a 16-byte block the body
-  // handles two words per round with no per-word branching.
+  // `len` bytes from an 8-byte aligned word array; reads one word past the last one it needs
   __device__ __forceinline__ void words(const uint64_t* w, uint32_t len) {
     const uint32_t nw = len >> 3;
-    uint32_t i = 0;
-    if (k && nw) { put8w(w[0]); i = 1; }
-    const int rs = 63 - sh;  // (x >> 1) >> rs == x >> (64 - sh), and 0 when sh == 0
-    for (; i + 2 <= nw; i += 2) {
-      const uint64_t a = w[i], b = w[i + 1];
-      const uint64_t t0 = lo | (a << sh);
-      const uint64_t t1 = ((a >> 1) >> rs) | (b << sh);
-      lo = (b >> 1) >> rs;
-      store16(t0, t1);
-    }
-    if (i < nw) put8w(w[i]);
+    uint64_t nxt = w[0];
+    for (uint32_t i = 0; i < nw; i++) { const uint64_t cur = nxt; nxt = w[i + 1]; put8w(cur); }
     const uint32_t rem = len & 7u;
-    if (rem) put64(w[nw] & (~0ull >> (8 * (8 - rem))), (int)rem);
+    if (rem) put64(nxt & (~0ull >> (8u * (8u - rem))), rem);
   }
-  __device__ __forceinline__ void finish() {
-    const int have = k * 8 + (sh >> 3);
-    if (have > head) store_partial(reinterpret_cast<uint8_t*>(p), k ? w0 : lo, lo, head, have);
+  // Returns false if the byte count differs from the size the event was given.
+  __device__ __forceinline__ bool finish(const uint8_t* dst, uint32_t size) {
+    const uint32_t e = sh >> 3;
+    if (e) {
+      const uint64_t t = lo | (0x20200Aull << sh);  // the next event begins "\n  "
+      if (e > 4u) *reinterpret_cast<uint64_t*>(base + wo) = t;
+      else *reinterpret_cast<uint32_t*>(base + wo) = (uint32_t)t;
+    }
+    return wo + e == (uint32_t)(reinterpret_cast<uintptr_t>(dst) & 31u) + size;
   }
 };
 struct CountSink2 : CountSink {
   __device__ __forceinline__ void put4(uint32_t) { n += 4; }
-  __device__ __forceinline__ void put64(uint64_t, int len) { n += (uint32_t)len; }
+  __device__ __forceinline__ void put64(uint64_t, uint32_t len) { n += len; }
   __device__ __forceinline__ void words(const uint64_t*, uint32_t len) { n += len; }
 };
 
 // ---- event programs ------------------------------------------------------------------------------------
 // An event is a fixed sequence of fields, each a literal followed by a value.  The sequence of a
-// record class is data (a table in constant memory), so all classes share one small formatting loop:
-// the emit kernel stays a few tens of KiB of code, and the lanes of a warp, which format events of one
-// class, run the loop in lock step.  Per event the class-specific code only gathers the values.
+// record class is data (a table in constant memory), so all classes share one small formatting loop
+// and the lanes of a warp, which format events of one class, run it in lock step.  A field's value
+// is read from the thread's area in shared memory: the staged record itself, with the values that
+// are computed rather than stored (converted times, the linked op, occupancy ...) written by the
+// class's gather step into parts of the record that no field reads.
 enum : uint8_t { T_NONE = 0, T_U64, T_I64, T_TS, T_DBL, T_NAME, T_CSTR, T_MD /* the metadata entries of a CPU-side activity */ };
-struct FieldSrc { const char* lit; uint8_t type; };
-struct FieldDesc { uint16_t off, len; uint8_t type, pad; };
+enum : uint8_t { VK_U32 = 0, VK_I32 /* sign-extended */, VK_64 };
+struct FieldSrc { const char* lit; uint8_t type; uint8_t vk; uint16_t voff; };
+struct FieldDesc { uint16_t off, len; uint8_t type, vk; uint16_t voff; };
 
 constexpr int c_strlen(const char* s) { int n = 0; while (s[n]) n++; return n; }
 template <int NF> constexpr int prog_words(const FieldSrc (&src)[NF]) {  // 64-bit words
   int w = 0;
   for (int f = 0; f < NF; f++) w += (c_strlen(src[f].lit) + 7) / 8;
-  return w > 0 ? w : 1;
+  return w + 1;  // one spare word: a copy reads one word past the literal
 }
 template <int NF, int NW> struct Prog {
   FieldDesc f[NF];
@@ -615,7 +630,7 @@ template <int NF, int NW> constexpr Prog<NF, NW> make_prog(const FieldSrc (&src)
   int pos = 0;
   for (int f = 0; f < NF; f++) {
     const int n = c_strlen(src[f].lit);
-    p.f[f].off = (uint16_t)pos; p.f[f].len = (uint16_t)n; p.f[f].type = src[f].type; p.f[f].pad = 0;
+    p.f[f].off = (uint16_t)pos; p.f[f].len = (uint16_t)n; p.f[f].type = src[f].type; p.f[f].vk = src[f].vk; p.f[f].voff = src[f].voff;
     for (int i = 0; i < n; i++) p.w[pos + i / 8] |= (uint64_t)(unsigned char)src[f].lit[i] << (8 * (i % 8));
     pos += (n + 7) / 8;
   }
@@ -624,74 +639,102 @@ template <int NF, int NW> constexpr Prog<NF, NW> make_prog(const FieldSrc (&src)
 #define XHEAD(cat) "\n  {\n    \"ph\": \"X\",\n    \"cat\": \"" cat "\",\n    \"name\": \""
 #define FLOW_TAIL "\n  },"
 
-// -- small constant strings: activity type names (libkineto/include/ActivityType.h:80-112), memcpy and
-// memory kinds (libkineto/src/cupti_strings.cpp:15-66), limiting factors (CuptiActivity.h:476-497) --
-// -- runtime / driver API record --
+// Byte offsets inside a thread's area.  R_: a field of the record as CUPTI wrote it.  S_: a computed
+// value, stored over record bytes that nothing reads (or past the record's end).
+// -- runtime / driver API record (40 bytes) --
+enum : int { AR_CBID = 4, AS_TS = 8, AS_DUR = 16, AS_PID = 24, AS_TID = 28, AR_CORR = 32, AS_EXT = 36, AS_NAME = 40 };
 enum : int { A_HEAD_RT, A_HEAD_DR, A_NAME, A_INVALID, A_PID, A_TID, A_TS, A_DUR, A_ARGS, A_EXT, A_EXTC, A_CBID, A_CORR, A_CLOSE,
              A_FLOW_S, A_FLOW_F, A_FPID, A_FTID, A_FTS, A_FCAT, A_FBP, A_FEND, A_COUNT };
 #define K2J_API_FIELDS \
-    {XHEAD("cuda_runtime"), T_NONE}, {XHEAD("cuda_driver"), T_NONE}, {"", T_NAME}, {"INVALID", T_NONE}, \
-    {"\",\n    \"pid\": ", T_I64}, {",\n    \"tid\": ", T_I64}, {",\n    \"ts\": ", T_TS}, {",\n    \"dur\": ", T_TS}, \
-    {"\n    ,\n    \"args\": {\n      ", T_NONE}, {"\"External id\": ", T_I64}, {",", T_NONE}, \
-    {"\"cbid\": ", T_U64}, {", \"correlation\": ", T_U64}, {"\n    }\n  },", T_NONE}, \
-    {"\n  {\n    \"ph\": \"s\",\n    \"id\": ", T_U64}, {"\n  {\n    \"ph\": \"f\",\n    \"id\": ", T_U64}, \
-    {",\n    \"pid\": ", T_I64}, {",\n    \"tid\": ", T_I64}, {",\n    \"ts\": ", T_TS}, \
+    {XHEAD("cuda_runtime"), T_NONE}, {XHEAD("cuda_driver"), T_NONE}, {"", T_NAME, VK_U32, AS_NAME}, {"INVALID", T_NONE}, \
+    {"\",\n    \"pid\": ", T_I64, VK_I32, AS_PID}, {",\n    \"tid\": ", T_I64, VK_U32, AS_TID}, {",\n    \"ts\": ", T_TS, VK_64, AS_TS}, \
+    {",\n    \"dur\": ", T_TS, VK_64, AS_DUR}, \
+    {"\n    ,\n    \"args\": {\n      ", T_NONE}, {"\"External id\": ", T_I64, VK_I32, AS_EXT}, {",", T_NONE}, \
+    {"\"cbid\": ", T_U64, VK_U32, AR_CBID}, {", \"correlation\": ", T_U64, VK_U32, AR_CORR}, {"\n    }\n  },", T_NONE}, \
+    {"\n  {\n    \"ph\": \"s\",\n    \"id\": ", T_U64, VK_U32, AR_CORR}, {"\n  {\n    \"ph\": \"f\",\n    \"id\": ", T_U64, VK_U32, AR_CORR}, \
+    {",\n    \"pid\": ", T_I64, VK_I32, AS_PID}, {",\n    \"tid\": ", T_I64, VK_U32, AS_TID}, {",\n    \"ts\": ", T_TS, VK_64, AS_TS}, \
     {",\n    \"cat\": \"ac2g\",\n    \"name\": \"ac2g\"\n    ", T_NONE}, {", \"bp\": \"e\"", T_NONE}, {FLOW_TAIL, T_NONE}
 
-// -- kernel record (GpuActivity<Kernel>, libkineto/src/CuptiActivity.h:499-576) --
+// -- kernel record (GpuActivity<Kernel>, libkineto/src/CuptiActivity.h:499-576; 208 bytes) --
+enum : int { KS_REGS = 8, KS_SMEM = 12, KS_TS = 16, KS_DUR = 24, KS_BPS = 32, KR_DEV = 40, KR_CTX = 44, KR_STREAM = 48, KR_GRID = 52,
+             KR_BLOCK = 64, KS_PCT = 84, KS_ACTIVE = 88, KR_CORR = 92, KS_EXT = 96, KS_LIMIT = 100, KR_NAME = 104, KS_LREGS = 108,
+             KS_LSMEM = 112, KS_LWARPS = 116, KR_QUEUED = 120, KS_WPS = 128, KS_LBLOCKS = 136, KS_LBARR = 140, KR_NODE = 144,
+             KS_AREGS = 152, KR_GRAPH = 156, KS_ASMEM = 160, KR_CHAN = 168, KR_CHTYPE = 172 };
 enum : int { K_HEAD, K_PID, K_TID, K_TS, K_DUR, K_ARGS, K_EXT, K_EXTC, K_QUEUED, K_DEV, K_CTX, K_STREAM, K_CORR, K_REGS, K_SMEM,
              K_BPS, K_WPS, K_GX, K_GY, K_GZ, K_BX, K_BY, K_BZ, K_OCCPCT, K_ACTIVE, K_LIMIT, K_LREGS, K_LSMEM, K_LWARPS, K_LBLOCKS,
              K_LBARR, K_AREGS, K_ASMEM, K_GRAPH, K_NODE, K_CHAN, K_CHTYPE, K_CLOSE, K_FLOW, K_FPID, K_FTID, K_FTS, K_FEND, K_COUNT };
 #define K2J_KERNEL_FIELDS \
-    {XHEAD("kernel"), T_NAME}, {"\",\n    \"pid\": ", T_U64}, {",\n    \"tid\": ", T_U64}, {",\n    \"ts\": ", T_TS}, \
-    {",\n    \"dur\": ", T_TS}, {"\n    ,\n    \"args\": {\n      ", T_NONE}, {"\"External id\": ", T_I64}, {",", T_NONE}, \
-    {"\"queued\": ", T_U64}, {", \"device\": ", T_U64}, {", \"context\": ", T_U64}, {", \"stream\": ", T_U64}, \
-    {", \"correlation\": ", T_U64}, {", \"registers per thread\": ", T_U64}, {", \"shared memory\": ", T_I64}, \
-    {", \"blocks per SM\": ", T_DBL}, {", \"warps per SM\": ", T_DBL}, {", \"grid\": [", T_I64}, {", ", T_I64}, {", ", T_I64}, \
-    {"], \"block\": [", T_I64}, {", ", T_I64}, {", ", T_I64}, {"], \"est. achieved occupancy %\": ", T_I64}, \
-    {", \"occupancy\": {\"activeBlocksPerMultiprocessor\": ", T_I64}, {", \"limitingFactors\": \"", T_CSTR}, \
-    {"\", \"blockLimitRegs\": ", T_I64}, {", \"blockLimitSharedMem\": ", T_I64}, {", \"blockLimitWarps\": ", T_I64}, \
-    {", \"blockLimitBlocks\": ", T_I64}, {", \"blockLimitBarriers\": ", T_I64}, {", \"allocatedRegistersPerBlock\": ", T_I64}, \
-    {", \"allocatedSharedMemPerBlock\": ", T_U64}, {"}, \"graph id\": ", T_U64}, {", \"graph node id\": ", T_U64}, \
-    {", \"channel\": ", T_U64}, {", \"channel_type\": ", T_U64}, {"\n    }\n  },", T_NONE}, \
-    {"\n  {\n    \"ph\": \"f\",\n    \"id\": ", T_U64}, {",\n    \"pid\": ", T_U64}, {",\n    \"tid\": ", T_U64}, {",\n    \"ts\": ", T_TS}, \
+    {XHEAD("kernel"), T_NAME, VK_U32, KR_NAME}, {"\",\n    \"pid\": ", T_U64, VK_U32, KR_DEV}, {",\n    \"tid\": ", T_U64, VK_U32, KR_STREAM}, \
+    {",\n    \"ts\": ", T_TS, VK_64, KS_TS}, {",\n    \"dur\": ", T_TS, VK_64, KS_DUR}, {"\n    ,\n    \"args\": {\n      ", T_NONE}, \
+    {"\"External id\": ", T_I64, VK_I32, KS_EXT}, {",", T_NONE}, \
+    {"\"queued\": ", T_U64, VK_64, KR_QUEUED}, {", \"device\": ", T_U64, VK_U32, KR_DEV}, {", \"context\": ", T_U64, VK_U32, KR_CTX}, \
+    {", \"stream\": ", T_U64, VK_U32, KR_STREAM}, {", \"correlation\": ", T_U64, VK_U32, KR_CORR}, \
+    {", \"registers per thread\": ", T_U64, VK_U32, KS_REGS}, {", \"shared memory\": ", T_I64, VK_I32, KS_SMEM}, \
+    {", \"blocks per SM\": ", T_DBL, VK_64, KS_BPS}, {", \"warps per SM\": ", T_DBL, VK_64, KS_WPS}, \
+    {", \"grid\": [", T_I64, VK_I32, KR_GRID}, {", ", T_I64, VK_I32, KR_GRID + 4}, {", ", T_I64, VK_I32, KR_GRID + 8}, \
+    {"], \"block\": [", T_I64, VK_I32, KR_BLOCK}, {", ", T_I64, VK_I32, KR_BLOCK + 4}, {", ", T_I64, VK_I32, KR_BLOCK + 8}, \
+    {"], \"est. achieved occupancy %\": ", T_I64, VK_I32, KS_PCT}, \
+    {", \"occupancy\": {\"activeBlocksPerMultiprocessor\": ", T_I64, VK_I32, KS_ACTIVE}, {", \"limitingFactors\": \"", T_CSTR, VK_U32, KS_LIMIT}, \
+    {"\", \"blockLimitRegs\": ", T_I64, VK_I32, KS_LREGS}, {", \"blockLimitSharedMem\": ", T_I64, VK_I32, KS_LSMEM}, \
+    {", \"blockLimitWarps\": ", T_I64, VK_I32, KS_LWARPS}, {", \"blockLimitBlocks\": ", T_I64, VK_I32, KS_LBLOCKS}, \
+    {", \"blockLimitBarriers\": ", T_I64, VK_I32, KS_LBARR}, {", \"allocatedRegistersPerBlock\": ", T_I64, VK_I32, KS_AREGS}, \
+    {", \"allocatedSharedMemPerBlock\": ", T_U64, VK_64, KS_ASMEM}, {"}, \"graph id\": ", T_U64, VK_U32, KR_GRAPH}, \
+    {", \"graph node id\": ", T_U64, VK_64, KR_NODE}, {", \"channel\": ", T_U64, VK_U32, KR_CHAN}, \
+    {", \"channel_type\": ", T_U64, VK_U32, KR_CHTYPE}, {"\n    }\n  },", T_NONE}, \
+    {"\n  {\n    \"ph\": \"f\",\n    \"id\": ", T_U64, VK_U32, KR_CORR}, {",\n    \"pid\": ", T_U64, VK_U32, KR_DEV}, \
+    {",\n    \"tid\": ", T_U64, VK_U32, KR_STREAM}, {",\n    \"ts\": ", T_TS, VK_64, KS_TS}, \
     {",\n    \"cat\": \"ac2g\",\n    \"name\": \"ac2g\"\n    , \"bp\": \"e\"\n  },", T_NONE}
 
-// -- memcpy / memcpy2 / memset records (libkineto/src/CuptiActivity.h:586-712) --
+// -- memcpy / memcpy2 / memset records (libkineto/src/CuptiActivity.h:586-712; 88 / 96 / 88 bytes).  The
+// fields whose position differs between the layouts are copied to common slots past the record. --
+enum : int { MR_BYTES = 8, MS_TS = 16, MS_DUR = 24, MR_DEV = 32, MR_CTX = 36, MR_STREAM = 40, MR_FROMDEV = 44, MR_FROMCTX = 48,
+             MR_TODEV = 52, MR_TOCTX = 56, MS_KIND0 = 100, MS_KIND1 = 104, MS_KIND2 = 108, MS_EXT = 112, MS_BW = 120, MS_GRAPH = 128,
+             MS_NODE = 136, MS_CHAN = 144, MS_CHTYPE = 148, MS_CORR = 152 };
 enum : int { M_CPY_KIND, M_CPY_SRC, M_CPY_DST, M_SET_KIND, M_PID, M_TID, M_TS, M_DUR, M_ARGS, M_EXT, M_EXTC, M_FROMDEV, M_INDEV,
              M_TODEV, M_FROMCTX, M_INCTX, M_TOCTX, M_DEV, M_CTX, M_STREAM, M_CORR, M_BYTES, M_BW, M_GRAPH, M_NODE, M_CHAN, M_CHTYPE,
              M_CLOSE, M_FLOW, M_FPID, M_FTID, M_FTS, M_FEND, M_COUNT };
 #define K2J_MEM_FIELDS \
-    {XHEAD("gpu_memcpy") "Memcpy ", T_CSTR}, {" (", T_CSTR}, {" -> ", T_CSTR}, {XHEAD("gpu_memset") "Memset (", T_CSTR}, \
-    {")\",\n    \"pid\": ", T_U64}, {",\n    \"tid\": ", T_U64}, {",\n    \"ts\": ", T_TS}, {",\n    \"dur\": ", T_TS}, \
-    {"\n    ,\n    \"args\": {\n      ", T_NONE}, {"\"External id\": ", T_I64}, {",", T_NONE}, \
-    {"\"fromDevice\": ", T_U64}, {", \"inDevice\": ", T_U64}, {", \"toDevice\": ", T_U64}, {", \"fromContext\": ", T_U64}, \
-    {", \"inContext\": ", T_U64}, {", \"toContext\": ", T_U64}, {"\"device\": ", T_U64}, {", \"context\": ", T_U64}, \
-    {", \"stream\": ", T_U64}, {", \"correlation\": ", T_U64}, {", \"bytes\": ", T_U64}, {", \"memory bandwidth (GB/s)\": ", T_DBL}, \
-    {", \"graph id\": ", T_U64}, {", \"graph node id\": ", T_U64}, {", \"channel\": ", T_U64}, {", \"channel_type\": ", T_U64}, \
+    {XHEAD("gpu_memcpy") "Memcpy ", T_CSTR, VK_U32, MS_KIND0}, {" (", T_CSTR, VK_U32, MS_KIND1}, {" -> ", T_CSTR, VK_U32, MS_KIND2}, \
+    {XHEAD("gpu_memset") "Memset (", T_CSTR, VK_U32, MS_KIND0}, \
+    {")\",\n    \"pid\": ", T_U64, VK_U32, MR_DEV}, {",\n    \"tid\": ", T_U64, VK_U32, MR_STREAM}, {",\n    \"ts\": ", T_TS, VK_64, MS_TS}, \
+    {",\n    \"dur\": ", T_TS, VK_64, MS_DUR}, \
+    {"\n    ,\n    \"args\": {\n      ", T_NONE}, {"\"External id\": ", T_I64, VK_I32, MS_EXT}, {",", T_NONE}, \
+    {"\"fromDevice\": ", T_U64, VK_U32, MR_FROMDEV}, {", \"inDevice\": ", T_U64, VK_U32, MR_DEV}, {", \"toDevice\": ", T_U64, VK_U32, MR_TODEV}, \
+    {", \"fromContext\": ", T_U64, VK_U32, MR_FROMCTX}, {", \"inContext\": ", T_U64, VK_U32, MR_CTX}, {", \"toContext\": ", T_U64, VK_U32, MR_TOCTX}, \
+    {"\"device\": ", T_U64, VK_U32, MR_DEV}, {", \"context\": ", T_U64, VK_U32, MR_CTX}, \
+    {", \"stream\": ", T_U64, VK_U32, MR_STREAM}, {", \"correlation\": ", T_U64, VK_U32, MS_CORR}, {", \"bytes\": ", T_U64, VK_64, MR_BYTES}, \
+    {", \"memory bandwidth (GB/s)\": ", T_DBL, VK_64, MS_BW}, \
+    {", \"graph id\": ", T_U64, VK_U32, MS_GRAPH}, {", \"graph node id\": ", T_U64, VK_64, MS_NODE}, {", \"channel\": ", T_U64, VK_U32, MS_CHAN}, \
+    {", \"channel_type\": ", T_U64, VK_U32, MS_CHTYPE}, \
     {"\n    }\n  },", T_NONE}, \
-    {"\n  {\n    \"ph\": \"f\",\n    \"id\": ", T_U64}, {",\n    \"pid\": ", T_U64}, {",\n    \"tid\": ", T_U64}, {",\n    \"ts\": ", T_TS}, \
+    {"\n  {\n    \"ph\": \"f\",\n    \"id\": ", T_U64, VK_U32, MS_CORR}, {",\n    \"pid\": ", T_U64, VK_U32, MR_DEV}, \
+    {",\n    \"tid\": ", T_U64, VK_U32, MR_STREAM}, {",\n    \"ts\": ", T_TS, VK_64, MS_TS}, \
     {",\n    \"cat\": \"ac2g\",\n    \"name\": \"ac2g\"\n    , \"bp\": \"e\"\n  },", T_NONE}
 
-// -- CPU-side activity: head, (metadata entries are formatted by ev_op itself), tail --
+// -- CPU-side activity (no record: every value is a slot): head, metadata entries, tail --
+enum : int { OS_CAT = 0, OS_NAME = 4, OS_PID = 8, OS_EXT = 12, OS_TID = 16, OS_TS = 24, OS_DUR = 32, OS_ROW = 40, OS_FLOW = 44, OS_FTS = 48 };
 enum : int { O_CAT, O_NAME, O_PID, O_TID, O_TS, O_DUR, O_PAD, O_ARGS, O_EXT, O_EXTC, O_MD,
              P_ARGS_CLOSE, P_CLOSE, P_FLOW_S, P_FLOW_F, P_FPID, P_FTID, P_FTS, P_FWDBWD, P_AC2G, P_FBP, P_FEND, O_COUNT };
 #define K2J_OPHEAD_FIELDS \
-    {"\n  {\n    \"ph\": \"X\",\n    \"cat\": \"", T_CSTR}, {"\",\n    \"name\": \"", T_NAME}, {"\",\n    \"pid\": ", T_I64}, \
-    {",\n    \"tid\": ", T_I64}, {",\n    \"ts\": ", T_TS}, {",\n    \"dur\": ", T_TS}, {"\n    ", T_NONE}, \
-    {",\n    \"args\": {\n      ", T_NONE}, {"\"External id\": ", T_I64}, {",", T_NONE}
+    {"\n  {\n    \"ph\": \"X\",\n    \"cat\": \"", T_CSTR, VK_U32, OS_CAT}, {"\",\n    \"name\": \"", T_NAME, VK_U32, OS_NAME}, \
+    {"\",\n    \"pid\": ", T_I64, VK_I32, OS_PID}, \
+    {",\n    \"tid\": ", T_I64, VK_64, OS_TID}, {",\n    \"ts\": ", T_TS, VK_64, OS_TS}, {",\n    \"dur\": ", T_TS, VK_64, OS_DUR}, {"\n    ", T_NONE}, \
+    {",\n    \"args\": {\n      ", T_NONE}, {"\"External id\": ", T_I64, VK_I32, OS_EXT}, {",", T_NONE}
 #define K2J_OPTAIL_FIELDS \
-    {"\n    }", T_NONE}, {"\n  },", T_NONE}, {"\n  {\n    \"ph\": \"s\",\n    \"id\": ", T_U64}, \
-    {"\n  {\n    \"ph\": \"f\",\n    \"id\": ", T_U64}, {",\n    \"pid\": ", T_I64}, {",\n    \"tid\": ", T_I64}, {",\n    \"ts\": ", T_TS}, \
+    {"\n    }", T_NONE}, {"\n  },", T_NONE}, {"\n  {\n    \"ph\": \"s\",\n    \"id\": ", T_U64, VK_U32, OS_FLOW}, \
+    {"\n  {\n    \"ph\": \"f\",\n    \"id\": ", T_U64, VK_U32, OS_FLOW}, {",\n    \"pid\": ", T_I64, VK_I32, OS_PID}, \
+    {",\n    \"tid\": ", T_I64, VK_64, OS_TID}, {",\n    \"ts\": ", T_TS, VK_64, OS_FTS}, \
     {",\n    \"cat\": \"fwdbwd\",\n    \"name\": \"fwdbwd\"\n    ", T_NONE}, {",\n    \"cat\": \"ac2g\",\n    \"name\": \"ac2g\"\n    ", T_NONE}, \
     {", \"bp\": \"e\"", T_NONE}, {FLOW_TAIL, T_NONE}
 
 // -- gpu_user_annotation span --
+enum : int { NS_NAME = 0, NS_PID = 4, NS_TID = 8, NS_EXT = 12, NS_TS = 16, NS_DUR = 24 };
 enum : int { N_HEAD, N_PID, N_TID, N_TS, N_DUR, N_PAD, N_EXT, N_ARGS_CLOSE, N_CLOSE, N_COUNT };
 #define K2J_ANN_FIELDS \
-    {XHEAD("gpu_user_annotation"), T_NAME}, {"\",\n    \"pid\": ", T_U64}, {",\n    \"tid\": ", T_U64}, {",\n    \"ts\": ", T_TS}, \
-    {",\n    \"dur\": ", T_TS}, {"\n    ", T_NONE}, {",\n    \"args\": {\n      \"External id\": ", T_I64}, {"\n    }", T_NONE}, \
-    {"\n  },", T_NONE}
+    {XHEAD("gpu_user_annotation"), T_NAME, VK_U32, NS_NAME}, {"\",\n    \"pid\": ", T_U64, VK_U32, NS_PID}, \
+    {",\n    \"tid\": ", T_U64, VK_U32, NS_TID}, {",\n    \"ts\": ", T_TS, VK_64, NS_TS}, \
+    {",\n    \"dur\": ", T_TS, VK_64, NS_DUR}, {"\n    ", T_NONE}, {",\n    \"args\": {\n      \"External id\": ", T_I64, VK_I32, NS_EXT}, \
+    {"\n    }", T_NONE}, {"\n  },", T_NONE}
 
 
 // One table for everything: [api][kernel][mem][op head, metadata marker, op tail][annotation][constant strings].
@@ -719,7 +762,7 @@ enum : int { CS_TYPE = 0, CS_MEMCPY_KIND = 29, CS_MEMORY_KIND = 41, CS_LIMIT = 5
 
 constexpr int API_BASE = 0, KERNEL_BASE = API_BASE + A_COUNT, MEM_BASE = KERNEL_BASE + K_COUNT, OP_BASE = MEM_BASE + M_COUNT,
               ANN_BASE = OP_BASE + O_COUNT, CSTR_BASE = ANN_BASE + N_COUNT, FIELD_COUNT = CSTR_BASE + CS_COUNT;
-constexpr FieldSrc kAllFields[] = {K2J_API_FIELDS, K2J_KERNEL_FIELDS, K2J_MEM_FIELDS, K2J_OPHEAD_FIELDS, {"", T_MD},
+constexpr FieldSrc kAllFields[] = {K2J_API_FIELDS, K2J_KERNEL_FIELDS, K2J_MEM_FIELDS, K2J_OPHEAD_FIELDS, {"", T_MD, VK_U32, OS_ROW},
                                    K2J_OPTAIL_FIELDS, K2J_ANN_FIELDS, K2J_CSTR_FIELDS};
 static_assert(sizeof(kAllFields) / sizeof(kAllFields[0]) == FIELD_COUNT, "field table and enums disagree");
 constexpr int kAllWords = prog_words(kAllFields);
@@ -769,6 +812,7 @@ template <class S> __device__ __forceinline__ void put_pool_words(S& s, const ui
 }
 template <class S> __device__ __forceinline__ void put_name(S& s, const Dev& d, uint32_t id, unsigned long long* name_bytes) {
   if (id >= d.n_strings) { atomicAdd(&d.counters->device_check, 1ull); return; }
+
   const uint32_t len = d.esc_name_len[id];
   put_pool_words(s, d.esc_name + esc_name_pos(d, id), len);
   *name_bytes += len;
@@ -846,60 +890,58 @@ __device__ __noinline__ void span_update(const Dev& d, uint32_t corr, uint32_t d
 
 struct Tally { uint32_t x, flow; unsigned long long name_bytes; uint64_t ev; };
 
-// Per-event values that are computed rather than read straight from the record.  They stay in
-// registers; everything else is re-read from the record (an L1 hit) when its field comes up.
-struct EvCtx {
-  const uint8_t* r; uint64_t j;
-  int64_t ts_rel, dur, pid, tid;
-  int32_t ext; uint32_t corr, name, aux;   // aux: cbid (api), activity type (op), layout shift (memcpy2)
-  uint32_t* sm;                             // this thread's column of the per-block scratch (see X_*)
-};
-// Rarely used per-event values live in shared memory (word i of thread t at [i * kEventThreads + t]),
-// which keeps the formatting loop's register footprint small.
-enum : int { X_D0_LO, X_D0_HI, X_D1_LO, X_D1_HI, X_OCC_PCT, X_OCC_ACTIVE, X_OCC_LIMIT, X_OCC_LREGS, X_OCC_LSMEM, X_OCC_LWARPS,
-             X_OCC_LBLOCKS, X_OCC_LBARR, X_OCC_AREGS, X_OCC_ASMEM_LO, X_OCC_ASMEM_HI, X_COUNT };
-constexpr int kCtxStride = 128;  // must equal kEventThreads (checked below)
-__device__ __forceinline__ void xs(const EvCtx& c, int i, uint32_t v) { c.sm[i * kCtxStride] = v; }
-__device__ __forceinline__ uint32_t xl(const EvCtx& c, int i) { return c.sm[i * kCtxStride]; }
-__device__ __forceinline__ void xs64(const EvCtx& c, int i, uint64_t v) { xs(c, i, (uint32_t)v); xs(c, i + 1, (uint32_t)(v >> 32)); }
-__device__ __forceinline__ uint64_t xl64(const EvCtx& c, int i) { return (uint64_t)xl(c, i) | ((uint64_t)xl(c, i + 1) << 32); }
+// A thread's area in shared memory: the staged record plus value slots (see the S_ offsets above).
+constexpr int kRecStride = 27;              // 8-byte units per thread: 26 for the longest record, odd so that 64-bit
+                                            // reads of 32 lanes fall in distinct banks
+constexpr int kAreaWords = 2 * kRecStride;  // the same in 32-bit words
+__device__ __forceinline__ uint32_t a32(const uint32_t* a, int off) { return a[off >> 2]; }
+__device__ __forceinline__ uint64_t a64(const uint32_t* a, int off) { return (uint64_t)a[off >> 2] | ((uint64_t)a[(off >> 2) + 1] << 32); }
+__device__ __forceinline__ void s32(uint32_t* a, int off, uint32_t v) { a[off >> 2] = v; }
+__device__ __forceinline__ void s64(uint32_t* a, int off, uint64_t v) { a[off >> 2] = (uint32_t)v; a[(off >> 2) + 1] = (uint32_t)(v >> 32); }
+// value of a field: 32 bits zero- or sign-extended, or 64 bits (no branches)
+__device__ __forceinline__ uint64_t slot_value(const uint32_t* a, uint32_t voff, uint32_t vk) {
+  const uint32_t lo = a[voff >> 2];
+  uint32_t hi = vk == VK_I32 ? (uint32_t)((int32_t)lo >> 31) : 0u;
+  if (vk == VK_64) hi = a[(voff >> 2) + 1];
+  return (uint64_t)lo | ((uint64_t)hi << 32);
+}
 
-// Each gather returns false if the record produces no event (`*filt`: 1 blocklisted, 2 outside the window).
+// Each gather reads the staged record in `a`, writes the computed slots and returns the set of fields
+// the event prints; 0 if the record produces no event (`*filt`: 1 blocklisted, 2 outside the window).
+// `counting`: the size pass, which also finds the linked CPU op; the emit pass gets it as `ext_known`.
 
 // handleRuntimeActivity / handleDriverActivity (libkineto/src/CuptiActivityProfiler.cpp:304-358)
-__device__ __forceinline__ bool gather_api(const Dev& d, const uint8_t* r, EvCtx& c, uint64_t* present, Tally& t, uint32_t* filt,
-                                           bool counting, int32_t ext_known) {
-  const uint2 a = *reinterpret_cast<const uint2*>(r);        // kind, cbid (40-byte records are 8-byte aligned)
-  const uint64_t st = *reinterpret_cast<const uint64_t*>(r + 8), en = *reinterpret_cast<const uint64_t*>(r + 16);
-  const uint2 b = *reinterpret_cast<const uint2*>(r + 24);   // processId, threadId
-  const uint32_t corr = *reinterpret_cast<const uint32_t*>(r + 32);
-  const bool driver = a.x == K_DRIVER;
-  const uint32_t cbid = a.y;
+__device__ __forceinline__ uint64_t gather_api(const Dev& d, uint32_t* a, Tally& t, uint32_t* filt, bool counting, int32_t* ext_io) {
+  const uint32_t kind = a32(a, 0), cbid = a32(a, AR_CBID);
+  const uint64_t st = a64(a, 8), en = a64(a, 16);
+  const uint32_t corr = a32(a, AR_CORR);
+  const bool driver = kind == K_DRIVER;
   bool flow_start;
   if (!driver) {
     // CuptiCbidRegistry.cpp:127-161 blocklist; :57-122 flow-starting callbacks
-    if (cbid == 17u || cbid == 16u || cbid == 10u || cbid == 133u || cbid == 134u || cbid == 136u) { *filt = 1; return false; }
+    if (cbid == 17u || cbid == 16u || cbid == 10u || cbid == 133u || cbid == 134u || cbid == 136u) { *filt = 1; return 0; }
     flow_start = cbid == 211u || cbid == 269u || cbid == 272u || cbid == 430u || cbid == 311u || cbid == 131u ||
                  cbid == 165u || cbid == 147u || (cbid >= 31u && cbid <= 52u);
   } else {
     // CuptiCbidRegistry.cpp:166-207: only these driver callbacks are tracked
-    if (!(cbid == 307u || cbid == 652u || (cbid >= 549u && cbid <= 552u) || cbid == 554u || cbid == 555u)) return false;
+    if (!(cbid == 307u || cbid == 652u || (cbid >= 549u && cbid <= 552u) || cbid == 554u || cbid == 555u)) return 0;
     flow_start = cbid == 307u || cbid == 652u;
   }
   const int64_t ts = conv_ts(d, st), dur = conv_dur(d, st, en);
-  if (out_of_range(d, ts, dur)) { *filt = 2; return false; }
-  int32_t tid = (int32_t)b.y;
+  if (out_of_range(d, ts, dur)) { *filt = 2; return 0; }
+  int32_t tid = (int32_t)a32(a, 28);
   {  // resourceInfo_.find({processId(), tid}), CuptiActivityProfiler.cpp:315-319
     const uint32_t idx = tab_find(d.tid_tab, d.tid_mask, (uint32_t)tid);
     if (idx != 0xFFFFFFFFu) tid = idx < d.n_tid_pairs ? d.tid_pairs[2 * idx + 1] : (int32_t)d.op_resource[idx - d.n_tid_pairs];
   }
-  int32_t ext = ext_known;
-  if (counting) linked_op(d, corr, &ext);
+  int32_t ext = *ext_io;
+  if (counting) { linked_op(d, corr, &ext); *ext_io = ext; }
   const bool has_ext = ext != 0;
   const uint32_t ntab = driver ? d.n_dr : d.n_rt;
   const bool named = cbid < ntab;
-  c.ts_rel = rel_ts(d, ts); c.dur = dur < 0 ? 0 : dur; c.pid = d.pid; c.tid = abs_tid(tid); c.ext = ext; c.corr = corr;
-  c.aux = cbid; c.name = named ? (driver ? d.dr_names : d.rt_names)[cbid] : 0u;
+  s64(a, AS_TS, (uint64_t)rel_ts(d, ts)); s64(a, AS_DUR, (uint64_t)(dur < 0 ? 0 : dur));
+  s32(a, AS_PID, (uint32_t)d.pid); s32(a, AS_TID, (uint32_t)abs_tid(tid)); s32(a, AS_EXT, (uint32_t)ext);
+  s32(a, AS_NAME, named ? (driver ? d.dr_names : d.rt_names)[cbid] : 0u);
   uint64_t p = 0;
   auto on = [&](int f) { p |= 1ull << f; };
   on(driver ? A_HEAD_DR : A_HEAD_RT); on(named ? A_NAME : A_INVALID);
@@ -913,20 +955,7 @@ __device__ __forceinline__ bool gather_api(const Dev& d, const uint8_t* r, EvCtx
     on(A_FEND);
     t.flow++;
   }
-  *present = p;
-  return true;
-}
-__device__ __forceinline__ uint64_t value_api(int f, const EvCtx& c) {
-  switch (f) {
-    case A_NAME: return c.name;
-    case A_PID: case A_FPID: return (uint64_t)c.pid;
-    case A_TID: case A_FTID: return (uint64_t)c.tid;
-    case A_TS: case A_FTS: return (uint64_t)c.ts_rel;
-    case A_DUR: return (uint64_t)c.dur;
-    case A_EXT: return (uint64_t)(int64_t)c.ext;
-    case A_CBID: return c.aux;
-    default: return c.corr;  // A_CORR, A_FLOW_S, A_FLOW_F
-  }
+  return p;
 }
 
 // computeOccupancyMetrics (libkineto/src/DeviceProperties.cpp:176-222) with NVIDIA's occupancy calculator.
@@ -963,19 +992,17 @@ __device__ __forceinline__ void occupancy_metrics(const Dev& d, uint32_t dev, bo
 }
 
 // GpuActivity<Kernel> (libkineto/src/CuptiActivity.h:499-576)
-__device__ __forceinline__ bool gather_kernel(const Dev& d, const uint8_t* r, EvCtx& c, uint64_t* present, Tally& t, uint32_t* filt,
-                                              bool counting, int32_t ext_known) {
-  const uint64_t st = *reinterpret_cast<const uint64_t*>(r + 16), en = *reinterpret_cast<const uint64_t*>(r + 24);
+__device__ __forceinline__ uint64_t gather_kernel(const Dev& d, uint32_t* a, Tally& t, uint32_t* filt, bool counting, int32_t* ext_io) {
+  const uint64_t st = a64(a, 16), en = a64(a, 24);
   const int64_t ts = conv_ts(d, st), dur = conv_dur(d, st, en);
-  if (out_of_range(d, ts, dur)) { *filt = 2; return false; }
-  const uint32_t dev = *reinterpret_cast<const uint32_t*>(r + 40);
-  const uint32_t stream = *reinterpret_cast<const uint32_t*>(r + 48), corr = *reinterpret_cast<const uint32_t*>(r + 92);
-  const int32_t gx = *reinterpret_cast<const int32_t*>(r + 52), gy = *reinterpret_cast<const int32_t*>(r + 56), gz = *reinterpret_cast<const int32_t*>(r + 60);
-  const int32_t bx = *reinterpret_cast<const int32_t*>(r + 64), by = *reinterpret_cast<const int32_t*>(r + 68), bz = *reinterpret_cast<const int32_t*>(r + 72);
-  const int32_t ssm = *reinterpret_cast<const int32_t*>(r + 76), dsm = *reinterpret_cast<const int32_t*>(r + 80);
-  const uint32_t regs = *reinterpret_cast<const uint16_t*>(r + 6);
-  int32_t ext = ext_known;
-  if (counting) linked_op(d, corr, &ext);
+  if (out_of_range(d, ts, dur)) { *filt = 2; return 0; }
+  const uint32_t dev = a32(a, KR_DEV), stream = a32(a, KR_STREAM), corr = a32(a, KR_CORR);
+  const int32_t gx = (int32_t)a32(a, KR_GRID), gy = (int32_t)a32(a, KR_GRID + 4), gz = (int32_t)a32(a, KR_GRID + 8);
+  const int32_t bx = (int32_t)a32(a, KR_BLOCK), by = (int32_t)a32(a, KR_BLOCK + 4), bz = (int32_t)a32(a, KR_BLOCK + 8);
+  const int32_t ssm = (int32_t)a32(a, 76), dsm = (int32_t)a32(a, 80);
+  const uint32_t regs = a32(a, 4) >> 16;  // registersPerThread: 16 bits at byte 6
+  int32_t ext = *ext_io;
+  if (counting) { linked_op(d, corr, &ext); *ext_io = ext; }
   const bool has_ext = ext != 0;
   // blocksPerSm / warpsPerSm (DeviceProperties.cpp:161-174): 32-bit wrapping products, single-precision
   // arithmetic without contraction.
@@ -988,73 +1015,52 @@ __device__ __forceinline__ bool gather_kernel(const Dev& d, const uint8_t* r, Ev
   cudaOccResult occ;
   float occupancy;
   occupancy_metrics(d, dev, have_dev, sm_count, grid_prod, block_prod, regs, ssm, dsm, &occ, &occupancy);
-  xs(c, X_OCC_PCT, (uint32_t)(int32_t)llround(__dmul_rn((double)occupancy, 100.0)));
-  xs(c, X_OCC_ACTIVE, (uint32_t)occ.activeBlocksPerMultiprocessor); xs(c, X_OCC_LIMIT, (uint32_t)(CS_LIMIT + (int)(occ.limitingFactors & 31u)));
-  xs(c, X_OCC_LREGS, (uint32_t)occ.blockLimitRegs); xs(c, X_OCC_LSMEM, (uint32_t)occ.blockLimitSharedMem);
-  xs(c, X_OCC_LWARPS, (uint32_t)occ.blockLimitWarps); xs(c, X_OCC_LBLOCKS, (uint32_t)occ.blockLimitBlocks);
-  xs(c, X_OCC_LBARR, (uint32_t)occ.blockLimitBarriers); xs(c, X_OCC_AREGS, (uint32_t)occ.allocatedRegistersPerBlock);
-  xs64(c, X_OCC_ASMEM_LO, (uint64_t)occ.allocatedSharedMemPerBlock);
-  xs64(c, X_D0_LO, (uint64_t)__double_as_longlong((double)bps)); xs64(c, X_D1_LO, (uint64_t)__double_as_longlong((double)wps));
-  c.ts_rel = rel_ts(d, ts); c.dur = dur < 0 ? 0 : dur; c.pid = dev; c.tid = stream; c.ext = ext; c.corr = corr;
+  s32(a, KS_PCT, (uint32_t)(int32_t)llround(__dmul_rn((double)occupancy, 100.0)));
+  s32(a, KS_ACTIVE, (uint32_t)occ.activeBlocksPerMultiprocessor); s32(a, KS_LIMIT, (uint32_t)(CS_LIMIT + (int)(occ.limitingFactors & 31u)));
+  s32(a, KS_LREGS, (uint32_t)occ.blockLimitRegs); s32(a, KS_LSMEM, (uint32_t)occ.blockLimitSharedMem);
+  s32(a, KS_LWARPS, (uint32_t)occ.blockLimitWarps); s32(a, KS_LBLOCKS, (uint32_t)occ.blockLimitBlocks);
+  s32(a, KS_LBARR, (uint32_t)occ.blockLimitBarriers); s32(a, KS_AREGS, (uint32_t)occ.allocatedRegistersPerBlock);
+  s64(a, KS_ASMEM, (uint64_t)occ.allocatedSharedMemPerBlock);
+  s64(a, KS_BPS, (uint64_t)__double_as_longlong((double)bps)); s64(a, KS_WPS, (uint64_t)__double_as_longlong((double)wps));
+  s64(a, KS_TS, (uint64_t)rel_ts(d, ts)); s64(a, KS_DUR, (uint64_t)(dur < 0 ? 0 : dur));
+  s32(a, KS_REGS, regs); s32(a, KS_SMEM, (uint32_t)ssm + (uint32_t)dsm); s32(a, KS_EXT, (uint32_t)ext);
   uint64_t p = (1ull << K_COUNT) - 1ull;  // every field except the optional ones below
   if (!has_ext) p &= ~((1ull << K_EXT) | (1ull << K_EXTC));
   t.x++;
   if (corr > 0) t.flow++;
   else p &= ~((1ull << K_FLOW) | (1ull << K_FPID) | (1ull << K_FTID) | (1ull << K_FTS) | (1ull << K_FEND));
-  *present = p;
   if (counting && d.span_key != nullptr) span_update(d, corr, dev, stream, ts, dur, t.ev);
-  return true;
-}
-__device__ __forceinline__ uint64_t value_kernel(int f, const EvCtx& c) {
-  const uint8_t* r = c.r;
-  switch (f) {
-    case K_HEAD: return (uint32_t)*reinterpret_cast<const uint64_t*>(r + 104);
-    case K_PID: case K_FPID: case K_DEV: return (uint64_t)c.pid;
-    case K_TID: case K_FTID: case K_STREAM: return (uint64_t)c.tid;
-    case K_TS: case K_FTS: return (uint64_t)c.ts_rel;
-    case K_DUR: return (uint64_t)c.dur;
-    case K_EXT: return (uint64_t)(int64_t)c.ext;
-    case K_QUEUED: return *reinterpret_cast<const uint64_t*>(r + 120);
-    case K_CTX: return *reinterpret_cast<const uint32_t*>(r + 44);
-    case K_CORR: case K_FLOW: return c.corr;
-    case K_REGS: return *reinterpret_cast<const uint16_t*>(r + 6);
-    case K_SMEM: return (uint64_t)(int64_t)(int32_t)(*reinterpret_cast<const uint32_t*>(r + 76) + *reinterpret_cast<const uint32_t*>(r + 80));
-    case K_BPS: return xl64(c, X_D0_LO);
-    case K_WPS: return xl64(c, X_D1_LO);
-    case K_GX: case K_GY: case K_GZ: return (uint64_t)(int64_t)*reinterpret_cast<const int32_t*>(r + 52 + 4 * (f - K_GX));
-    case K_BX: case K_BY: case K_BZ: return (uint64_t)(int64_t)*reinterpret_cast<const int32_t*>(r + 64 + 4 * (f - K_BX));
-    case K_OCCPCT: return (uint64_t)(int64_t)(int32_t)xl(c, X_OCC_PCT);
-    case K_ACTIVE: return (uint64_t)(int64_t)(int32_t)xl(c, X_OCC_ACTIVE);
-    case K_LIMIT: return xl(c, X_OCC_LIMIT);
-    case K_LREGS: return (uint64_t)(int64_t)(int32_t)xl(c, X_OCC_LREGS);
-    case K_LSMEM: return (uint64_t)(int64_t)(int32_t)xl(c, X_OCC_LSMEM);
-    case K_LWARPS: return (uint64_t)(int64_t)(int32_t)xl(c, X_OCC_LWARPS);
-    case K_LBLOCKS: return (uint64_t)(int64_t)(int32_t)xl(c, X_OCC_LBLOCKS);
-    case K_LBARR: return (uint64_t)(int64_t)(int32_t)xl(c, X_OCC_LBARR);
-    case K_AREGS: return (uint64_t)(int64_t)(int32_t)xl(c, X_OCC_AREGS);
-    case K_ASMEM: return xl64(c, X_OCC_ASMEM_LO);
-    case K_GRAPH: return *reinterpret_cast<const uint32_t*>(r + 156);
-    case K_NODE: return *reinterpret_cast<const uint64_t*>(r + 144);
-    case K_CHAN: return *reinterpret_cast<const uint32_t*>(r + 168);
-    default: return *reinterpret_cast<const uint32_t*>(r + 172);  // K_CHTYPE
-  }
+  return p;
 }
 
 // memcpy / memcpy2 / memset records (libkineto/src/CuptiActivity.h:586-712)
 template <int CLS>
-__device__ __forceinline__ bool gather_mem(const Dev& d, const uint8_t* r, EvCtx& c, uint64_t* present, Tally& t, uint32_t* filt,
-                                           bool counting, int32_t ext_known) {
-  const uint64_t st = *reinterpret_cast<const uint64_t*>(r + 16), en = *reinterpret_cast<const uint64_t*>(r + 24);
+__device__ __forceinline__ uint64_t gather_mem(const Dev& d, uint32_t* a, Tally& t, uint32_t* filt, bool counting, int32_t* ext_io) {
+  const uint64_t st = a64(a, 16), en = a64(a, 24);
   const int64_t ts = conv_ts(d, st), dur = conv_dur(d, st, en);
-  if (out_of_range(d, ts, dur)) { *filt = 2; return false; }
-  const uint64_t bytes = *reinterpret_cast<const uint64_t*>(r + 8);
-  const uint32_t dev = *reinterpret_cast<const uint32_t*>(r + 32), stream = *reinterpret_cast<const uint32_t*>(r + 40);
-  const uint32_t corr = *reinterpret_cast<const uint32_t*>(r + (CLS == C_MEMCPY2 ? 60 : 44));
-  int32_t ext = ext_known;
-  if (counting) linked_op(d, corr, &ext);
+  if (out_of_range(d, ts, dur)) { *filt = 2; return 0; }
+  const uint64_t bytes = a64(a, MR_BYTES);
+  const uint32_t dev = a32(a, MR_DEV), stream = a32(a, MR_STREAM);
+  constexpr int g = CLS == C_MEMCPY2 ? 8 : 0;  // byte shift of the trailing fields in the peer-to-peer layout
+  const uint32_t corr = a32(a, CLS == C_MEMCPY2 ? 60 : 44);
+  int32_t ext = *ext_io;
+  if (counting) { linked_op(d, corr, &ext); *ext_io = ext; }
   const bool has_ext = ext != 0;
-  c.ts_rel = rel_ts(d, ts); c.dur = dur < 0 ? 0 : dur; c.pid = dev; c.tid = stream; c.ext = ext; c.corr = corr;
-  c.aux = CLS == C_MEMCPY2 ? 8u : 0u;  // byte shift of the trailing fields in the peer-to-peer layout
+  const uint32_t w1 = a32(a, 4);
+  const uint64_t node = a64(a, 64 + g);
+  const uint32_t graph = a32(a, 72 + g), chan = a32(a, 76 + g), chtype = a32(a, 80 + g);
+  if (CLS == C_MEMSET) {
+    const uint32_t k = a32(a, 48) >> 16;  // memoryKind: 16 bits at byte 50
+    s32(a, MS_KIND0, CS_MEMORY_KIND + (k <= 7 ? k : 8));
+  } else {
+    const uint32_t k0 = w1 & 0xffu, k1 = (w1 >> 8) & 0xffu, k2 = (w1 >> 16) & 0xffu;  // copyKind, srcKind, dstKind
+    s32(a, MS_KIND0, CS_MEMCPY_KIND + (k0 <= 10 ? k0 : 11));
+    s32(a, MS_KIND1, CS_MEMORY_KIND + (k1 <= 7 ? k1 : 8));
+    s32(a, MS_KIND2, CS_MEMORY_KIND + (k2 <= 7 ? k2 : 8));
+  }
+  s64(a, MS_TS, (uint64_t)rel_ts(d, ts)); s64(a, MS_DUR, (uint64_t)(dur < 0 ? 0 : dur));
+  s32(a, MS_EXT, (uint32_t)ext); s32(a, MS_CORR, corr);
+  s32(a, MS_GRAPH, graph); s64(a, MS_NODE, node); s32(a, MS_CHAN, chan); s32(a, MS_CHTYPE, chtype);
   uint64_t p = 0;
   auto on = [&](int f) { p |= 1ull << f; };
   if (CLS == C_MEMSET) on(M_SET_KIND); else { on(M_CPY_KIND); on(M_CPY_SRC); on(M_CPY_DST); }
@@ -1065,51 +1071,23 @@ __device__ __forceinline__ bool gather_mem(const Dev& d, const uint8_t* r, EvCtx
   on(M_STREAM); on(M_CORR); on(M_BYTES);
   if (dur != 0) {  // addBandwidthTypedMetadata, CuptiActivity.h:460-470
     on(M_BW);
-    xs64(c, X_D0_LO, (uint64_t)__double_as_longlong(__ddiv_rn(__ull2double_rn(bytes), __ll2double_rn(dur))));
+    s64(a, MS_BW, (uint64_t)__double_as_longlong(__ddiv_rn(__ull2double_rn(bytes), __ll2double_rn(dur))));
   }
   on(M_GRAPH); on(M_NODE); on(M_CHAN); on(M_CHTYPE); on(M_CLOSE);
   t.x++;
   if (corr > 0) { on(M_FLOW); on(M_FPID); on(M_FTID); on(M_FTS); on(M_FEND); t.flow++; }
-  *present = p;
   if (counting && d.span_key != nullptr) span_update(d, corr, dev, stream, ts, dur, t.ev);
-  return true;
-}
-__device__ __forceinline__ uint64_t value_mem(int f, const EvCtx& c) {
-  const uint8_t* r = c.r;
-  const uint32_t g = c.aux;
-  switch (f) {
-    case M_CPY_KIND: { const uint32_t k = r[4]; return CS_MEMCPY_KIND + (k <= 10 ? k : 11); }
-    case M_CPY_SRC: { const uint32_t k = r[5]; return CS_MEMORY_KIND + (k <= 7 ? k : 8); }
-    case M_CPY_DST: { const uint32_t k = r[6]; return CS_MEMORY_KIND + (k <= 7 ? k : 8); }
-    case M_SET_KIND: { const uint32_t k = *reinterpret_cast<const uint16_t*>(r + 50); return CS_MEMORY_KIND + (k <= 7 ? k : 8); }
-    case M_PID: case M_FPID: case M_DEV: case M_INDEV: return (uint64_t)c.pid;
-    case M_TID: case M_FTID: case M_STREAM: return (uint64_t)c.tid;
-    case M_TS: case M_FTS: return (uint64_t)c.ts_rel;
-    case M_DUR: return (uint64_t)c.dur;
-    case M_EXT: return (uint64_t)(int64_t)c.ext;
-    case M_FROMDEV: return *reinterpret_cast<const uint32_t*>(r + 44);
-    case M_TODEV: return *reinterpret_cast<const uint32_t*>(r + 52);
-    case M_FROMCTX: return *reinterpret_cast<const uint32_t*>(r + 48);
-    case M_INCTX: case M_CTX: return *reinterpret_cast<const uint32_t*>(r + 36);
-    case M_TOCTX: return *reinterpret_cast<const uint32_t*>(r + 56);
-    case M_CORR: case M_FLOW: return c.corr;
-    case M_BYTES: return *reinterpret_cast<const uint64_t*>(r + 8);
-    case M_BW: return xl64(c, X_D0_LO);
-    case M_GRAPH: return *reinterpret_cast<const uint32_t*>(r + 72 + g);
-    case M_NODE: return *reinterpret_cast<const uint64_t*>(r + 64 + g);
-    case M_CHAN: return *reinterpret_cast<const uint32_t*>(r + 76 + g);
-    default: return *reinterpret_cast<const uint32_t*>(r + 80 + g);  // M_CHTYPE
-  }
+  return p;
 }
 
 // CPU-side activity: ChromeTraceLogger::handleActivity for a GenericTraceActivity (output_json.cpp:837-963)
-__device__ __forceinline__ bool gather_op(const Dev& d, uint64_t i, EvCtx& c, uint64_t* present, Tally& t) {
+__device__ __forceinline__ uint64_t gather_op(const Dev& d, uint64_t i, uint32_t* a, Tally& t) {
   const int32_t type = d.op_type[i];
-  if ((uint32_t)type >= 29u) { atomicAdd(&d.counters->device_check, 1ull); return false; }
-  if (!((d.type_mask >> type) & 1u)) return false;  // type not selected: joins, but is not logged
+  if ((uint32_t)type >= 29u) { atomicAdd(&d.counters->device_check, 1ull); return 0; }
+  if (!((d.type_mask >> type) & 1u)) return 0;  // type not selected: joins, but is not logged
   if (type == 9 || type == 17 || type == 26 || type == 28) {  // instant / counter events: not implemented
     atomicAdd(&d.counters->device_check, 1ull);
-    return false;
+    return 0;
   }
   int64_t ts = d.op_start[i];
   int64_t dur = d.op_end[i] - ts;
@@ -1122,9 +1100,11 @@ __device__ __forceinline__ bool gather_op(const Dev& d, uint64_t i, EvCtx& c, ui
   if (!excluded) ext = d.op_id[i];
   const bool has_md = d.op_mdoff[i + 1] > d.op_mdoff[i];
   const bool has_args = ext != 0 || has_md;
-  c.ts_rel = rel_ts(d, ts); c.dur = dur; xs64(c, X_D0_LO, (uint64_t)rel_ts(d, flow_ts));
-  c.pid = op_pid(d, d.op_device[i]); c.tid = abs_tid(d.op_resource[i]); c.ext = ext; c.aux = (uint32_t)type;
-  c.name = d.op_name[i]; c.corr = d.op_flow[i];
+  const uint32_t flow = d.op_flow[i];
+  s32(a, OS_CAT, (uint32_t)(CS_TYPE + type)); s32(a, OS_NAME, d.op_name[i]); s32(a, OS_PID, (uint32_t)op_pid(d, d.op_device[i]));
+  s32(a, OS_EXT, (uint32_t)ext); s64(a, OS_TID, (uint64_t)abs_tid(d.op_resource[i]));
+  s64(a, OS_TS, (uint64_t)rel_ts(d, ts)); s64(a, OS_DUR, (uint64_t)dur); s32(a, OS_ROW, (uint32_t)i); s32(a, OS_FLOW, flow);
+  s64(a, OS_FTS, (uint64_t)rel_ts(d, flow_ts));
   uint64_t p = 0;
   auto on = [&](int f) { p |= 1ull << f; };
   on(O_CAT); on(O_NAME); on(O_PID); on(O_TID); on(O_TS); on(O_DUR); on(O_PAD);
@@ -1135,192 +1115,159 @@ __device__ __forceinline__ bool gather_op(const Dev& d, uint64_t i, EvCtx& c, ui
   on(P_CLOSE);
   t.x++;
   const uint32_t ft = d.op_flowt[i] & 0xfu;
-  if (c.corr > 0 && (ft == 1u || ft == 2u)) {  // handleGenericLink, output_json.cpp:973-995
+  if (flow > 0 && (ft == 1u || ft == 2u)) {  // handleGenericLink, output_json.cpp:973-995
     const bool start = (d.op_flowt[i] >> 4) & 1u;
     on(start ? P_FLOW_S : P_FLOW_F); on(P_FPID); on(P_FTID); on(P_FTS); on(ft == 1u ? P_FWDBWD : P_AC2G);
     if (!start) on(P_FBP);
     on(P_FEND);
     t.flow++;
   }
-  *present = p;
-  return true;
-}
-__device__ __forceinline__ uint64_t value_op(int f, const EvCtx& c) {
-  switch (f) {
-    case O_CAT: return CS_TYPE + c.aux;
-    case O_NAME: return c.name;
-    case O_PID: case P_FPID: return (uint64_t)c.pid;
-    case O_TID: case P_FTID: return (uint64_t)c.tid;
-    case O_TS: return (uint64_t)c.ts_rel;
-    case O_DUR: return (uint64_t)c.dur;
-    case O_EXT: return (uint64_t)(int64_t)c.ext;
-    case O_MD: return c.j;
-    case P_FTS: return xl64(c, X_D0_LO);
-    default: return c.corr;  // P_FLOW_S, P_FLOW_F
-  }
-}
-__device__ __forceinline__ uint64_t value_ann(int f, const EvCtx& c) {
-  switch (f) {
-    case N_HEAD: return c.name;
-    case N_PID: return (uint64_t)c.pid;
-    case N_TID: return (uint64_t)c.tid;
-    case N_TS: return (uint64_t)c.ts_rel;
-    case N_DUR: return (uint64_t)c.dur;
-    default: return (uint64_t)(int64_t)c.ext;  // N_EXT
-  }
-}
-
-constexpr int C_ANN = 10;  // program selector for annotation spans (not a record class)
-
-// The formatting loop shared by every class: fields [base, base + nf) of the table.  `present` has one
-// bit per field.  T_MD (CPU-side activities only) formats the typed metadata entries of the op
-// (JsonTypedMetadataVisitor, libkineto/include/TypedMetadataJson.h:72-158).
-__device__ __forceinline__ uint64_t field_value(int cls, int f, const EvCtx& c) {
-  switch (cls) {
-    case C_API: return value_api(f, c);
-    case C_KERNEL: return value_kernel(f, c);
-    case C_MEMCPY: case C_MEMCPY2: case C_MEMSET: return value_mem(f, c);
-    case C_ANN: return value_ann(f, c);
-    default: return value_op(f, c);
-  }
+  return p;
 }
 
 // The value that follows a field's literal.  T_MD (CPU-side activities only) formats the typed metadata
-// entries of the op (JsonTypedMetadataVisitor, libkineto/include/TypedMetadataJson.h:72-158).
+// entries of the op (JsonTypedMetadataVisitor, libkineto/include/TypedMetadataJson.h:72-158): each entry
+// is mapped onto one of the value types, so the kernel holds one copy of every formatter.
+enum : int { T_BOOL = 8, T_MDSTR, T_QMDSTR };
 template <class S>
 __device__ __forceinline__ void put_value(S& s, const Dev& d, int type, uint64_t v, unsigned long long* name_bytes) {
-  switch (type) {
-    case T_NONE: break;
-    case T_U64: put_dec(s, v); break;
-    case T_I64: put_sdec(s, (int64_t)v); break;
-    case T_TS: put_ts2(s, (int64_t)v); break;
-    case T_DBL: put_dbl(s, __longlong_as_double((long long)v)); break;
-    case T_NAME: put_name(s, d, (uint32_t)v, name_bytes); break;
-    case T_CSTR: { const FieldDesc cs = g_fields.f[CSTR_BASE + (uint32_t)v]; s.words(g_fields.w + cs.off, cs.len); break; }
-    default: {  // T_MD
-      const uint32_t m0 = d.op_mdoff[v], m1 = d.op_mdoff[v + 1];
-      for (uint32_t e = m0; e < m1; e++) {
-        const MdEntry md = d.md[e];
-        if (e > m0) s.put(0x202Cu, 2);  // ", "
-        put_char(s, '"'); put_mdstr(s, d, md.key); s.put(0x203A22u, 3);  // "\": "
-        switch (md.type) {
-          case 0: put_sdec(s, (int64_t)md.value); break;
-          case 1: put_dec(s, md.value); break;
-          case 2: put_dbl(s, __longlong_as_double((long long)md.value)); break;
-          case 3: if (md.value) s.put4(0x65757274u); else { s.put4(0x736C6166u); put_char(s, 'e'); } break;  // true / false
-          case 4: put_char(s, '"'); put_mdstr(s, d, (uint32_t)md.value); put_char(s, '"'); break;
-          default: put_mdstr(s, d, (uint32_t)md.value); break;
-        }
-      }
-      break;
+  if (type == T_NONE) return;
+  uint32_t e = 0, m1 = 0, m0 = 0;
+  const bool md_mode = type == T_MD;
+  if (md_mode) { m0 = e = d.op_mdoff[v]; m1 = d.op_mdoff[v + 1]; if (e >= m1) return; }
+  do {
+    if (md_mode) {
+      const MdEntry md = d.md[e];
+      if (e > m0) s.put(0x202Cu, 2);  // ", "
+      put_char(s, '"'); put_mdstr(s, d, md.key); s.put(0x203A22u, 3);  // "\": "
+      v = md.value;
+      type = md.type == 0 ? T_I64 : md.type == 1 ? T_U64 : md.type == 2 ? T_DBL : md.type == 3 ? T_BOOL : md.type == 4 ? T_QMDSTR : T_MDSTR;
     }
-  }
+    switch (type) {
+      case T_U64: case T_I64: case T_TS: {
+        uint64_t mag = v;
+        uint32_t fr = 0;
+        if (type == T_I64 && (int64_t)v < 0) { put_char(s, '-'); mag = 0ull - v; }
+        if (type == T_TS) { mag = v / 1000ull; fr = (uint32_t)(v - mag * 1000ull); }  // "{}.{:03}" of ns/1000, ns%1000
+        put_dec(s, mag);
+        if (type == T_TS) {
+          if (S::kCounting) s.skip(4);
+          else {
+            const uint32_t x = (fr * 41u) >> 12, r = fr - x * 100u, y = (r * 103u) >> 10, z = r - y * 10u;
+            s.put4(0x3030302Eu + (x << 8) + (y << 16) + (z << 24));
+          }
+        }
+        break;
+      }
+      case T_DBL: put_dbl(s, __longlong_as_double((long long)v)); break;
+      case T_NAME: put_name(s, d, (uint32_t)v, name_bytes); break;
+      case T_CSTR: { const FieldDesc cs = g_fields.f[CSTR_BASE + (uint32_t)v]; s.words(g_fields.w + cs.off, cs.len); break; }
+      case T_BOOL: if (v) s.put4(0x65757274u); else s.put64(0x65736C6166ull, 5); break;  // true / false
+      default: {  // T_MDSTR, T_QMDSTR
+        if (type == T_QMDSTR) put_char(s, '"');
+        put_mdstr(s, d, (uint32_t)v);
+        if (type == T_QMDSTR) put_char(s, '"');
+        break;
+      }
+    }
+  } while (md_mode && ++e < m1);
 }
 
 // Emit pass: walks the set bits of `present`.  Descriptor and value of the NEXT field are fetched before
-// the current one is formatted, so their load latency hides behind the formatting work.
+// the current one is formatted, so their latency hides behind the formatting work.
 template <class S>
-__device__ __forceinline__ void run_fields(S& s, const Dev& d, int cls, int base, const EvCtx& c, uint64_t present,
+__device__ __forceinline__ void run_fields(S& s, const Dev& d, const uint32_t* a, int base, uint64_t present,
                                            unsigned long long* name_bytes) {
   if (!present) return;
   int f = __ffsll((long long)present) - 1;
   present &= present - 1;
   FieldDesc fd = g_fields.f[base + f];
-  uint64_t v = fd.type != T_NONE ? field_value(cls, f, c) : 0ull;
+  uint64_t v = slot_value(a, fd.voff, fd.vk);
   while (true) {
     const bool more = present != 0;
-    int fn = 0;
     FieldDesc fdn = fd;
     uint64_t vn = 0;
     if (more) {
-      fn = __ffsll((long long)present) - 1;
+      f = __ffsll((long long)present) - 1;
       present &= present - 1;
-      fdn = g_fields.f[base + fn];
-      vn = fdn.type != T_NONE ? field_value(cls, fn, c) : 0ull;
+      fdn = g_fields.f[base + f];
+      vn = slot_value(a, fdn.voff, fdn.vk);
     }
     s.words(g_fields.w + fd.off, fd.len);
     put_value(s, d, fd.type, v, name_bytes);
     if (!more) break;
-    f = fn; fd = fdn; v = vn;
+    fd = fdn; v = vn;
   }
 }
 
-// Size pass: the same fields as straight-line code.  Field types and literal lengths are compile-time
-// constants here, so each present field costs its value's digit count and one addition.
+// Size pass: the same fields as straight-line code.  Field types, literal lengths and value slots are
+// compile-time constants here, so each present field costs its value's digit count and one addition.
 template <int I> struct FieldInfo {
   static constexpr int type = kAllFields[I].type;
   static constexpr uint32_t len = (uint32_t)c_strlen(kAllFields[I].lit);
+  static constexpr uint32_t voff = kAllFields[I].voff;
+  static constexpr uint32_t vk = kAllFields[I].vk;
 };
-template <int CLS, int BASE, int F, int NF, class S>
-__device__ __forceinline__ void count_fields(S& s, const Dev& d, const EvCtx& c, uint64_t present, unsigned long long* name_bytes) {
+template <int BASE, int F, int NF, class S>
+__device__ __forceinline__ void count_fields(S& s, const Dev& d, const uint32_t* a, uint64_t present, unsigned long long* name_bytes) {
   if constexpr (F < NF) {
     if ((present >> F) & 1ull) {
       s.n += FieldInfo<BASE + F>::len;
-      if constexpr (FieldInfo<BASE + F>::type != T_NONE) put_value(s, d, FieldInfo<BASE + F>::type, field_value(CLS, F, c), name_bytes);
+      if constexpr (FieldInfo<BASE + F>::type != T_NONE)
+        put_value(s, d, FieldInfo<BASE + F>::type, slot_value(a, FieldInfo<BASE + F>::voff, FieldInfo<BASE + F>::vk), name_bytes);
     }
-    count_fields<CLS, BASE, F + 1, NF>(s, d, c, present, name_bytes);
+    count_fields<BASE, F + 1, NF>(s, d, a, present, name_bytes);
   }
 }
-template <int CLS, int BASE, int NF, class S>
-__device__ __forceinline__ void do_fields(S& s, const Dev& d, const EvCtx& c, uint64_t present, unsigned long long* name_bytes) {
-  if constexpr (S::kCounting) count_fields<CLS, BASE, 0, NF>(s, d, c, present, name_bytes);
-  else run_fields(s, d, CLS, BASE, c, present, name_bytes);
-}
-
 constexpr int kEventThreads = 128;
-static_assert(kEventThreads == kCtxStride, "scratch column stride");
 
 template <class S>
-__device__ __forceinline__ void format_event(S& s, const Dev& d, int cls, const uint8_t* r, uint64_t j, Tally& t, uint32_t* filt,
-                                             uint32_t* scratch, int32_t* ext) {
-  EvCtx c;
-  c.r = r; c.j = j; c.sm = scratch;
-  uint64_t present = 0;
+__device__ __forceinline__ void format_event(S& s, const Dev& d, int cls, uint32_t* a, uint64_t j, Tally& t, uint32_t* filt, int32_t* ext) {
   unsigned long long* nb = &t.name_bytes;
-  if (S::kCounting) {
-    // straight-line field code per class
-    switch (cls) {
-      case C_API: if (gather_api(d, r, c, &present, t, filt, true, 0)) { *ext = c.ext; do_fields<C_API, API_BASE, A_COUNT>(s, d, c, present, nb); } break;
-      case C_KERNEL: if (gather_kernel(d, r, c, &present, t, filt, true, 0)) { *ext = c.ext; do_fields<C_KERNEL, KERNEL_BASE, K_COUNT>(s, d, c, present, nb); } break;
-      case C_MEMCPY: if (gather_mem<C_MEMCPY>(d, r, c, &present, t, filt, true, 0)) { *ext = c.ext; do_fields<C_MEMCPY, MEM_BASE, M_COUNT>(s, d, c, present, nb); } break;
-      case C_MEMCPY2: if (gather_mem<C_MEMCPY2>(d, r, c, &present, t, filt, true, 0)) { *ext = c.ext; do_fields<C_MEMCPY2, MEM_BASE, M_COUNT>(s, d, c, present, nb); } break;
-      case C_MEMSET: if (gather_mem<C_MEMSET>(d, r, c, &present, t, filt, true, 0)) { *ext = c.ext; do_fields<C_MEMSET, MEM_BASE, M_COUNT>(s, d, c, present, nb); } break;
-      default: if (gather_op(d, j, c, &present, t)) do_fields<C_OP, OP_BASE, O_COUNT>(s, d, c, present, nb); break;
+  if constexpr (S::kCounting) {
+    uint64_t p;
+    switch (cls) {  // straight-line field code per class
+      case C_API: if ((p = gather_api(d, a, t, filt, true, ext))) count_fields<API_BASE, 0, A_COUNT>(s, d, a, p, nb); break;
+      case C_KERNEL: if ((p = gather_kernel(d, a, t, filt, true, ext))) count_fields<KERNEL_BASE, 0, K_COUNT>(s, d, a, p, nb); break;
+      case C_MEMCPY: if ((p = gather_mem<C_MEMCPY>(d, a, t, filt, true, ext))) count_fields<MEM_BASE, 0, M_COUNT>(s, d, a, p, nb); break;
+      case C_MEMCPY2: if ((p = gather_mem<C_MEMCPY2>(d, a, t, filt, true, ext))) count_fields<MEM_BASE, 0, M_COUNT>(s, d, a, p, nb); break;
+      case C_MEMSET: if ((p = gather_mem<C_MEMSET>(d, a, t, filt, true, ext))) count_fields<MEM_BASE, 0, M_COUNT>(s, d, a, p, nb); break;
+      default: if ((p = gather_op(d, j, a, t))) count_fields<OP_BASE, 0, O_COUNT>(s, d, a, p, nb); break;
     }
-    return;
+  } else {
+    uint64_t p;
+    int base;
+    switch (cls) {  // one copy of the field loop for all classes
+      case C_API: p = gather_api(d, a, t, filt, false, ext); base = API_BASE; break;
+      case C_KERNEL: p = gather_kernel(d, a, t, filt, false, ext); base = KERNEL_BASE; break;
+      case C_MEMCPY: p = gather_mem<C_MEMCPY>(d, a, t, filt, false, ext); base = MEM_BASE; break;
+      case C_MEMCPY2: p = gather_mem<C_MEMCPY2>(d, a, t, filt, false, ext); base = MEM_BASE; break;
+      case C_MEMSET: p = gather_mem<C_MEMSET>(d, a, t, filt, false, ext); base = MEM_BASE; break;
+      default: p = gather_op(d, j, a, t); base = OP_BASE; break;
+    }
+    run_fields(s, d, a, base, p, nb);
   }
-  int base = 0;
-  bool ok;
-  switch (cls) {
-    case C_API: ok = gather_api(d, r, c, &present, t, filt, false, *ext); base = API_BASE; break;
-    case C_KERNEL: ok = gather_kernel(d, r, c, &present, t, filt, false, *ext); base = KERNEL_BASE; break;
-    case C_MEMCPY: ok = gather_mem<C_MEMCPY>(d, r, c, &present, t, filt, false, *ext); base = MEM_BASE; break;
-    case C_MEMCPY2: ok = gather_mem<C_MEMCPY2>(d, r, c, &present, t, filt, false, *ext); base = MEM_BASE; break;
-    case C_MEMSET: ok = gather_mem<C_MEMSET>(d, r, c, &present, t, filt, false, *ext); base = MEM_BASE; break;
-    default: ok = gather_op(d, j, c, &present, t); base = OP_BASE; break;
-  }
-  if (ok) run_fields(s, d, cls, base, c, present, nb);
 }
 
 // 8-byte units of a record of each class (C_API .. C_MEMSET)
 __device__ __forceinline__ uint32_t class_units(int cls) {
   return cls == C_KERNEL ? 26u : cls == C_MEMCPY2 ? 12u : cls == C_API ? 5u : 11u;
 }
-constexpr int kRecStride = 27;  // 8-byte units per staged record: 26 for the longest record, odd so that 64-bit reads of the
-                                // 32 lanes fall in distinct banks
 
 // One thread per work item.  Work items are class-sorted (each class padded to a multiple of 32),
 // so a warp formats events of one shape.  WRITE = false: store the byte length; WRITE = true: write
-// the bytes at ev_off[event].  The emit pass first copies the 32 records of a warp into shared memory
-// with coalesced loads (lane = 8-byte unit of a record), so that the field loop reads record fields
-// at shared-memory latency instead of one cache line per lane.
+// the bytes at ev_off[event].  Either pass first copies the 32 records of a warp into shared memory
+// with coalesced loads (lane = 8-byte unit of a record); all later reads of record fields and of the
+// values computed from them are shared-memory reads at table-given offsets.
 template <bool WRITE>
-__global__ void __launch_bounds__(kEventThreads, WRITE ? 6 : 8) k_events(Dev d) {
-  __shared__ uint32_t s_ctx[X_COUNT * kEventThreads];
-  __shared__ uint64_t s_rec[WRITE ? kEventThreads * kRecStride : 1];
+__global__ void __launch_bounds__(kEventThreads, WRITE ? 7 : 8) k_events(Dev d) {
+  __shared__ uint64_t s_rec[kEventThreads * kRecStride];
+  __shared__ uint64_t s_park[WRITE ? 3 * kEventThreads : 1];
   __shared__ unsigned long long s_cnt[8];
-  if (threadIdx.x < 8) s_cnt[threadIdx.x] = 0;
-  __syncthreads();
+  if (!WRITE) {
+    if (threadIdx.x < 8) s_cnt[threadIdx.x] = 0;
+    __syncthreads();
+  }
   const uint64_t i = (uint64_t)blockIdx.x * kEventThreads + threadIdx.x;
   Tally t; t.x = 0; t.flow = 0; t.name_bytes = 0; t.ev = 0;
   uint32_t filt = 0;
@@ -1351,40 +1298,44 @@ __global__ void __launch_bounds__(kEventThreads, WRITE ? 6 : 8) k_events(Dev d) 
       if (size) {
         off = d.ev_off[ev];
         if (cls != C_OP) ext = d.ev_ext[ev];
-        if (off + size > d.out_cap) { atomicAdd(&d.counters->device_check, 1ull); size = 0; }
+        if (size < kMinEventBytes || off + size > d.out_cap) { atomicAdd(&d.counters->device_check, 1ull); size = 0; }
       }
-      if (!size) r = nullptr;
+      if (!size) { r = nullptr; cls = -1; }
     }
   }
-  if (WRITE) {
-    // stage this warp's records: every lane's class is the warp's class (or none)
+  {
+    // stage this warp's records: every lane's class is the warp's class (or none).  Asynchronous
+    // 8-byte copies, so all of a warp's record loads are in flight together and take no registers.
     const uint32_t lane = threadIdx.x & 31u, wbase = threadIdx.x & ~31u;
-    const int cls0 = __shfl_sync(0xffffffffu, cls, 0);
+    const int cls0 = __reduce_max_sync(0xffffffffu, cls);
     if (cls0 >= 0 && cls0 != C_OP) {
       const uint32_t nu = class_units(cls0), rpi = 32u / nu;
       const uint32_t sub = lane / nu, unit = lane - sub * nu;
       const unsigned long long mine = (unsigned long long)reinterpret_cast<uintptr_t>(r);
-#pragma unroll 4
+      const uint32_t sdst = (uint32_t)__cvta_generic_to_shared(&s_rec[(wbase + sub) * kRecStride + unit]);
       for (uint32_t k = 0; k < 32u; k += rpi) {
         const uint32_t rec = k + sub;
-        const uint64_t* src = reinterpret_cast<const uint64_t*>((uintptr_t)__shfl_sync(0xffffffffu, mine, rec & 31u));
-        if (sub < rpi && rec < 32u && src != nullptr) s_rec[(wbase + rec) * kRecStride + unit] = src[unit];
+        const unsigned long long src = __shfl_sync(0xffffffffu, mine, rec & 31u);
+        if (sub < rpi && rec < 32u && src != 0ull)
+          asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(sdst + k * (uint32_t)(kRecStride * 8)), "l"(src + 8ull * unit) : "memory");
       }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
       __syncwarp();
-      r = reinterpret_cast<const uint8_t*>(&s_rec[threadIdx.x * kRecStride]);
     }
   }
+  uint32_t* area = reinterpret_cast<uint32_t*>(&s_rec[threadIdx.x * kRecStride]);
   if (cls >= 0) {
     if (!WRITE) {
       CountSink2 s;
-      format_event(s, d, cls, r, j, t, &filt, &s_ctx[threadIdx.x], &ext);
+      format_event(s, d, cls, area, j, t, &filt, &ext);
       d.ev_size[ev] = filt ? 0u : s.n;
       if (cls != C_OP) d.ev_ext[ev] = ext;
-    } else if (size) {
+    } else {
       GlobalSink s;
-      s.init(d.out + off);
-      format_event(s, d, cls, r, j, t, &filt, &s_ctx[threadIdx.x], &ext);
-      s.finish();
+      s.init(d.out + off, size, &s_park[threadIdx.x]);
+      format_event(s, d, cls, area, j, t, &filt, &ext);
+      if (!s.finish(d.out + off, size)) atomicAdd(&d.counters->device_check, 1ull);
     }
   }
   if (!WRITE) {  // counters are tallied once, in the size pass
@@ -1454,25 +1405,28 @@ __global__ void k_span_collect(Dev d, SpanRec* out, unsigned int* n_out) {
 template <bool WRITE>
 __global__ void __launch_bounds__(kEventThreads) k_annotations(Dev d, const SpanRec* spans, uint32_t n, uint32_t* sizes,
                                                                const uint64_t* offs, uint64_t out_base) {
+  __shared__ uint32_t s_area[kEventThreads * 8];
+  __shared__ uint64_t s_park[WRITE ? 3 * kEventThreads : 1];
   const uint32_t i = blockIdx.x * kEventThreads + threadIdx.x;
   if (i >= n) return;
   const SpanRec r = spans[i];
   int64_t dur = r.end - r.start;
   if (dur < 0) dur = 0;
   unsigned long long nb = 0;
-  __shared__ uint32_t s_ctx[X_COUNT * kEventThreads];
-  EvCtx c;
-  c.r = nullptr; c.j = 0; c.sm = &s_ctx[threadIdx.x];
-  c.name = r.op_row < d.n_ops ? d.op_name[r.op_row] : 0xFFFFFFFFu; c.pid = r.device; c.tid = r.stream;
-  c.ts_rel = rel_ts(d, r.start - 1); c.dur = dur + 2; c.ext = r.op_id;
+  uint32_t* a = &s_area[threadIdx.x * 8];
+  s32(a, NS_NAME, r.op_row < d.n_ops ? d.op_name[r.op_row] : 0xFFFFFFFFu); s32(a, NS_PID, r.device); s32(a, NS_TID, r.stream);
+  s32(a, NS_EXT, (uint32_t)r.op_id); s64(a, NS_TS, (uint64_t)rel_ts(d, r.start - 1)); s64(a, NS_DUR, (uint64_t)(dur + 2));
   uint64_t p = (1ull << N_COUNT) - 1ull;
   if (r.op_id == 0) p &= ~((1ull << N_EXT) | (1ull << N_ARGS_CLOSE));
-  if (!WRITE) { CountSink2 s; count_fields<C_ANN, ANN_BASE, 0, N_COUNT>(s, d, c, p, &nb); sizes[i] = s.n; }
+  if (!WRITE) { CountSink2 s; count_fields<ANN_BASE, 0, N_COUNT>(s, d, a, p, &nb); sizes[i] = s.n; }
   else {
+    const uint32_t size = sizes[i];
+    uint8_t* dst = d.out + out_base + offs[i];
+    if (size < kMinEventBytes || out_base + offs[i] + size > d.out_cap) { atomicAdd(&d.counters->device_check, 1ull); return; }
     GlobalSink s;
-    s.init(d.out + out_base + offs[i]);
-    run_fields(s, d, C_ANN, ANN_BASE, c, p, &nb);
-    s.finish();
+    s.init(dst, size, &s_park[threadIdx.x]);
+    run_fields(s, d, a, ANN_BASE, p, &nb);
+    if (!s.finish(dst, size)) atomicAdd(&d.counters->device_check, 1ull);
   }
 }
 
