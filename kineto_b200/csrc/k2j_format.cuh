@@ -69,12 +69,14 @@ struct Lit {
   } while (0)
 
 // ------------------------------------------------------------------------------------------------
-// Sinks.  put(w, len): append the low `len` (1..4) bytes of w; bytes of w above `len` must be zero.
+// Sinks.  put(w, len) / put64(w, len): append the low `len` (1..4 / 0..8) bytes of w; bytes of w above
+// `len` must be zero.
 // ------------------------------------------------------------------------------------------------
 struct CountSink {
   static constexpr bool kCounting = true;
   uint32_t n = 0;
   K2J_HD void put(uint32_t, int len) { n += (uint32_t)len; }
+  K2J_HD void put64(uint64_t, uint32_t len) { n += len; }
   K2J_HD void skip(uint32_t len) { n += len; }
   template <int N> K2J_HD void lit(const Lit<N>&) { n += N; }
 };
@@ -85,6 +87,7 @@ struct StringSink {  // CPU test sink
   static constexpr bool kCounting = false;
   std::string s;
   void put(uint32_t w, int len) { for (int i = 0; i < len; i++) s += (char)((w >> (8 * i)) & 0xff); }
+  void put64(uint64_t w, uint32_t len) { for (uint32_t i = 0; i < len; i++) s += (char)((w >> (8 * i)) & 0xff); }
   void skip(uint32_t) {}
   template <int N> void lit(const Lit<N>& l) {
     for (int i = 0; i < N; i++) s += (char)((l.w[i / 4] >> (8 * (i % 4))) & 0xff);
@@ -92,10 +95,7 @@ struct StringSink {  // CPU test sink
 };
 #endif
 
-template <class S> K2J_HD void put8(S& s, uint64_t a, int len) {  // len 1..8, bytes above len zero
-  if (len > 4) { s.put((uint32_t)a, 4); s.put((uint32_t)(a >> 32), len - 4); }
-  else s.put((uint32_t)a, len);
-}
+template <class S> K2J_HD void put8(S& s, uint64_t a, int len) { s.put64(a, (uint32_t)len); }  // len 1..8, bytes above len zero
 template <class S> K2J_HD void put_char(S& s, char c) { s.put((uint32_t)(unsigned char)c, 1); }
 
 // ------------------------------------------------------------------------------------------------
@@ -252,60 +252,80 @@ template <class S> K2J_HD void put_nonfinite(S& s, double v) {
   else s.put(0x00666E69u, 3);                            // "inf"
 }
 
-// Emits `count` digits of `dec` (which has `nd` digits) starting at digit index `from` (0 = most
-// significant).
-template <class S> K2J_HD void put_digit_range(S& s, uint64_t dec, int nd, int from, int count) {
-  if (count <= 0) return;
-  if (S::kCounting) { s.skip((uint32_t)count); return; }
-  // dec < 10^17: chars = [h][m8][l8] zero-padded to 17; first significant at 17 - nd.
-  uint64_t hi = dec / 100000000ull;
-  uint32_t lo = (uint32_t)(dec - hi * 100000000ull);
-  uint64_t top = hi / 100000000ull;
-  uint32_t mid = (uint32_t)(hi - top * 100000000ull);
-  uint64_t a1 = ascii8(mid), a2 = ascii8(lo);
-  uint64_t a0 = 0x30ull + top;  // single char
-  int pos = 17 - nd + from;     // index into the 17-char string
-  while (count > 0) {
-    // fetch up to 4 chars starting at pos
-    uint32_t w = 0; int got = 0;
-    while (got < 4 && got < count) {
-      int p = pos + got;
-      uint32_t ch = p == 0 ? (uint32_t)a0 : (p <= 8 ? (uint32_t)((a1 >> (8 * (p - 1))) & 0xff)
-                                                    : (uint32_t)((a2 >> (8 * (p - 9))) & 0xff));
-      w |= ch << (8 * got);
-      got++;
-    }
-    s.put(w, got);
-    pos += got; count -= got;
+// The 17 zero-padded decimal digits of dec (< 10^17) as ASCII in three registers: characters 0..7,
+// 8..15 and 16.  Pieces of the digit string are then cut out with shifts, eight characters at a time.
+struct Digits17 { uint64_t x0, x1, x2; };
+K2J_HD Digits17 digits17(uint64_t dec) {
+  const uint64_t hi = dec / 100000000ull;
+  const uint32_t lo = (uint32_t)(dec - hi * 100000000ull);
+  const uint32_t top = (uint32_t)(hi / 100000000ull);
+  const uint32_t mid = (uint32_t)(hi - (uint64_t)top * 100000000ull);
+  const uint64_t a1 = ascii8(mid), a2 = ascii8(lo);
+  Digits17 D;
+  D.x0 = (uint64_t)(0x30u + top) | (a1 << 8);
+  D.x1 = (a1 >> 56) | (a2 << 8);
+  D.x2 = a2 >> 56;
+  return D;
+}
+// the 8 characters starting at character `o` (0..16); characters past the 17th read as zero bytes
+K2J_HD uint64_t digits_at(const Digits17& D, int o) {
+  const int wi = o >> 3, sh = (o & 7) * 8;
+  const uint64_t a = wi == 0 ? D.x0 : wi == 1 ? D.x1 : D.x2;
+  const uint64_t b = wi == 0 ? D.x1 : wi == 1 ? D.x2 : 0ull;
+  return (a >> sh) | ((b << 1) << (63 - sh));
+}
+template <class S> K2J_HD void put_digits(S& s, const Digits17& D, int o, int n) {
+  while (n > 0) {
+    const int m = n < 8 ? n : 8;
+    s.put64(digits_at(D, o) & (~0ull >> (8 * (8 - m))), (uint32_t)m);
+    o += m; n -= m;
+  }
+}
+template <class S> K2J_HD void put_zeros(S& s, int n) {
+  while (n > 0) {
+    const int m = n < 8 ? n : 8;
+    s.put64(0x3030303030303030ull >> (8 * (8 - m)), (uint32_t)m);
+    n -= m;
   }
 }
 
-// fmt::format("{}", v) for finite v.
+// fmt::format("{}", v) for finite v: the shortest digits that round-trip, fixed notation when the decimal
+// exponent lies in [-4, 16), exponent notation otherwise.
 template <class S> K2J_HD void put_double(S& s, double v) {
-  DoubleLayout L = double_layout(v);
+  const DoubleLayout L = double_layout(v);
   if (L.neg) put_char(s, '-');
   if (L.zero) { put_char(s, '0'); return; }
   const int nd = L.nd, e10 = L.e10;
+  if (S::kCounting) {
+    if (e10 < -4 || e10 >= 16) {
+      const int a = e10 < 0 ? -e10 : e10;
+      s.skip((uint32_t)(nd + (nd > 1 ? 1 : 0) + 2 + (a < 100 ? 2 : 3)));
+    } else if (e10 >= nd - 1) s.skip((uint32_t)(e10 + 1));
+    else if (e10 >= 0) s.skip((uint32_t)(nd + 1));
+    else s.skip((uint32_t)(nd + 1 - e10));
+    return;
+  }
+  const Digits17 D = digits17(L.dec);
+  const int z = 17 - nd;  // leading zeros of the padded string
   if (e10 < -4 || e10 >= 16) {
-    put_digit_range(s, L.dec, nd, 0, 1);
-    if (nd > 1) { put_char(s, '.'); put_digit_range(s, L.dec, nd, 1, nd - 1); }
-    int a = e10 < 0 ? -e10 : e10;
+    s.put64(digits_at(D, z) & 0xffull, 1);
+    if (nd > 1) { put_char(s, '.'); put_digits(s, D, z + 1, nd - 1); }
+    const int a = e10 < 0 ? -e10 : e10;
     s.put(0x65u | ((e10 < 0 ? 0x2Du : 0x2Bu) << 8), 2);  // 'e' then sign
     if (a < 10) put_char(s, '0');
     put_small(s, (uint32_t)a);
     return;
   }
   if (e10 >= nd - 1) {
-    put_digit_range(s, L.dec, nd, 0, nd);
-    for (int i = 0; i < e10 - (nd - 1); i++) put_char(s, '0');
+    put_digits(s, D, z, nd);
+    put_zeros(s, e10 - (nd - 1));
   } else if (e10 >= 0) {
-    put_digit_range(s, L.dec, nd, 0, e10 + 1);
+    put_digits(s, D, z, e10 + 1);
     put_char(s, '.');
-    put_digit_range(s, L.dec, nd, e10 + 1, nd - e10 - 1);
+    put_digits(s, D, z + e10 + 1, nd - e10 - 1);
   } else {
-    s.put(0x2E30u, 2);  // "0."
-    for (int i = 0; i < -e10 - 1; i++) put_char(s, '0');
-    put_digit_range(s, L.dec, nd, 0, nd);
+    s.put64(0x303030302E30ull & (~0ull >> (8 * (7 + e10))), (uint32_t)(1 - e10));  // "0." and -e10 - 1 zeros
+    put_digits(s, D, z, nd);
   }
 }
 // TypedMetadataJson.h:172-178: finite values bare, non-finite values quoted.
