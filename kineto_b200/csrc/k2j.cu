@@ -591,6 +591,7 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
   }
   if (d.n_ext_all) { k_build_corr<<<(uint32_t)((d.n_ext_all + 255) / 256), 256, 0, s>>>(d, own_begin, own_end); c->launches++; }
   if (d.n_join_ops) { k_build_ops<<<(uint32_t)((d.n_join_ops + 255) / 256), 256, 0, s>>>(d); c->launches++; }
+  if (d.n_ext_all) { k_resolve_corr<<<(corr_cap + 255) / 256, 256, 0, s>>>(d); c->launches++; }
   K2J_CUDA(c, cudaGetLastError());
   K2J_CUDA(c, cudaEventRecord(c->ev[2], s));
 

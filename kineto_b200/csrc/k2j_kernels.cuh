@@ -840,15 +840,29 @@ __device__ __forceinline__ bool out_of_range(const Dev& d, int64_t ts, int64_t d
 // linkedActivity(int32_t correlationId, cpuCorrelationMap_) (GenericActivityProfiler.cpp:397-408):
 // the id is sign-extended before the lookup while keys were stored zero-extended, so ids >= 2^31
 // never match; the external id must equal a CPU-op id exactly as a 64-bit value.
+// k_resolve_corr does the two dependent lookups once per table entry and leaves the linked op's id
+// (or 0) in the entry's low half, so that an event needs a single probe.
+__global__ void k_resolve_corr(Dev d) {
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i > d.corr_mask) return;
+  const unsigned long long e = d.corr_tab[i];
+  if (e == 0) return;
+  const int64_t ext = (int64_t)d.ext_all[(uint32_t)e - 1u].external_id;
+  uint32_t id = 0;
+  if (ext == (int64_t)(int32_t)ext && tab_find(d.op_tab, d.op_mask, (uint32_t)(int32_t)ext) != 0xFFFFFFFFu)
+    id = (uint32_t)(int32_t)ext;  // the linked op's correlationId() is the key it was found under
+  d.corr_tab[i] = (e & 0xFFFFFFFF00000000ull) | id;
+}
 __device__ __forceinline__ bool linked_op(const Dev& d, uint32_t corr, int32_t* op_id) {
-  if (corr & 0x80000000u) return false;
-  const uint32_t idx = tab_find(d.corr_tab, d.corr_mask, corr);
-  if (idx == 0xFFFFFFFFu) return false;
-  const int64_t ext = (int64_t)d.ext_all[idx].external_id;
-  if (ext != (int64_t)(int32_t)ext) return false;
-  if (tab_find(d.op_tab, d.op_mask, (uint32_t)(int32_t)ext) == 0xFFFFFFFFu) return false;
-  *op_id = (int32_t)ext;  // the linked op's correlationId() is the key it was found under
-  return true;
+  if ((corr & 0x80000000u) || d.corr_tab == nullptr) return false;
+  uint32_t i = hash32(corr) & d.corr_mask;
+  for (uint32_t probes = 0; probes <= d.corr_mask; probes++) {
+    const unsigned long long e = d.corr_tab[i];
+    if (e == 0) return false;  // empty, or correlation id 0 without a link
+    if ((uint32_t)(e >> 32) == corr) { *op_id = (int32_t)(uint32_t)e; return (uint32_t)e != 0; }
+    i = (i + 1) & d.corr_mask;
+  }
+  return false;
 }
 
 // GenericActivityProfiler::handleGpuActivity's user-annotation step (GenericActivityProfiler.cpp:424-434)
