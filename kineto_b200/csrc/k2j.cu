@@ -63,7 +63,7 @@ struct k2j_ctx {
   std::vector<uint64_t> h_buf_off, h_buf_valid;
   std::vector<uint32_t> h_buf_chunk_base;
   DevBuf d_buf_off, d_buf_valid, d_buf_chunk_base;
-  DevBuf esc_name, esc_md, esc_name_len, esc_md_len;
+  DevBuf esc_name, esc_md, esc_name_len, esc_md_len, walk_cnt;
   DevBuf slot_code, exit_map, chunk_entry, chunk_cnt, chunk_base, scan_sums, scan_totals;
   DevBuf ds_tab, span_key, span_nstart, span_end, span_nfirst, span_row, span_out, span_cnt, ann_size, ann_off;
   DevBuf sort_keys[2], sort_vals[2], sort_hist, sort_base, sort_rank;
@@ -263,7 +263,7 @@ void k2j_destroy(k2j_ctx* c) {
                     &c->op_flow, &c->op_flowt, &c->op_mdoff, &c->op_md})
     in->own.release();
   for (DevBuf* b : {&c->d_props, &c->d_buf_off, &c->d_buf_valid, &c->d_buf_chunk_base, &c->esc_name, &c->esc_md,
-                    &c->esc_name_len, &c->esc_md_len, &c->slot_code, &c->exit_map, &c->chunk_entry, &c->chunk_cnt,
+                    &c->esc_name_len, &c->esc_md_len, &c->walk_cnt, &c->slot_code, &c->exit_map, &c->chunk_entry, &c->chunk_cnt,
                     &c->chunk_base, &c->scan_sums, &c->scan_totals, &c->ds_tab, &c->span_key, &c->span_nstart, &c->span_end, &c->span_nfirst, &c->span_row,
                     &c->span_out, &c->span_cnt, &c->ann_size, &c->ann_off, &c->sort_keys[0], &c->sort_keys[1], &c->sort_vals[0],
                     &c->sort_vals[1], &c->sort_hist, &c->sort_base, &c->sort_rank, &c->tid_tab, &c->corr_tab, &c->user_tab, &c->op_tab,
@@ -460,16 +460,16 @@ k2j_status k2j_segment(k2j_ctx* c, k2j_segment_info* info) {
   if (nch) {
     K2J_CUDA(c, c->slot_code.reserve(c->cupti_bytes / 8 + 64));
     K2J_CUDA(c, c->exit_map.reserve((size_t)nch * 32));
+    K2J_CUDA(c, c->walk_cnt.reserve((size_t)nch * 32 * 3 * 4));
     K2J_CUDA(c, c->chunk_entry.reserve(nch));
     K2J_CUDA(c, c->chunk_cnt.reserve((size_t)nch * C_NCOL * 4));
     K2J_CUDA(c, c->chunk_base.reserve((size_t)nch * C_NCOL * 8));
-    d.slot_code = c->slot_code.as<uint8_t>(); d.exit_map = c->exit_map.as<uint8_t>();
+    d.slot_code = c->slot_code.as<uint8_t>(); d.exit_map = c->exit_map.as<uint8_t>(); d.walk_cnt = c->walk_cnt.as<uint32_t>();
     d.chunk_entry = c->chunk_entry.as<uint8_t>(); d.chunk_cnt = c->chunk_cnt.as<uint32_t>();
     d.chunk_base = c->chunk_base.as<uint64_t>();
     k_seg_chunks<<<seg_blocks, kSegWarps * 32, 0, s>>>(d);
     k_seg_compose<<<c->n_buf, 256, 0, s>>>(d);
-    k_seg_count<<<seg_blocks, kSegWarps * 32, 0, s>>>(d);
-    c->launches += 3;
+    c->launches += 2;
     K2J_CUDA(c, cudaGetLastError());
     k2j_status st = run_scan(c, d.chunk_cnt, nch, C_NCOL, d.chunk_base, c->scan_totals.as<uint64_t>(), &c->launches);
     if (st) return st;

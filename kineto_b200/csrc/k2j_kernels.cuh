@@ -6,8 +6,8 @@
 //   k_escape_pool    per distinct string: JSON-sanitised copies (name flavour, metadata flavour)
 //   k_seg_chunks     per 4 KiB chunk of every CUPTI buffer: record length per 8-byte slot, and for
 //                    each of the 26 possible entry slots the slot at which a walk leaves the chunk
-//   k_seg_compose    per buffer: chains the exit maps -> true entry slot of every chunk
-//   k_seg_count      per chunk: walk from the true entry, count records per class
+//                    and the records per class it meets
+//   k_seg_compose    per buffer: chains the exit maps -> true entry slot of every chunk -> its counts
 //   k_scan_*         exclusive scans (chunk counts, later event sizes)
 //   k_seg_write      per chunk: walk again, fill the per-class work lists, insert
 //                    EXTERNAL_CORRELATION records into the correlation tables (last writer wins)
@@ -81,6 +81,7 @@ struct Dev {
   const uint64_t* buf_off; const uint64_t* buf_valid; const uint32_t* buf_chunk_base; uint32_t n_buf, n_chunks;
   uint8_t* slot_code;      // per 8-byte slot of the CUPTI bytes
   uint8_t* exit_map;       // n_chunks x 32
+  uint32_t* walk_cnt;      // n_chunks x 32 x 3: packed class counts of the walk from each entry slot
   uint8_t* chunk_entry;    // n_chunks
   uint32_t* chunk_cnt;     // C_NCOL columns x n_chunks
   uint64_t* chunk_base;    // C_NCOL columns x n_chunks (exclusive scan of chunk_cnt)
@@ -238,7 +239,15 @@ __device__ __forceinline__ ChunkGeom chunk_geom(const Dev& d, uint32_t chunk) {
 
 constexpr int kSegWarps = 8;
 
-// One warp per chunk: slot codes and exit map.
+// Class column of a slot code for the count matrix (C_EXT_USER counts as C_EXT; see C_USER).
+__device__ __forceinline__ uint32_t code_class(uint32_t code) {
+  const uint32_t cls = code >> 5;
+  return cls == (uint32_t)C_EXT_USER ? (uint32_t)C_EXT : cls;
+}
+
+// One warp per chunk: slot codes; then lane e (< 26) walks the chunk as if it were entered at slot e
+// and leaves behind where that walk exits (the exit map) and how many records of each class it met
+// (nine 8-bit counts packed in three words: a 4 KiB chunk holds at most 170 records).
 __global__ void __launch_bounds__(kSegWarps * 32) k_seg_chunks(Dev d) {
   __shared__ uint8_t s_code[kSegWarps][kChunkSlots];
   const uint32_t w = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -265,24 +274,35 @@ __global__ void __launch_bounds__(kSegWarps * 32) k_seg_chunks(Dev d) {
   }
   __syncwarp();
   uint8_t code = kEntryNone;
+  uint32_t c0 = 0, c1 = 0, c2 = 0;  // counts of columns 0-3, 4-7, 8
   if (lane < kMaxEntry) {
     uint32_t pos = lane;
     code = 0;
     // Bounded: every step advances by at least 3 slots.
     for (int it = 0; it < kChunkSlots; it++) {
-      if (pos >= g.nvalid) { code = g.last ? (pos == g.nvalid ? 0 : kExitTerminate) : (uint8_t)(pos - g.nvalid); break; }
-      const uint32_t n = s_code[w][pos] & 31u;
-      if (n == 0) { code = kExitTerminate; break; }
+      if (pos >= g.nvalid) { code = g.last ? 0 : (uint8_t)(pos - g.nvalid); break; }
+      const uint32_t sc = s_code[w][pos];
+      const uint32_t n = sc & 31u;
+      if (n == 0 || (g.last && pos + n > g.nvalid)) { code = kExitTerminate; c1 += 1u << 24; break; }  // column 7: unexpected
+      const uint32_t cls = code_class(sc);
+      c0 += cls < 4u ? 1u << (8 * cls) : 0u;
+      c1 += cls >= 4u ? 1u << (8 * (cls - 4u)) : 0u;              // columns 4 (memset) and 5 (external correlation)
+      c1 += cls != (uint32_t)C_EXT ? 1u << 16 : 0u;                // column 6: records that own an event slot
+      c2 += (sc >> 5) == (uint32_t)C_EXT_USER ? 1u : 0u;           // column 8
       pos += n;
     }
   }
   d.exit_map[(uint64_t)chunk * 32 + lane] = code;
+  uint32_t* cw = d.walk_cnt + ((uint64_t)chunk * 32 + lane) * 3;
+  cw[0] = c0; cw[1] = c1; cw[2] = c2;
 }
 
-// One block per buffer: chain the exit maps.
+// One block per buffer: chain the exit maps to the true entry slot of every chunk, then copy the counts
+// of the walk that started there into the count matrix.
 __global__ void __launch_bounds__(256) k_seg_compose(Dev d) {
   constexpr int kTile = 1024;
   __shared__ uint8_t s_map[kTile * 32];
+  __shared__ uint8_t s_ent[kTile];
   __shared__ uint32_t s_entry;
   const uint32_t b = blockIdx.x;
   const uint32_t c0 = d.buf_chunk_base[b], c1 = d.buf_chunk_base[b + 1];
@@ -297,7 +317,7 @@ __global__ void __launch_bounds__(256) k_seg_compose(Dev d) {
     if (threadIdx.x == 0) {
       uint32_t e = s_entry;
       for (uint32_t c = 0; c < n; c++) {
-        d.chunk_entry[t0 + c] = (uint8_t)e;
+        s_ent[c] = (uint8_t)e;
         if (e != kEntryNone) {
           const uint8_t x = s_map[c * 32 + e];
           e = (x >= kMaxEntry) ? kEntryNone : x;
@@ -305,20 +325,21 @@ __global__ void __launch_bounds__(256) k_seg_compose(Dev d) {
       }
       s_entry = e;
     }
-  }
-}
-
-// Walk helper: lane 0 of a warp walks one chunk from its true entry.  `visit(pos, code)` is called per
-// record that starts in the chunk.  Returns false if the walk ended on an unknown kind.
-template <class F>
-__device__ __forceinline__ void walk_chunk(const uint8_t* codes, uint32_t entry, const ChunkGeom& g, F visit) {
-  uint32_t pos = entry;
-  for (int it = 0; it < kChunkSlots && pos < g.nvalid; it++) {
-    const uint32_t code = codes[pos];
-    const uint32_t n = code & 31u;
-    if (n == 0 || (g.last && pos + n > g.nvalid)) { visit(pos, 0u); return; }  // unknown kind or overrun
-    visit(pos, code);
-    pos += n;
+    __syncthreads();
+    for (uint32_t c = threadIdx.x; c < n; c += blockDim.x) {
+      const uint32_t e = s_ent[c];
+      d.chunk_entry[t0 + c] = (uint8_t)e;
+      uint32_t w0 = 0, w1 = 0, w2 = 0;
+      if (e != kEntryNone) {
+        const uint32_t* cw = d.walk_cnt + ((uint64_t)(t0 + c) * 32 + e) * 3;
+        w0 = cw[0]; w1 = cw[1]; w2 = cw[2];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; i++) d.chunk_cnt[(uint64_t)i * d.n_chunks + t0 + c] = (w0 >> (8 * i)) & 0xffu;
+#pragma unroll
+      for (int i = 0; i < 4; i++) d.chunk_cnt[(uint64_t)(4 + i) * d.n_chunks + t0 + c] = (w1 >> (8 * i)) & 0xffu;
+      d.chunk_cnt[(uint64_t)8 * d.n_chunks + t0 + c] = w2;
+    }
   }
 }
 
@@ -327,41 +348,12 @@ __device__ __forceinline__ void load_codes(const Dev& d, const ChunkGeom& g, uin
   __syncwarp();
 }
 
-__global__ void __launch_bounds__(kSegWarps * 32) k_seg_count(Dev d) {
-  __shared__ uint8_t s_code[kSegWarps][kChunkSlots];
-  const uint32_t w = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t chunk = blockIdx.x * kSegWarps + w;
-  if (chunk >= d.n_chunks) return;
-  const ChunkGeom g = chunk_geom(d, chunk);
-  const uint32_t entry = d.chunk_entry[chunk];
-  uint32_t cnt[C_NCOL];
-#pragma unroll
-  for (int i = 0; i < C_NCOL; i++) cnt[i] = 0;
-  if (entry != kEntryNone) {
-    load_codes(d, g, s_code[w], lane);
-    if (lane == 0) {
-      walk_chunk(s_code[w], entry, g, [&](uint32_t, uint32_t code) {
-        if (code == 0) { cnt[C_UNEXPECTED]++; return; }
-        uint32_t cls = code >> 5;
-        cnt[C_USER] += (cls == (uint32_t)C_EXT_USER);
-        if (cls == (uint32_t)C_EXT_USER) cls = C_EXT;
-#pragma unroll
-        for (int i = 0; i < C_NCLASS; i++) cnt[i] += (cls == (uint32_t)i);
-        cnt[C_EVENTS] += (cls != (uint32_t)C_EXT);
-      });
-    }
-  }
-  if (lane == 0) {
-#pragma unroll
-    for (int i = 0; i < C_NCOL; i++) d.chunk_cnt[(uint64_t)i * d.n_chunks + chunk] = cnt[i];
-  }
-}
-
+// One warp per chunk.  Lane 0 walks the chunk from its true entry and notes where records start; the
+// warp then ranks the records within their class (32 at a time, by ballot) and writes the per-class
+// work lists and the compacted EXTERNAL_CORRELATION records.
 __global__ void __launch_bounds__(kSegWarps * 32) k_seg_write(Dev d) {
   __shared__ uint8_t s_code[kSegWarps][kChunkSlots];
   __shared__ uint16_t s_pos[kSegWarps][kChunkSlots / 3 + 2];
-  __shared__ uint16_t s_rank[kSegWarps][kChunkSlots / 3 + 2];
-  __shared__ uint16_t s_evrank[kSegWarps][kChunkSlots / 3 + 2];
   __shared__ uint32_t s_n[kSegWarps];
   const uint32_t w = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t chunk = blockIdx.x * kSegWarps + w;
@@ -371,43 +363,50 @@ __global__ void __launch_bounds__(kSegWarps * 32) k_seg_write(Dev d) {
   const ChunkGeom g = chunk_geom(d, chunk);
   load_codes(d, g, s_code[w], lane);
   if (lane == 0) {
-    uint32_t cnt[C_NCLASS];
-#pragma unroll
-    for (int i = 0; i < C_NCLASS; i++) cnt[i] = 0;
-    uint32_t n = 0, ev = 0;
-    walk_chunk(s_code[w], entry, g, [&](uint32_t pos, uint32_t code) {
-      if (code == 0) return;
-      uint32_t cls = code >> 5;
-      if (cls == (uint32_t)C_EXT_USER) cls = C_EXT;
-      uint32_t r = 0;
-#pragma unroll
-      for (int i = 0; i < C_NCLASS; i++) if (cls == (uint32_t)i) r = cnt[i]++;
-      s_pos[w][n] = (uint16_t)(pos | (cls << 12));
-      s_rank[w][n] = (uint16_t)r;
-      s_evrank[w][n] = (uint16_t)ev;
-      ev += (cls != (uint32_t)C_EXT);
-      n++;
-    });
+    uint32_t n = 0, pos = entry;
+    for (int it = 0; it < kChunkSlots && pos < g.nvalid; it++) {  // bounded: every step advances by at least 3 slots
+      const uint32_t len = s_code[w][pos] & 31u;
+      if (len == 0 || (g.last && pos + len > g.nvalid)) break;    // unknown kind or overrun: the walk ends
+      s_pos[w][n++] = (uint16_t)pos;
+      pos += len;
+    }
     s_n[w] = n;
   }
   __syncwarp();
   const uint32_t n = s_n[w];
-  const uint64_t ev_base = d.n_ops + d.chunk_base[(uint64_t)C_EVENTS * d.n_chunks + chunk];
-  for (uint32_t i = lane; i < n; i += 32) {
-    const uint32_t pos = s_pos[w][i] & 0xfffu, cls = s_pos[w][i] >> 12;
-    const uint64_t slot = g.slot0 + pos;
-    if (cls == (uint32_t)C_EXT) {
-      const uint8_t* r = d.cupti + slot * 8;
-      ExtRec e;
-      e.external_kind = *reinterpret_cast<const uint32_t*>(r + 4);
-      e.external_id = *reinterpret_cast<const uint64_t*>(r + 8);
-      e.correlation_id = *reinterpret_cast<const uint32_t*>(r + 16);
-      d.ext_local[d.chunk_base[(uint64_t)C_EXT * d.n_chunks + chunk] + s_rank[w][i]] = e;
-    } else {
-      const uint64_t dst = d.cls_begin[cls] + d.chunk_base[(uint64_t)cls * d.n_chunks + chunk] + s_rank[w][i];
-      d.work_slot[dst] = (uint32_t)slot;
-      d.work_ev[dst] = (uint32_t)(ev_base + s_evrank[w][i]);
+  uint64_t base[C_NCLASS];
+#pragma unroll
+  for (int c = 0; c < C_NCLASS; c++) base[c] = d.chunk_base[(uint64_t)c * d.n_chunks + chunk] + (c == C_EXT ? 0 : d.cls_begin[c]);
+  uint64_t ev_base = d.n_ops + d.chunk_base[(uint64_t)C_EVENTS * d.n_chunks + chunk];
+  const uint32_t lt = (1u << lane) - 1u;
+  for (uint32_t i0 = 0; i0 < n; i0 += 32) {
+    const uint32_t i = i0 + lane;
+    const bool on = i < n;
+    const uint32_t pos = on ? s_pos[w][i] : 0u;
+    const uint32_t cls = on ? code_class(s_code[w][pos]) : 0xffu;
+    const uint32_t evm = __ballot_sync(0xffffffffu, on && cls != (uint32_t)C_EXT);
+    uint64_t dst = 0;
+#pragma unroll
+    for (int c = 0; c < C_NCLASS; c++) {
+      const uint32_t m = __ballot_sync(0xffffffffu, cls == (uint32_t)c);
+      if (cls == (uint32_t)c) dst = base[c] + __popc(m & lt);
+      base[c] += __popc(m);
     }
+    if (on) {
+      const uint64_t slot = g.slot0 + pos;
+      if (cls == (uint32_t)C_EXT) {
+        const uint8_t* r = d.cupti + slot * 8;
+        ExtRec e;
+        e.external_kind = *reinterpret_cast<const uint32_t*>(r + 4);
+        e.external_id = *reinterpret_cast<const uint64_t*>(r + 8);
+        e.correlation_id = *reinterpret_cast<const uint32_t*>(r + 16);
+        d.ext_local[dst] = e;
+      } else {
+        d.work_slot[dst] = (uint32_t)slot;
+        d.work_ev[dst] = (uint32_t)(ev_base + __popc(evm & lt));
+      }
+    }
+    ev_base += __popc(evm);
   }
 }
 
