@@ -559,7 +559,8 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
   d.user_tab = c->user_tab.as<unsigned long long>(); d.user_mask = corr_cap - 1;
   d.op_tab = c->op_tab.as<unsigned long long>(); d.op_mask = op_cap - 1;
   K2J_CUDA(c, cudaMemsetAsync(d.corr_tab, 0, (size_t)corr_cap * 8, s));
-  K2J_CUDA(c, cudaMemsetAsync(d.user_tab, 0, (size_t)corr_cap * 8, s));
+  // the user-annotation table is only written and read when CUSTOM1 correlation records exist
+  if (c->have_global_join || totals[C_USER] > 0) K2J_CUDA(c, cudaMemsetAsync(d.user_tab, 0, (size_t)corr_cap * 8, s));
   K2J_CUDA(c, cudaMemsetAsync(d.op_tab, 0, (size_t)op_cap * 8, s));
   const uint32_t tid_cap = std::max<uint32_t>(16384, pow2_at_least(4ull * c->n_tid));
   K2J_CUDA(c, c->tid_tab.reserve((size_t)tid_cap * 8));

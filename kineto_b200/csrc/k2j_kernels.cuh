@@ -852,16 +852,21 @@ __global__ void k_resolve_corr(Dev d) {
     id = (uint32_t)(int32_t)ext;  // the linked op's correlationId() is the key it was found under
   d.corr_tab[i] = (e & 0xFFFFFFFF00000000ull) | id;
 }
-__device__ __forceinline__ bool linked_op(const Dev& d, uint32_t corr, int32_t* op_id) {
-  if ((corr & 0x80000000u) || d.corr_tab == nullptr) return false;
+// The first probe is split off so that callers can issue its load early, next to other loads.
+__device__ __forceinline__ unsigned long long linked_op_peek(const Dev& d, uint32_t corr) {
+  if ((corr & 0x80000000u) || d.corr_tab == nullptr) return 0ull;
+  return d.corr_tab[hash32(corr) & d.corr_mask];
+}
+__device__ __forceinline__ void linked_op(const Dev& d, uint32_t corr, unsigned long long first, int32_t* op_id) {
+  if ((corr & 0x80000000u) || d.corr_tab == nullptr) return;
   uint32_t i = hash32(corr) & d.corr_mask;
+  unsigned long long e = first;
   for (uint32_t probes = 0; probes <= d.corr_mask; probes++) {
-    const unsigned long long e = d.corr_tab[i];
-    if (e == 0) return false;  // empty, or correlation id 0 without a link
-    if ((uint32_t)(e >> 32) == corr) { *op_id = (int32_t)(uint32_t)e; return (uint32_t)e != 0; }
+    if (e == 0) return;  // empty, or correlation id 0 without a link
+    if ((uint32_t)(e >> 32) == corr) { *op_id = (int32_t)(uint32_t)e; return; }
     i = (i + 1) & d.corr_mask;
+    e = d.corr_tab[i];
   }
-  return false;
 }
 
 // GenericActivityProfiler::handleGpuActivity's user-annotation step (GenericActivityProfiler.cpp:424-434)
@@ -929,6 +934,14 @@ __device__ __forceinline__ uint64_t gather_api(const Dev& d, uint32_t* a, Tally&
   const uint64_t st = a64(a, 8), en = a64(a, 16);
   const uint32_t corr = a32(a, AR_CORR);
   const bool driver = kind == K_DRIVER;
+  // issue the independent table loads together, before the checks that consume them
+  int32_t tid = (int32_t)a32(a, 28);
+  const uint32_t tid_slot = hash32((uint32_t)tid) & d.tid_mask;
+  const unsigned long long tid_first = d.tid_tab[tid_slot];
+  const unsigned long long corr_first = counting ? linked_op_peek(d, corr) : 0ull;
+  const uint32_t ntab = driver ? d.n_dr : d.n_rt;
+  const bool named = cbid < ntab;
+  const uint32_t name_id = named ? (driver ? d.dr_names : d.rt_names)[cbid] : 0u;
   bool flow_start;
   if (!driver) {
     // CuptiCbidRegistry.cpp:127-161 blocklist; :57-122 flow-starting callbacks
@@ -942,19 +955,22 @@ __device__ __forceinline__ uint64_t gather_api(const Dev& d, uint32_t* a, Tally&
   }
   const int64_t ts = conv_ts(d, st), dur = conv_dur(d, st, en);
   if (out_of_range(d, ts, dur)) { *filt = 2; return 0; }
-  int32_t tid = (int32_t)a32(a, 28);
   {  // resourceInfo_.find({processId(), tid}), CuptiActivityProfiler.cpp:315-319
-    const uint32_t idx = tab_find(d.tid_tab, d.tid_mask, (uint32_t)tid);
+    uint32_t idx = 0xFFFFFFFFu, i = tid_slot;
+    unsigned long long e = tid_first;
+    for (uint32_t probes = 0; probes <= d.tid_mask && e != 0; probes++) {
+      if ((uint32_t)(e >> 32) == (uint32_t)tid) { idx = (uint32_t)e - 1u; break; }
+      i = (i + 1) & d.tid_mask;
+      e = d.tid_tab[i];
+    }
     if (idx != 0xFFFFFFFFu) tid = idx < d.n_tid_pairs ? d.tid_pairs[2 * idx + 1] : (int32_t)d.op_resource[idx - d.n_tid_pairs];
   }
   int32_t ext = *ext_io;
-  if (counting) { linked_op(d, corr, &ext); *ext_io = ext; }
+  if (counting) { linked_op(d, corr, corr_first, &ext); *ext_io = ext; }
   const bool has_ext = ext != 0;
-  const uint32_t ntab = driver ? d.n_dr : d.n_rt;
-  const bool named = cbid < ntab;
   s64(a, AS_TS, (uint64_t)rel_ts(d, ts)); s64(a, AS_DUR, (uint64_t)(dur < 0 ? 0 : dur));
   s32(a, AS_PID, (uint32_t)d.pid); s32(a, AS_TID, (uint32_t)abs_tid(tid)); s32(a, AS_EXT, (uint32_t)ext);
-  s32(a, AS_NAME, named ? (driver ? d.dr_names : d.rt_names)[cbid] : 0u);
+  s32(a, AS_NAME, name_id);
   uint64_t p = 0;
   auto on = [&](int f) { p |= 1ull << f; };
   on(driver ? A_HEAD_DR : A_HEAD_RT); on(named ? A_NAME : A_INVALID);
@@ -980,6 +996,9 @@ __device__ __forceinline__ void occupancy_metrics(const Dev& d, uint32_t dev, bo
   occ.blockLimitSharedMem = 0; occ.blockLimitBlocks = 0; occ.blockLimitBarriers = 0; occ.allocatedRegistersPerBlock = 0;
   occ.allocatedSharedMemPerBlock = 0; occ.partitionedGCConfig = PARTITIONED_GC_OFF;
   float occupancy = -1.0f;  // OccupancyMetrics default (DeviceProperties.h:54)
+#ifdef K2J_NO_OCC
+  have_dev = false;
+#endif
   if (have_dev) {
     const DevProps& dp = d.props[dev];
     const float blocks_per_sm = sm_count != 0 ? __fdiv_rn(__int2float_rn(grid_prod), __int2float_rn(sm_count)) : -1.0f;
@@ -1006,6 +1025,7 @@ __device__ __forceinline__ void occupancy_metrics(const Dev& d, uint32_t dev, bo
 
 // GpuActivity<Kernel> (libkineto/src/CuptiActivity.h:499-576)
 __device__ __forceinline__ uint64_t gather_kernel(const Dev& d, uint32_t* a, Tally& t, uint32_t* filt, bool counting, int32_t* ext_io) {
+  const unsigned long long corr_first = counting ? linked_op_peek(d, a32(a, KR_CORR)) : 0ull;  // issued early
   const uint64_t st = a64(a, 16), en = a64(a, 24);
   const int64_t ts = conv_ts(d, st), dur = conv_dur(d, st, en);
   if (out_of_range(d, ts, dur)) { *filt = 2; return 0; }
@@ -1015,7 +1035,7 @@ __device__ __forceinline__ uint64_t gather_kernel(const Dev& d, uint32_t* a, Tal
   const int32_t ssm = (int32_t)a32(a, 76), dsm = (int32_t)a32(a, 80);
   const uint32_t regs = a32(a, 4) >> 16;  // registersPerThread: 16 bits at byte 6
   int32_t ext = *ext_io;
-  if (counting) { linked_op(d, corr, &ext); *ext_io = ext; }
+  if (counting) { linked_op(d, corr, corr_first, &ext); *ext_io = ext; }
   const bool has_ext = ext != 0;
   // blocksPerSm / warpsPerSm (DeviceProperties.cpp:161-174): 32-bit wrapping products, single-precision
   // arithmetic without contraction.
@@ -1057,7 +1077,7 @@ __device__ __forceinline__ uint64_t gather_mem(const Dev& d, uint32_t* a, Tally&
   constexpr int g = CLS == C_MEMCPY2 ? 8 : 0;  // byte shift of the trailing fields in the peer-to-peer layout
   const uint32_t corr = a32(a, CLS == C_MEMCPY2 ? 60 : 44);
   int32_t ext = *ext_io;
-  if (counting) { linked_op(d, corr, &ext); *ext_io = ext; }
+  if (counting) { linked_op(d, corr, linked_op_peek(d, corr), &ext); *ext_io = ext; }
   const bool has_ext = ext != 0;
   const uint32_t w1 = a32(a, 4);
   const uint64_t node = a64(a, 64 + g);
