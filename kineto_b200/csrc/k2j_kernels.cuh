@@ -996,9 +996,6 @@ __device__ __forceinline__ void occupancy_metrics(const Dev& d, uint32_t dev, bo
   occ.blockLimitSharedMem = 0; occ.blockLimitBlocks = 0; occ.blockLimitBarriers = 0; occ.allocatedRegistersPerBlock = 0;
   occ.allocatedSharedMemPerBlock = 0; occ.partitionedGCConfig = PARTITIONED_GC_OFF;
   float occupancy = -1.0f;  // OccupancyMetrics default (DeviceProperties.h:54)
-#ifdef K2J_NO_OCC
-  have_dev = false;
-#endif
   if (have_dev) {
     const DevProps& dp = d.props[dev];
     const float blocks_per_sm = sm_count != 0 ? __fdiv_rn(__int2float_rn(grid_prod), __int2float_rn(sm_count)) : -1.0f;
