@@ -40,6 +40,9 @@ FALLBACK_HBM_GBS = 6650.0
 EMIT_TRAFFIC_PER_OUT_BYTE = 1.353
 
 
+E2E_DEPTH = 2  # contexts alternating in the end-to-end leg
+
+
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -200,7 +203,7 @@ def run_ours(args):
 
     exchange_events = []
 
-    def exchange_and_emit():
+    def exchange_and_emit(ctx=ctx, stream=stream):
         """segment -> (all-gather join keys) -> emit; returns the result dict."""
         if world == 1:
             return ctx.run()
@@ -241,7 +244,10 @@ def run_ours(args):
     ms_exchange = sum(a.elapsed_time(b) for a, b in exchange_events[-args.steps:]) / args.steps if world > 1 else 0.0
     n_records = res["n_records"] + len(trace.op_start)
 
-    # ---- end to end: pinned host buffers in, pinned host buffer out ----
+    # ---- end to end: pinned host buffers in, pinned host buffers out ----
+    # Two contexts on two streams alternate: while the text of one step travels to the host, the next
+    # step's inputs travel to the device and are formatted.  Every step still uploads all of its
+    # inputs and downloads all of its output inside the timed region.
     host = {}
     for k in api.K2J.ARRAYS:
         a = np.ascontiguousarray(getattr(trace, k))
@@ -249,26 +255,40 @@ def run_ours(args):
         a = a.view(np.int64) if a.dtype == np.uint64 else (a.view(np.int32) if a.dtype == np.uint32 else a)
         host[k] = torch.from_numpy(a).pin_memory()
     h2d = sum(t.numel() * t.element_size() for t in host.values())
-    out_host = torch.empty(res["out_bytes"] + 4096, dtype=torch.uint8).pin_memory()
+    lanes = []
+    for i in range(E2E_DEPTH):
+        s_i = stream if i == 0 else torch.cuda.Stream(dev)
+        c_i = ctx if i == 0 else api.K2J(local, s_i.cuda_stream)
+        lanes.append((c_i, s_i, torch.empty(res["out_bytes"] + 4096, dtype=torch.uint8).pin_memory()))
 
-    def e2e_step():
-        ctx.load(trace, host)
-        r = exchange_and_emit()
-        ctx.copy_output(out_host)
+    def e2e_step(i):
+        c_i, s_i, out_i = lanes[i % E2E_DEPTH]
+        with torch.cuda.stream(s_i):
+            c_i.synchronize()  # the copy this lane started E2E_DEPTH steps ago has landed
+            c_i.load(trace, host)
+            r = exchange_and_emit(c_i, s_i)
+            c_i.copy_output_async(out_i)
         return r
 
-    for _ in range(max(1, args.warmup - 1)):
-        e2e_step()
+    def e2e_drain():
+        for c_i, _, _ in lanes:
+            c_i.synchronize()
+
+    for i in range(max(E2E_DEPTH, args.warmup - 1)):
+        e2e_step(i)
+    e2e_drain()
     barrier()
     t0 = time.perf_counter()
-    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    f0.record(stream)
-    for _ in range(args.steps):
-        r2 = e2e_step()
-    f1.record(stream)
+    for i in range(args.steps):
+        r2 = e2e_step(i)
+    e2e_drain()
+    torch.cuda.synchronize()
+    ms_e2e = 1e3 * (time.perf_counter() - t0)  # several streams: host clock around fully drained work
     barrier()
-    ms_e2e = max(f0.elapsed_time(f1), 1e3 * (time.perf_counter() - t0))
-    assert bytes(out_host[:64].numpy().tobytes()).startswith(b'\n  {\n    "ph": "X"')
+    for _, _, out_i in lanes[:min(E2E_DEPTH, args.steps)]:
+        assert bytes(out_i[:64].numpy().tobytes()).startswith(b'\n  {\n    "ph": "X"')
+    for c_i, _, _ in lanes[1:]:
+        c_i.close()
 
     # ---- max over ranks ----
     if world > 1:
@@ -301,7 +321,10 @@ def run_ours(args):
             "dtype": "u8", "data": "synthetic", "config": config(args, world), "clocks": clocks,
             "e2e": {"value": total_records * args.steps / (ms_e2e * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": total_h2d, "d2h_bytes_per_step": total_out,
-                    "output_gb_per_s": total_out * args.steps / (ms_e2e * 1e-3) / 1e9},
+                    "output_gb_per_s": total_out * args.steps / (ms_e2e * 1e-3) / 1e9,
+                    "contexts": E2E_DEPTH,
+                    "note": "%d contexts alternate so that one step's download overlaps the next step's upload and "
+                            "kernels; every step moves all of its bytes; host clock around the drained region" % E2E_DEPTH},
             "gpu_launches": launches,
             "output_gb_per_s": total_out * args.steps / (ms * 1e-3) / 1e9,
             "output_bytes_per_step": total_out,

@@ -224,6 +224,14 @@ k2j_status k2j_exclusive_scan_u32_noalloc(int device, void* stream, const uint32
 k2j_status k2j_output(k2j_ctx* ctx, const void** device_ptr, uint64_t* n_bytes);
 /* Copies the text to host memory (pinned memory makes the copy asynchronous up to its final wait). */
 k2j_status k2j_copy_output(k2j_ctx* ctx, void* host_dst, uint64_t capacity);
+/* The same copy, only enqueued on the context's stream: it returns before the bytes have arrived.
+ * k2j_synchronize (or any later call that waits on the stream) completes it; the context's output must
+ * not be overwritten by another run before that.  A caller with two contexts can so keep the copy of
+ * one trace running while the next trace is uploaded and formatted (no reference counterpart: the
+ * reference writes its file synchronously, libkineto/src/output_json.cpp:1098-1107). */
+k2j_status k2j_copy_output_async(k2j_ctx* ctx, void* host_dst, uint64_t capacity);
+/* Waits for everything enqueued on the context's stream. */
+k2j_status k2j_synchronize(k2j_ctx* ctx);
 
 /* Library version string. */
 const char* k2j_version(void);

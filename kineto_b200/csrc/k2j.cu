@@ -713,4 +713,20 @@ k2j_status k2j_copy_output(k2j_ctx* c, void* dst, uint64_t cap) {
   return K2J_OK;
 }
 
+k2j_status k2j_copy_output_async(k2j_ctx* c, void* dst, uint64_t cap) {
+  if (!c) return K2J_ERR_INVALID_ARGUMENT;
+  if (!c->ran) return fail(c, K2J_ERR_STATE, "no completed run");
+  if (cap < c->out_bytes || (!dst && c->out_bytes)) return fail(c, K2J_ERR_INVALID_ARGUMENT, "destination too small");
+  K2J_CUDA(c, cudaSetDevice(c->device));
+  if (c->out_bytes) K2J_CUDA(c, cudaMemcpyAsync(dst, c->out.p, c->out_bytes, cudaMemcpyDeviceToHost, c->stream));
+  return K2J_OK;
+}
+
+k2j_status k2j_synchronize(k2j_ctx* c) {
+  if (!c) return K2J_ERR_INVALID_ARGUMENT;
+  K2J_CUDA(c, cudaSetDevice(c->device));
+  K2J_CUDA(c, cudaStreamSynchronize(c->stream));
+  return K2J_OK;
+}
+
 }  // extern "C"
