@@ -46,7 +46,7 @@ E2E_DEPTH = 2  # contexts alternating in the end-to-end leg
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--launches", type=int, default=1_000_000, help="kernel launches per GPU")
@@ -225,9 +225,9 @@ def run_ours(args):
     for _ in range(args.warmup):
         res = exchange_and_emit()
     sampler = ClockSampler(local)
-    barrier()
     if rank == 0:
-        sampler.start()
+        sampler.start()  # before the barrier: its set-up must not delay rank 0 inside the other ranks' timed region
+    barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     stage = {k: 0.0 for k in ("ms_segment", "ms_join", "ms_size", "ms_scan", "ms_emit")}

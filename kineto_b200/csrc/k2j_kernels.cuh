@@ -523,36 +523,41 @@ constexpr uint32_t kMinEventBytes = 16;
 
 struct GlobalSink {
   static constexpr bool kCounting = false;
+  static constexpr int kParkStride = 128;  // = threads per block of the kernels that use the sink
   uint64_t lo; uint32_t sh;
   uint32_t wo;            // byte offset (from base) of the 8-byte word being filled
-  uint32_t c8, lim8;      // words stored singly: 0 <= wo - c8 < lim8 and outside the block range
-  uint32_t c32, lim32;    // words of whole blocks: 0 <= wo - c32 < lim32
+  uint32_t w0;            // offset of the event's first word (0, 8, 16 or 24)
+  uint32_t c32, lim32;    // blocks lying wholly inside the event: 0 <= offset - c32 < lim32
   uint8_t* base;          // 32-byte aligned
-  uint64_t* park;         // this thread's column of the parking area: word k at park[k * kParkStride]
-  static constexpr int kParkStride = 128;  // = threads per block of the kernels that use the sink
+  uint64_t* park;         // this thread's column of the parking area: word k of the open block at park[k * kParkStride]
   __device__ __forceinline__ void init(uint8_t* dst, uint32_t size, uint64_t* park_column) {
     const uint32_t phase32 = (uint32_t)(reinterpret_cast<uintptr_t>(dst) & 31u), phase = phase32 & 7u;
     base = dst - phase32; sh = 8u * phase; lo = 0; park = park_column;
-    wo = phase32 & ~7u;
-    const uint32_t end = phase32 + size;
-    c8 = wo + 8u; lim8 = (end & ~7u) - c8;           // strictly between the first word and the word holding the end
+    wo = w0 = phase32 & ~7u;
     c32 = phase32 ? 32u : 0u;
-    const uint32_t last_blk = end & ~31u;
+    const uint32_t last_blk = (phase32 + size) & ~31u;
     lim32 = last_blk > c32 ? last_blk - c32 : 0u;
     const uint64_t w = ((kEventTail8 >> 1) >> (63u - sh)) | (kEventHead8 << sh);
     if (phase < 4u) *reinterpret_cast<uint64_t*>(base + wo) = w;
     else *reinterpret_cast<uint32_t*>(base + wo + 4) = (uint32_t)(w >> 32);
   }
+  // The fourth word of a block is complete.  Normally the block lies inside the event and leaves as one
+  // 256-bit store; the event's first block, when the event starts inside it, leaves word by word
+  // (its first word was written by init).
+  __device__ __forceinline__ void block_out(uint64_t t) {
+    if ((wo - c32) < lim32) {
+      const uint64_t a = park[0], b = park[kParkStride], c = park[2 * kParkStride];
+      asm volatile("st.global.v4.b64 [%0], {%1, %2, %3, %4};" ::"l"(base + (wo & ~31u)), "l"(a), "l"(b), "l"(c), "l"(t) : "memory");
+    } else {
+      for (uint32_t o = w0 + 8u; o < 24u + 8u; o += 8u)
+        *reinterpret_cast<uint64_t*>(base + (wo & ~31u) + o) = o == 24u ? t : park[(o >> 3) * kParkStride];
+    }
+  }
   // a completed word `t` at offset `wo`; `on`: this lane really has one
   __device__ __forceinline__ void word_out(uint64_t t, bool on) {
-    const bool blk = on && (wo - c32) < lim32;
     const uint32_t k = (wo >> 3) & 3u;
-    if (blk && k != 3u) park[k * kParkStride] = t;
-    if (blk && k == 3u) {
-      const uint64_t w0 = park[0], w1 = park[kParkStride], w2 = park[2 * kParkStride];
-      asm volatile("st.global.v4.b64 [%0], {%1, %2, %3, %4};" ::"l"(base + (wo & ~31u)), "l"(w0), "l"(w1), "l"(w2), "l"(t) : "memory");
-    }
-    if (on && !blk && (wo - c8) < lim8) *reinterpret_cast<uint64_t*>(base + wo) = t;
+    if (on && k != 3u) park[k * kParkStride] = t;
+    if (on && k == 3u) block_out(t);
   }
   __device__ __forceinline__ void put8w(uint64_t w) {  // append 8 bytes
     word_out(lo | (w << sh), true);
@@ -585,8 +590,12 @@ struct GlobalSink {
     const uint32_t rem = len & 7u;
     if (rem) put64(nxt & (~0ull >> (8u * (8u - rem))), rem);
   }
-  // Returns false if the byte count differs from the size the event was given.
+  // Writes what is left: the complete words of the open (last) block, then the word holding the event's
+  // end.  Returns false if the byte count differs from the size the event was given.
   __device__ __forceinline__ bool finish(const uint8_t* dst, uint32_t size) {
+    const uint32_t blk = wo & ~31u;
+    for (uint32_t o = blk == 0u ? w0 + 8u : blk; o < wo; o += 8u)   // the event's very first word was written by init
+      *reinterpret_cast<uint64_t*>(base + o) = park[((o >> 3) & 3u) * kParkStride];
     const uint32_t e = sh >> 3;
     if (e) {
       const uint64_t t = lo | (0x20200Aull << sh);  // the next event begins "\n  "
