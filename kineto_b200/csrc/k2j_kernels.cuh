@@ -1377,12 +1377,17 @@ __global__ void __launch_bounds__(kEventThreads, WRITE ? 7 : 8) k_events(Dev d) 
       if (!s.finish(d.out + off, size)) atomicAdd(&d.counters->device_check, 1ull);
     }
   }
-  if (!WRITE) {  // counters are tallied once, in the size pass
-    if (t.x) atomicAdd(&s_cnt[0], (unsigned long long)t.x);
-    if (t.flow) atomicAdd(&s_cnt[1], (unsigned long long)t.flow);
-    if (filt == 2) atomicAdd(&s_cnt[2], 1ull);
-    if (filt == 1) atomicAdd(&s_cnt[3], 1ull);
-    if (t.name_bytes) atomicAdd(&s_cnt[4], t.name_bytes);
+  if (!WRITE) {  // counters are tallied once, in the size pass: warp sums, then one shared atomic per warp
+    const uint32_t wx = __reduce_add_sync(0xffffffffu, t.x), wf = __reduce_add_sync(0xffffffffu, t.flow);
+    const uint32_t wo = __reduce_add_sync(0xffffffffu, filt == 2u ? 1u : 0u), wb = __reduce_add_sync(0xffffffffu, filt == 1u ? 1u : 0u);
+    const uint32_t wn = __reduce_add_sync(0xffffffffu, (uint32_t)t.name_bytes);  // a name is far shorter than 2^27 bytes
+    if ((threadIdx.x & 31u) == 0) {
+      if (wx) atomicAdd(&s_cnt[0], (unsigned long long)wx);
+      if (wf) atomicAdd(&s_cnt[1], (unsigned long long)wf);
+      if (wo) atomicAdd(&s_cnt[2], (unsigned long long)wo);
+      if (wb) atomicAdd(&s_cnt[3], (unsigned long long)wb);
+      if (wn) atomicAdd(&s_cnt[4], (unsigned long long)wn);
+    }
     __syncthreads();
     if (threadIdx.x == 0) {
       if (s_cnt[0]) atomicAdd(&d.counters->x_events, s_cnt[0]);
