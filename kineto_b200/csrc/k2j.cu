@@ -63,7 +63,7 @@ struct k2j_ctx {
   std::vector<uint64_t> h_buf_off, h_buf_valid;
   std::vector<uint32_t> h_buf_chunk_base;
   DevBuf d_buf_off, d_buf_valid, d_buf_chunk_base;
-  DevBuf esc_name, esc_md, esc_name_len, esc_md_len, walk_cnt;
+  DevBuf esc_name, esc_md, esc_name_len, esc_md_len, walk_cnt, need_corr, need_op;
   DevBuf slot_code, exit_map, chunk_entry, chunk_cnt, chunk_base, scan_sums, scan_totals;
   DevBuf ds_tab, span_key, span_nstart, span_end, span_nfirst, span_row, span_out, span_cnt, ann_size, ann_off;
   DevBuf sort_keys[2], sort_vals[2], sort_hist, sort_base, sort_rank;
@@ -263,7 +263,7 @@ void k2j_destroy(k2j_ctx* c) {
                     &c->op_flow, &c->op_flowt, &c->op_mdoff, &c->op_md})
     in->own.release();
   for (DevBuf* b : {&c->d_props, &c->d_buf_off, &c->d_buf_valid, &c->d_buf_chunk_base, &c->esc_name, &c->esc_md,
-                    &c->esc_name_len, &c->esc_md_len, &c->walk_cnt, &c->slot_code, &c->exit_map, &c->chunk_entry, &c->chunk_cnt,
+                    &c->esc_name_len, &c->esc_md_len, &c->walk_cnt, &c->need_corr, &c->need_op, &c->slot_code, &c->exit_map, &c->chunk_entry, &c->chunk_cnt,
                     &c->chunk_base, &c->scan_sums, &c->scan_totals, &c->ds_tab, &c->span_key, &c->span_nstart, &c->span_end, &c->span_nfirst, &c->span_row,
                     &c->span_out, &c->span_cnt, &c->ann_size, &c->ann_off, &c->sort_keys[0], &c->sort_keys[1], &c->sort_vals[0],
                     &c->sort_vals[1], &c->sort_hist, &c->sort_base, &c->sort_rank, &c->tid_tab, &c->corr_tab, &c->user_tab, &c->op_tab,
@@ -589,6 +589,20 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
     K2J_CUDA(c, cudaMemsetAsync(d.span_nstart, 0, (size_t)span_cap * 8, s));
     K2J_CUDA(c, cudaMemsetAsync(d.span_end, 0, (size_t)span_cap * 8, s));
     K2J_CUDA(c, cudaMemsetAsync(d.span_nfirst, 0, (size_t)span_cap * 8, s));
+  }
+  d.need_corr = nullptr; d.need_op = nullptr;
+  if (c->have_global_join && d.n_ext_all > 3 * std::max<uint64_t>(1, totals[C_EXT])) {
+    // Four or more shards' worth of keys: only those this shard's events can look up enter its tables
+    // (see k_mark_corr).  Below that the marking pass costs more than the inserts it saves.
+    const uint32_t corr_bits = std::max<uint32_t>(1u << 20, pow2_at_least(16 * std::max<uint64_t>(1, n_gpu_events)));
+    const uint32_t op_bits = corr_bits;
+    K2J_CUDA(c, c->need_corr.reserve(corr_bits / 8));
+    K2J_CUDA(c, c->need_op.reserve(op_bits / 8));
+    d.need_corr = c->need_corr.as<uint32_t>(); d.need_corr_mask = corr_bits - 1;
+    d.need_op = c->need_op.as<uint32_t>(); d.need_op_mask = op_bits - 1;
+    K2J_CUDA(c, cudaMemsetAsync(d.need_corr, 0, corr_bits / 8, s));
+    K2J_CUDA(c, cudaMemsetAsync(d.need_op, 0, op_bits / 8, s));
+    if (d.ops_begin) { k_mark_corr<<<(uint32_t)((d.ops_begin + 255) / 256), 256, 0, s>>>(d); c->launches++; }
   }
   if (d.n_ext_all) { k_build_corr<<<(uint32_t)((d.n_ext_all + 255) / 256), 256, 0, s>>>(d, own_begin, own_end); c->launches++; }
   if (d.n_join_ops) { k_build_ops<<<(uint32_t)((d.n_join_ops + 255) / 256), 256, 0, s>>>(d); c->launches++; }

@@ -94,6 +94,9 @@ struct Dev {
   // the array the tables are built from (ext_all: the same array, or all shards' arrays gathered)
   ExtRec* ext_local; const ExtRec* ext_all; uint64_t n_ext_all;
   const int32_t* join_op_ids; uint64_t n_join_ops;  // CPU-op ids the join sees (local or gathered)
+  // sharded runs: bit sets (by hash) of the correlation ids this shard's events carry and of the CPU-op ids
+  // the matching records name; keys outside them are not inserted.  nullptr: insert everything.
+  uint32_t* need_corr; uint32_t need_corr_mask; uint32_t* need_op; uint32_t need_op_mask;
   // join tables: 64-bit entries (key << 32 | value + 1), 0 = empty
   unsigned long long* corr_tab; uint32_t corr_mask;
   unsigned long long* user_tab; uint32_t user_mask;
@@ -425,11 +428,35 @@ __global__ void k_build_tids(Dev d) {
   }
   if (!tab_insert_min(d.tid_tab, d.tid_mask, key, (uint32_t)i)) atomicAdd(&d.counters->device_check, 1ull);
 }
+__device__ __forceinline__ bool bit_test(const uint32_t* bits, uint32_t mask, uint32_t key) {
+  const uint32_t h = hash32(key ^ 0x9E3779B9u) & mask;
+  return (bits[h >> 5] >> (h & 31u)) & 1u;
+}
+__device__ __forceinline__ void bit_set(uint32_t* bits, uint32_t mask, uint32_t key) {
+  const uint32_t h = hash32(key ^ 0x9E3779B9u) & mask;
+  atomicOr(&bits[h >> 5], 1u << (h & 31u));
+}
+// Sharded runs: marks the correlation id of every GPU-side record of this shard.  With the gathered
+// arrays of W shards each rank would otherwise insert W times its own share of keys into its tables,
+// although its events can only ever look up their own correlation ids.
+__global__ void k_mark_corr(Dev d) {
+  const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= d.ops_begin) return;
+  int cls = 0;
+#pragma unroll
+  for (int c = 1; c < C_EXT; c++) if (i >= d.cls_begin[c]) cls = c;
+  if (i - d.cls_begin[cls] >= d.cls_count[cls]) return;  // padding
+  const uint8_t* r = d.cupti + (uint64_t)d.work_slot[i] * 8;
+  const int off = cls == C_API ? 32 : cls == C_KERNEL ? 92 : cls == C_MEMCPY2 ? 60 : 44;
+  bit_set(d.need_corr, d.need_corr_mask, *reinterpret_cast<const uint32_t*>(r + off));
+}
 // CPU-op id -> position (last writer wins): activityMap_[id] = op, GenericActivityProfiler.cpp:262.
 __global__ void k_build_ops(Dev d) {
   const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= d.n_join_ops) return;
-  if (!tab_insert(d.op_tab, d.op_mask, (uint32_t)d.join_op_ids[i], (uint32_t)i)) atomicAdd(&d.counters->device_check, 1ull);
+  const uint32_t id = (uint32_t)d.join_op_ids[i];
+  if (d.need_op != nullptr && !bit_test(d.need_op, d.need_op_mask, id)) return;
+  if (!tab_insert(d.op_tab, d.op_mask, id, (uint32_t)i)) atomicAdd(&d.counters->device_check, 1ull);
 }
 // correlation id -> index of the winning EXTERNAL_CORRELATION record (handleCorrelationActivity,
 // CuptiActivityProfiler.cpp:290-302).  `count_invalid`: only the shard that owns a record counts it.
@@ -438,9 +465,16 @@ __global__ void k_build_corr(Dev d, uint64_t own_begin, uint64_t own_end) {
   if (i >= d.n_ext_all) return;
   const ExtRec e = d.ext_all[i];
   bool ok = true;
-  if (e.external_kind == 3u) ok = tab_insert(d.corr_tab, d.corr_mask, e.correlation_id, (uint32_t)i);
-  else if (e.external_kind == 4u) { ok = tab_insert(d.user_tab, d.user_mask, e.correlation_id, (uint32_t)i); atomicAdd(&d.counters->n_user, 1ull); }
-  else if (i >= own_begin && i < own_end) atomicAdd(&d.counters->invalid_external_correlation, 1ull);
+  if (e.external_kind == 3u) {
+    if (d.need_corr != nullptr) {
+      if (!bit_test(d.need_corr, d.need_corr_mask, e.correlation_id)) return;
+      if ((int64_t)e.external_id == (int64_t)(int32_t)e.external_id) bit_set(d.need_op, d.need_op_mask, (uint32_t)e.external_id);
+    }
+    ok = tab_insert(d.corr_tab, d.corr_mask, e.correlation_id, (uint32_t)i);
+  } else if (e.external_kind == 4u) {
+    atomicAdd(&d.counters->n_user, 1ull);
+    if (d.need_corr == nullptr) ok = tab_insert(d.user_tab, d.user_mask, e.correlation_id, (uint32_t)i);  // spans: single-shard runs only
+  } else if (i >= own_begin && i < own_end) atomicAdd(&d.counters->invalid_external_correlation, 1ull);
   if (!ok) atomicAdd(&d.counters->device_check, 1ull);
 }
 
