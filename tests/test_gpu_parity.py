@@ -175,11 +175,12 @@ def test_exclusive_scan_entry_point(n):
         ctx.close()
 
 
-def test_sharded_runs_concatenate_to_the_whole():
+@pytest.mark.parametrize("n_shards", [3, 5])
+def test_sharded_runs_concatenate_to_the_whole(n_shards):
     """Size-independent property at the benchmark's full size: processing contiguous buffer ranges
     separately, with the join arrays gathered from all of them, gives exactly the bytes of one run
     over the whole trace (events are emitted in record order and depend only on the record and the
-    join)."""
+    join).  With five shards the gathered keys pass through the per-shard key filter."""
     import torch
     from kineto_b200 import api
     n = 1_000_000
@@ -195,10 +196,10 @@ def test_sharded_runs_concatenate_to_the_whole():
         nb = t.n_buffers
         parts = []
         bt = t.buftab.reshape(-1, 2)
-        cuts = [0, nb // 3, 2 * nb // 3, nb]
-        op_cuts = [0, n // 4, n // 2, n]
+        cuts = [nb * i // n_shards for i in range(n_shards + 1)]
+        op_cuts = [0] + [n * (i + 1) // (n_shards + 1) for i in range(n_shards - 1)] + [n]
         infos = []
-        ctxs = [api.K2J(0) for _ in range(3)]
+        ctxs = [api.K2J(0) for _ in range(n_shards)]
         try:
             for i, c in enumerate(ctxs):
                 sub = tf.Trace(**{attr: getattr(t, attr) for _, attr, _ in tf._SECTIONS})
@@ -225,8 +226,6 @@ def test_sharded_runs_concatenate_to_the_whole():
         finally:
             for c in ctxs:
                 c.close()
-        ops_parts = [p[:c_res] for p, c_res in zip(parts, [None] * 3)]
-        del ops_parts
         # CPU-op events come first in every shard: reorder to [all ops][all gpu events]
         ops_txt = b"".join(p[:c.result["ops_bytes"]] for p, c in zip(parts, ctxs))
         gpu_txt = b"".join(p[c.result["ops_bytes"]:] for p, c in zip(parts, ctxs))

@@ -69,3 +69,24 @@ def test_two_gloo_ranks_reproduce_the_whole_trace(tmp_path):
     # the join really crosses shards: most kernels of shard 0 are linked to ops of shard 1 and vice versa
     alone, _ = helpers.run_port(shards[0])
     assert alone != outs[0]
+
+
+def _uneven_main(rank, port, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(WORLD))
+    dist.init_process_group("gloo", rank=rank, world_size=WORLD)
+    n_ext, n_ops = (5, 0) if rank == 0 else (8, 7)   # ragged: different record counts, an odd id count, an empty side
+    ext = torch.arange(n_ext * 2, dtype=torch.int64) + 1000 * rank
+    ops = torch.arange(n_ops, dtype=torch.int32) + 100 * rank
+    ext_all, ops_all, own_begin = sharding.gather_join_keys(ext, ops, rank, WORLD, dist)
+    want_ext = torch.cat([torch.arange(10, dtype=torch.int64), torch.arange(16, dtype=torch.int64) + 1000])
+    want_ops = torch.arange(7, dtype=torch.int32) + 100
+    ok = torch.equal(ext_all, want_ext) and torch.equal(ops_all, want_ops) and own_begin == (0 if rank == 0 else 5)
+    np.save(os.path.join(tmp, "ok%d.npy" % rank), np.array([int(ok)]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_join_key_exchange_with_ragged_shards(tmp_path):
+    port = 31500 + (os.getpid() % 2000)
+    mp.spawn(_uneven_main, args=(port, str(tmp_path)), nprocs=WORLD, join=True)
+    assert all(int(np.load(str(tmp_path / ("ok%d.npy" % r)))[0]) == 1 for r in range(WORLD))
