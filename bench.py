@@ -37,7 +37,7 @@ UNIT = "records/s"
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one k_events<true> launch divided by the JSON bytes
 # it wrote, from the ncu capture summarised in profiles/ (None until a capture exists).
-EMIT_TRAFFIC_PER_OUT_BYTE = 1.353
+EMIT_TRAFFIC_PER_OUT_BYTE = 1.036  # dram read+write of the emit launch per output byte (ncu, profiles/event_kernels_kernel_launches_100k.txt)
 
 
 E2E_DEPTH = 2  # contexts alternating in the end-to-end leg
