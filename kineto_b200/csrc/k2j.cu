@@ -68,7 +68,7 @@ struct k2j_ctx {
   DevBuf ds_tab, span_key, span_nstart, span_end, span_nfirst, span_row, span_out, span_cnt, ann_size, ann_off;
   DevBuf sort_keys[2], sort_vals[2], sort_hist, sort_base, sort_rank;
   DevBuf tid_tab, corr_tab, user_tab, op_tab, work_slot, work_ev, ev_size, ev_off, ev_ext, out, counters;
-  uint64_t* h_totals = nullptr;   // pinned: C_NCOL column totals, then the byte total
+  uint64_t* h_totals = nullptr;   // pinned, 16 words: [0, C_NCOL) column totals, 10 text bytes, 11 bytes of CPU-op text, 12 annotation bytes, 13 sort, 14 scan entry point
   Counters* h_counters = nullptr; // pinned
   cudaEvent_t ev[8]{};
   uint64_t out_bytes = 0;
@@ -217,11 +217,11 @@ k2j_status order_annotations(k2j_ctx* c, uint32_t span_cap, uint32_t* n_out, uin
       d, c->span_out.as<SpanRec>(), n, c->ann_size.as<uint32_t>(), nullptr, 0);
   c->launches++;
   K2J_CUDA(c, cudaGetLastError());
-  k2j_status st = run_scan(c, c->ann_size.as<uint32_t>(), n, 1, c->ann_off.as<uint64_t>(), c->scan_totals.as<uint64_t>() + 10, &c->launches);
+  k2j_status st = run_scan(c, c->ann_size.as<uint32_t>(), n, 1, c->ann_off.as<uint64_t>(), c->scan_totals.as<uint64_t>() + 12, &c->launches);
   if (st) return st;
-  K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 10, c->scan_totals.as<uint64_t>() + 10, 8, cudaMemcpyDeviceToHost, s));
+  K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 12, c->scan_totals.as<uint64_t>() + 12, 8, cudaMemcpyDeviceToHost, s));
   K2J_CUDA(c, cudaStreamSynchronize(s));  // also covers `ordered`, which goes out of scope
-  *bytes_out = c->h_totals[10];
+  *bytes_out = c->h_totals[12];
   return K2J_OK;
 }
 
@@ -625,14 +625,14 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
     c->launches++;
     K2J_CUDA(c, cudaGetLastError());
     K2J_CUDA(c, cudaEventRecord(c->ev[3], s));
-    k2j_status st = run_scan(c, d.ev_size, d.n_events, 1, c->ev_off.as<uint64_t>(), c->scan_totals.as<uint64_t>() + 8, &c->launches);
+    k2j_status st = run_scan(c, d.ev_size, d.n_events, 1, c->ev_off.as<uint64_t>(), c->scan_totals.as<uint64_t>() + 10, &c->launches);
     if (st) return st;
-    K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 8, c->scan_totals.as<uint64_t>() + 8, 8, cudaMemcpyDeviceToHost, s));
+    K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 10, c->scan_totals.as<uint64_t>() + 10, 8, cudaMemcpyDeviceToHost, s));
     if (n_gpu_events)
-      K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 9, c->ev_off.as<uint64_t>() + c->n_ops, 8, cudaMemcpyDeviceToHost, s));
+      K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 11, c->ev_off.as<uint64_t>() + c->n_ops, 8, cudaMemcpyDeviceToHost, s));
     K2J_CUDA(c, cudaEventRecord(c->ev[4], s));
     K2J_CUDA(c, cudaStreamSynchronize(s));
-    total_bytes = c->h_totals[8];
+    total_bytes = c->h_totals[10];
     if (spans_on) {
       k2j_status st2 = order_annotations(c, span_cap, &n_spans, &ann_bytes);
       if (st2) return st2;
@@ -658,7 +658,7 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
 
   res->out_bytes = total_bytes + ann_bytes;
   res->annotation_bytes = ann_bytes;
-  res->ops_bytes = n_gpu_events ? c->h_totals[9] : total_bytes;
+  res->ops_bytes = n_gpu_events ? c->h_totals[11] : total_bytes;
   res->n_records = totals[C_EVENTS] + totals[C_EXT] + totals[C_UNEXPECTED];
   res->x_events = c->h_counters->x_events + (ann_bytes ? n_spans : 0);
   res->flow_events = c->h_counters->flow_events;
@@ -667,7 +667,7 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
   res->invalid_external_correlation_events = c->h_counters->invalid_external_correlation;
   res->unexpected_cuda_events = totals[C_UNEXPECTED];
   res->in_bytes = 208 * totals[C_KERNEL] + 88 * totals[C_MEMCPY] + 96 * totals[C_MEMCPY2] + 88 * totals[C_MEMSET] +
-                  40 * totals[C_API] + 24 * totals[C_EXT];
+                  40 * totals[C_API] + 24 * totals[C_EXT] + 56 * totals[C_OVERHEAD];
   res->name_bytes = c->h_counters->name_bytes;
   res->kernel_launches = c->launches;
   cudaEventElapsedTime(&res->ms_segment, c->ev[0], c->ev[1]);
@@ -702,11 +702,11 @@ k2j_status k2j_exclusive_scan_u32(k2j_ctx* c, const uint32_t* sizes, uint64_t n,
   *total = 0;
   if (n == 0) return K2J_OK;
   uint32_t launches = 0;
-  k2j_status st = run_scan(c, sizes, n, 1, offsets, c->scan_totals.as<uint64_t>() + 12, &launches);
+  k2j_status st = run_scan(c, sizes, n, 1, offsets, c->scan_totals.as<uint64_t>() + 14, &launches);
   if (st) return st;
-  K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 12, c->scan_totals.as<uint64_t>() + 12, 8, cudaMemcpyDeviceToHost, c->stream));
+  K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 14, c->scan_totals.as<uint64_t>() + 14, 8, cudaMemcpyDeviceToHost, c->stream));
   K2J_CUDA(c, cudaStreamSynchronize(c->stream));
-  *total = c->h_totals[12];
+  *total = c->h_totals[14];
   return K2J_OK;
 }
 

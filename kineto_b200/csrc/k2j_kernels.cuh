@@ -25,20 +25,20 @@
 namespace k2j {
 
 // ---- record classes ---------------------------------------------------------------------------
-enum : int { C_API = 0, C_KERNEL = 1, C_MEMCPY = 2, C_MEMCPY2 = 3, C_MEMSET = 4, C_EXT = 5,
-             C_EXT_USER = 6 /* slot class only: EXTERNAL_CORRELATION of kind CUSTOM1; counted in C_EXT too */,
-             C_NCLASS = 6,
-             C_EVENTS = 6 /* column 6 of the count matrix: records that own an event slot */,
-             C_UNEXPECTED = 7 /* column 7: records of unknown kind */,
-             C_USER = 8 /* column 8: CUSTOM1 correlation records */, C_NCOL = 9, C_OP = 9 };
-enum : uint32_t { K_MEMCPY = 1, K_MEMSET = 2, K_DRIVER = 4, K_RUNTIME = 5, K_KERNEL = 10, K_MEMCPY2 = 22, K_EXTCORR = 39 };
+enum : int { C_API = 0, C_KERNEL = 1, C_MEMCPY = 2, C_MEMCPY2 = 3, C_MEMSET = 4, C_OVERHEAD = 5, C_EXT = 6,
+             C_EXT_USER = 7 /* slot class only: EXTERNAL_CORRELATION of kind CUSTOM1; counted in C_EXT too */,
+             C_NCLASS = 7,
+             C_EVENTS = 7 /* column 7 of the count matrix: records that own an event slot */,
+             C_UNEXPECTED = 8 /* column 8: records of unknown kind */,
+             C_USER = 9 /* column 9: CUSTOM1 correlation records */, C_NCOL = 10, C_OP = 10 };
+enum : uint32_t { K_MEMCPY = 1, K_MEMSET = 2, K_DRIVER = 4, K_RUNTIME = 5, K_KERNEL = 10, K_OVERHEAD = 17, K_MEMCPY2 = 22, K_EXTCORR = 39 };
 
 constexpr int kChunkSlots = 512;            // 4 KiB of 8-byte slots
 constexpr int kMaxEntry = 26;               // longest record is 208 B = 26 slots
 constexpr uint8_t kExitTerminate = 254;     // the walk hit a record it cannot size
 constexpr uint8_t kEntryNone = 255;         // chunk is unreachable
 
-// size/8 | class<<5 for a record kind; 0 = unknown
+// size/8 | class<<5 for a record kind (5 + 3 bits); 0 = unknown
 __device__ __forceinline__ uint32_t slot_code(uint32_t kind, uint32_t word1) {
   switch (kind) {
     case K_KERNEL: return 26u | (C_KERNEL << 5);
@@ -46,6 +46,7 @@ __device__ __forceinline__ uint32_t slot_code(uint32_t kind, uint32_t word1) {
     case K_MEMCPY2: return 12u | (C_MEMCPY2 << 5);
     case K_MEMSET: return 11u | (C_MEMSET << 5);
     case K_RUNTIME: case K_DRIVER: return 5u | (C_API << 5);
+    case K_OVERHEAD: return 7u | (C_OVERHEAD << 5);  // CUpti_ActivityOverhead3, 56 bytes
     case K_EXTCORR: return 3u | ((word1 == 4u ? C_EXT_USER : C_EXT) << 5);  // word1 = externalKind
     default: return 0u;
   }
@@ -277,7 +278,7 @@ __global__ void __launch_bounds__(kSegWarps * 32) k_seg_chunks(Dev d) {
   }
   __syncwarp();
   uint8_t code = kEntryNone;
-  uint32_t c0 = 0, c1 = 0, c2 = 0;  // counts of columns 0-3, 4-7, 8
+  uint32_t c0 = 0, c1 = 0, c2 = 0;  // 8-bit counts of columns 0-3, 4-7, 8-9
   if (lane < kMaxEntry) {
     uint32_t pos = lane;
     code = 0;
@@ -286,12 +287,12 @@ __global__ void __launch_bounds__(kSegWarps * 32) k_seg_chunks(Dev d) {
       if (pos >= g.nvalid) { code = g.last ? 0 : (uint8_t)(pos - g.nvalid); break; }
       const uint32_t sc = s_code[w][pos];
       const uint32_t n = sc & 31u;
-      if (n == 0 || (g.last && pos + n > g.nvalid)) { code = kExitTerminate; c1 += 1u << 24; break; }  // column 7: unexpected
+      if (n == 0 || (g.last && pos + n > g.nvalid)) { code = kExitTerminate; c2 += 1u << (8 * (C_UNEXPECTED - 8)); break; }
       const uint32_t cls = code_class(sc);
       c0 += cls < 4u ? 1u << (8 * cls) : 0u;
-      c1 += cls >= 4u ? 1u << (8 * (cls - 4u)) : 0u;              // columns 4 (memset) and 5 (external correlation)
-      c1 += cls != (uint32_t)C_EXT ? 1u << 16 : 0u;                // column 6: records that own an event slot
-      c2 += (sc >> 5) == (uint32_t)C_EXT_USER ? 1u : 0u;           // column 8
+      c1 += cls >= 4u ? 1u << (8 * (cls - 4u)) : 0u;                                 // classes 4..6
+      c1 += cls != (uint32_t)C_EXT ? 1u << (8 * (C_EVENTS - 4)) : 0u;                 // records that own an event slot
+      c2 += (sc >> 5) == (uint32_t)C_EXT_USER ? 1u << (8 * (C_USER - 8)) : 0u;
       pos += n;
     }
   }
@@ -341,7 +342,8 @@ __global__ void __launch_bounds__(256) k_seg_compose(Dev d) {
       for (int i = 0; i < 4; i++) d.chunk_cnt[(uint64_t)i * d.n_chunks + t0 + c] = (w0 >> (8 * i)) & 0xffu;
 #pragma unroll
       for (int i = 0; i < 4; i++) d.chunk_cnt[(uint64_t)(4 + i) * d.n_chunks + t0 + c] = (w1 >> (8 * i)) & 0xffu;
-      d.chunk_cnt[(uint64_t)8 * d.n_chunks + t0 + c] = w2;
+#pragma unroll
+      for (int i = 0; i < C_NCOL - 8; i++) d.chunk_cnt[(uint64_t)(8 + i) * d.n_chunks + t0 + c] = (w2 >> (8 * i)) & 0xffu;
     }
   }
 }
@@ -445,7 +447,7 @@ __global__ void k_mark_corr(Dev d) {
   int cls = 0;
 #pragma unroll
   for (int c = 1; c < C_EXT; c++) if (i >= d.cls_begin[c]) cls = c;
-  if (i - d.cls_begin[cls] >= d.cls_count[cls]) return;  // padding
+  if (i - d.cls_begin[cls] >= d.cls_count[cls] || cls == C_OVERHEAD) return;  // padding; overhead records join nothing
   const uint8_t* r = d.cupti + (uint64_t)d.work_slot[i] * 8;
   const int off = cls == C_API ? 32 : cls == C_KERNEL ? 92 : cls == C_MEMCPY2 ? 60 : 44;
   bit_set(d.need_corr, d.need_corr_mask, *reinterpret_cast<const uint32_t*>(r + off));
@@ -755,11 +757,11 @@ enum : int { M_CPY_KIND, M_CPY_SRC, M_CPY_DST, M_SET_KIND, M_PID, M_TID, M_TS, M
 
 // -- CPU-side activity (no record: every value is a slot): head, metadata entries, tail --
 enum : int { OS_CAT = 0, OS_NAME = 4, OS_PID = 8, OS_EXT = 12, OS_TID = 16, OS_TS = 24, OS_DUR = 32, OS_ROW = 40, OS_FLOW = 44, OS_FTS = 48 };
-enum : int { O_CAT, O_NAME, O_PID, O_TID, O_TS, O_DUR, O_PAD, O_ARGS, O_EXT, O_EXTC, O_MD,
+enum : int { O_CAT, O_NAME, O_CNAME /* a constant-string name instead of a pool name */, O_PID, O_TID, O_TS, O_DUR, O_PAD, O_ARGS, O_EXT, O_EXTC, O_MD,
              P_ARGS_CLOSE, P_CLOSE, P_FLOW_S, P_FLOW_F, P_FPID, P_FTID, P_FTS, P_FWDBWD, P_AC2G, P_FBP, P_FEND, O_COUNT };
 #define K2J_OPHEAD_FIELDS \
     {"\n  {\n    \"ph\": \"X\",\n    \"cat\": \"", T_CSTR, VK_U32, OS_CAT}, {"\",\n    \"name\": \"", T_NAME, VK_U32, OS_NAME}, \
-    {"\",\n    \"pid\": ", T_I64, VK_I32, OS_PID}, \
+    {"\",\n    \"name\": \"", T_CSTR, VK_U32, OS_NAME}, {"\",\n    \"pid\": ", T_I64, VK_I32, OS_PID}, \
     {",\n    \"tid\": ", T_I64, VK_64, OS_TID}, {",\n    \"ts\": ", T_TS, VK_64, OS_TS}, {",\n    \"dur\": ", T_TS, VK_64, OS_DUR}, {"\n    ", T_NONE}, \
     {",\n    \"args\": {\n      ", T_NONE}, {"\"External id\": ", T_I64, VK_I32, OS_EXT}, {",", T_NONE}
 #define K2J_OPTAIL_FIELDS \
@@ -780,7 +782,7 @@ enum : int { N_HEAD, N_PID, N_TID, N_TS, N_DUR, N_PAD, N_EXT, N_ARGS_CLOSE, N_CL
 
 
 // One table for everything: [api][kernel][mem][op head, metadata marker, op tail][annotation][constant strings].
-enum : int { CS_TYPE = 0, CS_MEMCPY_KIND = 29, CS_MEMORY_KIND = 41, CS_LIMIT = 50, CS_COUNT = 82 };
+enum : int { CS_TYPE = 0, CS_MEMCPY_KIND = 29, CS_MEMORY_KIND = 41, CS_LIMIT = 50, CS_OVERHEAD = 82, CS_COUNT = 93 };
 #define K2J_CSTR_FIELDS \
     {"cpu_op", 0}, {"user_annotation", 0}, {"gpu_user_annotation", 0}, {"gpu_memcpy", 0}, {"gpu_memset", 0}, {"kernel", 0}, \
     {"external_correlation", 0}, {"cuda_runtime", 0}, {"cuda_driver", 0}, {"cpu_instant_event", 0}, {"python_function", 0}, \
@@ -799,7 +801,10 @@ enum : int { CS_TYPE = 0, CS_MEMCPY_KIND = 29, CS_MEMORY_KIND = 41, CS_LIMIT = 5
     {"WARPS|SMEM|BARRIERS", 0}, {"REGS|SMEM|BARRIERS", 0}, {"WARPS|REGS|SMEM|BARRIERS", 0}, {"BLOCKS|BARRIERS", 0}, \
     {"WARPS|BLOCKS|BARRIERS", 0}, {"REGS|BLOCKS|BARRIERS", 0}, {"WARPS|REGS|BLOCKS|BARRIERS", 0}, \
     {"SMEM|BLOCKS|BARRIERS", 0}, {"WARPS|SMEM|BLOCKS|BARRIERS", 0}, {"REGS|SMEM|BLOCKS|BARRIERS", 0}, \
-    {"WARPS|REGS|SMEM|BLOCKS|BARRIERS", 0}
+    {"WARPS|REGS|SMEM|BLOCKS|BARRIERS", 0}, \
+    {"Unknown", 0}, {"Driver Compiler", 0}, {"Buffer Flush", 0}, {"Instrumentation", 0}, {"Resource", 0}, \
+    {"Runtime Triggered Module Loading", 0}, {"Lazy Function Loading", 0}, {"Command Buffer Full", 0}, \
+    {"Activity Buffer Request", 0}, {"Force Int", 0}, {"Unrecognized", 0}
 
 
 constexpr int API_BASE = 0, KERNEL_BASE = API_BASE + A_COUNT, MEM_BASE = KERNEL_BASE + K_COUNT, OP_BASE = MEM_BASE + M_COUNT,
@@ -1153,6 +1158,26 @@ __device__ __forceinline__ uint64_t gather_mem(const Dev& d, uint32_t* a, Tally&
   return p;
 }
 
+// handleOverheadActivity (libkineto/src/CuptiActivityProfiler.cpp:360-377) with OverheadActivity
+// (libkineto/src/CuptiActivity.h:144-179, names libkineto/src/cupti_strings.cpp:68-97): device -1, resource 0,
+// no correlation id, no metadata, no flow.  The event has the shape of a CPU-side activity without
+// arguments, so it uses that field program with a constant-string name.
+__device__ __forceinline__ uint64_t gather_overhead(const Dev& d, uint32_t* a, Tally& t, uint32_t* filt) {
+  const uint32_t kind = a32(a, 4);
+  const uint64_t st = a64(a, 24), en = a64(a, 32);
+  const int64_t ts = conv_ts(d, st), dur = conv_dur(d, st, en);
+  if (out_of_range(d, ts, dur)) { *filt = 2; return 0; }
+  uint32_t idx = 10;  // "Unrecognized"
+  if (kind <= 1u) idx = kind;
+  else if ((kind & 0xffffu) == 0u && (kind >> 16) >= 1u && (kind >> 16) <= 7u) idx = 1u + (kind >> 16);
+  else if (kind == 0x7fffffffu) idx = 9;
+  s32(a, OS_CAT, (uint32_t)(CS_TYPE + 11)); s32(a, OS_NAME, (uint32_t)CS_OVERHEAD + idx); s32(a, OS_PID, 0xFFFFFFFFu);
+  s32(a, OS_EXT, 0u); s64(a, OS_TID, 0ull); s64(a, OS_TS, (uint64_t)rel_ts(d, ts)); s64(a, OS_DUR, (uint64_t)(dur < 0 ? 0 : dur));
+  t.x++;
+  return (1ull << O_CAT) | (1ull << O_CNAME) | (1ull << O_PID) | (1ull << O_TID) | (1ull << O_TS) | (1ull << O_DUR) |
+         (1ull << O_PAD) | (1ull << P_CLOSE);
+}
+
 // CPU-side activity: ChromeTraceLogger::handleActivity for a GenericTraceActivity (output_json.cpp:837-963)
 __device__ __forceinline__ uint64_t gather_op(const Dev& d, uint64_t i, uint32_t* a, Tally& t) {
   const int32_t type = d.op_type[i];
@@ -1305,6 +1330,7 @@ __device__ __forceinline__ void format_event(S& s, const Dev& d, int cls, uint32
       case C_MEMCPY: if ((p = gather_mem<C_MEMCPY>(d, a, t, filt, true, ext))) count_fields<MEM_BASE, 0, M_COUNT>(s, d, a, p, nb); break;
       case C_MEMCPY2: if ((p = gather_mem<C_MEMCPY2>(d, a, t, filt, true, ext))) count_fields<MEM_BASE, 0, M_COUNT>(s, d, a, p, nb); break;
       case C_MEMSET: if ((p = gather_mem<C_MEMSET>(d, a, t, filt, true, ext))) count_fields<MEM_BASE, 0, M_COUNT>(s, d, a, p, nb); break;
+      case C_OVERHEAD: if ((p = gather_overhead(d, a, t, filt))) count_fields<OP_BASE, 0, O_COUNT>(s, d, a, p, nb); break;
       default: if ((p = gather_op(d, j, a, t))) count_fields<OP_BASE, 0, O_COUNT>(s, d, a, p, nb); break;
     }
   } else {
@@ -1316,15 +1342,16 @@ __device__ __forceinline__ void format_event(S& s, const Dev& d, int cls, uint32
       case C_MEMCPY: p = gather_mem<C_MEMCPY>(d, a, t, filt, false, ext); base = MEM_BASE; break;
       case C_MEMCPY2: p = gather_mem<C_MEMCPY2>(d, a, t, filt, false, ext); base = MEM_BASE; break;
       case C_MEMSET: p = gather_mem<C_MEMSET>(d, a, t, filt, false, ext); base = MEM_BASE; break;
+      case C_OVERHEAD: p = gather_overhead(d, a, t, filt); base = OP_BASE; break;
       default: p = gather_op(d, j, a, t); base = OP_BASE; break;
     }
     run_fields(s, d, a, base, p, nb);
   }
 }
 
-// 8-byte units of a record of each class (C_API .. C_MEMSET)
+// 8-byte units of a record of each class (C_API .. C_OVERHEAD)
 __device__ __forceinline__ uint32_t class_units(int cls) {
-  return cls == C_KERNEL ? 26u : cls == C_MEMCPY2 ? 12u : cls == C_API ? 5u : 11u;
+  return cls == C_KERNEL ? 26u : cls == C_MEMCPY2 ? 12u : cls == C_API ? 5u : cls == C_OVERHEAD ? 7u : 11u;
 }
 
 // One thread per work item.  Work items are class-sorted (each class padded to a multiple of 32),
@@ -1444,7 +1471,7 @@ __global__ void k_sort_keys(Dev d, uint64_t* keys, uint32_t* vals, uint64_t span
   for (int c = 1; c < C_EXT; c++) if (i >= d.cls_begin[c]) cls = c;
   if (i - d.cls_begin[cls] >= d.cls_count[cls]) return;  // padding
   const uint8_t* r = d.cupti + (uint64_t)d.work_slot[i] * 8;
-  const int64_t ts = conv_ts(d, *reinterpret_cast<const uint64_t*>(r + (cls == C_API ? 8 : 16)));
+  const int64_t ts = conv_ts(d, *reinterpret_cast<const uint64_t*>(r + (cls == C_API ? 8 : cls == C_OVERHEAD ? 24 : 16)));
   uint64_t key = 0;
   if (ts >= d.win_start) { key = (uint64_t)(ts - d.win_start); if (key > span) key = span + 1; }
   const uint32_t e = d.work_ev[i] - (uint32_t)d.n_ops;

@@ -382,8 +382,16 @@ void B200TraceLogger::handleActivity(const libkineto::ITraceActivity& a) {
       m.tidPairs.push_back((int32_t)rec.threadId); m.tidPairs.push_back((int32_t)a.resourceId());
     }
     m.appendRecord(rec);
+  } else if (auto* ov = dynamic_cast<const OverheadActivity*>(&a)) {
+    // the wrapper holds the 40-byte prefix of the record (CUpti_ActivityOverhead); the GPU path takes the
+    // record as CUPTI writes it today (CUpti_ActivityOverhead3, 56 bytes)
+    CUpti_ActivityOverhead3 rec;
+    memset(&rec, 0, sizeof rec);
+    memcpy(&rec, &ov->raw(), sizeof(CUpti_ActivityOverhead));
+    convert(rec);
+    m.appendRecord(rec);
   } else {
-    // Synchronisation, CUDA-event and overhead records and foreign activity classes are not handled by
+    // Synchronisation and CUDA-event records and foreign activity classes are not handled by
     // the GPU path yet; there is no CPU path to fall back to, so they are counted and reported.
     if (skipped_++ == 0) LOG(ERROR) << "B200TraceLogger: unsupported activity class for '" << a.name() << "'; skipped";
   }

@@ -180,6 +180,11 @@ class TraceBuilder:
                          memoryKind=memory_kind, deviceId=device, contextId=context, streamId=stream,
                          graphId=graph, graphNodeId=graph_node, channelID=channel, channelType=channel_type)
 
+    def overhead(self, start, end, overhead_kind=1 << 16, corr=0, object_kind=1, pid=0, tid=0):
+        """CUpti_ActivityOverhead (CUPTI_ACTIVITY_KIND_OVERHEAD); `overhead_kind` is the CUPTI enum value."""
+        return self._rec(tf.KIND_OVERHEAD, start=start, end=end, overheadKind=overhead_kind, objectKind=object_kind,
+                         objectId0=pid, objectId1=tid, correlationId=corr)
+
     def raw_record(self, kind: int, size: int):
         """A record of a kind the path does not know, `size` bytes (multiple of 8)."""
         r = np.zeros(size // 4, np.uint32)

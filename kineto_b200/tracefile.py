@@ -36,6 +36,7 @@ RECORD_SIZE = {
     KIND_RUNTIME: 40,
     KIND_DRIVER: 40,
     KIND_EXTERNAL_CORRELATION: 24,
+    KIND_OVERHEAD: 56,
 }
 
 
@@ -80,7 +81,11 @@ API = _dt(40, [
 EXTCORR = _dt(24, [
     ("kind", "<u4", 0), ("externalKind", "<u4", 4), ("externalId", "<u8", 8),
     ("correlationId", "<u4", 16)])
-RECORD_DTYPE = {KIND_CONCURRENT_KERNEL: KERNEL9, KIND_MEMCPY: MEMCPY5, KIND_MEMCPY2: MEMCPYP2P4,
+OVERHEAD = _dt(56, [  # CUpti_ActivityOverhead3; the reference reads its 40-byte prefix (CUpti_ActivityOverhead)
+    ("kind", "<u4", 0), ("overheadKind", "<u4", 4), ("objectKind", "<u4", 8), ("objectId0", "<u4", 12),
+    ("objectId1", "<u4", 16), ("objectId2", "<u4", 20), ("start", "<u8", 24), ("end", "<u8", 32),
+    ("correlationId", "<u4", 40), ("overheadData", "<u8", 48)])
+RECORD_DTYPE = {KIND_OVERHEAD: OVERHEAD, KIND_CONCURRENT_KERNEL: KERNEL9, KIND_MEMCPY: MEMCPY5, KIND_MEMCPY2: MEMCPYP2P4,
                 KIND_MEMSET: MEMSET4, KIND_RUNTIME: API, KIND_DRIVER: API,
                 KIND_EXTERNAL_CORRELATION: EXTCORR}
 

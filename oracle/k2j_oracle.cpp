@@ -44,9 +44,9 @@
 
 namespace {
 
-enum : uint32_t { K_MEMCPY = 1, K_MEMSET = 2, K_DRIVER = 4, K_RUNTIME = 5, K_KERNEL = 10, K_MEMCPY2 = 22, K_EXTCORR = 39 };
+enum : uint32_t { K_MEMCPY = 1, K_MEMSET = 2, K_DRIVER = 4, K_RUNTIME = 5, K_KERNEL = 10, K_OVERHEAD = 17, K_MEMCPY2 = 22, K_EXTCORR = 39 };
 enum : int { T_CPU_OP = 0, T_GPU_USER_ANNOTATION = 2, T_GPU_MEMCPY = 3, T_GPU_MEMSET = 4, T_KERNEL = 5, T_RUNTIME = 7,
-             T_DRIVER = 8, T_CPU_INSTANT = 9, T_MTIA_COUNTERS = 17, T_XPU_RUNTIME = 21, T_XPU_DRIVER = 22,
+             T_DRIVER = 8, T_CPU_INSTANT = 9, T_OVERHEAD = 11, T_MTIA_COUNTERS = 17, T_XPU_RUNTIME = 21, T_XPU_DRIVER = 22,
              T_PU1_RUNTIME = 24, T_PU1_DRIVER = 25, T_XPU_SCOPE = 26, T_HW_COUNTERS = 28, T_COUNT = 29 };
 const char* kTypeNames[T_COUNT] = {  // libkineto/include/ActivityType.h:80-112
     "cpu_op", "user_annotation", "gpu_user_annotation", "gpu_memcpy", "gpu_memset", "kernel",
@@ -64,6 +64,7 @@ size_t recSize(uint32_t kind) {
     case K_MEMSET: return 88;
     case K_RUNTIME: case K_DRIVER: return 40;
     case K_EXTCORR: return 24;
+    case K_OVERHEAD: return 56;  // CUpti_ActivityOverhead3
     default: return 0;
   }
 }
@@ -559,8 +560,37 @@ struct Run {
     e.md = f.j; emit(out, e); afterGpu(e);
   }
 
+  // handleOverheadActivity (libkineto/src/CuptiActivityProfiler.cpp:360-377) with OverheadActivity
+  // (libkineto/src/CuptiActivity.h:144-179): device -1, resource 0, no correlation id, no metadata, no link.
+  static const char* overheadKindStr(uint32_t k) {  // libkineto/src/cupti_strings.cpp:68-97
+    switch (k) {
+      case 0: return "Unknown";
+      case 1: return "Driver Compiler";
+      case 1u << 16: return "Buffer Flush";
+      case 2u << 16: return "Instrumentation";
+      case 3u << 16: return "Resource";
+      case 4u << 16: return "Runtime Triggered Module Loading";
+      case 5u << 16: return "Lazy Function Loading";
+      case 6u << 16: return "Command Buffer Full";
+      case 7u << 16: return "Activity Buffer Request";
+      case 0x7fffffffu: return "Force Int";
+      default: return "Unrecognized";
+    }
+  }
+  void overheadRecord(const uint8_t* r) {
+    Event e; e.type = T_OVERHEAD;
+    e.name = overheadKindStr(rd<uint32_t>(r, 4));
+    const uint64_t st = rd<uint64_t>(r, 24), en = rd<uint64_t>(r, 32);
+    e.ts = conv(st); e.dur = p.ts_mode ? conv(en) - conv(st) : (int64_t)(en - st);
+    e.device = -1; e.resource = 0; e.hasLinked = false; e.linkedId = 0; e.corrId = 0;
+    e.flowId = 0; e.flowType = 0; e.flowStart = false;
+    if (outOfRange(e.ts, e.dur)) return;
+    emit(out, e);
+  }
+
   int64_t recordStart(const uint8_t* r, uint32_t kind) {
     switch (kind) {
+      case K_OVERHEAD: return conv(rd<uint64_t>(r, 24));
       case K_RUNTIME: case K_DRIVER: return conv(rd<uint64_t>(r, 8));
       case K_KERNEL: case K_MEMCPY: case K_MEMCPY2: case K_MEMSET: return conv(rd<uint64_t>(r, 16));
       default: return INT64_MIN;
@@ -586,6 +616,7 @@ struct Run {
         case K_MEMCPY: memcpyRecord(r); break;
         case K_MEMCPY2: memcpy2Record(r); break;
         case K_MEMSET: memsetRecord(r); break;
+        case K_OVERHEAD: overheadRecord(r); break;
         default: c.unexpected++; break;
       }
     }

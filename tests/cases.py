@@ -91,6 +91,12 @@ def edge_trace(flags=0) -> tf.Trace:
     b.kernel(t0 + 6000, t0 + 6100, 140, "regs limited", block=(1024, 1, 1), regs=128)
     b.kernel(t0 + 6000, t0 + 6100, 141, "big ids", queued=(1 << 64) - 1, graph=0xFFFFFFFF, graph_node=(1 << 64) - 1,
              channel=0xFFFFFFFF, channel_type=0x7FFFFFFF, context=0xFFFFFFFF, stream=0xFFFFFFFF)
+    # overhead records (CUPTI_ACTIVITY_KIND_OVERHEAD): every named kind, an unknown kind, window corner cases
+    for i, k in enumerate([0, 1, 1 << 16, 2 << 16, 3 << 16, 4 << 16, 5 << 16, 6 << 16, 7 << 16, 0x7FFFFFFF, 12345]):
+        b.overhead(t0 + 6500 + i, t0 + 6600 + 3 * i, overhead_kind=k, corr=100 if i == 2 else 0, pid=77, tid=88)
+    b.overhead(t0 + 6700, t0 + 6690)                                         # negative duration
+    b.overhead(0, 0)                                                         # no timestamps: outside the window
+    b.overhead(t0 + 999_990, t0 + 1_000_001)                                 # ends after the window
     b.new_buffer()
     # ---- third buffer: an unknown kind ends the walk of this buffer ----
     b.kernel(t0 + 7000, t0 + 7100, 150, "before the unknown record")
