@@ -134,6 +134,41 @@ def tsc_trace(n=3000) -> tf.Trace:
     return synth.gen_kernel_launches(n, seed=21, pool_size=64, ts_mode=1)
 
 
+def overhead_mix_trace(n=3000, seed=41, flags=0) -> tf.Trace:
+    """Random mixture of every record kind the path formats, overhead records included, packed into
+    small buffers so that records of every size straddle chunk and buffer boundaries."""
+    rng = np.random.default_rng(seed)
+    b = synth.TraceBuilder(n_devices=4, flags=flags, buffer_bytes=1 << 20)
+    t0 = b.t0
+    b.window = (t0, t0 + 50_000_000)
+    b.thread(1001, 5001)
+    for i in range(n // 10):
+        b.op(t0 + 100 * i, t0 + 100 * i + 60, i + 1, "aten::op%d" % (i % 7))
+    kinds = [0, 1 << 16, 2 << 16, 3 << 16, 5 << 16, 99]
+    for i in range(n):
+        ts = t0 + 1000 + 37 * i
+        k = int(rng.integers(0, 8))
+        corr = 1000 + i
+        if k == 0:
+            b.extcorr(corr, int(rng.integers(1, n // 10 + 5)))
+        elif k == 1:
+            b.runtime(ts, ts + 20, corr - int(rng.integers(0, 3)))
+        elif k == 2:
+            b.kernel(ts, ts + int(rng.integers(1, 5000)), corr - int(rng.integers(0, 3)), "k%d" % (i % 13), device=i % 4,
+                     stream=7 + i % 5, grid=(int(rng.integers(1, 500)), 1, 1), block=(int(rng.integers(1, 1025)), 1, 1))
+        elif k == 3:
+            b.memcpy(ts, ts + int(rng.integers(0, 900)), corr - 1, int(rng.integers(1, 1 << 30)))
+        elif k == 4:
+            b.memset(ts, ts + 5, corr - 1, int(rng.integers(1, 1 << 20)))
+        elif k == 5:
+            b.memcpy_p2p(ts, ts + 7, corr - 2, int(rng.integers(1, 1 << 24)))
+        else:
+            b.overhead(ts, ts + int(rng.integers(0, 300)), overhead_kind=kinds[int(rng.integers(0, len(kinds)))])
+        if rng.random() < 0.004:
+            b.new_buffer()
+    return b.build()
+
+
 CASES = {
     "edge": edge_trace,
     "generic_300": lambda: synth.gen_generic_kernels(300, seed=31, pool_size=40),

@@ -54,6 +54,8 @@ def test_gpu_matches_reference_golden(name):
     cases.edge_trace,
     lambda: cases.edge_trace(flags=1),
     cases.annotation_trace,
+    lambda: cases.overhead_mix_trace(60_000, seed=42),
+    lambda: cases.with_flags(cases.overhead_mix_trace(20_000, seed=43), tf.FLAG_SORT_BY_START),
     lambda: synth.gen_kernel_launches(60_000, seed=206, pool_size=300, user_annotations=40),
     lambda: cases.with_flags(synth.gen_kernel_launches(70_000, seed=207, pool_size=300), tf.FLAG_SORT_BY_START),
     lambda: cases.with_flags(synth.gen_mixed(120_000, seed=208, pool_size=900), tf.FLAG_SORT_BY_START),
@@ -61,7 +63,7 @@ def test_gpu_matches_reference_golden(name):
     lambda: cases.with_flags(cases.tsc_trace(9_000), tf.FLAG_SORT_BY_START),
     lambda: cases.with_flags(cases.annotation_trace(), tf.FLAG_SORT_BY_START),
 ], ids=["generic", "launches", "shard", "mixed", "mixed_small_buffers", "tsc", "edge", "edge_annot", "annotations",
-        "launches_annot", "sorted_launches", "sorted_mixed", "sorted_annot", "sorted_tsc", "sorted_small"])
+        "overhead_mix", "sorted_overhead_mix", "launches_annot", "sorted_launches", "sorted_mixed", "sorted_annot", "sorted_tsc", "sorted_small"])
 def test_gpu_matches_port(gen):
     trace = gen()
     want, stats = helpers.run_port(trace)

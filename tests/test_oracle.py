@@ -42,8 +42,9 @@ def test_golden_container_is_reproducible(name):
     cases.edge_trace,
     lambda: cases.edge_trace(flags=1),
     cases.annotation_trace,
+    cases.overhead_mix_trace,
     lambda: synth.gen_kernel_launches(4000, seed=105, pool_size=100, user_annotations=25),
-], ids=["generic", "launches", "shard", "mixed", "tsc", "edge", "edge_annot", "annotations", "launches_annot"])
+], ids=["generic", "launches", "shard", "mixed", "tsc", "edge", "edge_annot", "annotations", "overhead_mix", "launches_annot"])
 def test_port_matches_live_reference(gen):
     trace = gen()
     doc, _ = helpers.run_ref(trace)
