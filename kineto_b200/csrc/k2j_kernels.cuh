@@ -957,8 +957,9 @@ __device__ __noinline__ void span_update(const Dev& d, uint32_t corr, uint32_t d
 struct Tally { uint32_t x, flow; unsigned long long name_bytes; uint64_t ev; };
 
 // A thread's area in shared memory: the staged record plus value slots (see the S_ offsets above).
-constexpr int kRecStride = 27;              // 8-byte units per thread: 26 for the longest record, odd so that 64-bit
-                                            // reads of 32 lanes fall in distinct banks
+constexpr int kRecStride = 23;              // 8-byte units per thread: 22 for the part of the longest record (Kernel9) that
+                                            // fields read (176 of its 208 bytes); odd, so that 64-bit reads of 32 lanes
+                                            // fall in distinct banks
 constexpr int kAreaWords = 2 * kRecStride;  // the same in 32-bit words
 __device__ __forceinline__ uint32_t a32(const uint32_t* a, int off) { return a[off >> 2]; }
 __device__ __forceinline__ uint64_t a64(const uint32_t* a, int off) { return (uint64_t)a[off >> 2] | ((uint64_t)a[(off >> 2) + 1] << 32); }
@@ -1349,9 +1350,9 @@ __device__ __forceinline__ void format_event(S& s, const Dev& d, int cls, uint32
   }
 }
 
-// 8-byte units of a record of each class (C_API .. C_OVERHEAD)
+// 8-byte units staged of a record of each class (C_API .. C_OVERHEAD): whole records, except the kernel record's unread tail
 __device__ __forceinline__ uint32_t class_units(int cls) {
-  return cls == C_KERNEL ? 26u : cls == C_MEMCPY2 ? 12u : cls == C_API ? 5u : cls == C_OVERHEAD ? 7u : 11u;
+  return cls == C_KERNEL ? 22u : cls == C_MEMCPY2 ? 12u : cls == C_API ? 5u : cls == C_OVERHEAD ? 7u : 11u;
 }
 
 // One thread per work item.  Work items are class-sorted (each class padded to a multiple of 32),
@@ -1360,7 +1361,7 @@ __device__ __forceinline__ uint32_t class_units(int cls) {
 // with coalesced loads (lane = 8-byte unit of a record); all later reads of record fields and of the
 // values computed from them are shared-memory reads at table-given offsets.
 template <bool WRITE>
-__global__ void __launch_bounds__(kEventThreads, WRITE ? 7 : 8) k_events(Dev d) {
+__global__ void __launch_bounds__(kEventThreads, 8) k_events(Dev d) {
   __shared__ uint64_t s_rec[kEventThreads * kRecStride];
   __shared__ uint64_t s_park[WRITE ? 3 * kEventThreads : 1];
   __shared__ unsigned long long s_cnt[8];
