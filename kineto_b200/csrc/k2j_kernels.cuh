@@ -348,16 +348,23 @@ __global__ void __launch_bounds__(256) k_seg_compose(Dev d) {
   }
 }
 
-__device__ __forceinline__ void load_codes(const Dev& d, const ChunkGeom& g, uint8_t* s, uint32_t lane) {
-  for (uint32_t i = lane; i < (uint32_t)kChunkSlots; i += 32) s[i] = i < g.nvalid ? d.slot_code[g.slot0 + i] : 0;
+// Copies the chunk's slot codes to shared memory as 32-bit words; the chunk's first code lands at the
+// returned byte offset (0..3) of `s`, which holds kChunkSlots + 4 bytes.
+__device__ __forceinline__ uint32_t load_codes(const Dev& d, const ChunkGeom& g, uint8_t* s, uint32_t lane) {
+  const uint64_t a0 = g.slot0 & ~3ull;
+  const uint32_t off = (uint32_t)(g.slot0 & 3ull);
+  const uint32_t nwords = (off + g.nvalid + 3u) >> 2;
+  const uint32_t* src = reinterpret_cast<const uint32_t*>(d.slot_code + a0);
+  for (uint32_t i = lane; i < (uint32_t)(kChunkSlots + 4) / 4; i += 32) reinterpret_cast<uint32_t*>(s)[i] = i < nwords ? src[i] : 0u;
   __syncwarp();
+  return off;
 }
 
 // One warp per chunk.  Lane 0 walks the chunk from its true entry and notes where records start; the
 // warp then ranks the records within their class (32 at a time, by ballot) and writes the per-class
 // work lists and the compacted EXTERNAL_CORRELATION records.
 __global__ void __launch_bounds__(kSegWarps * 32) k_seg_write(Dev d) {
-  __shared__ uint8_t s_code[kSegWarps][kChunkSlots];
+  __shared__ __align__(4) uint8_t s_code[kSegWarps][kChunkSlots + 4];
   __shared__ uint16_t s_pos[kSegWarps][kChunkSlots / 3 + 2];
   __shared__ uint32_t s_n[kSegWarps];
   const uint32_t w = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -366,11 +373,11 @@ __global__ void __launch_bounds__(kSegWarps * 32) k_seg_write(Dev d) {
   const uint32_t entry = d.chunk_entry[chunk];
   if (entry == kEntryNone) return;
   const ChunkGeom g = chunk_geom(d, chunk);
-  load_codes(d, g, s_code[w], lane);
+  const uint8_t* codes = s_code[w] + load_codes(d, g, s_code[w], lane);
   if (lane == 0) {
     uint32_t n = 0, pos = entry;
     for (int it = 0; it < kChunkSlots && pos < g.nvalid; it++) {  // bounded: every step advances by at least 3 slots
-      const uint32_t len = s_code[w][pos] & 31u;
+      const uint32_t len = codes[pos] & 31u;
       if (len == 0 || (g.last && pos + len > g.nvalid)) break;    // unknown kind or overrun: the walk ends
       s_pos[w][n++] = (uint16_t)pos;
       pos += len;
@@ -388,7 +395,7 @@ __global__ void __launch_bounds__(kSegWarps * 32) k_seg_write(Dev d) {
     const uint32_t i = i0 + lane;
     const bool on = i < n;
     const uint32_t pos = on ? s_pos[w][i] : 0u;
-    const uint32_t cls = on ? code_class(s_code[w][pos]) : 0xffu;
+    const uint32_t cls = on ? code_class(codes[pos]) : 0xffu;
     const uint32_t evm = __ballot_sync(0xffffffffu, on && cls != (uint32_t)C_EXT);
     uint64_t dst = 0;
 #pragma unroll
