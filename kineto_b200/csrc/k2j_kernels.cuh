@@ -33,6 +33,7 @@ enum : int { C_API = 0, C_KERNEL = 1, C_MEMCPY = 2, C_MEMCPY2 = 3, C_MEMSET = 4,
              C_USER = 9 /* column 9: CUSTOM1 correlation records */, C_NCOL = 10, C_OP = 10 };
 enum : uint32_t { K_MEMCPY = 1, K_MEMSET = 2, K_DRIVER = 4, K_RUNTIME = 5, K_KERNEL = 10, K_OVERHEAD = 17, K_MEMCPY2 = 22, K_EXTCORR = 39 };
 
+static_assert(C_EXT_USER == C_EXT + 1 && C_EXT_USER < 8, "slot class layout");
 constexpr int kChunkSlots = 512;            // 4 KiB of 8-byte slots
 constexpr int kMaxEntry = 26;               // longest record is 208 B = 26 slots
 constexpr uint8_t kExitTerminate = 254;     // the walk hit a record it cannot size
@@ -251,9 +252,23 @@ __device__ __forceinline__ uint32_t code_class(uint32_t code) {
 
 // One warp per chunk: slot codes; then lane e (< 26) walks the chunk as if it were entered at slot e
 // and leaves behind where that walk exits (the exit map) and how many records of each class it met
-// (nine 8-bit counts packed in three words: a 4 KiB chunk holds at most 170 records).
+// (ten 8-bit counts packed in three words: a 4 KiB chunk holds at most 170 records).  Kind -> code and
+// class -> count increments come from two small tables in shared memory, so neither the decode nor
+// the walk branches on the record kind.
 __global__ void __launch_bounds__(kSegWarps * 32) k_seg_chunks(Dev d) {
   __shared__ uint8_t s_code[kSegWarps][kChunkSlots];
+  __shared__ uint8_t s_kind[64];     // slot code of record kinds 0..63 (CUSTOM1 correlation records add one class)
+  __shared__ uint32_t s_inc[8][3];   // per slot class: increments of the three packed count words
+  if (threadIdx.x < 64) s_kind[threadIdx.x] = (uint8_t)slot_code(threadIdx.x, 0u);
+  if (threadIdx.x < 8) {
+    const uint32_t sc = threadIdx.x, cls = sc == (uint32_t)C_EXT_USER ? (uint32_t)C_EXT : sc;
+    uint32_t i0 = 0, i1 = 0, i2 = 0;
+    if (cls < 4u) i0 = 1u << (8 * cls); else i1 = 1u << (8 * (cls - 4u));
+    if (cls != (uint32_t)C_EXT) i1 += 1u << (8 * (C_EVENTS - 4));   // records that own an event slot
+    if (sc == (uint32_t)C_EXT_USER) i2 = 1u << (8 * (C_USER - 8));
+    s_inc[sc][0] = i0; s_inc[sc][1] = i1; s_inc[sc][2] = i2;
+  }
+  __syncthreads();
   const uint32_t w = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t chunk = blockIdx.x * kSegWarps + w;
   if (chunk >= d.n_chunks) return;
@@ -266,7 +281,11 @@ __global__ void __launch_bounds__(kSegWarps * 32) k_seg_chunks(Dev d) {
 #pragma unroll
     for (int q = 0; q < 4; q++) {
       uint32_t code = 0;
-      if (s + q < g.nvalid) { const uint2 w2 = words[g.slot0 + s + q]; code = slot_code(w2.x, w2.y); }
+      if (s + q < g.nvalid) {
+        const uint2 w2 = words[g.slot0 + s + q];
+        code = w2.x < 64u ? s_kind[w2.x] : 0u;
+        code += (w2.x == K_EXTCORR && w2.y == 4u) ? 1u << 5 : 0u;  // externalKind CUSTOM1: class C_EXT_USER = C_EXT + 1
+      }
       packed |= code << (8 * q);
     }
     *reinterpret_cast<uint32_t*>(&s_code[w][s]) = packed;
@@ -288,11 +307,8 @@ __global__ void __launch_bounds__(kSegWarps * 32) k_seg_chunks(Dev d) {
       const uint32_t sc = s_code[w][pos];
       const uint32_t n = sc & 31u;
       if (n == 0 || (g.last && pos + n > g.nvalid)) { code = kExitTerminate; c2 += 1u << (8 * (C_UNEXPECTED - 8)); break; }
-      const uint32_t cls = code_class(sc);
-      c0 += cls < 4u ? 1u << (8 * cls) : 0u;
-      c1 += cls >= 4u ? 1u << (8 * (cls - 4u)) : 0u;                                 // classes 4..6
-      c1 += cls != (uint32_t)C_EXT ? 1u << (8 * (C_EVENTS - 4)) : 0u;                 // records that own an event slot
-      c2 += (sc >> 5) == (uint32_t)C_EXT_USER ? 1u << (8 * (C_USER - 8)) : 0u;
+      const uint32_t* inc = s_inc[sc >> 5];
+      c0 += inc[0]; c1 += inc[1]; c2 += inc[2];
       pos += n;
     }
   }
@@ -302,15 +318,25 @@ __global__ void __launch_bounds__(kSegWarps * 32) k_seg_chunks(Dev d) {
 }
 
 // One block per buffer: chain the exit maps to the true entry slot of every chunk, then copy the counts
-// of the walk that started there into the count matrix.
+// of the walk that started there into the count matrix.  The chain over a tile of 1024 chunks runs in
+// three short phases instead of 1024 dependent steps: (A) for each of 32 segments of 32 chunks and each
+// possible entry, where a walk leaves the segment; (B) one thread chains the 32 segment maps;
+// (C) one lane per segment walks its 32 chunks from the segment's true entry.
 __global__ void __launch_bounds__(256) k_seg_compose(Dev d) {
-  constexpr int kTile = 1024;
+  constexpr int kTile = 1024, kSeg = 32;
   __shared__ uint8_t s_map[kTile * 32];
   __shared__ uint8_t s_ent[kTile];
+  __shared__ uint8_t s_segmap[kTile / kSeg][32];
+  __shared__ uint8_t s_segent[kTile / kSeg];
   __shared__ uint32_t s_entry;
   const uint32_t b = blockIdx.x;
   const uint32_t c0 = d.buf_chunk_base[b], c1 = d.buf_chunk_base[b + 1];
   if (threadIdx.x == 0) s_entry = 0;
+  auto step = [&](uint32_t e, uint32_t c, uint32_t n) -> uint32_t {  // entry of chunk c+1 given the entry of chunk c
+    if (e == kEntryNone || c >= n) return e;
+    const uint8_t x = s_map[c * 32 + e];
+    return x >= kMaxEntry ? (uint32_t)kEntryNone : (uint32_t)x;
+  };
   for (uint32_t t0 = c0; t0 < c1; t0 += kTile) {
     const uint32_t n = min((uint32_t)kTile, c1 - t0);
     __syncthreads();
@@ -318,16 +344,29 @@ __global__ void __launch_bounds__(256) k_seg_compose(Dev d) {
     uint4* dst = reinterpret_cast<uint4*>(s_map);
     for (uint32_t i = threadIdx.x; i < n * 2; i += blockDim.x) dst[i] = src[i];
     __syncthreads();
+    // (A) 32 segments x 26 entries independent chains of 32 steps
+    for (uint32_t q = threadIdx.x; q < (kTile / kSeg) * 32; q += blockDim.x) {
+      const uint32_t seg = q >> 5, e0 = q & 31u;
+      uint32_t e = e0 < (uint32_t)kMaxEntry ? e0 : (uint32_t)kEntryNone;
+      for (uint32_t c = seg * kSeg; c < (seg + 1) * kSeg; c++) e = step(e, c, n);
+      s_segmap[seg][e0] = (uint8_t)e;
+    }
+    __syncthreads();
+    // (B) chain the segments
     if (threadIdx.x == 0) {
       uint32_t e = s_entry;
-      for (uint32_t c = 0; c < n; c++) {
-        s_ent[c] = (uint8_t)e;
-        if (e != kEntryNone) {
-          const uint8_t x = s_map[c * 32 + e];
-          e = (x >= kMaxEntry) ? kEntryNone : x;
-        }
+      for (uint32_t seg = 0; seg < kTile / kSeg; seg++) {
+        s_segent[seg] = (uint8_t)e;
+        if (e != kEntryNone) e = s_segmap[seg][e];
       }
       s_entry = e;
+    }
+    __syncthreads();
+    // (C) entries of the chunks of each segment
+    if (threadIdx.x < kTile / kSeg) {
+      const uint32_t seg = threadIdx.x;
+      uint32_t e = s_segent[seg];
+      for (uint32_t c = seg * kSeg; c < (seg + 1) * kSeg; c++) { s_ent[c] = (uint8_t)e; e = step(e, c, n); }
     }
     __syncthreads();
     for (uint32_t c = threadIdx.x; c < n; c += blockDim.x) {
