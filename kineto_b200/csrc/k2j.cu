@@ -267,7 +267,7 @@ void k2j_destroy(k2j_ctx* c) {
                     &c->chunk_base, &c->scan_sums, &c->scan_totals, &c->ds_tab, &c->span_key, &c->span_nstart, &c->span_end, &c->span_nfirst, &c->span_row,
                     &c->span_out, &c->span_cnt, &c->ann_size, &c->ann_off, &c->sort_keys[0], &c->sort_keys[1], &c->sort_vals[0],
                     &c->sort_vals[1], &c->sort_hist, &c->sort_base, &c->sort_rank, &c->tid_tab, &c->corr_tab, &c->user_tab, &c->op_tab,
-                    &c->work_slot, &c->work_ev, &c->ev_size, &c->ev_off, &c->out, &c->counters, &c->ext_local})
+                    &c->work_slot, &c->work_ev, &c->ev_size, &c->ev_off, &c->ev_ext, &c->out, &c->counters, &c->ext_local})
     b->release();
   if (c->h_totals) cudaFreeHost(c->h_totals);
   if (c->h_counters) cudaFreeHost(c->h_counters);
