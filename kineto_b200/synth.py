@@ -185,6 +185,16 @@ class TraceBuilder:
         return self._rec(tf.KIND_OVERHEAD, start=start, end=end, overheadKind=overhead_kind, objectKind=object_kind,
                          objectId0=pid, objectId1=tid, correlationId=corr)
 
+    def sync(self, start, end, corr, type=tf.SYNC_TYPE_STREAM_SYNCHRONIZE, context=1, stream=7, event=0):
+        """CUpti_ActivitySynchronization; `stream` 0xFFFFFFFF means "no stream applies"."""
+        return self._rec(tf.KIND_SYNCHRONIZATION, type=type, start=start, end=end, correlationId=corr,
+                         contextId=context, streamId=stream, cudaEventId=event)
+
+    def cuda_event(self, ts, corr, event, context=1, stream=7):
+        """CUpti_ActivityCudaEvent2 (a cudaEventRecord as seen by the device)."""
+        return self._rec(tf.KIND_CUDA_EVENT, correlationId=corr, contextId=context, streamId=stream, eventId=event,
+                         deviceTimestamp=ts)
+
     def raw_record(self, kind: int, size: int):
         """A record of a kind the path does not know, `size` bytes (multiple of 8)."""
         r = np.zeros(size // 4, np.uint32)

@@ -37,6 +37,8 @@ RECORD_SIZE = {
     KIND_DRIVER: 40,
     KIND_EXTERNAL_CORRELATION: 24,
     KIND_OVERHEAD: 56,
+    KIND_SYNCHRONIZATION: 40,
+    KIND_CUDA_EVENT: 56,
 }
 
 
@@ -85,7 +87,14 @@ OVERHEAD = _dt(56, [  # CUpti_ActivityOverhead3; the reference reads its 40-byte
     ("kind", "<u4", 0), ("overheadKind", "<u4", 4), ("objectKind", "<u4", 8), ("objectId0", "<u4", 12),
     ("objectId1", "<u4", 16), ("objectId2", "<u4", 20), ("start", "<u8", 24), ("end", "<u8", 32),
     ("correlationId", "<u4", 40), ("overheadData", "<u8", 48)])
-RECORD_DTYPE = {KIND_OVERHEAD: OVERHEAD, KIND_CONCURRENT_KERNEL: KERNEL9, KIND_MEMCPY: MEMCPY5, KIND_MEMCPY2: MEMCPYP2P4,
+SYNC = _dt(40, [  # CUpti_ActivitySynchronization
+    ("kind", "<u4", 0), ("type", "<u4", 4), ("start", "<u8", 8), ("end", "<u8", 16),
+    ("correlationId", "<u4", 24), ("contextId", "<u4", 28), ("streamId", "<u4", 32), ("cudaEventId", "<u4", 36)])
+CUDA_EVENT2 = _dt(56, [  # CUpti_ActivityCudaEvent2 (CUDA 12.8+)
+    ("kind", "<u4", 0), ("correlationId", "<u4", 4), ("contextId", "<u4", 8), ("streamId", "<u4", 12),
+    ("eventId", "<u4", 16), ("deviceTimestamp", "<u8", 40)])
+SYNC_TYPE_EVENT_SYNCHRONIZE, SYNC_TYPE_STREAM_WAIT_EVENT, SYNC_TYPE_STREAM_SYNCHRONIZE, SYNC_TYPE_CONTEXT_SYNCHRONIZE = 1, 2, 3, 4
+RECORD_DTYPE = {KIND_OVERHEAD: OVERHEAD, KIND_SYNCHRONIZATION: SYNC, KIND_CUDA_EVENT: CUDA_EVENT2, KIND_CONCURRENT_KERNEL: KERNEL9, KIND_MEMCPY: MEMCPY5, KIND_MEMCPY2: MEMCPYP2P4,
                 KIND_MEMSET: MEMSET4, KIND_RUNTIME: API, KIND_DRIVER: API,
                 KIND_EXTERNAL_CORRELATION: EXTCORR}
 

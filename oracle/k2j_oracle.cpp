@@ -21,6 +21,8 @@
 //   JSON text                           libkineto/src/output_json.cpp:72-126, :144-153, :193-203,
 //                                       :237-259, :318-345, :837-1021
 //   user-annotation spans               libkineto/src/GenericActivityProfiler.cpp:277-327
+//   synchronisation / CUDA event records libkineto/src/CuptiActivityProfiler.cpp:221-254, :379-514,
+//                                       libkineto/src/CuptiActivity.h:180-411, output_json.cpp:914-943, :1006-1012
 //
 // Output: the "activities" part of the trace file, i.e. every event written between the header /
 // metadata rows and the CPU trace span: CPU-op events, then GPU-side events in buffer order, then
@@ -34,6 +36,7 @@
 #include <cstdio>
 #include <cstring>
 #include <map>
+#include <set>
 #include <string>
 #include <unordered_map>
 #include <vector>
@@ -44,9 +47,9 @@
 
 namespace {
 
-enum : uint32_t { K_MEMCPY = 1, K_MEMSET = 2, K_DRIVER = 4, K_RUNTIME = 5, K_KERNEL = 10, K_OVERHEAD = 17, K_MEMCPY2 = 22, K_EXTCORR = 39 };
+enum : uint32_t { K_MEMCPY = 1, K_MEMSET = 2, K_DRIVER = 4, K_RUNTIME = 5, K_KERNEL = 10, K_OVERHEAD = 17, K_MEMCPY2 = 22, K_CUDA_EVENT = 36, K_SYNC = 38, K_EXTCORR = 39 };
 enum : int { T_CPU_OP = 0, T_GPU_USER_ANNOTATION = 2, T_GPU_MEMCPY = 3, T_GPU_MEMSET = 4, T_KERNEL = 5, T_RUNTIME = 7,
-             T_DRIVER = 8, T_CPU_INSTANT = 9, T_OVERHEAD = 11, T_MTIA_COUNTERS = 17, T_XPU_RUNTIME = 21, T_XPU_DRIVER = 22,
+             T_DRIVER = 8, T_CPU_INSTANT = 9, T_OVERHEAD = 11, T_CUDA_SYNC = 15, T_CUDA_EVENT = 16, T_MTIA_COUNTERS = 17, T_XPU_RUNTIME = 21, T_XPU_DRIVER = 22,
              T_PU1_RUNTIME = 24, T_PU1_DRIVER = 25, T_XPU_SCOPE = 26, T_HW_COUNTERS = 28, T_COUNT = 29 };
 const char* kTypeNames[T_COUNT] = {  // libkineto/include/ActivityType.h:80-112
     "cpu_op", "user_annotation", "gpu_user_annotation", "gpu_memcpy", "gpu_memset", "kernel",
@@ -65,6 +68,8 @@ size_t recSize(uint32_t kind) {
     case K_RUNTIME: case K_DRIVER: return 40;
     case K_EXTCORR: return 24;
     case K_OVERHEAD: return 56;  // CUpti_ActivityOverhead3
+    case K_SYNC: return 40;      // CUpti_ActivitySynchronization
+    case K_CUDA_EVENT: return 56;  // CUpti_ActivityCudaEvent2
     default: return 0;
   }
 }
@@ -184,6 +189,7 @@ struct Out {
   std::string buf;
   int64_t base;
   Counters* c;
+  std::set<int64_t> syncRows;  // syncStreamMetadataEmitted_, output_json.cpp:919-920
   int64_t rel(int64_t t) const { int64_t r = t - base; return r < 0 ? 0 : r; }
   void xEvent(const char* cat, const std::string& name, int64_t pid, int64_t tid, int64_t ts, int64_t dur, const std::string& args) {
     buf += "\n  {\n    \"ph\": \"X\",\n    \"cat\": \""; buf += cat;
@@ -214,7 +220,9 @@ struct Out {
 struct Event {
   int type; std::string name; int64_t ts, dur, device, resource; bool hasLinked; int64_t linkedId;
   int64_t corrId; std::string md; int64_t flowId; int flowType; bool flowStart;
+  bool streamSync = false;  // a CUDA_SYNC activity named "Stream Sync": shown on a row of its own
 };
+constexpr int64_t kSyncStreamTidOffset = 1000000;  // output_json.h:237
 void emit(Out& o, const Event& e) {
   int64_t ts = e.ts, dur = e.dur < 0 ? 0 : e.dur;
   if (e.type == T_GPU_USER_ANNOTATION) { ts -= 1; dur += 2; }
@@ -232,10 +240,27 @@ void emit(Out& o, const Event& e) {
   std::string md = e.md;
   sanitize(md);
   if (!md.empty() && !allSpace(md)) { if (!args.empty()) args += ","; args += md; }
-  o.xEvent(kTypeNames[e.type], eventName(e.name), e.device, sanitizeTid(e.resource), o.rel(ts), dur, args);
+  int64_t resource = e.resource;
+  if (e.streamSync) {  // output_json.cpp:914-943: two metadata rows the first time a (device, row) pair shows up
+    const int64_t syncTid = resource + kSyncStreamTidOffset;
+    if (o.syncRows.insert((int64_t)((uint64_t)e.device << 32) | syncTid).second) {
+      const int64_t mt = o.rel(ts);
+      for (int k = 0; k < 2; k++) {
+        o.buf += k == 0 ? "\n  {\n    \"name\": \"thread_name\", \"ph\": \"M\", \"ts\": " : "\n  {\n    \"name\": \"thread_sort_index\", \"ph\": \"M\", \"ts\": ";
+        appendTs(o.buf, mt);
+        o.buf += ", \"pid\": "; appendI(o.buf, e.device);
+        o.buf += ", \"tid\": "; appendI(o.buf, syncTid);
+        o.buf += k == 0 ? ",\n    \"args\": {\n      \"name\": \"stream " : ",\n    \"args\": {\n      \"sort_index\": ";
+        appendI(o.buf, resource);
+        o.buf += k == 0 ? " (sync)\"\n    }\n  }," : "\n    }\n  },";
+      }
+    }
+    resource = syncTid;
+  }
+  o.xEvent(kTypeNames[e.type], eventName(e.name), e.device, sanitizeTid(resource), o.rel(ts), dur, args);
   if (e.flowId > 0) {
     const char* fname = e.flowType == 1 ? "fwdbwd" : e.flowType == 2 ? "ac2g" : nullptr;
-    if (fname) o.flow(e.flowStart ? 's' : 'f', e.flowId, e.device, sanitizeTid(e.resource), o.rel(e.ts), fname);
+    if (fname) o.flow(e.flowStart ? 's' : 'f', e.flowId, e.device, sanitizeTid(resource), o.rel(e.ts), fname);
   }
 }
 
@@ -260,6 +285,13 @@ struct Run {
   struct Span { int64_t start, end; size_t op; int64_t device, resource; };
   std::map<std::pair<int64_t, int64_t>, std::unordered_map<int64_t, Span>> userSpans;
   size_t seg[3] = {0, 0, 0};
+  // synchronisation records: context -> device (first writer wins), (context, event) -> CUDA event records
+  // ordered by correlation id, the (device, stream) pairs that showed GPU work, deferred stream-wait events
+  std::unordered_map<uint32_t, uint32_t> ctxToDev;
+  struct WaitInfo { uint32_t stream, corr; };
+  std::map<std::pair<uint32_t, uint32_t>, std::vector<WaitInfo>> waitEvents;
+  std::set<std::pair<int64_t, int64_t>> seenStreams;
+  std::vector<const uint8_t*> deferred;
 
   explicit Run(const K2JTraceFile& f) : tf(f), p(*f.ptr<k2jt_params>("PARAMS")) {
     out.base = p.base_time_ns; out.c = &c;
@@ -370,6 +402,81 @@ struct Run {
       if (kind == K_EXTCORR) { uint32_t ek = rd<uint32_t>(r, 4); if (ek != 3 && ek != 4) c.invalid_external_correlation++; }
     });
   }
+  void noteCtx(uint32_t ctx, uint32_t dev) { ctxToDev.emplace(ctx, dev); }  // updateCtxToDeviceId, CuptiActivityProfiler.cpp:221-239
+  void pass1Sync() {  // the rest of buildProcessingState, CuptiActivityProfiler.cpp:256-287
+    forEachRecord([&](const uint8_t* r, uint32_t kind) {
+      switch (kind) {
+        case K_KERNEL: noteCtx(rd<uint32_t>(r, 44), rd<uint32_t>(r, 40)); break;
+        case K_MEMCPY: case K_MEMSET: noteCtx(rd<uint32_t>(r, 36), rd<uint32_t>(r, 32)); break;
+        case K_MEMCPY2: noteCtx(rd<uint32_t>(r, 48), rd<uint32_t>(r, 44)); noteCtx(rd<uint32_t>(r, 56), rd<uint32_t>(r, 52)); break;
+        case K_CUDA_EVENT: {  // updateWaitEventMap, :243-254: kept sorted by correlation id, a new record goes before its equals
+          auto& v = waitEvents[{rd<uint32_t>(r, 8), rd<uint32_t>(r, 16)}];
+          const uint32_t corr = rd<uint32_t>(r, 4);
+          auto pos = std::lower_bound(v.begin(), v.end(), corr, [](const WaitInfo& w, uint32_t c) { return w.corr < c; });
+          v.insert(pos, WaitInfo{rd<uint32_t>(r, 12), corr});
+          break;
+        }
+        default: break;
+      }
+    });
+  }
+  uint32_t ctxDevice(uint32_t ctx) const { auto it = ctxToDev.find(ctx); return it == ctxToDev.end() ? 0 : it->second; }
+  static int32_t streamForTrace(uint32_t s) { return (int32_t)s; }  // streamIdForTrace, CuptiActivity.h:316-323
+  static const char* syncTypeStr(uint32_t t) {  // libkineto/src/cupti_strings.cpp:137-151
+    return t == 1 ? "Event Sync" : t == 2 ? "Stream Wait Event" : t == 3 ? "Stream Sync" : t == 4 ? "Context Sync" : "Unknown Sync";
+  }
+  void cudaEventRecord(const uint8_t* r) {  // handleCudaEventActivity, CuptiActivityProfiler.cpp:404-434
+    Event e; e.type = T_CUDA_EVENT; e.name = "cudaEvent";
+    const uint32_t corr = rd<uint32_t>(r, 4), ctx = rd<uint32_t>(r, 8), stream = rd<uint32_t>(r, 12);
+    e.ts = conv(rd<uint64_t>(r, 40)); e.dur = 1;
+    e.device = ctxDevice(ctx); e.resource = streamForTrace(stream);
+    e.hasLinked = linked(corr, &e.linkedId);
+    e.corrId = corr; e.flowId = corr; e.flowType = 2; e.flowStart = false;
+    if (outOfRange(e.ts, e.dur)) return;
+    Frag f;
+    f.u64("event_id", rd<uint32_t>(r, 16)); f.i64("stream", streamForTrace(stream)); f.u64("correlation", corr);
+    f.i64("device", e.device); f.u64("context", ctx);
+    e.md = f.j;
+    emit(out, e);
+  }
+  void logSync(const uint8_t* r) {  // the log_event functor of handleCudaSyncActivity, CuptiActivityProfiler.cpp:464-486
+    const uint32_t type = rd<uint32_t>(r, 4), corr = rd<uint32_t>(r, 24), ctx = rd<uint32_t>(r, 28), stream = rd<uint32_t>(r, 32);
+    const uint32_t event = rd<uint32_t>(r, 36);
+    int32_t srcStream = -1, srcCorr = -1;
+    const bool eventSync = type == 1 || type == 2;
+    if (eventSync) {  // getWaitEventInfo, :379-402: the last record whose correlation id is not above the query's
+      auto it = waitEvents.find({ctx, event});
+      if (it != waitEvents.end()) {
+        const auto& v = it->second;
+        auto pos = std::upper_bound(v.begin(), v.end(), corr, [](uint32_t c, const WaitInfo& w) { return c < w.corr; });
+        if (pos != v.begin()) { srcStream = (int32_t)std::prev(pos)->stream; srcCorr = (int32_t)std::prev(pos)->corr; }
+      }
+    }
+    Event e; e.type = T_CUDA_SYNC; e.name = syncTypeStr(type);
+    const uint64_t st = rd<uint64_t>(r, 8), en = rd<uint64_t>(r, 16);
+    e.ts = conv(st); e.dur = p.ts_mode ? conv(en) - conv(st) : (int64_t)(en - st);
+    e.device = ctxDevice(ctx); e.resource = streamForTrace(stream);
+    e.hasLinked = linked(corr, &e.linkedId);
+    e.corrId = corr; e.flowId = corr; e.flowType = 2; e.flowStart = false;
+    e.streamSync = type == 3;
+    if (outOfRange(e.ts, e.dur)) return;
+    Frag f;
+    f.str("cuda_sync_kind", syncTypeStr(type));
+    if (eventSync) {
+      f.i64("wait_on_stream", srcStream); f.i64("wait_on_cuda_event_record_corr_id", srcCorr); f.u64("wait_on_cuda_event_id", event);
+    }
+    f.i64("stream", streamForTrace(stream)); f.u64("correlation", corr); f.i64("device", e.device); f.u64("context", ctx);
+    e.md = f.j;
+    emit(out, e);
+  }
+  void syncRecord(const uint8_t* r) {  // handleCudaSyncActivity: stream-wait events wait for the end of the pass
+    if (rd<uint32_t>(r, 4) == 2) deferred.push_back(r);
+    else logSync(r);
+  }
+  void deferredSyncs() {  // logDeferredEvents, CuptiActivityProfiler.cpp:502-514
+    for (const uint8_t* r : deferred)
+      if (seenStreams.count({(int64_t)ctxDevice(rd<uint32_t>(r, 28)), (int64_t)rd<uint32_t>(r, 32)})) logSync(r);
+  }
   void pass1() {
     forEachRecord([&](const uint8_t* r, uint32_t kind) {
       if (kind != K_EXTCORR) return;
@@ -416,7 +523,8 @@ struct Run {
     e.hasLinked = linked(corr, &e.linkedId);
     e.corrId = corr; e.flowId = corr; e.flowType = 2; e.flowStart = false;
   }
-  void afterGpu(const Event& e) {  // GenericActivityProfiler.cpp:424-434
+  void afterGpu(const Event& e) {  // GenericActivityProfiler.cpp:419, :424-434
+    seenStreams.insert({e.device, e.resource});
     if (!(p.flags & 1)) return;
     auto it = userCorr.find(e.corrId);
     if (it == userCorr.end()) return;
@@ -593,6 +701,8 @@ struct Run {
       case K_OVERHEAD: return conv(rd<uint64_t>(r, 24));
       case K_RUNTIME: case K_DRIVER: return conv(rd<uint64_t>(r, 8));
       case K_KERNEL: case K_MEMCPY: case K_MEMCPY2: case K_MEMSET: return conv(rd<uint64_t>(r, 16));
+      case K_SYNC: return conv(rd<uint64_t>(r, 8));
+      case K_CUDA_EVENT: return conv(rd<uint64_t>(r, 40));
       default: return INT64_MIN;
     }
   }
@@ -617,9 +727,12 @@ struct Run {
         case K_MEMCPY2: memcpy2Record(r); break;
         case K_MEMSET: memsetRecord(r); break;
         case K_OVERHEAD: overheadRecord(r); break;
+        case K_SYNC: syncRecord(r); break;
+        case K_CUDA_EVENT: cudaEventRecord(r); break;
         default: c.unexpected++; break;
       }
     }
+    deferredSyncs();
   }
 
   void annotations() {  // GpuUserEventMap::logEvents, GenericActivityProfiler.cpp:320-327
@@ -638,7 +751,7 @@ struct Run {
     for (size_t i = 0; i < tf.count<int32_t>("TIDMAP") / 2; i++) tidMap.emplace(tm[2 * i], tm[2 * i + 1]);
     cpuOps();
     seg[0] = out.buf.size();
-    if (p.mode != 0) { if (globalJoin()) pass1Global(); else pass1(); pass2(); }
+    if (p.mode != 0) { if (globalJoin()) pass1Global(); else pass1(); pass1Sync(); pass2(); }
     seg[1] = out.buf.size();
     if (p.mode != 0) annotations();
     seg[2] = out.buf.size();

@@ -50,6 +50,9 @@ size_t recordSize(uint32_t kind) {
     case CUPTI_ACTIVITY_KIND_RUNTIME:
     case CUPTI_ACTIVITY_KIND_DRIVER: return sizeof(CUpti_ActivityAPI);
     case CUPTI_ACTIVITY_KIND_EXTERNAL_CORRELATION: return sizeof(CUpti_ActivityExternalCorrelation);
+    case CUPTI_ACTIVITY_KIND_OVERHEAD: return sizeof(CUpti_ActivityOverhead3);
+    case CUPTI_ACTIVITY_KIND_SYNCHRONIZATION: return sizeof(CUpti_ActivitySynchronization);
+    case CUPTI_ACTIVITY_KIND_CUDA_EVENT: return sizeof(CUpti_ActivityCudaEvent2);
     default: return 0;
   }
 }

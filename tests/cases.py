@@ -169,12 +169,119 @@ def overhead_mix_trace(n=3000, seed=41, flags=0) -> tf.Trace:
     return b.build()
 
 
+def sync_trace(flags=0) -> tf.Trace:
+    """CUDA synchronisation and CUDA event records (CUPTI_ACTIVITY_KIND_SYNCHRONIZATION / CUDA_EVENT): the
+    context -> device map, the (context, event) -> record lookup, deferred stream-wait events, the
+    dedicated row of stream syncs and its once-per-row metadata."""
+    NO = 0xFFFFFFFF
+    b = synth.TraceBuilder(n_devices=4, flags=flags, buffer_bytes=1 << 20)
+    t0 = b.t0
+    b.window = (t0, t0 + 1_000_000)
+    b.op(t0 + 100, t0 + 900, 1, "aten::sync_user")
+    b.op(t0 + 100, t0 + 900, 2, "aten::other")
+    # a sync before any record names its context: device 0
+    b.sync(t0 + 10, t0 + 20, 200, type=tf.SYNC_TYPE_CONTEXT_SYNCHRONIZE, context=5, stream=NO)
+    b.kernel(t0 + 100, t0 + 200, 201, "on device 1", device=1, context=5, stream=9)
+    b.kernel(t0 + 100, t0 + 200, 202, "second writer of context 5", device=3, context=5, stream=9)
+    b.memcpy(t0 + 100, t0 + 110, 203, 64, device=2, context=6, stream=11)
+    b.memset(t0 + 100, t0 + 110, 204, 64, device=3, context=7, stream=12)
+    b.memcpy_p2p(t0 + 100, t0 + 110, 205, 64, device=0, context=1, stream=7, src_device=2, src_context=8,
+                 dst_device=3, dst_context=9)
+    b.memcpy_p2p(t0 + 100, t0 + 110, 206, 64, device=0, context=1, stream=7, src_device=1, src_context=10,
+                 dst_device=2, dst_context=10)
+    b.kernel(t0 - 500, t0 - 400, 207, "out of window: still names context 11", device=2, context=11, stream=13)
+    # CUDA events: several records per (context, event)
+    b.extcorr(300, 1)
+    b.cuda_event(t0 + 300, 300, event=70, context=5, stream=9)
+    b.cuda_event(t0 + 310, 310, event=70, context=5, stream=10)
+    b.cuda_event(t0 + 320, 320, event=70, context=5, stream=NO)
+    b.cuda_event(t0 + 330, 310, event=70, context=5, stream=14)     # same correlation id as an earlier record
+    b.cuda_event(t0 + 340, 305, event=70, context=6, stream=15)     # other context
+    b.cuda_event(t0 + 350, 0, event=71, context=5, stream=16)       # correlation 0: no flow
+    b.cuda_event(t0 - 5, 301, event=72, context=5, stream=9)        # before the window
+    b.cuda_event(t0 + 1_000_000, 302, event=72, context=5, stream=9)  # ts + 1 ns ends after the window
+    b.cuda_event(0, 303, event=73, context=12, stream=9)            # unknown context
+    b.new_buffer()
+    # synchronisation records
+    b.extcorr(400, 2)
+    b.sync(t0 + 400, t0 + 450, 400, type=tf.SYNC_TYPE_EVENT_SYNCHRONIZE, context=5, stream=NO, event=70)  # before every record
+    b.sync(t0 + 400, t0 + 450, 309, type=tf.SYNC_TYPE_EVENT_SYNCHRONIZE, context=5, stream=9, event=70)   # -> record 300
+    b.sync(t0 + 400, t0 + 450, 310, type=tf.SYNC_TYPE_EVENT_SYNCHRONIZE, context=5, stream=9, event=70)   # equal id
+    b.sync(t0 + 400, t0 + 450, 315, type=tf.SYNC_TYPE_EVENT_SYNCHRONIZE, context=5, stream=9, event=70)
+    b.sync(t0 + 400, t0 + 450, 1000, type=tf.SYNC_TYPE_EVENT_SYNCHRONIZE, context=5, stream=9, event=70)  # -> stream -1
+    b.sync(t0 + 400, t0 + 450, 299, type=tf.SYNC_TYPE_EVENT_SYNCHRONIZE, context=5, stream=9, event=70)   # none precedes
+    b.sync(t0 + 400, t0 + 450, 500, type=tf.SYNC_TYPE_EVENT_SYNCHRONIZE, context=6, stream=11, event=70)
+    b.sync(t0 + 400, t0 + 450, 500, type=tf.SYNC_TYPE_EVENT_SYNCHRONIZE, context=6, stream=11, event=99)  # unknown event
+    b.sync(t0 + 500, t0 + 560, 501, type=tf.SYNC_TYPE_STREAM_SYNCHRONIZE, context=5, stream=9)
+    b.sync(t0 + 510, t0 + 570, 0, type=tf.SYNC_TYPE_STREAM_SYNCHRONIZE, context=5, stream=9)             # same row: no metadata
+    b.sync(t0 + 520, t0 + 580, 502, type=tf.SYNC_TYPE_STREAM_SYNCHRONIZE, context=6, stream=9)            # other device
+    b.sync(t0 - 50, t0 + 10, 503, type=tf.SYNC_TYPE_STREAM_SYNCHRONIZE, context=7, stream=12)             # out of window ...
+    b.sync(t0 + 530, t0 + 531, 504, type=tf.SYNC_TYPE_STREAM_SYNCHRONIZE, context=7, stream=12)           # ... so this one is first
+    b.sync(t0 + 540, t0 + 541, 505, type=tf.SYNC_TYPE_STREAM_SYNCHRONIZE, context=7, stream=NO)
+    b.sync(t0 + 550, t0 + 540, 506, type=tf.SYNC_TYPE_STREAM_SYNCHRONIZE, context=77, stream=3)           # negative duration
+    b.sync(t0 + 560, t0 + 565, 507, type=tf.SYNC_TYPE_CONTEXT_SYNCHRONIZE, context=9, stream=NO)
+    b.sync(t0 + 570, t0 + 575, 508, type=0, context=8, stream=4)
+    b.sync(t0 + 580, t0 + 585, 509, type=99, context=10, stream=4, event=70)
+    # stream-wait events: deferred to the end, dropped on streams without GPU work in the window
+    b.sync(t0 + 600, t0 + 605, 320, type=tf.SYNC_TYPE_STREAM_WAIT_EVENT, context=5, stream=9, event=70)    # (1, 9) seen
+    b.sync(t0 + 610, t0 + 615, 321, type=tf.SYNC_TYPE_STREAM_WAIT_EVENT, context=5, stream=10, event=70)   # (1, 10) never
+    b.sync(t0 + 620, t0 + 625, 322, type=tf.SYNC_TYPE_STREAM_WAIT_EVENT, context=11, stream=13, event=1)   # only out of window
+    b.sync(t0 + 630, t0 + 635, 323, type=tf.SYNC_TYPE_STREAM_WAIT_EVENT, context=6, stream=21, event=70)   # seen later
+    b.sync(t0 - 30, t0 + 635, 324, type=tf.SYNC_TYPE_STREAM_WAIT_EVENT, context=5, stream=9, event=70)     # out of window
+    b.sync(t0 + 640, t0 + 645, 400, type=tf.SYNC_TYPE_STREAM_WAIT_EVENT, context=6, stream=11, event=70)   # linked
+    b.sync(t0 + 650, t0 + 655, 325, type=tf.SYNC_TYPE_STREAM_WAIT_EVENT, context=5, stream=NO, event=70)
+    b.new_buffer()
+    b.kernel(t0 + 700, t0 + 800, 600, "makes (2, 21) a seen stream", device=2, context=6, stream=21)
+    b.kernel(t0 + 700, t0 + 800, 601, "after the deferred records", device=1, context=5, stream=NO)
+    b.runtime(t0 + 700, t0 + 710, 602)
+    return b.build()
+
+
+def sync_mix_trace(n=3000, seed=43, flags=0) -> tf.Trace:
+    """Random mixture with synchronisation and CUDA event records: few contexts, events and streams, so that
+    lookups hit records with equal and neighbouring correlation ids and stream-wait events meet both seen
+    and unseen streams; small buffers."""
+    rng = np.random.default_rng(seed)
+    b = synth.TraceBuilder(n_devices=4, flags=flags, buffer_bytes=1 << 20)
+    t0 = b.t0
+    b.window = (t0, t0 + 100_000)
+    for i in range(n // 20):
+        b.op(t0 + 100 * i, t0 + 100 * i + 60, i + 1, "aten::op%d" % (i % 7))
+    for i in range(n):
+        ts = t0 - 2000 + 37 * i            # the first and the last records fall outside the window
+        k = int(rng.integers(0, 10))
+        corr = 1000 + int(rng.integers(0, n // 4))
+        ctx = int(rng.integers(1, 7))
+        stream = int(rng.choice([7, 8, 9, 20, 0xFFFFFFFF]))
+        if k == 0:
+            b.extcorr(corr, int(rng.integers(1, n // 20 + 5)))
+        elif k == 1:
+            b.runtime(ts, ts + 20, corr)
+        elif k == 2:
+            b.kernel(ts, ts + int(rng.integers(1, 500)), corr, "k%d" % (i % 13), device=int(rng.integers(0, 4)), context=ctx,
+                     stream=stream)
+        elif k == 3:
+            b.memcpy(ts, ts + int(rng.integers(0, 90)), corr, 4096, device=int(rng.integers(0, 4)), context=ctx, stream=stream)
+        elif k == 4:
+            b.memcpy_p2p(ts, ts + 7, corr, 64, device=0, context=ctx, stream=stream, src_device=int(rng.integers(0, 4)),
+                         src_context=int(rng.integers(1, 9)), dst_device=int(rng.integers(0, 4)), dst_context=int(rng.integers(1, 9)))
+        elif k in (5, 6):
+            b.cuda_event(ts, corr, event=int(rng.integers(1, 6)), context=ctx, stream=stream)
+        else:
+            b.sync(ts, ts + int(rng.integers(0, 60)), corr, type=int(rng.integers(0, 6)), context=int(rng.integers(1, 9)),
+                   stream=stream, event=int(rng.integers(1, 7)))
+        if rng.random() < 0.004:
+            b.new_buffer()
+    return b.build()
+
+
 CASES = {
     "edge": edge_trace,
     "generic_300": lambda: synth.gen_generic_kernels(300, seed=31, pool_size=40),
     "launches_150": lambda: synth.gen_kernel_launches(150, seed=32, pool_size=50),
     "mixed_400": lambda: synth.gen_mixed(400, seed=33, pool_size=100, escape_fraction=0.2),
     "tsc_100": lambda: tsc_trace(100),
+    "sync": sync_trace,
 }
 
 

@@ -44,7 +44,11 @@ def test_golden_container_is_reproducible(name):
     cases.annotation_trace,
     cases.overhead_mix_trace,
     lambda: synth.gen_kernel_launches(4000, seed=105, pool_size=100, user_annotations=25),
-], ids=["generic", "launches", "shard", "mixed", "tsc", "edge", "edge_annot", "annotations", "overhead_mix", "launches_annot"])
+    cases.sync_trace,
+    cases.sync_mix_trace,
+    lambda: cases.sync_mix_trace(5000, seed=44, flags=1),
+], ids=["generic", "launches", "shard", "mixed", "tsc", "edge", "edge_annot", "annotations", "overhead_mix", "launches_annot",
+        "sync", "sync_mix", "sync_mix_annot"])
 def test_port_matches_live_reference(gen):
     trace = gen()
     doc, _ = helpers.run_ref(trace)
@@ -82,6 +86,26 @@ def test_reference_known_answers_in_port_output():
     assert b'"name": "Memcpy HtoD (Pinned -> Device)"' in out
     assert b'"name": "cudaMemcpy"' in out
     assert b'"name": "Kernel"' in out
+
+
+def test_reference_sync_known_answers_in_port_output():
+    """The out-of-order case of the reference's own test (libkineto/test/CuptiActivityProfilerTest.cpp:660-740):
+    a stream-wait event and an event sync come before the CUDA event record and the kernel they refer to; both
+    must name the record's correlation id and stream, and the wait event shows because its stream has a kernel."""
+    b = synth.TraceBuilder(n_devices=4)
+    t0 = b.t0
+    for name, s, e, i in [("op1", 10, 50, 1), ("op_record", 60, 80, 100), ("op_wait", 90, 110, 200), ("op_evt_sync", 120, 140, 300)]:
+        b.op(t0 + s, t0 + e, i, name)
+    b.runtime(t0 + 10, t0 + 20, 1)
+    b.sync(t0 + 100, t0 + 110, 200, type=tf.SYNC_TYPE_STREAM_WAIT_EVENT, context=7, stream=13, event=7777)
+    b.sync(t0 + 120, t0 + 140, 300, type=tf.SYNC_TYPE_EVENT_SYNCHRONIZE, context=7, stream=0xFFFFFFFF, event=7777)
+    b.cuda_event(t0 + 25, 100, event=7777, context=7, stream=11)
+    b.kernel(t0 + 30, t0 + 50, 1, "k", device=3, context=7, stream=13)
+    out, _ = helpers.run_port(b.build())
+    want = b'"wait_on_stream": 11, "wait_on_cuda_event_record_corr_id": 100, "wait_on_cuda_event_id": 7777'
+    assert out.count(b'"cuda_sync_kind": "Stream Wait Event", ' + want) == 1
+    assert out.count(b'"cuda_sync_kind": "Event Sync", ' + want) == 1
+    assert out.rfind(b'"name": "Stream Wait Event"') > out.rfind(b'"cat": "kernel"')   # deferred to the end of the pass
 
 
 def test_port_double_formatting_known_answers():
