@@ -68,7 +68,7 @@ struct k2j_ctx {
   DevBuf ds_tab, span_key, span_nstart, span_end, span_nfirst, span_row, span_out, span_cnt, ann_size, ann_off;
   DevBuf sort_keys[2], sort_vals[2], sort_hist, sort_base, sort_rank;
   DevBuf tid_tab, corr_tab, user_tab, op_tab, work_slot, work_ev, ev_size, ev_off, ev_ext, out, counters;
-  uint64_t* h_totals = nullptr;   // pinned, 16 words: [0, C_NCOL) column totals, 10 text bytes, 11 bytes of CPU-op text, 12 annotation bytes, 13 sort, 14 scan entry point
+  uint64_t* h_totals = nullptr;   // pinned, 32 words: [0, C_NCOL) column totals, 20 text bytes, 21 bytes of CPU-op text, 22 annotation bytes, 23 sort, 24 scan entry point
   Counters* h_counters = nullptr; // pinned
   cudaEvent_t ev[8]{};
   uint64_t out_bytes = 0;
@@ -77,6 +77,7 @@ struct k2j_ctx {
   uint64_t totals[C_NCOL] = {0};
   uint32_t launches = 0;
   DevBuf ext_local;
+  DevBuf ctx_tab, evt_recs, seen_tab, row_key, row_first, corr_zero;  // synchronisation records
   const void* g_ext = nullptr; uint64_t g_n_ext = 0, g_own_begin = 0;
   const int32_t* g_op_ids = nullptr; uint64_t g_n_ops = 0;
 };
@@ -140,14 +141,8 @@ k2j_status run_scan(k2j_ctx* c, const uint32_t* in, uint64_t n, uint32_t cols, u
   return K2J_OK;
 }
 
-// Stable LSD radix sort of the GPU-side events by start timestamp; afterwards work_ev holds sorted ranks.
-k2j_status sort_gpu_events(k2j_ctx* c, uint64_t n) {
-  cudaStream_t s = c->stream;
-  Dev& d = c->d;
-  const uint64_t span = (uint64_t)(c->params.window_end_ns - c->params.window_start_ns);
-  int bits = 1;
-  while (bits < 64 && ((span + 1) >> bits)) bits++;
-  const int passes = (bits + 7) / 8;
+// Workspaces of the radix sort for n pairs.
+k2j_status sort_reserve(k2j_ctx* c, uint64_t n) {
   const uint32_t tiles = (uint32_t)((n + kSortTile - 1) / kSortTile);
   for (int i = 0; i < 2; i++) {
     K2J_CUDA(c, c->sort_keys[i].reserve(n * 8));
@@ -155,16 +150,19 @@ k2j_status sort_gpu_events(k2j_ctx* c, uint64_t n) {
   }
   K2J_CUDA(c, c->sort_hist.reserve((size_t)tiles * 256 * 4));
   K2J_CUDA(c, c->sort_base.reserve((size_t)tiles * 256 * 8));
-  K2J_CUDA(c, c->sort_rank.reserve(n * 4));
-  const uint32_t wl_blocks = (uint32_t)((d.ops_begin + 255) / 256);
-  k_sort_keys<<<wl_blocks, 256, 0, s>>>(d, c->sort_keys[0].as<uint64_t>(), c->sort_vals[0].as<uint32_t>(), span);
-  c->launches++;
-  int cur = 0;
+  return K2J_OK;
+}
+// Stable sort of the n pairs in sort_keys[*cur] / sort_vals[*cur] by the low 8 * passes bits of the key; *cur names
+// the buffers that hold the result.
+k2j_status sort_passes(k2j_ctx* c, uint64_t n, int passes, int* cur_io) {
+  cudaStream_t s = c->stream;
+  const uint32_t tiles = (uint32_t)((n + kSortTile - 1) / kSortTile);
+  int cur = *cur_io;
   for (int pass = 0; pass < passes; pass++) {
     k_rs_hist<<<tiles, kSortThreads, 0, s>>>(c->sort_keys[cur].as<uint64_t>(), n, 8 * pass, c->sort_hist.as<uint32_t>(), tiles);
     c->launches++;
     k2j_status st = run_scan(c, c->sort_hist.as<uint32_t>(), (uint64_t)tiles * 256, 1, c->sort_base.as<uint64_t>(),
-                             c->scan_totals.as<uint64_t>() + 13, &c->launches);
+                             c->scan_totals.as<uint64_t>() + 23, &c->launches);
     if (st) return st;
     k_rs_scatter<<<tiles, kSortThreads, 0, s>>>(c->sort_keys[cur].as<uint64_t>(), c->sort_vals[cur].as<uint32_t>(), n, 8 * pass,
                                                 c->sort_base.as<uint64_t>(), tiles, c->sort_keys[cur ^ 1].as<uint64_t>(),
@@ -172,6 +170,51 @@ k2j_status sort_gpu_events(k2j_ctx* c, uint64_t n) {
     c->launches++;
     cur ^= 1;
   }
+  *cur_io = cur;
+  K2J_CUDA(c, cudaGetLastError());
+  return K2J_OK;
+}
+
+// CUDA event records ordered by (context, event, correlation id, position): two stable sorts, by correlation id
+// and then by context << 32 | event id.  The lookups of synchronisation records search the result.
+k2j_status sort_cuda_events(k2j_ctx* c, uint64_t n) {
+  cudaStream_t s = c->stream;
+  Dev& d = c->d;
+  k2j_status st = sort_reserve(c, n);
+  if (st) return st;
+  K2J_CUDA(c, c->evt_recs.reserve(n * sizeof(EvtRec)));
+  const uint32_t blocks = (uint32_t)((n + 255) / 256);
+  int cur = 0;
+  k_evt_keys<<<blocks, 256, 0, s>>>(d, c->sort_keys[cur].as<uint64_t>(), c->sort_vals[cur].as<uint32_t>(), 0);
+  c->launches++;
+  if ((st = sort_passes(c, n, 4, &cur))) return st;
+  k_evt_keys<<<blocks, 256, 0, s>>>(d, c->sort_keys[cur].as<uint64_t>(), c->sort_vals[cur].as<uint32_t>(), 1);
+  c->launches++;
+  if ((st = sort_passes(c, n, 8, &cur))) return st;
+  k_evt_finish<<<blocks, 256, 0, s>>>(d, c->sort_keys[cur].as<uint64_t>(), c->sort_vals[cur].as<uint32_t>(), c->evt_recs.as<EvtRec>());
+  c->launches++;
+  K2J_CUDA(c, cudaGetLastError());
+  d.evt = c->evt_recs.as<EvtRec>(); d.n_evt = (uint32_t)n;
+  return K2J_OK;
+}
+
+// Stable LSD radix sort of the GPU-side events by start timestamp; afterwards work_ev holds sorted ranks.
+k2j_status sort_gpu_events(k2j_ctx* c, uint64_t n) {
+  cudaStream_t s = c->stream;
+  Dev& d = c->d;
+  const uint64_t span = (uint64_t)(c->params.window_end_ns - c->params.window_start_ns);
+  const uint64_t max_key = c->totals[C_WAIT] ? 2 * span + 3 : span + 1;  // deferred records sort behind the rest
+  int bits = 1;
+  while (bits < 64 && (max_key >> bits)) bits++;
+  const int passes = (bits + 7) / 8;
+  k2j_status st0 = sort_reserve(c, n);
+  if (st0) return st0;
+  K2J_CUDA(c, c->sort_rank.reserve(n * 4));
+  const uint32_t wl_blocks = (uint32_t)((d.ops_begin + 255) / 256);
+  k_sort_keys<<<wl_blocks, 256, 0, s>>>(d, c->sort_keys[0].as<uint64_t>(), c->sort_vals[0].as<uint32_t>(), span);
+  c->launches++;
+  int cur = 0;
+  if ((st0 = sort_passes(c, n, passes, &cur))) return st0;
   k_rs_invert<<<(uint32_t)((n + 255) / 256), 256, 0, s>>>(c->sort_vals[cur].as<uint32_t>(), n, c->sort_rank.as<uint32_t>());
   k_sort_remap<<<wl_blocks, 256, 0, s>>>(d, c->sort_rank.as<uint32_t>());
   c->launches += 2;
@@ -217,11 +260,11 @@ k2j_status order_annotations(k2j_ctx* c, uint32_t span_cap, uint32_t* n_out, uin
       d, c->span_out.as<SpanRec>(), n, c->ann_size.as<uint32_t>(), nullptr, 0);
   c->launches++;
   K2J_CUDA(c, cudaGetLastError());
-  k2j_status st = run_scan(c, c->ann_size.as<uint32_t>(), n, 1, c->ann_off.as<uint64_t>(), c->scan_totals.as<uint64_t>() + 12, &c->launches);
+  k2j_status st = run_scan(c, c->ann_size.as<uint32_t>(), n, 1, c->ann_off.as<uint64_t>(), c->scan_totals.as<uint64_t>() + 22, &c->launches);
   if (st) return st;
-  K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 12, c->scan_totals.as<uint64_t>() + 12, 8, cudaMemcpyDeviceToHost, s));
+  K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 22, c->scan_totals.as<uint64_t>() + 22, 8, cudaMemcpyDeviceToHost, s));
   K2J_CUDA(c, cudaStreamSynchronize(s));  // also covers `ordered`, which goes out of scope
-  *bytes_out = c->h_totals[12];
+  *bytes_out = c->h_totals[22];
   return K2J_OK;
 }
 
@@ -245,9 +288,9 @@ k2j_status k2j_create(int device, void* stream, k2j_ctx** out) {
     if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) { delete c; return K2J_ERR_CUDA; }
     c->own_stream = true;
   }
-  bool ok = cudaMallocHost((void**)&c->h_totals, 16 * sizeof(uint64_t)) == cudaSuccess &&
+  bool ok = cudaMallocHost((void**)&c->h_totals, 32 * sizeof(uint64_t)) == cudaSuccess &&
             cudaMallocHost((void**)&c->h_counters, sizeof(Counters)) == cudaSuccess &&
-            c->counters.reserve(sizeof(Counters)) == cudaSuccess && c->scan_totals.reserve(16 * 8) == cudaSuccess;
+            c->counters.reserve(sizeof(Counters)) == cudaSuccess && c->scan_totals.reserve(32 * 8) == cudaSuccess;
   for (auto& e : c->ev) ok = ok && cudaEventCreate(&e) == cudaSuccess;
   if (!ok) { k2j_destroy(c); return K2J_ERR_CUDA; }
   *out = c;
@@ -267,7 +310,8 @@ void k2j_destroy(k2j_ctx* c) {
                     &c->chunk_base, &c->scan_sums, &c->scan_totals, &c->ds_tab, &c->span_key, &c->span_nstart, &c->span_end, &c->span_nfirst, &c->span_row,
                     &c->span_out, &c->span_cnt, &c->ann_size, &c->ann_off, &c->sort_keys[0], &c->sort_keys[1], &c->sort_vals[0],
                     &c->sort_vals[1], &c->sort_hist, &c->sort_base, &c->sort_rank, &c->tid_tab, &c->corr_tab, &c->user_tab, &c->op_tab,
-                    &c->work_slot, &c->work_ev, &c->ev_size, &c->ev_off, &c->ev_ext, &c->out, &c->counters, &c->ext_local})
+                    &c->work_slot, &c->work_ev, &c->ev_size, &c->ev_off, &c->ev_ext, &c->out, &c->counters, &c->ext_local, &c->ctx_tab, &c->evt_recs,
+                    &c->seen_tab, &c->row_key, &c->row_first, &c->corr_zero})
     b->release();
   if (c->h_totals) cudaFreeHost(c->h_totals);
   if (c->h_counters) cudaFreeHost(c->h_counters);
@@ -487,7 +531,8 @@ k2j_status k2j_segment(k2j_ctx* c, k2j_segment_info* info) {
   }
   d.ops_begin = pos;
   d.n_work = pos + c->n_ops;
-  d.n_events = c->n_ops + totals[C_EVENTS];
+  d.n_events = c->n_ops + totals[C_EVENTS] + totals[C_WAIT];
+  d.wait_ev_base = c->n_ops + totals[C_EVENTS];
   if (d.n_events >= 0xFFFFFFF0ull) return fail(c, K2J_ERR_INVALID_ARGUMENT, "more than 2^32 events in one call");
   K2J_CUDA(c, c->work_slot.reserve(std::max<uint64_t>(1, pos) * 4));
   K2J_CUDA(c, c->work_ev.reserve(std::max<uint64_t>(1, pos) * 4));
@@ -499,7 +544,7 @@ k2j_status k2j_segment(k2j_ctx* c, k2j_segment_info* info) {
   K2J_CUDA(c, cudaEventRecord(c->ev[1], s));
   c->segmented = true;
   if (info) {
-    info->n_records = totals[C_EVENTS] + totals[C_EXT] + totals[C_UNEXPECTED];
+    info->n_records = totals[C_EVENTS] + totals[C_WAIT] + totals[C_EXT] + totals[C_UNEXPECTED];
     info->n_external = totals[C_EXT];
     info->external_records = reinterpret_cast<const k2j_external_record*>(d.ext_local);
     info->n_ops = c->n_ops;
@@ -533,7 +578,10 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
   cudaStream_t s = c->stream;
   Dev& d = c->d;
   const uint64_t* totals = c->totals;
-  const uint64_t n_gpu_events = totals[C_EVENTS];
+  const uint64_t n_gpu_events = totals[C_EVENTS] + totals[C_WAIT];
+  const uint64_t n_sync = totals[C_SYNC] + totals[C_WAIT], n_cuda_events = totals[C_CUDAEVENT];
+  if (n_sync + n_cuda_events > 0 && c->have_global_join)
+    return fail(c, K2J_ERR_UNSUPPORTED, "synchronisation and CUDA event records across shards are not implemented");
   K2J_CUDA(c, cudaEventRecord(c->ev[6], s));
 
   // ---- join tables ----
@@ -604,6 +652,38 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
     K2J_CUDA(c, cudaMemsetAsync(d.need_op, 0, op_bits / 8, s));
     if (d.ops_begin) { k_mark_corr<<<(uint32_t)((d.ops_begin + 255) / 256), 256, 0, s>>>(d); c->launches++; }
   }
+  // synchronisation and CUDA event records: their lookup structures exist only when such records do
+  d.ctx_tab = nullptr; d.evt = nullptr; d.n_evt = 0; d.seen_tab = nullptr; d.row_key = nullptr; d.row_first = nullptr; d.corr_zero = nullptr;
+  d.work_origin = 0; d.wait_pass = 0;
+  if (n_sync + n_cuda_events > 0) {
+    K2J_CUDA(c, c->corr_zero.reserve(corr_cap / 8 + 8));
+    d.corr_zero = c->corr_zero.as<uint32_t>();
+    K2J_CUDA(c, cudaMemsetAsync(d.corr_zero, 0, corr_cap / 8 + 8, s));
+    const uint32_t ctx_cap = 1u << 14;   // distinct CUDA contexts of one trace: a few per device
+    K2J_CUDA(c, c->ctx_tab.reserve((size_t)ctx_cap * 8));
+    d.ctx_tab = c->ctx_tab.as<unsigned long long>(); d.ctx_mask = ctx_cap - 1;
+    K2J_CUDA(c, cudaMemsetAsync(d.ctx_tab, 0, (size_t)ctx_cap * 8, s));
+    const uint64_t n_named = d.cls_begin[C_OVERHEAD] - d.cls_begin[C_KERNEL];
+    if (n_named) { k_build_ctx<<<(uint32_t)((n_named + 255) / 256), 256, 0, s>>>(d); c->launches++; }
+    if (n_sync && n_cuda_events) {
+      k2j_status st = sort_cuda_events(c, n_cuda_events);
+      if (st) return st;
+    }
+    if (totals[C_WAIT]) {
+      const uint32_t seen_cap = 1u << 16;  // (device, stream) pairs
+      K2J_CUDA(c, c->seen_tab.reserve((size_t)seen_cap * 8));
+      d.seen_tab = c->seen_tab.as<unsigned long long>(); d.seen_mask = seen_cap - 1;
+      K2J_CUDA(c, cudaMemsetAsync(d.seen_tab, 0, (size_t)seen_cap * 8, s));
+    }
+    if (totals[C_SYNC]) {
+      const uint32_t row_cap = pow2_at_least(2 * totals[C_SYNC] + 16);
+      K2J_CUDA(c, c->row_key.reserve((size_t)row_cap * 8));
+      K2J_CUDA(c, c->row_first.reserve((size_t)row_cap * 4));
+      d.row_key = c->row_key.as<unsigned long long>(); d.row_first = c->row_first.as<uint32_t>(); d.row_mask = row_cap - 1;
+      K2J_CUDA(c, cudaMemsetAsync(d.row_key, 0, (size_t)row_cap * 8, s));
+      K2J_CUDA(c, cudaMemsetAsync(d.row_first, 0xFF, (size_t)row_cap * 4, s));
+    }
+  }
   if (d.n_ext_all) { k_build_corr<<<(uint32_t)((d.n_ext_all + 255) / 256), 256, 0, s>>>(d, own_begin, own_end); c->launches++; }
   if (d.n_join_ops) { k_build_ops<<<(uint32_t)((d.n_join_ops + 255) / 256), 256, 0, s>>>(d); c->launches++; }
   if (d.n_ext_all) { k_resolve_corr<<<(corr_cap + 255) / 256, 256, 0, s>>>(d); c->launches++; }
@@ -615,6 +695,8 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
     k2j_status st = sort_gpu_events(c, n_gpu_events);
     if (st) return st;
   }
+  // the first stream sync of every (device, stream) row, in emission order
+  if (totals[C_SYNC]) { k_sync_rows<<<(uint32_t)((totals[C_SYNC] + 255) / 256), 256, 0, s>>>(d); c->launches++; }
 
   // ---- size pass, scan, emit pass ----
   uint64_t total_bytes = 0, ann_bytes = 0;
@@ -623,16 +705,23 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
     const uint32_t ev_blocks = (uint32_t)((d.n_work + kEventThreads - 1) / kEventThreads);
     k_events<false><<<ev_blocks, kEventThreads, 0, s>>>(d);
     c->launches++;
+    if (totals[C_WAIT]) {  // deferred synchronisation records: sized once every stream with GPU work is known
+      Dev dw = d;
+      dw.wait_pass = 1; dw.work_origin = d.cls_begin[C_WAIT];
+      dw.n_work = d.cls_begin[C_WAIT] + ((totals[C_WAIT] + 31) & ~31ull);
+      k_events<false><<<(uint32_t)((dw.n_work - dw.work_origin + kEventThreads - 1) / kEventThreads), kEventThreads, 0, s>>>(dw);
+      c->launches++;
+    }
     K2J_CUDA(c, cudaGetLastError());
     K2J_CUDA(c, cudaEventRecord(c->ev[3], s));
-    k2j_status st = run_scan(c, d.ev_size, d.n_events, 1, c->ev_off.as<uint64_t>(), c->scan_totals.as<uint64_t>() + 10, &c->launches);
+    k2j_status st = run_scan(c, d.ev_size, d.n_events, 1, c->ev_off.as<uint64_t>(), c->scan_totals.as<uint64_t>() + 20, &c->launches);
     if (st) return st;
-    K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 10, c->scan_totals.as<uint64_t>() + 10, 8, cudaMemcpyDeviceToHost, s));
+    K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 20, c->scan_totals.as<uint64_t>() + 20, 8, cudaMemcpyDeviceToHost, s));
     if (n_gpu_events)
-      K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 11, c->ev_off.as<uint64_t>() + c->n_ops, 8, cudaMemcpyDeviceToHost, s));
+      K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 21, c->ev_off.as<uint64_t>() + c->n_ops, 8, cudaMemcpyDeviceToHost, s));
     K2J_CUDA(c, cudaEventRecord(c->ev[4], s));
     K2J_CUDA(c, cudaStreamSynchronize(s));
-    total_bytes = c->h_totals[10];
+    total_bytes = c->h_totals[20];
     if (spans_on) {
       k2j_status st2 = order_annotations(c, span_cap, &n_spans, &ann_bytes);
       if (st2) return st2;
@@ -658,8 +747,8 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
 
   res->out_bytes = total_bytes + ann_bytes;
   res->annotation_bytes = ann_bytes;
-  res->ops_bytes = n_gpu_events ? c->h_totals[11] : total_bytes;
-  res->n_records = totals[C_EVENTS] + totals[C_EXT] + totals[C_UNEXPECTED];
+  res->ops_bytes = n_gpu_events ? c->h_totals[21] : total_bytes;
+  res->n_records = totals[C_EVENTS] + totals[C_WAIT] + totals[C_EXT] + totals[C_UNEXPECTED];
   res->x_events = c->h_counters->x_events + (ann_bytes ? n_spans : 0);
   res->flow_events = c->h_counters->flow_events;
   res->out_of_range_events = c->h_counters->out_of_range;
@@ -667,7 +756,8 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
   res->invalid_external_correlation_events = c->h_counters->invalid_external_correlation;
   res->unexpected_cuda_events = totals[C_UNEXPECTED];
   res->in_bytes = 208 * totals[C_KERNEL] + 88 * totals[C_MEMCPY] + 96 * totals[C_MEMCPY2] + 88 * totals[C_MEMSET] +
-                  40 * totals[C_API] + 24 * totals[C_EXT] + 56 * totals[C_OVERHEAD];
+                  40 * totals[C_API] + 24 * totals[C_EXT] + 56 * totals[C_OVERHEAD] + 40 * (totals[C_SYNC] + totals[C_WAIT]) +
+                  56 * totals[C_CUDAEVENT];
   res->name_bytes = c->h_counters->name_bytes;
   res->kernel_launches = c->launches;
   cudaEventElapsedTime(&res->ms_segment, c->ev[0], c->ev[1]);
@@ -702,11 +792,11 @@ k2j_status k2j_exclusive_scan_u32(k2j_ctx* c, const uint32_t* sizes, uint64_t n,
   *total = 0;
   if (n == 0) return K2J_OK;
   uint32_t launches = 0;
-  k2j_status st = run_scan(c, sizes, n, 1, offsets, c->scan_totals.as<uint64_t>() + 14, &launches);
+  k2j_status st = run_scan(c, sizes, n, 1, offsets, c->scan_totals.as<uint64_t>() + 24, &launches);
   if (st) return st;
-  K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 14, c->scan_totals.as<uint64_t>() + 14, 8, cudaMemcpyDeviceToHost, c->stream));
+  K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 24, c->scan_totals.as<uint64_t>() + 24, 8, cudaMemcpyDeviceToHost, c->stream));
   K2J_CUDA(c, cudaStreamSynchronize(c->stream));
-  *total = c->h_totals[14];
+  *total = c->h_totals[24];
   return K2J_OK;
 }
 

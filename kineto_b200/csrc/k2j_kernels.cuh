@@ -25,31 +25,59 @@
 namespace k2j {
 
 // ---- record classes ---------------------------------------------------------------------------
-enum : int { C_API = 0, C_KERNEL = 1, C_MEMCPY = 2, C_MEMCPY2 = 3, C_MEMSET = 4, C_OVERHEAD = 5, C_EXT = 6,
-             C_EXT_USER = 7 /* slot class only: EXTERNAL_CORRELATION of kind CUSTOM1; counted in C_EXT too */,
-             C_NCLASS = 7,
-             C_EVENTS = 7 /* column 7 of the count matrix: records that own an event slot */,
-             C_UNEXPECTED = 8 /* column 8: records of unknown kind */,
-             C_USER = 9 /* column 9: CUSTOM1 correlation records */, C_NCOL = 10, C_OP = 10 };
-enum : uint32_t { K_MEMCPY = 1, K_MEMSET = 2, K_DRIVER = 4, K_RUNTIME = 5, K_KERNEL = 10, K_OVERHEAD = 17, K_MEMCPY2 = 22, K_EXTCORR = 39 };
-
-static_assert(C_EXT_USER == C_EXT + 1 && C_EXT_USER < 8, "slot class layout");
+enum : int { C_API = 0, C_KERNEL = 1, C_MEMCPY = 2, C_MEMCPY2 = 3, C_MEMSET = 4, C_OVERHEAD = 5,
+             C_SYNC = 6 /* synchronisation records logged where they stand */, C_CUDAEVENT = 7,
+             C_WAIT = 8 /* stream-wait-event synchronisation records: logged after everything else */, C_EXT = 9,
+             C_EXT_USER = 10 /* slot class only: EXTERNAL_CORRELATION of kind CUSTOM1; counted in C_EXT too */,
+             C_NCLASS = 10,
+             C_UNEXPECTED = 10 /* column 10 of the count matrix: records of unknown kind */,
+             C_USER = 11 /* column 11: CUSTOM1 correlation records */,
+             C_EVENTS = 12 /* column 12: records that own an event slot in buffer order (classes C_API .. C_CUDAEVENT) */,
+             C_NCOL = 13, C_NPACKED = 12 /* columns a walk counts (8 bits each, three words) */, C_OP = 13 };
+enum : uint32_t { K_MEMCPY = 1, K_MEMSET = 2, K_DRIVER = 4, K_RUNTIME = 5, K_KERNEL = 10, K_OVERHEAD = 17, K_MEMCPY2 = 22,
+                  K_CUDA_EVENT = 36, K_SYNC = 38, K_EXTCORR = 39 };
 constexpr int kChunkSlots = 512;            // 4 KiB of 8-byte slots
 constexpr int kMaxEntry = 26;               // longest record is 208 B = 26 slots
 constexpr uint8_t kExitTerminate = 254;     // the walk hit a record it cannot size
 constexpr uint8_t kEntryNone = 255;         // chunk is unreachable
 
-// size/8 | class<<5 for a record kind (5 + 3 bits); 0 = unknown
-__device__ __forceinline__ uint32_t slot_code(uint32_t kind, uint32_t word1) {
+// Slot code of a record: size/8 in the low five bits, a group number in the high three; 0 = unknown kind.  Eleven
+// slot classes share eight groups: classes of one group differ in size, so (group, size) names the class.
+constexpr uint32_t kCodeApi = 5u | (0u << 5), kCodeKernel = 26u | (1u << 5), kCodeMemcpy = 11u | (2u << 5),
+                   kCodeMemcpy2 = 12u | (3u << 5), kCodeMemset = 11u | (4u << 5), kCodeOverhead = 7u | (5u << 5),
+                   kCodeExt = 3u | (6u << 5), kCodeExtUser = 3u | (7u << 5),
+                   kCodeSync = 5u | (1u << 5) /* CUpti_ActivitySynchronization, 40 bytes */, kCodeWait = 5u | (2u << 5),
+                   kCodeCudaEvent = 7u | (1u << 5) /* CUpti_ActivityCudaEvent2, 56 bytes */;
+static_assert(kCodeWait == kCodeSync + 32u && kCodeExtUser == kCodeExt + 32u, "the decode adds one group for these");
+__host__ __device__ constexpr uint32_t slot_code(uint32_t kind, uint32_t word1) {
   switch (kind) {
-    case K_KERNEL: return 26u | (C_KERNEL << 5);
-    case K_MEMCPY: return 11u | (C_MEMCPY << 5);
-    case K_MEMCPY2: return 12u | (C_MEMCPY2 << 5);
-    case K_MEMSET: return 11u | (C_MEMSET << 5);
-    case K_RUNTIME: case K_DRIVER: return 5u | (C_API << 5);
-    case K_OVERHEAD: return 7u | (C_OVERHEAD << 5);  // CUpti_ActivityOverhead3, 56 bytes
-    case K_EXTCORR: return 3u | ((word1 == 4u ? C_EXT_USER : C_EXT) << 5);  // word1 = externalKind
+    case K_KERNEL: return kCodeKernel;
+    case K_MEMCPY: return kCodeMemcpy;
+    case K_MEMCPY2: return kCodeMemcpy2;
+    case K_MEMSET: return kCodeMemset;
+    case K_RUNTIME: case K_DRIVER: return kCodeApi;
+    case K_OVERHEAD: return kCodeOverhead;  // CUpti_ActivityOverhead3, 56 bytes
+    case K_EXTCORR: return word1 == 4u ? kCodeExtUser : kCodeExt;  // word1 = externalKind
+    case K_SYNC: return word1 == 2u ? kCodeWait : kCodeSync;       // word1 = type; 2 = STREAM_WAIT_EVENT
+    case K_CUDA_EVENT: return kCodeCudaEvent;
     default: return 0u;
+  }
+}
+// Slot class (C_API .. C_EXT_USER) of a slot code; 0xff for codes no record has.
+__host__ __device__ constexpr uint32_t code_slot_class(uint32_t code) {
+  switch (code) {
+    case kCodeApi: return C_API;
+    case kCodeKernel: return C_KERNEL;
+    case kCodeMemcpy: return C_MEMCPY;
+    case kCodeMemcpy2: return C_MEMCPY2;
+    case kCodeMemset: return C_MEMSET;
+    case kCodeOverhead: return C_OVERHEAD;
+    case kCodeSync: return C_SYNC;
+    case kCodeCudaEvent: return C_CUDAEVENT;
+    case kCodeWait: return C_WAIT;
+    case kCodeExt: return C_EXT;
+    case kCodeExtUser: return C_EXT_USER;
+    default: return 0xffu;
   }
 }
 
@@ -66,6 +94,7 @@ struct Counters {
 struct MdEntry { uint32_t key, type; uint64_t value; };
 struct ExtRec { uint64_t external_id; uint32_t correlation_id; uint32_t external_kind; };
 struct SpanRec { int64_t start, end; uint64_t first_event; uint32_t device, stream; int32_t op_id; uint32_t op_row; };
+struct EvtRec { uint64_t key; uint32_t corr, stream; };  // a CUDA event record: key = context << 32 | event id
 
 struct Dev {
   // scalars
@@ -110,6 +139,16 @@ struct Dev {
   // work lists (class-sorted) and per-event arrays
   uint32_t* work_slot; uint32_t* work_ev; uint64_t cls_begin[C_NCLASS]; uint64_t cls_count[C_NCLASS];
   uint64_t ops_begin; uint64_t n_work;
+  uint64_t work_origin;    // first work item of this launch (0, or the first deferred synchronisation record)
+  int32_t wait_pass;       // size pass over the deferred synchronisation records only
+  uint64_t wait_ev_base;   // event number of the first deferred synchronisation record
+  // synchronisation records: context -> first record naming it, CUDA event records sorted by (context, event,
+  // correlation id, position), (device, stream) pairs with GPU work in the window, first stream sync of every row
+  unsigned long long* ctx_tab; uint32_t ctx_mask;
+  const EvtRec* evt; uint32_t n_evt;
+  unsigned long long* seen_tab; uint32_t seen_mask;
+  unsigned long long* row_key; uint32_t* row_first; uint32_t row_mask;
+  uint32_t* corr_zero;     // one bit per correlation-table slot: the entry links to a CPU op whose id is 0
   uint32_t* ev_size; const uint64_t* ev_off; uint64_t n_events;
   int32_t* ev_ext;        // per event: id of the linked CPU op found by the size pass (0 = none)
   uint8_t* out; uint64_t out_cap;
@@ -246,27 +285,29 @@ constexpr int kSegWarps = 8;
 
 // Class column of a slot code for the count matrix (C_EXT_USER counts as C_EXT; see C_USER).
 __device__ __forceinline__ uint32_t code_class(uint32_t code) {
-  const uint32_t cls = code >> 5;
+  const uint32_t cls = code_slot_class(code);
   return cls == (uint32_t)C_EXT_USER ? (uint32_t)C_EXT : cls;
 }
 
 // One warp per chunk: slot codes; then lane e (< 26) walks the chunk as if it were entered at slot e
 // and leaves behind where that walk exits (the exit map) and how many records of each class it met
-// (ten 8-bit counts packed in three words: a 4 KiB chunk holds at most 170 records).  Kind -> code and
+// (twelve 8-bit counts packed in three words: a 4 KiB chunk holds at most 170 records).  Kind -> code and
 // class -> count increments come from two small tables in shared memory, so neither the decode nor
 // the walk branches on the record kind.
 __global__ void __launch_bounds__(kSegWarps * 32) k_seg_chunks(Dev d) {
   __shared__ uint8_t s_code[kSegWarps][kChunkSlots];
   __shared__ uint8_t s_kind[64];     // slot code of record kinds 0..63 (CUSTOM1 correlation records add one class)
-  __shared__ uint32_t s_inc[8][3];   // per slot class: increments of the three packed count words
+  __shared__ uint32_t s_inc[256][3]; // per slot code: increments of the three packed count words
+  static_assert(kSegWarps * 32 == 256, "one thread per slot code");
   if (threadIdx.x < 64) s_kind[threadIdx.x] = (uint8_t)slot_code(threadIdx.x, 0u);
-  if (threadIdx.x < 8) {
-    const uint32_t sc = threadIdx.x, cls = sc == (uint32_t)C_EXT_USER ? (uint32_t)C_EXT : sc;
-    uint32_t i0 = 0, i1 = 0, i2 = 0;
-    if (cls < 4u) i0 = 1u << (8 * cls); else i1 = 1u << (8 * (cls - 4u));
-    if (cls != (uint32_t)C_EXT) i1 += 1u << (8 * (C_EVENTS - 4));   // records that own an event slot
-    if (sc == (uint32_t)C_EXT_USER) i2 = 1u << (8 * (C_USER - 8));
-    s_inc[sc][0] = i0; s_inc[sc][1] = i1; s_inc[sc][2] = i2;
+  {
+    const uint32_t sc = code_slot_class(threadIdx.x), cls = sc == (uint32_t)C_EXT_USER ? (uint32_t)C_EXT : sc;
+    uint32_t inc[3] = {0u, 0u, 0u};
+    if (sc != 0xffu) {
+      inc[cls >> 2] = 1u << (8 * (cls & 3u));
+      if (sc == (uint32_t)C_EXT_USER) inc[C_USER >> 2] += 1u << (8 * (C_USER & 3));
+    }
+    s_inc[threadIdx.x][0] = inc[0]; s_inc[threadIdx.x][1] = inc[1]; s_inc[threadIdx.x][2] = inc[2];
   }
   __syncthreads();
   const uint32_t w = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -284,7 +325,8 @@ __global__ void __launch_bounds__(kSegWarps * 32) k_seg_chunks(Dev d) {
       if (s + q < g.nvalid) {
         const uint2 w2 = words[g.slot0 + s + q];
         code = w2.x < 64u ? s_kind[w2.x] : 0u;
-        code += (w2.x == K_EXTCORR && w2.y == 4u) ? 1u << 5 : 0u;  // externalKind CUSTOM1: class C_EXT_USER = C_EXT + 1
+        code += (w2.x == K_EXTCORR && w2.y == 4u) ? 1u << 5 : 0u;  // externalKind CUSTOM1: the next group
+        code += (w2.x == K_SYNC && w2.y == 2u) ? 1u << 5 : 0u;     // a stream-wait event: the next group
       }
       packed |= code << (8 * q);
     }
@@ -297,7 +339,7 @@ __global__ void __launch_bounds__(kSegWarps * 32) k_seg_chunks(Dev d) {
   }
   __syncwarp();
   uint8_t code = kEntryNone;
-  uint32_t c0 = 0, c1 = 0, c2 = 0;  // 8-bit counts of columns 0-3, 4-7, 8-9
+  uint32_t c0 = 0, c1 = 0, c2 = 0;  // 8-bit counts of columns 0-3, 4-7, 8-11
   if (lane < kMaxEntry) {
     uint32_t pos = lane;
     code = 0;
@@ -307,7 +349,7 @@ __global__ void __launch_bounds__(kSegWarps * 32) k_seg_chunks(Dev d) {
       const uint32_t sc = s_code[w][pos];
       const uint32_t n = sc & 31u;
       if (n == 0 || (g.last && pos + n > g.nvalid)) { code = kExitTerminate; c2 += 1u << (8 * (C_UNEXPECTED - 8)); break; }
-      const uint32_t* inc = s_inc[sc >> 5];
+      const uint32_t* inc = s_inc[sc];
       c0 += inc[0]; c1 += inc[1]; c2 += inc[2];
       pos += n;
     }
@@ -382,7 +424,10 @@ __global__ void __launch_bounds__(256) k_seg_compose(Dev d) {
 #pragma unroll
       for (int i = 0; i < 4; i++) d.chunk_cnt[(uint64_t)(4 + i) * d.n_chunks + t0 + c] = (w1 >> (8 * i)) & 0xffu;
 #pragma unroll
-      for (int i = 0; i < C_NCOL - 8; i++) d.chunk_cnt[(uint64_t)(8 + i) * d.n_chunks + t0 + c] = (w2 >> (8 * i)) & 0xffu;
+      for (int i = 0; i < C_NPACKED - 8; i++) d.chunk_cnt[(uint64_t)(8 + i) * d.n_chunks + t0 + c] = (w2 >> (8 * i)) & 0xffu;
+      // records that own an event slot in buffer order: classes C_API .. C_CUDAEVENT = the bytes of w0 and w1
+      d.chunk_cnt[(uint64_t)C_EVENTS * d.n_chunks + t0 + c] = (((w0 & 0x00ff00ffu) + ((w0 >> 8) & 0x00ff00ffu) +
+                                                                 (w1 & 0x00ff00ffu) + ((w1 >> 8) & 0x00ff00ffu)) * 0x00010001u) >> 16;
     }
   }
 }
@@ -435,7 +480,7 @@ __global__ void __launch_bounds__(kSegWarps * 32) k_seg_write(Dev d) {
     const bool on = i < n;
     const uint32_t pos = on ? s_pos[w][i] : 0u;
     const uint32_t cls = on ? code_class(codes[pos]) : 0xffu;
-    const uint32_t evm = __ballot_sync(0xffffffffu, on && cls != (uint32_t)C_EXT);
+    const uint32_t evm = __ballot_sync(0xffffffffu, on && cls < (uint32_t)C_WAIT);
     uint64_t dst = 0;
 #pragma unroll
     for (int c = 0; c < C_NCLASS; c++) {
@@ -454,7 +499,8 @@ __global__ void __launch_bounds__(kSegWarps * 32) k_seg_write(Dev d) {
         d.ext_local[dst] = e;
       } else {
         d.work_slot[dst] = (uint32_t)slot;
-        d.work_ev[dst] = (uint32_t)(ev_base + __popc(evm & lt));
+        // deferred records are numbered after every other event, in the order they stand in the buffers
+        d.work_ev[dst] = cls == (uint32_t)C_WAIT ? (uint32_t)(d.wait_ev_base + (dst - d.cls_begin[C_WAIT])) : (uint32_t)(ev_base + __popc(evm & lt));
       }
     }
     ev_base += __popc(evm);
@@ -495,7 +541,7 @@ __global__ void k_mark_corr(Dev d) {
   for (int c = 1; c < C_EXT; c++) if (i >= d.cls_begin[c]) cls = c;
   if (i - d.cls_begin[cls] >= d.cls_count[cls] || cls == C_OVERHEAD) return;  // padding; overhead records join nothing
   const uint8_t* r = d.cupti + (uint64_t)d.work_slot[i] * 8;
-  const int off = cls == C_API ? 32 : cls == C_KERNEL ? 92 : cls == C_MEMCPY2 ? 60 : 44;
+  const int off = cls == C_API ? 32 : cls == C_KERNEL ? 92 : cls == C_MEMCPY2 ? 60 : cls == C_CUDAEVENT ? 4 : (cls == C_SYNC || cls == C_WAIT) ? 24 : 44;
   bit_set(d.need_corr, d.need_corr_mask, *reinterpret_cast<const uint32_t*>(r + off));
 }
 // CPU-op id -> position (last writer wins): activityMap_[id] = op, GenericActivityProfiler.cpp:262.
@@ -827,8 +873,36 @@ enum : int { N_HEAD, N_PID, N_TID, N_TS, N_DUR, N_PAD, N_EXT, N_ARGS_CLOSE, N_CL
     {"\n    }", T_NONE}, {"\n  },", T_NONE}
 
 
-// One table for everything: [api][kernel][mem][op head, metadata marker, op tail][annotation][constant strings].
-enum : int { CS_TYPE = 0, CS_MEMCPY_KIND = 29, CS_MEMORY_KIND = 41, CS_LIMIT = 50, CS_OVERHEAD = 82, CS_COUNT = 93 };
+// -- synchronisation record (CudaSyncActivity, libkineto/src/CuptiActivity.h:181-211, :325-373; 40 bytes) and CUDA
+// event record (CudaEventActivity, :233-262, :375-411; its fields are copied to the same slots).  A stream sync
+// sits on a row of its own, and the first one of a row is preceded by two metadata rows
+// (libkineto/src/output_json.cpp:914-943). --
+enum : int { YS_TS = 8, YS_DUR = 16, YR_CORR = 24, YR_CTX = 28, YS_STREAM = 32, YR_EVENT = 36, YS_PID = 40, YS_EXT = 44, YS_TID = 48,
+             YS_NAME = 56, YS_SRCSTREAM = 60, YS_SRCCORR = 64, YS_ROWTID = 72 };
+enum : int { Y_MROW1, Y_MPID1, Y_MTID1, Y_MNAME, Y_MROW2, Y_MPID2, Y_MTID2, Y_MSORT, Y_MEND, Y_HEAD_SYNC, Y_HEAD_EVENT, Y_PID, Y_TID,
+             Y_TS, Y_DUR, Y_ARGS, Y_EXT, Y_EXTC, Y_KIND, Y_WSTREAM, Y_WCORR, Y_WEVENT, Y_EVENTID, Y_STREAM_A, Y_STREAM_B, Y_CORR,
+             Y_DEV, Y_CTX, Y_CLOSE, Y_FLOW, Y_FPID, Y_FTID, Y_FTS, Y_FEND, Y_COUNT };
+#define K2J_SYNC_FIELDS \
+    {"\n  {\n    \"name\": \"thread_name\", \"ph\": \"M\", \"ts\": ", T_TS, VK_64, YS_TS}, {", \"pid\": ", T_U64, VK_U32, YS_PID}, \
+    {", \"tid\": ", T_I64, VK_64, YS_ROWTID}, {",\n    \"args\": {\n      \"name\": \"stream ", T_I64, VK_I32, YS_STREAM}, \
+    {" (sync)\"\n    }\n  },\n  {\n    \"name\": \"thread_sort_index\", \"ph\": \"M\", \"ts\": ", T_TS, VK_64, YS_TS}, \
+    {", \"pid\": ", T_U64, VK_U32, YS_PID}, {", \"tid\": ", T_I64, VK_64, YS_ROWTID}, \
+    {",\n    \"args\": {\n      \"sort_index\": ", T_I64, VK_I32, YS_STREAM}, {"\n    }\n  },", T_NONE}, \
+    {XHEAD("cuda_sync"), T_CSTR, VK_U32, YS_NAME}, {XHEAD("cuda_event") "cudaEvent", T_NONE}, \
+    {"\",\n    \"pid\": ", T_U64, VK_U32, YS_PID}, {",\n    \"tid\": ", T_U64, VK_64, YS_TID}, {",\n    \"ts\": ", T_TS, VK_64, YS_TS}, \
+    {",\n    \"dur\": ", T_TS, VK_64, YS_DUR}, {"\n    ,\n    \"args\": {\n      ", T_NONE}, \
+    {"\"External id\": ", T_I64, VK_I32, YS_EXT}, {",", T_NONE}, {"\"cuda_sync_kind\": \"", T_CSTR, VK_U32, YS_NAME}, \
+    {"\", \"wait_on_stream\": ", T_I64, VK_I32, YS_SRCSTREAM}, {", \"wait_on_cuda_event_record_corr_id\": ", T_I64, VK_I32, YS_SRCCORR}, \
+    {", \"wait_on_cuda_event_id\": ", T_U64, VK_U32, YR_EVENT}, {"\"event_id\": ", T_U64, VK_U32, YR_EVENT}, \
+    {", \"stream\": ", T_I64, VK_I32, YS_STREAM}, {"\", \"stream\": ", T_I64, VK_I32, YS_STREAM}, \
+    {", \"correlation\": ", T_U64, VK_U32, YR_CORR}, {", \"device\": ", T_U64, VK_U32, YS_PID}, {", \"context\": ", T_U64, VK_U32, YR_CTX}, \
+    {"\n    }\n  },", T_NONE}, \
+    {"\n  {\n    \"ph\": \"f\",\n    \"id\": ", T_U64, VK_U32, YR_CORR}, {",\n    \"pid\": ", T_U64, VK_U32, YS_PID}, \
+    {",\n    \"tid\": ", T_U64, VK_64, YS_TID}, {",\n    \"ts\": ", T_TS, VK_64, YS_TS}, \
+    {",\n    \"cat\": \"ac2g\",\n    \"name\": \"ac2g\"\n    , \"bp\": \"e\"\n  },", T_NONE}
+
+// One table for everything: [api][kernel][mem][op head, metadata marker, op tail][annotation][sync][constant strings].
+enum : int { CS_TYPE = 0, CS_MEMCPY_KIND = 29, CS_MEMORY_KIND = 41, CS_LIMIT = 50, CS_OVERHEAD = 82, CS_SYNC = 93, CS_COUNT = 98 };
 #define K2J_CSTR_FIELDS \
     {"cpu_op", 0}, {"user_annotation", 0}, {"gpu_user_annotation", 0}, {"gpu_memcpy", 0}, {"gpu_memset", 0}, {"kernel", 0}, \
     {"external_correlation", 0}, {"cuda_runtime", 0}, {"cuda_driver", 0}, {"cpu_instant_event", 0}, {"python_function", 0}, \
@@ -850,13 +924,15 @@ enum : int { CS_TYPE = 0, CS_MEMCPY_KIND = 29, CS_MEMORY_KIND = 41, CS_LIMIT = 5
     {"WARPS|REGS|SMEM|BLOCKS|BARRIERS", 0}, \
     {"Unknown", 0}, {"Driver Compiler", 0}, {"Buffer Flush", 0}, {"Instrumentation", 0}, {"Resource", 0}, \
     {"Runtime Triggered Module Loading", 0}, {"Lazy Function Loading", 0}, {"Command Buffer Full", 0}, \
-    {"Activity Buffer Request", 0}, {"Force Int", 0}, {"Unrecognized", 0}
+    {"Activity Buffer Request", 0}, {"Force Int", 0}, {"Unrecognized", 0}, \
+    {"Unknown Sync", 0}, {"Event Sync", 0}, {"Stream Wait Event", 0}, {"Stream Sync", 0}, {"Context Sync", 0}
 
 
 constexpr int API_BASE = 0, KERNEL_BASE = API_BASE + A_COUNT, MEM_BASE = KERNEL_BASE + K_COUNT, OP_BASE = MEM_BASE + M_COUNT,
-              ANN_BASE = OP_BASE + O_COUNT, CSTR_BASE = ANN_BASE + N_COUNT, FIELD_COUNT = CSTR_BASE + CS_COUNT;
+              ANN_BASE = OP_BASE + O_COUNT, SYNC_BASE = ANN_BASE + N_COUNT, CSTR_BASE = SYNC_BASE + Y_COUNT,
+              FIELD_COUNT = CSTR_BASE + CS_COUNT;
 constexpr FieldSrc kAllFields[] = {K2J_API_FIELDS, K2J_KERNEL_FIELDS, K2J_MEM_FIELDS, K2J_OPHEAD_FIELDS, {"", T_MD, VK_U32, OS_ROW},
-                                   K2J_OPTAIL_FIELDS, K2J_ANN_FIELDS, K2J_CSTR_FIELDS};
+                                   K2J_OPTAIL_FIELDS, K2J_ANN_FIELDS, K2J_SYNC_FIELDS, K2J_CSTR_FIELDS};
 static_assert(sizeof(kAllFields) / sizeof(kAllFields[0]) == FIELD_COUNT, "field table and enums disagree");
 constexpr int kAllWords = prog_words(kAllFields);
 __constant__ Prog<FIELD_COUNT, kAllWords> g_fields = make_prog<FIELD_COUNT, kAllWords>(kAllFields);
@@ -943,7 +1019,10 @@ __global__ void k_resolve_corr(Dev d) {
   const int64_t ext = (int64_t)d.ext_all[(uint32_t)e - 1u].external_id;
   uint32_t id = 0;
   if (ext == (int64_t)(int32_t)ext && tab_find(d.op_tab, d.op_mask, (uint32_t)(int32_t)ext) != 0xFFFFFFFFu)
+  {
     id = (uint32_t)(int32_t)ext;  // the linked op's correlationId() is the key it was found under
+    if (id == 0u && d.corr_zero != nullptr) atomicOr(&d.corr_zero[i >> 5], 1u << (i & 31u));  // linked, to the op whose id is 0
+  }
   d.corr_tab[i] = (e & 0xFFFFFFFF00000000ull) | id;
 }
 // The first probe is split off so that callers can issue its load early, next to other loads.
@@ -998,6 +1077,120 @@ __device__ __noinline__ void span_update(const Dev& d, uint32_t corr, uint32_t d
   atomicMax(&d.span_end[j], (unsigned long long)(ts + dur));
   atomicMax(&d.span_nfirst[j], ~(unsigned long long)ev);
   d.span_row[j] = row;
+}
+
+// ---- synchronisation and CUDA event records: the lookups of CuptiActivityProfiler.cpp:221-254, :379-402, :502-514 ----
+// A set of 64-bit keys (0 = empty slot).  Returns the key's slot, or 0xFFFFFFFF if absent (or the table is full).
+__device__ __forceinline__ uint32_t set64_slot(unsigned long long* tab, uint32_t mask, unsigned long long key, bool insert) {
+  uint32_t i = hash32((uint32_t)(key >> 32) * 0x9E3779B1u ^ (uint32_t)key) & mask;
+  for (uint32_t probes = 0; probes <= mask; probes++) {
+    unsigned long long old = tab[i];
+    if (old == 0) {
+      if (!insert) return 0xFFFFFFFFu;
+      old = atomicCAS(&tab[i], 0ull, key);
+      if (old == 0) return i;
+    }
+    if (old == key) return i;
+    i = (i + 1) & mask;
+  }
+  return 0xFFFFFFFFu;
+}
+__device__ __forceinline__ unsigned long long dev_stream_key(uint32_t dev, uint32_t stream) {
+  return (((unsigned long long)dev << 32) | stream) + 1ull;
+}
+// seenDeviceStreams_ (GenericActivityProfiler.cpp:419): streams with a kernel, copy or memset inside the window.
+__device__ __forceinline__ void seen_insert(const Dev& d, uint32_t dev, uint32_t stream) {
+  if (set64_slot(d.seen_tab, d.seen_mask, dev_stream_key(dev, stream), true) == 0xFFFFFFFFu) atomicAdd(&d.counters->device_check, 1ull);
+}
+// ctxToDeviceId (CuptiActivityProfiler.cpp:221-239): the first kernel, copy or memset record that names a context
+// decides its device; a peer-to-peer copy names its source context, then its destination context.  Values are
+// record positions, so the smallest one is the first writer in processing order.
+__global__ void k_build_ctx(Dev d) {
+  const uint64_t i = d.cls_begin[C_KERNEL] + (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= d.cls_begin[C_OVERHEAD]) return;
+  int cls = C_KERNEL;
+#pragma unroll
+  for (int c = C_MEMCPY; c <= C_MEMSET; c++) if (i >= d.cls_begin[c]) cls = c;
+  if (i - d.cls_begin[cls] >= d.cls_count[cls]) return;  // padding
+  const uint32_t slot = d.work_slot[i];
+  const uint8_t* r = d.cupti + (uint64_t)slot * 8;
+  bool ok;
+  if (cls == C_MEMCPY2) {
+    ok = tab_insert_min(d.ctx_tab, d.ctx_mask, *reinterpret_cast<const uint32_t*>(r + 48), slot);
+    ok = tab_insert_min(d.ctx_tab, d.ctx_mask, *reinterpret_cast<const uint32_t*>(r + 56), slot) && ok;
+  } else ok = tab_insert_min(d.ctx_tab, d.ctx_mask, *reinterpret_cast<const uint32_t*>(r + (cls == C_KERNEL ? 44 : 36)), slot);
+  if (!ok) atomicAdd(&d.counters->device_check, 1ull);
+}
+// contextIdtoDeviceId (CuptiActivityProfiler.cpp:527-530): device 0 for a context no record names.
+__device__ __forceinline__ uint32_t ctx_device(const Dev& d, uint32_t ctx) {
+  const uint32_t slot = tab_find(d.ctx_tab, d.ctx_mask, ctx);
+  if (slot == 0xFFFFFFFFu) return 0u;
+  const uint8_t* r = d.cupti + (uint64_t)slot * 8;
+  const uint32_t kind = *reinterpret_cast<const uint32_t*>(r);
+  if (kind == K_KERNEL) return *reinterpret_cast<const uint32_t*>(r + 40);
+  if (kind == K_MEMCPY2) return *reinterpret_cast<const uint32_t*>(r + (*reinterpret_cast<const uint32_t*>(r + 48) == ctx ? 44 : 52));
+  return *reinterpret_cast<const uint32_t*>(r + 32);
+}
+// Sort keys of the CUDA event records (work items of class C_CUDAEVENT, in processing order).  Stage 0: the
+// correlation id; stage 1, on the result of the first sort: context << 32 | event id.  Both sorts are stable, so
+// records end up ordered by (context, event, correlation id, position).
+__global__ void k_evt_keys(Dev d, uint64_t* keys, uint32_t* vals, int stage) {
+  const uint64_t p = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= d.cls_count[C_CUDAEVENT]) return;
+  const uint32_t j = stage == 0 ? (uint32_t)p : vals[p];
+  const uint8_t* r = d.cupti + (uint64_t)d.work_slot[d.cls_begin[C_CUDAEVENT] + j] * 8;
+  if (stage == 0) { keys[p] = *reinterpret_cast<const uint32_t*>(r + 4); vals[p] = j; }
+  else keys[p] = ((uint64_t)*reinterpret_cast<const uint32_t*>(r + 8) << 32) | *reinterpret_cast<const uint32_t*>(r + 16);
+}
+__global__ void k_evt_finish(Dev d, const uint64_t* keys, const uint32_t* vals, EvtRec* out) {
+  const uint64_t p = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= d.cls_count[C_CUDAEVENT]) return;
+  const uint8_t* r = d.cupti + (uint64_t)d.work_slot[d.cls_begin[C_CUDAEVENT] + vals[p]] * 8;
+  EvtRec e;
+  e.key = keys[p]; e.corr = *reinterpret_cast<const uint32_t*>(r + 4); e.stream = *reinterpret_cast<const uint32_t*>(r + 12);
+  out[p] = e;
+}
+// getWaitEventInfo (CuptiActivityProfiler.cpp:379-402) over updateWaitEventMap's vectors (:243-254): among the
+// records of (context, event) the largest correlation id not above the query's; among records with that id the
+// one that came first (a new record is inserted before its equals, and the last of the equals is taken).
+__device__ __forceinline__ bool wait_event_find(const Dev& d, uint32_t ctx, uint32_t event, uint32_t corr, int32_t* stream, int32_t* rcorr) {
+  if (d.evt == nullptr || d.n_evt == 0) return false;
+  const uint64_t key = ((uint64_t)ctx << 32) | event;
+  uint32_t lo = 0, hi = d.n_evt;
+  for (int it = 0; it < 34 && lo < hi; it++) {  // first record above (key, corr)
+    const uint32_t mid = lo + ((hi - lo) >> 1);
+    const EvtRec r = d.evt[mid];
+    if (r.key < key || (r.key == key && r.corr <= corr)) lo = mid + 1; else hi = mid;
+  }
+  if (lo == 0) return false;
+  const EvtRec last = d.evt[lo - 1];
+  if (last.key != key) return false;
+  uint32_t lo2 = 0, hi2 = lo - 1;
+  for (int it = 0; it < 34 && lo2 < hi2; it++) {  // first record not below (key, last.corr)
+    const uint32_t mid = lo2 + ((hi2 - lo2) >> 1);
+    const EvtRec r = d.evt[mid];
+    if (r.key < key || (r.key == key && r.corr < last.corr)) lo2 = mid + 1; else hi2 = mid;
+  }
+  const EvtRec first = d.evt[lo2];
+  *stream = (int32_t)first.stream; *rcorr = (int32_t)first.corr;
+  return true;
+}
+// linkedActivity for record types that print their own correlation id when nothing is linked: tells "linked to the
+// CPU op whose id is 0" from "not linked" (k_resolve_corr leaves 0 in the entry for both and marks the former).
+__device__ __forceinline__ bool linked_op_full(const Dev& d, uint32_t corr, int32_t* id) {
+  if ((corr & 0x80000000u) || d.corr_tab == nullptr) return false;
+  uint32_t i = hash32(corr) & d.corr_mask;
+  for (uint32_t probes = 0; probes <= d.corr_mask; probes++) {
+    const unsigned long long e = d.corr_tab[i];
+    if (e == 0) return false;
+    if ((uint32_t)(e >> 32) == corr) {
+      if ((uint32_t)e != 0u) { *id = (int32_t)(uint32_t)e; return true; }
+      if (d.corr_zero != nullptr && ((d.corr_zero[i >> 5] >> (i & 31u)) & 1u)) { *id = 0; return true; }
+      return false;
+    }
+    i = (i + 1) & d.corr_mask;
+  }
+  return false;
 }
 
 struct Tally { uint32_t x, flow; unsigned long long name_bytes; uint64_t ev; };
@@ -1154,6 +1347,7 @@ __device__ __forceinline__ uint64_t gather_kernel(const Dev& d, uint32_t* a, Tal
   t.x++;
   if (corr > 0) t.flow++;
   else p &= ~((1ull << K_FLOW) | (1ull << K_FPID) | (1ull << K_FTID) | (1ull << K_FTS) | (1ull << K_FEND));
+  if (counting && d.seen_tab != nullptr) seen_insert(d, dev, stream);
   if (counting && d.span_key != nullptr) span_update(d, corr, dev, stream, ts, dur, t.ev);
   return p;
 }
@@ -1201,6 +1395,7 @@ __device__ __forceinline__ uint64_t gather_mem(const Dev& d, uint32_t* a, Tally&
   on(M_GRAPH); on(M_NODE); on(M_CHAN); on(M_CHTYPE); on(M_CLOSE);
   t.x++;
   if (corr > 0) { on(M_FLOW); on(M_FPID); on(M_FTID); on(M_FTS); on(M_FEND); t.flow++; }
+  if (counting && d.seen_tab != nullptr) seen_insert(d, dev, stream);
   if (counting && d.span_key != nullptr) span_update(d, corr, dev, stream, ts, dur, t.ev);
   return p;
 }
@@ -1223,6 +1418,84 @@ __device__ __forceinline__ uint64_t gather_overhead(const Dev& d, uint32_t* a, T
   t.x++;
   return (1ull << O_CAT) | (1ull << O_CNAME) | (1ull << O_PID) | (1ull << O_TID) | (1ull << O_TS) | (1ull << O_DUR) |
          (1ull << O_PAD) | (1ull << P_CLOSE);
+}
+
+// Reads a synchronisation or CUDA event record into registers (the two layouts differ).
+struct SyncFields { uint32_t type, corr, ctx, stream, event; uint64_t start, end; };
+template <int CLS> __device__ __forceinline__ SyncFields sync_fields(const uint32_t* a) {
+  SyncFields f;
+  if (CLS == C_CUDAEVENT) {  // CUpti_ActivityCudaEvent2: the device timestamp is the start, the duration is 1 ns
+    f.type = 0; f.corr = a32(a, 4); f.ctx = a32(a, 8); f.stream = a32(a, 12); f.event = a32(a, 16); f.start = a64(a, 40); f.end = 0;
+  } else {
+    f.type = a32(a, 4); f.start = a64(a, 8); f.end = a64(a, 16); f.corr = a32(a, 24); f.ctx = a32(a, 28); f.stream = a32(a, 32);
+    f.event = a32(a, 36);
+  }
+  return f;
+}
+// handleCudaSyncActivity / handleCudaEventActivity (libkineto/src/CuptiActivityProfiler.cpp:404-500) with
+// CudaSyncActivity / CudaEventActivity (libkineto/src/CuptiActivity.h:325-411).  A deferred record (C_WAIT) is
+// dropped, before the window check, when its stream showed no GPU work (logDeferredEvents, :502-514).
+template <int CLS>
+__device__ __forceinline__ uint64_t gather_sync(const Dev& d, uint32_t* a, Tally& t, uint32_t* filt, bool counting, int32_t* ext_io) {
+  const SyncFields f = sync_fields<CLS>(a);
+  const uint32_t dev = ctx_device(d, f.ctx);
+  if (CLS == C_WAIT && counting &&
+      (d.seen_tab == nullptr || set64_slot(d.seen_tab, d.seen_mask, dev_stream_key(dev, f.stream), false) == 0xFFFFFFFFu))
+    return 0;
+  const int64_t ts = conv_ts(d, f.start), dur = CLS == C_CUDAEVENT ? 1 : conv_dur(d, f.start, f.end);
+  if (out_of_range(d, ts, dur)) { *filt = 2; return 0; }
+  int32_t ext = *ext_io;
+  if (counting) {  // "External id": the linked op's id, else the record's own correlation id (output_json.cpp:871-895)
+    int32_t id = 0;
+    ext = linked_op_full(d, f.corr, &id) ? id : (int32_t)f.corr;
+    *ext_io = ext;
+  }
+  const bool event_sync = CLS != C_CUDAEVENT && (f.type == 1u || f.type == 2u);  // isEventSync, CuptiActivity.h:308-312
+  int64_t tid = (int64_t)(int32_t)f.stream;  // streamIdForTrace: "no stream" shows as -1
+  uint64_t p = 0;
+  auto on = [&](int fl) { p |= 1ull << fl; };
+  if (CLS == C_SYNC && f.type == 3u) {  // a stream sync: own row, announced once
+    tid += 1000000;  // kSyncStreamTidOffset, output_json.h:237
+    s64(a, YS_ROWTID, (uint64_t)tid);
+    const uint32_t slot = d.row_key != nullptr ? set64_slot(d.row_key, d.row_mask, dev_stream_key(dev, f.stream), false) : 0xFFFFFFFFu;
+    if (slot != 0xFFFFFFFFu && d.row_first[slot] == (uint32_t)t.ev) {
+      on(Y_MROW1); on(Y_MPID1); on(Y_MTID1); on(Y_MNAME); on(Y_MROW2); on(Y_MPID2); on(Y_MTID2); on(Y_MSORT); on(Y_MEND);
+    }
+  }
+  if (event_sync) {
+    int32_t src_stream = -1, src_corr = -1;
+    wait_event_find(d, f.ctx, f.event, f.corr, &src_stream, &src_corr);
+    s32(a, YS_SRCSTREAM, (uint32_t)src_stream); s32(a, YS_SRCCORR, (uint32_t)src_corr);
+  }
+  s64(a, YS_TS, (uint64_t)rel_ts(d, ts)); s64(a, YS_DUR, (uint64_t)(dur < 0 ? 0 : dur));
+  s32(a, YR_CORR, f.corr); s32(a, YR_CTX, f.ctx); s32(a, YS_STREAM, f.stream); s32(a, YR_EVENT, f.event);
+  s32(a, YS_PID, dev); s32(a, YS_EXT, (uint32_t)ext); s64(a, YS_TID, (uint64_t)abs_tid(tid));
+  s32(a, YS_NAME, (uint32_t)CS_SYNC + (f.type >= 1u && f.type <= 4u ? f.type : 0u));
+  on(CLS == C_CUDAEVENT ? Y_HEAD_EVENT : Y_HEAD_SYNC); on(Y_PID); on(Y_TID); on(Y_TS); on(Y_DUR); on(Y_ARGS);
+  if (ext != 0) { on(Y_EXT); on(Y_EXTC); }
+  if (CLS == C_CUDAEVENT) { on(Y_EVENTID); on(Y_STREAM_A); }
+  else {
+    on(Y_KIND);
+    if (event_sync) { on(Y_WSTREAM); on(Y_WCORR); on(Y_WEVENT); on(Y_STREAM_A); } else on(Y_STREAM_B);
+  }
+  on(Y_CORR); on(Y_DEV); on(Y_CTX); on(Y_CLOSE);
+  t.x++;
+  if (f.corr > 0) { on(Y_FLOW); on(Y_FPID); on(Y_FTID); on(Y_FTS); on(Y_FEND); t.flow++; }
+  return p;
+}
+// Which stream sync comes first on its row, in emission order: the smallest event number per (device, stream)
+// among the stream syncs that are logged.
+__global__ void k_sync_rows(Dev d) {
+  const uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= d.cls_count[C_SYNC]) return;
+  const uint64_t i = d.cls_begin[C_SYNC] + j;
+  const uint32_t* r = reinterpret_cast<const uint32_t*>(d.cupti + (uint64_t)d.work_slot[i] * 8);
+  if (r[1] != 3u) return;
+  const uint64_t st = (uint64_t)r[2] | ((uint64_t)r[3] << 32), en = (uint64_t)r[4] | ((uint64_t)r[5] << 32);
+  if (out_of_range(d, conv_ts(d, st), conv_dur(d, st, en))) return;
+  const uint32_t slot = set64_slot(d.row_key, d.row_mask, dev_stream_key(ctx_device(d, r[7]), r[8]), true);
+  if (slot == 0xFFFFFFFFu) { atomicAdd(&d.counters->device_check, 1ull); return; }
+  atomicMin(&d.row_first[slot], d.work_ev[i]);
 }
 
 // CPU-side activity: ChromeTraceLogger::handleActivity for a GenericTraceActivity (output_json.cpp:837-963)
@@ -1378,6 +1651,9 @@ __device__ __forceinline__ void format_event(S& s, const Dev& d, int cls, uint32
       case C_MEMCPY2: if ((p = gather_mem<C_MEMCPY2>(d, a, t, filt, true, ext))) count_fields<MEM_BASE, 0, M_COUNT>(s, d, a, p, nb); break;
       case C_MEMSET: if ((p = gather_mem<C_MEMSET>(d, a, t, filt, true, ext))) count_fields<MEM_BASE, 0, M_COUNT>(s, d, a, p, nb); break;
       case C_OVERHEAD: if ((p = gather_overhead(d, a, t, filt))) count_fields<OP_BASE, 0, O_COUNT>(s, d, a, p, nb); break;
+      case C_SYNC: if ((p = gather_sync<C_SYNC>(d, a, t, filt, true, ext))) count_fields<SYNC_BASE, 0, Y_COUNT>(s, d, a, p, nb); break;
+      case C_WAIT: if ((p = gather_sync<C_WAIT>(d, a, t, filt, true, ext))) count_fields<SYNC_BASE, 0, Y_COUNT>(s, d, a, p, nb); break;
+      case C_CUDAEVENT: if ((p = gather_sync<C_CUDAEVENT>(d, a, t, filt, true, ext))) count_fields<SYNC_BASE, 0, Y_COUNT>(s, d, a, p, nb); break;
       default: if ((p = gather_op(d, j, a, t))) count_fields<OP_BASE, 0, O_COUNT>(s, d, a, p, nb); break;
     }
   } else {
@@ -1390,6 +1666,9 @@ __device__ __forceinline__ void format_event(S& s, const Dev& d, int cls, uint32
       case C_MEMCPY2: p = gather_mem<C_MEMCPY2>(d, a, t, filt, false, ext); base = MEM_BASE; break;
       case C_MEMSET: p = gather_mem<C_MEMSET>(d, a, t, filt, false, ext); base = MEM_BASE; break;
       case C_OVERHEAD: p = gather_overhead(d, a, t, filt); base = OP_BASE; break;
+      case C_SYNC: p = gather_sync<C_SYNC>(d, a, t, filt, false, ext); base = SYNC_BASE; break;
+      case C_WAIT: p = gather_sync<C_WAIT>(d, a, t, filt, false, ext); base = SYNC_BASE; break;
+      case C_CUDAEVENT: p = gather_sync<C_CUDAEVENT>(d, a, t, filt, false, ext); base = SYNC_BASE; break;
       default: p = gather_op(d, j, a, t); base = OP_BASE; break;
     }
     run_fields(s, d, a, base, p, nb);
@@ -1398,7 +1677,8 @@ __device__ __forceinline__ void format_event(S& s, const Dev& d, int cls, uint32
 
 // 8-byte units staged of a record of each class (C_API .. C_OVERHEAD): whole records, except the kernel record's unread tail
 __device__ __forceinline__ uint32_t class_units(int cls) {
-  return cls == C_KERNEL ? 22u : cls == C_MEMCPY2 ? 12u : cls == C_API ? 5u : cls == C_OVERHEAD ? 7u : 11u;
+  return cls == C_KERNEL ? 22u : cls == C_MEMCPY2 ? 12u : (cls == C_API || cls == C_SYNC || cls == C_WAIT) ? 5u
+         : (cls == C_OVERHEAD || cls == C_CUDAEVENT) ? 7u : 11u;
 }
 
 // One thread per work item.  Work items are class-sorted (each class padded to a multiple of 32),
@@ -1415,7 +1695,7 @@ __global__ void __launch_bounds__(kEventThreads, 8) k_events(Dev d) {
     if (threadIdx.x < 8) s_cnt[threadIdx.x] = 0;
     __syncthreads();
   }
-  const uint64_t i = (uint64_t)blockIdx.x * kEventThreads + threadIdx.x;
+  const uint64_t i = d.work_origin + (uint64_t)blockIdx.x * kEventThreads + threadIdx.x;
   Tally t; t.x = 0; t.flow = 0; t.name_bytes = 0; t.ev = 0;
   uint32_t filt = 0;
   int cls = -1;
@@ -1430,6 +1710,8 @@ __global__ void __launch_bounds__(kEventThreads, 8) k_events(Dev d) {
       if (j >= d.cls_count[cls]) cls = -1;  // padding
     }
     if (cls == C_OP && j >= d.n_ops) cls = -1;
+    // deferred synchronisation records are sized in a pass of their own, once the streams with GPU work are known
+    if (!WRITE && (cls == C_WAIT) != (d.wait_pass != 0)) cls = -1;
   }
   uint64_t ev = 0;
   const uint8_t* r = nullptr;
@@ -1518,9 +1800,11 @@ __global__ void k_sort_keys(Dev d, uint64_t* keys, uint32_t* vals, uint64_t span
   for (int c = 1; c < C_EXT; c++) if (i >= d.cls_begin[c]) cls = c;
   if (i - d.cls_begin[cls] >= d.cls_count[cls]) return;  // padding
   const uint8_t* r = d.cupti + (uint64_t)d.work_slot[i] * 8;
-  const int64_t ts = conv_ts(d, *reinterpret_cast<const uint64_t*>(r + (cls == C_API ? 8 : cls == C_OVERHEAD ? 24 : 16)));
+  const int64_t ts = conv_ts(d, *reinterpret_cast<const uint64_t*>(r + ((cls == C_API || cls == C_SYNC || cls == C_WAIT) ? 8
+                                                                         : cls == C_OVERHEAD ? 24 : cls == C_CUDAEVENT ? 40 : 16)));
   uint64_t key = 0;
   if (ts >= d.win_start) { key = (uint64_t)(ts - d.win_start); if (key > span) key = span + 1; }
+  if (cls == C_WAIT) key += span + 2;  // deferred records stay behind everything else
   const uint32_t e = d.work_ev[i] - (uint32_t)d.n_ops;
   keys[e] = key;
   vals[e] = e;

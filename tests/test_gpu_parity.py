@@ -13,7 +13,7 @@ from kineto_b200 import tracefile as tf
 pytestmark = pytest.mark.gpu
 
 GOLDEN = sorted(f[:-5] for f in os.listdir(helpers.GOLDEN) if f.endswith(".k2jt"))
-UNSUPPORTED_ON_GPU = {"sync"}  # synchronisation and CUDA event records: oracle only so far
+UNSUPPORTED_ON_GPU = set()
 
 
 def gpu_run(trace, **kw):
@@ -62,8 +62,14 @@ def test_gpu_matches_reference_golden(name):
     lambda: cases.with_flags(synth.gen_kernel_launches(20_000, seed=209, pool_size=100, user_annotations=15), tf.FLAG_SORT_BY_START),
     lambda: cases.with_flags(cases.tsc_trace(9_000), tf.FLAG_SORT_BY_START),
     lambda: cases.with_flags(cases.annotation_trace(), tf.FLAG_SORT_BY_START),
+    cases.sync_trace,
+    lambda: cases.sync_mix_trace(40_000, seed=45),
+    lambda: cases.sync_mix_trace(9_000, seed=46, flags=1),
+    lambda: cases.with_flags(cases.sync_trace(), tf.FLAG_SORT_BY_START),
+    lambda: cases.with_flags(cases.sync_mix_trace(30_000, seed=47), tf.FLAG_SORT_BY_START),
 ], ids=["generic", "launches", "shard", "mixed", "mixed_small_buffers", "tsc", "edge", "edge_annot", "annotations",
-        "overhead_mix", "sorted_overhead_mix", "launches_annot", "sorted_launches", "sorted_mixed", "sorted_annot", "sorted_tsc", "sorted_small"])
+        "overhead_mix", "sorted_overhead_mix", "launches_annot", "sorted_launches", "sorted_mixed", "sorted_annot", "sorted_tsc", "sorted_small",
+        "sync", "sync_mix", "sync_mix_annot", "sorted_sync", "sorted_sync_mix"])
 def test_gpu_matches_port(gen):
     trace = gen()
     want, stats = helpers.run_port(trace)
