@@ -125,6 +125,12 @@ struct B200TraceLogger::Impl {
     std::vector<uint8_t> flowt;
     std::vector<k2j_md_entry> md;
     std::vector<uint8_t> cupti;
+    // Records put in front of `cupti` that only feed lookups (their timestamps lie before the window, so they
+    // print nothing): what the profiler had already resolved for a synchronisation activity when it reached the
+    // logger - its context's device, the CUDA event record it waits on - restated as the records that make the
+    // device-side lookups give the same answer.
+    std::vector<uint8_t> prefix;
+    std::unordered_map<uint32_t, bool> ctxDeclared;
     bool hasCupti = false;
   };
   Run run;
@@ -139,6 +145,21 @@ struct B200TraceLogger::Impl {
     const uint8_t* p = reinterpret_cast<const uint8_t*>(&rec);
     run.cupti.insert(run.cupti.end(), p, p + sizeof(T));
     run.hasCupti = true;
+  }
+  template <class T> void appendPrefix(const T& rec) {
+    const uint8_t* p = reinterpret_cast<const uint8_t*>(&rec);
+    run.prefix.insert(run.prefix.end(), p, p + sizeof(T));
+  }
+  // The context -> device pair a synchronisation activity was given (contextIdtoDeviceId,
+  // libkineto/src/CuptiActivityProfiler.cpp:527-530), as a memset record that is the context's first writer.
+  void declareContext(uint32_t ctx, uint32_t device) {
+    if (run.ctxDeclared.count(ctx)) return;
+    run.ctxDeclared[ctx] = true;
+    CUpti_ActivityMemsetType m;
+    memset(&m, 0, sizeof m);
+    m.kind = CUPTI_ACTIVITY_KIND_MEMSET;
+    m.contextId = ctx; m.deviceId = device;
+    appendPrefix(m);
   }
   void addLink(const libkineto::ITraceActivity& a) {
     if (!a.linkedActivity()) return;
@@ -174,7 +195,7 @@ bool B200TraceLogger::Impl::flushRun() {
   }
   k2j_params p{};
   p.base_time_ns = ChromeTraceBaseTime::singleton().get();
-  p.window_start_ns = INT64_MIN;  // records arrive already filtered by the profiler
+  p.window_start_ns = 1;  // records arrive already filtered by the profiler; lookup-only records carry timestamp 0
   p.window_end_ns = INT64_MAX;
   p.pid = processId();
   p.ts_mode = 0;  // CuptiActivity<T>::timestamp() was not used: raw timestamps are converted below
@@ -200,6 +221,8 @@ bool B200TraceLogger::Impl::flushRun() {
   ops.n_ops = n; ops.start_ns = r.start.data(); ops.end_ns = r.end.data(); ops.id = r.id.data(); ops.device = r.dev.data();
   ops.resource = r.resource.data(); ops.thread = r.thread.data(); ops.type = r.type.data(); ops.name = r.name.data();
   ops.flow_id = r.flow.data(); ops.flow_info = r.flowt.data(); ops.md_off = r.mdoff.data(); ops.md = r.md.data();
+  r.prefix.insert(r.prefix.end(), r.cupti.begin(), r.cupti.end());
+  r.cupti.swap(r.prefix);
   const uint64_t buftab[2] = {0, r.cupti.size()};
   k2j_result res;
   bool ok = k2j_set_params(ctx, &p, props.data()) == K2J_OK &&
@@ -390,9 +413,39 @@ void B200TraceLogger::handleActivity(const libkineto::ITraceActivity& a) {
     memcpy(&rec, &ov->raw(), sizeof(CUpti_ActivityOverhead));
     convert(rec);
     m.appendRecord(rec);
+  } else if (auto* sy = dynamic_cast<const CudaSyncActivity*>(&a)) {
+    m.addLink(a);
+    CUpti_ActivitySynchronization rec = sy->raw();
+    convert(rec);
+    m.declareContext(rec.contextId, (uint32_t)a.deviceId());
+    if (isEventSync(rec.type)) {
+      // the CUDA event record the profiler found (CuptiActivityProfiler.cpp:452-461) is only visible as metadata
+      MdCollector mc;
+      a.visitTypedMetadata(mc);
+      int64_t srcStream = -1, srcCorr = -1;
+      for (auto& e : mc.entries) {
+        if (e.key == "wait_on_stream") srcStream = (int64_t)e.value;
+        else if (e.key == "wait_on_cuda_event_record_corr_id") srcCorr = (int64_t)e.value;
+      }
+      if (srcCorr != -1 || srcStream != -1) {
+        CUpti_ActivityCudaEventType ev;
+        memset(&ev, 0, sizeof ev);
+        ev.kind = CUPTI_ACTIVITY_KIND_CUDA_EVENT;
+        ev.correlationId = (uint32_t)srcCorr; ev.contextId = rec.contextId; ev.streamId = (uint32_t)srcStream;
+        ev.eventId = rec.cudaEventId;
+        m.appendPrefix(ev);
+      }
+    }
+    m.appendRecord(rec);
+  } else if (auto* ce = dynamic_cast<const CudaEventActivity*>(&a)) {
+    m.addLink(a);
+    CUpti_ActivityCudaEventType rec = ce->raw();
+    rec.deviceTimestamp = (uint64_t)convertCuptiTimestamp(rec.deviceTimestamp);
+    m.declareContext(rec.contextId, (uint32_t)a.deviceId());
+    m.appendRecord(rec);
   } else {
-    // Synchronisation and CUDA-event records and foreign activity classes are not handled by
-    // the GPU path yet; there is no CPU path to fall back to, so they are counted and reported.
+    // Foreign activity classes are not handled by the GPU path; there is no CPU path to fall back to, so they
+    // are counted and reported.
     if (skipped_++ == 0) LOG(ERROR) << "B200TraceLogger: unsupported activity class for '" << a.name() << "'; skipped";
   }
 }

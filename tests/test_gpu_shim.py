@@ -22,7 +22,9 @@ SHIM = os.path.join(helpers.ROOT, "oracle", "_ref", "shim_driver")
     lambda: cases.edge_trace(flags=1),
     cases.annotation_trace,
     lambda: cases.tsc_trace(1500),
-], ids=["launches_annot", "mixed", "edge", "annotations", "tsc"])
+    cases.sync_trace,
+    lambda: cases.sync_mix_trace(6000, seed=48),
+], ids=["launches_annot", "mixed", "edge", "annotations", "tsc", "sync", "sync_mix"])
 def test_logger_shim_writes_the_reference_file(gen, tmp_path):
     trace = gen()
     p = str(tmp_path / "t.k2jt")
