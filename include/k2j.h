@@ -162,7 +162,12 @@ k2j_status k2j_set_ops(k2j_ctx* ctx, const k2j_ops* ops);
 /* The drained CUPTI activity buffers: what CuptiActivityApi::processActivities iterates
  * (libkineto/src/CuptiActivityApi.cpp:235-246).  `buftab` holds (byte offset, valid bytes) per
  * buffer, in processing order; records are packed back to back, 8-byte aligned, sized by kind.
- * The `name` field of kernel records holds a string id. At most 32 GiB per call. */
+ * The `name` field of kernel records holds a string id. At most 32 GiB per call.
+ * Kinds that are sized and formatted: CONCURRENT_KERNEL (CUpti_ActivityKernel9), MEMCPY (Memcpy5), MEMCPY2
+ * (MemcpyPtoP4), MEMSET (Memset4), RUNTIME / DRIVER (ActivityAPI), EXTERNAL_CORRELATION, OVERHEAD (Overhead3),
+ * SYNCHRONIZATION (ActivitySynchronization) and CUDA_EVENT (CudaEvent2)
+ * (libkineto/src/CuptiActivityProfiler.cpp:532-588).  A record of any other kind ends the walk of its buffer and
+ * is counted in unexpected_cuda_events. */
 k2j_status k2j_set_cupti(k2j_ctx* ctx, const uint8_t* bytes, uint64_t n_bytes, const uint64_t* buftab,
                          uint32_t n_buffers);
 
