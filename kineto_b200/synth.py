@@ -619,3 +619,121 @@ def gen_mixed(n=10_000_000, seed=3, n_devices=8, n_streams=32, pool_size=50_000,
     last = max(int(kern["end"].max()) if len(kern) else 0, int(api["end"].max()))
     window = (t0 - 1000, last + 1_000_000)
     return _finish(t, pool, 1, window, n_devices)
+
+
+def _shape_strings(rng, pool, count, max_len=256):
+    """`count` (Input Dims, Input type) string-id pairs: nested lists of tensor shapes and the matching dtype
+    lists, as PyTorch's profiler renders them, up to `max_len` bytes."""
+    dtypes = ["float", "c10::Half", "c10::BFloat16", "long int", "int", "bool", "Scalar", ""]
+    dims, types = [], []
+    for _ in range(count):
+        while True:
+            n_in = int(rng.integers(1, 9))
+            shapes = [[int(x) for x in rng.integers(1, 65536, int(rng.integers(0, 5)))] for _ in range(n_in)]
+            d = "[" + ", ".join("[" + ", ".join(map(str, s)) + "]" for s in shapes) + "]"
+            ty = "[" + ", ".join('"%s"' % dtypes[int(rng.integers(0, len(dtypes)))] for _ in range(n_in)) + "]"
+            if len(d) <= max_len and len(ty) <= max_len:
+                break
+        dims.append(pool.add(d))
+        types.append(pool.add(ty))
+    return np.array(dims, np.uint64), np.array(types, np.uint64)
+
+
+def _span_tree(rng, n_ops, t0, root_ns=20_000_000, max_depth=(1, 16), children_mean=3.0):
+    """Nested spans, level by level: roots follow one another; a node below its root's depth limit (uniform in
+    `max_depth`) and wide enough to hold them gets Poisson(`children_mean`) children that split its interior.
+    Every root's tree is grown in full; the first `n_ops` nodes in order of their start time are returned as
+    (start, end, depth, root)."""
+    starts, ends, depths, roots = [], [], [], []
+    total, next_t, root_id = 0, t0, 0
+    while total < n_ops:
+        n_roots = max(1, (n_ops - total) // 100_000)
+        s = next_t + np.arange(n_roots, dtype=np.int64) * (root_ns + 1000)
+        e = s + root_ns
+        next_t = int(e[-1]) + 1000
+        limit = rng.integers(max_depth[0], max_depth[1] + 1, n_roots)
+        root = root_id + np.arange(n_roots)
+        root_id += n_roots
+        depth = 1
+        while len(s):
+            starts.append(s); ends.append(e); depths.append(np.full(len(s), depth, np.int32)); roots.append(root)
+            total += len(s)
+            k = rng.poisson(children_mean, len(s))
+            k = np.where((depth < limit) & (e - s >= 64 * (k + 1)), k, 0)
+            par = np.repeat(np.arange(len(s)), k)
+            if len(par) == 0:
+                break
+            idx = np.arange(len(par)) - np.repeat(np.cumsum(k) - k, k)   # child number within its parent
+            w = (e[par] - s[par] - 16) // k[par]
+            cs = s[par] + 8 + idx * w
+            s, e, limit, root = cs, cs + w - 4, limit[par], root[par]
+            depth += 1
+    s, e, d, r = (np.concatenate(x) for x in (starts, ends, depths, roots))
+    o = np.argsort(s, kind="stable")[:n_ops]
+    return s[o], e[o], d[o], r[o]
+
+
+def gen_op_tree(n_ops=200_000, launches_per_op=2.0, seed=4, n_devices=8, n_streams=32, pool_size=4096,
+                name_len=(20, 400), n_shapes=2048, buffer_bytes=4 << 20) -> tf.Trace:
+    """A CPU op tree of nested record_function spans (depth limit uniform 1-16 per root, Poisson(3) children)
+    whose ops carry `Input Dims` / `Input type` strings of up to 256 bytes, forward-backward flow pairs between
+    ops, and `launches_per_op * n_ops` kernel launches (EXTERNAL_CORRELATION + cudaLaunchKernel + Kernel9
+    records: two GPU-side activities each) issued by random ops of the tree."""
+    rng = np.random.default_rng(seed)
+    pool = tf.StringPool()
+    names = np.array([pool.add(s) for s in name_pool(rng, pool_size, *name_len)], np.uint64)
+    t0 = DEFAULT_BASE_TIME + 1_000_000_000
+    s, e, depth, _ = _span_tree(rng, n_ops, t0)
+    n = len(s)
+    t = tf.Trace()
+    t.op_start, t.op_end = s, e
+    t.op_id = np.arange(1, n + 1, dtype=np.int32)
+    t.op_device = np.full(n, DEFAULT_PID, np.int32)
+    thr = rng.integers(0, 16, n)
+    t.op_resource = (50_000 + thr).astype(np.int64)
+    t.op_thread = (1_000_000 + 7 * thr).astype(np.int32)
+    t.op_type = np.full(n, CPU_OP, np.int32)
+    aten = np.array([pool.add(x) for x in _ATEN], np.uint32)
+    t.op_name = aten[rng.integers(0, len(aten), n)]
+    # forward-backward links: every 16th op starts a flow that the op 8 places later ends
+    t.op_flow = np.zeros(n, np.uint32)
+    t.op_flowt = np.zeros(n, np.uint8)
+    src = np.arange(0, n - 8, 16)
+    t.op_flow[src] = t.op_flow[src + 8] = (src // 16 + 1).astype(np.uint32)
+    t.op_flowt[src], t.op_flowt[src + 8] = 1 | (1 << 4), 1
+    keys = ["Sequence number", "Input Dims", "Input type", "Record function id"]
+    order = md_visit_order(tuple(keys))
+    dims, types = _shape_strings(rng, pool, n_shapes)
+    pick = rng.integers(0, n_shapes, n)
+    cols = {"Sequence number": (tf.MD_INT64, np.arange(n).astype(np.uint64)),
+            "Input Dims": (tf.MD_RAWJSON, dims[pick]), "Input type": (tf.MD_RAWJSON, types[pick]),
+            "Record function id": (tf.MD_INT64, depth.astype(np.uint64))}
+    nk = len(keys)
+    md = np.zeros(n * nk, tf.MD_ENTRY)
+    for j, k in enumerate(order):
+        md["key"][j::nk] = pool.add(k)
+        md["type"][j::nk] = cols[k][0]
+        md["value"][j::nk] = cols[k][1]
+    t.md = md
+    t.op_mdoff = (np.arange(n + 1, dtype=np.uint32) * nk).astype(np.uint32)
+    t.tidmap = np.stack([1_000_000 + 7 * np.arange(16), 50_000 + np.arange(16)], 1).astype(np.int32).reshape(-1)
+    # launches
+    m = int(launches_per_op * n)
+    owner = np.sort(rng.integers(0, n, m))
+    corr = (np.arange(m, dtype=np.int64) + 1000).astype(np.uint32)
+    ext = np.zeros(m, tf.EXTCORR)
+    ext["kind"], ext["externalKind"] = tf.KIND_EXTERNAL_CORRELATION, tf.EXTERNAL_KIND_CUSTOM0
+    ext["externalId"], ext["correlationId"] = t.op_id[owner].astype(np.uint64), corr
+    api = np.zeros(m, tf.API)
+    api["kind"], api["cbid"] = tf.KIND_RUNTIME, CBID_cudaLaunchKernel
+    api["start"] = s[owner] + rng.integers(0, 8, m)
+    api["end"] = api["start"] + rng.integers(1500, 9000, m)
+    api["processId"], api["threadId"] = DEFAULT_PID, t.op_thread[owner].astype(np.uint32)
+    api["correlationId"] = corr
+    perm = rng.permutation(m)
+    kstart = api["start"][perm].astype(np.int64) + rng.integers(3000, 200_000, m)
+    kern = _kernel_records(rng, m, names, kstart, _lognormal_dur(rng, m), corr[perm], n_devices, n_streams)
+    window = (t0 - 1000, int(max(e.max(), kstart.max())) + 10_000_000_000)
+    t.cupti, offs = tf.interleave([ext, api, kern], np.tile(np.array([0, 1, 2], np.int8), m))
+    t.buftab = tf.make_buftab(offs, buffer_bytes)
+    return _finish(t, pool, 1, window, n_devices)

@@ -221,6 +221,7 @@ struct Event {
   int type; std::string name; int64_t ts, dur, device, resource; bool hasLinked; int64_t linkedId;
   int64_t corrId; std::string md; int64_t flowId; int flowType; bool flowStart;
   bool streamSync = false;  // a CUDA_SYNC activity named "Stream Sync": shown on a row of its own
+  std::string extra;        // collective arguments of a kernel launched by record_param_comms: appended as they are
 };
 constexpr int64_t kSyncStreamTidOffset = 1000000;  // output_json.h:237
 void emit(Out& o, const Event& e) {
@@ -240,6 +241,7 @@ void emit(Out& o, const Event& e) {
   std::string md = e.md;
   sanitize(md);
   if (!md.empty() && !allSpace(md)) { if (!args.empty()) args += ","; args += md; }
+  args += e.extra;  // every entry brings its own leading comma: a kernel's own metadata is never empty
   int64_t resource = e.resource;
   if (e.streamSync) {  // output_json.cpp:914-943: two metadata rows the first time a (device, row) pair shows up
     const int64_t syncTid = resource + kSyncStreamTidOffset;
@@ -359,6 +361,65 @@ struct Run {
     if (it2 == activityMap.end()) return false;
     *id = tf.ptr<int32_t>("OPID")[it2->second];
     return true;
+  }
+  // Collective metadata copied from the linked record_param_comms CPU op onto a kernel event
+  // (ChromeTraceLogger::appendCollectiveArgs, libkineto/src/output_json.cpp:718-801; handleActivity :900-906).
+  // Values are the op's metadata rendered by metadataValueToString (libkineto/src/GenericTraceActivity.cpp:20-47);
+  // nothing here is sanitised.  Ops of other shards carry no metadata here, so sharded runs do not enrich.
+  std::string mdValue(size_t row, const char* key, bool* found = nullptr) {
+    const uint32_t* off = tf.ptr<uint32_t>("OPMDOFF");
+    const k2jt_md_entry* md = tf.ptr<k2jt_md_entry>("MDENT");
+    for (uint32_t e = off[row]; e < off[row + 1]; e++) {
+      if (tf.str(md[e].key) != key) continue;
+      if (found) *found = true;
+      std::string v;
+      switch (md[e].type) {
+        case 0: appendI(v, (int64_t)md[e].value); break;
+        case 1: appendU(v, md[e].value); break;
+        case 2: { double d; memcpy(&d, &md[e].value, 8); appendFmtDouble(v, d); break; }
+        case 3: v = md[e].value ? "true" : "false"; break;
+        default: v = tf.str((uint32_t)md[e].value); break;
+      }
+      return v;
+    }
+    return "";
+  }
+  static std::string stripQuotes(std::string v) {
+    if (v.size() >= 2 && v.front() == '"' && v.back() == '"') { v.pop_back(); v.erase(0, 1); }
+    return v;
+  }
+  std::string collectiveArgs(uint32_t corr) {
+    if (globalJoin()) return "";
+    auto it = cpuCorr.find((int64_t)(int32_t)corr);
+    if (it == cpuCorr.end()) return "";
+    auto it2 = activityMap.find(it->second);
+    if (it2 == activityMap.end()) return "";
+    const size_t row = it2->second;
+    if (tf.str(tf.ptr<uint32_t>("OPNAME")[row]) != "record_param_comms") return "";
+    std::string a;
+    auto raw = [&](const char* k, const std::string& v) { a += ",\""; a += k; a += "\": "; a += v; };
+    auto quoted = [&](const char* k, const std::string& v) { a += ",\""; a += k; a += "\": \""; a += v; a += "\""; };
+    const std::string name = stripQuotes(mdValue(row, "Collective name")), inMsg = mdValue(row, "In msg nelems"),
+                      outMsg = mdValue(row, "Out msg nelems"), groupSize = mdValue(row, "Group size"),
+                      dtype = stripQuotes(mdValue(row, "dtype"));
+    if (!name.empty() && !inMsg.empty() && !outMsg.empty() && !groupSize.empty() && !dtype.empty()) {
+      quoted("Collective name", name); raw("In msg nelems", inMsg); raw("Out msg nelems", outMsg); raw("Group size", groupSize);
+      quoted("dtype", dtype);
+    }
+    const std::string inStart = stripQuotes(mdValue(row, "Input Tensors start")), outStart = stripQuotes(mdValue(row, "Output Tensors start"));
+    if (!inStart.empty()) quoted("Input Tensors start", inStart);
+    if (!outStart.empty()) quoted("Output Tensors start", outStart);
+    const std::string inSplit = stripQuotes(mdValue(row, "In split size")), outSplit = stripQuotes(mdValue(row, "Out split size"));
+    if (!inSplit.empty() && !outSplit.empty()) { quoted("In split size", inSplit); quoted("Out split size", outSplit); }
+    for (const char* k : {"Process Group Name", "Process Group Description", "Process Group Ranks"}) {
+      const std::string v = stripQuotes(mdValue(row, k));
+      if (!v.empty()) quoted(k, v);
+    }
+    for (const char* k : {"Dst Rank", "Src Rank", "Seq", "Comms Id"}) {
+      const std::string v = mdValue(row, k);
+      if (!v.empty()) raw(k, v);
+    }
+    return a;
   }
   bool outOfRange(int64_t ts, int64_t dur) {
     bool oor = ts < p.window_start_ns || (ts + dur) > p.window_end_ns;
@@ -615,6 +676,7 @@ struct Run {
     f.endDict();
     graphAndChannel(f, rd<uint32_t>(r, 156), rd<uint64_t>(r, 144), rd<uint32_t>(r, 168), rd<uint32_t>(r, 172));
     e.md = f.j;
+    e.extra = collectiveArgs(corr);
     emit(out, e);
     afterGpu(e);
   }

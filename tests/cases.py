@@ -275,6 +275,54 @@ def sync_mix_trace(n=3000, seed=43, flags=0) -> tf.Trace:
     return b.build()
 
 
+def collective_trace(n=40, seed=51) -> tf.Trace:
+    """Kernels launched from record_param_comms CPU ops: the logger copies the op's collective metadata onto the
+    kernel event (libkineto/src/output_json.cpp:718-801, :900-906).  Covers complete and incomplete key sets,
+    quoted and unquoted strings, every value type, and ops that are not collectives."""
+    rng = np.random.default_rng(seed)
+    b = synth.TraceBuilder(n_devices=8)
+    t0 = b.t0
+    colls = ["allreduce", "allgather", "reduce_scatter", "all_to_all"]
+    S, R, I, U, D, B = tf.MD_STRING, tf.MD_RAWJSON, tf.MD_INT64, tf.MD_UINT64, tf.MD_DOUBLE, tf.MD_BOOL
+    for i in range(n):
+        name = colls[i % 4]
+        size = int(np.exp(rng.uniform(np.log(1 << 10), np.log(1 << 32))))
+        ranks = list(range(int(rng.integers(2, 9))))
+        md = [("Collective name", S if i % 3 else R, name if i % 3 else '"%s"' % name),
+              ("In msg nelems", I, size), ("Out msg nelems", I, size * (len(ranks) if name == "allgather" else 1)),
+              ("Group size", I, len(ranks)), ("dtype", S, "BFloat16" if i % 2 else '"Float"'),
+              ("Process Group Name", S, str(i % 3)), ("Process Group Description", S, "default_pg" if i % 3 == 0 else "tp\\group"),
+              ("Process Group Ranks", R, str(ranks)), ("Rank", I, 3), ("Seq", I, i), ("Comms Id", U, (1 << 63) + i)]
+        if name == "all_to_all":
+            md += [("In split size", R, str([size // len(ranks)] * len(ranks))), ("Out split size", R, "[]" if i % 8 == 3 else str(ranks))]
+        if i % 5 == 1:
+            md += [("Input Tensors start", R, "[139800000000000]"), ("Output Tensors start", S, "[1, 2]")]
+        if i % 7 == 2:
+            md += [("Src Rank", I, 1), ("Dst Rank", I, -1)]
+        if i % 9 == 4:
+            md = [m for m in md if m[0] != "Group size"]             # incomplete: the first five keys are dropped together
+        if i % 11 == 5:
+            md = [m for m in md if m[0] != "dtype"] + [("dtype", S, '""')]   # a quoted empty string counts as absent
+        if i % 13 == 6:
+            md += [("Dst Rank", D, 2.5), ("Src Rank", B, 1)] if i % 7 != 2 else []
+        b.op(t0 + 1000 * i, t0 + 1000 * i + 800, 100 + i, "record_param_comms", md=md)
+        b.extcorr(500 + i, 100 + i)
+        b.runtime(t0 + 1000 * i + 10, t0 + 1000 * i + 20, 500 + i)
+        b.kernel(t0 + 1000 * i + 300, t0 + 1000 * i + 700, 500 + i, "ncclDevKernel_%s_RING_LL(ncclDevKernelArgs)" % name,
+                 device=i % 8, stream=20 + i % 3)
+    # not collectives: another op name, a copy launched by a collective op, a kernel without a link
+    b.op(t0 + 90_000, t0 + 90_500, 900, "aten::add", md=[("Collective name", S, "allreduce")])
+    b.extcorr(901, 900)
+    b.kernel(t0 + 90_100, t0 + 90_200, 901, "linked to an ordinary op")
+    b.extcorr(902, 100)
+    b.memcpy(t0 + 90_300, t0 + 90_400, 902, 4096)
+    b.kernel(t0 + 90_500, t0 + 90_600, 903, "no link")
+    b.op(t0 + 91_000, t0 + 91_500, 950, "record_param_comms")                      # no metadata at all
+    b.extcorr(951, 950)
+    b.kernel(t0 + 91_100, t0 + 91_200, 951, "collective op without metadata")
+    return b.build()
+
+
 CASES = {
     "edge": edge_trace,
     "generic_300": lambda: synth.gen_generic_kernels(300, seed=31, pool_size=40),
@@ -282,6 +330,7 @@ CASES = {
     "mixed_400": lambda: synth.gen_mixed(400, seed=33, pool_size=100, escape_fraction=0.2),
     "tsc_100": lambda: tsc_trace(100),
     "sync": sync_trace,
+    "collectives": collective_trace,
 }
 
 

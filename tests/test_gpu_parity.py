@@ -67,9 +67,10 @@ def test_gpu_matches_reference_golden(name):
     lambda: cases.sync_mix_trace(9_000, seed=46, flags=1),
     lambda: cases.with_flags(cases.sync_trace(), tf.FLAG_SORT_BY_START),
     lambda: cases.with_flags(cases.sync_mix_trace(30_000, seed=47), tf.FLAG_SORT_BY_START),
+    lambda: synth.gen_op_tree(60_000, seed=210, pool_size=500, n_shapes=256),
 ], ids=["generic", "launches", "shard", "mixed", "mixed_small_buffers", "tsc", "edge", "edge_annot", "annotations",
         "overhead_mix", "sorted_overhead_mix", "launches_annot", "sorted_launches", "sorted_mixed", "sorted_annot", "sorted_tsc", "sorted_small",
-        "sync", "sync_mix", "sync_mix_annot", "sorted_sync", "sorted_sync_mix"])
+        "sync", "sync_mix", "sync_mix_annot", "sorted_sync", "sorted_sync_mix", "op_tree"])
 def test_gpu_matches_port(gen):
     trace = gen()
     want, stats = helpers.run_port(trace)
