@@ -68,7 +68,7 @@ struct k2j_ctx {
   DevBuf ds_tab, span_key, span_nstart, span_end, span_nfirst, span_row, span_out, span_cnt, ann_size, ann_off;
   DevBuf sort_keys[2], sort_vals[2], sort_hist, sort_base, sort_rank;
   DevBuf tid_tab, corr_tab, user_tab, op_tab, work_slot, work_ev, ev_size, ev_off, ev_ext, out, counters;
-  uint64_t* h_totals = nullptr;   // pinned, 32 words: [0, C_NCOL) column totals, 20 text bytes, 21 bytes of CPU-op text, 22 annotation bytes, 23 sort, 24 scan entry point
+  uint64_t* h_totals = nullptr;   // pinned, 32 words: [0, C_NCOL) column totals, 20 text bytes, 21 bytes of CPU-op text, 22 annotation bytes, 23 sort, 24 scan entry point, 25 the record_param_comms flag
   Counters* h_counters = nullptr; // pinned
   cudaEvent_t ev[8]{};
   uint64_t out_bytes = 0;
@@ -78,6 +78,7 @@ struct k2j_ctx {
   uint32_t launches = 0;
   DevBuf ext_local;
   DevBuf ctx_tab, evt_recs, seen_tab, row_key, row_first, corr_zero;  // synchronisation records
+  DevBuf str_class, comms_flag;                                       // collective enrichment
   const void* g_ext = nullptr; uint64_t g_n_ext = 0, g_own_begin = 0;
   const int32_t* g_op_ids = nullptr; uint64_t g_n_ops = 0;
 };
@@ -311,7 +312,7 @@ void k2j_destroy(k2j_ctx* c) {
                     &c->span_out, &c->span_cnt, &c->ann_size, &c->ann_off, &c->sort_keys[0], &c->sort_keys[1], &c->sort_vals[0],
                     &c->sort_vals[1], &c->sort_hist, &c->sort_base, &c->sort_rank, &c->tid_tab, &c->corr_tab, &c->user_tab, &c->op_tab,
                     &c->work_slot, &c->work_ev, &c->ev_size, &c->ev_off, &c->ev_ext, &c->out, &c->counters, &c->ext_local, &c->ctx_tab, &c->evt_recs,
-                    &c->seen_tab, &c->row_key, &c->row_first, &c->corr_zero})
+                    &c->seen_tab, &c->row_key, &c->row_first, &c->corr_zero, &c->str_class, &c->comms_flag})
     b->release();
   if (c->h_totals) cudaFreeHost(c->h_totals);
   if (c->h_counters) cudaFreeHost(c->h_counters);
@@ -370,6 +371,7 @@ k2j_status k2j_set_strings(k2j_ctx* c, const uint64_t* off, const uint8_t* data,
   K2J_CUDA(c, c->esc_md.reserve(total + 8 * (n + 1) + 16));
   K2J_CUDA(c, c->esc_name_len.reserve((n + 1) * 4));
   K2J_CUDA(c, c->esc_md_len.reserve((n + 1) * 4));
+  K2J_CUDA(c, c->str_class.reserve(n + 1));
   return K2J_OK;
 }
 
@@ -472,6 +474,7 @@ k2j_status k2j_segment(k2j_ctx* c, k2j_segment_info* info) {
   d.pool_off = (const uint64_t*)c->pool_off.dev; d.pool_data = (const uint8_t*)c->pool_data.dev; d.n_strings = (uint32_t)c->n_strings;
   d.esc_name = c->esc_name.as<uint8_t>(); d.esc_md = c->esc_md.as<uint8_t>();
   d.esc_name_len = c->esc_name_len.as<uint32_t>(); d.esc_md_len = c->esc_md_len.as<uint32_t>();
+  d.str_class = c->str_class.as<uint8_t>();
   d.rt_names = (const uint32_t*)c->rt_names.dev; d.n_rt = c->n_rt; d.dr_names = (const uint32_t*)c->dr_names.dev; d.n_dr = c->n_dr;
   d.tid_pairs = (const int32_t*)c->tid_pairs.dev; d.n_tid_pairs = c->n_tid;
   d.cupti = (const uint8_t*)c->cupti.dev; d.cupti_bytes = c->cupti_bytes;
@@ -652,6 +655,16 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
     K2J_CUDA(c, cudaMemsetAsync(d.need_op, 0, op_bits / 8, s));
     if (d.ops_begin) { k_mark_corr<<<(uint32_t)((d.ops_begin + 255) / 256), 256, 0, s>>>(d); c->launches++; }
   }
+  // collective enrichment: kernels look at their linked op's name only if some op is a record_param_comms call;
+  // ops of other shards carry no metadata here, so sharded runs do not enrich
+  d.has_comms = nullptr;
+  if (!c->have_global_join && c->n_ops && c->n_strings) {
+    K2J_CUDA(c, c->comms_flag.reserve(16));
+    K2J_CUDA(c, cudaMemsetAsync(c->comms_flag.p, 0, 4, s));
+    k_find_comms<<<(uint32_t)((c->n_ops + 255) / 256), 256, 0, s>>>(d, c->comms_flag.as<uint32_t>());
+    c->launches++;
+    d.has_comms = c->comms_flag.as<uint32_t>();
+  }
   // synchronisation and CUDA event records: their lookup structures exist only when such records do
   d.ctx_tab = nullptr; d.evt = nullptr; d.n_evt = 0; d.seen_tab = nullptr; d.row_key = nullptr; d.row_first = nullptr; d.corr_zero = nullptr;
   d.work_origin = 0; d.wait_pass = 0;
@@ -719,6 +732,8 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
     K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 20, c->scan_totals.as<uint64_t>() + 20, 8, cudaMemcpyDeviceToHost, s));
     if (n_gpu_events)
       K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 21, c->ev_off.as<uint64_t>() + c->n_ops, 8, cudaMemcpyDeviceToHost, s));
+    c->h_totals[25] = 0;
+    if (d.has_comms) K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 25, d.has_comms, 4, cudaMemcpyDeviceToHost, s));
     K2J_CUDA(c, cudaEventRecord(c->ev[4], s));
     K2J_CUDA(c, cudaStreamSynchronize(s));
     total_bytes = c->h_totals[20];
@@ -730,6 +745,15 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
     d.out = c->out.as<uint8_t>(); d.out_cap = total_bytes + ann_bytes;
     K2J_CUDA(c, cudaEventRecord(c->ev[7], s));
     if (total_bytes) { k_events<true><<<ev_blocks, kEventThreads, 0, s>>>(d); c->launches++; }
+    if (total_bytes && c->h_totals[25] != 0 && totals[C_KERNEL]) {
+      // kernel events that carry collective metadata: a launch of their own over the kernel records, so that the
+      // launch above holds no code for them
+      Dev dk = d;
+      dk.work_origin = d.cls_begin[C_KERNEL];
+      dk.n_work = d.cls_begin[C_KERNEL] + ((totals[C_KERNEL] + 31) & ~31ull);
+      k_events<true, true><<<(uint32_t)((dk.n_work - dk.work_origin + kEventThreads - 1) / kEventThreads), kEventThreads, 0, s>>>(dk);
+      c->launches++;
+    }
     if (ann_bytes) {
       k_annotations<true><<<(n_spans + kEventThreads - 1) / kEventThreads, kEventThreads, 0, s>>>(
           d, c->span_out.as<SpanRec>(), n_spans, c->ann_size.as<uint32_t>(), c->ann_off.as<uint64_t>(), total_bytes);

@@ -105,6 +105,8 @@ struct Dev {
   // strings
   const uint64_t* pool_off; const uint8_t* pool_data; uint32_t n_strings;
   uint32_t* esc_name_len; uint32_t* esc_md_len; uint8_t* esc_name; uint8_t* esc_md;
+  uint8_t* str_class;      // per pool string: 0, 1 = "record_param_comms", 2 + k = the k-th collective metadata key
+  const uint32_t* has_comms;  // non-zero when a CPU-side activity of this run is named record_param_comms (nullptr: no enrichment)
   const uint32_t* rt_names; uint32_t n_rt; const uint32_t* dr_names; uint32_t n_dr;
   const int32_t* tid_pairs; uint32_t n_tid_pairs; unsigned long long* tid_tab; uint32_t tid_mask;
   // CUPTI bytes and segmentation
@@ -216,6 +218,14 @@ __device__ __forceinline__ uint32_t tab_find(const unsigned long long* tab, uint
 // One warp per string.  Name flavour (output_json.cpp:946-949): "kernel" -> "Kernel"; '\\' -> '/';
 // '\n' dropped; any remaining byte outside 0x20..0x7e turns the whole name into "unknown"; '"' gets a
 // backslash.  Metadata flavour (output_json.cpp:896-897): only '\\' -> '/' and '\n' dropped.
+// Strings the collective enrichment looks for (libkineto/src/output_json.cpp:34-52): the CPU op's name, then the
+// metadata keys in the order appendCollectiveArgs (:718-801) reads them.
+constexpr int kCollKeys = 16;
+__constant__ char g_coll_str[1 + kCollKeys][28] = {
+    "record_param_comms", "Collective name", "In msg nelems", "Out msg nelems", "Group size", "dtype", "Input Tensors start",
+    "Output Tensors start", "In split size", "Out split size", "Process Group Name", "Process Group Description",
+    "Process Group Ranks", "Dst Rank", "Src Rank", "Seq", "Comms Id"};
+__constant__ uint8_t g_coll_len[1 + kCollKeys] = {18, 15, 13, 14, 10, 5, 19, 20, 13, 14, 18, 25, 19, 8, 8, 3, 8};
 __global__ void k_escape_pool(Dev d) {
   const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const uint32_t lane = threadIdx.x & 31;
@@ -225,6 +235,17 @@ __global__ void k_escape_pool(Dev d) {
   const uint8_t* src = d.pool_data + b;
   uint8_t* dn = d.esc_name + esc_name_pos(d, warp);
   uint8_t* dm = d.esc_md + esc_md_pos(d, warp);
+  {  // class of the string for the collective enrichment: a byte-wise match against seventeen short constants
+    const uint8_t raw = lane < len ? src[lane] : 0;
+    uint32_t cls = 0;
+    if (len >= 3 && len <= 25) {
+      for (int k = 0; k <= kCollKeys; k++) {
+        const bool same = len == g_coll_len[k] && (lane >= len || raw == (uint8_t)g_coll_str[k][lane]);
+        if (__all_sync(0xffffffffu, same)) cls = 1u + (uint32_t)k;
+      }
+    }
+    if (lane == 0) d.str_class[warp] = (uint8_t)cls;
+  }
   bool is_kernel = false;
   if (len == 6) {
     is_kernel = src[0] == 'k' && src[1] == 'e' && src[2] == 'r' && src[3] == 'n' && src[4] == 'e' && src[5] == 'l';
@@ -544,6 +565,14 @@ __global__ void k_mark_corr(Dev d) {
   const int off = cls == C_API ? 32 : cls == C_KERNEL ? 92 : cls == C_MEMCPY2 ? 60 : cls == C_CUDAEVENT ? 4 : (cls == C_SYNC || cls == C_WAIT) ? 24 : 44;
   bit_set(d.need_corr, d.need_corr_mask, *reinterpret_cast<const uint32_t*>(r + off));
 }
+// Is any CPU-side activity of this run named record_param_comms?  Kernel events look at their linked op's name
+// only if so.
+__global__ void k_find_comms(Dev d, uint32_t* flag) {
+  const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= d.n_ops) return;
+  const uint32_t name = d.op_name[i];
+  if (name < d.n_strings && d.str_class[name] == 1u) *flag = 1u;
+}
 // CPU-op id -> position (last writer wins): activityMap_[id] = op, GenericActivityProfiler.cpp:262.
 __global__ void k_build_ops(Dev d) {
   const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -746,7 +775,8 @@ struct CountSink2 : CountSink {
 // is read from the thread's area in shared memory: the staged record itself, with the values that
 // are computed rather than stored (converted times, the linked op, occupancy ...) written by the
 // class's gather step into parts of the record that no field reads.
-enum : uint8_t { T_NONE = 0, T_U64, T_I64, T_TS, T_DBL, T_NAME, T_CSTR, T_MD /* the metadata entries of a CPU-side activity */ };
+enum : uint8_t { T_NONE = 0, T_U64, T_I64, T_TS, T_DBL, T_NAME, T_CSTR, T_MD /* the metadata entries of a CPU-side activity */,
+                 T_COLL = 11 /* collective metadata copied from the linked record_param_comms op */ };
 enum : uint8_t { VK_U32 = 0, VK_I32 /* sign-extended */, VK_64 };
 struct FieldSrc { const char* lit; uint8_t type; uint8_t vk; uint16_t voff; };
 struct FieldDesc { uint16_t off, len; uint8_t type, vk; uint16_t voff; };
@@ -792,13 +822,13 @@ enum : int { A_HEAD_RT, A_HEAD_DR, A_NAME, A_INVALID, A_PID, A_TID, A_TS, A_DUR,
     {",\n    \"cat\": \"ac2g\",\n    \"name\": \"ac2g\"\n    ", T_NONE}, {", \"bp\": \"e\"", T_NONE}, {FLOW_TAIL, T_NONE}
 
 // -- kernel record (GpuActivity<Kernel>, libkineto/src/CuptiActivity.h:499-576; 208 bytes) --
-enum : int { KS_REGS = 8, KS_SMEM = 12, KS_TS = 16, KS_DUR = 24, KS_BPS = 32, KR_DEV = 40, KR_CTX = 44, KR_STREAM = 48, KR_GRID = 52,
+enum : int { KS_COLLROW = 0 /* row of the linked record_param_comms op */, KS_REGS = 8, KS_SMEM = 12, KS_TS = 16, KS_DUR = 24, KS_BPS = 32, KR_DEV = 40, KR_CTX = 44, KR_STREAM = 48, KR_GRID = 52,
              KR_BLOCK = 64, KS_PCT = 84, KS_ACTIVE = 88, KR_CORR = 92, KS_EXT = 96, KS_LIMIT = 100, KR_NAME = 104, KS_LREGS = 108,
              KS_LSMEM = 112, KS_LWARPS = 116, KR_QUEUED = 120, KS_WPS = 128, KS_LBLOCKS = 136, KS_LBARR = 140, KR_NODE = 144,
              KS_AREGS = 152, KR_GRAPH = 156, KS_ASMEM = 160, KR_CHAN = 168, KR_CHTYPE = 172 };
 enum : int { K_HEAD, K_PID, K_TID, K_TS, K_DUR, K_ARGS, K_EXT, K_EXTC, K_QUEUED, K_DEV, K_CTX, K_STREAM, K_CORR, K_REGS, K_SMEM,
              K_BPS, K_WPS, K_GX, K_GY, K_GZ, K_BX, K_BY, K_BZ, K_OCCPCT, K_ACTIVE, K_LIMIT, K_LREGS, K_LSMEM, K_LWARPS, K_LBLOCKS,
-             K_LBARR, K_AREGS, K_ASMEM, K_GRAPH, K_NODE, K_CHAN, K_CHTYPE, K_CLOSE, K_FLOW, K_FPID, K_FTID, K_FTS, K_FEND, K_COUNT };
+             K_LBARR, K_AREGS, K_ASMEM, K_GRAPH, K_NODE, K_CHAN, K_CHTYPE, K_COLL, K_CLOSE, K_FLOW, K_FPID, K_FTID, K_FTS, K_FEND, K_COUNT };
 #define K2J_KERNEL_FIELDS \
     {XHEAD("kernel"), T_NAME, VK_U32, KR_NAME}, {"\",\n    \"pid\": ", T_U64, VK_U32, KR_DEV}, {",\n    \"tid\": ", T_U64, VK_U32, KR_STREAM}, \
     {",\n    \"ts\": ", T_TS, VK_64, KS_TS}, {",\n    \"dur\": ", T_TS, VK_64, KS_DUR}, {"\n    ,\n    \"args\": {\n      ", T_NONE}, \
@@ -816,7 +846,7 @@ enum : int { K_HEAD, K_PID, K_TID, K_TS, K_DUR, K_ARGS, K_EXT, K_EXTC, K_QUEUED,
     {", \"blockLimitBarriers\": ", T_I64, VK_I32, KS_LBARR}, {", \"allocatedRegistersPerBlock\": ", T_I64, VK_I32, KS_AREGS}, \
     {", \"allocatedSharedMemPerBlock\": ", T_U64, VK_64, KS_ASMEM}, {"}, \"graph id\": ", T_U64, VK_U32, KR_GRAPH}, \
     {", \"graph node id\": ", T_U64, VK_64, KR_NODE}, {", \"channel\": ", T_U64, VK_U32, KR_CHAN}, \
-    {", \"channel_type\": ", T_U64, VK_U32, KR_CHTYPE}, {"\n    }\n  },", T_NONE}, \
+    {", \"channel_type\": ", T_U64, VK_U32, KR_CHTYPE}, {"", T_COLL, VK_U32, KS_COLLROW}, {"\n    }\n  },", T_NONE}, \
     {"\n  {\n    \"ph\": \"f\",\n    \"id\": ", T_U64, VK_U32, KR_CORR}, {",\n    \"pid\": ", T_U64, VK_U32, KR_DEV}, \
     {",\n    \"tid\": ", T_U64, VK_U32, KR_STREAM}, {",\n    \"ts\": ", T_TS, VK_64, KS_TS}, \
     {",\n    \"cat\": \"ac2g\",\n    \"name\": \"ac2g\"\n    , \"bp\": \"e\"\n  },", T_NONE}
@@ -902,7 +932,8 @@ enum : int { Y_MROW1, Y_MPID1, Y_MTID1, Y_MNAME, Y_MROW2, Y_MPID2, Y_MTID2, Y_MS
     {",\n    \"cat\": \"ac2g\",\n    \"name\": \"ac2g\"\n    , \"bp\": \"e\"\n  },", T_NONE}
 
 // One table for everything: [api][kernel][mem][op head, metadata marker, op tail][annotation][sync][constant strings].
-enum : int { CS_TYPE = 0, CS_MEMCPY_KIND = 29, CS_MEMORY_KIND = 41, CS_LIMIT = 50, CS_OVERHEAD = 82, CS_SYNC = 93, CS_COUNT = 98 };
+enum : int { CS_TYPE = 0, CS_MEMCPY_KIND = 29, CS_MEMORY_KIND = 41, CS_LIMIT = 50, CS_OVERHEAD = 82, CS_SYNC = 93, CS_COLL = 98,
+             CS_COUNT = 114 };
 #define K2J_CSTR_FIELDS \
     {"cpu_op", 0}, {"user_annotation", 0}, {"gpu_user_annotation", 0}, {"gpu_memcpy", 0}, {"gpu_memset", 0}, {"kernel", 0}, \
     {"external_correlation", 0}, {"cuda_runtime", 0}, {"cuda_driver", 0}, {"cpu_instant_event", 0}, {"python_function", 0}, \
@@ -925,7 +956,11 @@ enum : int { CS_TYPE = 0, CS_MEMCPY_KIND = 29, CS_MEMORY_KIND = 41, CS_LIMIT = 5
     {"Unknown", 0}, {"Driver Compiler", 0}, {"Buffer Flush", 0}, {"Instrumentation", 0}, {"Resource", 0}, \
     {"Runtime Triggered Module Loading", 0}, {"Lazy Function Loading", 0}, {"Command Buffer Full", 0}, \
     {"Activity Buffer Request", 0}, {"Force Int", 0}, {"Unrecognized", 0}, \
-    {"Unknown Sync", 0}, {"Event Sync", 0}, {"Stream Wait Event", 0}, {"Stream Sync", 0}, {"Context Sync", 0}
+    {"Unknown Sync", 0}, {"Event Sync", 0}, {"Stream Wait Event", 0}, {"Stream Sync", 0}, {"Context Sync", 0}, \
+    {",\"Collective name\": ", 0}, {",\"In msg nelems\": ", 0}, {",\"Out msg nelems\": ", 0}, {",\"Group size\": ", 0}, \
+    {",\"dtype\": ", 0}, {",\"Input Tensors start\": ", 0}, {",\"Output Tensors start\": ", 0}, {",\"In split size\": ", 0}, \
+    {",\"Out split size\": ", 0}, {",\"Process Group Name\": ", 0}, {",\"Process Group Description\": ", 0}, \
+    {",\"Process Group Ranks\": ", 0}, {",\"Dst Rank\": ", 0}, {",\"Src Rank\": ", 0}, {",\"Seq\": ", 0}, {",\"Comms Id\": ", 0}
 
 
 constexpr int API_BASE = 0, KERNEL_BASE = API_BASE + A_COUNT, MEM_BASE = KERNEL_BASE + K_COUNT, OP_BASE = MEM_BASE + M_COUNT,
@@ -1342,8 +1377,13 @@ __device__ __forceinline__ uint64_t gather_kernel(const Dev& d, uint32_t* a, Tal
   s64(a, KS_BPS, (uint64_t)__double_as_longlong((double)bps)); s64(a, KS_WPS, (uint64_t)__double_as_longlong((double)wps));
   s64(a, KS_TS, (uint64_t)rel_ts(d, ts)); s64(a, KS_DUR, (uint64_t)(dur < 0 ? 0 : dur));
   s32(a, KS_REGS, regs); s32(a, KS_SMEM, (uint32_t)ssm + (uint32_t)dsm); s32(a, KS_EXT, (uint32_t)ext);
-  uint64_t p = (1ull << K_COUNT) - 1ull;  // every field except the optional ones below
+  uint64_t p = ((1ull << K_COUNT) - 1ull) & ~(1ull << K_COLL);  // every field except the optional ones below
   if (!has_ext) p &= ~((1ull << K_EXT) | (1ull << K_EXTC));
+  else if (d.has_comms != nullptr && *d.has_comms != 0u) {
+    // a kernel launched by a record_param_comms op carries that op's collective metadata (output_json.cpp:900-906)
+    const uint32_t row = tab_find(d.op_tab, d.op_mask, (uint32_t)ext);
+    if (row < d.n_ops && d.op_name[row] < d.n_strings && d.str_class[d.op_name[row]] == 1u) { p |= 1ull << K_COLL; s32(a, KS_COLLROW, row); }
+  }
   t.x++;
   if (corr > 0) t.flow++;
   else p &= ~((1ull << K_FLOW) | (1ull << K_FPID) | (1ull << K_FTID) | (1ull << K_FTS) | (1ull << K_FEND));
@@ -1543,23 +1583,83 @@ __device__ __forceinline__ uint64_t gather_op(const Dev& d, uint64_t i, uint32_t
   return p;
 }
 
+// ChromeTraceLogger::appendCollectiveArgs (libkineto/src/output_json.cpp:718-801) for the CPU op in row `row`: the
+// op's metadata values rendered as metadataValueToString does (libkineto/src/GenericTraceActivity.cpp:20-47), string
+// values with one surrounding pair of quotes stripped where the reference strips it, nothing sanitised.  Every
+// entry is written as ,"key": value (ArgsBuilder::addRaw / addQuoted, :161-170).
+constexpr uint32_t kCollStrip = 0x0FF1u;   // keys whose string value loses one surrounding pair of quotes (and is quoted again)
+// The op's entry for key k, or 0xFFFFFFFF.
+__device__ __forceinline__ uint32_t coll_entry(const Dev& d, uint32_t row, uint32_t k) {
+  uint32_t found = 0xFFFFFFFFu;
+  for (uint32_t e = d.op_mdoff[row], m1 = d.op_mdoff[row + 1]; e < m1; e++) {
+    const uint32_t key = d.md[e].key;
+    if (key < d.n_strings && d.str_class[key] == 2u + k) found = e;
+  }
+  return found;
+}
+// [begin, end) of a string value in the pool, one surrounding pair of quotes stripped on request.
+__device__ __forceinline__ void coll_text(const Dev& d, uint32_t id, bool strip, uint64_t* b, uint64_t* e) {
+  uint64_t lo = 0, hi = 0;
+  if (id < d.n_strings) { lo = d.pool_off[id]; hi = d.pool_off[id + 1]; }
+  if (strip && hi - lo >= 2 && d.pool_data[lo] == '"' && d.pool_data[hi - 1] == '"') { lo++; hi--; }
+  *b = lo; *e = hi;
+}
+// Bit k set: key k is written.  Numbers and booleans are never empty; a string is empty when nothing is left of it.
+// The first five keys are written together or not at all, and so are the two split sizes.
+__device__ __forceinline__ uint32_t coll_mask(const Dev& d, uint32_t row) {
+  uint32_t mask = 0;
+  for (uint32_t e = d.op_mdoff[row], m1 = d.op_mdoff[row + 1]; e < m1; e++) {
+    const MdEntry md = d.md[e];
+    const uint32_t cls = md.key < d.n_strings ? d.str_class[md.key] : 0u;
+    if (cls < 2u) continue;
+    const uint32_t k = cls - 2u;
+    bool nonempty = true;
+    if (md.type >= 4u) { uint64_t b, e2; coll_text(d, (uint32_t)md.value, (kCollStrip >> k) & 1u, &b, &e2); nonempty = e2 > b; }
+    mask = nonempty ? (mask | (1u << k)) : (mask & ~(1u << k));
+  }
+  if ((mask & 0x1Fu) != 0x1Fu) mask &= ~0x1Fu;
+  if ((mask & 0x180u) != 0x180u) mask &= ~0x180u;
+  return mask;
+}
+
 // The value that follows a field's literal.  T_MD (CPU-side activities only) formats the typed metadata
 // entries of the op (JsonTypedMetadataVisitor, libkineto/include/TypedMetadataJson.h:72-158): each entry
 // is mapped onto one of the value types, so the kernel holds one copy of every formatter.
-enum : int { T_BOOL = 8, T_MDSTR, T_QMDSTR };
-template <class S>
+enum : int { T_BOOL = 8, T_MDSTR, T_QMDSTR, T_RAWSTR = 12 /* pool bytes as they are */, T_RAWSTRIP /* ... minus one pair of quotes */ };
+template <class S, bool COLL = true>
 __device__ __forceinline__ void put_value(S& s, const Dev& d, int type, uint64_t v, unsigned long long* name_bytes) {
   if (type == T_NONE) return;
-  uint32_t e = 0, m1 = 0, m0 = 0;
-  const bool md_mode = type == T_MD;
-  if (md_mode) { m0 = e = d.op_mdoff[v]; m1 = d.op_mdoff[v + 1]; if (e >= m1) return; }
+  // Two field types loop over the entries of a CPU-side activity: its own metadata (T_MD) and the collective keys
+  // copied onto a kernel (T_COLL).  Every other type takes the switch once.
+  uint32_t e = 0, m1 = 0, m0 = 0, cmask = 0;
+  const bool coll = COLL && type == T_COLL;
+  const bool md_mode = type == T_MD || coll;
+  if (md_mode) {
+    if (!coll) { m0 = e = d.op_mdoff[v]; m1 = d.op_mdoff[v + 1]; if (e >= m1) return; }
+    else { m0 = (uint32_t)v; cmask = coll_mask(d, m0); if (!cmask) return; }
+  }
+  bool more = false, close_quote = false;
   do {
     if (md_mode) {
-      const MdEntry md = d.md[e];
-      if (e > m0) s.put(0x202Cu, 2);  // ", "
-      put_char(s, '"'); put_mdstr(s, d, md.key); s.put(0x203A22u, 3);  // "\": "
-      v = md.value;
-      type = md.type == 0 ? T_I64 : md.type == 1 ? T_U64 : md.type == 2 ? T_DBL : md.type == 3 ? T_BOOL : md.type == 4 ? T_QMDSTR : T_MDSTR;
+      if (!coll) {
+        const MdEntry md = d.md[e];
+        if (e > m0) s.put(0x202Cu, 2);  // ", "
+        put_char(s, '"'); put_mdstr(s, d, md.key); s.put(0x203A22u, 3);  // "\": "
+        v = md.value;
+        type = md.type == 0 ? T_I64 : md.type == 1 ? T_U64 : md.type == 2 ? T_DBL : md.type == 3 ? T_BOOL : md.type == 4 ? T_QMDSTR : T_MDSTR;
+        more = ++e < m1;
+      } else {  // the next collective key: its literal, then the op's value through the formatters below
+        const uint32_t k = (uint32_t)__ffs((int)cmask) - 1u;
+        cmask &= cmask - 1u;
+        const MdEntry md = d.md[coll_entry(d, m0, k)];
+        const FieldDesc cs = g_fields.f[CSTR_BASE + CS_COLL + k];
+        s.words(g_fields.w + cs.off, cs.len);
+        close_quote = (kCollStrip >> k) & 1u;
+        if (close_quote) put_char(s, '"');
+        v = md.value;
+        type = md.type == 0 ? T_I64 : md.type == 1 ? T_U64 : md.type == 2 ? T_DBL : md.type == 3 ? T_BOOL : close_quote ? T_RAWSTRIP : T_RAWSTR;
+        more = cmask != 0u;
+      }
     }
     switch (type) {
       case T_U64: case T_I64: case T_TS: {
@@ -1581,19 +1681,24 @@ __device__ __forceinline__ void put_value(S& s, const Dev& d, int type, uint64_t
       case T_NAME: put_name(s, d, (uint32_t)v, name_bytes); break;
       case T_CSTR: { const FieldDesc cs = g_fields.f[CSTR_BASE + (uint32_t)v]; s.words(g_fields.w + cs.off, cs.len); break; }
       case T_BOOL: if (v) s.put4(0x65757274u); else s.put64(0x65736C6166ull, 5); break;  // true / false
-      default: {  // T_MDSTR, T_QMDSTR
+      default: {  // T_MDSTR, T_QMDSTR, T_RAWSTR, T_RAWSTRIP
         if (type == T_QMDSTR) put_char(s, '"');
-        put_mdstr(s, d, (uint32_t)v);
-        if (type == T_QMDSTR) put_char(s, '"');
+        if (COLL && type >= T_RAWSTR) {
+          uint64_t b, e2;
+          coll_text(d, (uint32_t)v, type == T_RAWSTRIP, &b, &e2);
+          for (uint64_t i = b; i < e2; i++) put_char(s, (char)d.pool_data[i]);
+        } else put_mdstr(s, d, (uint32_t)v);
+        if (type == T_QMDSTR || close_quote) put_char(s, '"');
         break;
       }
     }
-  } while (md_mode && ++e < m1);
+    if (md_mode && close_quote && type < T_RAWSTR) put_char(s, '"');  // a quoted number (strings close their own quote)
+  } while (md_mode && more);
 }
 
 // Emit pass: walks the set bits of `present`.  Descriptor and value of the NEXT field are fetched before
 // the current one is formatted, so their latency hides behind the formatting work.
-template <class S>
+template <class S, bool COLL = true>
 __device__ __forceinline__ void run_fields(S& s, const Dev& d, const uint32_t* a, int base, uint64_t present,
                                            unsigned long long* name_bytes) {
   if (!present) return;
@@ -1612,7 +1717,7 @@ __device__ __forceinline__ void run_fields(S& s, const Dev& d, const uint32_t* a
       vn = slot_value(a, fdn.voff, fdn.vk);
     }
     s.words(g_fields.w + fd.off, fd.len);
-    put_value(s, d, fd.type, v, name_bytes);
+    put_value<S, COLL>(s, d, fd.type, v, name_bytes);
     if (!more) break;
     fd = fdn; v = vn;
   }
@@ -1639,8 +1744,11 @@ __device__ __forceinline__ void count_fields(S& s, const Dev& d, const uint32_t*
 }
 constexpr int kEventThreads = 128;
 
-template <class S>
-__device__ __forceinline__ void format_event(S& s, const Dev& d, int cls, uint32_t* a, uint64_t j, Tally& t, uint32_t* filt, int32_t* ext) {
+// COLL (emit pass only): this launch writes the kernel events that carry collective metadata, and only those; the
+// launch without it writes everything else and holds no code for them.  Returns false when the event is left to
+// the other launch.
+template <class S, bool COLL = true>
+__device__ __forceinline__ bool format_event(S& s, const Dev& d, int cls, uint32_t* a, uint64_t j, Tally& t, uint32_t* filt, int32_t* ext) {
   unsigned long long* nb = &t.name_bytes;
   if constexpr (S::kCounting) {
     uint64_t p;
@@ -1671,8 +1779,10 @@ __device__ __forceinline__ void format_event(S& s, const Dev& d, int cls, uint32
       case C_CUDAEVENT: p = gather_sync<C_CUDAEVENT>(d, a, t, filt, false, ext); base = SYNC_BASE; break;
       default: p = gather_op(d, j, a, t); base = OP_BASE; break;
     }
-    run_fields(s, d, a, base, p, nb);
+    if ((((p >> K_COLL) & 1ull) != 0 && cls == C_KERNEL) != COLL) return false;
+    run_fields<S, COLL>(s, d, a, base, p, nb);
   }
+  return true;
 }
 
 // 8-byte units staged of a record of each class (C_API .. C_OVERHEAD): whole records, except the kernel record's unread tail
@@ -1686,7 +1796,7 @@ __device__ __forceinline__ uint32_t class_units(int cls) {
 // the bytes at ev_off[event].  Either pass first copies the 32 records of a warp into shared memory
 // with coalesced loads (lane = 8-byte unit of a record); all later reads of record fields and of the
 // values computed from them are shared-memory reads at table-given offsets.
-template <bool WRITE>
+template <bool WRITE, bool COLL = false>
 __global__ void __launch_bounds__(kEventThreads, 8) k_events(Dev d) {
   __shared__ uint64_t s_rec[kEventThreads * kRecStride];
   __shared__ uint64_t s_park[WRITE ? 3 * kEventThreads : 1];
@@ -1763,8 +1873,8 @@ __global__ void __launch_bounds__(kEventThreads, 8) k_events(Dev d) {
     } else {
       GlobalSink s;
       s.init(d.out + off, size, &s_park[threadIdx.x]);
-      format_event(s, d, cls, area, j, t, &filt, &ext);
-      if (!s.finish(d.out + off, size)) atomicAdd(&d.counters->device_check, 1ull);
+      if (format_event<GlobalSink, COLL>(s, d, cls, area, j, t, &filt, &ext) && !s.finish(d.out + off, size))
+        atomicAdd(&d.counters->device_check, 1ull);
     }
   }
   if (!WRITE) {  // counters are tallied once, in the size pass: warp sums, then one shared atomic per warp

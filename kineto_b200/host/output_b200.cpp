@@ -131,6 +131,7 @@ struct B200TraceLogger::Impl {
     // device-side lookups give the same answer.
     std::vector<uint8_t> prefix;
     std::unordered_map<uint32_t, bool> ctxDeclared;
+    std::unordered_set<int32_t> opIds;  // ids of the CPU-side activities of this run
     bool hasCupti = false;
   };
   Run run;
@@ -170,9 +171,37 @@ struct B200TraceLogger::Impl {
     e.externalId = (uint64_t)a.linkedActivity()->correlationId();
     e.correlationId = (uint32_t)a.correlationId();
     appendRecord(e);
-    linkedIds.push_back((int32_t)a.linkedActivity()->correlationId());
+    // an op logged in an earlier run is made joinable again (see flushRun); one of this run keeps its own row, so
+    // that its name and metadata stay reachable from the records linked to it
+    if (!run.opIds.count((int32_t)a.linkedActivity()->correlationId()))
+      linkedIds.push_back((int32_t)a.linkedActivity()->correlationId());
   }
   std::vector<int32_t> linkedIds;
+  // What ChromeTraceLogger::appendCollectiveMetadata (libkineto/src/output_json.cpp:803-835) keeps for the trailer:
+  // the job's rank and size from the first collective of the default process group, and every process group seen.
+  // Host work per collective kernel; the kernel event's own collective arguments are written by the GPU path.
+  DistributedInfo distInfo;
+  std::unordered_map<std::string, pgConfig> pgMap;
+  static std::string stripQuotes(std::string v) {
+    if (v.size() >= 2 && v.front() == '"' && v.back() == '"') { v.pop_back(); v.erase(0, 1); }
+    return v;
+  }
+  void noteCollective(const libkineto::ITraceActivity& op) {
+    const std::string groupSize = op.getMetadataValue("Group size");
+    std::string pgName = stripQuotes(op.getMetadataValue("Process Group Name"));
+    std::string pgDesc = stripQuotes(op.getMetadataValue("Process Group Description"));
+    std::string ranks = stripQuotes(op.getMetadataValue("Process Group Ranks"));
+    if (distInfo.backend.empty() && pgDesc == "default_pg") {
+      distInfo.backend = "nccl";
+      distInfo.rank = op.getMetadataValue("Rank");
+      distInfo.world_size = groupSize;
+      distInfo.nccl_version = "unknown";
+    }
+    pgConfig cfg;
+    cfg.pg_name = pgName; cfg.pg_desc = std::move(pgDesc); cfg.backend_config = "cuda:nccl"; cfg.pg_size = groupSize;
+    cfg.ranks = std::move(ranks);
+    pgMap.insert({pgName, cfg});
+  }
 
   bool flushRun();
 };
@@ -335,6 +364,7 @@ void B200TraceLogger::handleGenericActivity(const libkineto::GenericTraceActivit
   if (m.run.hasCupti) m.flushRun();  // a run is CPU-side activities followed by CUPTI records
   auto& r = m.run;
   r.start.push_back(op.startTime); r.end.push_back(op.endTime); r.id.push_back(op.id); r.dev.push_back(op.device);
+  r.opIds.insert(op.id);
   r.resource.push_back(op.resource); r.thread.push_back(op.threadId); r.type.push_back((int32_t)op.activityType);
   r.name.push_back(m.intern(op.activityName)); r.flow.push_back(op.flow.id);
   r.flowt.push_back((uint8_t)(op.flow.type | (op.flow.start << 4)));
@@ -363,6 +393,7 @@ void B200TraceLogger::handleActivity(const libkineto::ITraceActivity& a) {
   };
   if (auto* k = dynamic_cast<const GpuActivity<CUpti_ActivityKernelType>*>(&a)) {
     m.addLink(a);
+    if (a.linkedActivity() && a.linkedActivity()->name() == "record_param_comms") m.noteCollective(*a.linkedActivity());
     CUpti_ActivityKernelType rec = k->raw();
     convert(rec);
     auto it = m.kernelNameIds.find(rec.name);
@@ -459,6 +490,19 @@ void B200TraceLogger::finalizeTrace(const Config&, std::unique_ptr<ActivityBuffe
   sanitize(fileName);
   std::string s = instantRow("Record Window End", "\"\"", "\"\"", rel(endTime), true);
   s += "\n  ],";
+  if (!impl_->distInfo.backend.empty()) {  // addOnDemandDistMetadata, output_json.cpp:1030-1064
+    const DistributedInfo& di = impl_->distInfo;
+    s += fmt::format("\n  \"distributedInfo\": {{\"backend\": \"{}\", \"rank\": {}, \"world_size\": {}, \"pg_count\": {}, \"pg_config\": [",
+                     di.backend, di.rank, di.world_size, std::to_string(impl_->pgMap.size()));
+    bool first = true;
+    for (const auto& el : impl_->pgMap) {
+      if (!first) s += ",";
+      s += fmt::format("{{\"pg_name\": \"{}\", \"pg_desc\": \"{}\", \"backend_config\": \"{}\", \"pg_size\": {}, \"ranks\": \"{}\"}}",
+                       el.second.pg_name, el.second.pg_desc, el.second.backend_config, el.second.pg_size, el.second.ranks);
+      first = false;
+    }
+    s += fmt::format("], \"nccl_version\": \"{}\"}},", di.nccl_version);
+  }
   s += fmt::format("\"traceName\": \"{}\" }}", fileName);
   impl_->text(s);
   fclose(impl_->out);

@@ -305,6 +305,8 @@ def collective_trace(n=40, seed=51) -> tf.Trace:
             md = [m for m in md if m[0] != "dtype"] + [("dtype", S, '""')]   # a quoted empty string counts as absent
         if i % 13 == 6:
             md += [("Dst Rank", D, 2.5), ("Src Rank", B, 1)] if i % 7 != 2 else []
+        while len({m[0] for m in md}) > 13:   # one bucket generation of the reference's metadata map
+            md.pop()
         b.op(t0 + 1000 * i, t0 + 1000 * i + 800, 100 + i, "record_param_comms", md=md)
         b.extcorr(500 + i, 100 + i)
         b.runtime(t0 + 1000 * i + 10, t0 + 1000 * i + 20, 500 + i)

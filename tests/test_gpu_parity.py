@@ -68,9 +68,11 @@ def test_gpu_matches_reference_golden(name):
     lambda: cases.with_flags(cases.sync_trace(), tf.FLAG_SORT_BY_START),
     lambda: cases.with_flags(cases.sync_mix_trace(30_000, seed=47), tf.FLAG_SORT_BY_START),
     lambda: synth.gen_op_tree(60_000, seed=210, pool_size=500, n_shapes=256),
+    lambda: cases.collective_trace(3000, seed=53),
+    lambda: cases.with_flags(cases.collective_trace(500, seed=54), tf.FLAG_SORT_BY_START),
 ], ids=["generic", "launches", "shard", "mixed", "mixed_small_buffers", "tsc", "edge", "edge_annot", "annotations",
         "overhead_mix", "sorted_overhead_mix", "launches_annot", "sorted_launches", "sorted_mixed", "sorted_annot", "sorted_tsc", "sorted_small",
-        "sync", "sync_mix", "sync_mix_annot", "sorted_sync", "sorted_sync_mix", "op_tree"])
+        "sync", "sync_mix", "sync_mix_annot", "sorted_sync", "sorted_sync_mix", "op_tree", "collectives", "sorted_collectives"])
 def test_gpu_matches_port(gen):
     trace = gen()
     want, stats = helpers.run_port(trace)

@@ -24,7 +24,8 @@ SHIM = os.path.join(helpers.ROOT, "oracle", "_ref", "shim_driver")
     lambda: cases.tsc_trace(1500),
     cases.sync_trace,
     lambda: cases.sync_mix_trace(6000, seed=48),
-], ids=["launches_annot", "mixed", "edge", "annotations", "tsc", "sync", "sync_mix"])
+    lambda: cases.collective_trace(300, seed=55),
+], ids=["launches_annot", "mixed", "edge", "annotations", "tsc", "sync", "sync_mix", "collectives"])
 def test_logger_shim_writes_the_reference_file(gen, tmp_path):
     trace = gen()
     p = str(tmp_path / "t.k2jt")

@@ -48,8 +48,10 @@ def test_golden_container_is_reproducible(name):
     cases.sync_mix_trace,
     lambda: cases.sync_mix_trace(5000, seed=44, flags=1),
     lambda: synth.gen_op_tree(3000, seed=106, pool_size=100, n_shapes=64),
+    cases.collective_trace,
+    lambda: cases.collective_trace(400, seed=52),
 ], ids=["generic", "launches", "shard", "mixed", "tsc", "edge", "edge_annot", "annotations", "overhead_mix", "launches_annot",
-        "sync", "sync_mix", "sync_mix_annot", "op_tree"])
+        "sync", "sync_mix", "sync_mix_annot", "op_tree", "collectives", "collectives_400"])
 def test_port_matches_live_reference(gen):
     trace = gen()
     doc, _ = helpers.run_ref(trace)
