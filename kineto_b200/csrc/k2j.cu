@@ -658,10 +658,10 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
   // collective enrichment: kernels look at their linked op's name only if some op is a record_param_comms call;
   // ops of other shards carry no metadata here, so sharded runs do not enrich
   d.has_comms = nullptr;
-  if (!c->have_global_join && c->n_ops && c->n_strings) {
+  if (c->n_ops && c->n_strings) {
     K2J_CUDA(c, c->comms_flag.reserve(16));
     K2J_CUDA(c, cudaMemsetAsync(c->comms_flag.p, 0, 4, s));
-    k_find_comms<<<(uint32_t)((c->n_ops + 255) / 256), 256, 0, s>>>(d, c->comms_flag.as<uint32_t>());
+    k_find_comms<<<(uint32_t)((c->n_ops + 255) / 256), 256, 0, s>>>(d, c->comms_flag.as<uint32_t>(), c->have_global_join ? 0 : 1);
     c->launches++;
     d.has_comms = c->comms_flag.as<uint32_t>();
   }
@@ -745,7 +745,14 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
     d.out = c->out.as<uint8_t>(); d.out_cap = total_bytes + ann_bytes;
     K2J_CUDA(c, cudaEventRecord(c->ev[7], s));
     if (total_bytes) { k_events<true><<<ev_blocks, kEventThreads, 0, s>>>(d); c->launches++; }
-    if (total_bytes && c->h_totals[25] != 0 && totals[C_KERNEL]) {
+    if (total_bytes && (c->h_totals[25] & 2) && c->n_ops) {
+      // instant events: the same extra launch over the CPU-side activities
+      Dev di = d;
+      di.work_origin = d.ops_begin;
+      k_events<true, true><<<(uint32_t)((di.n_work - di.work_origin + kEventThreads - 1) / kEventThreads), kEventThreads, 0, s>>>(di);
+      c->launches++;
+    }
+    if (total_bytes && (c->h_totals[25] & 1) && totals[C_KERNEL]) {
       // kernel events that carry collective metadata: a launch of their own over the kernel records, so that the
       // launch above holds no code for them
       Dev dk = d;

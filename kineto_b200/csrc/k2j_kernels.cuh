@@ -472,6 +472,7 @@ __global__ void __launch_bounds__(kSegWarps * 32) k_seg_write(Dev d) {
   __shared__ __align__(4) uint8_t s_code[kSegWarps][kChunkSlots + 4];
   __shared__ uint16_t s_pos[kSegWarps][kChunkSlots / 3 + 2];
   __shared__ uint32_t s_n[kSegWarps];
+  __shared__ uint64_t s_base[kSegWarps][C_NCLASS];
   const uint32_t w = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t chunk = blockIdx.x * kSegWarps + w;
   if (chunk >= d.n_chunks) return;
@@ -491,9 +492,9 @@ __global__ void __launch_bounds__(kSegWarps * 32) k_seg_write(Dev d) {
   }
   __syncwarp();
   const uint32_t n = s_n[w];
-  uint64_t base[C_NCLASS];
-#pragma unroll
-  for (int c = 0; c < C_NCLASS; c++) base[c] = d.chunk_base[(uint64_t)c * d.n_chunks + chunk] + (c == C_EXT ? 0 : d.cls_begin[c]);
+  // next free position of every class (work list, or the compacted EXTERNAL_CORRELATION array)
+  if (lane < (uint32_t)C_NCLASS) s_base[w][lane] = d.chunk_base[(uint64_t)lane * d.n_chunks + chunk] + (lane == (uint32_t)C_EXT ? 0 : d.cls_begin[lane]);
+  __syncwarp();
   uint64_t ev_base = d.n_ops + d.chunk_base[(uint64_t)C_EVENTS * d.n_chunks + chunk];
   const uint32_t lt = (1u << lane) - 1u;
   for (uint32_t i0 = 0; i0 < n; i0 += 32) {
@@ -502,13 +503,12 @@ __global__ void __launch_bounds__(kSegWarps * 32) k_seg_write(Dev d) {
     const uint32_t pos = on ? s_pos[w][i] : 0u;
     const uint32_t cls = on ? code_class(codes[pos]) : 0xffu;
     const uint32_t evm = __ballot_sync(0xffffffffu, on && cls < (uint32_t)C_WAIT);
-    uint64_t dst = 0;
-#pragma unroll
-    for (int c = 0; c < C_NCLASS; c++) {
-      const uint32_t m = __ballot_sync(0xffffffffu, cls == (uint32_t)c);
-      if (cls == (uint32_t)c) dst = base[c] + __popc(m & lt);
-      base[c] += __popc(m);
-    }
+    // rank within the class: the lanes holding records of one class find each other in one step
+    const uint32_t peers = __match_any_sync(0xffffffffu, cls);
+    const uint64_t dst = on ? s_base[w][cls] + __popc(peers & lt) : 0;
+    __syncwarp();
+    if (on && (peers & lt) == 0u) s_base[w][cls] += __popc(peers);
+    __syncwarp();
     if (on) {
       const uint64_t slot = g.slot0 + pos;
       if (cls == (uint32_t)C_EXT) {
@@ -565,13 +565,14 @@ __global__ void k_mark_corr(Dev d) {
   const int off = cls == C_API ? 32 : cls == C_KERNEL ? 92 : cls == C_MEMCPY2 ? 60 : cls == C_CUDAEVENT ? 4 : (cls == C_SYNC || cls == C_WAIT) ? 24 : 44;
   bit_set(d.need_corr, d.need_corr_mask, *reinterpret_cast<const uint32_t*>(r + off));
 }
-// Is any CPU-side activity of this run named record_param_comms?  Kernel events look at their linked op's name
-// only if so.
-__global__ void k_find_comms(Dev d, uint32_t* flag) {
+// Is any CPU-side activity of this run named record_param_comms (bit 0: kernel events look at their linked op's
+// name only if so), is any an instant event (bit 1)?
+__global__ void k_find_comms(Dev d, uint32_t* flag, int comms_on) {
   const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= d.n_ops) return;
   const uint32_t name = d.op_name[i];
-  if (name < d.n_strings && d.str_class[name] == 1u) *flag = 1u;
+  if (comms_on && name < d.n_strings && d.str_class[name] == 1u) atomicOr(flag, 1u);
+  if (d.op_type[i] == 9) atomicOr(flag, 2u);  // an instant event: written by the same extra launch
 }
 // CPU-op id -> position (last writer wins): activityMap_[id] = op, GenericActivityProfiler.cpp:262.
 __global__ void k_build_ops(Dev d) {
@@ -776,7 +777,9 @@ struct CountSink2 : CountSink {
 // are computed rather than stored (converted times, the linked op, occupancy ...) written by the
 // class's gather step into parts of the record that no field reads.
 enum : uint8_t { T_NONE = 0, T_U64, T_I64, T_TS, T_DBL, T_NAME, T_CSTR, T_MD /* the metadata entries of a CPU-side activity */,
-                 T_COLL = 11 /* collective metadata copied from the linked record_param_comms op */ };
+                 T_COLL = 11 /* collective metadata copied from the linked record_param_comms op */,
+                 T_RAWSTR = 12 /* a pool string as it is */, T_RAWSTRIP /* ... minus one surrounding pair of quotes */,
+                 T_MDRAW /* metadata entries with keys and strings as they are */ };
 enum : uint8_t { VK_U32 = 0, VK_I32 /* sign-extended */, VK_64 };
 struct FieldSrc { const char* lit; uint8_t type; uint8_t vk; uint16_t voff; };
 struct FieldDesc { uint16_t off, len; uint8_t type, vk; uint16_t voff; };
@@ -879,11 +882,15 @@ enum : int { M_CPY_KIND, M_CPY_SRC, M_CPY_DST, M_SET_KIND, M_PID, M_TID, M_TS, M
 
 // -- CPU-side activity (no record: every value is a slot): head, metadata entries, tail --
 enum : int { OS_CAT = 0, OS_NAME = 4, OS_PID = 8, OS_EXT = 12, OS_TID = 16, OS_TS = 24, OS_DUR = 32, OS_ROW = 40, OS_FLOW = 44, OS_FTS = 48 };
-enum : int { O_CAT, O_NAME, O_CNAME /* a constant-string name instead of a pool name */, O_PID, O_TID, O_TS, O_DUR, O_PAD, O_ARGS, O_EXT, O_EXTC, O_MD,
+enum : int { O_CAT, O_NAME, O_CNAME /* a constant-string name instead of a pool name */,
+             I_HEAD, I_NAME /* an instant event: libkineto/src/output_json.cpp:261-293, :660-676 */, O_PID, O_TID, O_TS, O_DUR, O_PAD, O_ARGS,
+             O_EXT, O_EXTC, O_MD, I_MD /* the same entries, nothing sanitised */,
              P_ARGS_CLOSE, P_CLOSE, P_FLOW_S, P_FLOW_F, P_FPID, P_FTID, P_FTS, P_FWDBWD, P_AC2G, P_FBP, P_FEND, O_COUNT };
 #define K2J_OPHEAD_FIELDS \
     {"\n  {\n    \"ph\": \"X\",\n    \"cat\": \"", T_CSTR, VK_U32, OS_CAT}, {"\",\n    \"name\": \"", T_NAME, VK_U32, OS_NAME}, \
-    {"\",\n    \"name\": \"", T_CSTR, VK_U32, OS_NAME}, {"\",\n    \"pid\": ", T_I64, VK_I32, OS_PID}, \
+    {"\",\n    \"name\": \"", T_CSTR, VK_U32, OS_NAME}, \
+    {"\n  {\n    \"ph\": \"i\",\n    \n    \"cat\": \"", T_CSTR, VK_U32, OS_CAT}, {"\",\n    \"s\": \"t\",\n    \"name\": \"", T_RAWSTR, VK_U32, OS_NAME}, \
+    {"\",\n    \"pid\": ", T_I64, VK_I32, OS_PID}, \
     {",\n    \"tid\": ", T_I64, VK_64, OS_TID}, {",\n    \"ts\": ", T_TS, VK_64, OS_TS}, {",\n    \"dur\": ", T_TS, VK_64, OS_DUR}, {"\n    ", T_NONE}, \
     {",\n    \"args\": {\n      ", T_NONE}, {"\"External id\": ", T_I64, VK_I32, OS_EXT}, {",", T_NONE}
 #define K2J_OPTAIL_FIELDS \
@@ -967,6 +974,7 @@ constexpr int API_BASE = 0, KERNEL_BASE = API_BASE + A_COUNT, MEM_BASE = KERNEL_
               ANN_BASE = OP_BASE + O_COUNT, SYNC_BASE = ANN_BASE + N_COUNT, CSTR_BASE = SYNC_BASE + Y_COUNT,
               FIELD_COUNT = CSTR_BASE + CS_COUNT;
 constexpr FieldSrc kAllFields[] = {K2J_API_FIELDS, K2J_KERNEL_FIELDS, K2J_MEM_FIELDS, K2J_OPHEAD_FIELDS, {"", T_MD, VK_U32, OS_ROW},
+                                   {"", T_MDRAW, VK_U32, OS_ROW},
                                    K2J_OPTAIL_FIELDS, K2J_ANN_FIELDS, K2J_SYNC_FIELDS, K2J_CSTR_FIELDS};
 static_assert(sizeof(kAllFields) / sizeof(kAllFields[0]) == FIELD_COUNT, "field table and enums disagree");
 constexpr int kAllWords = prog_words(kAllFields);
@@ -1379,7 +1387,7 @@ __device__ __forceinline__ uint64_t gather_kernel(const Dev& d, uint32_t* a, Tal
   s32(a, KS_REGS, regs); s32(a, KS_SMEM, (uint32_t)ssm + (uint32_t)dsm); s32(a, KS_EXT, (uint32_t)ext);
   uint64_t p = ((1ull << K_COUNT) - 1ull) & ~(1ull << K_COLL);  // every field except the optional ones below
   if (!has_ext) p &= ~((1ull << K_EXT) | (1ull << K_EXTC));
-  else if (d.has_comms != nullptr && *d.has_comms != 0u) {
+  else if (d.has_comms != nullptr && (*d.has_comms & 1u) != 0u) {
     // a kernel launched by a record_param_comms op carries that op's collective metadata (output_json.cpp:900-906)
     const uint32_t row = tab_find(d.op_tab, d.op_mask, (uint32_t)ext);
     if (row < d.n_ops && d.op_name[row] < d.n_strings && d.str_class[d.op_name[row]] == 1u) { p |= 1ull << K_COLL; s32(a, KS_COLLROW, row); }
@@ -1543,9 +1551,17 @@ __device__ __forceinline__ uint64_t gather_op(const Dev& d, uint64_t i, uint32_t
   const int32_t type = d.op_type[i];
   if ((uint32_t)type >= 29u) { atomicAdd(&d.counters->device_check, 1ull); return 0; }
   if (!((d.type_mask >> type) & 1u)) return 0;  // type not selected: joins, but is not logged
-  if (type == 9 || type == 17 || type == 26 || type == 28) {  // instant / counter events: not implemented
+  if (type == 17 || type == 26 || type == 28) {  // counter events (other profilers' activity types): not implemented
     atomicAdd(&d.counters->device_check, 1ull);
     return 0;
+  }
+  if (type == 9) {  // CPU_INSTANT_EVENT: handleGenericInstantEvent, output_json.cpp:660-676 (no duration, no flow, raw text)
+    s32(a, OS_CAT, (uint32_t)(CS_TYPE + type)); s32(a, OS_NAME, d.op_name[i]); s32(a, OS_PID, (uint32_t)op_pid(d, d.op_device[i]));
+    s64(a, OS_TID, (uint64_t)abs_tid(d.op_resource[i])); s64(a, OS_TS, (uint64_t)rel_ts(d, d.op_start[i])); s32(a, OS_ROW, (uint32_t)i);
+    uint64_t pi = (1ull << I_HEAD) | (1ull << I_NAME) | (1ull << O_PID) | (1ull << O_TID) | (1ull << O_TS) | (1ull << O_PAD) | (1ull << P_CLOSE);
+    if (d.op_mdoff[i + 1] > d.op_mdoff[i]) pi |= (1ull << O_ARGS) | (1ull << I_MD) | (1ull << P_ARGS_CLOSE);
+    t.x++;
+    return pi;
   }
   int64_t ts = d.op_start[i];
   int64_t dur = d.op_end[i] - ts;
@@ -1625,15 +1641,15 @@ __device__ __forceinline__ uint32_t coll_mask(const Dev& d, uint32_t row) {
 // The value that follows a field's literal.  T_MD (CPU-side activities only) formats the typed metadata
 // entries of the op (JsonTypedMetadataVisitor, libkineto/include/TypedMetadataJson.h:72-158): each entry
 // is mapped onto one of the value types, so the kernel holds one copy of every formatter.
-enum : int { T_BOOL = 8, T_MDSTR, T_QMDSTR, T_RAWSTR = 12 /* pool bytes as they are */, T_RAWSTRIP /* ... minus one pair of quotes */ };
+enum : int { T_BOOL = 8, T_MDSTR, T_QMDSTR };
 template <class S, bool COLL = true>
 __device__ __forceinline__ void put_value(S& s, const Dev& d, int type, uint64_t v, unsigned long long* name_bytes) {
   if (type == T_NONE) return;
   // Two field types loop over the entries of a CPU-side activity: its own metadata (T_MD) and the collective keys
   // copied onto a kernel (T_COLL).  Every other type takes the switch once.
   uint32_t e = 0, m1 = 0, m0 = 0, cmask = 0;
-  const bool coll = COLL && type == T_COLL;
-  const bool md_mode = type == T_MD || coll;
+  const bool coll = COLL && type == T_COLL, raw_md = COLL && type == T_MDRAW;
+  const bool md_mode = type == T_MD || coll || raw_md;
   if (md_mode) {
     if (!coll) { m0 = e = d.op_mdoff[v]; m1 = d.op_mdoff[v + 1]; if (e >= m1) return; }
     else { m0 = (uint32_t)v; cmask = coll_mask(d, m0); if (!cmask) return; }
@@ -1642,11 +1658,16 @@ __device__ __forceinline__ void put_value(S& s, const Dev& d, int type, uint64_t
   do {
     if (md_mode) {
       if (!coll) {
+        close_quote = false;
         const MdEntry md = d.md[e];
         if (e > m0) s.put(0x202Cu, 2);  // ", "
-        put_char(s, '"'); put_mdstr(s, d, md.key); s.put(0x203A22u, 3);  // "\": "
+        put_char(s, '"');
+        if (raw_md) { uint64_t b, e2; coll_text(d, md.key, false, &b, &e2); for (uint64_t i = b; i < e2; i++) put_char(s, (char)d.pool_data[i]); }
+        else put_mdstr(s, d, md.key);
+        s.put(0x203A22u, 3);  // "\": "
         v = md.value;
         type = md.type == 0 ? T_I64 : md.type == 1 ? T_U64 : md.type == 2 ? T_DBL : md.type == 3 ? T_BOOL : md.type == 4 ? T_QMDSTR : T_MDSTR;
+        if (raw_md && md.type >= 4u) { type = T_RAWSTR; close_quote = md.type == 4u; if (close_quote) put_char(s, '"'); }
         more = ++e < m1;
       } else {  // the next collective key: its literal, then the op's value through the formatters below
         const uint32_t k = (uint32_t)__ffs((int)cmask) - 1u;
@@ -1779,7 +1800,9 @@ __device__ __forceinline__ bool format_event(S& s, const Dev& d, int cls, uint32
       case C_CUDAEVENT: p = gather_sync<C_CUDAEVENT>(d, a, t, filt, false, ext); base = SYNC_BASE; break;
       default: p = gather_op(d, j, a, t); base = OP_BASE; break;
     }
-    if ((((p >> K_COLL) & 1ull) != 0 && cls == C_KERNEL) != COLL) return false;
+    // rare shapes: kernels with collective metadata, instant events
+    const bool rare = (cls == C_KERNEL && ((p >> K_COLL) & 1ull) != 0) || (cls == C_OP && ((p >> I_HEAD) & 1ull) != 0);
+    if (rare != COLL) return false;
     run_fields<S, COLL>(s, d, a, base, p, nb);
   }
   return true;

@@ -17,7 +17,7 @@ from .md_order import md_visit_order
 
 # ActivityType values (libkineto/include/ActivityType.h:19-47)
 CPU_OP, USER_ANNOTATION, GPU_USER_ANNOTATION, GPU_MEMCPY, GPU_MEMSET, CONCURRENT_KERNEL = range(6)
-CUDA_RUNTIME, CUDA_DRIVER = 7, 8
+CUDA_RUNTIME, CUDA_DRIVER, CPU_INSTANT_EVENT = 7, 8, 9
 PYTHON_FUNCTION = 10
 LINK_FWD_BWD, LINK_ASYNC_CPU_GPU = 1, 2
 
@@ -391,7 +391,8 @@ def _kernel_records(rng, n, names, starts, durs, corr, n_devices, n_streams):
 
 
 def gen_kernel_launches(n=1_000_000, seed=2, n_devices=8, n_streams=32, pool_size=4096, name_len=(20, 400),
-                        orphan_fraction=0.0, buffer_bytes=4 << 20, ts_mode=0, shard=(0, 1), user_annotations=0) -> tf.Trace:
+                        orphan_fraction=0.0, buffer_bytes=4 << 20, ts_mode=0, shard=(0, 1), user_annotations=0,
+                        memory_events=0.0) -> tf.Trace:
     """`n` kernel launches: per launch one EXTERNAL_CORRELATION(CUSTOM0) record, one cudaLaunchKernel
     runtime record and one CUpti_ActivityKernel9, plus `n` CPU ops.  Kernel records carry the
     correlation ids in a seeded permutation, so the join is not positional.
@@ -441,6 +442,28 @@ def gen_kernel_launches(n=1_000_000, seed=2, n_devices=8, n_streams=32, pool_siz
         for rec in (api, kern):
             rec["start"], rec["end"] = ns_to_ticks(rec["start"], conv), ns_to_ticks(rec["end"], conv)
     t = ops
+    if memory_events > 0:
+        # PyTorch memory events: `memory_events * n` cpu_instant_event rows named "[memory]" with six integer entries
+        m = int(memory_events * n)
+        at = np.sort(rng.integers(0, n, m))
+        keys = ["Device Type", "Device Id", "Addr", "Bytes", "Total Allocated", "Total Reserved"]
+        vals = {"Device Type": np.ones(m, np.uint64), "Device Id": rng.integers(0, n_devices, m).astype(np.uint64),
+                "Addr": (139_800_000_000_000 + 512 * rng.integers(0, 1 << 30, m)).astype(np.uint64),
+                "Bytes": (rng.integers(-(1 << 28), 1 << 28, m)).astype(np.int64).view(np.uint64),
+                "Total Allocated": rng.integers(0, 1 << 36, m).astype(np.uint64), "Total Reserved": rng.integers(0, 1 << 37, m).astype(np.uint64)}
+        md = np.zeros(m * 6, tf.MD_ENTRY)
+        for j, k in enumerate(md_visit_order(tuple(keys))):
+            md["key"][j::6] = pool.add(k)
+            md["type"][j::6] = tf.MD_INT64
+            md["value"][j::6] = vals[k]
+        add = dict(op_start=t.op_start[at] + 7, op_end=t.op_start[at] + 7, op_id=np.zeros(m, np.int32),
+                   op_device=np.full(m, DEFAULT_PID, np.int32), op_resource=t.op_resource[at], op_thread=t.op_thread[at],
+                   op_type=np.full(m, CPU_INSTANT_EVENT, np.int32), op_name=np.full(m, pool.add("[memory]"), np.uint32),
+                   op_flow=np.zeros(m, np.uint32), op_flowt=np.zeros(m, np.uint8))
+        for col, v in add.items():
+            setattr(t, col, np.concatenate([getattr(t, col), v.astype(getattr(t, col).dtype)]))
+        t.op_mdoff = np.concatenate([t.op_mdoff, t.op_mdoff[-1] + 6 * np.arange(1, m + 1, dtype=np.uint32)]).astype(np.uint32)
+        t.md = np.concatenate([t.md, md])
     if user_annotations:
         # `user_annotations` user_annotation ops (ids above every cpu_op id), each covering a contiguous
         # run of launches through a CUSTOM1 correlation record per launch
@@ -737,3 +760,74 @@ def gen_op_tree(n_ops=200_000, launches_per_op=2.0, seed=4, n_devices=8, n_strea
     t.cupti, offs = tf.interleave([ext, api, kern], np.tile(np.array([0, 1, 2], np.int8), m))
     t.buftab = tf.make_buftab(offs, buffer_bytes)
     return _finish(t, pool, 1, window, n_devices)
+
+
+def gen_distributed_rank(n=200_000, rank=0, world=8, seed=5, coll_fraction=0.2, n_devices=8, n_streams=32,
+                         pool_size=4096, name_len=(20, 400), buffer_bytes=4 << 20) -> tf.Trace:
+    """One rank's trace of a distributed job: `n` kernel launches of which `coll_fraction` are NCCL collectives
+    issued by record_param_comms ops that carry the collective metadata (type among allreduce / allgather /
+    reduce_scatter / all_to_all, message size log-uniform 1 KB - 4 GB, process groups of 2-8 ranks).  Ranks differ
+    by their seed stream and by the `Rank` value; each rank's trace is processed on its own."""
+    rng = np.random.default_rng([seed, rank])
+    pool = tf.StringPool()
+    names = np.array([pool.add(s) for s in name_pool(rng, pool_size, *name_len)], np.uint64)
+    t0 = DEFAULT_BASE_TIME + 1_000_000_000
+    op_starts = _monotone_starts(rng, n, t0, 3000.0)
+    ops, thr = _cpu_ops(rng, pool, n, op_starts, DEFAULT_PID, with_md=False)
+    is_coll = rng.random(n) < coll_fraction
+    nc = int(is_coll.sum())
+    colls = ["allreduce", "allgather", "reduce_scatter", "all_to_all"]
+    ops.op_name = np.where(is_coll, np.uint32(pool.add("record_param_comms")), ops.op_name).astype(np.uint32)
+    # metadata: three entries for ordinary ops, ten for collectives (one key set each, so one visit order each)
+    keys_n = ["Sequence number", "Fwd thread id", "Input Dims"]
+    keys_c = ["Collective name", "In msg nelems", "Out msg nelems", "Group size", "dtype", "Process Group Name",
+              "Process Group Description", "Process Group Ranks", "Rank", "Seq"]
+    dims = np.array([pool.add(s) for s in ["[[32, 64, 28, 28], [64, 64, 3, 3]]", "[[8, 1024], [1024, 4096]]", "[[], [128]]"]], np.uint64)
+    groups = [list(range(k)) for k in range(2, world + 1)]
+    group_ids = np.array([pool.add(str(g)) for g in groups], np.uint64)
+    gpick = rng.integers(0, len(groups), n)
+    size = np.exp(rng.uniform(np.log(1 << 10), np.log(1 << 32), n)).astype(np.uint64)
+    kind = rng.integers(0, 4, n)
+    gsize = np.array([len(g) for g in groups], np.uint64)[gpick]
+    cols_n = {"Sequence number": (tf.MD_INT64, np.arange(n).astype(np.uint64)), "Fwd thread id": (tf.MD_INT64, (thr % 3).astype(np.uint64)),
+              "Input Dims": (tf.MD_RAWJSON, dims[rng.integers(0, len(dims), n)])}
+    cols_c = {"Collective name": (tf.MD_STRING, np.array([pool.add(c) for c in colls], np.uint64)[kind]),
+              "In msg nelems": (tf.MD_INT64, size), "Out msg nelems": (tf.MD_INT64, np.where(kind == 1, size * gsize, size)),
+              "Group size": (tf.MD_INT64, gsize), "dtype": (tf.MD_STRING, np.array([pool.add(x) for x in ["Float", "BFloat16", "Half"]], np.uint64)[rng.integers(0, 3, n)]),
+              "Process Group Name": (tf.MD_STRING, np.array([pool.add(str(i)) for i in range(len(groups))], np.uint64)[gpick]),
+              "Process Group Description": (tf.MD_STRING, np.where(gpick == len(groups) - 1, np.uint64(pool.add("default_pg")), np.uint64(pool.add("model_parallel")))),
+              "Process Group Ranks": (tf.MD_RAWJSON, group_ids[gpick]), "Rank": (tf.MD_INT64, np.full(n, rank, np.uint64)),
+              "Seq": (tf.MD_INT64, np.cumsum(is_coll).astype(np.uint64))}
+    cnt = np.where(is_coll, len(keys_c), len(keys_n)).astype(np.uint32)
+    mdoff = np.concatenate([[0], np.cumsum(cnt)]).astype(np.uint32)
+    md = np.zeros(int(mdoff[-1]), tf.MD_ENTRY)
+    for sel, keys, cols in ((~is_coll, keys_n, cols_n), (is_coll, keys_c, cols_c)):
+        base = mdoff[:-1][sel]
+        for j, k in enumerate(md_visit_order(tuple(keys))):
+            md["key"][base + j] = pool.add(k)
+            md["type"][base + j] = cols[k][0]
+            md["value"][base + j] = cols[k][1][sel]
+    ops.md, ops.op_mdoff = md, mdoff
+    # launches: every op launches one kernel; collective kernels carry NCCL names
+    corr = (np.arange(n, dtype=np.int64) + 1000).astype(np.uint32)
+    ext = np.zeros(n, tf.EXTCORR)
+    ext["kind"], ext["externalKind"] = tf.KIND_EXTERNAL_CORRELATION, tf.EXTERNAL_KIND_CUSTOM0
+    ext["externalId"], ext["correlationId"] = ops.op_id.astype(np.uint64), corr
+    api = np.zeros(n, tf.API)
+    api["kind"], api["cbid"] = tf.KIND_RUNTIME, CBID_cudaLaunchKernel
+    api["start"] = op_starts + rng.integers(200, 1500, n)
+    api["end"] = api["start"] + rng.integers(1500, 9000, n)
+    api["processId"], api["threadId"] = DEFAULT_PID, ops.op_thread.astype(np.uint32)
+    api["correlationId"] = corr
+    perm = rng.permutation(n)
+    kstart = api["start"][perm].astype(np.int64) + rng.integers(3000, 200_000, n)
+    kern = _kernel_records(rng, n, names, kstart, _lognormal_dur(rng, n), corr[perm], n_devices, n_streams)
+    nccl = np.array([pool.add("ncclDevKernel_%s_RING_LL(ncclDevKernelArgsStorage<4096ul>)" % c) for c in
+                     ["AllReduce_Sum_bf16", "AllGather", "ReduceScatter_Sum_bf16", "SendRecv"]], np.uint64)
+    kern["name"] = np.where(is_coll[perm], nccl[kind[perm]], kern["name"])
+    kern["deviceId"], kern["contextId"] = rank % n_devices, rank % n_devices + 1      # one GPU per rank
+    window = (t0 - 1000, int(kstart.max()) + 10_000_000_000)
+    t = ops
+    t.cupti, offs = tf.interleave([ext, api, kern], np.tile(np.array([0, 1, 2], np.int8), n))
+    t.buftab = tf.make_buftab(offs, buffer_bytes)
+    return _finish(t, pool, 1, window, n_devices, flags=tf.FLAG_SORT_BY_START)

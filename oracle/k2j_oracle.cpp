@@ -203,6 +203,19 @@ struct Out {
     buf += "\n  },";
     c->x_events++;
   }
+  // writeInstantEvent, libkineto/src/output_json.cpp:261-293, as handleGenericInstantEvent (:660-676) calls it:
+  // scope "t", name and metadata exactly as the activity holds them (nothing is sanitised or escaped here).
+  void instant(const char* cat, const std::string& name, int64_t pid, int64_t tid, int64_t ts, const std::string& md) {
+    buf += "\n  {\n    \"ph\": \"i\",\n    \n    \"cat\": \""; buf += cat;
+    buf += "\",\n    \"s\": \"t\",\n    \"name\": \""; buf += name;
+    buf += "\",\n    \"pid\": "; appendI(buf, pid);
+    buf += ",\n    \"tid\": "; appendI(buf, tid);
+    buf += ",\n    \"ts\": "; appendTs(buf, ts);
+    buf += "\n    ";
+    if (!md.empty() && !allSpace(md)) { buf += ",\n    \"args\": {\n      "; buf += md; buf += "\n    }"; }
+    buf += "\n  },";
+    c->x_events++;  // counted with the complete events
+  }
   void flow(char ph, int64_t id, int64_t pid, int64_t tid, int64_t ts, const char* name) {
     buf += "\n  {\n    \"ph\": \""; buf += ph;
     buf += "\",\n    \"id\": "; appendI(buf, id);
@@ -341,7 +354,9 @@ struct Run {
       // processCpuTrace logs an op only if its type is selected (GenericActivityProfiler.cpp:248);
       // the default selection is types 0..17, GPU_USER_ANNOTATION being switchable by flags bit 0.
       const bool selected = p.mode == 0 || (e.type < 18 && (e.type != T_GPU_USER_ANNOTATION || (p.flags & 1)));
-      if (selected) emit(out, e);
+      if (selected && e.type == T_CPU_INSTANT)  // handleActivity's early exit, libkineto/src/output_json.cpp:842-845
+        out.instant(kTypeNames[e.type], e.name, e.device, sanitizeTid(e.resource), out.rel(e.ts), e.md);
+      else if (selected) emit(out, e);
       activityMap[e.corrId] = i;
       // recordThreadInfo(resourceId, getThreadId, deviceId), GenericActivityProfiler.cpp:272: only keys
       // of this process are ever looked up; sysTid is an int32 parameter.

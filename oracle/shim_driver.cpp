@@ -152,6 +152,7 @@ void setupFakes(const K2JTraceFile&, const k2jt_params& p) {
   }
 }
 
+double g_save_ref_s = 0, g_save_b200_s = 0;  // ActivityTrace::save() through each logger
 double runBoth(const K2JTraceFile& tf, const k2jt_params& p, const std::string& outRef, const std::string& outB200, size_t* skipped) {
   // Mutable copy of the raw records: kernel name fields become real pointers.
   std::vector<uint8_t> cupti(tf.ptr<uint8_t>("CUPTI"), tf.ptr<uint8_t>("CUPTI") + tf.count<uint8_t>("CUPTI"));
@@ -248,10 +249,14 @@ double runBoth(const K2JTraceFile& tf, const k2jt_params& p, const std::string& 
   auto logger = std::make_unique<MemoryTraceLogger>(cfg);
   profiler.processTrace(*logger);
   ActivityTrace trace(std::move(logger), loggerFactory);
+  auto ta = std::chrono::steady_clock::now();
   trace.save("file://" + outRef);
+  auto tb = std::chrono::steady_clock::now();
   trace.save("b200://" + outB200);
   *skipped = last ? last->skippedActivities() : 0;
   auto t1 = std::chrono::steady_clock::now();
+  g_save_ref_s = std::chrono::duration<double>(tb - ta).count();
+  g_save_b200_s = std::chrono::duration<double>(t1 - tb).count();
   profiler.reset();
   return std::chrono::duration<double>(t1 - t0).count();
 }
@@ -271,7 +276,8 @@ int main(int argc, char** argv) {
     setupFakes(tf, p);
     size_t skipped = 0;
     double s = runBoth(tf, p, argv[2], argv[3], &skipped);
-    printf("{\"seconds\": %.6f, \"skipped\": %zu}\n", s, skipped);
+    printf("{\"seconds\": %.6f, \"skipped\": %zu, \"save_reference_s\": %.6f, \"save_b200_s\": %.6f}\n", s, skipped, g_save_ref_s,
+           g_save_b200_s);
   } catch (const std::exception& e) {
     fprintf(stderr, "shim_driver: %s\n", e.what());
     return 1;

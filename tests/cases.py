@@ -325,6 +325,27 @@ def collective_trace(n=40, seed=51) -> tf.Trace:
     return b.build()
 
 
+def instant_trace() -> tf.Trace:
+    """CPU instant events (PyTorch's memory events): their own event shape, no sanitising of name or metadata."""
+    b = synth.TraceBuilder(n_devices=2)
+    t0 = b.t0
+    I, S, R, D = tf.MD_INT64, tf.MD_STRING, tf.MD_RAWJSON, tf.MD_DOUBLE
+    b.op(t0 + 100, t0 + 900, 1, "aten::empty")
+    b.op(t0 + 150, t0 + 150, 0, "[memory]", type=synth.CPU_INSTANT_EVENT, md=[("Total Reserved", I, 1 << 33), ("Total Allocated", I, 123456789),
+                                                                               ("Bytes", I, -4096), ("Addr", I, 139800000000000),
+                                                                               ("Device Id", I, 0), ("Device Type", I, 1)])
+    b.op(t0 + 160, t0 + 999, 7, 'back\\slash "quoted"\nname', type=synth.CPU_INSTANT_EVENT, resource=-77,
+         md=[("k\\ey", S, 'C:\\dir\n"x"'), ("raw", R, "[1, 2]"), ("d", D, 0.5)])
+    b.op(t0 + 170, t0 + 170, 8, "no metadata", type=synth.CPU_INSTANT_EVENT, device=0, flow_id=5, flow_type=1, flow_start=1)
+    b.op(b.base - 5, t0, 9, "before the base time", type=synth.CPU_INSTANT_EVENT, device=1, resource=I64_MIN)
+    b.op(t0 + 180, t0 + 190, 9, "op after instants, same id as one of them")
+    b.extcorr(300, 9)
+    b.kernel(t0 + 500, t0 + 600, 300, "linked to id 9")
+    b.extcorr(301, 7)
+    b.kernel(t0 + 500, t0 + 600, 301, "linked to an instant event")
+    return b.build()
+
+
 CASES = {
     "edge": edge_trace,
     "generic_300": lambda: synth.gen_generic_kernels(300, seed=31, pool_size=40),
@@ -333,7 +354,17 @@ CASES = {
     "tsc_100": lambda: tsc_trace(100),
     "sync": sync_trace,
     "collectives": collective_trace,
+    "instant": instant_trace,
 }
+
+
+def without_flags(trace: tf.Trace) -> tf.Trace:
+    """Copy of `trace` with every flag bit cleared (the reference itself never sorts)."""
+    import copy
+    t = copy.copy(trace)
+    t.params = trace.params.copy()
+    t.params["flags"] = 0
+    return t
 
 
 def with_flags(trace: tf.Trace, extra: int) -> tf.Trace:

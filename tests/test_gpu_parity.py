@@ -70,9 +70,13 @@ def test_gpu_matches_reference_golden(name):
     lambda: synth.gen_op_tree(60_000, seed=210, pool_size=500, n_shapes=256),
     lambda: cases.collective_trace(3000, seed=53),
     lambda: cases.with_flags(cases.collective_trace(500, seed=54), tf.FLAG_SORT_BY_START),
+    lambda: synth.gen_distributed_rank(80_000, rank=2, seed=211, pool_size=500),
+    lambda: cases.without_flags(synth.gen_distributed_rank(30_000, rank=7, seed=212, pool_size=300)),
+    cases.instant_trace,
+    lambda: synth.gen_kernel_launches(20_000, seed=213, pool_size=100, memory_events=0.5),
 ], ids=["generic", "launches", "shard", "mixed", "mixed_small_buffers", "tsc", "edge", "edge_annot", "annotations",
         "overhead_mix", "sorted_overhead_mix", "launches_annot", "sorted_launches", "sorted_mixed", "sorted_annot", "sorted_tsc", "sorted_small",
-        "sync", "sync_mix", "sync_mix_annot", "sorted_sync", "sorted_sync_mix", "op_tree", "collectives", "sorted_collectives"])
+        "sync", "sync_mix", "sync_mix_annot", "sorted_sync", "sorted_sync_mix", "op_tree", "collectives", "sorted_collectives", "distributed_rank_sorted", "distributed_rank", "instant", "launches_memory_events"])
 def test_gpu_matches_port(gen):
     trace = gen()
     want, stats = helpers.run_port(trace)
@@ -154,8 +158,8 @@ def test_error_behaviour():
         with pytest.raises(api.K2JError) as e:
             ctx.run()
         assert e.value.status == 5
-        # unsupported CPU activity type (instant event)
-        a3 = dict(a, op_type=np.full(len(t.op_type), 9, np.int32))
+        # unsupported CPU activity type (a counter event of another profiler)
+        a3 = dict(a, op_type=np.full(len(t.op_type), 17, np.int32))
         ctx.set_arrays(a3, t.buftab, t.tidmap)
         with pytest.raises(api.K2JError) as e:
             ctx.run()

@@ -25,7 +25,9 @@ SHIM = os.path.join(helpers.ROOT, "oracle", "_ref", "shim_driver")
     cases.sync_trace,
     lambda: cases.sync_mix_trace(6000, seed=48),
     lambda: cases.collective_trace(300, seed=55),
-], ids=["launches_annot", "mixed", "edge", "annotations", "tsc", "sync", "sync_mix", "collectives"])
+    lambda: cases.without_flags(synth.gen_distributed_rank(5000, rank=1, seed=403, pool_size=100)),
+    cases.instant_trace,
+], ids=["launches_annot", "mixed", "edge", "annotations", "tsc", "sync", "sync_mix", "collectives", "distributed_rank", "instant"])
 def test_logger_shim_writes_the_reference_file(gen, tmp_path):
     trace = gen()
     p = str(tmp_path / "t.k2jt")

@@ -50,8 +50,10 @@ def test_golden_container_is_reproducible(name):
     lambda: synth.gen_op_tree(3000, seed=106, pool_size=100, n_shapes=64),
     cases.collective_trace,
     lambda: cases.collective_trace(400, seed=52),
+    lambda: cases.without_flags(synth.gen_distributed_rank(3000, rank=5, seed=107, pool_size=100)),
+    cases.instant_trace,
 ], ids=["generic", "launches", "shard", "mixed", "tsc", "edge", "edge_annot", "annotations", "overhead_mix", "launches_annot",
-        "sync", "sync_mix", "sync_mix_annot", "op_tree", "collectives", "collectives_400"])
+        "sync", "sync_mix", "sync_mix_annot", "op_tree", "collectives", "collectives_400", "distributed_rank", "instant"])
 def test_port_matches_live_reference(gen):
     trace = gen()
     doc, _ = helpers.run_ref(trace)
