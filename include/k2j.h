@@ -27,7 +27,8 @@ typedef enum {
   K2J_ERR_CUDA = 2,             /* a CUDA runtime call failed; see k2j_last_error */
   K2J_ERR_UNSUPPORTED = 3,      /* input uses a feature this build does not implement */
   K2J_ERR_STATE = 4,            /* call order violated (e.g. output requested before a run) */
-  K2J_ERR_DEVICE_CHECK = 5      /* a kernel's own bounds/consistency check tripped */
+  K2J_ERR_DEVICE_CHECK = 5,     /* a kernel's own bounds/consistency check tripped */
+  K2J_ERR_IO = 6                /* writing the output to a file descriptor failed */
 } k2j_status;
 
 /* Scalars of one trace.
@@ -235,6 +236,13 @@ k2j_status k2j_copy_output(k2j_ctx* ctx, void* host_dst, uint64_t capacity);
  * one trace running while the next trace is uploaded and formatted (no reference counterpart: the
  * reference writes its file synchronously, libkineto/src/output_json.cpp:1098-1107). */
 k2j_status k2j_copy_output_async(k2j_ctx* ctx, void* host_dst, uint64_t capacity);
+/* Writes the text to an open file descriptor at its current position: the device-to-host copy runs in chunks
+ * through two pinned staging buffers of the context, so the copy of one chunk overlaps the write() of the one
+ * before it, and the text is never held whole in host memory.  `written` (optional) receives the byte count.
+ * Stands where the reference streams its events into an ofstream (libkineto/src/output_json.cpp:485-492,
+ * :237-259); the caller keeps the reference's temporary-file-then-rename protocol (:1098-1107).
+ * A failed write() returns K2J_ERR_IO with errno's text as the context's last error. */
+k2j_status k2j_write_output(k2j_ctx* ctx, int fd, uint64_t* written);
 /* Waits for everything enqueued on the context's stream. */
 k2j_status k2j_synchronize(k2j_ctx* ctx);
 

@@ -3,6 +3,8 @@
 #include "../../include/k2j.h"
 
 #include <cuda_runtime.h>
+#include <errno.h>
+#include <unistd.h>
 #include <stdarg.h>
 #include <stdio.h>
 #include <string.h>
@@ -70,6 +72,8 @@ struct k2j_ctx {
   DevBuf tid_tab, corr_tab, user_tab, op_tab, work_slot, work_ev, ev_size, ev_off, ev_ext, out, counters;
   uint64_t* h_totals = nullptr;   // pinned, 32 words: [0, C_NCOL) column totals, 20 text bytes, 21 bytes of CPU-op text, 22 annotation bytes, 23 sort, 24 scan entry point, 25 the record_param_comms flag
   Counters* h_counters = nullptr; // pinned
+  void* h_stage[2] = {nullptr, nullptr};            // pinned staging buffers of k2j_write_output
+  cudaEvent_t stage_ev[2] = {nullptr, nullptr};
   cudaEvent_t ev[8]{};
   uint64_t out_bytes = 0;
   bool ran = false, segmented = false, have_global_join = false;
@@ -316,6 +320,10 @@ void k2j_destroy(k2j_ctx* c) {
     b->release();
   if (c->h_totals) cudaFreeHost(c->h_totals);
   if (c->h_counters) cudaFreeHost(c->h_counters);
+  for (int i = 0; i < 2; i++) {
+    if (c->h_stage[i]) cudaFreeHost(c->h_stage[i]);
+    if (c->stage_ev[i]) cudaEventDestroy(c->stage_ev[i]);
+  }
   for (auto& e : c->ev) if (e) cudaEventDestroy(e);
   if (c->own_stream && c->stream) cudaStreamDestroy(c->stream);
   delete c;
@@ -854,6 +862,44 @@ k2j_status k2j_copy_output_async(k2j_ctx* c, void* dst, uint64_t cap) {
   if (cap < c->out_bytes || (!dst && c->out_bytes)) return fail(c, K2J_ERR_INVALID_ARGUMENT, "destination too small");
   K2J_CUDA(c, cudaSetDevice(c->device));
   if (c->out_bytes) K2J_CUDA(c, cudaMemcpyAsync(dst, c->out.p, c->out_bytes, cudaMemcpyDeviceToHost, c->stream));
+  return K2J_OK;
+}
+
+k2j_status k2j_write_output(k2j_ctx* c, int fd, uint64_t* written) {
+  if (!c) return K2J_ERR_INVALID_ARGUMENT;
+  if (!c->ran) return fail(c, K2J_ERR_STATE, "no completed run");
+  if (fd < 0) return fail(c, K2J_ERR_INVALID_ARGUMENT, "bad file descriptor");
+  K2J_CUDA(c, cudaSetDevice(c->device));
+  constexpr size_t kChunk = 16u << 20;
+  for (int i = 0; i < 2; i++) {
+    if (!c->h_stage[i]) K2J_CUDA(c, cudaMallocHost(&c->h_stage[i], kChunk));
+    if (!c->stage_ev[i]) K2J_CUDA(c, cudaEventCreateWithFlags(&c->stage_ev[i], cudaEventDisableTiming));
+  }
+  auto write_all = [&](const char* p, size_t n) -> bool {
+    while (n) {
+      const ssize_t w = write(fd, p, n);
+      if (w < 0) { if (errno == EINTR) continue; return false; }
+      p += w; n -= (size_t)w;
+    }
+    return true;
+  };
+  const uint64_t total = c->out_bytes;
+  const uint64_t n_chunks = (total + kChunk - 1) / kChunk;
+  bool io_ok = true;
+  for (uint64_t i = 0; i <= n_chunks; i++) {
+    if (i < n_chunks) {  // chunk i starts its way to the host ...
+      const size_t len = (size_t)std::min<uint64_t>(kChunk, total - i * kChunk);
+      K2J_CUDA(c, cudaMemcpyAsync(c->h_stage[i & 1], c->out.as<uint8_t>() + i * kChunk, len, cudaMemcpyDeviceToHost, c->stream));
+      K2J_CUDA(c, cudaEventRecord(c->stage_ev[i & 1], c->stream));
+    }
+    if (i > 0) {         // ... while chunk i - 1, which has arrived, goes to the file
+      K2J_CUDA(c, cudaEventSynchronize(c->stage_ev[(i - 1) & 1]));
+      const size_t len = (size_t)std::min<uint64_t>(kChunk, total - (i - 1) * kChunk);
+      if (io_ok && !write_all(static_cast<const char*>(c->h_stage[(i - 1) & 1]), len)) io_ok = false;  // keep draining the copies
+    }
+  }
+  if (!io_ok) return fail(c, K2J_ERR_IO, "write: %s", strerror(errno));
+  if (written) *written = total;
   return K2J_OK;
 }
 

@@ -7,9 +7,13 @@
 #include <fmt/format.h>
 
 #include <algorithm>
+#include <chrono>
+#include <cstdlib>
 #include <cstdio>
 #include <cstring>
+#include <deque>
 #include <map>
+#include <mutex>
 
 #include <cuda_runtime_api.h>
 
@@ -68,47 +72,91 @@ std::string instantRow(const std::string& name, const std::string& pid, const st
 
 // Typed metadata of a GenericTraceActivity in visit order.
 struct MdCollector final : public libkineto::ITypedMetadataVisitor {
-  struct Entry { std::string key; uint32_t type; uint64_t value; std::string text; };
+  // Keys and string values are views into the visited activity (alive for the duration of the visit and of the
+  // interning that follows); only rendered collections own their text.
+  struct Entry { std::string_view key; uint32_t type; uint64_t value; std::string_view text; };
   std::vector<Entry> entries;
-  void visitValue(const MetadataField<int64_t>& f, int64_t v) override { entries.push_back({std::string(f.name), K2J_MD_INT64, (uint64_t)v, {}}); }
+  std::deque<std::string> owned;
+  void visitValue(const MetadataField<int64_t>& f, int64_t v) override { entries.push_back({f.name, K2J_MD_INT64, (uint64_t)v, {}}); }
   void visitValue(const MetadataField<double>& f, double v) override {
     uint64_t b; memcpy(&b, &v, 8);
-    entries.push_back({std::string(f.name), K2J_MD_DOUBLE, b, {}});
+    entries.push_back({f.name, K2J_MD_DOUBLE, b, {}});
   }
-  void visitValue(const MetadataField<bool>& f, bool v) override { entries.push_back({std::string(f.name), K2J_MD_BOOL, v ? 1u : 0u, {}}); }
-  void visitValue(const MetadataField<std::string>& f, std::string_view v) override { entries.push_back({std::string(f.name), K2J_MD_STRING, 0, std::string(v)}); }
+  void visitValue(const MetadataField<bool>& f, bool v) override { entries.push_back({f.name, K2J_MD_BOOL, v ? 1u : 0u, {}}); }
+  void visitValue(const MetadataField<std::string>& f, std::string_view v) override { entries.push_back({f.name, K2J_MD_STRING, 0, v}); }
   void visitValue(const MetadataField<std::vector<int64_t>>& f, const std::vector<int64_t>& v) override { raw(f.name, v); }
   void visitValue(const MetadataField<std::vector<std::string>>& f, const std::vector<std::string>& v) override { raw(f.name, v); }
-  void visitValue(const MetadataField<RawJson>& f, const RawJson& v) override { entries.push_back({std::string(f.name), K2J_MD_RAWJSON, 0, v.value}); }
-  void visitValue(const MetadataField<uint64_t>& f, uint64_t v) override { entries.push_back({std::string(f.name), K2J_MD_UINT64, v, {}}); }
+  void visitValue(const MetadataField<RawJson>& f, const RawJson& v) override { entries.push_back({f.name, K2J_MD_RAWJSON, 0, v.value}); }
+  void visitValue(const MetadataField<uint64_t>& f, uint64_t v) override { entries.push_back({f.name, K2J_MD_UINT64, v, {}}); }
   void visitValue(const MetadataField<InputShapes>& f, const InputShapes& v) override { raw(f.name, v); }
-  void visitUnsupported(std::string_view name) override { entries.push_back({std::string(name), K2J_MD_STRING, 0, "<unsupported metadata type>"}); }
+  void visitUnsupported(std::string_view name) override { entries.push_back({name, K2J_MD_STRING, 0, "<unsupported metadata type>"}); }
   void beginDict(std::string_view) override {}
   void endDict() override {}
   template <class T> void raw(std::string_view name, const T& v) {  // collections: text once, as the reference renders them
-    std::string out;
-    libkineto::internal::JsonTypedMetadataVisitor::appendArray(out, v);
-    entries.push_back({std::string(name), K2J_MD_RAWJSON, 0, out});
+    owned.emplace_back();
+    libkineto::internal::JsonTypedMetadataVisitor::appendArray(owned.back(), v);
+    entries.push_back({name, K2J_MD_RAWJSON, 0, owned.back()});
   }
 };
 
 }  // namespace
 
+// Wall-clock breakdown of the logger's host side, printed at finalizeTrace when K2J_SHIM_TIMING is set.
+struct Stopwatch {
+  double total = 0;
+  std::chrono::steady_clock::time_point t0;
+  void start() { t0 = std::chrono::steady_clock::now(); }
+  void stop() { total += std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count(); }
+};
+struct Timed {
+  Stopwatch& w;
+  explicit Timed(Stopwatch& sw) : w(sw) { w.start(); }
+  ~Timed() { w.stop(); }
+};
+
+// k2j contexts outlive the loggers that use them: a logger is created per ActivityTrace::save(), while a context's
+// workspaces on the GPU are grow-only and cost tens of milliseconds to allocate.  A finished logger hands its
+// context back; the next logger on that device takes it.  Contexts are kept until the process exits.
+struct ContextPool {
+  static std::mutex& mu() { static std::mutex m; return m; }
+  static std::vector<std::pair<int, k2j_ctx*>>& free() { static std::vector<std::pair<int, k2j_ctx*>> v; return v; }
+  static k2j_ctx* take(int device) {
+    {
+      std::lock_guard<std::mutex> g(mu());
+      auto& v = free();
+      for (size_t i = 0; i < v.size(); i++)
+        if (v[i].first == device) { k2j_ctx* c = v[i].second; v.erase(v.begin() + i); return c; }
+    }
+    k2j_ctx* c = nullptr;
+    return k2j_create(device, nullptr, &c) == K2J_OK ? c : nullptr;
+  }
+  static void give(int device, k2j_ctx* c) {
+    if (!c) return;
+    std::lock_guard<std::mutex> g(mu());
+    free().push_back({device, c});
+  }
+};
+
 struct B200TraceLogger::Impl {
+  Stopwatch tOps, tRecords, tSetup, tRun, tWrite;
   std::string fileName, tempFileName;
   FILE* out = nullptr;
   k2j_ctx* ctx = nullptr;
   int device = 0;
 
   // string pool shared by all runs
-  std::unordered_map<std::string, uint32_t> ids;
+  struct SvHash {
+    using is_transparent = void;
+    size_t operator()(std::string_view v) const { return std::hash<std::string_view>{}(v); }
+  };
+  std::unordered_map<std::string, uint32_t, SvHash, std::equal_to<>> ids;  // looked up by view: no copy per call
   std::vector<uint64_t> poolOff{0};
   std::vector<uint8_t> poolData;
-  uint32_t intern(const std::string& s) {
+  uint32_t intern(std::string_view s) {
     auto it = ids.find(s);
     if (it != ids.end()) return it->second;
     uint32_t id = (uint32_t)ids.size();
-    ids.emplace(s, id);
+    ids.emplace(std::string(s), id);
     poolData.insert(poolData.end(), s.begin(), s.end());
     poolOff.push_back(poolData.size());
     return id;
@@ -131,7 +179,20 @@ struct B200TraceLogger::Impl {
     // device-side lookups give the same answer.
     std::vector<uint8_t> prefix;
     std::unordered_map<uint32_t, bool> ctxDeclared;
-    std::unordered_set<int32_t> opIds;  // ids of the CPU-side activities of this run
+    // ids of the CPU-side activities of this run: a bitmap for the usual small non-negative ids, a set for the rest
+    std::vector<uint64_t> opIdBits;
+    std::unordered_set<int32_t> opIdRest;
+    void noteOp(int32_t id) {
+      if (id >= 0 && id < (1 << 28)) {
+        const size_t w = (size_t)id >> 6;
+        if (w >= opIdBits.size()) opIdBits.resize(std::max(w + 1, opIdBits.size() * 2), 0);
+        opIdBits[w] |= 1ull << (id & 63);
+      } else opIdRest.insert(id);
+    }
+    bool hasOp(int32_t id) const {
+      if (id >= 0 && id < (1 << 28)) { const size_t w = (size_t)id >> 6; return w < opIdBits.size() && ((opIdBits[w] >> (id & 63)) & 1); }
+      return opIdRest.count(id) != 0;
+    }
     bool hasCupti = false;
   };
   Run run;
@@ -173,7 +234,7 @@ struct B200TraceLogger::Impl {
     appendRecord(e);
     // an op logged in an earlier run is made joinable again (see flushRun); one of this run keeps its own row, so
     // that its name and metadata stay reachable from the records linked to it
-    if (!run.opIds.count((int32_t)a.linkedActivity()->correlationId()))
+    if (!run.hasOp((int32_t)a.linkedActivity()->correlationId()))
       linkedIds.push_back((int32_t)a.linkedActivity()->correlationId());
   }
   std::vector<int32_t> linkedIds;
@@ -254,23 +315,28 @@ bool B200TraceLogger::Impl::flushRun() {
   r.cupti.swap(r.prefix);
   const uint64_t buftab[2] = {0, r.cupti.size()};
   k2j_result res;
+  tSetup.start();
   bool ok = k2j_set_params(ctx, &p, props.data()) == K2J_OK &&
             k2j_set_strings(ctx, poolOff.data(), poolData.data(), poolOff.size() - 1) == K2J_OK &&
             k2j_set_cbid_names(ctx, rtNames.data(), (uint32_t)rtNames.size(), drNames.data(), (uint32_t)drNames.size()) == K2J_OK &&
             k2j_set_thread_map(ctx, tidPairs.data(), (uint32_t)(tidPairs.size() / 2)) == K2J_OK &&
             k2j_set_ops(ctx, &ops) == K2J_OK &&
-            k2j_set_cupti(ctx, r.cupti.data(), r.cupti.size(), buftab, r.cupti.empty() ? 0 : 1) == K2J_OK &&
-            k2j_run(ctx, &res) == K2J_OK;
+            k2j_set_cupti(ctx, r.cupti.data(), r.cupti.size(), buftab, r.cupti.empty() ? 0 : 1) == K2J_OK;
+  tSetup.stop();
+  tRun.start();
+  ok = ok && k2j_run(ctx, &res) == K2J_OK;
+  tRun.stop();
   if (!ok) {
     LOG(ERROR) << "B200TraceLogger: " << k2j_last_error(ctx);
     return false;
   }
-  std::vector<char> buf(res.out_bytes);
-  if (k2j_copy_output(ctx, buf.data(), buf.size()) != K2J_OK) {
+  // the text goes from the device to the file in chunks, the copy of one overlapping the write of the one before
+  Timed timed(tWrite);
+  fflush(out);
+  if (k2j_write_output(ctx, fileno(out), nullptr) != K2J_OK) {
     LOG(ERROR) << "B200TraceLogger: " << k2j_last_error(ctx);
     return false;
   }
-  fwrite(buf.data(), 1, buf.size(), out);
   return true;
 }
 
@@ -280,7 +346,8 @@ B200TraceLogger::B200TraceLogger(const std::string& traceFileName, int cudaDevic
   impl_->device = cudaDevice;
   impl_->out = fopen(impl_->tempFileName.c_str(), "wb");
   if (!impl_->out) PLOG(ERROR) << "Failed to open '" << impl_->fileName << "'";
-  if (k2j_create(cudaDevice, nullptr, &impl_->ctx) != K2J_OK) {
+  impl_->ctx = ContextPool::take(cudaDevice);
+  if (!impl_->ctx) {
     // No GPU path, and deliberately no CPU path: like ChromeTraceLogger with an unopened file, every
     // handler returns without writing.
     LOG(ERROR) << "B200TraceLogger: cannot create a k2j context on CUDA device " << cudaDevice;
@@ -292,7 +359,7 @@ B200TraceLogger::B200TraceLogger(const std::string& traceFileName, int cudaDevic
 
 B200TraceLogger::~B200TraceLogger() {
   if (impl_->out) fclose(impl_->out);
-  k2j_destroy(impl_->ctx);
+  ContextPool::give(impl_->device, impl_->ctx);
 }
 
 void B200TraceLogger::handleTraceStart(const std::unordered_map<std::string, std::string>& metadata,
@@ -361,10 +428,11 @@ void B200TraceLogger::handleTraceSpan(const TraceSpan& span) {
 void B200TraceLogger::handleGenericActivity(const libkineto::GenericTraceActivity& op) {
   if (!impl_->out) return;
   Impl& m = *impl_;
+  Timed timed(m.tOps);
   if (m.run.hasCupti) m.flushRun();  // a run is CPU-side activities followed by CUPTI records
   auto& r = m.run;
   r.start.push_back(op.startTime); r.end.push_back(op.endTime); r.id.push_back(op.id); r.dev.push_back(op.device);
-  r.opIds.insert(op.id);
+  r.noteOp(op.id);
   r.resource.push_back(op.resource); r.thread.push_back(op.threadId); r.type.push_back((int32_t)op.activityType);
   r.name.push_back(m.intern(op.activityName)); r.flow.push_back(op.flow.id);
   r.flowt.push_back((uint8_t)(op.flow.type | (op.flow.start << 4)));
@@ -381,7 +449,16 @@ void B200TraceLogger::handleGenericActivity(const libkineto::GenericTraceActivit
 void B200TraceLogger::handleActivity(const libkineto::ITraceActivity& a) {
   if (!impl_->out) return;
   Impl& m = *impl_;
-  if (auto* g = dynamic_cast<const libkineto::GenericTraceActivity*>(&a)) { handleGenericActivity(*g); return; }
+  // The activity's type names the one wrapper class worth trying, so a record costs one successful dynamic_cast
+  // instead of a chain of failing ones; anything else is tried as a GenericTraceActivity at the end.
+  const libkineto::ActivityType ty = a.type();
+  const bool cuptiType = ty == ActivityType::CONCURRENT_KERNEL || ty == ActivityType::GPU_MEMCPY || ty == ActivityType::GPU_MEMSET ||
+                         ty == ActivityType::CUDA_RUNTIME || ty == ActivityType::CUDA_DRIVER || ty == ActivityType::OVERHEAD ||
+                         ty == ActivityType::CUDA_SYNC || ty == ActivityType::CUDA_EVENT;
+  if (!cuptiType) {
+    if (auto* g = dynamic_cast<const libkineto::GenericTraceActivity*>(&a)) { handleGenericActivity(*g); return; }
+  }
+  Timed timed(m.tRecords);
   auto convert = [](auto& rec) {  // timestamps as the wrapper reports them (CuptiTimestamp.h:29-51)
     const uint64_t s = rec.start, e = rec.end;
     rec.start = (uint64_t)convertCuptiTimestamp(s);
@@ -389,9 +466,10 @@ void B200TraceLogger::handleActivity(const libkineto::ITraceActivity& a) {
   };
   auto cbidName = [&](std::vector<uint32_t>& tab, uint32_t cbid, bool driver) {
     if (cbid >= tab.size()) tab.resize(cbid + 1, m.invalidId);
+    if (tab[cbid] != m.invalidId) return;  // named before
     tab[cbid] = m.intern(driver ? driverCbidName(cbid) : runtimeCbidName(cbid));
   };
-  if (auto* k = dynamic_cast<const GpuActivity<CUpti_ActivityKernelType>*>(&a)) {
+  if (auto* k = ty == ActivityType::CONCURRENT_KERNEL ? dynamic_cast<const GpuActivity<CUpti_ActivityKernelType>*>(&a) : nullptr) {
     m.addLink(a);
     if (a.linkedActivity() && a.linkedActivity()->name() == "record_param_comms") m.noteCollective(*a.linkedActivity());
     CUpti_ActivityKernelType rec = k->raw();
@@ -401,22 +479,22 @@ void B200TraceLogger::handleActivity(const libkineto::ITraceActivity& a) {
     uint64_t id64 = id;
     memcpy(&rec.name, &id64, 8);
     m.appendRecord(rec);
-  } else if (auto* c = dynamic_cast<const GpuActivity<CUpti_ActivityMemcpyType>*>(&a)) {
+  } else if (auto* c = ty == ActivityType::GPU_MEMCPY ? dynamic_cast<const GpuActivity<CUpti_ActivityMemcpyType>*>(&a) : nullptr) {
     m.addLink(a);
     CUpti_ActivityMemcpyType rec = c->raw();
     convert(rec);
     m.appendRecord(rec);
-  } else if (auto* c2 = dynamic_cast<const GpuActivity<CUpti_ActivityMemcpyPtoPType>*>(&a)) {
+  } else if (auto* c2 = ty == ActivityType::GPU_MEMCPY ? dynamic_cast<const GpuActivity<CUpti_ActivityMemcpyPtoPType>*>(&a) : nullptr) {
     m.addLink(a);
     CUpti_ActivityMemcpyPtoPType rec = c2->raw();
     convert(rec);
     m.appendRecord(rec);
-  } else if (auto* s = dynamic_cast<const GpuActivity<CUpti_ActivityMemsetType>*>(&a)) {
+  } else if (auto* s = ty == ActivityType::GPU_MEMSET ? dynamic_cast<const GpuActivity<CUpti_ActivityMemsetType>*>(&a) : nullptr) {
     m.addLink(a);
     CUpti_ActivityMemsetType rec = s->raw();
     convert(rec);
     m.appendRecord(rec);
-  } else if (auto* rt = dynamic_cast<const RuntimeActivity*>(&a)) {
+  } else if (auto* rt = ty == ActivityType::CUDA_RUNTIME ? dynamic_cast<const RuntimeActivity*>(&a) : nullptr) {
     m.addLink(a);
     CUpti_ActivityAPI rec = rt->raw();
     convert(rec);
@@ -426,7 +504,7 @@ void B200TraceLogger::handleActivity(const libkineto::ITraceActivity& a) {
       m.tidPairs.push_back((int32_t)rec.threadId); m.tidPairs.push_back((int32_t)a.resourceId());
     }
     m.appendRecord(rec);
-  } else if (auto* dr = dynamic_cast<const DriverActivity*>(&a)) {
+  } else if (auto* dr = ty == ActivityType::CUDA_DRIVER ? dynamic_cast<const DriverActivity*>(&a) : nullptr) {
     m.addLink(a);
     CUpti_ActivityAPI rec = dr->raw();
     convert(rec);
@@ -436,7 +514,7 @@ void B200TraceLogger::handleActivity(const libkineto::ITraceActivity& a) {
       m.tidPairs.push_back((int32_t)rec.threadId); m.tidPairs.push_back((int32_t)a.resourceId());
     }
     m.appendRecord(rec);
-  } else if (auto* ov = dynamic_cast<const OverheadActivity*>(&a)) {
+  } else if (auto* ov = ty == ActivityType::OVERHEAD ? dynamic_cast<const OverheadActivity*>(&a) : nullptr) {
     // the wrapper holds the 40-byte prefix of the record (CUpti_ActivityOverhead); the GPU path takes the
     // record as CUPTI writes it today (CUpti_ActivityOverhead3, 56 bytes)
     CUpti_ActivityOverhead3 rec;
@@ -444,7 +522,7 @@ void B200TraceLogger::handleActivity(const libkineto::ITraceActivity& a) {
     memcpy(&rec, &ov->raw(), sizeof(CUpti_ActivityOverhead));
     convert(rec);
     m.appendRecord(rec);
-  } else if (auto* sy = dynamic_cast<const CudaSyncActivity*>(&a)) {
+  } else if (auto* sy = ty == ActivityType::CUDA_SYNC ? dynamic_cast<const CudaSyncActivity*>(&a) : nullptr) {
     m.addLink(a);
     CUpti_ActivitySynchronization rec = sy->raw();
     convert(rec);
@@ -468,12 +546,16 @@ void B200TraceLogger::handleActivity(const libkineto::ITraceActivity& a) {
       }
     }
     m.appendRecord(rec);
-  } else if (auto* ce = dynamic_cast<const CudaEventActivity*>(&a)) {
+  } else if (auto* ce = ty == ActivityType::CUDA_EVENT ? dynamic_cast<const CudaEventActivity*>(&a) : nullptr) {
     m.addLink(a);
     CUpti_ActivityCudaEventType rec = ce->raw();
     rec.deviceTimestamp = (uint64_t)convertCuptiTimestamp(rec.deviceTimestamp);
     m.declareContext(rec.contextId, (uint32_t)a.deviceId());
     m.appendRecord(rec);
+  } else if (auto* g = cuptiType ? dynamic_cast<const libkineto::GenericTraceActivity*>(&a) : nullptr) {
+    m.tRecords.stop();  // a generic activity that carries one of the CUPTI types
+    handleGenericActivity(*g);
+    m.tRecords.start();
   } else {
     // Foreign activity classes are not handled by the GPU path; there is no CPU path to fall back to, so they
     // are counted and reported.
@@ -505,6 +587,9 @@ void B200TraceLogger::finalizeTrace(const Config&, std::unique_ptr<ActivityBuffe
   }
   s += fmt::format("\"traceName\": \"{}\" }}", fileName);
   impl_->text(s);
+  if (getenv("K2J_SHIM_TIMING"))
+    fprintf(stderr, "B200TraceLogger host seconds: cpu activities %.3f, cupti activities %.3f, set inputs %.3f, k2j_run %.3f, copy + write %.3f\n",
+            impl_->tOps.total, impl_->tRecords.total, impl_->tSetup.total, impl_->tRun.total, impl_->tWrite.total);
   fclose(impl_->out);
   impl_->out = nullptr;
   remove(impl_->fileName.c_str());

@@ -108,6 +108,36 @@ def test_device_resident_inputs_and_context_reuse():
         ctx.close()
 
 
+def test_write_output_streams_the_same_bytes(tmp_path):
+    """k2j_write_output: text larger than its staging chunks, a small one and an empty one arrive in the file as
+    copy_output returns them, appended at the descriptor's position; a bad descriptor is an I/O error."""
+    from kineto_b200 import api
+    ctx = api.K2J(0)
+    try:
+        path = str(tmp_path / "out.json")
+        want = b"header"
+        with open(path, "wb") as f:
+            f.write(b"header")
+            f.flush()
+            for trace in (synth.gen_kernel_launches(30_000, seed=303, pool_size=200), cases.edge_trace(), synth.TraceBuilder().build()):
+                ctx.load(trace)
+                ctx.run()
+                text = ctx.copy_output().tobytes()
+                assert ctx.write_output(f.fileno()) == len(text)
+                want += text
+        assert len(want) > (48 << 20)   # several 16 MiB chunks
+        assert open(path, "rb").read() == want
+        r, w = os.pipe()
+        os.close(w); os.close(r)
+        ctx.load(cases.edge_trace())
+        ctx.run()
+        with pytest.raises(api.K2JError) as e:
+            ctx.write_output(r)
+        assert e.value.status == 6
+    finally:
+        ctx.close()
+
+
 def test_empty_and_degenerate_inputs():
     from kineto_b200 import api
     b = synth.TraceBuilder()
