@@ -1088,7 +1088,18 @@ __device__ __forceinline__ void linked_op(const Dev& d, uint32_t corr, unsigned 
 // GenericActivityProfiler::handleGpuActivity's user-annotation step (GenericActivityProfiler.cpp:424-434)
 // with GpuUserEventMap::insertOrExtendEvent (:292-311): per (device, stream) and annotation op the span
 // [min start, max end] over the GPU activities correlated to it.  Runs in the size pass only.
-__device__ __noinline__ void span_update(const Dev& d, uint32_t corr, uint32_t dev, uint32_t stream, int64_t ts,
+// Out of line (rare), with the tables it touches passed by value: a reference to the kernel's parameter block would
+// make every thread of the size pass copy that block (about 1 KB) into local memory at kernel entry.
+struct SpanArgs {
+  const unsigned long long* user_tab; uint32_t user_mask; const ExtRec* ext_all; const unsigned long long* op_tab; uint32_t op_mask;
+  unsigned long long* ds_tab; uint32_t ds_mask; unsigned long long* span_key; unsigned long long* span_nstart;
+  unsigned long long* span_end; unsigned long long* span_nfirst; uint32_t* span_row; uint32_t span_mask; Counters* counters;
+};
+__device__ __forceinline__ SpanArgs span_args(const Dev& d) {
+  return SpanArgs{d.user_tab, d.user_mask, d.ext_all, d.op_tab, d.op_mask, d.ds_tab, d.ds_mask, d.span_key, d.span_nstart,
+                  d.span_end, d.span_nfirst, d.span_row, d.span_mask, d.counters};
+}
+__device__ __noinline__ void span_update(const SpanArgs d, uint32_t corr, uint32_t dev, uint32_t stream, int64_t ts,
                                          int64_t dur, uint64_t ev) {
   const uint32_t idx = tab_find(d.user_tab, d.user_mask, corr);
   if (idx == 0xFFFFFFFFu) return;
@@ -1396,7 +1407,7 @@ __device__ __forceinline__ uint64_t gather_kernel(const Dev& d, uint32_t* a, Tal
   if (corr > 0) t.flow++;
   else p &= ~((1ull << K_FLOW) | (1ull << K_FPID) | (1ull << K_FTID) | (1ull << K_FTS) | (1ull << K_FEND));
   if (counting && d.seen_tab != nullptr) seen_insert(d, dev, stream);
-  if (counting && d.span_key != nullptr) span_update(d, corr, dev, stream, ts, dur, t.ev);
+  if (counting && d.span_key != nullptr) span_update(span_args(d), corr, dev, stream, ts, dur, t.ev);
   return p;
 }
 
@@ -1444,7 +1455,7 @@ __device__ __forceinline__ uint64_t gather_mem(const Dev& d, uint32_t* a, Tally&
   t.x++;
   if (corr > 0) { on(M_FLOW); on(M_FPID); on(M_FTID); on(M_FTS); on(M_FEND); t.flow++; }
   if (counting && d.seen_tab != nullptr) seen_insert(d, dev, stream);
-  if (counting && d.span_key != nullptr) span_update(d, corr, dev, stream, ts, dur, t.ev);
+  if (counting && d.span_key != nullptr) span_update(span_args(d), corr, dev, stream, ts, dur, t.ev);
   return p;
 }
 
