@@ -977,6 +977,11 @@ constexpr FieldSrc kAllFields[] = {K2J_API_FIELDS, K2J_KERNEL_FIELDS, K2J_MEM_FI
                                    {"", T_MDRAW, VK_U32, OS_ROW},
                                    K2J_OPTAIL_FIELDS, K2J_ANN_FIELDS, K2J_SYNC_FIELDS, K2J_CSTR_FIELDS};
 static_assert(sizeof(kAllFields) / sizeof(kAllFields[0]) == FIELD_COUNT, "field table and enums disagree");
+constexpr bool wide_values_aligned() {
+  for (int f = 0; f < FIELD_COUNT; f++) if (kAllFields[f].vk == VK_64 && kAllFields[f].voff % 8 != 0) return false;
+  return true;
+}
+static_assert(wide_values_aligned(), "64-bit values must sit at multiples of 8 (slot_value loads one aligned unit)");
 constexpr int kAllWords = prog_words(kAllFields);
 __constant__ Prog<FIELD_COUNT, kAllWords> g_fields = make_prog<FIELD_COUNT, kAllWords>(kAllFields);
 
@@ -1259,10 +1264,14 @@ __device__ __forceinline__ uint64_t a64(const uint32_t* a, int off) { return (ui
 __device__ __forceinline__ void s32(uint32_t* a, int off, uint32_t v) { a[off >> 2] = v; }
 __device__ __forceinline__ void s64(uint32_t* a, int off, uint64_t v) { a[off >> 2] = (uint32_t)v; a[(off >> 2) + 1] = (uint32_t)(v >> 32); }
 // value of a field: 32 bits zero- or sign-extended, or 64 bits (no branches)
+// One 64-bit load of the aligned unit that holds the value: areas are an odd number of units apart, so the 64-bit
+// loads of a warp touch every bank pair once, while 32-bit loads at that stride would collide two ways.  (64-bit
+// values sit at multiples of 8.)
 __device__ __forceinline__ uint64_t slot_value(const uint32_t* a, uint32_t voff, uint32_t vk) {
-  const uint32_t lo = a[voff >> 2];
+  const uint64_t u = reinterpret_cast<const uint64_t*>(a)[voff >> 3];
+  const uint32_t lo = (voff & 4u) ? (uint32_t)(u >> 32) : (uint32_t)u;
   uint32_t hi = vk == VK_I32 ? (uint32_t)((int32_t)lo >> 31) : 0u;
-  if (vk == VK_64) hi = a[(voff >> 2) + 1];
+  if (vk == VK_64) hi = (uint32_t)(u >> 32);
   return (uint64_t)lo | ((uint64_t)hi << 32);
 }
 
@@ -1985,7 +1994,7 @@ __global__ void k_span_collect(Dev d, SpanRec* out, unsigned int* n_out) {
 template <bool WRITE>
 __global__ void __launch_bounds__(kEventThreads) k_annotations(Dev d, const SpanRec* spans, uint32_t n, uint32_t* sizes,
                                                                const uint64_t* offs, uint64_t out_base) {
-  __shared__ uint32_t s_area[kEventThreads * 8];
+  __shared__ uint64_t s_area[kEventThreads * 4];  // 32 bytes per span, 8-byte aligned for slot_value's 64-bit loads
   __shared__ uint64_t s_park[WRITE ? 3 * kEventThreads : 1];
   const uint32_t i = blockIdx.x * kEventThreads + threadIdx.x;
   if (i >= n) return;
@@ -1993,7 +2002,7 @@ __global__ void __launch_bounds__(kEventThreads) k_annotations(Dev d, const Span
   int64_t dur = r.end - r.start;
   if (dur < 0) dur = 0;
   unsigned long long nb = 0;
-  uint32_t* a = &s_area[threadIdx.x * 8];
+  uint32_t* a = reinterpret_cast<uint32_t*>(&s_area[threadIdx.x * 4]);
   s32(a, NS_NAME, r.op_row < d.n_ops ? d.op_name[r.op_row] : 0xFFFFFFFFu); s32(a, NS_PID, r.device); s32(a, NS_TID, r.stream);
   s32(a, NS_EXT, (uint32_t)r.op_id); s64(a, NS_TS, (uint64_t)rel_ts(d, r.start - 1)); s64(a, NS_DUR, (uint64_t)(dur + 2));
   uint64_t p = (1ull << N_COUNT) - 1ull;
