@@ -53,6 +53,12 @@ def test_md_order_matches_libstdcpp():
         k = [words[i] for i in rng.permutation(len(words))[:int(rng.integers(1, 13))]]
         ref = subprocess.run([helpers.REF_DRIVER, "--md-order", *k], capture_output=True, text=True).stdout.split("\n")[:-1]
         assert list(md_order.md_visit_order(tuple(k))) == ref
+    # more than 13 keys: the container moves to 29, then 59 buckets and re-links its nodes
+    many = words + ["key%d" % i for i in range(50)]
+    for _ in range(30):
+        k = [many[i] for i in rng.permutation(len(many))[:int(rng.integers(14, 62))]]
+        ref = subprocess.run([helpers.REF_DRIVER, "--md-order", *k], capture_output=True, text=True).stdout.split("\n")[:-1]
+        assert list(md_order.md_visit_order(tuple(k))) == ref
 
 
 @pytest.mark.skipif(not helpers.have_ref(), reason="reference build not present")
