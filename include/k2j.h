@@ -243,6 +243,12 @@ k2j_status k2j_copy_output_async(k2j_ctx* ctx, void* host_dst, uint64_t capacity
  * :237-259); the caller keeps the reference's temporary-file-then-rename protocol (:1098-1107).
  * A failed write() returns K2J_ERR_IO with errno's text as the context's last error. */
 k2j_status k2j_write_output(k2j_ctx* ctx, int fd, uint64_t* written);
+/* The same for the bytes [begin, begin + n_bytes) of the text, written with pwrite at `file_offset` (the
+ * descriptor's position is neither used nor moved).  Several contexts, in one process or in several, so fill
+ * disjoint parts of one file: the shards of a trace write their CPU-op events and their GPU-side events where
+ * they belong in the whole trace's text (the reference is single-process and has no counterpart;
+ * libkineto/src/output_membuf.h:91-107 fixes the order of the parts). */
+k2j_status k2j_write_output_at(k2j_ctx* ctx, int fd, uint64_t file_offset, uint64_t begin, uint64_t n_bytes);
 /* Waits for everything enqueued on the context's stream. */
 k2j_status k2j_synchronize(k2j_ctx* ctx);
 

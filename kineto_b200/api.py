@@ -66,7 +66,7 @@ class SegmentInfo(C.Structure):
 
 EXPORTS = ["k2j_exclusive_scan_u32", "k2j_exclusive_scan_u32_noalloc", "k2j_segment", "k2j_set_global_join", "k2j_emit", "k2j_create", "k2j_destroy", "k2j_last_error", "k2j_set_params", "k2j_set_strings",
            "k2j_set_cbid_names", "k2j_set_thread_map", "k2j_set_ops", "k2j_set_cupti", "k2j_run", "k2j_output",
-           "k2j_copy_output", "k2j_copy_output_async", "k2j_write_output", "k2j_synchronize", "k2j_version"]
+           "k2j_copy_output", "k2j_copy_output_async", "k2j_write_output", "k2j_write_output_at", "k2j_synchronize", "k2j_version"]
 
 _lib = None
 
@@ -101,6 +101,7 @@ def load_library():
     lib.k2j_copy_output.argtypes = [vp, vp, C.c_uint64]
     lib.k2j_copy_output_async.argtypes = [vp, vp, C.c_uint64]
     lib.k2j_write_output.argtypes = [vp, C.c_int, C.POINTER(C.c_uint64)]
+    lib.k2j_write_output_at.argtypes = [vp, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64]
     lib.k2j_synchronize.argtypes = [vp]
     lib.k2j_version.restype = C.c_char_p
     _lib = lib
@@ -252,6 +253,10 @@ class K2J:
         n = C.c_uint64()
         self._check(self.lib.k2j_write_output(self.h, fd, C.byref(n)))
         return n.value
+
+    def write_output_at(self, fd: int, file_offset: int, begin: int, n_bytes: int):
+        """Writes bytes [begin, begin + n_bytes) of the text at `file_offset` of `fd` (pwrite)."""
+        self._check(self.lib.k2j_write_output_at(self.h, fd, file_offset, begin, n_bytes))
 
     def synchronize(self):
         self._check(self.lib.k2j_synchronize(self.h))

@@ -865,42 +865,60 @@ k2j_status k2j_copy_output_async(k2j_ctx* c, void* dst, uint64_t cap) {
   return K2J_OK;
 }
 
-k2j_status k2j_write_output(k2j_ctx* c, int fd, uint64_t* written) {
-  if (!c) return K2J_ERR_INVALID_ARGUMENT;
-  if (!c->ran) return fail(c, K2J_ERR_STATE, "no completed run");
-  if (fd < 0) return fail(c, K2J_ERR_INVALID_ARGUMENT, "bad file descriptor");
-  K2J_CUDA(c, cudaSetDevice(c->device));
+// Streams bytes [begin, begin + total) of the output to `fd` in chunks through the two pinned staging buffers: the
+// copy of chunk i overlaps the write of chunk i - 1.  `positioned`: pwrite at file_offset, else write at the
+// descriptor's position.
+static k2j_status stream_output(k2j_ctx* c, int fd, bool positioned, uint64_t file_offset, uint64_t begin, uint64_t total) {
   constexpr size_t kChunk = 16u << 20;
   for (int i = 0; i < 2; i++) {
     if (!c->h_stage[i]) K2J_CUDA(c, cudaMallocHost(&c->h_stage[i], kChunk));
     if (!c->stage_ev[i]) K2J_CUDA(c, cudaEventCreateWithFlags(&c->stage_ev[i], cudaEventDisableTiming));
   }
-  auto write_all = [&](const char* p, size_t n) -> bool {
+  auto write_all = [&](const char* p, size_t n, uint64_t off) -> bool {
     while (n) {
-      const ssize_t w = write(fd, p, n);
+      const ssize_t w = positioned ? pwrite(fd, p, n, (off_t)off) : write(fd, p, n);
       if (w < 0) { if (errno == EINTR) continue; return false; }
-      p += w; n -= (size_t)w;
+      p += w; n -= (size_t)w; off += (uint64_t)w;
     }
     return true;
   };
-  const uint64_t total = c->out_bytes;
   const uint64_t n_chunks = (total + kChunk - 1) / kChunk;
   bool io_ok = true;
   for (uint64_t i = 0; i <= n_chunks; i++) {
     if (i < n_chunks) {  // chunk i starts its way to the host ...
       const size_t len = (size_t)std::min<uint64_t>(kChunk, total - i * kChunk);
-      K2J_CUDA(c, cudaMemcpyAsync(c->h_stage[i & 1], c->out.as<uint8_t>() + i * kChunk, len, cudaMemcpyDeviceToHost, c->stream));
+      K2J_CUDA(c, cudaMemcpyAsync(c->h_stage[i & 1], c->out.as<uint8_t>() + begin + i * kChunk, len, cudaMemcpyDeviceToHost, c->stream));
       K2J_CUDA(c, cudaEventRecord(c->stage_ev[i & 1], c->stream));
     }
     if (i > 0) {         // ... while chunk i - 1, which has arrived, goes to the file
       K2J_CUDA(c, cudaEventSynchronize(c->stage_ev[(i - 1) & 1]));
       const size_t len = (size_t)std::min<uint64_t>(kChunk, total - (i - 1) * kChunk);
-      if (io_ok && !write_all(static_cast<const char*>(c->h_stage[(i - 1) & 1]), len)) io_ok = false;  // keep draining the copies
+      if (io_ok && !write_all(static_cast<const char*>(c->h_stage[(i - 1) & 1]), len, file_offset + (i - 1) * kChunk))
+        io_ok = false;  // keep draining the copies
     }
   }
   if (!io_ok) return fail(c, K2J_ERR_IO, "write: %s", strerror(errno));
-  if (written) *written = total;
   return K2J_OK;
+}
+
+k2j_status k2j_write_output(k2j_ctx* c, int fd, uint64_t* written) {
+  if (!c) return K2J_ERR_INVALID_ARGUMENT;
+  if (!c->ran) return fail(c, K2J_ERR_STATE, "no completed run");
+  if (fd < 0) return fail(c, K2J_ERR_INVALID_ARGUMENT, "bad file descriptor");
+  K2J_CUDA(c, cudaSetDevice(c->device));
+  k2j_status st = stream_output(c, fd, false, 0, 0, c->out_bytes);
+  if (st) return st;
+  if (written) *written = c->out_bytes;
+  return K2J_OK;
+}
+
+k2j_status k2j_write_output_at(k2j_ctx* c, int fd, uint64_t file_offset, uint64_t begin, uint64_t n_bytes) {
+  if (!c) return K2J_ERR_INVALID_ARGUMENT;
+  if (!c->ran) return fail(c, K2J_ERR_STATE, "no completed run");
+  if (fd < 0) return fail(c, K2J_ERR_INVALID_ARGUMENT, "bad file descriptor");
+  if (begin > c->out_bytes || n_bytes > c->out_bytes - begin) return fail(c, K2J_ERR_INVALID_ARGUMENT, "range outside the output");
+  K2J_CUDA(c, cudaSetDevice(c->device));
+  return stream_output(c, fd, true, file_offset, begin, n_bytes);
 }
 
 k2j_status k2j_synchronize(k2j_ctx* c) {

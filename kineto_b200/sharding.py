@@ -58,3 +58,45 @@ def output_bases(out_bytes: int, rank: int, world: int, dist, device):
     dist.all_gather_into_tensor(sizes, mine)
     sizes = sizes.cpu()
     return int(sizes[:rank].sum()), int(sizes.sum())
+
+
+def shared_file_layout(ops_bytes: int, out_bytes: int, rank: int, world: int, dist, device):
+    """Where this shard's text goes in the whole trace's activities text.  The reference writes every CPU-side
+    activity before the first GPU-side one (libkineto/src/output_membuf.h:91-107), and a shard's text is its own
+    CPU-op events followed by its GPU-side events, so a shard has two destinations: its CPU-op events after those
+    of the lower ranks, its GPU-side events after ALL CPU-op events and the lower ranks' GPU-side events.
+    One collective of two numbers per rank.  Returns (ops_offset, gpu_offset, total_bytes); also sums nothing
+    else: counters are reduced by `reduce_counters`."""
+    import torch
+
+    mine = torch.tensor([ops_bytes, out_bytes - ops_bytes], dtype=torch.int64, device=device)
+    sizes = torch.empty(world * 2, dtype=torch.int64, device=device)
+    dist.all_gather_into_tensor(sizes, mine)
+    sizes = sizes.cpu().view(world, 2)
+    all_ops = int(sizes[:, 0].sum())
+    return int(sizes[:rank, 0].sum()), all_ops + int(sizes[:rank, 1].sum()), all_ops + int(sizes[:, 1].sum())
+
+
+def write_shared_file(write_at, fd: int, base: int, ops_bytes: int, out_bytes: int, rank: int, world: int, dist, device):
+    """Every rank writes its two parts into the one file open as `fd` (each rank opens the file itself), the
+    activities text starting at file offset `base`.  `write_at(fd, file_offset, begin, n_bytes)` writes bytes
+    [begin, begin + n_bytes) of the shard's text: `K2J.write_output_at` on a GPU.  Returns the total length of
+    the activities text; the caller adds header and trailer and renames the file."""
+    ops_off, gpu_off, total = shared_file_layout(ops_bytes, out_bytes, rank, world, dist, device)
+    write_at(fd, base + ops_off, 0, ops_bytes)
+    write_at(fd, base + gpu_off, ops_bytes, out_bytes - ops_bytes)
+    return total
+
+
+_COUNTERS = ("x_events", "flow_events", "n_records", "out_of_range_events", "blocklisted_runtime_events",
+             "invalid_external_correlation_events", "unexpected_cuda_events", "out_bytes")
+
+
+def reduce_counters(result: dict, dist, device) -> dict:
+    """Sums the per-shard event and error counts over the ranks (the reference keeps one set per trace:
+    GenericActivityProfiler::ErrorCounts, libkineto/src/GenericActivityProfiler.h:528-535)."""
+    import torch
+
+    t = torch.tensor([int(result[k]) for k in _COUNTERS], dtype=torch.int64, device=device)
+    dist.all_reduce(t)
+    return dict(zip(_COUNTERS, (int(v) for v in t.cpu())))

@@ -37,6 +37,16 @@ def _rank_main(rank, port, tmp):
         shard.g_ops = ops_all.cpu().numpy()
         want, stats = helpers.run_port(shard)
         ok = got == want and res["x_events"] == stats["x_events"] and res["ops_bytes"] == stats["ops_end"]
+        # both ranks stream their two parts into one file (k2j_write_output_at)
+        path = os.path.join(tmp, "whole.json")
+        if rank == 0:
+            open(path, "wb").close()
+        dist.barrier()
+        fd = os.open(path, os.O_WRONLY)
+        total = sharding.write_shared_file(ctx.write_output_at, fd, 0, res["ops_bytes"], res["out_bytes"], rank, WORLD, dist, dev)
+        os.close(fd)
+        np.save(os.path.join(tmp, "part%d.npy" % rank), np.frombuffer(got, np.uint8))
+        open(os.path.join(tmp, "meta%d" % rank), "w").write("%d %d" % (res["ops_bytes"], total))
         alone, _ = helpers.run_port(synth.gen_kernel_launches(N, seed=91, pool_size=500, shard=(rank, WORLD)))
         open(os.path.join(tmp, "ok%d" % rank), "w").write("%d %d" % (int(ok), int(alone != want)))
         dist.barrier()
@@ -54,3 +64,8 @@ def test_two_gpu_ranks_match_checker(tmp_path):
         ok, crosses = open(str(tmp_path / ("ok%d" % r))).read().split()
         assert ok == "1", "rank %d output differs from the checker" % r
         assert crosses == "1"   # the join does reach into the other shard
+    parts = [np.load(str(tmp_path / ("part%d.npy" % r))).tobytes() for r in range(WORLD)]
+    metas = [[int(x) for x in open(str(tmp_path / ("meta%d" % r))).read().split()] for r in range(WORLD)]
+    want = b"".join(p[:m[0]] for p, m in zip(parts, metas)) + b"".join(p[m[0]:] for p, m in zip(parts, metas))
+    assert metas[0][1] == len(want)
+    assert open(str(tmp_path / "whole.json"), "rb").read() == want

@@ -127,6 +127,20 @@ def test_write_output_streams_the_same_bytes(tmp_path):
                 want += text
         assert len(want) > (48 << 20)   # several 16 MiB chunks
         assert open(path, "rb").read() == want
+        # positioned range writes: the text's two halves, second half first, behind a gap
+        ctx.load(synth.gen_kernel_launches(30_000, seed=304, pool_size=200))
+        res = ctx.run()
+        text = ctx.copy_output().tobytes()
+        cut = res["ops_bytes"]
+        p2 = str(tmp_path / "at.json")
+        fd = os.open(p2, os.O_WRONLY | os.O_CREAT)
+        ctx.write_output_at(fd, 100 + cut, cut, len(text) - cut)
+        ctx.write_output_at(fd, 100, 0, cut)
+        ctx.write_output_at(fd, 0, 0, 0)
+        os.close(fd)
+        assert open(p2, "rb").read() == bytes(100) + text
+        with pytest.raises(api.K2JError):
+            ctx.write_output_at(1, 0, len(text), 1)   # range outside the output
         r, w = os.pipe()
         os.close(w); os.close(r)
         ctx.load(cases.edge_trace())

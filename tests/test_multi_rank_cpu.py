@@ -40,6 +40,21 @@ def _rank_main(rank, port, tmp):
     shard.g_ops = ops_all.numpy()
     out, stats = helpers.run_port(shard)
     base, total = sharding.output_bases(len(out), rank, WORLD, dist, "cpu")
+    # both ranks fill one file: CPU-op events of all ranks first, then the GPU-side events
+    path = os.path.join(tmp, "whole.json")
+    if rank == 0:
+        open(path, "wb").write(b"HEAD")
+    dist.barrier()
+    fd = os.open(path, os.O_WRONLY)
+    total2 = sharding.write_shared_file(lambda f, off, b, n: os.pwrite(f, out[b:b + n], off), fd, 4, stats["ops_end"], len(out),
+                                        rank, WORLD, dist, "cpu")
+    os.close(fd)
+    assert total2 == total
+    summed = sharding.reduce_counters(dict(x_events=stats["x_events"], flow_events=stats["flow_events"], n_records=stats["records"],
+                                           out_of_range_events=stats["out_of_range"], blocklisted_runtime_events=0,
+                                           invalid_external_correlation_events=0, unexpected_cuda_events=0, out_bytes=len(out)),
+                                      dist, "cpu")
+    assert summed["out_bytes"] == total and summed["x_events"] == 3 * N * WORLD and summed["n_records"] == 3 * N * WORLD
     np.save(os.path.join(tmp, "out%d.npy" % rank), np.frombuffer(out, np.uint8))
     np.save(os.path.join(tmp, "meta%d.npy" % rank), np.array([stats["ops_end"], base, total, len(out)]))
     dist.barrier()
@@ -66,6 +81,7 @@ def test_two_gloo_ranks_reproduce_the_whole_trace(tmp_path):
     gpu_txt = b"".join(o[int(m[0]):] for o, m in zip(outs, metas))
     assert ops_txt + gpu_txt == want, helpers.first_diff(want, ops_txt + gpu_txt)
     assert int(metas[1][1]) == len(outs[0]) and int(metas[0][2]) == len(outs[0]) + len(outs[1])
+    assert open(str(tmp_path / "whole.json"), "rb").read() == b"HEAD" + want   # the ranks' positioned writes
     # the join really crosses shards: most kernels of shard 0 are linked to ops of shard 1 and vice versa
     alone, _ = helpers.run_port(shards[0])
     assert alone != outs[0]
