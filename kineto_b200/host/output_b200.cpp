@@ -14,6 +14,8 @@
 #include <deque>
 #include <map>
 #include <mutex>
+#include <thread>
+#include <typeinfo>
 
 #include <cuda_runtime_api.h>
 
@@ -178,7 +180,6 @@ struct B200TraceLogger::Impl {
     // logger - its context's device, the CUDA event record it waits on - restated as the records that make the
     // device-side lookups give the same answer.
     std::vector<uint8_t> prefix;
-    std::unordered_map<uint32_t, bool> ctxDeclared;
     // ids of the CPU-side activities of this run: a bitmap for the usual small non-negative ids, a set for the rest
     std::vector<uint64_t> opIdBits;
     std::unordered_set<int32_t> opIdRest;
@@ -202,40 +203,6 @@ struct B200TraceLogger::Impl {
   void text(const std::string& s) {
     flushRun();
     if (out) fwrite(s.data(), 1, s.size(), out);
-  }
-  template <class T> void appendRecord(const T& rec) {
-    const uint8_t* p = reinterpret_cast<const uint8_t*>(&rec);
-    run.cupti.insert(run.cupti.end(), p, p + sizeof(T));
-    run.hasCupti = true;
-  }
-  template <class T> void appendPrefix(const T& rec) {
-    const uint8_t* p = reinterpret_cast<const uint8_t*>(&rec);
-    run.prefix.insert(run.prefix.end(), p, p + sizeof(T));
-  }
-  // The context -> device pair a synchronisation activity was given (contextIdtoDeviceId,
-  // libkineto/src/CuptiActivityProfiler.cpp:527-530), as a memset record that is the context's first writer.
-  void declareContext(uint32_t ctx, uint32_t device) {
-    if (run.ctxDeclared.count(ctx)) return;
-    run.ctxDeclared[ctx] = true;
-    CUpti_ActivityMemsetType m;
-    memset(&m, 0, sizeof m);
-    m.kind = CUPTI_ACTIVITY_KIND_MEMSET;
-    m.contextId = ctx; m.deviceId = device;
-    appendPrefix(m);
-  }
-  void addLink(const libkineto::ITraceActivity& a) {
-    if (!a.linkedActivity()) return;
-    CUpti_ActivityExternalCorrelation e;
-    memset(&e, 0, sizeof e);
-    e.kind = CUPTI_ACTIVITY_KIND_EXTERNAL_CORRELATION;
-    e.externalKind = CUPTI_EXTERNAL_CORRELATION_KIND_CUSTOM0;
-    e.externalId = (uint64_t)a.linkedActivity()->correlationId();
-    e.correlationId = (uint32_t)a.correlationId();
-    appendRecord(e);
-    // an op logged in an earlier run is made joinable again (see flushRun); one of this run keeps its own row, so
-    // that its name and metadata stay reachable from the records linked to it
-    if (!run.hasOp((int32_t)a.linkedActivity()->correlationId()))
-      linkedIds.push_back((int32_t)a.linkedActivity()->correlationId());
   }
   std::vector<int32_t> linkedIds;
   // What ChromeTraceLogger::appendCollectiveMetadata (libkineto/src/output_json.cpp:803-835) keeps for the trailer:
@@ -264,10 +231,46 @@ struct B200TraceLogger::Impl {
     pgMap.insert({pgName, cfg});
   }
 
+  // ---- CUPTI wrappers: gathered as pointers, packed when the run is flushed ----
+  // A wrapper stays alive and in place until the trace is finalised (the reference's own in-memory logger keeps
+  // the same pointers, libkineto/src/output_membuf.h:59-63), so turning wrappers into record bytes can wait for
+  // the flush and be split over threads: each thread packs a contiguous slice into a Piece, and the pieces are
+  // merged in order, which keeps every "first one wins" / "last one wins" rule of the serial order.
+  struct Piece {
+    std::vector<uint8_t> cupti, prefix;
+    std::vector<int32_t> linkedIds;
+    std::vector<const libkineto::ITraceActivity*> collectives;     // linked record_param_comms ops, in order
+    std::vector<int32_t> tidPairs;                                   // first sighting of each thread id, in order
+    std::unordered_map<int32_t, bool> tidSeen;
+    std::vector<uint32_t> rtCbids, drCbids;                          // callback ids met (distinct)
+    std::vector<bool> rtSeen, drSeen;
+    std::unordered_map<const void*, uint32_t> nameIds;               // raw kernel name pointer -> local id
+    std::vector<const void*> namePtrs;
+    std::vector<std::string> names;                                  // demangled, by local id
+    std::vector<uint32_t> kernelOffsets;                             // kernel records in `cupti` (their name field holds a local id)
+    std::unordered_map<uint32_t, bool> ctxDeclared;
+    size_t skipped = 0;
+    std::string firstSkippedName;
+    template <class T> void append(const T& rec) {
+      const uint8_t* q = reinterpret_cast<const uint8_t*>(&rec);
+      cupti.insert(cupti.end(), q, q + sizeof(T));
+    }
+    template <class T> void appendPrefix(const T& rec) {
+      const uint8_t* q = reinterpret_cast<const uint8_t*>(&rec);
+      prefix.insert(prefix.end(), q, q + sizeof(T));
+    }
+  };
+  std::vector<const libkineto::ITraceActivity*> pending;
+  size_t* skippedOut = nullptr;
+  void packOne(const libkineto::ITraceActivity& a, Piece& p) const;
+  void mergePiece(Piece& p);
+  void packPending();
+
   bool flushRun();
 };
 
 bool B200TraceLogger::Impl::flushRun() {
+  packPending();
   Run r;
   std::swap(r, run);
   std::vector<int32_t> links;
@@ -346,6 +349,7 @@ B200TraceLogger::B200TraceLogger(const std::string& traceFileName, int cudaDevic
   impl_->device = cudaDevice;
   impl_->out = fopen(impl_->tempFileName.c_str(), "wb");
   if (!impl_->out) PLOG(ERROR) << "Failed to open '" << impl_->fileName << "'";
+  impl_->skippedOut = &skipped_;
   impl_->ctx = ContextPool::take(cudaDevice);
   if (!impl_->ctx) {
     // No GPU path, and deliberately no CPU path: like ChromeTraceLogger with an unopened file, every
@@ -449,71 +453,110 @@ void B200TraceLogger::handleGenericActivity(const libkineto::GenericTraceActivit
 void B200TraceLogger::handleActivity(const libkineto::ITraceActivity& a) {
   if (!impl_->out) return;
   Impl& m = *impl_;
-  // The activity's type names the one wrapper class worth trying, so a record costs one successful dynamic_cast
-  // instead of a chain of failing ones; anything else is tried as a GenericTraceActivity at the end.
-  const libkineto::ActivityType ty = a.type();
-  const bool cuptiType = ty == ActivityType::CONCURRENT_KERNEL || ty == ActivityType::GPU_MEMCPY || ty == ActivityType::GPU_MEMSET ||
-                         ty == ActivityType::CUDA_RUNTIME || ty == ActivityType::CUDA_DRIVER || ty == ActivityType::OVERHEAD ||
-                         ty == ActivityType::CUDA_SYNC || ty == ActivityType::CUDA_EVENT;
-  if (!cuptiType) {
+  // The wrapper classes of the CUPTI path are gathered and packed at the flush; everything else is tried as a
+  // GenericTraceActivity now (it belongs to the columns of CPU-side activities, which are filled in arrival order).
+  const std::type_info& ti = typeid(a);
+  const bool wrapper = ti == typeid(GpuActivity<CUpti_ActivityKernelType>) || ti == typeid(RuntimeActivity) ||
+                       ti == typeid(GpuActivity<CUpti_ActivityMemcpyType>) || ti == typeid(GpuActivity<CUpti_ActivityMemsetType>) ||
+                       ti == typeid(GpuActivity<CUpti_ActivityMemcpyPtoPType>) || ti == typeid(DriverActivity) ||
+                       ti == typeid(OverheadActivity) || ti == typeid(CudaSyncActivity) || ti == typeid(CudaEventActivity);
+  if (!wrapper) {
     if (auto* g = dynamic_cast<const libkineto::GenericTraceActivity*>(&a)) { handleGenericActivity(*g); return; }
   }
-  Timed timed(m.tRecords);
+  m.pending.push_back(&a);   // classes derived from the wrappers, and foreign classes, are sorted out by packOne
+  m.run.hasCupti = true;
+}
+
+// One wrapper into its piece: the record with converted timestamps, in front of it the EXTERNAL_CORRELATION record
+// that restates linkedActivity(), and the side information the merge needs.  Reads shared state only.
+void B200TraceLogger::Impl::packOne(const libkineto::ITraceActivity& a, Piece& p) const {
+  const libkineto::ActivityType ty = a.type();
   auto convert = [](auto& rec) {  // timestamps as the wrapper reports them (CuptiTimestamp.h:29-51)
     const uint64_t s = rec.start, e = rec.end;
-    rec.start = (uint64_t)convertCuptiTimestamp(s);
-    rec.end = (uint64_t)(convertCuptiTimestamp(s) + convertCuptiDuration(s, e));
+    const int64_t cs = convertCuptiTimestamp(s);
+    rec.start = (uint64_t)cs;
+    rec.end = (uint64_t)(cs + convertCuptiDuration(s, e));
   };
-  auto cbidName = [&](std::vector<uint32_t>& tab, uint32_t cbid, bool driver) {
-    if (cbid >= tab.size()) tab.resize(cbid + 1, m.invalidId);
-    if (tab[cbid] != m.invalidId) return;  // named before
-    tab[cbid] = m.intern(driver ? driverCbidName(cbid) : runtimeCbidName(cbid));
+  auto link = [&]() {
+    const libkineto::ITraceActivity* l = a.linkedActivity();
+    if (!l) return l;
+    CUpti_ActivityExternalCorrelation e;
+    memset(&e, 0, sizeof e);
+    e.kind = CUPTI_ACTIVITY_KIND_EXTERNAL_CORRELATION;
+    e.externalKind = CUPTI_EXTERNAL_CORRELATION_KIND_CUSTOM0;
+    e.externalId = (uint64_t)l->correlationId();
+    e.correlationId = (uint32_t)a.correlationId();
+    p.append(e);
+    // an op logged in an earlier run is made joinable again (see flushRun); one of this run keeps its own row, so
+    // that its name and metadata stay reachable from the records linked to it
+    if (!run.hasOp((int32_t)l->correlationId())) p.linkedIds.push_back((int32_t)l->correlationId());
+    return l;
+  };
+  auto thread = [&](uint32_t tid) {
+    if (p.tidSeen.count((int32_t)tid)) return;
+    p.tidSeen[(int32_t)tid] = true;
+    p.tidPairs.push_back((int32_t)tid); p.tidPairs.push_back((int32_t)a.resourceId());
+  };
+  auto cbid = [](std::vector<uint32_t>& list, std::vector<bool>& seen, uint32_t c) {
+    if (c >= seen.size()) seen.resize(c + 1, false);
+    if (!seen[c]) { seen[c] = true; list.push_back(c); }
+  };
+  auto declare = [&](uint32_t ctx, uint32_t device) {  // contextIdtoDeviceId's answer as the context's first writer
+    if (p.ctxDeclared.count(ctx)) return;
+    p.ctxDeclared[ctx] = true;
+    CUpti_ActivityMemsetType ms;
+    memset(&ms, 0, sizeof ms);
+    ms.kind = CUPTI_ACTIVITY_KIND_MEMSET;
+    ms.contextId = ctx; ms.deviceId = device;
+    p.appendPrefix(ms);
   };
   if (auto* k = ty == ActivityType::CONCURRENT_KERNEL ? dynamic_cast<const GpuActivity<CUpti_ActivityKernelType>*>(&a) : nullptr) {
-    m.addLink(a);
-    if (a.linkedActivity() && a.linkedActivity()->name() == "record_param_comms") m.noteCollective(*a.linkedActivity());
+    const libkineto::ITraceActivity* l = link();
+    if (l && l->name() == "record_param_comms") p.collectives.push_back(l);
     CUpti_ActivityKernelType rec = k->raw();
     convert(rec);
-    auto it = m.kernelNameIds.find(rec.name);
-    uint32_t id = it != m.kernelNameIds.end() ? it->second : (m.kernelNameIds[rec.name] = m.intern(a.name()));
+    auto it = p.nameIds.find(rec.name);
+    uint32_t id;
+    if (it != p.nameIds.end()) id = it->second;
+    else {
+      id = (uint32_t)p.names.size();
+      p.nameIds[rec.name] = id;
+      p.namePtrs.push_back(rec.name);
+      p.names.push_back(a.name());
+    }
     uint64_t id64 = id;
     memcpy(&rec.name, &id64, 8);
-    m.appendRecord(rec);
+    p.kernelOffsets.push_back((uint32_t)p.cupti.size());
+    p.append(rec);
   } else if (auto* c = ty == ActivityType::GPU_MEMCPY ? dynamic_cast<const GpuActivity<CUpti_ActivityMemcpyType>*>(&a) : nullptr) {
-    m.addLink(a);
+    link();
     CUpti_ActivityMemcpyType rec = c->raw();
     convert(rec);
-    m.appendRecord(rec);
+    p.append(rec);
   } else if (auto* c2 = ty == ActivityType::GPU_MEMCPY ? dynamic_cast<const GpuActivity<CUpti_ActivityMemcpyPtoPType>*>(&a) : nullptr) {
-    m.addLink(a);
+    link();
     CUpti_ActivityMemcpyPtoPType rec = c2->raw();
     convert(rec);
-    m.appendRecord(rec);
+    p.append(rec);
   } else if (auto* s = ty == ActivityType::GPU_MEMSET ? dynamic_cast<const GpuActivity<CUpti_ActivityMemsetType>*>(&a) : nullptr) {
-    m.addLink(a);
+    link();
     CUpti_ActivityMemsetType rec = s->raw();
     convert(rec);
-    m.appendRecord(rec);
+    p.append(rec);
   } else if (auto* rt = ty == ActivityType::CUDA_RUNTIME ? dynamic_cast<const RuntimeActivity*>(&a) : nullptr) {
-    m.addLink(a);
+    link();
     CUpti_ActivityAPI rec = rt->raw();
     convert(rec);
-    cbidName(m.rtNames, rec.cbid, false);
-    if (!m.tidSeen.count((int32_t)rec.threadId)) {
-      m.tidSeen[(int32_t)rec.threadId] = true;
-      m.tidPairs.push_back((int32_t)rec.threadId); m.tidPairs.push_back((int32_t)a.resourceId());
-    }
-    m.appendRecord(rec);
+    cbid(p.rtCbids, p.rtSeen, rec.cbid);
+    thread(rec.threadId);
+    p.append(rec);
   } else if (auto* dr = ty == ActivityType::CUDA_DRIVER ? dynamic_cast<const DriverActivity*>(&a) : nullptr) {
-    m.addLink(a);
+    link();
     CUpti_ActivityAPI rec = dr->raw();
     convert(rec);
-    cbidName(m.drNames, rec.cbid, true);
-    if (!m.tidSeen.count((int32_t)rec.threadId)) {
-      m.tidSeen[(int32_t)rec.threadId] = true;
-      m.tidPairs.push_back((int32_t)rec.threadId); m.tidPairs.push_back((int32_t)a.resourceId());
-    }
-    m.appendRecord(rec);
+    cbid(p.drCbids, p.drSeen, rec.cbid);
+    thread(rec.threadId);
+    p.append(rec);
   } else if (auto* ov = ty == ActivityType::OVERHEAD ? dynamic_cast<const OverheadActivity*>(&a) : nullptr) {
     // the wrapper holds the 40-byte prefix of the record (CUpti_ActivityOverhead); the GPU path takes the
     // record as CUPTI writes it today (CUpti_ActivityOverhead3, 56 bytes)
@@ -521,12 +564,12 @@ void B200TraceLogger::handleActivity(const libkineto::ITraceActivity& a) {
     memset(&rec, 0, sizeof rec);
     memcpy(&rec, &ov->raw(), sizeof(CUpti_ActivityOverhead));
     convert(rec);
-    m.appendRecord(rec);
+    p.append(rec);
   } else if (auto* sy = ty == ActivityType::CUDA_SYNC ? dynamic_cast<const CudaSyncActivity*>(&a) : nullptr) {
-    m.addLink(a);
+    link();
     CUpti_ActivitySynchronization rec = sy->raw();
     convert(rec);
-    m.declareContext(rec.contextId, (uint32_t)a.deviceId());
+    declare(rec.contextId, (uint32_t)a.deviceId());
     if (isEventSync(rec.type)) {
       // the CUDA event record the profiler found (CuptiActivityProfiler.cpp:452-461) is only visible as metadata
       MdCollector mc;
@@ -542,25 +585,83 @@ void B200TraceLogger::handleActivity(const libkineto::ITraceActivity& a) {
         ev.kind = CUPTI_ACTIVITY_KIND_CUDA_EVENT;
         ev.correlationId = (uint32_t)srcCorr; ev.contextId = rec.contextId; ev.streamId = (uint32_t)srcStream;
         ev.eventId = rec.cudaEventId;
-        m.appendPrefix(ev);
+        p.appendPrefix(ev);
       }
     }
-    m.appendRecord(rec);
+    p.append(rec);
   } else if (auto* ce = ty == ActivityType::CUDA_EVENT ? dynamic_cast<const CudaEventActivity*>(&a) : nullptr) {
-    m.addLink(a);
+    link();
     CUpti_ActivityCudaEventType rec = ce->raw();
     rec.deviceTimestamp = (uint64_t)convertCuptiTimestamp(rec.deviceTimestamp);
-    m.declareContext(rec.contextId, (uint32_t)a.deviceId());
-    m.appendRecord(rec);
-  } else if (auto* g = cuptiType ? dynamic_cast<const libkineto::GenericTraceActivity*>(&a) : nullptr) {
-    m.tRecords.stop();  // a generic activity that carries one of the CUPTI types
-    handleGenericActivity(*g);
-    m.tRecords.start();
+    declare(rec.contextId, (uint32_t)a.deviceId());
+    p.append(rec);
   } else {
     // Foreign activity classes are not handled by the GPU path; there is no CPU path to fall back to, so they
     // are counted and reported.
-    if (skipped_++ == 0) LOG(ERROR) << "B200TraceLogger: unsupported activity class for '" << a.name() << "'; skipped";
+    if (p.skipped++ == 0) p.firstSkippedName = a.name();
   }
+}
+
+// A piece joins the run: local kernel-name ids become pool ids, first sightings stay first sightings.
+void B200TraceLogger::Impl::mergePiece(Piece& p) {
+  std::vector<uint32_t> global(p.names.size());
+  for (size_t i = 0; i < p.names.size(); i++) {
+    auto it = kernelNameIds.find(p.namePtrs[i]);
+    global[i] = it != kernelNameIds.end() ? it->second : (kernelNameIds[p.namePtrs[i]] = intern(p.names[i]));
+  }
+  for (uint32_t off : p.kernelOffsets) {
+    uint8_t* field = p.cupti.data() + off + offsetof(CUpti_ActivityKernelType, name);
+    uint64_t id;
+    memcpy(&id, field, 8);
+    id = global[(size_t)id];
+    memcpy(field, &id, 8);
+  }
+  run.cupti.insert(run.cupti.end(), p.cupti.begin(), p.cupti.end());
+  run.prefix.insert(run.prefix.end(), p.prefix.begin(), p.prefix.end());
+  linkedIds.insert(linkedIds.end(), p.linkedIds.begin(), p.linkedIds.end());
+  for (const libkineto::ITraceActivity* op : p.collectives) noteCollective(*op);
+  for (size_t i = 0; i + 1 < p.tidPairs.size(); i += 2) {
+    if (tidSeen.count(p.tidPairs[i])) continue;
+    tidSeen[p.tidPairs[i]] = true;
+    tidPairs.push_back(p.tidPairs[i]); tidPairs.push_back(p.tidPairs[i + 1]);
+  }
+  auto names = [&](std::vector<uint32_t>& tab, const std::vector<uint32_t>& cbids, bool driver) {
+    for (uint32_t c : cbids) {
+      if (c >= tab.size()) tab.resize(c + 1, invalidId);
+      if (tab[c] == invalidId) tab[c] = intern(driver ? driverCbidName(c) : runtimeCbidName(c));
+    }
+  };
+  names(rtNames, p.rtCbids, false);
+  names(drNames, p.drCbids, true);
+  if (p.skipped) {
+    if (*skippedOut == 0) LOG(ERROR) << "B200TraceLogger: unsupported activity class for '" << p.firstSkippedName << "'; skipped";
+    *skippedOut += p.skipped;
+  }
+}
+
+void B200TraceLogger::Impl::packPending() {
+  if (pending.empty()) return;
+  Timed timed(tRecords);
+  std::vector<const libkineto::ITraceActivity*> acts;
+  acts.swap(pending);
+  const size_t n = acts.size();
+  const unsigned hw = std::max(1u, std::thread::hardware_concurrency());
+  const size_t nt = n < 50000 ? 1 : std::min<size_t>({(size_t)hw, (size_t)8, n / 25000});
+  std::vector<Piece> pieces(nt);
+  auto work = [&](size_t t) {
+    const size_t lo = n * t / nt, hi = n * (t + 1) / nt;
+    Piece& p = pieces[t];
+    p.cupti.reserve((hi - lo) * 160);
+    for (size_t i = lo; i < hi; i++) packOne(*acts[i], p);
+  };
+  if (nt == 1) work(0);
+  else {
+    std::vector<std::thread> threads;
+    for (size_t t = 1; t < nt; t++) threads.emplace_back(work, t);
+    work(0);
+    for (auto& th : threads) th.join();
+  }
+  for (Piece& p : pieces) mergePiece(p);
 }
 
 void B200TraceLogger::finalizeTrace(const Config&, std::unique_ptr<ActivityBuffers> /*buffers*/, int64_t endTime) {

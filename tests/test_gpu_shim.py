@@ -27,7 +27,12 @@ SHIM = os.path.join(helpers.ROOT, "oracle", "_ref", "shim_driver")
     lambda: cases.collective_trace(300, seed=55),
     lambda: cases.without_flags(synth.gen_distributed_rank(5000, rank=1, seed=403, pool_size=100)),
     cases.instant_trace,
-], ids=["launches_annot", "mixed", "edge", "annotations", "tsc", "sync", "sync_mix", "collectives", "distributed_rank", "instant"])
+    # more than 50 000 wrappers: the logger packs them on several threads and merges the pieces in order
+    lambda: synth.gen_mixed(150_000, seed=404, pool_size=800, escape_fraction=0.05),
+    lambda: cases.sync_mix_trace(90_000, seed=49),
+    lambda: cases.without_flags(synth.gen_distributed_rank(60_000, rank=3, seed=405, pool_size=300)),
+], ids=["launches_annot", "mixed", "edge", "annotations", "tsc", "sync", "sync_mix", "collectives", "distributed_rank", "instant",
+        "mixed_threads", "sync_mix_threads", "distributed_rank_threads"])
 def test_logger_shim_writes_the_reference_file(gen, tmp_path):
     trace = gen()
     p = str(tmp_path / "t.k2jt")
