@@ -70,7 +70,7 @@ struct k2j_ctx {
   DevBuf ds_tab, span_key, span_nstart, span_end, span_nfirst, span_row, span_out, span_cnt, ann_size, ann_off;
   DevBuf sort_keys[2], sort_vals[2], sort_hist, sort_base, sort_rank;
   DevBuf tid_tab, corr_tab, user_tab, op_tab, work_slot, work_ev, ev_size, ev_off, ev_ext, out, counters;
-  uint64_t* h_totals = nullptr;   // pinned, 32 words: [0, C_NCOL) column totals, 20 text bytes, 21 bytes of CPU-op text, 22 annotation bytes, 23 sort, 24 scan entry point, 25 the record_param_comms flag
+  uint64_t* h_totals = nullptr;   // pinned, 32 words: [0, C_NCOL) column totals, 20 text bytes, 21 bytes of CPU-op text, 22 annotation bytes, 23 sort, 24 scan entry point, 25 the record_param_comms flag, 26 kernel events with collective metadata
   Counters* h_counters = nullptr; // pinned
   void* h_stage[2] = {nullptr, nullptr};            // pinned staging buffers of k2j_write_output
   cudaEvent_t stage_ev[2] = {nullptr, nullptr};
@@ -82,7 +82,7 @@ struct k2j_ctx {
   uint32_t launches = 0;
   DevBuf ext_local;
   DevBuf ctx_tab, evt_recs, seen_tab, row_key, row_first, corr_zero;  // synchronisation records
-  DevBuf str_class, comms_flag;                                       // collective enrichment
+  DevBuf str_class, comms_flag, coll_list;                            // collective enrichment
   const void* g_ext = nullptr; uint64_t g_n_ext = 0, g_own_begin = 0;
   const int32_t* g_op_ids = nullptr; uint64_t g_n_ops = 0;
 };
@@ -316,7 +316,7 @@ void k2j_destroy(k2j_ctx* c) {
                     &c->span_out, &c->span_cnt, &c->ann_size, &c->ann_off, &c->sort_keys[0], &c->sort_keys[1], &c->sort_vals[0],
                     &c->sort_vals[1], &c->sort_hist, &c->sort_base, &c->sort_rank, &c->tid_tab, &c->corr_tab, &c->user_tab, &c->op_tab,
                     &c->work_slot, &c->work_ev, &c->ev_size, &c->ev_off, &c->ev_ext, &c->out, &c->counters, &c->ext_local, &c->ctx_tab, &c->evt_recs,
-                    &c->seen_tab, &c->row_key, &c->row_first, &c->corr_zero, &c->str_class, &c->comms_flag})
+                    &c->seen_tab, &c->row_key, &c->row_first, &c->corr_zero, &c->str_class, &c->comms_flag, &c->coll_list})
     b->release();
   if (c->h_totals) cudaFreeHost(c->h_totals);
   if (c->h_counters) cudaFreeHost(c->h_counters);
@@ -673,6 +673,12 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
     c->launches++;
     d.has_comms = c->comms_flag.as<uint32_t>();
   }
+  d.work_indirect = nullptr; d.n_indirect = 0; d.coll_list = nullptr;
+  K2J_CUDA(c, cudaMemsetAsync(&d.counters->n_coll, 0, sizeof(unsigned long long), s));  // the list below starts empty
+  if (d.has_comms && !c->have_global_join && totals[C_KERNEL]) {
+    K2J_CUDA(c, c->coll_list.reserve(totals[C_KERNEL] * 4));
+    d.coll_list = c->coll_list.as<uint32_t>();
+  }
   // synchronisation and CUDA event records: their lookup structures exist only when such records do
   d.ctx_tab = nullptr; d.evt = nullptr; d.n_evt = 0; d.seen_tab = nullptr; d.row_key = nullptr; d.row_first = nullptr; d.corr_zero = nullptr;
   d.work_origin = 0; d.wait_pass = 0;
@@ -742,6 +748,8 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
       K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 21, c->ev_off.as<uint64_t>() + c->n_ops, 8, cudaMemcpyDeviceToHost, s));
     c->h_totals[25] = 0;
     if (d.has_comms) K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 25, d.has_comms, 4, cudaMemcpyDeviceToHost, s));
+    c->h_totals[26] = 0;
+    if (d.coll_list) K2J_CUDA(c, cudaMemcpyAsync(c->h_totals + 26, &d.counters->n_coll, 8, cudaMemcpyDeviceToHost, s));
     K2J_CUDA(c, cudaEventRecord(c->ev[4], s));
     K2J_CUDA(c, cudaStreamSynchronize(s));
     total_bytes = c->h_totals[20];
@@ -760,13 +768,12 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
       k_events<true, true><<<(uint32_t)((di.n_work - di.work_origin + kEventThreads - 1) / kEventThreads), kEventThreads, 0, s>>>(di);
       c->launches++;
     }
-    if (total_bytes && (c->h_totals[25] & 1) && totals[C_KERNEL]) {
-      // kernel events that carry collective metadata: a launch of their own over the kernel records, so that the
-      // launch above holds no code for them
+    if (total_bytes && c->h_totals[26] != 0) {
+      // kernel events that carry collective metadata: a launch of their own over the work items the size pass
+      // listed, so that the launch above holds no code for them
       Dev dk = d;
-      dk.work_origin = d.cls_begin[C_KERNEL];
-      dk.n_work = d.cls_begin[C_KERNEL] + ((totals[C_KERNEL] + 31) & ~31ull);
-      k_events<true, true><<<(uint32_t)((dk.n_work - dk.work_origin + kEventThreads - 1) / kEventThreads), kEventThreads, 0, s>>>(dk);
+      dk.work_indirect = d.coll_list; dk.n_indirect = c->h_totals[26];
+      k_events<true, true><<<(uint32_t)((dk.n_indirect + kEventThreads - 1) / kEventThreads), kEventThreads, 0, s>>>(dk);
       c->launches++;
     }
     if (ann_bytes) {

@@ -88,7 +88,7 @@ struct DevProps {
 
 struct Counters {
   unsigned long long x_events, flow_events, out_of_range, blocklisted_runtime, invalid_external_correlation,
-      unexpected, name_bytes, device_check, n_user;
+      unexpected, name_bytes, device_check, n_user, n_coll;
 };
 
 struct MdEntry { uint32_t key, type; uint64_t value; };
@@ -142,6 +142,8 @@ struct Dev {
   uint32_t* work_slot; uint32_t* work_ev; uint64_t cls_begin[C_NCLASS]; uint64_t cls_count[C_NCLASS];
   uint64_t ops_begin; uint64_t n_work;
   uint64_t work_origin;    // first work item of this launch (0, or the first deferred synchronisation record)
+  const uint32_t* work_indirect; uint64_t n_indirect;  // this launch handles the listed work items only (nullptr: a range)
+  uint32_t* coll_list;     // work items of the kernel events that carry collective metadata, appended by the size pass
   int32_t wait_pass;       // size pass over the deferred synchronisation records only
   uint64_t wait_ev_base;   // event number of the first deferred synchronisation record
   // synchronisation records: context -> first record naming it, CUDA event records sorted by (context, event,
@@ -1252,7 +1254,7 @@ __device__ __forceinline__ bool linked_op_full(const Dev& d, uint32_t corr, int3
   return false;
 }
 
-struct Tally { uint32_t x, flow; unsigned long long name_bytes; uint64_t ev; };
+struct Tally { uint32_t x, flow; unsigned long long name_bytes; uint64_t ev; uint64_t work; };
 
 // A thread's area in shared memory: the staged record plus value slots (see the S_ offsets above).
 constexpr int kRecStride = 23;              // 8-byte units per thread: 22 for the part of the longest record (Kernel9) that
@@ -1410,7 +1412,10 @@ __device__ __forceinline__ uint64_t gather_kernel(const Dev& d, uint32_t* a, Tal
   else if (d.has_comms != nullptr && (*d.has_comms & 1u) != 0u) {
     // a kernel launched by a record_param_comms op carries that op's collective metadata (output_json.cpp:900-906)
     const uint32_t row = tab_find(d.op_tab, d.op_mask, (uint32_t)ext);
-    if (row < d.n_ops && d.op_name[row] < d.n_strings && d.str_class[d.op_name[row]] == 1u) { p |= 1ull << K_COLL; s32(a, KS_COLLROW, row); }
+    if (row < d.n_ops && d.op_name[row] < d.n_strings && d.str_class[d.op_name[row]] == 1u) {
+      p |= 1ull << K_COLL; s32(a, KS_COLLROW, row);
+      if (counting && d.coll_list != nullptr) d.coll_list[atomicAdd(&d.counters->n_coll, 1ull)] = (uint32_t)t.work;  // for the extra emit launch
+    }
   }
   t.x++;
   if (corr > 0) t.flow++;
@@ -1642,9 +1647,12 @@ __device__ __forceinline__ void coll_text(const Dev& d, uint32_t id, bool strip,
 }
 // Bit k set: key k is written.  Numbers and booleans are never empty; a string is empty when nothing is left of it.
 // The first five keys are written together or not at all, and so are the two split sizes.
-__device__ __forceinline__ uint32_t coll_mask(const Dev& d, uint32_t row) {
+// *ents: four bits per key, the entry's position among the op's entries (15: look it up again).
+__device__ __forceinline__ uint32_t coll_mask(const Dev& d, uint32_t row, uint64_t* ents) {
   uint32_t mask = 0;
-  for (uint32_t e = d.op_mdoff[row], m1 = d.op_mdoff[row + 1]; e < m1; e++) {
+  uint64_t packed = 0;
+  const uint32_t e0 = d.op_mdoff[row];
+  for (uint32_t e = e0, m1 = d.op_mdoff[row + 1]; e < m1; e++) {
     const MdEntry md = d.md[e];
     const uint32_t cls = md.key < d.n_strings ? d.str_class[md.key] : 0u;
     if (cls < 2u) continue;
@@ -1652,7 +1660,10 @@ __device__ __forceinline__ uint32_t coll_mask(const Dev& d, uint32_t row) {
     bool nonempty = true;
     if (md.type >= 4u) { uint64_t b, e2; coll_text(d, (uint32_t)md.value, (kCollStrip >> k) & 1u, &b, &e2); nonempty = e2 > b; }
     mask = nonempty ? (mask | (1u << k)) : (mask & ~(1u << k));
+    const uint64_t pos = e - e0 < 15u ? e - e0 : 15u;
+    packed = (packed & ~(15ull << (4 * k))) | (pos << (4 * k));
   }
+  *ents = packed;
   if ((mask & 0x1Fu) != 0x1Fu) mask &= ~0x1Fu;
   if ((mask & 0x180u) != 0x180u) mask &= ~0x180u;
   return mask;
@@ -1668,11 +1679,12 @@ __device__ __forceinline__ void put_value(S& s, const Dev& d, int type, uint64_t
   // Two field types loop over the entries of a CPU-side activity: its own metadata (T_MD) and the collective keys
   // copied onto a kernel (T_COLL).  Every other type takes the switch once.
   uint32_t e = 0, m1 = 0, m0 = 0, cmask = 0;
+  uint64_t cents = 0;
   const bool coll = COLL && type == T_COLL, raw_md = COLL && type == T_MDRAW;
   const bool md_mode = type == T_MD || coll || raw_md;
   if (md_mode) {
     if (!coll) { m0 = e = d.op_mdoff[v]; m1 = d.op_mdoff[v + 1]; if (e >= m1) return; }
-    else { m0 = (uint32_t)v; cmask = coll_mask(d, m0); if (!cmask) return; }
+    else { m0 = (uint32_t)v; cmask = coll_mask(d, m0, &cents); if (!cmask) return; m1 = d.op_mdoff[m0]; }
   }
   bool more = false, close_quote = false;
   do {
@@ -1692,7 +1704,8 @@ __device__ __forceinline__ void put_value(S& s, const Dev& d, int type, uint64_t
       } else {  // the next collective key: its literal, then the op's value through the formatters below
         const uint32_t k = (uint32_t)__ffs((int)cmask) - 1u;
         cmask &= cmask - 1u;
-        const MdEntry md = d.md[coll_entry(d, m0, k)];
+        const uint32_t pos = (uint32_t)(cents >> (4 * k)) & 15u;
+        const MdEntry md = d.md[pos < 15u ? m1 + pos : coll_entry(d, m0, k)];
         const FieldDesc cs = g_fields.f[CSTR_BASE + CS_COLL + k];
         s.words(g_fields.w + cs.off, cs.len);
         close_quote = (kCollStrip >> k) & 1u;
@@ -1848,8 +1861,9 @@ __global__ void __launch_bounds__(kEventThreads, 8) k_events(Dev d) {
     if (threadIdx.x < 8) s_cnt[threadIdx.x] = 0;
     __syncthreads();
   }
-  const uint64_t i = d.work_origin + (uint64_t)blockIdx.x * kEventThreads + threadIdx.x;
-  Tally t; t.x = 0; t.flow = 0; t.name_bytes = 0; t.ev = 0;
+  uint64_t i = d.work_origin + (uint64_t)blockIdx.x * kEventThreads + threadIdx.x;
+  if (d.work_indirect != nullptr) i = i < d.n_indirect ? (uint64_t)d.work_indirect[i] : d.n_work;
+  Tally t; t.x = 0; t.flow = 0; t.name_bytes = 0; t.ev = 0; t.work = i;
   uint32_t filt = 0;
   int cls = -1;
   uint64_t j = 0;
