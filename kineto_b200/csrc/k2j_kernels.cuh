@@ -579,9 +579,13 @@ __global__ void k_find_comms(Dev d, uint32_t* flag, int comms_on) {
 // CPU-op id -> position (last writer wins): activityMap_[id] = op, GenericActivityProfiler.cpp:262.
 __global__ void k_build_ops(Dev d) {
   const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= d.n_join_ops) return;
-  const uint32_t id = (uint32_t)d.join_op_ids[i];
-  if (d.need_op != nullptr && !bit_test(d.need_op, d.need_op_mask, id)) return;
+  const bool in = i < d.n_join_ops;
+  const uint32_t id = in ? (uint32_t)d.join_op_ids[i] : 0u;
+  const bool valid = in && (d.need_op == nullptr || bit_test(d.need_op, d.need_op_mask, id));
+  // Ids repeat (every memory event of a PyTorch trace carries id 0): of the lanes of a warp that hold one id only the
+  // last, which is the one that must win, goes to the table, so a run of equal ids costs one atomic per warp.
+  const uint32_t peers = __match_any_sync(0xffffffffu, id) & __ballot_sync(0xffffffffu, valid);
+  if (!valid || (threadIdx.x & 31u) != 31u - (uint32_t)__clz((int)peers)) return;
   if (!tab_insert(d.op_tab, d.op_mask, id, (uint32_t)i)) atomicAdd(&d.counters->device_check, 1ull);
 }
 // correlation id -> index of the winning EXTERNAL_CORRELATION record (handleCorrelationActivity,
