@@ -152,6 +152,18 @@ def test_write_output_streams_the_same_bytes(tmp_path):
         ctx.close()
 
 
+def test_measure_module_runs():
+    """python -m kineto_b200.measure: one JSON line with stage times for another workload."""
+    import json
+    import subprocess
+    import sys
+    r = subprocess.run([sys.executable, "-m", "kineto_b200.measure", "--workload", "distributed_rank", "--n", "20000", "--runs", "2"],
+                       capture_output=True, text=True, cwd=helpers.ROOT)
+    assert r.returncode == 0, r.stderr[-1000:]
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["records"] == 80_000 and line["ms_emit"] > 0 and line["out_bytes"] > 10_000_000
+
+
 def test_empty_and_degenerate_inputs():
     from kineto_b200 import api
     b = synth.TraceBuilder()
