@@ -1735,7 +1735,12 @@ __device__ __forceinline__ void put_value(S& s, const Dev& d, int type, uint64_t
         }
         break;
       }
-      case T_DBL: put_dbl(s, __longlong_as_double((long long)v)); break;
+      case T_DBL: {
+        const double x = __longlong_as_double((long long)v);
+        // a collective value is the plain text of the number ("inf", "-nan"), not the JSON visitor's quoted form
+        if (COLL && coll && !double_is_finite(x)) put_nonfinite(s, x); else put_dbl(s, x);
+        break;
+      }
       case T_NAME: put_name(s, d, (uint32_t)v, name_bytes); break;
       case T_CSTR: { const FieldDesc cs = g_fields.f[CSTR_BASE + (uint32_t)v]; s.words(g_fields.w + cs.off, cs.len); break; }
       case T_BOOL: if (v) s.put4(0x65757274u); else s.put64(0x65736C6166ull, 5); break;  // true / false

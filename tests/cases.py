@@ -305,6 +305,9 @@ def collective_trace(n=40, seed=51) -> tf.Trace:
             md = [m for m in md if m[0] != "dtype"] + [("dtype", S, '""')]   # a quoted empty string counts as absent
         if i % 13 == 6:
             md += [("Dst Rank", D, 2.5), ("Src Rank", B, 1)] if i % 7 != 2 else []
+        if i % 17 == 8:   # non-finite doubles print as plain text here ("inf", "-nan"), quoted only where the key is
+            md = [m for m in md if m[0] not in ("Seq", "Comms Id", "Process Group Name")] + [
+                ("Seq", D, float("inf")), ("Comms Id", D, -float("nan")), ("Process Group Name", D, -float("inf"))]
         while len({m[0] for m in md}) > 13:   # one bucket generation of the reference's metadata map
             md.pop()
         b.op(t0 + 1000 * i, t0 + 1000 * i + 800, 100 + i, "record_param_comms", md=md)
