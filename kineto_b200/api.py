@@ -13,7 +13,7 @@ import numpy as np
 from . import tracefile as tf
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libk2j.so")
+LIB_PATH = os.environ.get("K2J_LIBRARY") or os.path.join(_HERE, "libk2j.so")  # K2J_LIBRARY: another build of the same ABI
 
 STATUS = {0: "OK", 1: "INVALID_ARGUMENT", 2: "CUDA", 3: "UNSUPPORTED", 4: "STATE", 5: "DEVICE_CHECK"}
 

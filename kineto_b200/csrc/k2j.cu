@@ -297,6 +297,9 @@ k2j_status k2j_create(int device, void* stream, k2j_ctx** out) {
             cudaMallocHost((void**)&c->h_counters, sizeof(Counters)) == cudaSuccess &&
             c->counters.reserve(sizeof(Counters)) == cudaSuccess && c->scan_totals.reserve(32 * 8) == cudaSuccess;
   for (auto& e : c->ev) ok = ok && cudaEventCreate(&e) == cudaSuccess;
+  // the emit kernels' shared memory (record areas + output windows) is above the 48 KiB that needs no opt-in
+  ok = ok && cudaFuncSetAttribute(k_events<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)events_smem_bytes(true)) == cudaSuccess &&
+       cudaFuncSetAttribute(k_events<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)events_smem_bytes(true)) == cudaSuccess;
   if (!ok) { k2j_destroy(c); return K2J_ERR_CUDA; }
   *out = c;
   return K2J_OK;
@@ -730,13 +733,13 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
   uint32_t n_spans = 0;
   if (d.n_work) {
     const uint32_t ev_blocks = (uint32_t)((d.n_work + kEventThreads - 1) / kEventThreads);
-    k_events<false><<<ev_blocks, kEventThreads, 0, s>>>(d);
+    k_events<false><<<ev_blocks, kEventThreads, events_smem_bytes(false), s>>>(d);
     c->launches++;
     if (totals[C_WAIT]) {  // deferred synchronisation records: sized once every stream with GPU work is known
       Dev dw = d;
       dw.wait_pass = 1; dw.work_origin = d.cls_begin[C_WAIT];
       dw.n_work = d.cls_begin[C_WAIT] + ((totals[C_WAIT] + 31) & ~31ull);
-      k_events<false><<<(uint32_t)((dw.n_work - dw.work_origin + kEventThreads - 1) / kEventThreads), kEventThreads, 0, s>>>(dw);
+      k_events<false><<<(uint32_t)((dw.n_work - dw.work_origin + kEventThreads - 1) / kEventThreads), kEventThreads, events_smem_bytes(false), s>>>(dw);
       c->launches++;
     }
     K2J_CUDA(c, cudaGetLastError());
@@ -760,12 +763,12 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
     K2J_CUDA(c, c->out.reserve(total_bytes + ann_bytes + 64));
     d.out = c->out.as<uint8_t>(); d.out_cap = total_bytes + ann_bytes;
     K2J_CUDA(c, cudaEventRecord(c->ev[7], s));
-    if (total_bytes) { k_events<true><<<ev_blocks, kEventThreads, 0, s>>>(d); c->launches++; }
+    if (total_bytes) { k_events<true><<<ev_blocks, kEventThreads, events_smem_bytes(true), s>>>(d); c->launches++; }
     if (total_bytes && (c->h_totals[25] & 2) && c->n_ops) {
       // instant events: the same extra launch over the CPU-side activities
       Dev di = d;
       di.work_origin = d.ops_begin;
-      k_events<true, true><<<(uint32_t)((di.n_work - di.work_origin + kEventThreads - 1) / kEventThreads), kEventThreads, 0, s>>>(di);
+      k_events<true, true><<<(uint32_t)((di.n_work - di.work_origin + kEventThreads - 1) / kEventThreads), kEventThreads, events_smem_bytes(true), s>>>(di);
       c->launches++;
     }
     if (total_bytes && c->h_totals[26] != 0) {
@@ -773,7 +776,7 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
       // listed, so that the launch above holds no code for them
       Dev dk = d;
       dk.work_indirect = d.coll_list; dk.n_indirect = c->h_totals[26];
-      k_events<true, true><<<(uint32_t)((dk.n_indirect + kEventThreads - 1) / kEventThreads), kEventThreads, 0, s>>>(dk);
+      k_events<true, true><<<(uint32_t)((dk.n_indirect + kEventThreads - 1) / kEventThreads), kEventThreads, events_smem_bytes(true), s>>>(dk);
       c->launches++;
     }
     if (ann_bytes) {

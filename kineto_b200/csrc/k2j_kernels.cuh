@@ -21,6 +21,7 @@
 #include <stdint.h>
 
 #include "k2j_format.cuh"
+#include "k2j_sink.cuh"
 
 namespace k2j {
 
@@ -671,108 +672,12 @@ __global__ void __launch_bounds__(kScanThreads) k_scan_apply(const uint32_t* in,
   for (int k = 0; k < kScanItems; k++) { const uint64_t i = base + k; if (i < n) dst[i] = ex; ex += v[k]; }
 }
 
-// ---- output sink: 32-byte stores straight to the final position, no branches ---------------------------
-// Bytes are gathered in a 64-bit shift register.  A completed 8-byte word that belongs to a 32-byte
-// block lying wholly inside the event is parked in shared memory; the block's fourth word leaves
-// together with the three parked ones as one 256-bit store (a full DRAM sector, so the L2 never has
-// to fetch the rest of a sector).  Words of the event's first and last (partial) block leave as 8-byte
-// stores.  Everything is predicated: lanes whose word is not complete simply skip the store.
-// The two 8-byte words an event may share with its neighbours are written without knowing the
-// neighbour's bytes: every event begins with "\n  {\n   " and ends with "\n  },", so the neighbour's (at
-// most three) bytes inside a shared 4-byte half are known constants, and a half that belongs wholly to
-// the neighbour is not touched.  Both owners write a shared half with the same bytes.
-constexpr uint64_t kEventHead8 = 0x2020200A7B20200Aull;  // "\n  {\n   "  first 8 bytes of every event
-constexpr uint64_t kEventTail8 = 0x2C7D20200A000000ull;  // "\n  },"      last 5 bytes of every event, in the top bytes
-constexpr uint32_t kMinEventBytes = 16;
-
-struct GlobalSink {
-  static constexpr bool kCounting = false;
-  static constexpr int kParkStride = 128;  // = threads per block of the kernels that use the sink
-  uint64_t lo; uint32_t sh;
-  uint32_t wo;            // byte offset (from base) of the 8-byte word being filled
-  uint32_t w0;            // offset of the event's first word (0, 8, 16 or 24)
-  uint32_t c32, lim32;    // blocks lying wholly inside the event: 0 <= offset - c32 < lim32
-  uint8_t* base;          // 32-byte aligned
-  uint64_t* park;         // this thread's column of the parking area: word k of the open block at park[k * kParkStride]
-  __device__ __forceinline__ void init(uint8_t* dst, uint32_t size, uint64_t* park_column) {
-    const uint32_t phase32 = (uint32_t)(reinterpret_cast<uintptr_t>(dst) & 31u), phase = phase32 & 7u;
-    base = dst - phase32; sh = 8u * phase; lo = 0; park = park_column;
-    wo = w0 = phase32 & ~7u;
-    c32 = phase32 ? 32u : 0u;
-    const uint32_t last_blk = (phase32 + size) & ~31u;
-    lim32 = last_blk > c32 ? last_blk - c32 : 0u;
-    const uint64_t w = ((kEventTail8 >> 1) >> (63u - sh)) | (kEventHead8 << sh);
-    if (phase < 4u) *reinterpret_cast<uint64_t*>(base + wo) = w;
-    else *reinterpret_cast<uint32_t*>(base + wo + 4) = (uint32_t)(w >> 32);
-  }
-  // The fourth word of a block is complete.  Normally the block lies inside the event and leaves as one
-  // 256-bit store; the event's first block, when the event starts inside it, leaves word by word
-  // (its first word was written by init).
-  __device__ __forceinline__ void block_out(uint64_t t) {
-    if ((wo - c32) < lim32) {
-      const uint64_t a = park[0], b = park[kParkStride], c = park[2 * kParkStride];
-      asm volatile("st.global.v4.b64 [%0], {%1, %2, %3, %4};" ::"l"(base + (wo & ~31u)), "l"(a), "l"(b), "l"(c), "l"(t) : "memory");
-    } else {
-      for (uint32_t o = w0 + 8u; o < 24u + 8u; o += 8u)
-        *reinterpret_cast<uint64_t*>(base + (wo & ~31u) + o) = o == 24u ? t : park[(o >> 3) * kParkStride];
-    }
-  }
-  // a completed word `t` at offset `wo`; `on`: this lane really has one
-  __device__ __forceinline__ void word_out(uint64_t t, bool on) {
-    const uint32_t k = (wo >> 3) & 3u;
-    if (on && k != 3u) park[k * kParkStride] = t;
-    if (on && k == 3u) block_out(t);
-  }
-  __device__ __forceinline__ void put8w(uint64_t w) {  // append 8 bytes
-    word_out(lo | (w << sh), true);
-    lo = (w >> 1) >> (63u - sh);
-    wo += 8u;
-  }
-  // append the low `len` (0..8) bytes of w; bytes above len must be zero
-  __device__ __forceinline__ void put64(uint64_t w, uint32_t len) {
-    const uint64_t t = lo | (w << sh);
-    const uint32_t s2 = sh + 8u * len;
-    const bool full = s2 >= 64u;
-    word_out(t, full);
-    lo = full ? ((w >> 1) >> (63u - sh)) : t;
-    wo += full ? 8u : 0u;
-    sh = s2 & 63u;
-  }
-  __device__ __forceinline__ void put(uint32_t w, int len) { put64((uint64_t)w, (uint32_t)len); }
-  __device__ __forceinline__ void put4(uint32_t w) { put64((uint64_t)w, 4u); }
-  __device__ __forceinline__ void skip(uint32_t) {}
-  template <int N> __device__ __forceinline__ void lit(const Lit<N>& l) {
-#pragma unroll
-    for (int i = 0; i < N / 4; i++) put4(l.w[i]);
-    if (N % 4) put(l.w[N / 4], N % 4);
-  }
-  // `len` bytes from an 8-byte aligned word array; reads one word past the last one it needs
-  __device__ __forceinline__ void words(const uint64_t* w, uint32_t len) {
-    const uint32_t nw = len >> 3;
-    uint64_t nxt = w[0];
-    for (uint32_t i = 0; i < nw; i++) { const uint64_t cur = nxt; nxt = w[i + 1]; put8w(cur); }
-    const uint32_t rem = len & 7u;
-    if (rem) put64(nxt & (~0ull >> (8u * (8u - rem))), rem);
-  }
-  // Writes what is left: the complete words of the open (last) block, then the word holding the event's
-  // end.  Returns false if the byte count differs from the size the event was given.
-  __device__ __forceinline__ bool finish(const uint8_t* dst, uint32_t size) {
-    const uint32_t blk = wo & ~31u;
-    for (uint32_t o = blk == 0u ? w0 + 8u : blk; o < wo; o += 8u)   // the event's very first word was written by init
-      *reinterpret_cast<uint64_t*>(base + o) = park[((o >> 3) & 3u) * kParkStride];
-    const uint32_t e = sh >> 3;
-    if (e) {
-      const uint64_t t = lo | (0x20200Aull << sh);  // the next event begins "\n  "
-      if (e > 4u) *reinterpret_cast<uint64_t*>(base + wo) = t;
-      else *reinterpret_cast<uint32_t*>(base + wo) = (uint32_t)t;
-    }
-    return wo + e == (uint32_t)(reinterpret_cast<uintptr_t>(dst) & 31u) + size;
-  }
-};
 struct CountSink2 : CountSink {
   __device__ __forceinline__ void put4(uint32_t) { n += 4; }
   __device__ __forceinline__ void put64(uint64_t, uint32_t len) { n += len; }
   __device__ __forceinline__ void words(const uint64_t*, uint32_t len) { n += len; }
+  __device__ __forceinline__ void bytes(const uint8_t*, uint32_t len) { n += len; }
+  __device__ __forceinline__ void ensure(uint32_t) {}
 };
 
 // ---- event programs ------------------------------------------------------------------------------------
@@ -1677,7 +1582,9 @@ __device__ __forceinline__ uint32_t coll_mask(const Dev& d, uint32_t row, uint64
 // entries of the op (JsonTypedMetadataVisitor, libkineto/include/TypedMetadataJson.h:72-158): each entry
 // is mapped onto one of the value types, so the kernel holds one copy of every formatter.
 enum : int { T_BOOL = 8, T_MDSTR, T_QMDSTR };
-template <class S, bool COLL = true>
+// ENSURE = false: the caller has asked the sink for room for a number; fields that loop over entries or copy
+// strings still ask for themselves.
+template <class S, bool COLL = true, bool ENSURE = true>
 __device__ __forceinline__ void put_value(S& s, const Dev& d, int type, uint64_t v, unsigned long long* name_bytes) {
   if (type == T_NONE) return;
   // Two field types loop over the entries of a CPU-side activity: its own metadata (T_MD) and the collective keys
@@ -1692,13 +1599,14 @@ __device__ __forceinline__ void put_value(S& s, const Dev& d, int type, uint64_t
   }
   bool more = false, close_quote = false;
   do {
+    if (ENSURE || md_mode) s.ensure(48);  // a number takes at most 24 bytes; quotes and separators around it come out of the sink's slack
     if (md_mode) {
       if (!coll) {
         close_quote = false;
         const MdEntry md = d.md[e];
         if (e > m0) s.put(0x202Cu, 2);  // ", "
         put_char(s, '"');
-        if (raw_md) { uint64_t b, e2; coll_text(d, md.key, false, &b, &e2); for (uint64_t i = b; i < e2; i++) put_char(s, (char)d.pool_data[i]); }
+        if (raw_md) { uint64_t b, e2; coll_text(d, md.key, false, &b, &e2); s.bytes(d.pool_data + b, (uint32_t)(e2 - b)); }
         else put_mdstr(s, d, md.key);
         s.put(0x203A22u, 3);  // "\": "
         v = md.value;
@@ -1749,7 +1657,7 @@ __device__ __forceinline__ void put_value(S& s, const Dev& d, int type, uint64_t
         if (COLL && type >= T_RAWSTR) {
           uint64_t b, e2;
           coll_text(d, (uint32_t)v, type == T_RAWSTRIP, &b, &e2);
-          for (uint64_t i = b; i < e2; i++) put_char(s, (char)d.pool_data[i]);
+          s.bytes(d.pool_data + b, (uint32_t)(e2 - b));
         } else put_mdstr(s, d, (uint32_t)v);
         if (type == T_QMDSTR || close_quote) put_char(s, '"');
         break;
@@ -1788,11 +1696,36 @@ __device__ __forceinline__ void run_fields(S& s, const Dev& d, const uint32_t* a
 
 // Size pass: the same fields as straight-line code.  Field types, literal lengths and value slots are
 // compile-time constants here, so each present field costs its value's digit count and one addition.
+constexpr int field_word_offset(int i) {  // position of field i's literal in g_fields.w (as make_prog lays it out)
+  int w = 0;
+  for (int f = 0; f < i; f++) w += (c_strlen(kAllFields[f].lit) + 7) / 8;
+  return w;
+}
+constexpr uint32_t longest_constant_string() {
+  uint32_t m = 0;
+  for (int f = CSTR_BASE; f < FIELD_COUNT; f++) if ((uint32_t)c_strlen(kAllFields[f].lit) > m) m = (uint32_t)c_strlen(kAllFields[f].lit);
+  return m;
+}
+// Most bytes a field's value can take; 0xffff for values of any length (names, metadata entries), which ask the
+// sink for room themselves.
+constexpr uint32_t value_max_bytes(int type, int vk) {
+  switch (type) {
+    case T_NONE: return 0;
+    case T_U64: return vk == VK_64 ? 20u : 10u;
+    case T_I64: return vk == VK_64 ? 20u : 11u;
+    case T_TS: return 24u;       // up to 20 digits, '.', three digits
+    case T_DBL: return 26u;      // 24 characters of a finite value; a non-finite one is shorter, in quotes
+    case T_CSTR: return longest_constant_string();
+    default: return 0xffffu;
+  }
+}
 template <int I> struct FieldInfo {
   static constexpr int type = kAllFields[I].type;
   static constexpr uint32_t len = (uint32_t)c_strlen(kAllFields[I].lit);
   static constexpr uint32_t voff = kAllFields[I].voff;
   static constexpr uint32_t vk = kAllFields[I].vk;
+  static constexpr int woff = field_word_offset(I);
+  static constexpr uint32_t vmax = value_max_bytes(kAllFields[I].type, kAllFields[I].vk);
 };
 template <int BASE, int F, int NF, class S>
 __device__ __forceinline__ void count_fields(S& s, const Dev& d, const uint32_t* a, uint64_t present, unsigned long long* name_bytes) {
@@ -1805,7 +1738,190 @@ __device__ __forceinline__ void count_fields(S& s, const Dev& d, const uint32_t*
     count_fields<BASE, F + 1, NF>(s, d, a, present, name_bytes);
   }
 }
+// Emit pass, hot record classes: the sink is asked for room once per group of fields whose longest possible text
+// fits the group size, not once per field; the groups are fixed at compile time.
+constexpr uint32_t kGroupBytes = 88;
+static_assert(kGroupBytes + 32 + kWinSlack <= (uint32_t)kWinBytes, "a group must fit a window that has just been flushed");
+// First field of a group?  (Walks the class's fields from its first one, as the field loop does.)
+constexpr bool group_starts_at(int base, int first, int f) {
+  uint32_t acc = 0xffffu;  // the first field always starts a group
+  bool starts = true;
+  for (int g = first; g <= f; g++) {
+    const uint32_t v = value_max_bytes(kAllFields[base + g].type, kAllFields[base + g].vk);
+    const uint32_t need = (uint32_t)c_strlen(kAllFields[base + g].lit) + (v == 0xffffu ? 0u : v);
+    starts = acc == 0xffffu || acc + need > kGroupBytes;
+    if (starts) acc = need; else acc += need;
+    if (v == 0xffffu) acc = 0xffffu;  // after a value of any length the next field asks again
+  }
+  return starts;
+}
+// Bytes the group starting at field f can take (f starts a group).
+constexpr uint32_t group_bytes_from(int base, int f, int nf) {
+  uint32_t acc = 0;
+  for (int g = f; g < nf; g++) {
+    const uint32_t v = value_max_bytes(kAllFields[base + g].type, kAllFields[base + g].vk);
+    const uint32_t need = (uint32_t)c_strlen(kAllFields[base + g].lit) + (v == 0xffffu ? 0u : v);
+    if (g > f && acc + need > kGroupBytes) break;
+    acc += need;
+    if (v == 0xffffu) break;
+  }
+  return acc;
+}
+// Number formatting of the hot classes' field loop: one out-of-line copy of each formatter per kernel, so that a
+// field costs a call instead of a copy of the formatter (with the formatters inlined the kernel is bound by
+// instruction fetch).  The sink travels in registers: window, position and open word in, position
+// and open word out; nothing here flushes, the caller has asked for the room.
+__device__ __forceinline__ WindowSink sink_at(uint32_t* win, uint32_t pos, uint32_t carry) {
+  WindowSink s;
+  s.win = win; s.pos = pos; s.carry = carry; s.w0 = 0; s.head = 0; s.gbase = nullptr;
+  return s;
+}
+__device__ __forceinline__ uint64_t sink_state(const WindowSink& s) { return (uint64_t)s.pos | ((uint64_t)s.carry << 32); }
+__device__ __noinline__ uint64_t app_u64(uint32_t* win, uint32_t pos, uint32_t carry, uint64_t v) {
+  WindowSink s = sink_at(win, pos, carry);
+  put_dec(s, v);
+  return sink_state(s);
+}
+__device__ __noinline__ uint64_t app_u32(uint32_t* win, uint32_t pos, uint32_t carry, uint32_t v) {
+  WindowSink s = sink_at(win, pos, carry);
+  if (v < 10000u) {
+    const int n = 1 + (v >= 10u) + (v >= 100u) + (v >= 1000u);
+    s.put(ascii4(v) >> (8 * (4 - n)), n);
+  } else if (v < 100000000u) {
+    const uint32_t hi = v / 10000u, lo = v - hi * 10000u;
+    const int n = 1 + (hi >= 10u) + (hi >= 100u) + (hi >= 1000u);
+    s.put64((uint64_t)(ascii4(hi) >> (8 * (4 - n))) | ((uint64_t)ascii4(lo) << (8 * n)), (uint32_t)(n + 4));
+  } else {  // 9 or 10 digits
+    const uint32_t hi = v / 100000000u, lo = v - hi * 100000000u;
+    const int n = 1 + (hi >= 10u);
+    s.put(ascii4(hi) >> (8 * (4 - n)), n);
+    s.put64(ascii8(lo), 8u);
+  }
+  return sink_state(s);
+}
+__device__ __noinline__ uint64_t app_i32(uint32_t* win, uint32_t pos, uint32_t carry, int32_t v) {
+  WindowSink s = sink_at(win, pos, carry);
+  uint32_t mag = (uint32_t)v;
+  if (v < 0) { put_char(s, '-'); mag = 0u - mag; }
+  return app_u32(win, s.pos, s.carry, mag);
+}
+__device__ __noinline__ uint64_t app_i64(uint32_t* win, uint32_t pos, uint32_t carry, int64_t v) {
+  WindowSink s = sink_at(win, pos, carry);
+  put_sdec(s, v);
+  return sink_state(s);
+}
+__device__ __noinline__ uint64_t app_ts(uint32_t* win, uint32_t pos, uint32_t carry, uint64_t ns) {
+  WindowSink s = sink_at(win, pos, carry);
+  put_ts2(s, (int64_t)ns);
+  return sink_state(s);
+}
+__device__ __noinline__ uint64_t app_dbl(uint32_t* win, uint32_t pos, uint32_t carry, uint64_t bits) {
+  WindowSink s = sink_at(win, pos, carry);
+  put_dbl(s, __longlong_as_double((long long)bits));
+  return sink_state(s);
+}
+// a constant string of the field table (at most longest_constant_string() bytes)
+__device__ __noinline__ uint64_t app_cstr(uint32_t* win, uint32_t pos, uint32_t carry, uint32_t index) {
+  WindowSink s = sink_at(win, pos, carry);
+  const FieldDesc cs = g_fields.f[CSTR_BASE + index];
+  const uint64_t* w = g_fields.w + cs.off;
+  for (uint32_t k = 0; k < ((uint32_t)cs.len >> 3); k++) s.put8w(w[k]);
+  const uint32_t rem = cs.len & 7u;
+  if (rem) s.put64(w[cs.len >> 3], rem);  // the table pads with zero bytes
+  return sink_state(s);
+}
+// Emit pass, the same fields as a loop: all lanes of a warp are at the same field at the same time, so the field's
+// descriptor and the words of its literal are warp-uniform constant loads, the loop's body is small enough to stay
+// in the instruction cache, and lanes whose event lacks a field sit out one iteration.  Descriptor (64 bits):
+// literal word offset 0..11, literal length 12..19, operation 20..23, value slot offset 24..35, group bytes 36..43
+// (non-zero: the field starts a group, see kGroupBytes).
+enum : uint32_t { OP_NONE = 0, OP_U32, OP_I32, OP_U64, OP_I64, OP_TS, OP_DBL, OP_CSTR, OP_OTHER };
+constexpr uint32_t field_op(int type, int vk) {
+  switch (type) {
+    case T_NONE: return OP_NONE;
+    case T_U64: return vk == VK_64 ? OP_U64 : OP_U32;
+    case T_I64: return vk == VK_64 ? OP_I64 : (vk == VK_I32 ? OP_I32 : OP_U32);
+    case T_TS: return OP_TS;
+    case T_DBL: return OP_DBL;
+    case T_CSTR: return OP_CSTR;
+    default: return OP_OTHER;
+  }
+}
+struct LoopDescs { uint64_t d[FIELD_COUNT]; };
+constexpr void fill_class_descs(LoopDescs& t, int base, int nf) {
+  for (int f = 0; f < nf; f++) {
+    const FieldSrc& src = kAllFields[base + f];
+    const uint64_t grp = group_starts_at(base, 0, f) ? group_bytes_from(base, f, nf) : 0;
+    t.d[base + f] = (uint64_t)field_word_offset(base + f) | ((uint64_t)c_strlen(src.lit) << 12) | ((uint64_t)field_op(src.type, src.vk) << 20) |
+                    ((uint64_t)src.voff << 24) | (grp << 36) | ((uint64_t)src.type << 44);
+  }
+}
+constexpr LoopDescs make_loop_descs() {
+  LoopDescs t{};
+  fill_class_descs(t, API_BASE, A_COUNT); fill_class_descs(t, KERNEL_BASE, K_COUNT); fill_class_descs(t, MEM_BASE, M_COUNT);
+  fill_class_descs(t, OP_BASE, O_COUNT);
+  return t;
+}
+constexpr uint32_t longest_group(const LoopDescs& t) {
+  uint32_t m = 0;
+  for (int f = 0; f < FIELD_COUNT; f++) if (((t.d[f] >> 36) & 0xffu) > m) m = (uint32_t)(t.d[f] >> 36) & 0xffu;
+  return m;
+}
+// a field that is longer than a group on its own still has to fit behind the open block of a flushed window
+static_assert(longest_group(make_loop_descs()) + 32 + 8 <= (uint32_t)kWinBytes && longest_group(make_loop_descs()) < 256, "group does not fit the window");
+__constant__ LoopDescs g_loop = make_loop_descs();
+template <int BASE, int NF>
+__device__ __forceinline__ void loop_fields(WindowSink& s, const Dev& d, const uint32_t* a, uint64_t present, unsigned long long* name_bytes) {
+#pragma unroll 1
+  for (int f = 0; f < NF; f++) {
+    const bool on = (present >> f) & 1ull;
+    const uint64_t desc = g_loop.d[BASE + f];
+    const uint32_t grp = (uint32_t)(desc >> 36) & 0xffu;
+    if (grp != 0u) s.ensure(grp);  // also when no lane has the field: the group's other fields rely on it
+    if (on) {
+      const uint32_t len = (uint32_t)(desc >> 12) & 0xffu;
+      if (len != 0u) {
+        const uint64_t* w = g_fields.w + ((uint32_t)desc & 0xfffu);
+        const uint32_t ph = s.pos & 3u, sft = ph << 3, nw = (len + 7u) >> 3;
+        uint32_t* p = s.win + (s.pos >> 2) * (uint32_t)kWinStride;
+        uint32_t c = s.carry, t0 = 0, t1 = 0;
+#pragma unroll 1
+        for (uint32_t k = 0; k < nw; k++) {  // whole words; the table pads every literal with zero bytes
+          const uint64_t x = w[k];
+          const uint32_t lo = (uint32_t)x, hi = (uint32_t)(x >> 32);
+          t0 = c | (lo << sft); t1 = funnel_l(lo, hi, sft);
+          p[0] = t0; p[kWinStride] = t1;
+          c = funnel_l(hi, 0u, sft);
+          p += 2 * kWinStride;
+        }
+        const uint32_t rem = len & 7u;  // bytes of the last word copied that belong to the literal (0: all eight)
+        const uint32_t k = rem == 0u ? 2u : (ph + rem) >> 2;  // words that last copy completed
+        s.carry = k == 0u ? t0 : (k == 1u ? t1 : c);
+        s.pos += len;
+      }
+      const uint32_t op = (uint32_t)(desc >> 20) & 0xfu, voff = (uint32_t)(desc >> 24) & 0xfffu;
+      if (op != OP_NONE) {
+        uint64_t st;
+        if (op == OP_U32) st = app_u32(s.win, s.pos, s.carry, a[voff >> 2]);
+        else if (op == OP_I32) st = app_i32(s.win, s.pos, s.carry, (int32_t)a[voff >> 2]);
+        else if (op == OP_TS) st = app_ts(s.win, s.pos, s.carry, reinterpret_cast<const uint64_t*>(a)[voff >> 3]);
+        else if (op == OP_U64) st = app_u64(s.win, s.pos, s.carry, reinterpret_cast<const uint64_t*>(a)[voff >> 3]);
+        else if (op == OP_CSTR) st = app_cstr(s.win, s.pos, s.carry, a[voff >> 2]);
+        else if (op == OP_DBL) st = app_dbl(s.win, s.pos, s.carry, reinterpret_cast<const uint64_t*>(a)[voff >> 3]);
+        else if (op == OP_I64) st = app_i64(s.win, s.pos, s.carry, (int64_t)reinterpret_cast<const uint64_t*>(a)[voff >> 3]);
+        else {  // names, metadata entries: they ask the sink for room themselves
+          put_value<WindowSink, false, true>(s, d, (int)((uint32_t)(desc >> 44) & 0xfu), (uint64_t)a[voff >> 2], name_bytes);
+          st = sink_state(s);
+        }
+        s.pos = (uint32_t)st; s.carry = (uint32_t)(st >> 32);
+      }
+    }
+  }
+}
 constexpr int kEventThreads = 128;
+constexpr size_t events_smem_bytes(bool write) {
+  return (size_t)kEventThreads * kRecStride * 8 + (write ? ((size_t)kEventThreads * kWinWords + kWinPadWords) * 4 : 0);
+}
 
 // COLL (emit pass only): this launch writes the kernel events that carry collective metadata, and only those; the
 // launch without it writes everything else and holds no code for them.  Returns false when the event is left to
@@ -1845,7 +1961,15 @@ __device__ __forceinline__ bool format_event(S& s, const Dev& d, int cls, uint32
     // rare shapes: kernels with collective metadata, instant events
     const bool rare = (cls == C_KERNEL && ((p >> K_COLL) & 1ull) != 0) || (cls == C_OP && ((p >> I_HEAD) & 1ull) != 0);
     if (rare != COLL) return false;
-    run_fields<S, COLL>(s, d, a, base, p, nb);
+    if constexpr (COLL) run_fields<S, COLL>(s, d, a, base, p, nb);
+    else {
+      // the classes nearly all events belong to run compile-time field code; the others share the table-driven loop
+      if (base == API_BASE) loop_fields<API_BASE, A_COUNT>(s, d, a, p, nb);
+      else if (base == KERNEL_BASE) loop_fields<KERNEL_BASE, K_COUNT>(s, d, a, p, nb);
+      else if (base == MEM_BASE) loop_fields<MEM_BASE, M_COUNT>(s, d, a, p, nb);
+      else if (cls == C_OP) loop_fields<OP_BASE, O_COUNT>(s, d, a, p, nb);
+      else run_fields<S, COLL>(s, d, a, base, p, nb);
+    }
   }
   return true;
 }
@@ -1862,9 +1986,11 @@ __device__ __forceinline__ uint32_t class_units(int cls) {
 // with coalesced loads (lane = 8-byte unit of a record); all later reads of record fields and of the
 // values computed from them are shared-memory reads at table-given offsets.
 template <bool WRITE, bool COLL = false>
-__global__ void __launch_bounds__(kEventThreads, 8) k_events(Dev d) {
-  __shared__ uint64_t s_rec[kEventThreads * kRecStride];
-  __shared__ uint64_t s_park[WRITE ? 3 * kEventThreads : 1];
+__global__ void __launch_bounds__(kEventThreads, WRITE ? 5 : 8) k_events(Dev d) {
+  // dynamic shared memory (events_smem_bytes): the threads' record areas, then (emit pass) their output windows
+  extern __shared__ uint64_t s_dyn[];
+  uint64_t* const s_rec = s_dyn;
+  uint32_t* const s_win = reinterpret_cast<uint32_t*>(s_dyn + kEventThreads * kRecStride);  // per warp: [kWinWords][32 lanes]; a pad after the last warp
   __shared__ unsigned long long s_cnt[8];
   if (!WRITE) {
     if (threadIdx.x < 8) s_cnt[threadIdx.x] = 0;
@@ -1937,9 +2063,9 @@ __global__ void __launch_bounds__(kEventThreads, 8) k_events(Dev d) {
       d.ev_size[ev] = filt ? 0u : s.n;
       if (cls != C_OP) d.ev_ext[ev] = ext;
     } else {
-      GlobalSink s;
-      s.init(d.out + off, size, &s_park[threadIdx.x]);
-      if (format_event<GlobalSink, COLL>(s, d, cls, area, j, t, &filt, &ext) && !s.finish(d.out + off, size))
+      WindowSink s;
+      s.init(d.out + off, size, s_win + (threadIdx.x >> 5) * (kWinWords * kWinStride) + (threadIdx.x & 31u));
+      if (format_event<WindowSink, COLL>(s, d, cls, area, j, t, &filt, &ext) && !s.finish(d.out + off, size))
         atomicAdd(&d.counters->device_check, 1ull);
     }
   }
@@ -2018,7 +2144,7 @@ template <bool WRITE>
 __global__ void __launch_bounds__(kEventThreads) k_annotations(Dev d, const SpanRec* spans, uint32_t n, uint32_t* sizes,
                                                                const uint64_t* offs, uint64_t out_base) {
   __shared__ uint64_t s_area[kEventThreads * 4];  // 32 bytes per span, 8-byte aligned for slot_value's 64-bit loads
-  __shared__ uint64_t s_park[WRITE ? 3 * kEventThreads : 1];
+  __shared__ uint32_t s_win[WRITE ? kEventThreads * kWinWords + kWinPadWords : 1];
   const uint32_t i = blockIdx.x * kEventThreads + threadIdx.x;
   if (i >= n) return;
   const SpanRec r = spans[i];
@@ -2035,8 +2161,8 @@ __global__ void __launch_bounds__(kEventThreads) k_annotations(Dev d, const Span
     const uint32_t size = sizes[i];
     uint8_t* dst = d.out + out_base + offs[i];
     if (size < kMinEventBytes || out_base + offs[i] + size > d.out_cap) { atomicAdd(&d.counters->device_check, 1ull); return; }
-    GlobalSink s;
-    s.init(dst, size, &s_park[threadIdx.x]);
+    WindowSink s;
+    s.init(dst, size, s_win + (threadIdx.x >> 5) * (kWinWords * kWinStride) + (threadIdx.x & 31u));
     run_fields(s, d, a, ANN_BASE, p, &nb);
     if (!s.finish(dst, size)) atomicAdd(&d.counters->device_check, 1ull);
   }

@@ -161,3 +161,19 @@ def test_tsc_conversion_matches_x87(fc):
                             ctypes.c_int64(17 * 10 ** 17), ctypes.c_uint64(mant), ctypes.c_int(exp),
                             o.ctypes.data_as(ctypes.c_void_p))
         assert (o1 == o2).all()
+
+
+def test_window_sink_on_cpu(tmp_path):
+    """The emit pass's output sink, compiled for the host: random events through every append primitive, written in
+    random order at every alignment, give the plain concatenation of their texts (windows flush, the open block
+    moves, neighbours share their boundary words)."""
+    so = str(tmp_path / "libsc.so")
+    subprocess.run(["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-I" + os.path.join(ROOT, "kineto_b200", "csrc"),
+                    os.path.join(ROOT, "tests", "native", "sink_check.cpp"), "-o", so], check=True)
+    sc = ctypes.CDLL(so)
+    sc.sc_fuzz.restype = ctypes.c_int64
+    sc.sc_fuzz.argtypes = [ctypes.c_uint64, ctypes.c_int, ctypes.c_int, ctypes.c_int]
+    for seed in range(1, 121):
+        assert sc.sc_fuzz(seed, 300, seed % 40, (seed * 7) % 400) == 0, seed
+    assert sc.sc_fuzz(1000, 2000, 0, 0) == 0      # shortest events only
+    assert sc.sc_fuzz(1001, 50, 6, 5000) == 0     # copies far longer than a window
