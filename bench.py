@@ -1,23 +1,35 @@
 """Benchmark of the trace post-processing hot path.
 
-    python bench.py --gpus N --steps K --warmup W            # this library (CUDA, sm_100a)
-    python bench.py --impl reference --gpus N --steps K ...   # the reference's CPU path on host cores
+    python bench.py --gpus N --steps K --warmup W [--workload W --n N]   # this library (CUDA, sm_100a)
+    python bench.py --impl reference --gpus N --steps K ...               # the reference's CPU path on host cores
 
-Workload (config.workload): the "kernel launches" configuration — per GPU 1 000 000 CUpti_ActivityKernel9
-records + 1 000 000 cudaLaunchKernel runtime records + 1 000 000 EXTERNAL_CORRELATION records +
-1 000 000 CPU ops, correlation ids shuffled by a seeded permutation, 8 devices x 32 streams, a pool
-of 4096 kernel names of 20-400 bytes; full join + timestamp handling + Chrome-trace JSON.  Seeded
-synthetic data stands in for a real capture.  With N > 1 the trace is N times as long and sharded by
-contiguous record range, one shard per GPU (weak scaling); the shards exchange their
-EXTERNAL_CORRELATION records and CPU-op ids with NCCL so the join covers the whole trace.
+Workloads (seeded synthetic traces that stand in for real captures; `--n` is the generator's size argument
+per GPU):
 
-One "step" = one pass of the path over the shard.  `value` counts input records (CUPTI records + CPU
-ops) per second with the inputs already resident in HBM; `e2e` is the same through the C ABI with
-pinned HOST buffers, host->device and device->host copies inside the timed region.
+    mixed             (default, n = 10 000 000)  10 M mixed activities per GPU: 60 % kernels, 20 % memcpy (HtoD /
+                      DtoH / DtoD / PtoP), 5 % memset, 15 % runtime-only calls, each with its launching runtime
+                      record, EXTERNAL_CORRELATION record and CPU op; 50 000 names of 20-400 bytes, 2 % with JSON
+                      escapes; 5 % orphaned correlation ids
+    kernel_launches   n Kernel9 + n cudaLaunchKernel + n EXTERNAL_CORRELATION records + n CPU ops, correlation ids
+                      shuffled by a seeded permutation, 4096 names
+    op_tree           a CPU op tree of n nested record_function spans with shape strings, flows, 2 n kernel launches
+    distributed_rank  one rank of a distributed job: n launches, 20 % NCCL collectives with metadata, events sorted
+                      by start time; with N GPUs every GPU formats its own rank's trace (no exchange)
+    memory_events     kernel_launches plus n / 2 cpu_instant_event rows
+    generic           n GenericTraceActivity kernel records fed straight to the JSON logger
+
+With N > 1 the mixed and kernel_launches traces are N times as long and sharded by contiguous record range, one
+shard per GPU (weak scaling); the shards exchange their EXTERNAL_CORRELATION records and CPU-op ids with NCCL so
+that the join covers the whole trace.
+
+One "step" = one pass of the path over the shard.  `value` counts input records (CUPTI records + CPU ops) per
+second with the inputs already resident in HBM; `e2e` is the same through the C ABI with pinned HOST buffers:
+host->device copies of every input and the slab-by-slab device->host copy of the text inside the timed region.
 """
 from __future__ import annotations
 
 import argparse
+import hashlib
 import json
 import os
 import statistics
@@ -35,12 +47,16 @@ import numpy as np  # noqa: E402
 METRIC = "trace_records_per_sec"
 UNIT = "records/s"
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one k_events<true> launch divided by the JSON bytes
-# it wrote, from the ncu capture summarised in profiles/ (None until a capture exists).
-EMIT_TRAFFIC_PER_OUT_BYTE = 1.036  # dram read+write of the emit launch per output byte (ncu, profiles/event_kernels_kernel_launches_100k.txt)
+# dram__bytes_read.sum + dram__bytes_write.sum of one emit launch (k_events<true, false>) divided by the JSON bytes it
+# wrote: ncu capture of a whole launch of the kernel_launches workload at 1 M launches (1.86 GB of text, far
+# beyond the L2), summarised in profiles/; traffic grows in proportion to the text, so the line scales it.
+EMIT_TRAFFIC_PER_OUT_BYTE = None
+SLAB_BYTES = 256 << 20
 
-
-E2E_DEPTH = 2  # contexts alternating in the end-to-end leg
+DEFAULT_N = {"mixed": 10_000_000, "kernel_launches": 1_000_000, "op_tree": 2_000_000, "distributed_rank": 2_000_000,
+             "memory_events": 1_000_000, "generic": 2_000_000}
+SHARDED = ("mixed", "kernel_launches")      # one trace, cut by record range, join keys exchanged
+REPLICATED = ("distributed_rank",)          # one independent trace per GPU
 
 
 def parse():
@@ -49,19 +65,52 @@ def parse():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--launches", type=int, default=1_000_000, help="kernel launches per GPU")
-    ap.add_argument("--cpu-sample", type=int, default=250_000, help="launches in the CPU-baseline sample")
+    ap.add_argument("--workload", default="mixed", choices=sorted(DEFAULT_N))
+    ap.add_argument("--n", type=int, default=0, help="size argument of the generator per GPU (0: the workload's default)")
+    ap.add_argument("--launches", type=int, default=0, help="same as --workload kernel_launches --n LAUNCHES")
+    ap.add_argument("--cpu-sample", type=int, default=250_000, help="size argument of the CPU-baseline / parity sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    return ap.parse_args()
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
+    ap.add_argument("--parity-full", action="store_true",
+                    help="also run the reference on the WHOLE benchmark trace and compare sha256 (minutes of CPU time)")
+    a = ap.parse_args()
+    if a.launches:
+        a.workload, a.n = "kernel_launches", a.launches
+    if not a.n:
+        a.n = DEFAULT_N[a.workload]
+    return a
 
 
-def config(args, world):
-    return {"workload": "kernel_launches: per GPU %d Kernel9 + %d cudaLaunchKernel + %d EXTERNAL_CORRELATION records"
-                        " + %d CPU ops, shuffled correlation ids, 8 devices x 32 streams, 4096 names of 20-400 B"
-                        % ((args.launches,) * 4),
-            "launches_per_gpu": args.launches, "sharding": "contiguous record range, %d shard(s)" % world,
-            "l2": "inputs (272 MB/GPU) and output (1.86 GB/GPU) exceed the 126 MB L2; no flush needed",
-            "seed": 2}
+def generate(workload, n, rank=0, world=1):
+    from kineto_b200 import synth
+    if workload == "mixed":
+        return synth.gen_mixed(n, seed=3, shard=(rank, world))
+    if workload == "kernel_launches":
+        return synth.gen_kernel_launches(n, seed=2, shard=(rank, world))
+    if workload == "op_tree":
+        return synth.gen_op_tree(n, seed=4 + rank)
+    if workload == "distributed_rank":
+        t = synth.gen_distributed_rank(n, rank=rank, seed=5)
+        t.params["flags"] |= 2  # events in order of their start time (64-bit radix sort)
+        return t
+    if workload == "memory_events":
+        return synth.gen_kernel_launches(n, seed=2 + rank, memory_events=0.5)
+    return synth.gen_generic_kernels(n, seed=1 + rank)
+
+
+def config(args, world, n):
+    what = {"mixed": "mixed: per GPU %d activities (60%% kernels, 20%% memcpy, 5%% memset, 15%% runtime-only), each with runtime + "
+                     "EXTERNAL_CORRELATION record + CPU op, 50k names of 20-400 B (2%% JSON escapes), 5%% orphans",
+            "kernel_launches": "kernel_launches: per GPU %d Kernel9 + cudaLaunchKernel + EXTERNAL_CORRELATION records + CPU ops, "
+                               "shuffled correlation ids, 8 devices x 32 streams, 4096 names of 20-400 B",
+            "op_tree": "op_tree: %d nested record_function spans with shape strings and flows, 2 launches per op",
+            "distributed_rank": "distributed_rank: per GPU one rank's trace, %d launches, 20%% collectives with metadata, sorted by start",
+            "memory_events": "memory_events: %d launches + half as many cpu_instant_event rows",
+            "generic": "generic: %d GenericTraceActivity kernel records"}[args.workload] % n
+    return {"workload": what, "name": args.workload, "n_per_gpu": n,
+            "sharding": ("contiguous record range, %d shard(s), join keys exchanged" % world) if args.workload in SHARDED
+            else ("%d independent trace(s)" % world),
+            "l2": "inputs and output of one step exceed the 126 MB L2 many times over; no flush needed", "seed": "fixed"}
 
 
 class ClockSampler:
@@ -113,39 +162,58 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(self.sm)}
 
 
-def make_shard(args, rank, world):
-    from kineto_b200 import synth
-    return synth.gen_kernel_launches(args.launches, seed=2, shard=(rank, world))
+def activities_span(doc: bytes) -> bytes:
+    """The events of a file written through ActivityTrace::save(): one run between the metadata rows and the trace span."""
+    a = doc.find(b'\n  {\n    "ph": "X",')
+    b = doc.rfind(b'\n  {\n    "ph": "X",\n    "cat": "Trace",')
+    return doc[a:b]
 
 
 # ------------------------------------------------------------------------------------------------
-# reference arm: the reference's own CPU code (oracle/_ref/ref_driver), all host cores
+# the reference's own CPU code (oracle/_ref/ref_driver), or our CPU restatement where it is absent
 # ------------------------------------------------------------------------------------------------
-def reference_records_per_sec(sample_launches, procs, repeat=1):
-    """Runs `procs` concurrent reference processes, each over its own copy of a sample trace of the
-    workload; returns (aggregate records/s, seconds, records per process, kind)."""
-    from kineto_b200 import synth
+def run_reference_once(trace, procs, keep_output=False):
+    """`procs` concurrent single-threaded reference processes, each over its own copy of `trace`.  Returns
+    (aggregate records/s, seconds, records per process, kind, sha256 of the activities text or None)."""
     ref = os.path.join(ROOT, "oracle", "_ref", "ref_driver")
-    trace = synth.gen_kernel_launches(sample_launches, seed=2)
-    n_rec = sample_launches * 4
     with tempfile.TemporaryDirectory(dir="/dev/shm" if os.path.isdir("/dev/shm") else None) as d:
         path = os.path.join(d, "sample.k2jt")
         trace.write(path)
         if os.path.exists(ref):
-            cmds = [[ref, path, os.path.join(d, "out%d.json" % i), "--repeat", str(repeat)] for i in range(procs)]
+            cmds = [[ref, path, os.path.join(d, "out%d.json" % i)] for i in range(procs)]
             ps = [subprocess.Popen(c, stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True) for c in cmds]
             outs = [p.communicate()[0] for p in ps]
             if any(p.returncode for p in ps):
                 raise RuntimeError("ref_driver failed")
             secs = max(json.loads(o.strip().splitlines()[-1])["seconds_mean"] for o in outs)
-            return n_rec * procs / secs, secs, n_rec, "reference"
-        # the reference binary is not present: time our CPU restatement instead (one core)
-        sys.path.insert(0, os.path.join(ROOT, "tests"))
-        import helpers
-        t0 = time.perf_counter()
-        helpers.run_port(trace, path=path)
-        secs = time.perf_counter() - t0
-        return n_rec / secs, secs, n_rec, "port"
+            digest = None
+            if keep_output:
+                doc = open(os.path.join(d, "out0.json"), "rb").read()
+                span = activities_span(doc) if int(trace.params["mode"][0]) == 1 else None
+                digest = (hashlib.sha256(span).hexdigest(), len(span)) if span is not None else None
+            kind = "reference"
+        else:  # the reference binary is not present: our CPU restatement (one core)
+            sys.path.insert(0, os.path.join(ROOT, "tests"))
+            import helpers
+            t0 = time.perf_counter()
+            data, _ = helpers.run_port(trace, path=path)
+            secs = time.perf_counter() - t0
+            digest = (hashlib.sha256(data).hexdigest(), len(data))
+            kind, procs = "port", 1
+    return secs, kind, procs, digest
+
+
+def cupti_record_count(trace):
+    """Number of CUPTI records of a generated trace (the generators pack whole records back to back)."""
+    from kineto_b200 import tracefile as tf
+    view, pos, n, total = memoryview(trace.cupti), 0, 0, len(trace.cupti)
+    while pos < total:
+        kind = int.from_bytes(view[pos:pos + 4], "little")
+        if kind not in tf.RECORD_SIZE:
+            break
+        pos += (tf.RECORD_SIZE[kind] + 7) & ~7
+        n += 1
+    return n
 
 
 def run_reference(args):
@@ -154,22 +222,28 @@ def run_reference(args):
         return
     cores = os.cpu_count() or 1
     procs = max(1, min(cores, 32))
-    sample = min(args.launches, 50_000)
+    sample_n = min(args.n, max(1000, args.cpu_sample // 5))
+    trace = generate(args.workload, sample_n)
+    n_rec = cupti_record_count(trace) + len(trace.op_start)
     vals, secs_all = [], []
     kind = "reference"
     for i in range(args.warmup + args.steps):
-        v, secs, n_rec, kind = reference_records_per_sec(sample, procs)
+        secs, kind, used, _ = run_reference_once(trace, procs)
         if i >= args.warmup:
-            vals.append(v)
+            vals.append(n_rec * used / secs)
             secs_all.append(secs)
     value = statistics.mean(vals)
+    cfg = config(args, args.gpus, args.n)
+    cfg["reference_sample"] = ("every step: %d concurrent single-threaded reference processes, each over a %s trace of size "
+                               "argument %d (%d records), processTrace + save to tmpfs; the reference has no multi-threaded "
+                               "path, so its throughput does not depend on the trace's length beyond its hash maps"
+                               % (procs, args.workload, sample_n, n_rec))
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * statistics.mean(secs_all),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-            "config": config(args, args.gpus),
+            "config": cfg,
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": procs if kind == "reference" else 1, "kind": kind,
-                             "sample": "%d concurrent single-threaded reference processes, each %d launches "
-                                       "(%d records) of the workload, processTrace + save to tmpfs" % (procs, sample, sample * 4)},
+                             "sample": cfg["reference_sample"]},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
@@ -177,6 +251,23 @@ def run_reference(args):
 # ------------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------------
+def fit_n(args, world):
+    """Per-GPU size argument, reduced when the host cannot hold the traces and the pinned copies of all ranks."""
+    try:
+        import psutil
+        avail = psutil.virtual_memory().available
+    except Exception:  # noqa: BLE001
+        return args.n, None
+    per_unit = {"mixed": 2300, "kernel_launches": 2700, "op_tree": 3500, "distributed_rank": 2500, "memory_events": 3000,
+                "generic": 700}[args.workload]  # host bytes per unit of n: trace + pinned inputs + pinned text (one lane)
+    lanes_extra = 1600 if world == 1 else 0     # the second pinned text buffer of the end-to-end leg
+    need = world * args.n * (per_unit + lanes_extra)
+    if need <= 0.7 * avail:
+        return args.n, None
+    n = int(0.7 * avail / (world * (per_unit + lanes_extra)))
+    return max(n, 10_000), "size argument reduced from %d to fit %.0f GB of free host memory" % (args.n, avail / 1e9)
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -191,8 +282,11 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    n, n_note = fit_n(args, world)
+    exchange = world > 1 and args.workload in SHARDED
+    depth = 2 if world == 1 else 1  # contexts alternating in the end-to-end leg
 
-    trace = make_shard(args, rank, world)
+    trace = generate(args.workload, n, rank, world if args.workload in SHARDED else 1)
     stream = torch.cuda.current_stream()
     ctx = api.K2J(local, stream.cuda_stream)
 
@@ -203,27 +297,28 @@ def run_ours(args):
 
     exchange_events = []
 
-    def exchange_and_emit(ctx=ctx, stream=stream):
-        """segment -> (all-gather join keys) -> emit; returns the result dict."""
-        if world == 1:
-            return ctx.run()
-        info = ctx.segment()
+    def prepare(c, s):
+        """segment -> (all-gather join keys): everything before the emit step."""
+        if not exchange:
+            c.segment(sync=False)
+            return
+        info = c.segment()
         n_ext, n_ops = int(info.n_external), int(info.n_ops)
         ext_local = api.device_view(info.external_records, n_ext * 2, "<i8", dev)
         ops_local = api.device_view(info.op_ids, n_ops, "<i4", dev)
         x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        x0.record(stream)
+        x0.record(s)
         ext_all, ops_all, own_begin = sharding.gather_join_keys(ext_local, ops_local, rank, world, dist)
-        x1.record(stream)
+        x1.record(s)
         exchange_events.append((x0, x1))
-        ctx.set_global_join(ext_all, ext_all.numel() // 2, own_begin, ops_all, ops_all.numel())
-        return ctx.emit()
+        c.set_global_join(ext_all, ext_all.numel() // 2, own_begin, ops_all, ops_all.numel())
 
-    # ---- resident: inputs already in HBM ----
+    # ---- resident: inputs already in HBM, the text stays in HBM ----
     dev_arrays = api.device_arrays(trace, dev)
     ctx.load(trace, dev_arrays)
     for _ in range(args.warmup):
-        res = exchange_and_emit()
+        prepare(ctx, stream)
+        res = ctx.emit()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()  # before the barrier: its set-up must not delay rank 0 inside the other ranks' timed region
@@ -233,7 +328,8 @@ def run_ours(args):
     stage = {k: 0.0 for k in ("ms_segment", "ms_join", "ms_size", "ms_scan", "ms_emit")}
     launches = 0
     for _ in range(args.steps):
-        res = exchange_and_emit()
+        prepare(ctx, stream)
+        res = ctx.emit()
         for k in stage:
             stage[k] += res[k]
         launches += res["kernel_launches"]
@@ -241,65 +337,86 @@ def run_ours(args):
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     ms = e0.elapsed_time(e1)
-    ms_exchange = sum(a.elapsed_time(b) for a, b in exchange_events[-args.steps:]) / args.steps if world > 1 else 0.0
+    ms_exchange = sum(a.elapsed_time(b) for a, b in exchange_events[-args.steps:]) / args.steps if exchange else 0.0
     n_records = res["n_records"] + len(trace.op_start)
+    out_bytes = res["out_bytes"]
+    resident_ptr, _ = ctx.output_ptr()
+    resident_text = api.device_view(resident_ptr, out_bytes, "|u1", dev) if out_bytes else None
 
-    # ---- end to end: pinned host buffers in, pinned host buffers out ----
-    # Two contexts on two streams alternate: while the text of one step travels to the host, the next
-    # step's inputs travel to the device and are formatted.  Every step still uploads all of its
-    # inputs and downloads all of its output inside the timed region.
-    host = {}
-    for k in api.K2J.ARRAYS:
-        a = np.ascontiguousarray(getattr(trace, k))
-        a = a.view(np.uint8) if a.dtype.fields is not None else a
-        a = a.view(np.int64) if a.dtype == np.uint64 else (a.view(np.int32) if a.dtype == np.uint32 else a)
-        host[k] = torch.from_numpy(a).pin_memory()
-    h2d = sum(t.numel() * t.element_size() for t in host.values())
-    lanes = []
-    for i in range(E2E_DEPTH):
-        s_i = stream if i == 0 else torch.cuda.Stream(dev)
-        c_i = ctx if i == 0 else api.K2J(local, s_i.cuda_stream)
-        lanes.append((c_i, s_i, torch.empty(res["out_bytes"] + 4096, dtype=torch.uint8).pin_memory()))
+    # ---- end to end: pinned host buffers in, one pinned host buffer out ----
+    # Every step uploads all of its inputs and downloads all of its text inside the timed region; inside a step the
+    # text leaves slab by slab while the next slab is written (k2j_emit_to_host).  On one GPU two contexts on two
+    # streams alternate, so that one step's download also overlaps the next step's upload.
+    ms_e2e, h2d, e2e_equal = None, 0, None
+    if not args.no_e2e:
+        host = {}
+        for k in api.K2J.ARRAYS:
+            a = np.ascontiguousarray(getattr(trace, k))
+            a = a.view(np.uint8) if a.dtype.fields is not None else a
+            a = a.view(np.int64) if a.dtype == np.uint64 else (a.view(np.int32) if a.dtype == np.uint32 else a)
+            host[k] = torch.from_numpy(a).pin_memory()
+        h2d = sum(t.numel() * t.element_size() for t in host.values())
+        lanes = []
+        for i in range(depth):
+            s_i = stream if i == 0 else torch.cuda.Stream(dev)
+            c_i = ctx if i == 0 else api.K2J(local, s_i.cuda_stream)
+            lanes.append((c_i, s_i, torch.empty(out_bytes + 4096, dtype=torch.uint8).pin_memory()))
 
-    def e2e_step(i):
-        c_i, s_i, out_i = lanes[i % E2E_DEPTH]
-        with torch.cuda.stream(s_i):
-            c_i.synchronize()  # the copy this lane started E2E_DEPTH steps ago has landed
-            c_i.load(trace, host)
-            r = exchange_and_emit(c_i, s_i)
-            c_i.copy_output_async(out_i)
-        return r
+        def e2e_step(i):
+            c_i, s_i, out_i = lanes[i % depth]
+            with torch.cuda.stream(s_i):
+                c_i.load(trace, host)
+                prepare(c_i, s_i)
+                return c_i.emit_to_host(out_i, SLAB_BYTES)  # returns when the whole text has arrived
 
-    def e2e_drain():
-        for c_i, _, _ in lanes:
-            c_i.synchronize()
+        # with two lanes the steps of the two contexts run on two host threads, so that their copies overlap
+        def run_e2e(count):
+            if depth == 1:
+                for i in range(count):
+                    e2e_step(i)
+                return
+            def worker(lane):
+                torch.cuda.set_device(local)
+                for i in range(lane, count, depth):
+                    e2e_step(i)
+            ts = [threading.Thread(target=worker, args=(lane,)) for lane in range(depth)]
+            for t in ts:
+                t.start()
+            for t in ts:
+                t.join()
 
-    for i in range(max(E2E_DEPTH, args.warmup - 1)):
-        e2e_step(i)
-    e2e_drain()
-    barrier()
-    t0 = time.perf_counter()
-    for i in range(args.steps):
-        r2 = e2e_step(i)
-    e2e_drain()
-    torch.cuda.synchronize()
-    ms_e2e = 1e3 * (time.perf_counter() - t0)  # several streams: host clock around fully drained work
-    barrier()
-    for _, _, out_i in lanes[:min(E2E_DEPTH, args.steps)]:
-        assert bytes(out_i[:64].numpy().tobytes()).startswith(b'\n  {\n    "ph": "X"')
-    for c_i, _, _ in lanes[1:]:
-        c_i.close()
+        run_e2e(max(depth, min(args.warmup, 3)))
+        barrier()
+        t0 = time.perf_counter()
+        run_e2e(args.steps)
+        torch.cuda.synchronize()
+        ms_e2e = 1e3 * (time.perf_counter() - t0)  # several streams and threads: host clock around fully drained work
+        barrier()
+        # the text that arrived on the host is the text of the resident run: length and every byte (checked on the GPU)
+        e2e_equal = True
+        for _, _, out_i in lanes[:min(depth, args.steps)]:
+            chunk = 1 << 30
+            for b in range(0, out_bytes, chunk):
+                e = min(out_bytes, b + chunk)
+                if not torch.equal(out_i[b:e].to(dev, non_blocking=False), resident_text[b:e]):
+                    e2e_equal = False
+        for c_i, _, _ in lanes[1:]:
+            c_i.close()
+        del lanes, host
 
     # ---- max over ranks ----
     if world > 1:
-        t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
+        t = torch.tensor([ms, ms_e2e or 0.0], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, ms_e2e = float(t[0]), float(t[1])
-        tot = torch.tensor([n_records, res["out_bytes"], h2d], dtype=torch.int64, device=dev)
+        ms, ms_e2e_max = float(t[0]), float(t[1])
+        ms_e2e = ms_e2e_max if ms_e2e is not None else None
+        tot = torch.tensor([n_records, out_bytes, h2d, int(bool(e2e_equal)) if e2e_equal is not None else 1], dtype=torch.int64, device=dev)
         dist.all_reduce(tot)
         total_records, total_out, total_h2d = int(tot[0]), int(tot[1]), int(tot[2])
+        if e2e_equal is not None:
+            e2e_equal = int(tot[3]) == world
     else:
-        total_records, total_out, total_h2d = n_records, res["out_bytes"], h2d
+        total_records, total_out, total_h2d = n_records, out_bytes, h2d
 
     if rank == 0:
         peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -310,41 +427,67 @@ def run_ours(args):
         emit_ms = stage["ms_emit"] / args.steps
         ops_bytes_in = sum(getattr(trace, k).nbytes for k in ("op_start", "op_end", "op_id", "op_device", "op_resource",
                                                              "op_type", "op_name", "op_flow", "op_flowt", "op_mdoff", "md"))
-        ext_bytes = 24 * (res["n_records"] - (res["x_events"] - len(trace.op_start)))
-        alg_emit = (res["in_bytes"] - ext_bytes) + ops_bytes_in + res["name_bytes"] + res["out_bytes"]
-        alg_all = res["in_bytes"] + ops_bytes_in + res["name_bytes"] + res["out_bytes"]
+        ext_bytes = 24 * (res["n_records"] - (res["x_events"] - len(trace.op_start))) if args.workload == "kernel_launches" else 0
+        alg_emit = (res["in_bytes"] - ext_bytes) + ops_bytes_in + res["name_bytes"] + out_bytes
+        alg_all = res["in_bytes"] + ops_bytes_in + res["name_bytes"] + out_bytes
         achieved = alg_emit / (emit_ms * 1e-3) / 1e9
         value = total_records * args.steps / (ms * 1e-3)
+        cfg = config(args, world, n)
+        if n_note:
+            cfg["note"] = n_note
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "u8", "data": "synthetic", "config": config(args, world), "clocks": clocks,
-            "e2e": {"value": total_records * args.steps / (ms_e2e * 1e-3), "unit": UNIT,
-                    "h2d_bytes_per_step": total_h2d, "d2h_bytes_per_step": total_out,
-                    "output_gb_per_s": total_out * args.steps / (ms_e2e * 1e-3) / 1e9,
-                    "contexts": E2E_DEPTH,
-                    "note": "%d contexts alternate so that one step's download overlaps the next step's upload and "
-                            "kernels; every step moves all of its bytes; host clock around the drained region" % E2E_DEPTH},
+            "dtype": "u8", "data": "synthetic", "config": cfg, "clocks": clocks,
             "gpu_launches": launches,
+            "records_per_step": total_records,
             "output_gb_per_s": total_out * args.steps / (ms * 1e-3) / 1e9,
             "output_bytes_per_step": total_out,
-            "roofline": {"bound": "hbm", "kernel": "k_events<true> (emit pass)", "achieved": achieved, "peak": peak,
+            "roofline": {"bound": "hbm", "kernel": "k_events<true, false> (emit pass)", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
                          "algorithmic_bytes_per_launch": alg_emit, "ms_per_launch": emit_ms,
-                         "traffic": (EMIT_TRAFFIC_PER_OUT_BYTE * res["out_bytes"]) if EMIT_TRAFFIC_PER_OUT_BYTE else None,
+                         "traffic": (EMIT_TRAFFIC_PER_OUT_BYTE * out_bytes) if EMIT_TRAFFIC_PER_OUT_BYTE else None,
                          "pipeline_frac": alg_all / (sum(stage.values()) / args.steps * 1e-3) / 1e9 / peak},
             "stage_ms_per_step": dict({k: v / args.steps for k, v in stage.items()}, ms_exchange=ms_exchange),
         }
+        if ms_e2e is not None:
+            line["e2e"] = {"value": total_records * args.steps / (ms_e2e * 1e-3), "unit": UNIT,
+                           "h2d_bytes_per_step": total_h2d, "d2h_bytes_per_step": total_out,
+                           "output_gb_per_s": total_out * args.steps / (ms_e2e * 1e-3) / 1e9,
+                           "contexts": depth, "slab_bytes": SLAB_BYTES, "text_equals_resident_run": e2e_equal,
+                           "note": "k2j_emit_to_host: the text leaves the GPU slab by slab while the next slab is written; "
+                                   "%d context(s) per GPU; every step moves all of its bytes; host clock around the drained region" % depth}
         if world == 1 and not args.no_cpu_baseline:
-            v, secs, n_rec, kind = reference_records_per_sec(min(args.cpu_sample, args.launches), 1)
-            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": 1, "kind": kind,
-                                    "sample": "%d launches (%d records) of the same workload, one single-threaded "
-                                              "process (the reference path is single-threaded), %.1f s, output on tmpfs"
-                                              % (min(args.cpu_sample, args.launches), n_rec, secs)}
+            line.update(cpu_baseline_and_parity(args, api, local))
+        if args.parity_full and world == 1:
+            secs, kind, _, digest = run_reference_once(trace, 1, keep_output=True)
+            text = resident_text.cpu().numpy().tobytes()
+            line["parity_full"] = {"sha256_match": digest is not None and digest[0] == hashlib.sha256(text).hexdigest(),
+                                   "bytes": len(text), "reference_bytes": digest[1] if digest else None,
+                                   "reference_seconds": secs, "kind": kind, "trace": "the benchmark trace itself"}
         print(json.dumps(line))
     ctx.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+def cpu_baseline_and_parity(args, api, device):
+    """The reference on one host core over a bounded sample of the same workload, and the same sample through the
+    CUDA path: throughput of the former, sha256 of both texts."""
+    sample_n = min(args.n, args.cpu_sample)
+    sample = generate(args.workload, sample_n)
+    secs, kind, _, digest = run_reference_once(sample, 1, keep_output=True)
+    text, r = api.process(sample, device=device)
+    n_rec = r["n_records"] + len(sample.op_start)
+    out = {"cpu_baseline": {"value": n_rec / secs, "unit": UNIT, "cores": 1, "kind": kind,
+                            "sample": "%s trace of size argument %d (%d records, %d bytes of text), one single-threaded process "
+                                      "(the reference path is single-threaded), %.1f s, output on tmpfs"
+                                      % (args.workload, sample_n, n_rec, len(text), secs)}}
+    if digest is not None:
+        out["parity"] = {"sha256_match": digest[0] == hashlib.sha256(text).hexdigest(), "bytes": len(text),
+                         "reference_bytes": digest[1], "sample": "the cpu_baseline sample (same generator, size argument %d)" % sample_n,
+                         "checker": kind}
+    return out
 
 
 if __name__ == "__main__":

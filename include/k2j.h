@@ -9,6 +9,12 @@
  * reference project).  Array arguments may be host or device memory: device memory is used in
  * place, host memory is copied to the GPU on the context's stream (asynchronously when it is
  * pinned).  Either way the arrays must stay valid and unchanged until k2j_run returns.
+ *
+ * Device memory handed to the library (input arrays, the gathered join arrays, scan inputs) is read by
+ * kernels on the context's stream: its contents must be complete before the call that uses them, or be
+ * produced by work that is ordered before the context's stream (the same stream, or an event the stream
+ * waits on).  A caller that fills such arrays on another stream (NCCL, a framework's current stream)
+ * either passes that stream to k2j_create or synchronises it first; the library inserts no such wait.
  */
 #ifndef K2J_H_
 #define K2J_H_
@@ -202,6 +208,18 @@ k2j_status k2j_segment(k2j_ctx* ctx, k2j_segment_info* info);
 k2j_status k2j_set_global_join(k2j_ctx* ctx, const void* external_all, uint64_t n_external_all, uint64_t own_begin,
                                const int32_t* op_ids_all, uint64_t n_ops_all);
 k2j_status k2j_emit(k2j_ctx* ctx, k2j_result* result);
+
+/* k2j_emit for traces whose text should not be held whole on the device: the text is produced in slabs of
+ * about `slab_bytes` (0: 256 MiB; two slabs are kept) and each slab leaves as soon as it is complete, while the
+ * next one is being written.  k2j_emit_to_host copies every slab to its place in `host_dst` (the whole text,
+ * result->out_bytes <= capacity; pinned memory lets the copies overlap the kernels): several contexts, one per
+ * GPU, so fill their parts of one host buffer.  k2j_emit_to_fd writes the slabs to `fd` at its current position,
+ * through the pinned staging buffers of k2j_write_output.  Afterwards the context holds no text (k2j_output and
+ * the copy / write calls return K2J_ERR_STATE).  An event longer than 1 MiB is K2J_ERR_UNSUPPORTED here.
+ * Stand where the reference streams events into its file as it produces them
+ * (libkineto/src/output_json.cpp:237-259, :485-492): the reference never holds the text either. */
+k2j_status k2j_emit_to_host(k2j_ctx* ctx, void* host_dst, uint64_t capacity, uint64_t slab_bytes, k2j_result* result);
+k2j_status k2j_emit_to_fd(k2j_ctx* ctx, int fd, uint64_t slab_bytes, k2j_result* result);
 
 /* The device-wide exclusive scan of the pipeline on its own: offsets[i] = sizes[0] + ... + sizes[i-1]
  * and *total = the sum, for n 32-bit sizes in device memory (offsets: n 64-bit values in device

@@ -15,7 +15,7 @@ from . import tracefile as tf
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("K2J_LIBRARY") or os.path.join(_HERE, "libk2j.so")  # K2J_LIBRARY: another build of the same ABI
 
-STATUS = {0: "OK", 1: "INVALID_ARGUMENT", 2: "CUDA", 3: "UNSUPPORTED", 4: "STATE", 5: "DEVICE_CHECK"}
+STATUS = {0: "OK", 1: "INVALID_ARGUMENT", 2: "CUDA", 3: "UNSUPPORTED", 4: "STATE", 5: "DEVICE_CHECK", 6: "IO"}
 
 
 class K2JError(RuntimeError):
@@ -64,7 +64,7 @@ class SegmentInfo(C.Structure):
                 ("n_ops", C.c_uint64), ("op_ids", C.c_void_p)]
 
 
-EXPORTS = ["k2j_exclusive_scan_u32", "k2j_exclusive_scan_u32_noalloc", "k2j_segment", "k2j_set_global_join", "k2j_emit", "k2j_create", "k2j_destroy", "k2j_last_error", "k2j_set_params", "k2j_set_strings",
+EXPORTS = ["k2j_emit_to_host", "k2j_emit_to_fd", "k2j_exclusive_scan_u32", "k2j_exclusive_scan_u32_noalloc", "k2j_segment", "k2j_set_global_join", "k2j_emit", "k2j_create", "k2j_destroy", "k2j_last_error", "k2j_set_params", "k2j_set_strings",
            "k2j_set_cbid_names", "k2j_set_thread_map", "k2j_set_ops", "k2j_set_cupti", "k2j_run", "k2j_output",
            "k2j_copy_output", "k2j_copy_output_async", "k2j_write_output", "k2j_write_output_at", "k2j_synchronize", "k2j_version"]
 
@@ -95,6 +95,8 @@ def load_library():
     lib.k2j_segment.argtypes = [vp, C.POINTER(SegmentInfo)]
     lib.k2j_set_global_join.argtypes = [vp, vp, C.c_uint64, C.c_uint64, vp, C.c_uint64]
     lib.k2j_emit.argtypes = [vp, C.POINTER(Result)]
+    lib.k2j_emit_to_host.argtypes = [vp, vp, C.c_uint64, C.c_uint64, C.POINTER(Result)]
+    lib.k2j_emit_to_fd.argtypes = [vp, C.c_int, C.c_uint64, C.POINTER(Result)]
     lib.k2j_exclusive_scan_u32.argtypes = [vp, vp, C.c_uint64, vp, C.POINTER(C.c_uint64)]
     lib.k2j_exclusive_scan_u32_noalloc.argtypes = [C.c_int, vp, vp, C.c_uint64, vp, vp]
     lib.k2j_output.argtypes = [vp, C.POINTER(vp), C.POINTER(C.c_uint64)]
@@ -203,7 +205,11 @@ class K2J:
         self._check(st)
         return self.result
 
-    def segment(self) -> SegmentInfo:
+    def segment(self, sync: bool = True):
+        """k2j_segment.  `sync=False`: no shard information is wanted, the call only enqueues the work."""
+        if not sync:
+            self._check(self.lib.k2j_segment(self.h, None))
+            return None
         info = SegmentInfo()
         self._check(self.lib.k2j_segment(self.h, C.byref(info)))
         return info
@@ -218,6 +224,23 @@ class K2J:
     def emit(self) -> dict:
         r = Result()
         st = self.lib.k2j_emit(self.h, C.byref(r))
+        self.result = r.as_dict()
+        self._check(st)
+        return self.result
+
+    def emit_to_host(self, dst, slab_bytes: int = 0) -> dict:
+        """Tiled emit: the text goes to `dst` (uint8 numpy array or pinned torch tensor) slab by slab."""
+        r = Result()
+        cap = dst.nbytes if isinstance(dst, np.ndarray) else dst.numel()
+        st = self.lib.k2j_emit_to_host(self.h, _ptr(dst) or 0, cap, slab_bytes, C.byref(r))
+        self.result = r.as_dict()
+        self._check(st)
+        return self.result
+
+    def emit_to_fd(self, fd: int, slab_bytes: int = 0) -> dict:
+        """Tiled emit: the text is written to the open file descriptor `fd` slab by slab."""
+        r = Result()
+        st = self.lib.k2j_emit_to_fd(self.h, fd, slab_bytes, C.byref(r))
         self.result = r.as_dict()
         self._check(st)
         return self.result
@@ -303,5 +326,5 @@ def device_view(ptr: int, n: int, typestr: str, device="cuda:0"):
     import torch
 
     if n == 0:
-        return torch.empty(0, dtype={"<i8": torch.int64, "<i4": torch.int32}[typestr], device=device)
+        return torch.empty(0, dtype={"<i8": torch.int64, "<i4": torch.int32, "|u1": torch.uint8}[typestr], device=device)
     return torch.as_tensor(_DeviceMemory(ptr, n, typestr), device=device)

@@ -81,6 +81,10 @@ struct k2j_ctx {
   uint64_t totals[C_NCOL] = {0};
   uint32_t launches = 0;
   DevBuf ext_local;
+  DevBuf slab[2], tile_bounds;                       // tiled runs: two output slabs, the slab table
+  cudaStream_t copy_stream = nullptr;                // device-to-host copies of finished slabs
+  cudaEvent_t slab_done[2] = {nullptr, nullptr}, slab_free[2] = {nullptr, nullptr};
+  bool streamed = false;                             // the last run handed its text on slab by slab: no resident output
   DevBuf ctx_tab, evt_recs, seen_tab, row_key, row_first, corr_zero;  // synchronisation records
   DevBuf str_class, comms_flag, coll_list;                            // collective enrichment
   const void* g_ext = nullptr; uint64_t g_n_ext = 0, g_own_begin = 0;
@@ -328,6 +332,13 @@ void k2j_destroy(k2j_ctx* c) {
     if (c->stage_ev[i]) cudaEventDestroy(c->stage_ev[i]);
   }
   for (auto& e : c->ev) if (e) cudaEventDestroy(e);
+  for (int i = 0; i < 2; i++) {
+    c->slab[i].release();
+    if (c->slab_done[i]) cudaEventDestroy(c->slab_done[i]);
+    if (c->slab_free[i]) cudaEventDestroy(c->slab_free[i]);
+  }
+  c->tile_bounds.release();
+  if (c->copy_stream) cudaStreamDestroy(c->copy_stream);
   if (c->own_stream && c->stream) cudaStreamDestroy(c->stream);
   delete c;
 }
@@ -583,12 +594,64 @@ k2j_status k2j_set_global_join(k2j_ctx* c, const void* ext_all, uint64_t n_ext_a
   return K2J_OK;
 }
 
-k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
+}  // extern "C"
+
+namespace {
+
+// Where a tiled run sends its text.
+struct TileSink {
+  int mode = 0;              // 0: the whole text stays in the context; 1: host memory; 2: a file descriptor
+  uint8_t* host = nullptr;   // mode 1
+  uint64_t capacity = 0;
+  int fd = -1;               // mode 2
+  uint64_t slab_bytes = 0;
+};
+constexpr uint64_t kSlabMargin = 1ull << 20;   // a slab holds the events that START in its range: room for the last one's end
+constexpr uint64_t kSlabPad = 64;              // bytes in front of a slab's text (an event's first store may begin before it)
+
+k2j_status stream_bytes(k2j_ctx* c, const uint8_t* src, int fd, bool positioned, uint64_t file_offset, uint64_t total, cudaStream_t stream);
+
+// The emit launches for the events whose text starts in [d.tile_begin, d.tile_end).  `ranges`: per class the work
+// items to look at ([begin, end) pairs, C_API .. C_WAIT, then the CPU-side activities); nullptr: everything.
+k2j_status launch_emit(k2j_ctx* c, const Dev& d, const uint64_t* ranges, bool instant, uint64_t n_coll, cudaStream_t s) {
+  auto launch = [&](uint64_t begin, uint64_t end) {
+    if (end <= begin) return;
+    Dev dr = d;
+    dr.work_origin = begin; dr.n_work = end;
+    k_events<true><<<(uint32_t)((end - begin + kEventThreads - 1) / kEventThreads), kEventThreads, events_smem_bytes(true), s>>>(dr);
+    c->launches++;
+  };
+  if (!ranges) launch(0, d.n_work);
+  else for (int k = 0; k <= C_EXT; k++) launch(ranges[2 * k], ranges[2 * k + 1]);
+  if (instant && c->n_ops) {
+    // instant events: the same extra launch over the CPU-side activities
+    Dev di = d;
+    di.work_origin = ranges ? ranges[2 * C_EXT] : d.ops_begin;
+    di.n_work = ranges ? ranges[2 * C_EXT + 1] : d.n_work;
+    if (di.n_work > di.work_origin) {
+      k_events<true, true><<<(uint32_t)((di.n_work - di.work_origin + kEventThreads - 1) / kEventThreads), kEventThreads, events_smem_bytes(true), s>>>(di);
+      c->launches++;
+    }
+  }
+  if (n_coll != 0) {
+    // kernel events that carry collective metadata: a launch of their own over the work items the size pass
+    // listed, so that the launch above holds no code for them
+    Dev dk = d;
+    dk.work_indirect = d.coll_list; dk.n_indirect = n_coll;
+    k_events<true, true><<<(uint32_t)((dk.n_indirect + kEventThreads - 1) / kEventThreads), kEventThreads, events_smem_bytes(true), s>>>(dk);
+    c->launches++;
+  }
+  K2J_CUDA(c, cudaGetLastError());
+  return K2J_OK;
+}
+
+k2j_status emit_core(k2j_ctx* c, k2j_result* res, const TileSink& sink) {
   if (!c) return K2J_ERR_INVALID_ARGUMENT;
   if (!res) return fail(c, K2J_ERR_INVALID_ARGUMENT, "null result");
   if (!c->segmented) return fail(c, K2J_ERR_STATE, "k2j_segment has not run");
   K2J_CUDA(c, cudaSetDevice(c->device));
   memset(res, 0, sizeof *res);
+  c->ran = false; c->streamed = false;
   cudaStream_t s = c->stream;
   Dev& d = c->d;
   const uint64_t* totals = c->totals;
@@ -597,6 +660,9 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
   if (n_sync + n_cuda_events > 0 && c->have_global_join)
     return fail(c, K2J_ERR_UNSUPPORTED, "synchronisation and CUDA event records across shards are not implemented");
   K2J_CUDA(c, cudaEventRecord(c->ev[6], s));
+  // every counter belongs to the emit step (segmentation counts through its scan columns): a second k2j_emit after
+  // one k2j_segment starts from zero, and an earlier failed check does not fail this run
+  K2J_CUDA(c, cudaMemsetAsync(d.counters, 0, sizeof(Counters), s));
 
   // ---- join tables ----
   uint64_t own_begin = 0, own_end = totals[C_EXT];
@@ -677,7 +743,6 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
     d.has_comms = c->comms_flag.as<uint32_t>();
   }
   d.work_indirect = nullptr; d.n_indirect = 0; d.coll_list = nullptr;
-  K2J_CUDA(c, cudaMemsetAsync(&d.counters->n_coll, 0, sizeof(unsigned long long), s));  // the list below starts empty
   if (d.has_comms && !c->have_global_join && totals[C_KERNEL]) {
     K2J_CUDA(c, c->coll_list.reserve(totals[C_KERNEL] * 4));
     d.coll_list = c->coll_list.as<uint32_t>();
@@ -760,31 +825,105 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
       k2j_status st2 = order_annotations(c, span_cap, &n_spans, &ann_bytes);
       if (st2) return st2;
     }
-    K2J_CUDA(c, c->out.reserve(total_bytes + ann_bytes + 64));
-    d.out = c->out.as<uint8_t>(); d.out_cap = total_bytes + ann_bytes;
+    (void)ev_blocks;
+    const bool instant = (c->h_totals[25] & 2) != 0;
+    const uint64_t n_coll = c->h_totals[26];
+    d.out_cap = total_bytes + ann_bytes;
     K2J_CUDA(c, cudaEventRecord(c->ev[7], s));
-    if (total_bytes) { k_events<true><<<ev_blocks, kEventThreads, events_smem_bytes(true), s>>>(d); c->launches++; }
-    if (total_bytes && (c->h_totals[25] & 2) && c->n_ops) {
-      // instant events: the same extra launch over the CPU-side activities
-      Dev di = d;
-      di.work_origin = d.ops_begin;
-      k_events<true, true><<<(uint32_t)((di.n_work - di.work_origin + kEventThreads - 1) / kEventThreads), kEventThreads, events_smem_bytes(true), s>>>(di);
-      c->launches++;
+    if (sink.mode == 0) {
+      // ---- the whole text stays in the context ----
+      K2J_CUDA(c, c->out.reserve(total_bytes + ann_bytes + 64));
+      d.out = c->out.as<uint8_t>(); d.tile_begin = 0; d.tile_end = total_bytes;
+      if (total_bytes) { k2j_status st3 = launch_emit(c, d, nullptr, instant, n_coll, s); if (st3) return st3; }
+      if (ann_bytes) {
+        k_annotations<true><<<(n_spans + kEventThreads - 1) / kEventThreads, kEventThreads, 0, s>>>(
+            d, c->span_out.as<SpanRec>(), n_spans, c->ann_size.as<uint32_t>(), c->ann_off.as<uint64_t>(), total_bytes);
+        c->launches++;
+      }
+      K2J_CUDA(c, cudaGetLastError());
+    } else {
+      // ---- tiled: slab t holds the events whose text starts in [t * slab, (t + 1) * slab); while slab t travels to
+      // the host (or the file) slab t + 1 is being written ----
+      if (sink.mode == 1 && (sink.capacity < total_bytes + ann_bytes || (!sink.host && total_bytes + ann_bytes)))
+        return fail(c, K2J_ERR_INVALID_ARGUMENT, "destination too small: the text has %llu bytes", (unsigned long long)(total_bytes + ann_bytes));
+      const uint64_t slab = sink.slab_bytes ? std::max<uint64_t>(sink.slab_bytes, 4ull << 20) : (256ull << 20);
+      const uint64_t n_tiles64 = (total_bytes + slab - 1) / slab;
+      if (n_tiles64 > 1000000ull) return fail(c, K2J_ERR_INVALID_ARGUMENT, "slab size too small for this trace");
+      const uint32_t n_tiles = (uint32_t)n_tiles64;
+      for (int i = 0; i < 2; i++) {
+        K2J_CUDA(c, c->slab[i].reserve(std::min<uint64_t>(slab, total_bytes + ann_bytes) + kSlabMargin + kSlabPad + 64));
+        if (!c->slab_done[i]) K2J_CUDA(c, cudaEventCreateWithFlags(&c->slab_done[i], cudaEventDisableTiming));
+        if (!c->slab_free[i]) K2J_CUDA(c, cudaEventCreateWithFlags(&c->slab_free[i], cudaEventDisableTiming));
+      }
+      if (!c->copy_stream) K2J_CUDA(c, cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking));
+      std::vector<uint64_t> bounds((size_t)(n_tiles + 1) * kTileCols);
+      if (n_tiles) {
+        K2J_CUDA(c, c->tile_bounds.reserve(bounds.size() * 8));
+        k_tile_bounds<<<(n_tiles + 1 + 127) / 128, 128, 0, s>>>(d, slab, n_tiles, total_bytes, c->tile_bounds.as<uint64_t>());
+        c->launches++;
+        K2J_CUDA(c, cudaMemcpyAsync(bounds.data(), c->tile_bounds.p, bounds.size() * 8, cudaMemcpyDeviceToHost, s));
+        K2J_CUDA(c, cudaStreamSynchronize(s));
+      }
+      const bool sorted = (c->params.flags & K2J_FLAG_SORT_BY_START) != 0;
+      uint64_t file_pos = 0;
+      // hands slab `k` (bytes [b0, b1) of the text) on; `wait_emit`: the slab's launches are recorded in slab_done[k & 1]
+      auto hand_on = [&](uint32_t k, uint64_t b0, uint64_t b1) -> k2j_status {
+        const uint8_t* src = c->slab[k & 1].as<uint8_t>() + kSlabPad;
+        if (sink.mode == 1) {
+          K2J_CUDA(c, cudaStreamWaitEvent(c->copy_stream, c->slab_done[k & 1], 0));
+          if (b1 > b0) K2J_CUDA(c, cudaMemcpyAsync(sink.host + b0, src, b1 - b0, cudaMemcpyDeviceToHost, c->copy_stream));
+          K2J_CUDA(c, cudaEventRecord(c->slab_free[k & 1], c->copy_stream));
+        } else {
+          K2J_CUDA(c, cudaEventSynchronize(c->slab_done[k & 1]));
+          k2j_status st4 = stream_bytes(c, src, sink.fd, false, 0, b1 - b0, c->copy_stream);
+          if (st4) return st4;
+          file_pos += b1 - b0;
+          K2J_CUDA(c, cudaEventRecord(c->slab_free[k & 1], c->copy_stream));
+        }
+        return K2J_OK;
+      };
+      const uint32_t n_slabs = n_tiles + (ann_bytes ? 1u : 0u);
+      for (uint32_t t = 0; t < n_slabs; t++) {
+        if (t >= 2) K2J_CUDA(c, cudaStreamWaitEvent(s, c->slab_free[t & 1], 0));  // the slab's previous text has left
+        if (t < n_tiles) {
+          const uint64_t* r0 = &bounds[(size_t)t * kTileCols];
+          const uint64_t* r1 = r0 + kTileCols;
+          if (r1[1] - r0[1] > slab + kSlabMargin) return fail(c, K2J_ERR_UNSUPPORTED, "an event of more than %llu bytes", (unsigned long long)kSlabMargin);
+          d.tile_begin = r0[1]; d.tile_end = r1[1];
+          d.out = c->slab[t & 1].as<uint8_t>() + kSlabPad - r0[1];
+          uint64_t ranges[2 * (C_EXT + 1)];
+          for (int k = 0; k < C_EXT; k++) {
+            ranges[2 * k] = sorted ? d.cls_begin[k] : r0[2 + k];
+            ranges[2 * k + 1] = sorted ? d.cls_begin[k] + d.cls_count[k] : r1[2 + k];
+          }
+          ranges[2 * C_EXT] = d.ops_begin + std::min<uint64_t>(r0[0], c->n_ops);   // CPU-side activities are events 0 .. n_ops
+          ranges[2 * C_EXT + 1] = d.ops_begin + std::min<uint64_t>(r1[0], c->n_ops);
+          k2j_status st3 = launch_emit(c, d, ranges, instant, n_coll, s);
+          if (st3) return st3;
+        } else {  // the user-annotation spans come last, as a slab of their own
+          d.tile_begin = total_bytes; d.tile_end = total_bytes + ann_bytes;
+          d.out = c->slab[t & 1].as<uint8_t>() + kSlabPad - total_bytes;
+          k_annotations<true><<<(n_spans + kEventThreads - 1) / kEventThreads, kEventThreads, 0, s>>>(
+              d, c->span_out.as<SpanRec>(), n_spans, c->ann_size.as<uint32_t>(), c->ann_off.as<uint64_t>(), total_bytes);
+          c->launches++;
+          K2J_CUDA(c, cudaGetLastError());
+        }
+        K2J_CUDA(c, cudaEventRecord(c->slab_done[t & 1], s));
+        if (t >= 1) {  // slab t - 1 leaves while slab t is being written
+          k2j_status st4 = hand_on(t - 1, t - 1 < n_tiles ? bounds[(size_t)(t - 1) * kTileCols + 1] : total_bytes,
+                                   t - 1 < n_tiles ? bounds[(size_t)t * kTileCols + 1] : total_bytes + ann_bytes);
+          if (st4) return st4;
+        }
+      }
+      if (n_slabs) {
+        const uint32_t t = n_slabs - 1;
+        k2j_status st4 = hand_on(t, t < n_tiles ? bounds[(size_t)t * kTileCols + 1] : total_bytes,
+                                 t < n_tiles ? bounds[(size_t)(t + 1) * kTileCols + 1] : total_bytes + ann_bytes);
+        if (st4) return st4;
+      }
+      K2J_CUDA(c, cudaStreamSynchronize(c->copy_stream));
+      (void)file_pos;
     }
-    if (total_bytes && c->h_totals[26] != 0) {
-      // kernel events that carry collective metadata: a launch of their own over the work items the size pass
-      // listed, so that the launch above holds no code for them
-      Dev dk = d;
-      dk.work_indirect = d.coll_list; dk.n_indirect = c->h_totals[26];
-      k_events<true, true><<<(uint32_t)((dk.n_indirect + kEventThreads - 1) / kEventThreads), kEventThreads, events_smem_bytes(true), s>>>(dk);
-      c->launches++;
-    }
-    if (ann_bytes) {
-      k_annotations<true><<<(n_spans + kEventThreads - 1) / kEventThreads, kEventThreads, 0, s>>>(
-          d, c->span_out.as<SpanRec>(), n_spans, c->ann_size.as<uint32_t>(), c->ann_off.as<uint64_t>(), total_bytes);
-      c->launches++;
-    }
-    K2J_CUDA(c, cudaGetLastError());
   } else {
     K2J_CUDA(c, cudaEventRecord(c->ev[3], s));
     K2J_CUDA(c, cudaEventRecord(c->ev[4], s));
@@ -816,13 +955,33 @@ k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) {
   cudaEventElapsedTime(&res->ms_emit, c->ev[7], c->ev[5]);
   res->ms_total = res->ms_segment + res->ms_join + res->ms_size + res->ms_scan + res->ms_emit;
   c->out_bytes = total_bytes + ann_bytes;
-  c->ran = true;
   if ((c->params.flags & K2J_FLAG_USER_ANNOTATIONS) && c->have_global_join && c->h_counters->n_user)
     return fail(c, K2J_ERR_UNSUPPORTED, "user-annotation spans across shards are not implemented");
   if (c->h_counters->device_check)
     return fail(c, K2J_ERR_DEVICE_CHECK, "%llu device-side checks failed (string id, table or output bound)",
                 (unsigned long long)c->h_counters->device_check);
+  c->ran = sink.mode == 0;  // only a run that completed without a failed check leaves text to serve
+  c->streamed = sink.mode != 0;
   return K2J_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+k2j_status k2j_emit(k2j_ctx* c, k2j_result* res) { return emit_core(c, res, TileSink{}); }
+
+k2j_status k2j_emit_to_host(k2j_ctx* c, void* host_dst, uint64_t capacity, uint64_t slab_bytes, k2j_result* res) {
+  TileSink sink;
+  sink.mode = 1; sink.host = static_cast<uint8_t*>(host_dst); sink.capacity = capacity; sink.slab_bytes = slab_bytes;
+  return emit_core(c, res, sink);
+}
+
+k2j_status k2j_emit_to_fd(k2j_ctx* c, int fd, uint64_t slab_bytes, k2j_result* res) {
+  if (c && fd < 0) return fail(c, K2J_ERR_INVALID_ARGUMENT, "bad file descriptor");
+  TileSink sink;
+  sink.mode = 2; sink.fd = fd; sink.slab_bytes = slab_bytes;
+  return emit_core(c, res, sink);
 }
 
 k2j_status k2j_run(k2j_ctx* c, k2j_result* res) {
@@ -878,45 +1037,56 @@ k2j_status k2j_copy_output_async(k2j_ctx* c, void* dst, uint64_t cap) {
 // Streams bytes [begin, begin + total) of the output to `fd` in chunks through the two pinned staging buffers: the
 // copy of chunk i overlaps the write of chunk i - 1.  `positioned`: pwrite at file_offset, else write at the
 // descriptor's position.
-static k2j_status stream_output(k2j_ctx* c, int fd, bool positioned, uint64_t file_offset, uint64_t begin, uint64_t total) {
+}  // extern "C"
+namespace {
+k2j_status stream_bytes(k2j_ctx* c, const uint8_t* src, int fd, bool positioned, uint64_t file_offset, uint64_t total, cudaStream_t stream) {
   constexpr size_t kChunk = 16u << 20;
   for (int i = 0; i < 2; i++) {
     if (!c->h_stage[i]) K2J_CUDA(c, cudaMallocHost(&c->h_stage[i], kChunk));
     if (!c->stage_ev[i]) K2J_CUDA(c, cudaEventCreateWithFlags(&c->stage_ev[i], cudaEventDisableTiming));
   }
+  int io_errno = 0;
   auto write_all = [&](const char* p, size_t n, uint64_t off) -> bool {
     while (n) {
       const ssize_t w = positioned ? pwrite(fd, p, n, (off_t)off) : write(fd, p, n);
-      if (w < 0) { if (errno == EINTR) continue; return false; }
+      if (w < 0) { if (errno == EINTR) continue; io_errno = errno; return false; }
+      if (w == 0) { io_errno = EIO; return false; }  // no progress on a non-empty write
       p += w; n -= (size_t)w; off += (uint64_t)w;
     }
     return true;
   };
   const uint64_t n_chunks = (total + kChunk - 1) / kChunk;
   bool io_ok = true;
-  for (uint64_t i = 0; i <= n_chunks; i++) {
+  cudaError_t e = cudaSuccess;
+  for (uint64_t i = 0; i <= n_chunks && e == cudaSuccess; i++) {
     if (i < n_chunks) {  // chunk i starts its way to the host ...
       const size_t len = (size_t)std::min<uint64_t>(kChunk, total - i * kChunk);
-      K2J_CUDA(c, cudaMemcpyAsync(c->h_stage[i & 1], c->out.as<uint8_t>() + begin + i * kChunk, len, cudaMemcpyDeviceToHost, c->stream));
-      K2J_CUDA(c, cudaEventRecord(c->stage_ev[i & 1], c->stream));
+      e = cudaMemcpyAsync(c->h_stage[i & 1], src + i * kChunk, len, cudaMemcpyDeviceToHost, stream);
+      if (e == cudaSuccess) e = cudaEventRecord(c->stage_ev[i & 1], stream);
     }
-    if (i > 0) {         // ... while chunk i - 1, which has arrived, goes to the file
-      K2J_CUDA(c, cudaEventSynchronize(c->stage_ev[(i - 1) & 1]));
+    if (i > 0 && e == cudaSuccess) {  // ... while chunk i - 1, which has arrived, goes to the file
+      e = cudaEventSynchronize(c->stage_ev[(i - 1) & 1]);
       const size_t len = (size_t)std::min<uint64_t>(kChunk, total - (i - 1) * kChunk);
-      if (io_ok && !write_all(static_cast<const char*>(c->h_stage[(i - 1) & 1]), len, file_offset + (i - 1) * kChunk))
+      if (e == cudaSuccess && io_ok && !write_all(static_cast<const char*>(c->h_stage[(i - 1) & 1]), len, file_offset + (i - 1) * kChunk))
         io_ok = false;  // keep draining the copies
     }
   }
-  if (!io_ok) return fail(c, K2J_ERR_IO, "write: %s", strerror(errno));
+  if (e != cudaSuccess) {
+    cudaStreamSynchronize(stream);  // no copy into the staging buffers stays in flight behind this call
+    return fail(c, K2J_ERR_CUDA, "streaming the output: %s", cudaGetErrorString(e));
+  }
+  if (!io_ok) return fail(c, K2J_ERR_IO, "write: %s", strerror(io_errno));
   return K2J_OK;
 }
+}  // namespace
+extern "C" {
 
 k2j_status k2j_write_output(k2j_ctx* c, int fd, uint64_t* written) {
   if (!c) return K2J_ERR_INVALID_ARGUMENT;
   if (!c->ran) return fail(c, K2J_ERR_STATE, "no completed run");
   if (fd < 0) return fail(c, K2J_ERR_INVALID_ARGUMENT, "bad file descriptor");
   K2J_CUDA(c, cudaSetDevice(c->device));
-  k2j_status st = stream_output(c, fd, false, 0, 0, c->out_bytes);
+  k2j_status st = stream_bytes(c, c->out.as<uint8_t>(), fd, false, 0, c->out_bytes, c->stream);
   if (st) return st;
   if (written) *written = c->out_bytes;
   return K2J_OK;
@@ -928,7 +1098,7 @@ k2j_status k2j_write_output_at(k2j_ctx* c, int fd, uint64_t file_offset, uint64_
   if (fd < 0) return fail(c, K2J_ERR_INVALID_ARGUMENT, "bad file descriptor");
   if (begin > c->out_bytes || n_bytes > c->out_bytes - begin) return fail(c, K2J_ERR_INVALID_ARGUMENT, "range outside the output");
   K2J_CUDA(c, cudaSetDevice(c->device));
-  return stream_output(c, fd, true, file_offset, begin, n_bytes);
+  return stream_bytes(c, c->out.as<uint8_t>() + begin, fd, true, file_offset, n_bytes, c->stream);
 }
 
 k2j_status k2j_synchronize(k2j_ctx* c) {

@@ -156,7 +156,9 @@ struct Dev {
   uint32_t* corr_zero;     // one bit per correlation-table slot: the entry links to a CPU op whose id is 0
   uint32_t* ev_size; const uint64_t* ev_off; uint64_t n_events;
   int32_t* ev_ext;        // per event: id of the linked CPU op found by the size pass (0 = none)
-  uint8_t* out; uint64_t out_cap;
+  uint8_t* out; uint64_t out_cap;  // address of output byte 0 (of the whole text), bytes of the whole text
+  uint64_t tile_begin, tile_end;   // this launch writes the events whose text starts in [tile_begin, tile_end): the whole
+                                   // text, or one slab of a tiled run (then `out` points outside the slab for other bytes)
   Counters* counters;
 };
 
@@ -2029,7 +2031,8 @@ __global__ void __launch_bounds__(kEventThreads, WRITE ? 5 : 8) k_events(Dev d) 
       if (size) {
         off = d.ev_off[ev];
         if (cls != C_OP) ext = d.ev_ext[ev];
-        if (size < kMinEventBytes || off + size > d.out_cap) { atomicAdd(&d.counters->device_check, 1ull); size = 0; }
+        if (off < d.tile_begin || off >= d.tile_end) size = 0;  // another slab's event
+        else if (size < kMinEventBytes || off + size > d.out_cap) { atomicAdd(&d.counters->device_check, 1ull); size = 0; }
       }
       if (!size) { r = nullptr; cls = -1; }
     }
@@ -2088,6 +2091,33 @@ __global__ void __launch_bounds__(kEventThreads, WRITE ? 5 : 8) k_events(Dev d) 
       if (s_cnt[3]) atomicAdd(&d.counters->blocklisted_runtime, s_cnt[3]);
       if (s_cnt[4]) atomicAdd(&d.counters->name_bytes, s_cnt[4]);
     }
+  }
+}
+
+// ---- tiled runs: which events and which work items belong to each slab of the output ----
+// Slab t holds the events whose text starts in [t * slab, (t + 1) * slab).  bounds is a (n_tiles + 1) x
+// kTileCols table: column 0 the first event of the slab, column 1 its first byte, columns 2 + c the first work
+// item of class c (C_API .. C_WAIT) whose event belongs to the slab or a later one.  Work items of a class are
+// in event order unless events were sorted by start time (then the launches of a slab cover whole classes
+// and the kernels skip the other slabs' events by their offsets).
+constexpr int kTileCols = 2 + C_EXT;
+__global__ void k_tile_bounds(Dev d, uint64_t slab, uint32_t n_tiles, uint64_t total, uint64_t* bounds) {
+  const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t > n_tiles) return;
+  uint64_t e = d.n_events;
+  if (t < n_tiles) {  // first event that starts at or after t * slab
+    const uint64_t target = (uint64_t)t * slab;
+    uint64_t lo = 0, hi = d.n_events;
+    for (int it = 0; it < 40 && lo < hi; it++) { const uint64_t mid = lo + ((hi - lo) >> 1); if (d.ev_off[mid] < target) lo = mid + 1; else hi = mid; }
+    e = lo;
+  }
+  uint64_t* row = bounds + (uint64_t)t * kTileCols;
+  row[0] = e;
+  row[1] = e < d.n_events ? d.ev_off[e] : total;
+  for (int c = 0; c < C_EXT; c++) {  // first work item of the class whose event number is >= e
+    uint64_t lo = d.cls_begin[c], hi = d.cls_begin[c] + d.cls_count[c];
+    for (int it = 0; it < 40 && lo < hi; it++) { const uint64_t mid = lo + ((hi - lo) >> 1); if ((uint64_t)d.work_ev[mid] < e) lo = mid + 1; else hi = mid; }
+    row[2 + c] = lo;
   }
 }
 

@@ -73,6 +73,34 @@ def _ident(rng: np.random.Generator, length: int) -> str:
     return s
 
 
+_cxa = None
+
+
+def demangles(name: bytes) -> bool:
+    """Does abi::__cxa_demangle accept `name`?  The reference shows kernel names through it
+    (libkineto/src/Demangle.cpp:30-50), and it accepts more than `_Z...` symbols: any string that parses as a
+    mangled TYPE demangles too ("G77" + 77 characters is an imaginary type of that name).  The library takes names
+    that are already demangled, so the generators only hand out names the demangler leaves alone."""
+    global _cxa
+    if _cxa is None:
+        import ctypes
+        import ctypes.util
+        lib = ctypes.CDLL(ctypes.util.find_library("stdc++") or "libstdc++.so.6")
+        libc = ctypes.CDLL(ctypes.util.find_library("c") or "libc.so.6")
+        lib.__cxa_demangle.restype = ctypes.c_void_p
+        lib.__cxa_demangle.argtypes = [ctypes.c_char_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int)]
+        libc.free.argtypes = [ctypes.c_void_p]
+        _cxa = (ctypes, lib, libc)
+    ctypes, lib, libc = _cxa
+    if b"\0" in name:
+        name = name.split(b"\0")[0]
+    status = ctypes.c_int(0)
+    p = lib.__cxa_demangle(name, None, None, ctypes.byref(status))
+    if p:
+        libc.free(p)
+    return status.value == 0
+
+
 def name_pool(rng, count: int, lo: int, hi: int, escape_fraction: float = 0.0) -> list[bytes]:
     """`count` distinct ASCII identifiers of length uniform in [lo, hi].  A fraction carries bytes
     the JSON writer treats specially: quote, backslash, newline, TAB/control, UTF-8 multibyte."""
@@ -89,7 +117,7 @@ def name_pool(rng, count: int, lo: int, hi: int, escape_fraction: float = 0.0) -
                 pos = int(rng.integers(1, len(b)))
                 b[pos:pos] = sp
             s = bytes(b[:max(n, 2)]) if len(b) > hi else bytes(b)
-        if s not in seen:
+        if s not in seen and not demangles(s):
             seen.add(s)
             out.append(s)
     return out
@@ -526,19 +554,34 @@ def ns_to_ticks(ns, conv):
 
 
 def gen_mixed(n=10_000_000, seed=3, n_devices=8, n_streams=32, pool_size=50_000, name_len=(20, 400),
-              escape_fraction=0.02, orphan_fraction=0.05, buffer_bytes=4 << 20) -> tf.Trace:
+              escape_fraction=0.02, orphan_fraction=0.05, buffer_bytes=4 << 20, shard=(0, 1), cross_fraction=0.05) -> tf.Trace:
     """Mixed trace: 60 % kernels, 20 % memcpy (bytes log-uniform 4 B..1 GB; HtoD/DtoH/DtoD/PtoP
     uniform, PtoP as MEMCPY2 records), 5 % memset, 15 % runtime-only calls; every GPU activity has a
     launching runtime record and an EXTERNAL_CORRELATION record; `orphan_fraction` of the
-    correlation ids have no CPU op; `escape_fraction` of the names carry JSON-special bytes."""
-    rng = np.random.default_rng(seed)
-    pool = tf.StringPool()
-    names = np.array([pool.add(s) for s in name_pool(rng, pool_size, *name_len, escape_fraction=escape_fraction)], np.uint64)
+    correlation ids have no CPU op; `escape_fraction` of the names carry JSON-special bytes.
+
+    `shard=(r, w)`: the trace has w*n activities and this call returns the r-th contiguous record range (string
+    pool, window and id ranges are those of the whole trace).  `cross_fraction` of a shard's kernel records belong
+    to launches at the end of the shard before it (GPU records arrive after their launch), so their
+    EXTERNAL_CORRELATION record and CPU op live in that shard."""
+    r, w = shard
+    lo = r * n
     t0 = DEFAULT_BASE_TIME + 1_000_000_000
+    if w == 1:
+        rng = np.random.default_rng(seed)
+        pool = tf.StringPool()
+        names = np.array([pool.add(s) for s in name_pool(rng, pool_size, *name_len, escape_fraction=escape_fraction)], np.uint64)
+        first_start = t0
+    else:
+        g = np.random.default_rng(seed)  # global draws: identical in every shard
+        pool = tf.StringPool()
+        names = np.array([pool.add(s) for s in name_pool(g, pool_size, *name_len, escape_fraction=escape_fraction)], np.uint64)
+        rng = np.random.default_rng([seed, r])
+        first_start = t0 + lo * 3002  # shards follow each other in time (mean gap between launches: 3001 ns)
     cls = rng.choice(4, n, p=[0.60, 0.20, 0.05, 0.15])  # 0 kernel 1 memcpy 2 memset 3 runtime-only
-    op_starts = _monotone_starts(rng, n, t0, 3000.0)
-    ops, thr = _cpu_ops(rng, pool, n, op_starts, DEFAULT_PID)
-    corr = (np.arange(n, dtype=np.int64) + 1000).astype(np.uint32)
+    op_starts = _monotone_starts(rng, n, first_start, 3000.0)
+    ops, thr = _cpu_ops(rng, pool, n, op_starts, DEFAULT_PID, id_base=lo)
+    corr = (np.arange(lo, lo + n, dtype=np.int64) + 1000).astype(np.uint32)
 
     gpu = cls < 3
     ext = np.zeros(n, tf.EXTCORR)
@@ -558,7 +601,12 @@ def gen_mixed(n=10_000_000, seed=3, n_devices=8, n_streams=32, pool_size=50_000,
 
     gstart = api["start"].astype(np.int64) + rng.integers(3000, 200_000, n)
     ik, im, iset = np.nonzero(cls == 0)[0], np.nonzero(cls == 1)[0], np.nonzero(cls == 2)[0]
-    kern = _kernel_records(rng, len(ik), names, gstart[ik], _lognormal_dur(rng, len(ik)), corr[ik], n_devices, n_streams)
+    kcorr = corr[ik]
+    if r > 0 and cross_fraction > 0:  # late arrivals: GPU records of launches near the end of the previous shard
+        late = np.random.default_rng([seed, r, 1]).random(len(ik)) < cross_fraction
+        back = np.random.default_rng([seed, r, 2]).integers(1, min(n, 50_000) + 1, len(ik))
+        kcorr = np.where(late, (lo - back + 1000).astype(np.uint32), kcorr)
+    kern = _kernel_records(rng, len(ik), names, gstart[ik], _lognormal_dur(rng, len(ik)), kcorr, n_devices, n_streams)
 
     nbytes = np.exp(rng.uniform(np.log(4), np.log(1 << 30), len(im))).astype(np.uint64)
     mkind = rng.integers(0, 4, len(im))  # HtoD DtoH DtoD PtoP
@@ -639,8 +687,11 @@ def gen_mixed(n=10_000_000, seed=3, n_devices=8, n_streams=32, pool_size=50_000,
     t = ops
     t.cupti, offs = tf.interleave([ext, api, kern, mc, pp, ms], order)
     t.buftab = tf.make_buftab(offs, buffer_bytes)
-    last = max(int(kern["end"].max()) if len(kern) else 0, int(api["end"].max()))
-    window = (t0 - 1000, last + 1_000_000)
+    if w == 1:
+        last = max(int(kern["end"].max()) if len(kern) else 0, int(api["end"].max()))
+        window = (t0 - 1000, last + 1_000_000)
+    else:  # one window for the whole trace, the same in every shard
+        window = (t0 - 1000, t0 + w * n * 3002 + 200 * n + 100_000_000_000)
     return _finish(t, pool, 1, window, n_devices)
 
 

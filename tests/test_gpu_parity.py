@@ -314,3 +314,58 @@ def test_full_size_against_reference():
     got, res = gpu_run(t)
     assert len(got) == len(want)
     assert got == want, helpers.first_diff(want, got)
+
+
+@pytest.mark.parametrize("gen", [
+    lambda: synth.gen_mixed(120_000, seed=301, pool_size=3000, escape_fraction=0.05),
+    lambda: synth.gen_kernel_launches(60_000, seed=302, pool_size=300, user_annotations=40),
+    lambda: cases.with_flags(synth.gen_mixed(90_000, seed=303, pool_size=2000), tf.FLAG_SORT_BY_START),
+    lambda: cases.sync_mix_trace(60_000, seed=304),
+    lambda: synth.gen_distributed_rank(40_000, rank=1, seed=305),
+    lambda: synth.gen_kernel_launches(30_000, seed=306, pool_size=300, memory_events=0.5),
+    lambda: synth.gen_op_tree(30_000, seed=307),
+    cases.edge_trace,
+])
+def test_tiled_emit_equals_resident_emit(gen, tmp_path):
+    """The text produced slab by slab (to host memory, and to a file descriptor) is the text of a run that keeps it
+    whole on the device: slabs of 4 MiB (the smallest), so that every trace here spans several slabs, the user
+    annotation spans leave as a slab of their own, and classes start and end inside slabs."""
+    import torch
+    from kineto_b200 import api
+    trace = gen()
+    want, res0 = gpu_run(trace)
+    ctx = api.K2J(0)
+    try:
+        ctx.load(trace)
+        ctx.segment()
+        dst = torch.empty(len(want) + 64, dtype=torch.uint8).pin_memory()
+        dst.fill_(0x55)
+        res = ctx.emit_to_host(dst, 4 << 20)
+        assert res["out_bytes"] == len(want)
+        got = dst[:len(want)].numpy().tobytes()
+        assert got == want, helpers.first_diff(want, got)
+        assert bytes(dst[len(want):].numpy().tobytes()) == b"\x55" * 64   # nothing past the text
+        for k in ("x_events", "flow_events", "out_of_range_events", "ops_bytes", "annotation_bytes"):
+            assert res[k] == res0[k], k
+        with pytest.raises(api.K2JError):   # no text stays in the context
+            ctx.output_ptr()
+        path = tmp_path / "tiled.json"
+        fd = os.open(path, os.O_WRONLY | os.O_CREAT | os.O_TRUNC)
+        try:
+            os.write(fd, b"HEADER")
+            ctx.segment()
+            res2 = ctx.emit_to_fd(fd, 4 << 20)
+        finally:
+            os.close(fd)
+        assert res2["out_bytes"] == len(want)
+        assert path.read_bytes() == b"HEADER" + want
+        small = torch.empty(max(1, len(want) // 2), dtype=torch.uint8).pin_memory()
+        ctx.segment()
+        with pytest.raises(api.K2JError) as e:
+            ctx.emit_to_host(small, 4 << 20)
+        assert e.value.status == 1
+        # and the context still serves an ordinary run afterwards
+        assert ctx.run()["out_bytes"] == len(want)
+        assert ctx.copy_output().tobytes() == want
+    finally:
+        ctx.close()
