@@ -152,16 +152,21 @@ def test_write_output_streams_the_same_bytes(tmp_path):
         ctx.close()
 
 
-def test_measure_module_runs():
-    """python -m kineto_b200.measure: one JSON line with stage times for another workload."""
+def test_bench_runs_another_workload():
+    """bench.py --workload: one JSON line with the contract's keys for a workload other than the default, small
+    enough for a test, with the text that travelled to the host equal to the resident run's and the sha256 of the
+    sample equal to the reference's (or, without the reference build, to the CPU restatement's)."""
     import json
     import subprocess
     import sys
-    r = subprocess.run([sys.executable, "-m", "kineto_b200.measure", "--workload", "distributed_rank", "--n", "20000", "--runs", "2"],
-                       capture_output=True, text=True, cwd=helpers.ROOT)
+    r = subprocess.run([sys.executable, os.path.join(helpers.ROOT, "bench.py"), "--workload", "distributed_rank", "--n", "20000",
+                        "--steps", "2", "--warmup", "3", "--cpu-sample", "5000"], capture_output=True, text=True, cwd=helpers.ROOT)
     assert r.returncode == 0, r.stderr[-1000:]
     line = json.loads(r.stdout.strip().splitlines()[-1])
-    assert line["records"] == 80_000 and line["ms_emit"] > 0 and line["out_bytes"] > 10_000_000
+    assert line["records_per_step"] == 80_000 and line["stage_ms_per_step"]["ms_emit"] > 0 and line["output_bytes_per_step"] > 10_000_000
+    assert line["e2e"]["text_equals_resident_run"] is True and line["e2e"]["d2h_bytes_per_step"] == line["output_bytes_per_step"]
+    assert line["parity"]["sha256_match"] is True and line["cpu_baseline"]["value"] > 0
+    assert line["roofline"]["frac"] > 0 and line["gpu_launches"] > 0
 
 
 def test_empty_and_degenerate_inputs():
