@@ -70,6 +70,12 @@ typedef struct {
 #define K2J_FLAG_PID0_OVERRIDE 4    /* CPU activities with device 0 are shown under params.pid: what
                                        ActivityTrace::save() writes after the pid-0 override of
                                        GenericActivityProfiler.cpp:263-271 */
+#define K2J_FLAG_UNFINISHED_OPS 8   /* CPU activities whose end precedes their start had not ended when the trace
+                                       stopped: they end at window_end_ns (processCpuTrace,
+                                       GenericActivityProfiler.cpp:255-258).  The "finished": false entry such an
+                                       activity gains there is part of its metadata like any other: the caller lists
+                                       it (K2J_MD_RAWJSON, text false) where the fixed-up activity visits it.  Without
+                                       the flag (a logger driven directly) such an activity lasts 0 ns. */
 
 /* cudaDeviceProp fields read by blocksPerSm / warpsPerSm / computeOccupancyMetrics
  * (libkineto/src/DeviceProperties.cpp:161-222). */
@@ -88,7 +94,11 @@ typedef struct {
   uint32_t type;  /* K2J_MD_* */
   uint64_t value; /* int64 / uint64 / double bits / bool / string id */
 } k2j_md_entry;
-enum { K2J_MD_INT64 = 0, K2J_MD_UINT64 = 1, K2J_MD_DOUBLE = 2, K2J_MD_BOOL = 3, K2J_MD_STRING = 4, K2J_MD_RAWJSON = 5 };
+enum { K2J_MD_INT64 = 0, K2J_MD_UINT64 = 1, K2J_MD_DOUBLE = 2, K2J_MD_BOOL = 3, K2J_MD_STRING = 4, K2J_MD_RAWJSON = 5,
+       K2J_MD_COUNTER = 6 /* a counter value (GenericTraceActivity::counterValues(), name and double bits) of an activity
+                             of type MTIA_COUNTERS, XPU_SCOPE_PROFILER or HARDWARE_COUNTERS, in the list's order after
+                             the other entries; such activities are written as counter events
+                             (libkineto/src/output_json.cpp:679-716) and their other entries are not printed */ };
 
 /* Columns of the CPU-side activities (libkineto::GenericTraceActivity fields,
  * libkineto/include/GenericTraceActivity.h:173-192): all arrays have n_ops elements except
@@ -173,8 +183,9 @@ k2j_status k2j_set_ops(k2j_ctx* ctx, const k2j_ops* ops);
  * Kinds that are sized and formatted: CONCURRENT_KERNEL (CUpti_ActivityKernel9), MEMCPY (Memcpy5), MEMCPY2
  * (MemcpyPtoP4), MEMSET (Memset4), RUNTIME / DRIVER (ActivityAPI), EXTERNAL_CORRELATION, OVERHEAD (Overhead3),
  * SYNCHRONIZATION (ActivitySynchronization) and CUDA_EVENT (CudaEvent2)
- * (libkineto/src/CuptiActivityProfiler.cpp:532-588).  A record of any other kind ends the walk of its buffer and
- * is counted in unexpected_cuda_events. */
+ * (libkineto/src/CuptiActivityProfiler.cpp:532-588).  A record of any other kind that the CUDA 12.9 CUPTI headers
+ * define is stepped over by the size of that kind's structure and counted in unexpected_cuda_events, as the
+ * reference counts it (:583-587); a kind the headers do not define ends the walk of its buffer (counted once). */
 k2j_status k2j_set_cupti(k2j_ctx* ctx, const uint8_t* bytes, uint64_t n_bytes, const uint64_t* buftab,
                          uint32_t n_buffers);
 
@@ -239,7 +250,11 @@ k2j_status k2j_exclusive_scan_u32(k2j_ctx* ctx, const uint32_t* sizes, uint64_t 
  * n above K2J_NOALLOC_SCAN_MAX is rejected with K2J_ERR_INVALID_ARGUMENT.  The first call on a device
  * looks up the scratch address and should come before any stream capture on that device.  All calls
  * on a device share the scratch: calls whose kernels could overlap on the GPU race and must be
- * ordered by the caller; nothing in the scratch needs clearing between calls. */
+ * ordered by the caller; nothing in the scratch needs clearing between calls.  With CUDA's default lazy
+ * module loading the driver sets the kernels and the array up (and allocates for them) when they are first
+ * used: one call with n >= 1 per device, or CUDA_MODULE_LOADING=EAGER, belongs before any region that must
+ * not allocate.  The looked-up address does not survive cudaDeviceReset: do not use the entry point across
+ * one.  The caller's current device is the same after the call as before. */
 #define K2J_NOALLOC_SCAN_MAX (1ull << 24)
 k2j_status k2j_exclusive_scan_u32_noalloc(int device, void* stream, const uint32_t* sizes, uint64_t n,
                                           uint64_t* offsets, uint64_t* total);

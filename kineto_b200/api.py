@@ -159,7 +159,7 @@ class K2J:
     def set_params(self, trace: tf.Trace):
         p = trace.params[0]
         cp = Params(int(p["base_time_ns"]), int(p["window_start_ns"]), int(p["window_end_ns"]), int(p["pid"]),
-                    int(p["ts_mode"]), int(p["flags"]) | (4 if int(p["mode"]) == 1 else 0), int(p["n_devices"]), int(p["conv_t0"]),
+                    int(p["ts_mode"]), int(p["flags"]) | (12 if int(p["mode"]) == 1 else 0), int(p["n_devices"]), int(p["conv_t0"]),
                     int(p["conv_t0_approx"]), int(p["conv_scale_mant"]), int(p["conv_scale_exp"]),
                     activity_type_mask(int(p["mode"]), int(p["flags"])))
         n = int(p["n_devices"])
@@ -300,6 +300,9 @@ def device_arrays(trace: tf.Trace, device="cuda:0") -> dict:
         elif a.dtype == np.uint32:
             a = a.view(np.int32)
         out[k] = torch.from_numpy(a).to(device)
+    # the copies ran on torch's current stream; a context reads the arrays on its own stream (see include/k2j.h on
+    # device memory handed to the library), so they are made complete here
+    torch.cuda.synchronize(device)
     return out
 
 

@@ -10,7 +10,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB = os.path.join(HERE, "libk2j.so")
 SRC = os.path.join(HERE, "csrc", "k2j.cu")
 SRC_NOALLOC = os.path.join(HERE, "csrc", "k2j_noalloc.cu")
-DEPS = [SRC, SRC_NOALLOC] + [os.path.join(HERE, "csrc", f) for f in ("k2j_kernels.cuh", "k2j_format.cuh", "k2j_sink.cuh", "k2j_sort.cuh", "k2j_pow10.h")] + [
+DEPS = [SRC, SRC_NOALLOC] + [os.path.join(HERE, "csrc", f) for f in ("k2j_kernels.cuh", "k2j_format.cuh", "k2j_sink.cuh", "k2j_sort.cuh", "k2j_pow10.h", "k2j_cupti_sizes.h")] + [
     os.path.join(os.path.dirname(HERE), "include", "k2j.h")]
 
 

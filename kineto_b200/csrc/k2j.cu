@@ -87,6 +87,7 @@ struct k2j_ctx {
   bool streamed = false;                             // the last run handed its text on slab by slab: no resident output
   DevBuf ctx_tab, evt_recs, seen_tab, row_key, row_first, corr_zero;  // synchronisation records
   DevBuf str_class, comms_flag, coll_list;                            // collective enrichment
+  DevBuf corr0;                                                       // correlation id 0 (see Dev::corr0)
   const void* g_ext = nullptr; uint64_t g_n_ext = 0, g_own_begin = 0;
   const int32_t* g_op_ids = nullptr; uint64_t g_n_ops = 0;
 };
@@ -323,7 +324,7 @@ void k2j_destroy(k2j_ctx* c) {
                     &c->span_out, &c->span_cnt, &c->ann_size, &c->ann_off, &c->sort_keys[0], &c->sort_keys[1], &c->sort_vals[0],
                     &c->sort_vals[1], &c->sort_hist, &c->sort_base, &c->sort_rank, &c->tid_tab, &c->corr_tab, &c->user_tab, &c->op_tab,
                     &c->work_slot, &c->work_ev, &c->ev_size, &c->ev_off, &c->ev_ext, &c->out, &c->counters, &c->ext_local, &c->ctx_tab, &c->evt_recs,
-                    &c->seen_tab, &c->row_key, &c->row_first, &c->corr_zero, &c->str_class, &c->comms_flag, &c->coll_list})
+                    &c->seen_tab, &c->row_key, &c->row_first, &c->corr_zero, &c->str_class, &c->comms_flag, &c->coll_list, &c->corr0})
     b->release();
   if (c->h_totals) cudaFreeHost(c->h_totals);
   if (c->h_counters) cudaFreeHost(c->h_counters);
@@ -687,6 +688,9 @@ k2j_status emit_core(k2j_ctx* c, k2j_result* res, const TileSink& sink) {
   d.user_tab = c->user_tab.as<unsigned long long>(); d.user_mask = corr_cap - 1;
   d.op_tab = c->op_tab.as<unsigned long long>(); d.op_mask = op_cap - 1;
   K2J_CUDA(c, cudaMemsetAsync(d.corr_tab, 0, (size_t)corr_cap * 8, s));
+  K2J_CUDA(c, c->corr0.reserve(16));
+  d.corr0 = c->corr0.as<unsigned long long>();
+  K2J_CUDA(c, cudaMemsetAsync(d.corr0, 0, 16, s));
   // the user-annotation table is only written and read when CUSTOM1 correlation records exist
   if (c->have_global_join || totals[C_USER] > 0) K2J_CUDA(c, cudaMemsetAsync(d.user_tab, 0, (size_t)corr_cap * 8, s));
   K2J_CUDA(c, cudaMemsetAsync(d.op_tab, 0, (size_t)op_cap * 8, s));

@@ -20,6 +20,7 @@
 #include <limits.h>
 #include <stdint.h>
 
+#include "k2j_cupti_sizes.h"
 #include "k2j_format.cuh"
 #include "k2j_sink.cuh"
 
@@ -64,6 +65,17 @@ __host__ __device__ constexpr uint32_t slot_code(uint32_t kind, uint32_t word1) 
     default: return 0u;
   }
 }
+// A kind the path does not format (the reference counts it and goes on, CuptiActivityProfiler.cpp:583-587): the walk
+// steps over it by the size of the kind's record in the CUPTI headers.  Its code has no class: group 0, or group 3
+// for the one length that group 0 uses already.  0: a kind the headers do not know; it ends the walk of its buffer.
+__host__ __device__ constexpr uint32_t skip_code_of_slots(uint32_t n) { return n == 0u ? 0u : (n == (kCodeApi & 31u) ? n | (3u << 5) : n); }
+struct SkipCodes { uint8_t c[kCuptiKinds]; };
+constexpr SkipCodes make_skip_codes() {
+  SkipCodes t{};
+  for (int k = 0; k < kCuptiKinds; k++) t.c[k] = slot_code((uint32_t)k, 0u) != 0u ? 0 : (uint8_t)skip_code_of_slots(kCuptiRecordSlots[k]);
+  return t;
+}
+__constant__ SkipCodes g_skip_codes = make_skip_codes();
 // Slot class (C_API .. C_EXT_USER) of a slot code; 0xff for codes no record has.
 __host__ __device__ constexpr uint32_t code_slot_class(uint32_t code) {
   switch (code) {
@@ -133,6 +145,10 @@ struct Dev {
   uint32_t* need_corr; uint32_t need_corr_mask; uint32_t* need_op; uint32_t need_op_mask;
   // join tables: 64-bit entries (key << 32 | value + 1), 0 = empty
   unsigned long long* corr_tab; uint32_t corr_mask;
+  // Correlation id 0 has no table entry (an entry's resolved form, key << 32 | linked id, would be the empty-slot
+  // marker for it): [0] the winning CUSTOM0 record's position + 1, [1] after k_resolve_corr bit 33 "links to a
+  // CPU op", low half that op's id.
+  unsigned long long* corr0;
   unsigned long long* user_tab; uint32_t user_mask;
   unsigned long long* op_tab; uint32_t op_mask;
   // user-annotation spans (GpuUserEventMap): (device, stream) set, then (set slot, op id) -> span
@@ -325,14 +341,14 @@ __global__ void __launch_bounds__(kSegWarps * 32) k_seg_chunks(Dev d) {
   __shared__ uint8_t s_kind[64];     // slot code of record kinds 0..63 (CUSTOM1 correlation records add one class)
   __shared__ uint32_t s_inc[256][3]; // per slot code: increments of the three packed count words
   static_assert(kSegWarps * 32 == 256, "one thread per slot code");
-  if (threadIdx.x < 64) s_kind[threadIdx.x] = (uint8_t)slot_code(threadIdx.x, 0u);
+  if (threadIdx.x < 64) { const uint32_t c = slot_code(threadIdx.x, 0u); s_kind[threadIdx.x] = (uint8_t)(c != 0u ? c : g_skip_codes.c[threadIdx.x]); }
   {
     const uint32_t sc = code_slot_class(threadIdx.x), cls = sc == (uint32_t)C_EXT_USER ? (uint32_t)C_EXT : sc;
     uint32_t inc[3] = {0u, 0u, 0u};
     if (sc != 0xffu) {
       inc[cls >> 2] = 1u << (8 * (cls & 3u));
       if (sc == (uint32_t)C_EXT_USER) inc[C_USER >> 2] += 1u << (8 * (C_USER & 3));
-    }
+    } else if ((threadIdx.x & 31u) != 0u) inc[C_UNEXPECTED >> 2] = 1u << (8 * (C_UNEXPECTED & 3));  // a record that is stepped over
     s_inc[threadIdx.x][0] = inc[0]; s_inc[threadIdx.x][1] = inc[1]; s_inc[threadIdx.x][2] = inc[2];
   }
   __syncthreads();
@@ -504,9 +520,9 @@ __global__ void __launch_bounds__(kSegWarps * 32) k_seg_write(Dev d) {
   const uint32_t lt = (1u << lane) - 1u;
   for (uint32_t i0 = 0; i0 < n; i0 += 32) {
     const uint32_t i = i0 + lane;
-    const bool on = i < n;
-    const uint32_t pos = on ? s_pos[w][i] : 0u;
-    const uint32_t cls = on ? code_class(codes[pos]) : 0xffu;
+    const uint32_t pos = i < n ? s_pos[w][i] : 0u;
+    const uint32_t cls = i < n ? code_class(codes[pos]) : 0xffu;
+    const bool on = cls != 0xffu;  // records of kinds that are only stepped over own nothing
     const uint32_t evm = __ballot_sync(0xffffffffu, on && cls < (uint32_t)C_WAIT);
     // rank within the class: the lanes holding records of one class find each other in one step
     const uint32_t peers = __match_any_sync(0xffffffffu, cls);
@@ -577,7 +593,8 @@ __global__ void k_find_comms(Dev d, uint32_t* flag, int comms_on) {
   if (i >= d.n_ops) return;
   const uint32_t name = d.op_name[i];
   if (comms_on && name < d.n_strings && d.str_class[name] == 1u) atomicOr(flag, 1u);
-  if (d.op_type[i] == 9) atomicOr(flag, 2u);  // an instant event: written by the same extra launch
+  const int type = d.op_type[i];
+  if (type == 9 || type == 17 || type == 26 || type == 28) atomicOr(flag, 2u);  // instant and counter events: written by the same extra launch
 }
 // CPU-op id -> position (last writer wins): activityMap_[id] = op, GenericActivityProfiler.cpp:262.
 __global__ void k_build_ops(Dev d) {
@@ -603,7 +620,8 @@ __global__ void k_build_corr(Dev d, uint64_t own_begin, uint64_t own_end) {
       if (!bit_test(d.need_corr, d.need_corr_mask, e.correlation_id)) return;
       if ((int64_t)e.external_id == (int64_t)(int32_t)e.external_id) bit_set(d.need_op, d.need_op_mask, (uint32_t)e.external_id);
     }
-    ok = tab_insert(d.corr_tab, d.corr_mask, e.correlation_id, (uint32_t)i);
+    if (e.correlation_id == 0u) atomicMax(&d.corr0[0], (unsigned long long)i + 1ull);
+    else ok = tab_insert(d.corr_tab, d.corr_mask, e.correlation_id, (uint32_t)i);
   } else if (e.external_kind == 4u) {
     atomicAdd(&d.counters->n_user, 1ull);
     if (d.need_corr == nullptr) ok = tab_insert(d.user_tab, d.user_mask, e.correlation_id, (uint32_t)i);  // spans: single-shard runs only
@@ -692,7 +710,9 @@ struct CountSink2 : CountSink {
 enum : uint8_t { T_NONE = 0, T_U64, T_I64, T_TS, T_DBL, T_NAME, T_CSTR, T_MD /* the metadata entries of a CPU-side activity */,
                  T_COLL = 11 /* collective metadata copied from the linked record_param_comms op */,
                  T_RAWSTR = 12 /* a pool string as it is */, T_RAWSTRIP /* ... minus one surrounding pair of quotes */,
-                 T_MDRAW /* metadata entries with keys and strings as they are */ };
+                 T_MDRAW /* metadata entries with keys and strings as they are */,
+                 T_MDCNT /* the counter values of a counter event: "name": value,... */,
+                 T_HWC /* one whole counter event per counter value (HARDWARE_COUNTERS) */ };
 enum : uint8_t { VK_U32 = 0, VK_I32 /* sign-extended */, VK_64 };
 struct FieldSrc { const char* lit; uint8_t type; uint8_t vk; uint16_t voff; };
 struct FieldDesc { uint16_t off, len; uint8_t type, vk; uint16_t voff; };
@@ -796,13 +816,16 @@ enum : int { M_CPY_KIND, M_CPY_SRC, M_CPY_DST, M_SET_KIND, M_PID, M_TID, M_TS, M
 // -- CPU-side activity (no record: every value is a slot): head, metadata entries, tail --
 enum : int { OS_CAT = 0, OS_NAME = 4, OS_PID = 8, OS_EXT = 12, OS_TID = 16, OS_TS = 24, OS_DUR = 32, OS_ROW = 40, OS_FLOW = 44, OS_FTS = 48 };
 enum : int { O_CAT, O_NAME, O_CNAME /* a constant-string name instead of a pool name */,
-             I_HEAD, I_NAME /* an instant event: libkineto/src/output_json.cpp:261-293, :660-676 */, O_PID, O_TID, O_TS, O_DUR, O_PAD, O_ARGS,
-             O_EXT, O_EXTC, O_MD, I_MD /* the same entries, nothing sanitised */,
+             I_HEAD, I_NAME /* an instant event: libkineto/src/output_json.cpp:261-293, :660-676 */,
+             C_HEAD, C_NAME /* a counter event: libkineto/src/output_json.cpp:294-316, :679-716 */, H_ALL /* HARDWARE_COUNTERS: one event per value */,
+             O_PID, O_TID, O_TS, O_DUR, O_PAD, O_ARGS,
+             O_EXT, O_EXTC, O_MD, I_MD /* the same entries, nothing sanitised */, C_MD /* counter values */,
              P_ARGS_CLOSE, P_CLOSE, P_FLOW_S, P_FLOW_F, P_FPID, P_FTID, P_FTS, P_FWDBWD, P_AC2G, P_FBP, P_FEND, O_COUNT };
 #define K2J_OPHEAD_FIELDS \
     {"\n  {\n    \"ph\": \"X\",\n    \"cat\": \"", T_CSTR, VK_U32, OS_CAT}, {"\",\n    \"name\": \"", T_NAME, VK_U32, OS_NAME}, \
     {"\",\n    \"name\": \"", T_CSTR, VK_U32, OS_NAME}, \
     {"\n  {\n    \"ph\": \"i\",\n    \n    \"cat\": \"", T_CSTR, VK_U32, OS_CAT}, {"\",\n    \"s\": \"t\",\n    \"name\": \"", T_RAWSTR, VK_U32, OS_NAME}, \
+    {"\n  {\n    \"ph\": \"C\",\n    \"cat\": \"", T_CSTR, VK_U32, OS_CAT}, {"\",\n    \"name\": \"", T_RAWSTR, VK_U32, OS_NAME}, {"", T_HWC, VK_U32, OS_ROW}, \
     {"\",\n    \"pid\": ", T_I64, VK_I32, OS_PID}, \
     {",\n    \"tid\": ", T_I64, VK_64, OS_TID}, {",\n    \"ts\": ", T_TS, VK_64, OS_TS}, {",\n    \"dur\": ", T_TS, VK_64, OS_DUR}, {"\n    ", T_NONE}, \
     {",\n    \"args\": {\n      ", T_NONE}, {"\"External id\": ", T_I64, VK_I32, OS_EXT}, {",", T_NONE}
@@ -853,7 +876,7 @@ enum : int { Y_MROW1, Y_MPID1, Y_MTID1, Y_MNAME, Y_MROW2, Y_MPID2, Y_MTID2, Y_MS
 
 // One table for everything: [api][kernel][mem][op head, metadata marker, op tail][annotation][sync][constant strings].
 enum : int { CS_TYPE = 0, CS_MEMCPY_KIND = 29, CS_MEMORY_KIND = 41, CS_LIMIT = 50, CS_OVERHEAD = 82, CS_SYNC = 93, CS_COLL = 98,
-             CS_COUNT = 114 };
+             CS_HWC = 114 /* the pieces of a HARDWARE_COUNTERS event */, CS_COUNT = 120 };
 #define K2J_CSTR_FIELDS \
     {"cpu_op", 0}, {"user_annotation", 0}, {"gpu_user_annotation", 0}, {"gpu_memcpy", 0}, {"gpu_memset", 0}, {"kernel", 0}, \
     {"external_correlation", 0}, {"cuda_runtime", 0}, {"cuda_driver", 0}, {"cpu_instant_event", 0}, {"python_function", 0}, \
@@ -880,14 +903,16 @@ enum : int { CS_TYPE = 0, CS_MEMCPY_KIND = 29, CS_MEMORY_KIND = 41, CS_LIMIT = 5
     {",\"Collective name\": ", 0}, {",\"In msg nelems\": ", 0}, {",\"Out msg nelems\": ", 0}, {",\"Group size\": ", 0}, \
     {",\"dtype\": ", 0}, {",\"Input Tensors start\": ", 0}, {",\"Output Tensors start\": ", 0}, {",\"In split size\": ", 0}, \
     {",\"Out split size\": ", 0}, {",\"Process Group Name\": ", 0}, {",\"Process Group Description\": ", 0}, \
-    {",\"Process Group Ranks\": ", 0}, {",\"Dst Rank\": ", 0}, {",\"Src Rank\": ", 0}, {",\"Seq\": ", 0}, {",\"Comms Id\": ", 0}
+    {",\"Process Group Ranks\": ", 0}, {",\"Dst Rank\": ", 0}, {",\"Src Rank\": ", 0}, {",\"Seq\": ", 0}, {",\"Comms Id\": ", 0}, \
+    {"\n  {\n    \"ph\": \"C\",\n    \"cat\": \"hardware_counters\",\n    \"name\": \"", 0}, {"\",\n    \"pid\": \"GPU ", 0}, \
+    {" Counters\",\n    \"tid\": ", 0}, {",\n    \"ts\": ", 0}, {",\n    \"args\": {\n      \"\": ", 0}, {"\n    }\n  },", 0}
 
 
 constexpr int API_BASE = 0, KERNEL_BASE = API_BASE + A_COUNT, MEM_BASE = KERNEL_BASE + K_COUNT, OP_BASE = MEM_BASE + M_COUNT,
               ANN_BASE = OP_BASE + O_COUNT, SYNC_BASE = ANN_BASE + N_COUNT, CSTR_BASE = SYNC_BASE + Y_COUNT,
               FIELD_COUNT = CSTR_BASE + CS_COUNT;
 constexpr FieldSrc kAllFields[] = {K2J_API_FIELDS, K2J_KERNEL_FIELDS, K2J_MEM_FIELDS, K2J_OPHEAD_FIELDS, {"", T_MD, VK_U32, OS_ROW},
-                                   {"", T_MDRAW, VK_U32, OS_ROW},
+                                   {"", T_MDRAW, VK_U32, OS_ROW}, {"", T_MDCNT, VK_U32, OS_ROW},
                                    K2J_OPTAIL_FIELDS, K2J_ANN_FIELDS, K2J_SYNC_FIELDS, K2J_CSTR_FIELDS};
 static_assert(sizeof(kAllFields) / sizeof(kAllFields[0]) == FIELD_COUNT, "field table and enums disagree");
 constexpr bool wide_values_aligned() {
@@ -974,6 +999,11 @@ __device__ __forceinline__ bool out_of_range(const Dev& d, int64_t ts, int64_t d
 // (or 0) in the entry's low half, so that an event needs a single probe.
 __global__ void k_resolve_corr(Dev d) {
   const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i == 0u && d.corr0[0] != 0ull) {  // correlation id 0
+    const int64_t ext = (int64_t)d.ext_all[d.corr0[0] - 1ull].external_id;
+    const bool linked = ext == (int64_t)(int32_t)ext && tab_find(d.op_tab, d.op_mask, (uint32_t)(int32_t)ext) != 0xFFFFFFFFu;
+    d.corr0[1] = linked ? ((1ull << 33) | (unsigned long long)(uint32_t)(int32_t)ext) : 0ull;
+  }
   if (i > d.corr_mask) return;
   const unsigned long long e = d.corr_tab[i];
   if (e == 0) return;
@@ -993,10 +1023,11 @@ __device__ __forceinline__ unsigned long long linked_op_peek(const Dev& d, uint3
 }
 __device__ __forceinline__ void linked_op(const Dev& d, uint32_t corr, unsigned long long first, int32_t* op_id) {
   if ((corr & 0x80000000u) || d.corr_tab == nullptr) return;
+  if (corr == 0u) { const unsigned long long z = d.corr0[1]; if ((z >> 33) & 1ull) *op_id = (int32_t)(uint32_t)z; return; }
   uint32_t i = hash32(corr) & d.corr_mask;
   unsigned long long e = first;
   for (uint32_t probes = 0; probes <= d.corr_mask; probes++) {
-    if (e == 0) return;  // empty, or correlation id 0 without a link
+    if (e == 0) return;  // an empty slot
     if ((uint32_t)(e >> 32) == corr) { *op_id = (int32_t)(uint32_t)e; return; }
     i = (i + 1) & d.corr_mask;
     e = d.corr_tab[i];
@@ -1151,6 +1182,7 @@ __device__ __forceinline__ bool wait_event_find(const Dev& d, uint32_t ctx, uint
 // CPU op whose id is 0" from "not linked" (k_resolve_corr leaves 0 in the entry for both and marks the former).
 __device__ __forceinline__ bool linked_op_full(const Dev& d, uint32_t corr, int32_t* id) {
   if ((corr & 0x80000000u) || d.corr_tab == nullptr) return false;
+  if (corr == 0u) { const unsigned long long z = d.corr0[1]; if ((z >> 33) & 1ull) { *id = (int32_t)(uint32_t)z; return true; } return false; }
   uint32_t i = hash32(corr) & d.corr_mask;
   for (uint32_t probes = 0; probes <= d.corr_mask; probes++) {
     const unsigned long long e = d.corr_tab[i];
@@ -1487,9 +1519,16 @@ __device__ __forceinline__ uint64_t gather_op(const Dev& d, uint64_t i, uint32_t
   const int32_t type = d.op_type[i];
   if ((uint32_t)type >= 29u) { atomicAdd(&d.counters->device_check, 1ull); return 0; }
   if (!((d.type_mask >> type) & 1u)) return 0;  // type not selected: joins, but is not logged
-  if (type == 17 || type == 26 || type == 28) {  // counter events (other profilers' activity types): not implemented
-    atomicAdd(&d.counters->device_check, 1ull);
-    return 0;
+  if (type == 17 || type == 26 || type == 28) {  // counter events: handleCounterEvent, output_json.cpp:679-716 (no duration, no flow, raw text)
+    s32(a, OS_CAT, (uint32_t)(CS_TYPE + type)); s32(a, OS_NAME, d.op_name[i]); s32(a, OS_PID, (uint32_t)op_pid(d, d.op_device[i]));
+    s64(a, OS_TID, (uint64_t)abs_tid(d.op_resource[i])); s64(a, OS_TS, (uint64_t)rel_ts(d, d.op_start[i])); s32(a, OS_ROW, (uint32_t)i);
+    if (type == 28) {  // HARDWARE_COUNTERS: one event per counter value, on a track named after the device
+      bool any = false;
+      for (uint32_t e = d.op_mdoff[i]; e < d.op_mdoff[i + 1]; e++) any = any || d.md[e].type == 6u;
+      return any ? (1ull << H_ALL) : 0ull;
+    }
+    return (1ull << C_HEAD) | (1ull << C_NAME) | (1ull << O_PID) | (1ull << O_TID) | (1ull << O_TS) | (1ull << O_ARGS) | (1ull << C_MD) |
+           (1ull << P_ARGS_CLOSE) | (1ull << P_CLOSE);
   }
   if (type == 9) {  // CPU_INSTANT_EVENT: handleGenericInstantEvent, output_json.cpp:660-676 (no duration, no flow, raw text)
     s32(a, OS_CAT, (uint32_t)(CS_TYPE + type)); s32(a, OS_NAME, d.op_name[i]); s32(a, OS_PID, (uint32_t)op_pid(d, d.op_device[i]));
@@ -1501,6 +1540,9 @@ __device__ __forceinline__ uint64_t gather_op(const Dev& d, uint64_t i, uint32_t
   }
   int64_t ts = d.op_start[i];
   int64_t dur = d.op_end[i] - ts;
+  // an activity that had not ended when the trace stopped ends with the capture window (processCpuTrace,
+  // GenericActivityProfiler.cpp:255-258; its "finished": false entry is part of its metadata like any other)
+  if (dur < 0 && (d.flags & 8)) dur = d.win_end - ts;
   if (dur < 0) dur = 0;
   const int64_t flow_ts = ts;
   if (type == 2) { ts -= 1; dur += 2; }  // GPU_USER_ANNOTATION, output_json.cpp:862-869
@@ -1580,6 +1622,43 @@ __device__ __forceinline__ uint32_t coll_mask(const Dev& d, uint32_t row, uint64
   return mask;
 }
 
+// The counter values of the CPU-side activity in row `row` (metadata entries of type 6: name, double).
+// handleCounterEvent (libkineto/src/output_json.cpp:679-716): MTIA_COUNTERS / XPU_SCOPE_PROFILER print them as one
+// argument list, "name": value joined by commas; HARDWARE_COUNTERS prints one whole event per value, named after
+// the counter, on the track "GPU <device> Counters", its single argument named "".  Values are fmt's "{}" of the
+// double, names are copied as they are.
+template <class S> __device__ __forceinline__ void put_cstr(S& s, uint32_t index) {
+  const FieldDesc cs = g_fields.f[CSTR_BASE + index];
+  s.words(g_fields.w + cs.off, cs.len);
+}
+template <class S>
+__device__ __forceinline__ void put_counters(S& s, const Dev& d, uint32_t row, bool hw) {
+  bool first = true;
+  for (uint32_t e = d.op_mdoff[row], m1 = d.op_mdoff[row + 1]; e < m1; e++) {
+    const MdEntry md = d.md[e];
+    if (md.type != 6u) continue;
+    uint64_t b = 0, e2 = 0;
+    coll_text(d, md.key, false, &b, &e2);
+    const double x = __longlong_as_double((long long)md.value);
+    s.ensure(48);
+    if (hw) {
+      put_cstr(s, CS_HWC + 0); s.bytes(d.pool_data + b, (uint32_t)(e2 - b));
+      put_cstr(s, CS_HWC + 1); s.ensure(48); put_sdec(s, (int64_t)op_pid(d, d.op_device[row]));
+      put_cstr(s, CS_HWC + 2); s.ensure(48); put_sdec(s, abs_tid(d.op_resource[row]));
+      put_cstr(s, CS_HWC + 3); s.ensure(48); put_ts2(s, rel_ts(d, d.op_start[row]));
+      put_cstr(s, CS_HWC + 4); s.ensure(48);
+      if (double_is_finite(x)) put_double(s, x); else put_nonfinite(s, x);
+      put_cstr(s, CS_HWC + 5);
+    } else {
+      if (!first) put_char(s, ',');
+      put_char(s, '"'); s.bytes(d.pool_data + b, (uint32_t)(e2 - b)); s.put(0x203A22u, 3);  // "\": "
+      s.ensure(48);
+      if (double_is_finite(x)) put_double(s, x); else put_nonfinite(s, x);
+    }
+    first = false;
+  }
+}
+
 // The value that follows a field's literal.  T_MD (CPU-side activities only) formats the typed metadata
 // entries of the op (JsonTypedMetadataVisitor, libkineto/include/TypedMetadataJson.h:72-158): each entry
 // is mapped onto one of the value types, so the kernel holds one copy of every formatter.
@@ -1589,6 +1668,7 @@ enum : int { T_BOOL = 8, T_MDSTR, T_QMDSTR };
 template <class S, bool COLL = true, bool ENSURE = true>
 __device__ __forceinline__ void put_value(S& s, const Dev& d, int type, uint64_t v, unsigned long long* name_bytes) {
   if (type == T_NONE) return;
+  if (COLL && (type == T_MDCNT || type == T_HWC)) { put_counters(s, d, (uint32_t)v, type == T_HWC); return; }
   // Two field types loop over the entries of a CPU-side activity: its own metadata (T_MD) and the collective keys
   // copied onto a kernel (T_COLL).  Every other type takes the switch once.
   uint32_t e = 0, m1 = 0, m0 = 0, cmask = 0;
@@ -1703,9 +1783,9 @@ constexpr int field_word_offset(int i) {  // position of field i's literal in g_
   for (int f = 0; f < i; f++) w += (c_strlen(kAllFields[f].lit) + 7) / 8;
   return w;
 }
-constexpr uint32_t longest_constant_string() {
+constexpr uint32_t longest_constant_string() {  // among those a T_CSTR value can name (the counter-event pieces are written by put_counters)
   uint32_t m = 0;
-  for (int f = CSTR_BASE; f < FIELD_COUNT; f++) if ((uint32_t)c_strlen(kAllFields[f].lit) > m) m = (uint32_t)c_strlen(kAllFields[f].lit);
+  for (int f = CSTR_BASE; f < CSTR_BASE + CS_HWC; f++) if ((uint32_t)c_strlen(kAllFields[f].lit) > m) m = (uint32_t)c_strlen(kAllFields[f].lit);
   return m;
 }
 // Most bytes a field's value can take; 0xffff for values of any length (names, metadata entries), which ask the
@@ -1836,7 +1916,7 @@ __device__ __noinline__ uint64_t app_cstr(uint32_t* win, uint32_t pos, uint32_t 
 // descriptor and the words of its literal are warp-uniform constant loads, the loop's body is small enough to stay
 // in the instruction cache, and lanes whose event lacks a field sit out one iteration.  Descriptor (64 bits):
 // literal word offset 0..11, literal length 12..19, operation 20..23, value slot offset 24..35, group bytes 36..43
-// (non-zero: the field starts a group, see kGroupBytes).
+// (non-zero: the field starts a group, see kGroupBytes), value type 44..49.
 enum : uint32_t { OP_NONE = 0, OP_U32, OP_I32, OP_U64, OP_I64, OP_TS, OP_DBL, OP_CSTR, OP_OTHER };
 constexpr uint32_t field_op(int type, int vk) {
   switch (type) {
@@ -1855,7 +1935,7 @@ constexpr void fill_class_descs(LoopDescs& t, int base, int nf) {
     const FieldSrc& src = kAllFields[base + f];
     const uint64_t grp = group_starts_at(base, 0, f) ? group_bytes_from(base, f, nf) : 0;
     t.d[base + f] = (uint64_t)field_word_offset(base + f) | ((uint64_t)c_strlen(src.lit) << 12) | ((uint64_t)field_op(src.type, src.vk) << 20) |
-                    ((uint64_t)src.voff << 24) | (grp << 36) | ((uint64_t)src.type << 44);
+                    ((uint64_t)src.voff << 24) | (grp << 36) | ((uint64_t)src.type << 44);  // type: 6 bits
   }
 }
 constexpr LoopDescs make_loop_descs() {
@@ -1912,7 +1992,7 @@ __device__ __forceinline__ void loop_fields(WindowSink& s, const Dev& d, const u
         else if (op == OP_DBL) st = app_dbl(s.win, s.pos, s.carry, reinterpret_cast<const uint64_t*>(a)[voff >> 3]);
         else if (op == OP_I64) st = app_i64(s.win, s.pos, s.carry, (int64_t)reinterpret_cast<const uint64_t*>(a)[voff >> 3]);
         else {  // names, metadata entries: they ask the sink for room themselves
-          put_value<WindowSink, false, true>(s, d, (int)((uint32_t)(desc >> 44) & 0xfu), (uint64_t)a[voff >> 2], name_bytes);
+          put_value<WindowSink, false, true>(s, d, (int)((uint32_t)(desc >> 44) & 0x3fu), (uint64_t)a[voff >> 2], name_bytes);
           st = sink_state(s);
         }
         s.pos = (uint32_t)st; s.carry = (uint32_t)(st >> 32);
@@ -1961,7 +2041,8 @@ __device__ __forceinline__ bool format_event(S& s, const Dev& d, int cls, uint32
       default: p = gather_op(d, j, a, t); base = OP_BASE; break;
     }
     // rare shapes: kernels with collective metadata, instant events
-    const bool rare = (cls == C_KERNEL && ((p >> K_COLL) & 1ull) != 0) || (cls == C_OP && ((p >> I_HEAD) & 1ull) != 0);
+    const bool rare = (cls == C_KERNEL && ((p >> K_COLL) & 1ull) != 0) ||
+                      (cls == C_OP && (p & ((1ull << I_HEAD) | (1ull << C_HEAD) | (1ull << H_ALL))) != 0);
     if (rare != COLL) return false;
     if constexpr (COLL) run_fields<S, COLL>(s, d, a, base, p, nb);
     else {

@@ -16,7 +16,13 @@
 //   * all calls on a device share the one scratch array: two calls whose kernels may overlap on the GPU
 //     (different streams without ordering) race on it and give wrong offsets.  Order them.
 //   * nothing in the scratch has to start at zero: each call overwrites every block sum it later reads,
-//     so leftovers of the previous call are harmless.
+//     so leftovers of the previous call are harmless;
+//   * under CUDA's default lazy module loading the driver sets up this file's kernels and the scratch array when
+//     they are first used, and that set-up allocates: make one call with n >= 1 on each device (or run with
+//     CUDA_MODULE_LOADING=EAGER) before entering a region that must not allocate;
+//   * the scratch address is looked up once per device and kept: do not use the entry point across a
+//     cudaDeviceReset of that device;
+//   * the caller's current device is the same after the call as before it.
 #include "../../include/k2j.h"
 
 #include <cuda_runtime.h>
@@ -36,6 +42,7 @@ constexpr size_t kNoAllocScratchBytes = (size_t)(kMaxBlocks + 32) * sizeof(unsig
 // The scratch itself.  In host code this name is only a handle for cudaGetSymbolAddress; it is not a
 // device address and must never be passed to a kernel directly.
 static __device__ __align__(256) unsigned long long g_noalloc_scratch[kMaxBlocks + 32];
+static_assert(sizeof(g_noalloc_scratch) == kNoAllocScratchBytes && kNoAllocScratchBytes <= 80 * 1024, "the scratch is meant to stay modest");
 
 constexpr int kMaxDevices = 64;
 unsigned long long* g_scratch_ptr[kMaxDevices] = {nullptr};
@@ -105,7 +112,13 @@ extern "C" k2j_status k2j_exclusive_scan_u32_noalloc(int device, void* stream, c
   if (device < 0 || device >= kMaxDevices) return K2J_ERR_INVALID_ARGUMENT;
   if (!total || (n && (!sizes || !offsets))) return K2J_ERR_INVALID_ARGUMENT;
   if (n > kMaxElems) return K2J_ERR_INVALID_ARGUMENT;  // beyond the fixed scratch: refuse, never truncate
+  int previous = -1;
+  if (cudaGetDevice(&previous) != cudaSuccess) { cudaGetLastError(); previous = -1; }
   if (cudaSetDevice(device) != cudaSuccess) { cudaGetLastError(); return K2J_ERR_CUDA; }
+  struct Restore {  // the caller's current device is put back on every way out
+    int dev;
+    ~Restore() { if (dev >= 0) cudaSetDevice(dev); }
+  } restore{previous != device ? previous : -1};
   unsigned long long* scratch;
   {
     std::lock_guard<std::mutex> guard(g_setup_mutex);

@@ -166,6 +166,14 @@ class TraceBuilder:
         self.records.append(r)
         return r
 
+    def other(self, kind: int, nbytes: int, fill: int = 0xAB):
+        """A record of a kind the path does not format: `nbytes` (a multiple of 8) of which the first four hold the kind."""
+        assert nbytes % 8 == 0 and nbytes >= 8
+        r = np.full(nbytes, fill, np.uint8)
+        r[:4] = np.array([kind], "<u4").view(np.uint8)
+        self.records.append(r)
+        return r
+
     def kernel(self, start, end, corr, name="kernel", device=0, context=1, stream=7, grid=(1, 1, 1),
                block=(32, 1, 1), regs=32, ssmem=0, dsmem=0, queued=0, graph=0, graph_node=0, channel=0,
                channel_type=0):
@@ -259,12 +267,13 @@ class TraceBuilder:
         mdoff, ents = [0], []
         for o in self.ops:
             md = o["md"]
+            counters = [m for m in md if m[1] == tf.MD_COUNTER]   # counter values are a list: they keep their order
+            md = [m for m in md if m[1] != tf.MD_COUNTER]
             keys = [k for k, _, _ in md]
-            for j in (_ordered_md(keys) if len(keys) > 1 else range(len(keys))):
-                k, ty, v = md[j]
+            for k, ty, v in [md[j] for j in (_ordered_md(keys) if len(keys) > 1 else range(len(keys)))] + counters:
                 if ty in (tf.MD_STRING, tf.MD_RAWJSON):
                     v = self.pool.add(v)
-                elif ty == tf.MD_DOUBLE:
+                elif ty in (tf.MD_DOUBLE, tf.MD_COUNTER):
                     v = int(np.array([v], np.float64).view(np.uint64)[0])
                 elif ty == tf.MD_INT64:
                     v = int(np.array([v], np.int64).view(np.uint64)[0])

@@ -111,7 +111,7 @@ DEVICE_PROPS = np.dtype([
     ("smem_per_block_optin", "<u8"), ("smem_per_sm", "<u8"), ("reserved_smem_per_block", "<u8"),
     ("total_global_mem", "<u8"), ("name", "S64")])
 MD_ENTRY = np.dtype([("key", "<u4"), ("type", "<u4"), ("value", "<u8")])
-MD_INT64, MD_UINT64, MD_DOUBLE, MD_BOOL, MD_STRING, MD_RAWJSON = range(6)
+MD_INT64, MD_UINT64, MD_DOUBLE, MD_BOOL, MD_STRING, MD_RAWJSON, MD_COUNTER = range(7)  # MD_COUNTER: a counter value (name, double)
 
 FLAG_USER_ANNOTATIONS = 1
 FLAG_SORT_BY_START = 2

@@ -44,6 +44,7 @@
 #include <cuda_occupancy.h>
 
 #include "trace_file.h"
+#include "../kineto_b200/csrc/k2j_cupti_sizes.h"  // generated from cupti_activity.h: record size per activity kind
 
 namespace {
 
@@ -70,7 +71,9 @@ size_t recSize(uint32_t kind) {
     case K_OVERHEAD: return 56;  // CUpti_ActivityOverhead3
     case K_SYNC: return 40;      // CUpti_ActivitySynchronization
     case K_CUDA_EVENT: return 56;  // CUpti_ActivityCudaEvent2
-    default: return 0;
+    // kinds the reference only counts (CuptiActivityProfiler.cpp:583-587): the record sizes of the CUDA 12.9 CUPTI
+    // headers, so that the walk can step over them; 0 for a kind the headers do not define
+    default: return kind < (uint32_t)k2j::kCuptiKinds ? 8u * k2j::kCuptiRecordSlots[kind] : 0;
   }
 }
 
@@ -216,6 +219,15 @@ struct Out {
     buf += "\n  },";
     c->x_events++;  // counted with the complete events
   }
+  // writeCounterEvent, libkineto/src/output_json.cpp:294-316: `pid` is text (a number, or a quoted track name)
+  void counter(const char* cat, const std::string& name, const std::string& pid, int64_t tid, int64_t ts, const std::string& args) {
+    buf += "\n  {\n    \"ph\": \"C\",\n    \"cat\": \""; buf += cat;
+    buf += "\",\n    \"name\": \""; buf += name;
+    buf += "\",\n    \"pid\": "; buf += pid;
+    buf += ",\n    \"tid\": "; appendI(buf, tid);
+    buf += ",\n    \"ts\": "; appendTs(buf, ts);
+    buf += ",\n    \"args\": {\n      "; buf += args; buf += "\n    }\n  },";
+  }
   void flow(char ph, int64_t id, int64_t pid, int64_t tid, int64_t ts, const char* name) {
     buf += "\n  {\n    \"ph\": \""; buf += ph;
     buf += "\",\n    \"id\": "; appendI(buf, id);
@@ -330,6 +342,28 @@ struct Run {
     }
     return f.j;
   }
+  // handleCounterEvent, libkineto/src/output_json.cpp:679-716: the activity's counter values (entries of type 6)
+  void counterEvents(const Event& e, size_t i) {
+    const uint32_t* off = tf.ptr<uint32_t>("OPMDOFF");
+    const k2jt_md_entry* md = tf.ptr<k2jt_md_entry>("MDENT");
+    std::string all;
+    for (uint32_t k = off[i]; k < off[i + 1]; k++) {
+      if (md[k].type != 6) continue;
+      double d; memcpy(&d, &md[k].value, 8);
+      std::string v; appendFmtDouble(v, d);
+      if (e.type == T_HW_COUNTERS) {
+        std::string pid = "\"GPU "; appendI(pid, e.device); pid += " Counters\"";
+        out.counter(kTypeNames[e.type], tf.str(md[k].key), pid, sanitizeTid(e.resource), out.rel(e.ts), "\"\": " + v);
+      } else {
+        if (!all.empty()) all += ",";
+        all += "\""; all += tf.str(md[k].key); all += "\": "; all += v;
+      }
+    }
+    if (e.type != T_HW_COUNTERS) {
+      std::string pid; appendI(pid, e.device);
+      out.counter(kTypeNames[e.type], e.name, pid, sanitizeTid(e.resource), out.rel(e.ts), all);
+    }
+  }
 
   void cpuOps() {
     size_t n = tf.count<int64_t>("OPSTART");
@@ -354,8 +388,13 @@ struct Run {
       // processCpuTrace logs an op only if its type is selected (GenericActivityProfiler.cpp:248);
       // the default selection is types 0..17, GPU_USER_ANNOTATION being switchable by flags bit 0.
       const bool selected = p.mode == 0 || (e.type < 18 && (e.type != T_GPU_USER_ANNOTATION || (p.flags & 1)));
+      // an activity that had not ended when the trace stopped ends with the capture window (processCpuTrace,
+      // GenericActivityProfiler.cpp:255-258; the "finished": false entry it gains is listed with its metadata)
+      if (p.mode == 1 && selected && e.dur < 0) e.dur = p.window_end_ns - e.ts;
       if (selected && e.type == T_CPU_INSTANT)  // handleActivity's early exit, libkineto/src/output_json.cpp:842-845
         out.instant(kTypeNames[e.type], e.name, e.device, sanitizeTid(e.resource), out.rel(e.ts), e.md);
+      else if (selected && (e.type == T_MTIA_COUNTERS || e.type == T_XPU_SCOPE || e.type == T_HW_COUNTERS))
+        counterEvents(e, i);  // :846-855
       else if (selected) emit(out, e);
       activityMap[e.corrId] = i;
       // recordThreadInfo(resourceId, getThreadId, deviceId), GenericActivityProfiler.cpp:272: only keys

@@ -50,6 +50,8 @@ extern "C" cudaDeviceProp* k2j_fake_device_prop(int i);
 extern "C" void k2j_fake_set_pid(int pid);
 extern "C" void k2j_fake_set_now_ns(long long ns);
 
+#include "../kineto_b200/csrc/k2j_cupti_sizes.h"  // generated from cupti_activity.h: record size per activity kind
+
 namespace {
 
 size_t recordSize(uint32_t kind) {
@@ -64,7 +66,8 @@ size_t recordSize(uint32_t kind) {
     case CUPTI_ACTIVITY_KIND_OVERHEAD: return sizeof(CUpti_ActivityOverhead3);  // what CUPTI 12.9 writes; the reference reads its 40-byte prefix
     case CUPTI_ACTIVITY_KIND_SYNCHRONIZATION: return sizeof(CUpti_ActivitySynchronization);
     case CUPTI_ACTIVITY_KIND_CUDA_EVENT: return sizeof(CUpti_ActivityCudaEvent2);
-    default: return 0;
+    // kinds the reference only counts: stepped over by the size of the kind's record in the CUPTI headers
+    default: return kind < (uint32_t)k2j::kCuptiKinds ? 8u * k2j::kCuptiRecordSlots[kind] : 0;
   }
 }
 
@@ -101,6 +104,7 @@ void addMetadata(GenericTraceActivity& op, const K2JTraceFile& tf, const k2jt_md
     case 3: op.addTypedMetadata(key, TypedValue{e.value != 0}); break;
     case 4: op.addMetadataQuoted(key, tf.str((uint32_t)e.value)); break;
     case 5: op.addTypedMetadata(key, TypedValue{RawJson{tf.str((uint32_t)e.value)}}); break;
+    case 6: { double d; memcpy(&d, &e.value, 8); op.addCounterValue(key, d); break; }
     default: throw std::runtime_error("bad metadata type");
   }
 }
@@ -140,14 +144,16 @@ void fillOp(GenericTraceActivity& op, const K2JTraceFile& tf, size_t i) {
   // The container lists entries in VISIT order.  Inserting them in reverse reproduces that order in
   // the reference's unordered_map (a new node goes to the front of the list, or to the front of its
   // bucket's run, which for a valid visit order is the same place); verified below.
-  for (uint32_t e = mdoff[i + 1]; e > mdoff[i]; e--) addMetadata(op, tf, md[e - 1]);
+  for (uint32_t e = mdoff[i + 1]; e > mdoff[i]; e--) if (md[e - 1].type != 6) addMetadata(op, tf, md[e - 1]);
+  for (uint32_t e = mdoff[i]; e < mdoff[i + 1]; e++) if (md[e].type == 6) addMetadata(op, tf, md[e]);  // counter values: a list, in order
   if (mdoff[i + 1] - mdoff[i] > 1) {
     OrderVisitor v;
     op.visitTypedMetadata(v);
-    for (uint32_t e = mdoff[i], k = 0; e < mdoff[i + 1]; e++, k++) {
-      if (v.keys[k] != tf.str(md[e].key)) {
+    for (uint32_t e = mdoff[i], k = 0; e < mdoff[i + 1]; e++) {
+      if (md[e].type == 6) continue;
+      if (v.keys[k++] != tf.str(md[e].key)) {
         fprintf(stderr, "metadata order mismatch at op %zu: container has '%s', reference visits '%s'\n",
-                i, tf.str(md[e].key).c_str(), v.keys[k].c_str());
+                i, tf.str(md[e].key).c_str(), v.keys[k - 1].c_str());
         exit(3);
       }
     }

@@ -349,6 +349,88 @@ def instant_trace() -> tf.Trace:
     return b.build()
 
 
+def gaps_trace(mode=1) -> tf.Trace:
+    """Behaviour of the reference that rarely shows: activities that had not ended when the trace stopped
+    (processCpuTrace ends them at the window's end and adds "finished": false), records of kinds the profiler only
+    counts (stepped over), a kind no header defines (ends the walk of its buffer), correlation id 0 with and
+    without a link next to keys that hash to the same table slot, and counter events."""
+    b = synth.TraceBuilder(mode=mode, n_devices=2, buffer_bytes=1 << 20)
+    t0 = b.t0
+    b.window = (t0, t0 + 5_000_000)
+    I, S, R, D, C = tf.MD_INT64, tf.MD_STRING, tf.MD_RAWJSON, tf.MD_DOUBLE, tf.MD_COUNTER
+    fin = ("finished", R, "false")
+    # ---- unfinished activities: end < start ----
+    b.op(t0 + 100, t0 + 50, 1, "aten::unfinished", md=[("Sequence number", I, 7), ("Input Dims", R, "[[2, 3], []]"), fin])
+    b.op(t0 + 200, 0, 2, "aten::end zero", md=[fin])
+    b.op(t0 + 300, t0 + 299, 3, "annotation that never closed", type=synth.USER_ANNOTATION,
+         md=[("a", I, 1), ("b", I, 2), ("c", I, 3), ("d", I, 4), ("e", S, "x"), fin], flow_id=4, flow_type=1, flow_start=1)
+    b.op(t0 + 6_000_000, t0 + 5_999_999, 4, "starts after the window's end", md=[fin])
+    b.op(t0 + 400, t0 + 500, 5, "finished in time", md=[("finished", R, "true")])
+    b.op(t0 + 600, t0 + 100, 0, "id 0, unfinished", md=[fin])
+    # ---- counter events ----
+    b.op(t0 + 700, t0 + 700, 11, "mtia counters", type=17, device=3, resource=-9,
+         md=[("ignored", I, 5), ("hbm_read_bw", C, 1.5), ("cache \"hit\"", C, 0.25), ("big", C, 1e22), ("nan", C, float("nan")),
+             ("neg inf", C, float("-inf")), ("zero", C, 0.0)])
+    b.op(t0 + 710, t0 + 715, 12, "mtia, no values", type=17)
+    if mode == 0:  # these two types are not in the profiler's default selection; a logger driven directly writes them
+        b.op(t0 + 720, t0 + 720, 13, "xpu scope", type=26, device=0, resource=I64_MIN, md=[("metric.a", C, 3.0), ("metric.b", C, 1e-7)])
+        b.op(t0 + 730, t0 + 730, 14, "hw counters", type=28, device=1, resource=42,
+             md=[("sm__cycles_active.avg", C, 123456.75), ("dram__bytes_read.sum", C, 1.8446744073709552e19), ("q\"uote", C, -2.5)])
+        b.op(t0 + 740, t0 + 740, 15, "hw counters without values", type=28, device=1, resource=42, md=[("x", I, 1)])
+        b.op(b.base - 10, t0, 16, "hw counter before the base time", type=28, device=0, resource=-3, md=[("c", C, 2.0)])
+    if mode == 0:  # a logger driven directly sees no CUPTI records
+        return b.build()
+    # ---- first buffer: kinds that are only counted ----
+    b.other(9, 32)                     # CONTEXT
+    b.extcorr(100, 1)
+    b.other(12, 56)                    # MARKER
+    b.runtime(t0 + 200, t0 + 300, 100)
+    b.other(49, 128)                   # MEMORY2
+    b.other(8, 184)                    # DEVICE
+    b.kernel(t0 + 500, t0 + 1500, 100, "after four skipped records", device=1, stream=9)
+    b.other(3, 208)                    # KERNEL (the serialised-kernel kind, same structure as CONCURRENT_KERNEL)
+    b.other(48, 40)                    # INTERNAL_LAUNCH_API: 40 bytes, like a runtime record
+    b.other(37, 24)                    # STREAM
+    b.memcpy(t0 + 1500, t0 + 2500, 100, 1 << 20)
+    for k in (6, 7, 11, 13, 14, 21, 23, 27, 28, 31, 32, 41, 45, 50, 52, 54):
+        b.other(k, 8 * [0, 12, 11, 26, 5, 5, 3, 3, 23, 4, 26, 4, 7, 4, 3, 7, 5, 7, 18, 5, 5, 4, 12, 4, 6, 13, 4, 3, 3, 7, 5, 4, 3, 19,
+                        19, 15, 7, 3, 7, 3, 17, 4, 4, 4, 4, 10, 21, 5, 5, 16, 9, 7, 8, 7, 8][k])
+    b.kernel(t0 + 1600, t0 + 1700, 100, "after sixteen more")
+    b.new_buffer()
+    # ---- second buffer: correlation id 0 ----
+    b.extcorr(0, 5)                    # correlation id 0, linked to op 5
+    b.kernel(t0 + 2000, t0 + 2100, 0, "correlation 0 (no flow), linked")
+    b.memset(t0 + 2000, t0 + 2100, 0, 64)
+    for corr, ext in ((2654435769, 3), (1, 2), (2, 1), (3, 99)):
+        b.extcorr(corr, ext)
+        b.kernel(t0 + 2200, t0 + 2300, corr, "corr %d" % corr)
+    b.new_buffer()
+    # ---- third buffer: a kind no header defines ends the walk; the records behind it are lost, as in a walk that
+    # cannot size the record ----
+    b.kernel(t0 + 3000, t0 + 3100, 1, "before the undefined kind")
+    b.other(60, 16)
+    b.kernel(t0 + 3200, t0 + 3300, 2, "never reached")
+    b.new_buffer()
+    b.kernel(t0 + 3400, t0 + 3500, 3, "next buffer is walked again")
+    b.other(0, 8)                      # kind 0 (INVALID): undefined as well
+    return b.build()
+
+
+def corr_zero_unlinked_trace() -> tf.Trace:
+    """Correlation id 0 whose external id names no CPU op, in front of keys that probe past the slot id 0 hashes to."""
+    b = synth.TraceBuilder(n_devices=1)
+    t0 = b.t0
+    b.op(t0 + 100, t0 + 200, 1, "op 1")
+    b.op(t0 + 100, t0 + 200, 0, "op 0")
+    b.extcorr(0, 77)                   # no op 77: correlation 0 stays unlinked
+    for corr in range(1, 40):
+        b.extcorr(corr, corr & 1)
+        b.kernel(t0 + 300 + corr, t0 + 400 + corr, corr, "k%d" % corr)
+    b.kernel(t0 + 500, t0 + 600, 0, "correlation 0, unlinked")
+    b.sync(t0 + 700, t0 + 800, 0, stream=7)            # a synchronisation record prints its own correlation id when unlinked
+    return b.build()
+
+
 CASES = {
     "edge": edge_trace,
     "generic_300": lambda: synth.gen_generic_kernels(300, seed=31, pool_size=40),
@@ -358,6 +440,9 @@ CASES = {
     "sync": sync_trace,
     "collectives": collective_trace,
     "instant": instant_trace,
+    "gaps": gaps_trace,
+    "gaps_direct": lambda: gaps_trace(mode=0),
+    "corr_zero": corr_zero_unlinked_trace,
 }
 
 

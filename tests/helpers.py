@@ -96,11 +96,11 @@ def split_events(doc: bytes):
     return doc[:first], [_EVENT_START + p for p in parts[1:]], doc[end:]
 
 
-_ACT = re.compile(rb'\n  \{\n    ("ph": "(X|s|f)",\n    "(cat|id)": |"name": "thread_(name|sort_index)", "ph": "M", "ts": |"ph": "i",\n    \n    "cat": "cpu_instant_event",)')
+_ACT = re.compile(rb'\n  \{\n    ("ph": "(X|s|f|C)",\n    "(cat|id)": |"name": "thread_(name|sort_index)", "ph": "M", "ts": |"ph": "i",\n    \n    "cat": "cpu_instant_event",)')
 
 
 def activities_segment(doc: bytes) -> bytes:
-    """The events the device pipeline is responsible for: every X / flow event except the
+    """The events the device pipeline is responsible for: every X / flow / counter event except the
     host-written "Trace" spans, plus the metadata rows the logger writes in line before the first
     stream sync of a row (libkineto/src/output_json.cpp:921-938; the header's metadata rows start with "ph") and the
     instant events of CPU-side activities (the host-written instant events have no category)."""

@@ -219,8 +219,8 @@ def test_error_behaviour():
         with pytest.raises(api.K2JError) as e:
             ctx.run()
         assert e.value.status == 5
-        # unsupported CPU activity type (a counter event of another profiler)
-        a3 = dict(a, op_type=np.full(len(t.op_type), 17, np.int32))
+        # a CPU activity type libkineto does not define
+        a3 = dict(a, op_type=np.full(len(t.op_type), 40, np.int32))
         ctx.set_arrays(a3, t.buftab, t.tidmap)
         with pytest.raises(api.K2JError) as e:
             ctx.run()
@@ -243,6 +243,7 @@ def test_exclusive_scan_entry_point(n):
     try:
         d_sizes = torch.from_numpy(sizes).cuda()
         d_off = torch.empty(n, dtype=torch.int64, device="cuda")
+        torch.cuda.synchronize()  # the context scans on its own stream: its inputs must be complete first
         total = ctx.exclusive_scan(d_sizes, d_off)
         want = np.concatenate([[0], np.cumsum(sizes.astype(np.int64))])
         assert total == want[-1]
@@ -293,6 +294,7 @@ def test_sharded_runs_concatenate_to_the_whole(n_shards):
                 return api.device_view(ptr, n_items, ts).clone()
             ext = torch.cat([view(i.external_records, int(i.n_external) * 2, "<i8") for i in infos])
             ops = torch.cat([view(i.op_ids, int(i.n_ops), "<i4") for i in infos])
+            torch.cuda.synchronize()  # the gathered arrays were built on torch's stream; the contexts read them on theirs
             begin = 0
             for c, i in zip(ctxs, infos):
                 c.set_global_join(ext, ext.numel() // 2, begin, ops, ops.numel())
