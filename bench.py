@@ -1,9 +1,9 @@
 """Benchmark of the trace post-processing hot path.
 
-    python bench.py --gpus N --steps K --warmup W [--workload W --n N]   # this library (CUDA, sm_100a)
+    python bench.py --gpus N --steps K --warmup W [--workload W --size N]   # this library (CUDA, sm_100a)
     python bench.py --impl reference --gpus N --steps K ...               # the reference's CPU path on host cores
 
-Workloads (seeded synthetic traces that stand in for real captures; `--n` is the generator's size argument
+Workloads (seeded synthetic traces that stand in for real captures; `--size` is the generator's size argument
 per GPU):
 
     mixed             (default, n = 10 000 000)  10 M mixed activities per GPU: 60 % kernels, 20 % memcpy (HtoD /
@@ -66,8 +66,8 @@ def parse():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="mixed", choices=sorted(DEFAULT_N))
-    ap.add_argument("--n", type=int, default=0, help="size argument of the generator per GPU (0: the workload's default)")
-    ap.add_argument("--launches", type=int, default=0, help="same as --workload kernel_launches --n LAUNCHES")
+    ap.add_argument("--size", dest="n", type=int, default=0, help="size argument of the generator per GPU (0: the workload's default)")
+    ap.add_argument("--launches", type=int, default=0, help="same as --workload kernel_launches --size LAUNCHES")
     ap.add_argument("--cpu-sample", type=int, default=250_000, help="size argument of the CPU-baseline / parity sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
@@ -296,6 +296,7 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     exchange_events = []
+    exchanges = {}
 
     def prepare(c, s):
         """segment -> (all-gather join keys): everything before the emit step."""
@@ -308,10 +309,11 @@ def run_ours(args):
         ops_local = api.device_view(info.op_ids, n_ops, "<i4", dev)
         x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         x0.record(s)
-        ext_all, ops_all, own_begin = sharding.gather_join_keys(ext_local, ops_local, rank, world, dist)
+        ex = exchanges.setdefault(id(c), sharding.JoinExchange(rank, world, dist, dev))
+        rows, ext_stride, ops_stride, counts = ex.gather(ext_local, ops_local)
         x1.record(s)
         exchange_events.append((x0, x1))
-        c.set_global_join(ext_all, ext_all.numel() // 2, own_begin, ops_all, ops_all.numel())
+        c.set_global_join_rows(rows, ext_stride, ops_stride, counts, world, rank)
 
     # ---- resident: inputs already in HBM, the text stays in HBM ----
     dev_arrays = api.device_arrays(trace, dev)

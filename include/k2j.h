@@ -218,6 +218,14 @@ typedef struct {
 k2j_status k2j_segment(k2j_ctx* ctx, k2j_segment_info* info);
 k2j_status k2j_set_global_join(k2j_ctx* ctx, const void* external_all, uint64_t n_external_all, uint64_t own_begin,
                                const int32_t* op_ids_all, uint64_t n_ops_all);
+/* k2j_set_global_join for arrays left as an all-gather of equal-sized rows delivers them, so that nothing has to
+ * be compacted (or counted on the host) between the collective and the run: row r (shard r) lies row_pitch_bytes
+ * after row r - 1; a row's records start at ext_rows + r * pitch, its ids at op_id_rows + r * pitch; ext_stride /
+ * ops_stride are the entries a row has room for, counts[2 r] / counts[2 r + 1] (device memory, written by the same
+ * exchange) the entries it holds.  Tables are then sized for this shard's own events. */
+k2j_status k2j_set_global_join_rows(k2j_ctx* ctx, const void* ext_rows, uint64_t ext_stride, const int32_t* op_id_rows,
+                                    uint64_t ops_stride, uint64_t row_pitch_bytes, const uint64_t* counts, uint32_t world,
+                                    uint32_t rank);
 k2j_status k2j_emit(k2j_ctx* ctx, k2j_result* result);
 
 /* k2j_emit for traces whose text should not be held whole on the device: the text is produced in slabs of

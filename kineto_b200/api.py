@@ -64,7 +64,7 @@ class SegmentInfo(C.Structure):
                 ("n_ops", C.c_uint64), ("op_ids", C.c_void_p)]
 
 
-EXPORTS = ["k2j_emit_to_host", "k2j_emit_to_fd", "k2j_exclusive_scan_u32", "k2j_exclusive_scan_u32_noalloc", "k2j_segment", "k2j_set_global_join", "k2j_emit", "k2j_create", "k2j_destroy", "k2j_last_error", "k2j_set_params", "k2j_set_strings",
+EXPORTS = ["k2j_set_global_join_rows", "k2j_emit_to_host", "k2j_emit_to_fd", "k2j_exclusive_scan_u32", "k2j_exclusive_scan_u32_noalloc", "k2j_segment", "k2j_set_global_join", "k2j_emit", "k2j_create", "k2j_destroy", "k2j_last_error", "k2j_set_params", "k2j_set_strings",
            "k2j_set_cbid_names", "k2j_set_thread_map", "k2j_set_ops", "k2j_set_cupti", "k2j_run", "k2j_output",
            "k2j_copy_output", "k2j_copy_output_async", "k2j_write_output", "k2j_write_output_at", "k2j_synchronize", "k2j_version"]
 
@@ -94,6 +94,7 @@ def load_library():
     lib.k2j_run.argtypes = [vp, C.POINTER(Result)]
     lib.k2j_segment.argtypes = [vp, C.POINTER(SegmentInfo)]
     lib.k2j_set_global_join.argtypes = [vp, vp, C.c_uint64, C.c_uint64, vp, C.c_uint64]
+    lib.k2j_set_global_join_rows.argtypes = [vp, vp, C.c_uint64, vp, C.c_uint64, C.c_uint64, vp, C.c_uint32, C.c_uint32]
     lib.k2j_emit.argtypes = [vp, C.POINTER(Result)]
     lib.k2j_emit_to_host.argtypes = [vp, vp, C.c_uint64, C.c_uint64, C.POINTER(Result)]
     lib.k2j_emit_to_fd.argtypes = [vp, C.c_int, C.c_uint64, C.POINTER(Result)]
@@ -220,6 +221,14 @@ class K2J:
         self._keep["g_ext"], self._keep["g_ops"] = ext_all, op_ids_all
         self._check(self.lib.k2j_set_global_join(self.h, _ptr(ext_all), n_ext_all, own_begin, _ptr(op_ids_all),
                                                  n_ops_all))
+
+    def set_global_join_rows(self, rows, ext_stride: int, ops_stride: int, counts, world: int, rank: int):
+        """`rows`: the int64 device tensor an all-gather of per-shard rows produced (sharding.JoinExchange): every row
+        holds ext_stride 16-byte records followed by ops_stride ids; `counts`: int64 device tensor, 2 per shard."""
+        self._keep["g_rows"], self._keep["g_counts"] = rows, counts
+        pitch = rows.numel() * 8 // world
+        self._check(self.lib.k2j_set_global_join_rows(self.h, rows.data_ptr(), ext_stride, rows.data_ptr() + ext_stride * 16,
+                                                      ops_stride, pitch, counts.data_ptr(), world, rank))
 
     def emit(self) -> dict:
         r = Result()

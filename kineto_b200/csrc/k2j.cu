@@ -90,6 +90,7 @@ struct k2j_ctx {
   DevBuf corr0;                                                       // correlation id 0 (see Dev::corr0)
   const void* g_ext = nullptr; uint64_t g_n_ext = 0, g_own_begin = 0;
   const int32_t* g_op_ids = nullptr; uint64_t g_n_ops = 0;
+  uint32_t g_ext_stride = 0, g_ops_stride = 0, g_world = 1; uint64_t g_pitch = 0; const uint64_t* g_counts = nullptr;  // rows of an all-gather
 };
 
 namespace {
@@ -591,6 +592,25 @@ k2j_status k2j_set_global_join(k2j_ctx* c, const void* ext_all, uint64_t n_ext_a
     return fail(c, K2J_ERR_INVALID_ARGUMENT, "gathered join arrays out of range");
   c->g_ext = ext_all; c->g_n_ext = n_ext_all; c->g_own_begin = own_begin;
   c->g_op_ids = op_ids_all; c->g_n_ops = n_ops_all;
+  c->g_counts = nullptr; c->g_world = 1;
+  c->have_global_join = true;
+  return K2J_OK;
+}
+
+k2j_status k2j_set_global_join_rows(k2j_ctx* c, const void* ext_rows, uint64_t ext_stride, const int32_t* op_id_rows, uint64_t ops_stride,
+                                    uint64_t row_pitch_bytes, const uint64_t* counts, uint32_t world, uint32_t rank) {
+  if (!c) return K2J_ERR_INVALID_ARGUMENT;
+  if (!c->segmented) return fail(c, K2J_ERR_STATE, "k2j_segment has not run");
+  if (!ext_rows || !op_id_rows || !counts || world == 0 || rank >= world) return fail(c, K2J_ERR_INVALID_ARGUMENT, "null join rows");
+  if (!is_device_ptr(ext_rows) || !is_device_ptr(op_id_rows) || !is_device_ptr(counts))
+    return fail(c, K2J_ERR_INVALID_ARGUMENT, "gathered join rows must be device memory");
+  if (ext_stride == 0 || ops_stride == 0 || ext_stride * world >= 0xFFFFFFF0ull || ops_stride * world >= 0xFFFFFFF0ull ||
+      c->totals[C_EXT] > ext_stride || c->n_ops > ops_stride || (row_pitch_bytes & 7))
+    return fail(c, K2J_ERR_INVALID_ARGUMENT, "join rows: stride smaller than this shard's share, or out of range");
+  c->g_ext = ext_rows; c->g_n_ext = ext_stride * world; c->g_own_begin = ext_stride * rank;
+  c->g_op_ids = op_id_rows; c->g_n_ops = ops_stride * world;
+  c->g_ext_stride = (uint32_t)ext_stride; c->g_ops_stride = (uint32_t)ops_stride; c->g_pitch = row_pitch_bytes;
+  c->g_counts = counts; c->g_world = world;
   c->have_global_join = true;
   return K2J_OK;
 }
@@ -670,17 +690,25 @@ k2j_status emit_core(k2j_ctx* c, k2j_result* res, const TileSink& sink) {
   if (c->have_global_join) {
     d.ext_all = (const ExtRec*)c->g_ext; d.n_ext_all = c->g_n_ext;
     d.join_op_ids = c->g_op_ids; d.n_join_ops = c->g_n_ops;
+    d.join_counts = c->g_counts; d.ext_stride = c->g_ext_stride; d.ops_stride = c->g_ops_stride; d.join_pitch = c->g_pitch;
     own_begin = c->g_own_begin; own_end = own_begin + totals[C_EXT];
   } else {
     d.ext_all = d.ext_local; d.n_ext_all = totals[C_EXT];
     d.join_op_ids = d.op_id; d.n_join_ops = c->n_ops;
+    d.join_counts = nullptr;
   }
   K2J_CUDA(c, c->ev_size.reserve(std::max<uint64_t>(1, d.n_events) * 4));
   K2J_CUDA(c, c->ev_off.reserve(std::max<uint64_t>(1, d.n_events) * 8));
   K2J_CUDA(c, c->ev_ext.reserve(std::max<uint64_t>(1, d.n_events) * 4));
   d.ev_size = c->ev_size.as<uint32_t>(); d.ev_off = c->ev_off.as<uint64_t>(); d.ev_ext = c->ev_ext.as<int32_t>();
-  const uint32_t corr_cap = pow2_at_least(2 * d.n_ext_all + 2);
-  const uint32_t op_cap = pow2_at_least(2 * d.n_join_ops + 2);
+  // With gathered keys only those this shard's events can look up enter its tables (see k_mark_corr), so the tables
+  // are sized by the shard: its events, plus the share of foreign keys the marking lets through by chance.
+  const bool filter = c->have_global_join;
+  // (a filtered table holds at most the bound below, usually about half of it: 1.4 slots per possible key are enough)
+  const uint32_t corr_cap = filter ? pow2_at_least(14 * std::min<uint64_t>(d.n_ext_all, n_gpu_events + d.n_ext_all / 16 + 1024) / 10 + 2)
+                                   : pow2_at_least(2 * d.n_ext_all + 2);
+  const uint32_t op_cap = filter ? pow2_at_least(14 * std::min<uint64_t>(d.n_join_ops, n_gpu_events + d.n_join_ops / 16 + 1024) / 10 + 2)
+                                 : pow2_at_least(2 * d.n_join_ops + 2);
   K2J_CUDA(c, c->corr_tab.reserve((size_t)corr_cap * 8));
   K2J_CUDA(c, c->user_tab.reserve((size_t)corr_cap * 8));
   K2J_CUDA(c, c->op_tab.reserve((size_t)op_cap * 8));
@@ -692,7 +720,7 @@ k2j_status emit_core(k2j_ctx* c, k2j_result* res, const TileSink& sink) {
   d.corr0 = c->corr0.as<unsigned long long>();
   K2J_CUDA(c, cudaMemsetAsync(d.corr0, 0, 16, s));
   // the user-annotation table is only written and read when CUSTOM1 correlation records exist
-  if (c->have_global_join || totals[C_USER] > 0) K2J_CUDA(c, cudaMemsetAsync(d.user_tab, 0, (size_t)corr_cap * 8, s));
+  if (!c->have_global_join && totals[C_USER] > 0) K2J_CUDA(c, cudaMemsetAsync(d.user_tab, 0, (size_t)corr_cap * 8, s));
   K2J_CUDA(c, cudaMemsetAsync(d.op_tab, 0, (size_t)op_cap * 8, s));
   const uint32_t tid_cap = std::max<uint32_t>(16384, pow2_at_least(4ull * c->n_tid));
   K2J_CUDA(c, c->tid_tab.reserve((size_t)tid_cap * 8));
@@ -723,10 +751,8 @@ k2j_status emit_core(k2j_ctx* c, k2j_result* res, const TileSink& sink) {
     K2J_CUDA(c, cudaMemsetAsync(d.span_nfirst, 0, (size_t)span_cap * 8, s));
   }
   d.need_corr = nullptr; d.need_op = nullptr;
-  if (c->have_global_join && d.n_ext_all > 3 * std::max<uint64_t>(1, totals[C_EXT])) {
-    // Four or more shards' worth of keys: only those this shard's events can look up enter its tables
-    // (see k_mark_corr).  Below that the marking pass costs more than the inserts it saves.
-    const uint32_t corr_bits = std::max<uint32_t>(1u << 20, pow2_at_least(16 * std::max<uint64_t>(1, n_gpu_events)));
+  if (filter) {
+    const uint32_t corr_bits = std::max<uint32_t>(1u << 20, pow2_at_least(32 * std::max<uint64_t>(1, n_gpu_events)));
     const uint32_t op_bits = corr_bits;
     K2J_CUDA(c, c->need_corr.reserve(corr_bits / 8));
     K2J_CUDA(c, c->need_op.reserve(op_bits / 8));

@@ -138,8 +138,13 @@ struct Dev {
   const uint8_t* op_flowt; const uint32_t* op_mdoff; const MdEntry* md;
   // EXTERNAL_CORRELATION records in processing order, compacted: the local shard's (ext_local) and
   // the array the tables are built from (ext_all: the same array, or all shards' arrays gathered)
+  // n_ext_all / n_join_ops are index ranges.  With several shards the arrays are what an all-gather of equal-sized
+  // rows left: row r (shard r) starts join_pitch bytes after row r - 1, holds join_counts[2 r] records and
+  // join_counts[2 r + 1] ids, and index i means entry i % stride of row i / stride (so indices still grow in
+  // processing order).  One shard: one row, join_counts == nullptr, every index valid.
   ExtRec* ext_local; const ExtRec* ext_all; uint64_t n_ext_all;
   const int32_t* join_op_ids; uint64_t n_join_ops;  // CPU-op ids the join sees (local or gathered)
+  uint32_t ext_stride, ops_stride; uint64_t join_pitch; const uint64_t* join_counts;
   // sharded runs: bit sets (by hash) of the correlation ids this shard's events carry and of the CPU-op ids
   // the matching records name; keys outside them are not inserted.  nullptr: insert everything.
   uint32_t* need_corr; uint32_t need_corr_mask; uint32_t* need_op; uint32_t need_op_mask;
@@ -183,6 +188,22 @@ struct Dev {
 __device__ __forceinline__ int32_t op_pid(const Dev& d, int32_t device) { return (device == 0 && (d.flags & 4)) ? d.pid : device; }
 __device__ __forceinline__ uint64_t esc_name_pos(const Dev& d, uint32_t id) { return ((2 * d.pool_off[id] + 7) & ~7ull) + 16ull * id; }
 __device__ __forceinline__ uint64_t esc_md_pos(const Dev& d, uint32_t id) { return ((d.pool_off[id] + 7) & ~7ull) + 8ull * id; }
+
+// Entry i of the gathered EXTERNAL_CORRELATION records / CPU-op ids; false: past the end of its row.
+__device__ __forceinline__ bool ext_at(const Dev& d, uint64_t i, ExtRec* out) {
+  if (d.join_counts == nullptr) { *out = d.ext_all[i]; return true; }
+  const uint32_t r = (uint32_t)(i / d.ext_stride), j = (uint32_t)(i - (uint64_t)r * d.ext_stride);
+  if ((uint64_t)j >= d.join_counts[2 * r]) return false;
+  *out = *reinterpret_cast<const ExtRec*>(reinterpret_cast<const uint8_t*>(d.ext_all) + (uint64_t)r * d.join_pitch + (uint64_t)j * sizeof(ExtRec));
+  return true;
+}
+__device__ __forceinline__ bool op_id_at(const Dev& d, uint64_t i, uint32_t* out) {
+  if (d.join_counts == nullptr) { *out = (uint32_t)d.join_op_ids[i]; return true; }
+  const uint32_t r = (uint32_t)(i / d.ops_stride), j = (uint32_t)(i - (uint64_t)r * d.ops_stride);
+  if ((uint64_t)j >= d.join_counts[2 * r + 1]) return false;
+  *out = (uint32_t)*reinterpret_cast<const int32_t*>(reinterpret_cast<const uint8_t*>(d.join_op_ids) + (uint64_t)r * d.join_pitch + (uint64_t)j * 4u);
+  return true;
+}
 
 // ---- hashing ----------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t hash32(uint32_t x) {
@@ -599,8 +620,8 @@ __global__ void k_find_comms(Dev d, uint32_t* flag, int comms_on) {
 // CPU-op id -> position (last writer wins): activityMap_[id] = op, GenericActivityProfiler.cpp:262.
 __global__ void k_build_ops(Dev d) {
   const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const bool in = i < d.n_join_ops;
-  const uint32_t id = in ? (uint32_t)d.join_op_ids[i] : 0u;
+  uint32_t id = 0u;
+  const bool in = i < d.n_join_ops && op_id_at(d, i, &id);
   const bool valid = in && (d.need_op == nullptr || bit_test(d.need_op, d.need_op_mask, id));
   // Ids repeat (every memory event of a PyTorch trace carries id 0): of the lanes of a warp that hold one id only the
   // last, which is the one that must win, goes to the table, so a run of equal ids costs one atomic per warp.
@@ -612,8 +633,8 @@ __global__ void k_build_ops(Dev d) {
 // CuptiActivityProfiler.cpp:290-302).  `count_invalid`: only the shard that owns a record counts it.
 __global__ void k_build_corr(Dev d, uint64_t own_begin, uint64_t own_end) {
   const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= d.n_ext_all) return;
-  const ExtRec e = d.ext_all[i];
+  ExtRec e;
+  if (i >= d.n_ext_all || !ext_at(d, i, &e)) return;
   bool ok = true;
   if (e.external_kind == 3u) {
     if (d.need_corr != nullptr) {
@@ -1000,14 +1021,16 @@ __device__ __forceinline__ bool out_of_range(const Dev& d, int64_t ts, int64_t d
 __global__ void k_resolve_corr(Dev d) {
   const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i == 0u && d.corr0[0] != 0ull) {  // correlation id 0
-    const int64_t ext = (int64_t)d.ext_all[d.corr0[0] - 1ull].external_id;
+    ExtRec z; ext_at(d, d.corr0[0] - 1ull, &z);
+    const int64_t ext = (int64_t)z.external_id;
     const bool linked = ext == (int64_t)(int32_t)ext && tab_find(d.op_tab, d.op_mask, (uint32_t)(int32_t)ext) != 0xFFFFFFFFu;
     d.corr0[1] = linked ? ((1ull << 33) | (unsigned long long)(uint32_t)(int32_t)ext) : 0ull;
   }
   if (i > d.corr_mask) return;
   const unsigned long long e = d.corr_tab[i];
   if (e == 0) return;
-  const int64_t ext = (int64_t)d.ext_all[(uint32_t)e - 1u].external_id;
+  ExtRec rec; ext_at(d, (uint32_t)e - 1u, &rec);
+  const int64_t ext = (int64_t)rec.external_id;
   uint32_t id = 0;
   if (ext == (int64_t)(int32_t)ext && tab_find(d.op_tab, d.op_mask, (uint32_t)(int32_t)ext) != 0xFFFFFFFFu)
   {

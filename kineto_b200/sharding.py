@@ -47,6 +47,45 @@ def gather_join_keys(ext_local, ops_local, rank: int, world: int, dist):
     return ext_all.contiguous(), ops_all.contiguous(), own_begin
 
 
+class JoinExchange:
+    """The same exchange without a host round trip per step.  Every rank sends one row: room for `ext_stride`
+    records and `ops_stride` ids (the largest shard's counts; agreed once, with a little head room, when the exchange
+    is created or has to grow), the rows are all-gathered as they are, and the library reads them in place
+    (k2j_set_global_join_rows) together with the all-gathered counts, which never leave the device."""
+
+    def __init__(self, rank: int, world: int, dist, device):
+        self.rank, self.world, self.dist, self.device = rank, world, dist, device
+        self.ext_stride = self.ops_stride = 0
+
+    def _agree(self, n_ext: int, n_ops: int):
+        import torch
+        t = torch.tensor([n_ext, n_ops], dtype=torch.int64, device=self.device)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        m = t.tolist()
+        self.ext_stride = max(1, int(m[0] * 1.02) + 16)
+        self.ops_stride = (max(1, int(m[1] * 1.02) + 16) + 1) & ~1      # two ids per 64-bit word
+        words = self.ext_stride * 2 + self.ops_stride // 2
+        self.row = torch.zeros(words, dtype=torch.int64, device=self.device)
+        self.rows = torch.empty(words * self.world, dtype=torch.int64, device=self.device)
+        self.counts = torch.empty(2 * self.world, dtype=torch.int64, device=self.device)
+        self.mine = torch.empty(2, dtype=torch.int64, device=self.device)
+
+    def gather(self, ext_local, ops_local):
+        """ext_local: int64 tensor, 2 words per record; ops_local: int32 tensor (both on the device).  Returns
+        (rows, ext_stride, ops_stride, counts) for K2J.set_global_join_rows."""
+        n_ext, n_ops = ext_local.numel() // 2, ops_local.numel()
+        if self.ext_stride == 0:
+            self._agree(n_ext, n_ops)   # first call, on every rank
+        elif n_ext > self.ext_stride or n_ops > self.ops_stride:
+            raise ValueError("this shard outgrew the row size the ranks agreed on: create a new JoinExchange on every rank")
+        self.row[:n_ext * 2] = ext_local
+        self.row[self.ext_stride * 2:].view(ops_local.dtype)[:n_ops] = ops_local
+        self.mine[0], self.mine[1] = n_ext, n_ops
+        self.dist.all_gather_into_tensor(self.counts, self.mine)
+        self.dist.all_gather_into_tensor(self.rows, self.row)
+        return self.rows, self.ext_stride, self.ops_stride, self.counts
+
+
 def output_bases(out_bytes: int, rank: int, world: int, dist, device):
     """All-gathers the per-shard text sizes; returns (this shard's byte offset in the whole file's
     activities section, total bytes).  CPU-op events of all shards precede GPU events in the

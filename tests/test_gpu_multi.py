@@ -33,6 +33,15 @@ def _rank_main(rank, port, tmp):
         ctx.set_global_join(ext_all, ext_all.numel() // 2, own_begin, ops_all, ops_all.numel())
         res = ctx.emit()
         got = ctx.copy_output().tobytes()
+        # the same through the exchange that leaves the rows of the all-gather where they are
+        info2 = ctx.segment()
+        ex = sharding.JoinExchange(rank, WORLD, dist, dev)
+        rows, ext_stride, ops_stride, counts = ex.gather(api.device_view(info2.external_records, int(info2.n_external) * 2, "<i8", dev),
+                                                         api.device_view(info2.op_ids, int(info2.n_ops), "<i4", dev))
+        ctx.set_global_join_rows(rows, ext_stride, ops_stride, counts, WORLD, rank)
+        res_rows = ctx.emit()
+        got_rows = ctx.copy_output().tobytes()
+        assert got_rows == got and res_rows["x_events"] == res["x_events"] and res_rows["invalid_external_correlation_events"] == res["invalid_external_correlation_events"]
         shard.g_ext = ext_all.cpu().numpy().view(np.uint64)
         shard.g_ops = ops_all.cpu().numpy()
         want, stats = helpers.run_port(shard)

@@ -159,7 +159,7 @@ def test_bench_runs_another_workload():
     import json
     import subprocess
     import sys
-    r = subprocess.run([sys.executable, os.path.join(helpers.ROOT, "bench.py"), "--workload", "distributed_rank", "--n", "20000",
+    r = subprocess.run([sys.executable, os.path.join(helpers.ROOT, "bench.py"), "--workload", "distributed_rank", "--size", "20000",
                         "--steps", "2", "--warmup", "3", "--cpu-sample", "5000"], capture_output=True, text=True, cwd=helpers.ROOT)
     assert r.returncode == 0, r.stderr[-1000:]
     line = json.loads(r.stdout.strip().splitlines()[-1])
