@@ -71,6 +71,7 @@ def parse():
     ap.add_argument("--cpu-sample", type=int, default=250_000, help="size argument of the CPU-baseline / parity sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
+    ap.add_argument("--no-save-e2e", action="store_true", help="skip the save() comparison through the reference's logger factory")
     ap.add_argument("--parity-full", action="store_true",
                     help="also run the reference on the WHOLE benchmark trace and compare sha256 (minutes of CPU time)")
     a = ap.parse_args()
@@ -473,6 +474,29 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def save_through_the_reference(args):
+    """ActivityTrace::save() of the unmodified reference, once with its own ChromeTraceLogger and once with the
+    B200TraceLogger registered in its logger factory, on 250 000 kernel launches (the reference's own replayed
+    processTrace() feeds both): seconds of each save() on the third replay of one process, and whether the two files
+    are the same bytes.  None when the driver was not built."""
+    shim = os.path.join(ROOT, "oracle", "_ref", "shim_driver")
+    if not os.path.exists(shim) or args.no_save_e2e:
+        return None
+    from kineto_b200 import synth
+    trace = synth.gen_kernel_launches(250_000, seed=11)
+    with tempfile.TemporaryDirectory(dir="/dev/shm" if os.path.isdir("/dev/shm") else None) as d:
+        path, ref, mine = (os.path.join(d, f) for f in ("t.k2jt", "ref.json", "b200.json"))
+        trace.write(path)
+        r = subprocess.run([shim, path, ref, mine, "--repeat", "3"], capture_output=True, text=True)
+        if r.returncode:
+            return {"error": r.stderr[-300:]}
+        info = json.loads(r.stdout.strip().splitlines()[-1])
+        a = open(ref, "rb").read().replace(ref.encode(), b"<trace>")
+        b = open(mine, "rb").read().replace(mine.encode(), b"<trace>")
+    return {"workload": "kernel_launches, size argument 250000", "save_reference_s": info["save_reference_s"],
+            "save_b200_s": info["save_b200_s"], "files_equal": a == b, "bytes": len(b), "skipped": info["skipped"]}
+
+
 def cpu_baseline_and_parity(args, api, device):
     """The reference on one host core over a bounded sample of the same workload, and the same sample through the
     CUDA path: throughput of the former, sha256 of both texts."""
@@ -488,6 +512,7 @@ def cpu_baseline_and_parity(args, api, device):
                             "sample": "%s trace of size argument %d (%d records, %d bytes of text), one single-threaded process "
                                       "(the reference path is single-threaded), %.1f s, output on tmpfs"
                                       % (args.workload, sample_n, n_rec, len(text), secs)}}
+    out["cpu_baseline"]["save_e2e"] = save_through_the_reference(args)
     if digest is not None:
         out["parity"] = {"sha256_match": digest[0] == hashlib.sha256(text).hexdigest(), "bytes": len(text),
                          "reference_bytes": digest[1],

@@ -293,6 +293,27 @@ k2j_status k2j_write_output_at(k2j_ctx* ctx, int fd, uint64_t file_offset, uint6
 /* Waits for everything enqueued on the context's stream. */
 k2j_status k2j_synchronize(k2j_ctx* ctx);
 
+/* ---- host-side string table: for callers that hold the drained buffers as CUPTI wrote them ----
+ * In such a buffer the `name` field of a kernel record is a `const char*` into CUPTI's memory, and the reference
+ * demangles it for every activity it logs (libkineto/src/CuptiActivity.h:297-300, libkineto/src/Demangle.cpp:33-53).
+ * k2j_intern_kernel_names walks the buffers (the (byte offset, valid bytes) table of k2j_set_cupti, records sized
+ * by kind the same way) IN PLACE and replaces each CONCURRENT_KERNEL record's name pointer by the id of its
+ * name in `names` - demangled as Demangle.cpp does when `demangle` is non-zero (names above 8192 bytes and names
+ * the demangler rejects are kept; a null pointer is the empty string) - so that the bytes can go to k2j_set_cupti
+ * as they are.  Each distinct pointer is demangled once; buffers are walked on up to 16 host threads; ids are
+ * given in order of first sight, so the result does not depend on the thread count.  The pointers must be
+ * readable NUL-terminated strings when the call is made (CUPTI keeps them for the life of the module).  No GPU work.
+ * k2j_names_intern gives the id of any other string of the trace (CPU-op names, metadata keys and values, callback
+ * names); k2j_names_pool returns the pool in the layout k2j_set_strings takes (valid until the next call that
+ * adds a string).  One table per trace; not thread-safe. */
+typedef struct k2j_names k2j_names;
+k2j_status k2j_names_create(k2j_names** out);
+void k2j_names_destroy(k2j_names* names);
+k2j_status k2j_names_intern(k2j_names* names, const char* s, uint64_t len, uint32_t* id);
+k2j_status k2j_names_pool(const k2j_names* names, const uint64_t** off, const uint8_t** data, uint64_t* n_strings);
+k2j_status k2j_intern_kernel_names(k2j_names* names, uint8_t* bytes, uint64_t n_bytes, const uint64_t* buftab,
+                                   uint32_t n_buffers, int demangle, uint64_t* n_kernel_records);
+
 /* Library version string. */
 const char* k2j_version(void);
 

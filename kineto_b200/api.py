@@ -66,7 +66,8 @@ class SegmentInfo(C.Structure):
 
 EXPORTS = ["k2j_set_global_join_rows", "k2j_emit_to_host", "k2j_emit_to_fd", "k2j_exclusive_scan_u32", "k2j_exclusive_scan_u32_noalloc", "k2j_segment", "k2j_set_global_join", "k2j_emit", "k2j_create", "k2j_destroy", "k2j_last_error", "k2j_set_params", "k2j_set_strings",
            "k2j_set_cbid_names", "k2j_set_thread_map", "k2j_set_ops", "k2j_set_cupti", "k2j_run", "k2j_output",
-           "k2j_copy_output", "k2j_copy_output_async", "k2j_write_output", "k2j_write_output_at", "k2j_synchronize", "k2j_version"]
+           "k2j_copy_output", "k2j_copy_output_async", "k2j_write_output", "k2j_write_output_at", "k2j_synchronize", "k2j_version",
+           "k2j_names_create", "k2j_names_destroy", "k2j_names_intern", "k2j_names_pool", "k2j_intern_kernel_names"]
 
 _lib = None
 
@@ -106,6 +107,12 @@ def load_library():
     lib.k2j_write_output.argtypes = [vp, C.c_int, C.POINTER(C.c_uint64)]
     lib.k2j_write_output_at.argtypes = [vp, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64]
     lib.k2j_synchronize.argtypes = [vp]
+    lib.k2j_names_create.argtypes = [C.POINTER(vp)]
+    lib.k2j_names_destroy.argtypes = [vp]
+    lib.k2j_names_destroy.restype = None
+    lib.k2j_names_intern.argtypes = [vp, C.c_char_p, C.c_uint64, C.POINTER(C.c_uint32)]
+    lib.k2j_names_pool.argtypes = [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(C.c_uint64)]
+    lib.k2j_intern_kernel_names.argtypes = [vp, vp, C.c_uint64, vp, C.c_uint32, C.c_int, C.POINTER(C.c_uint64)]
     lib.k2j_version.restype = C.c_char_p
     _lib = lib
     return lib
@@ -313,6 +320,53 @@ def device_arrays(trace: tf.Trace, device="cuda:0") -> dict:
     # device memory handed to the library), so they are made complete here
     torch.cuda.synchronize(device)
     return out
+
+
+class Names:
+    """Host-side string table (k2j_names): ids for the strings of a trace and, for drained CUPTI buffers that still
+    hold `const char*` kernel names, the in-place replacement of those pointers by ids.  No GPU is needed."""
+
+    def __init__(self):
+        self.lib = load_library()
+        self.h = C.c_void_p()
+        if self.lib.k2j_names_create(C.byref(self.h)) != 0:
+            raise RuntimeError("k2j_names_create failed")
+
+    def close(self):
+        if self.h:
+            self.lib.k2j_names_destroy(self.h)
+            self.h = C.c_void_p()
+
+    def __del__(self):
+        self.close()
+
+    def intern(self, s: bytes) -> int:
+        out = C.c_uint32()
+        st = self.lib.k2j_names_intern(self.h, s, len(s), C.byref(out))
+        if st != 0:
+            raise RuntimeError("k2j_names_intern: %s" % STATUS.get(st, st))
+        return out.value
+
+    def intern_kernel_names(self, cupti: np.ndarray, buftab: np.ndarray, demangle: bool = True) -> int:
+        """`cupti` (writable uint8 array) is changed in place; returns the number of kernel records seen."""
+        assert cupti.dtype == np.uint8 and cupti.flags.writeable and cupti.flags.c_contiguous
+        bt = np.ascontiguousarray(buftab, dtype=np.uint64)
+        n = C.c_uint64()
+        st = self.lib.k2j_intern_kernel_names(self.h, _ptr(cupti), cupti.size, _ptr(bt), bt.size // 2, int(demangle), C.byref(n))
+        if st != 0:
+            raise RuntimeError("k2j_intern_kernel_names: %s" % STATUS.get(st, st))
+        return n.value
+
+    def pool(self) -> tuple[np.ndarray, np.ndarray]:
+        """(offsets, bytes) as k2j_set_strings takes them (copies)."""
+        off, data, n = C.c_void_p(), C.c_void_p(), C.c_uint64()
+        st = self.lib.k2j_names_pool(self.h, C.byref(off), C.byref(data), C.byref(n))
+        if st != 0:
+            raise RuntimeError("k2j_names_pool: %s" % STATUS.get(st, st))
+        offs = np.ctypeslib.as_array(C.cast(off, C.POINTER(C.c_uint64)), shape=(n.value + 1,)).copy()
+        total = int(offs[-1])
+        blob = np.ctypeslib.as_array(C.cast(data, C.POINTER(C.c_uint8)), shape=(total,)).copy() if total else np.zeros(0, np.uint8)
+        return offs, blob
 
 
 def process(trace: tf.Trace, device: int = 0) -> tuple[bytes, dict]:

@@ -10,7 +10,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB = os.path.join(HERE, "libk2j.so")
 SRC = os.path.join(HERE, "csrc", "k2j.cu")
 SRC_NOALLOC = os.path.join(HERE, "csrc", "k2j_noalloc.cu")
-DEPS = [SRC, SRC_NOALLOC] + [os.path.join(HERE, "csrc", f) for f in ("k2j_kernels.cuh", "k2j_format.cuh", "k2j_sink.cuh", "k2j_sort.cuh", "k2j_pow10.h", "k2j_cupti_sizes.h")] + [
+SRC_NAMES = os.path.join(HERE, "csrc", "k2j_names.cpp")
+DEPS = [SRC, SRC_NOALLOC, SRC_NAMES] + [os.path.join(HERE, "csrc", f) for f in ("k2j_kernels.cuh", "k2j_format.cuh", "k2j_sink.cuh", "k2j_sort.cuh", "k2j_pow10.h", "k2j_cupti_sizes.h")] + [
     os.path.join(os.path.dirname(HERE), "include", "k2j.h")]
 
 
@@ -32,7 +33,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not needs_build():
         return LIB
     cmd = [nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-           "--shared", "-Xcompiler", "-fPIC", "-Xptxas", "-v", "-o", LIB, SRC, SRC_NOALLOC, "-lcudart"]
+           "--shared", "-Xcompiler", "-fPIC", "-Xptxas", "-v", "-o", LIB, SRC, SRC_NOALLOC, SRC_NAMES, "-lcudart"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or r.returncode != 0:
         sys.stderr.write(r.stdout + r.stderr)

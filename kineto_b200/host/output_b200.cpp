@@ -121,6 +121,23 @@ struct Timed {
 // context back; the next logger on that device takes it.  Contexts are kept until the process exits.
 struct ContextPool {
   static std::mutex& mu() { static std::mutex m; return m; }
+  // the occupancy fields need the properties of every device: read once per process, not once per flush
+  static const std::vector<k2j_device_props>& deviceProps() {
+    static const std::vector<k2j_device_props> props = [] {
+      std::vector<k2j_device_props> v;
+      int ndev = 0;
+      if (cudaGetDeviceCount(&ndev) != cudaSuccess) ndev = 0;
+      for (int i = 0; i < ndev; i++) {
+        cudaDeviceProp dp;
+        if (cudaGetDeviceProperties(&dp, i) != cudaSuccess) break;
+        v.push_back({dp.major, dp.minor, dp.maxThreadsPerBlock, dp.maxThreadsPerMultiProcessor, dp.regsPerBlock,
+                     dp.regsPerMultiprocessor, dp.warpSize, dp.multiProcessorCount, dp.sharedMemPerBlock,
+                     dp.sharedMemPerBlockOptin, dp.sharedMemPerMultiprocessor, dp.reservedSharedMemPerBlock});
+      }
+      return v;
+    }();
+    return props;
+  }
   static std::vector<std::pair<int, k2j_ctx*>>& free() { static std::vector<std::pair<int, k2j_ctx*>> v; return v; }
   static k2j_ctx* take(int device) {
     {
@@ -174,12 +191,13 @@ struct B200TraceLogger::Impl {
     std::vector<uint32_t> name, flow, mdoff{0};
     std::vector<uint8_t> flowt;
     std::vector<k2j_md_entry> md;
-    std::vector<uint8_t> cupti;
-    // Records put in front of `cupti` that only feed lookups (their timestamps lie before the window, so they
-    // print nothing): what the profiler had already resolved for a synchronisation activity when it reached the
-    // logger - its context's device, the CUDA event record it waits on - restated as the records that make the
-    // device-side lookups give the same answer.
-    std::vector<uint8_t> prefix;
+    // The run's record bytes, written once by the threads that packed them (no zero fill, no regrowth).  In front
+    // go the records that only feed lookups (their timestamps lie before the window, so they print nothing): what
+    // the profiler had already resolved for a synchronisation activity when it reached the logger - its context's
+    // device, the CUDA event record it waits on - restated as the records that make the device-side lookups give
+    // the same answer.
+    std::unique_ptr<uint8_t[]> cupti;
+    size_t cuptiBytes = 0;
     // ids of the CPU-side activities of this run: a bitmap for the usual small non-negative ids, a set for the rest
     std::vector<uint64_t> opIdBits;
     std::unordered_set<int32_t> opIdRest;
@@ -248,6 +266,7 @@ struct B200TraceLogger::Impl {
     std::vector<const void*> namePtrs;
     std::vector<std::string> names;                                  // demangled, by local id
     std::vector<uint32_t> kernelOffsets;                             // kernel records in `cupti` (their name field holds a local id)
+    std::vector<uint32_t> global;                                    // local name id -> pool id, set by mergePiece
     std::unordered_map<uint32_t, bool> ctxDeclared;
     size_t skipped = 0;
     std::string firstSkippedName;
@@ -261,6 +280,35 @@ struct B200TraceLogger::Impl {
     }
   };
   std::vector<const libkineto::ITraceActivity*> pending;
+  // ---- CPU-side activities: gathered as pointers too, turned into columns when the run is flushed ----
+  // The profiler keeps them alive and in place until the trace is finalised (GenericActivityProfiler.cpp:249-254;
+  // the in-memory logger replays its own copies, which live as long as it does, output_membuf.h:64-66, :91-107),
+  // so visiting their metadata - one unordered_map walk and several interned strings per activity - can be split
+  // over threads like the wrappers: each thread fills the columns of a contiguous slice with string ids of its
+  // own, and the slices are appended in order with their ids mapped to pool ids.  A caller that hands over
+  // activities that do not outlive the call sets copyOps (environment K2J_SHIM_COPY_OPS=1): they are then turned
+  // into columns at once, on the calling thread.
+  std::vector<const libkineto::GenericTraceActivity*> pendingOps;
+  bool copyOps = false;
+  struct OpPiece {
+    std::vector<int64_t> start, end, resource;
+    std::vector<int32_t> id, dev, thread, type;
+    std::vector<uint32_t> name, flow, mdoff;
+    std::vector<uint8_t> flowt;
+    std::vector<k2j_md_entry> md;
+    std::unordered_map<std::string_view, uint32_t> ids;   // views into the live activities or into `owned`
+    std::vector<std::string_view> strs;
+    std::deque<std::string> owned;
+    uint32_t local(std::string_view v) {
+      auto it = ids.find(v);
+      if (it != ids.end()) return it->second;
+      const uint32_t k = (uint32_t)strs.size();
+      ids.emplace(v, k); strs.push_back(v);
+      return k;
+    }
+  };
+  void opColumns(const libkineto::GenericTraceActivity& op, OpPiece& p) const;
+  void packOps();
   size_t* skippedOut = nullptr;
   void packOne(const libkineto::ITraceActivity& a, Piece& p) const;
   void mergePiece(Piece& p);
@@ -269,14 +317,84 @@ struct B200TraceLogger::Impl {
   bool flushRun();
 };
 
+// One CPU-side activity into the columns of its piece (string ids are the piece's own).
+void B200TraceLogger::Impl::opColumns(const libkineto::GenericTraceActivity& op, OpPiece& p) const {
+  p.start.push_back(op.startTime); p.end.push_back(op.endTime); p.id.push_back(op.id); p.dev.push_back(op.device);
+  p.resource.push_back(op.resource); p.thread.push_back(op.threadId); p.type.push_back((int32_t)op.activityType);
+  p.name.push_back(p.local(op.activityName)); p.flow.push_back(op.flow.id);
+  p.flowt.push_back((uint8_t)(op.flow.type | (op.flow.start << 4)));
+  MdCollector mc;
+  op.visitTypedMetadata(mc);
+  for (auto& e : mc.entries) {
+    k2j_md_entry k{p.local(e.key), e.type, e.value};
+    if (e.type == K2J_MD_STRING || e.type == K2J_MD_RAWJSON) {
+      // text rendered for this visit (collections) lives in the collector: the piece takes it over
+      bool ownedText = false;
+      for (const std::string& o : mc.owned) if (o.data() == e.text.data()) { ownedText = true; break; }
+      if (ownedText) { p.owned.emplace_back(e.text); k.value = p.local(p.owned.back()); }
+      else k.value = p.local(e.text);
+    }
+    p.md.push_back(k);
+  }
+  for (const auto& cv : op.counterValues()) {  // counter events (output_json.cpp:679-716): name and value, in order
+    uint64_t bits; const double v = cv.second; memcpy(&bits, &v, 8);
+    p.md.push_back(k2j_md_entry{p.local(cv.first), K2J_MD_COUNTER, bits});
+  }
+  p.mdoff.push_back((uint32_t)p.md.size());
+}
+
+void B200TraceLogger::Impl::packOps() {
+  if (pendingOps.empty()) return;
+  Timed timed(tOps);
+  std::vector<const libkineto::GenericTraceActivity*> acts;
+  acts.swap(pendingOps);
+  const size_t n = acts.size();
+  const unsigned hw = std::max(1u, std::thread::hardware_concurrency());
+  const size_t nt = n < 20000 ? 1 : std::min<size_t>({(size_t)hw, (size_t)16, n / 10000});
+  std::vector<OpPiece> pieces(nt);
+  auto work = [&](size_t t) {
+    const size_t lo = n * t / nt, hi = n * (t + 1) / nt;
+    OpPiece& p = pieces[t];
+    p.start.reserve(hi - lo); p.md.reserve(4 * (hi - lo));
+    for (size_t i = lo; i < hi; i++) opColumns(*acts[i], p);
+  };
+  if (nt == 1) work(0);
+  else {
+    std::vector<std::thread> threads;
+    for (size_t t = 1; t < nt; t++) threads.emplace_back(work, t);
+    work(0);
+    for (auto& th : threads) th.join();
+  }
+  Run& r = run;
+  for (OpPiece& p : pieces) {  // in order: ids of the piece become pool ids, its columns follow the run's
+    std::vector<uint32_t> global(p.strs.size());
+    for (size_t i = 0; i < p.strs.size(); i++) global[i] = intern(p.strs[i]);
+    const uint32_t mdBase = (uint32_t)r.md.size();
+    r.start.insert(r.start.end(), p.start.begin(), p.start.end()); r.end.insert(r.end.end(), p.end.begin(), p.end.end());
+    r.resource.insert(r.resource.end(), p.resource.begin(), p.resource.end()); r.id.insert(r.id.end(), p.id.begin(), p.id.end());
+    r.dev.insert(r.dev.end(), p.dev.begin(), p.dev.end()); r.thread.insert(r.thread.end(), p.thread.begin(), p.thread.end());
+    r.type.insert(r.type.end(), p.type.begin(), p.type.end()); r.flow.insert(r.flow.end(), p.flow.begin(), p.flow.end());
+    r.flowt.insert(r.flowt.end(), p.flowt.begin(), p.flowt.end());
+    for (uint32_t v : p.name) r.name.push_back(global[v]);
+    for (uint32_t v : p.mdoff) r.mdoff.push_back(mdBase + v);
+    for (k2j_md_entry e : p.md) {
+      e.key = global[e.key];
+      if (e.type == K2J_MD_STRING || e.type == K2J_MD_RAWJSON) e.value = global[(size_t)e.value];
+      r.md.push_back(e);
+    }
+    for (int32_t v : p.id) r.noteOp(v);
+  }
+}
+
 bool B200TraceLogger::Impl::flushRun() {
+  packOps();
   packPending();
   Run r;
   std::swap(r, run);
   std::vector<int32_t> links;
   std::swap(links, linkedIds);
   const size_t nops = r.start.size();
-  if (nops == 0 && r.cupti.empty()) return true;
+  if (nops == 0 && r.cuptiBytes == 0) return true;
   if (!ctx || !out) return false;
   // CPU ops a record is linked to may have been logged in an earlier run: make them joinable here as
   // unselected activities (type bit cleared below), which take part in the join but print nothing.
@@ -294,29 +412,14 @@ bool B200TraceLogger::Impl::flushRun() {
   p.ts_mode = 0;  // CuptiActivity<T>::timestamp() was not used: raw timestamps are converted below
   p.flags = 0;
   p.activity_type_mask = ~(1u << kHidden);
-  int ndev = 0;
-  if (cudaGetDeviceCount(&ndev) != cudaSuccess) ndev = 0;
-  std::vector<k2j_device_props> props(ndev);
-  for (int i = 0; i < ndev; i++) {
-    cudaDeviceProp dp;
-    if (cudaGetDeviceProperties(&dp, i) != cudaSuccess) { props.resize(i); break; }
-    props[i] = {dp.major, dp.minor, dp.maxThreadsPerBlock, dp.maxThreadsPerMultiProcessor, dp.regsPerBlock,
-                dp.regsPerMultiprocessor, dp.warpSize, dp.multiProcessorCount, dp.sharedMemPerBlock,
-                dp.sharedMemPerBlockOptin, dp.sharedMemPerMultiprocessor, dp.reservedSharedMemPerBlock};
-  }
+  const std::vector<k2j_device_props>& props = ContextPool::deviceProps();
   p.n_devices = (int32_t)props.size();
-  if (use_cupti_tsc()) {
-    // The reference converts through get_time_converter(); its constants are not exposed, so the raw
-    // timestamps are converted on the host into the record copies before upload (ts_mode stays 0).
-  }
   k2j_ops ops{};
   const size_t n = r.start.size();
   ops.n_ops = n; ops.start_ns = r.start.data(); ops.end_ns = r.end.data(); ops.id = r.id.data(); ops.device = r.dev.data();
   ops.resource = r.resource.data(); ops.thread = r.thread.data(); ops.type = r.type.data(); ops.name = r.name.data();
   ops.flow_id = r.flow.data(); ops.flow_info = r.flowt.data(); ops.md_off = r.mdoff.data(); ops.md = r.md.data();
-  r.prefix.insert(r.prefix.end(), r.cupti.begin(), r.cupti.end());
-  r.cupti.swap(r.prefix);
-  const uint64_t buftab[2] = {0, r.cupti.size()};
+  const uint64_t buftab[2] = {0, r.cuptiBytes};
   k2j_result res;
   tSetup.start();
   bool ok = k2j_set_params(ctx, &p, props.data()) == K2J_OK &&
@@ -324,7 +427,7 @@ bool B200TraceLogger::Impl::flushRun() {
             k2j_set_cbid_names(ctx, rtNames.data(), (uint32_t)rtNames.size(), drNames.data(), (uint32_t)drNames.size()) == K2J_OK &&
             k2j_set_thread_map(ctx, tidPairs.data(), (uint32_t)(tidPairs.size() / 2)) == K2J_OK &&
             k2j_set_ops(ctx, &ops) == K2J_OK &&
-            k2j_set_cupti(ctx, r.cupti.data(), r.cupti.size(), buftab, r.cupti.empty() ? 0 : 1) == K2J_OK;
+            k2j_set_cupti(ctx, r.cupti.get(), r.cuptiBytes, buftab, r.cuptiBytes ? 1 : 0) == K2J_OK;
   tSetup.stop();
   tRun.start();
   ok = ok && k2j_run(ctx, &res) == K2J_OK;
@@ -359,6 +462,8 @@ B200TraceLogger::B200TraceLogger(const std::string& traceFileName, int cudaDevic
     if (impl_->out) { fclose(impl_->out); impl_->out = nullptr; remove(impl_->tempFileName.c_str()); }
   }
   impl_->invalidId = impl_->intern("INVALID");
+  const char* copy = getenv("K2J_SHIM_COPY_OPS");
+  impl_->copyOps = copy && *copy && *copy != '0';
 }
 
 B200TraceLogger::~B200TraceLogger() {
@@ -432,22 +537,9 @@ void B200TraceLogger::handleTraceSpan(const TraceSpan& span) {
 void B200TraceLogger::handleGenericActivity(const libkineto::GenericTraceActivity& op) {
   if (!impl_->out) return;
   Impl& m = *impl_;
-  Timed timed(m.tOps);
   if (m.run.hasCupti) m.flushRun();  // a run is CPU-side activities followed by CUPTI records
-  auto& r = m.run;
-  r.start.push_back(op.startTime); r.end.push_back(op.endTime); r.id.push_back(op.id); r.dev.push_back(op.device);
-  r.noteOp(op.id);
-  r.resource.push_back(op.resource); r.thread.push_back(op.threadId); r.type.push_back((int32_t)op.activityType);
-  r.name.push_back(m.intern(op.activityName)); r.flow.push_back(op.flow.id);
-  r.flowt.push_back((uint8_t)(op.flow.type | (op.flow.start << 4)));
-  MdCollector mc;
-  op.visitTypedMetadata(mc);
-  for (auto& e : mc.entries) {
-    k2j_md_entry k{m.intern(e.key), e.type, e.value};
-    if (e.type == K2J_MD_STRING || e.type == K2J_MD_RAWJSON) k.value = m.intern(e.text);
-    r.md.push_back(k);
-  }
-  r.mdoff.push_back((uint32_t)r.md.size());
+  m.pendingOps.push_back(&op);
+  if (m.copyOps) m.packOps();        // the activity may not outlive this call: into columns now
 }
 
 void B200TraceLogger::handleActivity(const libkineto::ITraceActivity& a) {
@@ -512,7 +604,10 @@ void B200TraceLogger::Impl::packOne(const libkineto::ITraceActivity& a, Piece& p
   };
   if (auto* k = ty == ActivityType::CONCURRENT_KERNEL ? dynamic_cast<const GpuActivity<CUpti_ActivityKernelType>*>(&a) : nullptr) {
     const libkineto::ITraceActivity* l = link();
-    if (l && l->name() == "record_param_comms") p.collectives.push_back(l);
+    if (l) {  // a collective's CPU op: compared in place where the name is a member, no string per kernel
+      auto* g = dynamic_cast<const libkineto::GenericTraceActivity*>(l);
+      if (g ? g->activityName == "record_param_comms" : l->name() == "record_param_comms") p.collectives.push_back(l);
+    }
     CUpti_ActivityKernelType rec = k->raw();
     convert(rec);
     auto it = p.nameIds.find(rec.name);
@@ -602,22 +697,14 @@ void B200TraceLogger::Impl::packOne(const libkineto::ITraceActivity& a, Piece& p
   }
 }
 
-// A piece joins the run: local kernel-name ids become pool ids, first sightings stay first sightings.
+// A piece joins the run: local kernel-name ids get pool ids, first sightings stay first sightings.  Its record
+// bytes are moved by the threads afterwards (packPending).
 void B200TraceLogger::Impl::mergePiece(Piece& p) {
-  std::vector<uint32_t> global(p.names.size());
+  p.global.resize(p.names.size());
   for (size_t i = 0; i < p.names.size(); i++) {
     auto it = kernelNameIds.find(p.namePtrs[i]);
-    global[i] = it != kernelNameIds.end() ? it->second : (kernelNameIds[p.namePtrs[i]] = intern(p.names[i]));
+    p.global[i] = it != kernelNameIds.end() ? it->second : (kernelNameIds[p.namePtrs[i]] = intern(p.names[i]));
   }
-  for (uint32_t off : p.kernelOffsets) {
-    uint8_t* field = p.cupti.data() + off + offsetof(CUpti_ActivityKernelType, name);
-    uint64_t id;
-    memcpy(&id, field, 8);
-    id = global[(size_t)id];
-    memcpy(field, &id, 8);
-  }
-  run.cupti.insert(run.cupti.end(), p.cupti.begin(), p.cupti.end());
-  run.prefix.insert(run.prefix.end(), p.prefix.begin(), p.prefix.end());
   linkedIds.insert(linkedIds.end(), p.linkedIds.begin(), p.linkedIds.end());
   for (const libkineto::ITraceActivity* op : p.collectives) noteCollective(*op);
   for (size_t i = 0; i + 1 < p.tidPairs.size(); i += 2) {
@@ -646,22 +733,42 @@ void B200TraceLogger::Impl::packPending() {
   acts.swap(pending);
   const size_t n = acts.size();
   const unsigned hw = std::max(1u, std::thread::hardware_concurrency());
-  const size_t nt = n < 50000 ? 1 : std::min<size_t>({(size_t)hw, (size_t)8, n / 25000});
+  const size_t nt = n < 50000 ? 1 : std::min<size_t>({(size_t)hw, (size_t)16, n / 25000});
   std::vector<Piece> pieces(nt);
-  auto work = [&](size_t t) {
+  auto onThreads = [&](auto&& fn) {
+    if (nt == 1) { fn(0); return; }
+    std::vector<std::thread> threads;
+    for (size_t t = 1; t < nt; t++) threads.emplace_back(fn, t);
+    fn(0);
+    for (auto& th : threads) th.join();
+  };
+  onThreads([&](size_t t) {
     const size_t lo = n * t / nt, hi = n * (t + 1) / nt;
     Piece& p = pieces[t];
     p.cupti.reserve((hi - lo) * 160);
     for (size_t i = lo; i < hi; i++) packOne(*acts[i], p);
-  };
-  if (nt == 1) work(0);
-  else {
-    std::vector<std::thread> threads;
-    for (size_t t = 1; t < nt; t++) threads.emplace_back(work, t);
-    work(0);
-    for (auto& th : threads) th.join();
-  }
+  });
+  // where each piece's bytes go: all lookup-only records first, then the records, both in piece order
+  std::vector<size_t> prefixAt(nt), recordsAt(nt);
+  size_t total = 0;
+  for (size_t t = 0; t < nt; t++) { prefixAt[t] = total; total += pieces[t].prefix.size(); }
+  for (size_t t = 0; t < nt; t++) { recordsAt[t] = total; total += pieces[t].cupti.size(); }
   for (Piece& p : pieces) mergePiece(p);
+  run.cupti.reset(new uint8_t[total ? total : 1]);
+  run.cuptiBytes = total;
+  uint8_t* dst = run.cupti.get();
+  onThreads([&](size_t t) {
+    Piece& p = pieces[t];
+    for (uint32_t off : p.kernelOffsets) {
+      uint8_t* field = p.cupti.data() + off + offsetof(CUpti_ActivityKernelType, name);
+      uint64_t id;
+      memcpy(&id, field, 8);
+      id = p.global[(size_t)id];
+      memcpy(field, &id, 8);
+    }
+    if (!p.prefix.empty()) memcpy(dst + prefixAt[t], p.prefix.data(), p.prefix.size());
+    if (!p.cupti.empty()) memcpy(dst + recordsAt[t], p.cupti.data(), p.cupti.size());
+  });
 }
 
 void B200TraceLogger::finalizeTrace(const Config&, std::unique_ptr<ActivityBuffers> /*buffers*/, int64_t endTime) {

@@ -101,6 +101,18 @@ def demangles(name: bytes) -> bool:
     return status.value == 0
 
 
+def demangled(name: bytes) -> bytes:
+    """What the reference's demangle() shows for `name` (libkineto/src/Demangle.cpp:33-53)."""
+    if len(name) > 8192 or not demangles(name):
+        return name
+    ctypes, lib, libc = _cxa
+    status = ctypes.c_int(0)
+    p = lib.__cxa_demangle(name, None, None, ctypes.byref(status))
+    out = ctypes.string_at(p)
+    libc.free(p)
+    return out
+
+
 def name_pool(rng, count: int, lo: int, hi: int, escape_fraction: float = 0.0) -> list[bytes]:
     """`count` distinct ASCII identifiers of length uniform in [lo, hi].  A fraction carries bytes
     the JSON writer treats specially: quote, backslash, newline, TAB/control, UTF-8 multibyte."""

@@ -131,3 +131,42 @@ def activities_span(doc: bytes) -> bytes:
     a = doc.find(b'\n  {\n    "ph": "X",')
     b = doc.rfind(b'\n  {\n    "ph": "X",\n    "cat": "Trace",')
     return doc[a:b]
+
+
+MANGLED = [b"_Z3fooIiEvT_", b"_ZN2at6native12_GLOBAL__N_110sum_kernelIfLi4EEEvPT_PKS3_l", b"_Z10saxpy_halfiPK6__halfPS_",
+           b"_ZN7cutlass6KernelINS_4gemm6kernel4GemmIfEEEEvNT_6ParamsE", b"_Z", b"_Znot_a_symbol", b"G3abc", b"x" * 9000]
+
+
+def with_raw_kernel_names(trace, extra_names=()):
+    """A copy of `trace`'s CUPTI bytes as CUPTI would have written them: every kernel record's `name` field holds the
+    address of a NUL-terminated string instead of a string id.  `extra_names` (mangled symbols, say) replace the
+    names of the first kernels, in turn.  Returns (bytes array, keep-alive object, expected name per kernel record)."""
+    import ctypes
+    import numpy as np
+    from kineto_b200 import tracefile as tf
+    pool = trace.pool()
+    strings = [pool[i] for i in range(len(pool))]
+    texts = list(strings) + list(extra_names)
+    blob = b"\0".join(texts) + b"\0"
+    buf = ctypes.create_string_buffer(blob, len(blob))
+    base = ctypes.addressof(buf)
+    addr, pos = [], 0
+    for t in texts:
+        addr.append(base + pos)
+        pos += len(t) + 1
+    raw = np.array(trace.cupti, dtype=np.uint8, copy=True)
+    expected, k = [], 0
+    for b in range(trace.n_buffers):
+        at, valid = int(trace.buftab[2 * b]), int(trace.buftab[2 * b + 1])
+        end = at + valid
+        while at + 8 <= end:
+            kind = int(raw[at:at + 4].view(np.uint32)[0])
+            size = (tf.RECORD_SIZE[kind] + 7) & ~7
+            if kind == tf.KIND_CONCURRENT_KERNEL:
+                field = raw[at + 104:at + 112].view(np.uint64)
+                which = len(strings) + k if k < len(extra_names) else int(field[0])
+                field[0] = addr[which]
+                expected.append(texts[which])
+                k += 1
+            at += size
+    return raw, buf, expected

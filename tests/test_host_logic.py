@@ -177,3 +177,87 @@ def test_window_sink_on_cpu(tmp_path):
         assert sc.sc_fuzz(seed, 300, seed % 40, (seed * 7) % 400) == 0, seed
     assert sc.sc_fuzz(1000, 2000, 0, 0) == 0      # shortest events only
     assert sc.sc_fuzz(1001, 50, 6, 5000) == 0     # copies far longer than a window
+
+
+def kernel_name_ids(cupti, buftab):
+    from kineto_b200 import tracefile as tf
+    out = []
+    for b in range(len(buftab) // 2):
+        at, end = int(buftab[2 * b]), int(buftab[2 * b]) + int(buftab[2 * b + 1])
+        while at + 8 <= end:
+            kind = int(cupti[at:at + 4].view(np.uint32)[0])
+            if kind == tf.KIND_CONCURRENT_KERNEL:
+                out.append(int(cupti[at + 104:at + 112].view(np.uint64)[0]))
+            at += (tf.RECORD_SIZE[kind] + 7) & ~7
+    return out
+
+
+@pytest.mark.parametrize("n,demangle", [(3000, True), (3000, False), (120_000, True)], ids=["small", "kept_mangled", "threads"])
+def test_intern_kernel_names_replaces_pointers_by_ids_of_demangled_names(n, demangle):
+    """Buffers as CUPTI writes them (kernel names are pointers) become buffers for k2j_set_cupti: every kernel record
+    names the id of demangle(name) as libkineto/src/Demangle.cpp:33-53 gives it, each distinct string once in the
+    pool, ids in order of first sight whatever the number of threads (the large case is walked on several)."""
+    from kineto_b200 import api, synth
+    trace = synth.gen_mixed(n, seed=77, pool_size=300, escape_fraction=0.1)
+    raw, keep, expected = helpers.with_raw_kernel_names(trace, helpers.MANGLED)
+    names = api.Names()
+    pre = names.intern(b"cudaLaunchKernel")
+    assert pre == 0 and names.intern(b"cudaLaunchKernel") == 0 and names.intern(b"") == 1
+    seen = names.intern_kernel_names(raw, trace.buftab, demangle=demangle)
+    assert seen == len(expected) > len(helpers.MANGLED)
+    off, data = names.pool()
+    blob = data.tobytes()
+    strings = [blob[int(off[i]):int(off[i + 1])] for i in range(len(off) - 1)]
+    assert len(set(strings)) == len(strings)
+    want = [synth.demangled(e) if demangle else e for e in expected]
+    ids = kernel_name_ids(raw, trace.buftab)
+    assert [strings[i] for i in ids] == want
+    if demangle:
+        assert strings[ids[0]] == b"void foo<int>(int)" and strings[ids[4]] == b"_Z" and strings[ids[7]] == b"x" * 9000
+    first_sight = list(dict.fromkeys(want))
+    assert [s for s in strings[2:]] == [s for s in first_sight if s not in (b"cudaLaunchKernel", b"")]
+    # everything that is not a kernel name is untouched
+    a, b = np.array(trace.cupti, copy=True), raw.copy()
+    for arr in (a, b):
+        for at in kernel_offsets(arr, trace.buftab):
+            arr[at + 104:at + 112] = 0
+    assert np.array_equal(a, b)
+    del keep
+
+
+def kernel_offsets(cupti, buftab):
+    from kineto_b200 import tracefile as tf
+    for b in range(len(buftab) // 2):
+        at, end = int(buftab[2 * b]), int(buftab[2 * b]) + int(buftab[2 * b + 1])
+        while at + 8 <= end:
+            kind = int(cupti[at:at + 4].view(np.uint32)[0])
+            if kind == tf.KIND_CONCURRENT_KERNEL:
+                yield at
+            at += (tf.RECORD_SIZE[kind] + 7) & ~7
+
+
+def test_intern_kernel_names_rejects_bad_tables():
+    from kineto_b200 import api
+    names = api.Names()
+    buf = np.zeros(64, np.uint8)
+    for tab in ([4, 8], [0, 72], [128, 0]):
+        with pytest.raises(RuntimeError, match="INVALID_ARGUMENT"):
+            names.intern_kernel_names(buf, np.array(tab, np.uint64))
+    assert names.intern_kernel_names(buf, np.array([0, 64], np.uint64)) == 0  # kind 0: ends the walk
+    assert names.intern_kernel_names(np.zeros(0, np.uint8), np.zeros(0, np.uint64)) == 0
+
+
+def test_intern_kernel_names_round_trip_gives_the_generated_buffers():
+    """With the trace's own strings interned first (ids 0..n-1 in pool order), replacing the pointers gives back the
+    generated buffers bit for bit: the bytes k2j_set_cupti is tested with everywhere else."""
+    from kineto_b200 import api, synth
+    trace = synth.gen_kernel_launches(20_000, seed=79, pool_size=500, user_annotations=5)
+    raw, keep, _ = helpers.with_raw_kernel_names(trace)
+    assert not np.array_equal(raw, trace.cupti)
+    names = api.Names()
+    pool = trace.pool()
+    assert [names.intern(pool[i]) for i in range(len(pool))] == list(range(len(pool)))
+    names.intern_kernel_names(raw, trace.buftab)
+    assert np.array_equal(raw, trace.cupti)
+    off, data = names.pool()
+    assert np.array_equal(off, trace.pool_off) and np.array_equal(data, trace.pool_data)
