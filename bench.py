@@ -48,9 +48,10 @@ METRIC = "trace_records_per_sec"
 UNIT = "records/s"
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one emit launch (k_events<true, false>) divided by the JSON bytes it
-# wrote: ncu capture of a whole launch of the kernel_launches workload at 1 M launches (1.86 GB of text, far
-# beyond the L2), summarised in profiles/; traffic grows in proportion to the text, so the line scales it.
-EMIT_TRAFFIC_PER_OUT_BYTE = None
+# wrote, from ncu captures of whole launches at size argument 1 000 000 (1.5 and 1.9 GB of text, far beyond the L2;
+# profiles/emit_kernel_dram_traffic.txt).  Traffic grows in proportion to the text, so the line scales it to the
+# launch it timed; workloads without a capture report null.
+EMIT_TRAFFIC_PER_OUT_BYTE = {"mixed": 2254.8 / 1510.1, "kernel_launches": 2637.2 / 1858.1}
 SLAB_BYTES = 256 << 20
 
 DEFAULT_N = {"mixed": 10_000_000, "kernel_launches": 1_000_000, "op_tree": 2_000_000, "distributed_rank": 2_000_000,
@@ -449,7 +450,8 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "kernel": "k_events<true, false> (emit pass)", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
                          "algorithmic_bytes_per_launch": alg_emit, "ms_per_launch": emit_ms,
-                         "traffic": (EMIT_TRAFFIC_PER_OUT_BYTE * out_bytes) if EMIT_TRAFFIC_PER_OUT_BYTE else None,
+                         "traffic": (EMIT_TRAFFIC_PER_OUT_BYTE[args.workload] * out_bytes) if args.workload in EMIT_TRAFFIC_PER_OUT_BYTE else None,
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at size argument 1000000, scaled by the text bytes",
                          "pipeline_frac": alg_all / (sum(stage.values()) / args.steps * 1e-3) / 1e9 / peak},
             "stage_ms_per_step": dict({k: v / args.steps for k, v in stage.items()}, ms_exchange=ms_exchange),
         }

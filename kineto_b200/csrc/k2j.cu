@@ -4,7 +4,6 @@
 
 #include <cuda_runtime.h>
 #include <errno.h>
-#include <fcntl.h>
 #include <unistd.h>
 #include <stdarg.h>
 #include <stdio.h>
@@ -12,9 +11,7 @@
 
 #include <algorithm>
 #include <map>
-#include <mutex>
 #include <string>
-#include <thread>
 #include <unordered_map>
 #include <vector>
 
@@ -1098,52 +1095,6 @@ k2j_status stream_bytes(k2j_ctx* c, const uint8_t* src, int fd, bool positioned,
     }
     return true;
   };
-  // A descriptor with a position of its own (a regular file, not opened for appending) takes each chunk as several
-  // pwrite calls on threads: filling the page cache is the slow side (a few GB/s per thread), the copy from the
-  // GPU is not.  The descriptor's position is moved past the bytes afterwards, as write() would have left it.
-  constexpr unsigned kWriters = 4;
-  constexpr size_t kMinPerWriter = 1u << 20;
-  off_t start_pos = -1;
-  if (!positioned && total >= 2 * kMinPerWriter) {
-    const int fl = fcntl(fd, F_GETFL);
-    if (fl >= 0 && !(fl & O_APPEND)) start_pos = lseek(fd, 0, SEEK_CUR);
-  }
-  const bool parallel = positioned ? total >= 2 * kMinPerWriter : start_pos >= 0;
-  const uint64_t base_offset = positioned ? file_offset : (start_pos >= 0 ? (uint64_t)start_pos : 0);
-  std::mutex err_mu;
-  auto write_chunk = [&](const char* p, size_t n, uint64_t off) -> bool {
-    const unsigned parts = parallel ? (unsigned)std::min<size_t>(kWriters, std::max<size_t>(1, n / kMinPerWriter)) : 1;
-    if (parts <= 1) {
-      if (parallel && !positioned) {  // same call as the threads make
-        size_t left = n; uint64_t o = base_offset + off; const char* q = p;
-        while (left) {
-          const ssize_t w = pwrite(fd, q, left, (off_t)o);
-          if (w < 0) { if (errno == EINTR) continue; io_errno = errno; return false; }
-          if (w == 0) { io_errno = EIO; return false; }
-          q += w; left -= (size_t)w; o += (uint64_t)w;
-        }
-        return true;
-      }
-      return write_all(p, n, file_offset + off);
-    }
-    bool ok = true;
-    auto part = [&](unsigned k) {
-      size_t lo = n * k / parts, hi = n * (k + 1) / parts;
-      lo &= ~(size_t)4095; if (k + 1 < parts) hi &= ~(size_t)4095;
-      const char* q = p + lo; size_t left = hi - lo; uint64_t o = base_offset + off + lo;
-      while (left) {
-        const ssize_t w = pwrite(fd, q, left, (off_t)o);
-        if (w < 0 && errno == EINTR) continue;
-        if (w <= 0) { std::lock_guard<std::mutex> g(err_mu); io_errno = w < 0 ? errno : EIO; ok = false; return; }
-        q += w; left -= (size_t)w; o += (uint64_t)w;
-      }
-    };
-    std::thread th[kWriters];
-    for (unsigned k = 1; k < parts; k++) th[k] = std::thread(part, k);
-    part(0);
-    for (unsigned k = 1; k < parts; k++) th[k].join();
-    return ok;
-  };
   const uint64_t n_chunks = (total + kChunk - 1) / kChunk;
   bool io_ok = true;
   cudaError_t e = cudaSuccess;
@@ -1156,7 +1107,7 @@ k2j_status stream_bytes(k2j_ctx* c, const uint8_t* src, int fd, bool positioned,
     if (i > 0 && e == cudaSuccess) {  // ... while chunk i - 1, which has arrived, goes to the file
       e = cudaEventSynchronize(c->stage_ev[(i - 1) & 1]);
       const size_t len = (size_t)std::min<uint64_t>(kChunk, total - (i - 1) * kChunk);
-      if (e == cudaSuccess && io_ok && !write_chunk(static_cast<const char*>(c->h_stage[(i - 1) & 1]), len, (i - 1) * kChunk))
+      if (e == cudaSuccess && io_ok && !write_all(static_cast<const char*>(c->h_stage[(i - 1) & 1]), len, file_offset + (i - 1) * kChunk))
         io_ok = false;  // keep draining the copies
     }
   }
@@ -1165,8 +1116,6 @@ k2j_status stream_bytes(k2j_ctx* c, const uint8_t* src, int fd, bool positioned,
     return fail(c, K2J_ERR_CUDA, "streaming the output: %s", cudaGetErrorString(e));
   }
   if (!io_ok) return fail(c, K2J_ERR_IO, "write: %s", strerror(io_errno));
-  if (!positioned && start_pos >= 0 && lseek(fd, (off_t)((uint64_t)start_pos + total), SEEK_SET) < 0)
-    return fail(c, K2J_ERR_IO, "lseek: %s", strerror(errno));
   return K2J_OK;
 }
 }  // namespace
