@@ -153,27 +153,55 @@ struct WindowSink {
     for (int i = 0; i < N / 4; i++) put4(l.w[i]);
     if (N % 4) put(l.w[N / 4], N % 4);
   }
-  // `len` bytes from an 8-byte aligned word array, any length: 64 bytes at a time, asking for room first
+  // `len` bytes from an 8-byte aligned word array, any length: 64 bytes at a time, asking for room first.  The
+  // words of a piece are all loaded before the first one is appended: a load that waits behind the append of
+  // the word before it (the compiler cannot move it across the window's stores) pays the memory latency once
+  // per word instead of once per piece.
   K2J_HD void words(const uint64_t* w, uint32_t len) {
+    uint64_t x[8], y[8];
+    {
+      const uint32_t touched = ((len < 64u ? len : 64u) + 7u) >> 3;  // words read, the partial last one included
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
+      for (uint32_t k = 0; k < 8u; k++) x[k] = k < touched ? w[k] : 0ull;
+    }
     while (true) {
       const uint32_t n = len < 64u ? len : 64u;
+      {  // the piece after this one is on its way while this one is appended
+        const uint32_t left = len - n, touched = ((left < 64u ? left : 64u) + 7u) >> 3;
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
+        for (uint32_t k = 0; k < 8u; k++) y[k] = k < touched ? w[8 + k] : 0ull;
+      }
       ensure(n);
       const uint32_t nw = n >> 3;
       const uint32_t s = (pos & 3u) << 3;
       uint32_t i = pos >> 2, c = carry;
-      for (uint32_t k = 0; k < nw; k++) {
-        const uint64_t x = w[k];
-        const uint32_t lo = (uint32_t)x, hi = (uint32_t)(x >> 32);
-        W(i) = c | (lo << s); W(i + 1) = funnel_l(lo, hi, s);
-        c = funnel_l(hi, 0u, s);
-        i += 2;
+      uint64_t last = x[0];
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
+      for (uint32_t k = 0; k < 8u; k++) {
+        if (k < nw) {
+          const uint32_t lo = (uint32_t)x[k], hi = (uint32_t)(x[k] >> 32);
+          W(i) = c | (lo << s); W(i + 1) = funnel_l(lo, hi, s);
+          c = funnel_l(hi, 0u, s);
+          i += 2;
+        }
+        if (k == nw) last = x[k];
       }
       carry = c; pos += 8u * nw;
       const uint32_t rem = n & 7u;
-      if (rem) put64(w[nw] & (~0ull >> (8u * (8u - rem))), rem);
+      if (rem) put64(last & (~0ull >> (8u * (8u - rem))), rem);
       len -= n;
       if (len == 0u) break;
       w += 8;
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
+      for (uint32_t k = 0; k < 8u; k++) x[k] = y[k];
     }
   }
   // `len` bytes from any address: the bytes up to the next 8-byte boundary, then whole words
