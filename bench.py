@@ -289,7 +289,10 @@ def run_ours(args):
     depth = 2 if world == 1 else 1  # contexts alternating in the end-to-end leg
 
     trace = generate(args.workload, n, rank, world if args.workload in SHARDED else 1)
-    stream = torch.cuda.current_stream()
+    # one stream for the context's kernels, torch's copies, the NCCL exchange (ordered with the current stream) and the
+    # timing events
+    stream = torch.cuda.Stream(dev)
+    torch.cuda.set_stream(stream)
     ctx = api.K2J(local, stream.cuda_stream)
 
     def barrier():

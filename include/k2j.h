@@ -145,7 +145,8 @@ typedef struct {
 } k2j_result;
 
 /* Creates a context on CUDA device `device`.  `stream` is a cudaStream_t to run on, or NULL for a
- * stream owned by the context.  No reference counterpart: the reference keeps this state in the
+ * stream owned by the context (non-blocking: not ordered with the default stream; a caller that works on the
+ * default stream passes cudaStreamLegacy or cudaStreamPerThread, not the NULL handle).  No reference counterpart: the reference keeps this state in the
  * profiler and logger objects. */
 k2j_status k2j_create(int device, void* stream, k2j_ctx** out);
 void k2j_destroy(k2j_ctx* ctx);

@@ -142,7 +142,11 @@ class K2J:
     def __init__(self, device: int = 0, stream: int | None = None):
         self.lib = load_library()
         h = C.c_void_p()
-        st = self.lib.k2j_create(device, C.c_void_p(stream) if stream else None, C.byref(h))
+        # None: a stream owned by the context.  0 is the handle torch reports for the default stream: the context then
+        # runs on the legacy default stream (cudaStreamLegacy, handle 1), NOT on a stream of its own (which is what a
+        # NULL handle means to k2j_create), so that it stays ordered with the caller's work on that stream.
+        handle = None if stream is None else C.c_void_p(stream if stream != 0 else 1)
+        st = self.lib.k2j_create(device, handle, C.byref(h))
         if st != 0:
             raise K2JError(st, "k2j_create failed (is a CUDA device present?)")
         self.h = h

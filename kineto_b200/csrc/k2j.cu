@@ -762,7 +762,7 @@ k2j_status emit_core(k2j_ctx* c, k2j_result* res, const TileSink& sink) {
   }
   d.need_corr = nullptr; d.need_op = nullptr;
   if (filter) {
-    const uint32_t corr_bits = std::max<uint32_t>(1u << 20, pow2_at_least(32 * std::max<uint64_t>(1, n_gpu_events)));
+    const uint32_t corr_bits = std::max<uint32_t>(1u << 20, pow2_at_least(8 * std::max<uint64_t>(1, n_gpu_events)));
     const uint32_t op_bits = corr_bits;
     K2J_CUDA(c, c->need_corr.reserve(corr_bits / 8));
     K2J_CUDA(c, c->need_op.reserve(op_bits / 8));

@@ -585,13 +585,17 @@ __global__ void k_build_tids(Dev d) {
   }
   if (!tab_insert_min(d.tid_tab, d.tid_mask, key, (uint32_t)i)) atomicAdd(&d.counters->device_check, 1ull);
 }
+// A key owns two bits of one 32-bit word (one memory access per test or set): with eight bits of table per
+// marked key about one word bit in eight is set and a foreign key passes with probability of about 1 in 60,
+// from a table small enough to stay in the L2 while the gathered keys stream past it.
+__device__ __forceinline__ uint32_t bit_pair(uint32_t h) { return (1u << (h & 31u)) | (1u << (h >> 27)); }
 __device__ __forceinline__ bool bit_test(const uint32_t* bits, uint32_t mask, uint32_t key) {
-  const uint32_t h = hash32(key ^ 0x9E3779B9u) & mask;
-  return (bits[h >> 5] >> (h & 31u)) & 1u;
+  const uint32_t h = hash32(key ^ 0x9E3779B9u), m = bit_pair(h);
+  return (bits[(h & mask) >> 5] & m) == m;
 }
 __device__ __forceinline__ void bit_set(uint32_t* bits, uint32_t mask, uint32_t key) {
-  const uint32_t h = hash32(key ^ 0x9E3779B9u) & mask;
-  atomicOr(&bits[h >> 5], 1u << (h & 31u));
+  const uint32_t h = hash32(key ^ 0x9E3779B9u);
+  atomicOr(&bits[(h & mask) >> 5], bit_pair(h));
 }
 // Sharded runs: marks the correlation id of every GPU-side record of this shard.  With the gathered
 // arrays of W shards each rank would otherwise insert W times its own share of keys into its tables,
@@ -638,7 +642,8 @@ __global__ void k_build_corr(Dev d, uint64_t own_begin, uint64_t own_end) {
   bool ok = true;
   if (e.external_kind == 3u) {
     if (d.need_corr != nullptr) {
-      if (!bit_test(d.need_corr, d.need_corr_mask, e.correlation_id)) return;
+      // this shard's own records are nearly all wanted by its own events: they go in untested
+      if ((i < own_begin || i >= own_end) && !bit_test(d.need_corr, d.need_corr_mask, e.correlation_id)) return;
       if ((int64_t)e.external_id == (int64_t)(int32_t)e.external_id) bit_set(d.need_op, d.need_op_mask, (uint32_t)e.external_id);
     }
     if (e.correlation_id == 0u) atomicMax(&d.corr0[0], (unsigned long long)i + 1ull);

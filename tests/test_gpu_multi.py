@@ -1,5 +1,6 @@
 """Two ranks on two GPUs: segment -> NCCL all-gather of the join keys -> emit, compared per shard with
 the CPU checker given the same gathered keys.  Skipped on boxes with one GPU."""
+import datetime
 import os
 
 import numpy as np
@@ -21,9 +22,11 @@ def _rank_main(rank, port, tmp):
                       NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=WORLD, device_id=dev)
+    dist.init_process_group("nccl", rank=rank, world_size=WORLD, device_id=dev, timeout=datetime.timedelta(seconds=90))  # a rank that failed ends the other soon
     shard = synth.gen_kernel_launches(N, seed=91, pool_size=500, shard=(rank, WORLD))
-    ctx = api.K2J(rank, torch.cuda.current_stream().cuda_stream)
+    stream = torch.cuda.Stream(dev)   # the context, torch's copies and the collectives share it
+    torch.cuda.set_stream(stream)
+    ctx = api.K2J(rank, stream.cuda_stream)
     try:
         ctx.load(shard)
         info = ctx.segment()
@@ -59,16 +62,25 @@ def _rank_main(rank, port, tmp):
         alone, _ = helpers.run_port(synth.gen_kernel_launches(N, seed=91, pool_size=500, shard=(rank, WORLD)))
         open(os.path.join(tmp, "ok%d" % rank), "w").write("%d %d" % (int(ok), int(alone != want)))
         dist.barrier()
-    finally:
-        ctx.close()
-        dist.destroy_process_group()
+    except BaseException:
+        # a rank that failed says why and leaves at once: waiting in destroy_process_group for a peer that sits in a
+        # collective would hide the failure behind the peer's timeout
+        import traceback
+        open(os.path.join(tmp, "err%d" % rank), "w").write(traceback.format_exc())
+        os._exit(1)
+    ctx.close()
+    dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_two_gpu_ranks_match_checker(tmp_path):
     import torch.multiprocessing as mp
     port = 29700 + (os.getpid() % 2000)
-    mp.spawn(_rank_main, args=(port, str(tmp_path)), nprocs=WORLD, join=True)
+    try:
+        mp.spawn(_rank_main, args=(port, str(tmp_path)), nprocs=WORLD, join=True)
+    except Exception as e:  # noqa: BLE001
+        errs = [open(str(f)).read() for f in sorted(tmp_path.glob("err*"))]
+        pytest.fail("a rank failed: %s\n%s" % (e, "\n".join(errs)))
     for r in range(WORLD):
         ok, crosses = open(str(tmp_path / ("ok%d" % r))).read().split()
         assert ok == "1", "rank %d output differs from the checker" % r

@@ -301,6 +301,28 @@ def test_sharded_runs_concatenate_to_the_whole(n_shards):
                 begin += int(i.n_external)
                 c.emit()
                 parts.append(c.copy_output().tobytes())
+            # the same join keys as the equal-sized rows an all-gather leaves (sharding.JoinExchange), read in place
+            ext_stride = max(int(i.n_external) for i in infos) + 7
+            ops_stride = (max(int(i.n_ops) for i in infos) + 9) & ~1
+            words = ext_stride * 2 + ops_stride // 2
+            rows = torch.zeros(words * n_shards, dtype=torch.int64, device="cuda:0")
+            counts = torch.zeros(2 * n_shards, dtype=torch.int64, device="cuda:0")
+            pos_e = pos_o = 0
+            for r, i in enumerate(infos):
+                ne, no = int(i.n_external), int(i.n_ops)
+                row = rows[r * words:(r + 1) * words]
+                row[:ne * 2] = ext[pos_e * 2:(pos_e + ne) * 2]
+                row[ext_stride * 2:].view(torch.int32)[:no] = ops[pos_o:pos_o + no]
+                counts[2 * r], counts[2 * r + 1] = ne, no
+                pos_e += ne
+                pos_o += no
+            torch.cuda.synchronize()
+            for r, c in enumerate(ctxs):
+                c.segment()
+                c.set_global_join_rows(rows, ext_stride, ops_stride, counts, n_shards, r)
+                res_rows = c.emit()
+                assert c.copy_output().tobytes() == parts[r], "rows of shard %d" % r
+                assert res_rows["invalid_external_correlation_events"] == 0
         finally:
             for c in ctxs:
                 c.close()
