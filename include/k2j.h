@@ -195,6 +195,25 @@ k2j_status k2j_set_cupti(k2j_ctx* ctx, const uint8_t* bytes, uint64_t n_bytes, c
  * plus ChromeTraceLogger::handleActivity (libkineto/src/output_json.cpp:837-963) for every event. */
 k2j_status k2j_run(k2j_ctx* ctx, k2j_result* result);
 
+/* Sharded traces whose shards hold synchronisation or CUDA event records.  The reference fills the lookups
+ * those records use from the WHOLE trace before it logs anything: context -> device from the first kernel, copy
+ * or memset record that names the context (libkineto/src/CuptiActivityProfiler.cpp:221-239), (context, event) ->
+ * CUDA event record (:241-254, :379-402), the streams that showed GPU work inside the window, which gate deferred
+ * stream-wait records (:502-514), and the once-per-row announcement in front of a row's first stream
+ * synchronisation (libkineto/src/output_json.cpp:917-943).  A shard's share of that knowledge is carried by a few
+ * of its own records.  k2j_export_lookup_records (after k2j_segment) returns them, copied verbatim and in
+ * processing order into one CUPTI buffer in device memory of the context (valid until its next call): per context
+ * its first kernel / copy / memset record, per (device, stream) the first such record inside the window, per
+ * (context, stream) the first stream synchronisation inside the window, and every CUDA event record.  The caller
+ * all-gathers the shards' buffers and gives each shard, through k2j_set_cupti, the lower shards' buffers in front of
+ * its own buffers and the higher shards' behind them, then names the two byte ranges with k2j_set_guest_ranges
+ * (records below `front_end_bytes` and from `back_begin_bytes` on are guests; buffers must not straddle either
+ * boundary; k2j_set_cupti forgets the ranges).  Guest records take part in every lookup exactly as if the shard had
+ * met them itself, print nothing and are not counted.  Then k2j_segment, the join exchange and k2j_emit as usual.
+ * Without declared guest ranges a sharded run with such records is K2J_ERR_UNSUPPORTED. */
+k2j_status k2j_export_lookup_records(k2j_ctx* ctx, const void** records, uint64_t* n_bytes);
+k2j_status k2j_set_guest_ranges(k2j_ctx* ctx, uint64_t front_end_bytes, uint64_t back_begin_bytes);
+
 /* The same work in two steps, for traces sharded by contiguous record range over several GPUs (one
  * context per GPU).  k2j_segment walks this shard's buffers and compacts its EXTERNAL_CORRELATION
  * records (k2j_external_record, processing order).  The caller all-gathers those arrays and the CPU

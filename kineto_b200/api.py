@@ -67,7 +67,7 @@ class SegmentInfo(C.Structure):
 EXPORTS = ["k2j_set_global_join_rows", "k2j_emit_to_host", "k2j_emit_to_fd", "k2j_exclusive_scan_u32", "k2j_exclusive_scan_u32_noalloc", "k2j_segment", "k2j_set_global_join", "k2j_emit", "k2j_create", "k2j_destroy", "k2j_last_error", "k2j_set_params", "k2j_set_strings",
            "k2j_set_cbid_names", "k2j_set_thread_map", "k2j_set_ops", "k2j_set_cupti", "k2j_run", "k2j_output",
            "k2j_copy_output", "k2j_copy_output_async", "k2j_write_output", "k2j_write_output_at", "k2j_synchronize", "k2j_version",
-           "k2j_names_create", "k2j_names_destroy", "k2j_names_intern", "k2j_names_pool", "k2j_intern_kernel_names"]
+           "k2j_export_lookup_records", "k2j_set_guest_ranges", "k2j_names_create", "k2j_names_destroy", "k2j_names_intern", "k2j_names_pool", "k2j_intern_kernel_names"]
 
 _lib = None
 
@@ -107,6 +107,8 @@ def load_library():
     lib.k2j_write_output.argtypes = [vp, C.c_int, C.POINTER(C.c_uint64)]
     lib.k2j_write_output_at.argtypes = [vp, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64]
     lib.k2j_synchronize.argtypes = [vp]
+    lib.k2j_export_lookup_records.argtypes = [vp, C.POINTER(vp), C.POINTER(C.c_uint64)]
+    lib.k2j_set_guest_ranges.argtypes = [vp, C.c_uint64, C.c_uint64]
     lib.k2j_names_create.argtypes = [C.POINTER(vp)]
     lib.k2j_names_destroy.argtypes = [vp]
     lib.k2j_names_destroy.restype = None
@@ -225,6 +227,23 @@ class K2J:
         info = SegmentInfo()
         self._check(self.lib.k2j_segment(self.h, C.byref(info)))
         return info
+
+    def export_lookup_records(self) -> tuple[int, int]:
+        """(device address, byte count) of this shard's lookup records: one CUPTI buffer in the context's device
+        memory, valid until the context's next call (k2j_export_lookup_records)."""
+        ptr, n = C.c_void_p(), C.c_uint64()
+        self._check(self.lib.k2j_export_lookup_records(self.h, C.byref(ptr), C.byref(n)))
+        return ptr.value or 0, n.value
+
+    def set_cupti(self, cupti, buftab: np.ndarray):
+        """The CUPTI bytes alone (uint8 numpy array or device tensor) with their (offset, valid bytes) table."""
+        bt = np.ascontiguousarray(buftab, dtype=np.uint64)
+        self._keep["cupti"], self._keep["buftab"] = cupti, bt
+        n = cupti.nbytes if isinstance(cupti, np.ndarray) else cupti.numel()
+        self._check(self.lib.k2j_set_cupti(self.h, _ptr(cupti), n, _ptr(bt), bt.size // 2))
+
+    def set_guest_ranges(self, front_end_bytes: int, back_begin_bytes: int):
+        self._check(self.lib.k2j_set_guest_ranges(self.h, front_end_bytes, back_begin_bytes))
 
     def set_global_join(self, ext_all, n_ext_all: int, own_begin: int, op_ids_all, n_ops_all: int):
         """`ext_all`: device tensor of 16-byte external-correlation records of all shards in shard

@@ -100,6 +100,8 @@ struct k2j_ctx {
   DevBuf corr0;                                                       // correlation id 0 (see Dev::corr0)
   const void* g_ext = nullptr; uint64_t g_n_ext = 0, g_own_begin = 0;
   const int32_t* g_op_ids = nullptr; uint64_t g_n_ops = 0;
+  uint64_t guest_front_bytes = 0, guest_back_bytes = ~0ull; bool guests_declared = false;  // k2j_set_guest_ranges
+  DevBuf exp_keys, exp_first, exp_list, exp_out;
   uint32_t g_ext_stride = 0, g_ops_stride = 0, g_world = 1; uint64_t g_pitch = 0; const uint64_t* g_counts = nullptr;  // rows of an all-gather
 };
 
@@ -335,7 +337,8 @@ void k2j_destroy(k2j_ctx* c) {
                     &c->span_out, &c->span_cnt, &c->ann_size, &c->ann_off, &c->sort_keys[0], &c->sort_keys[1], &c->sort_vals[0],
                     &c->sort_vals[1], &c->sort_hist, &c->sort_base, &c->sort_rank, &c->tid_tab, &c->corr_tab, &c->user_tab, &c->op_tab,
                     &c->work_slot, &c->work_ev, &c->ev_size, &c->ev_off, &c->ev_ext, &c->out, &c->counters, &c->ext_local, &c->ctx_tab, &c->evt_recs,
-                    &c->seen_tab, &c->row_key, &c->row_first, &c->corr_zero, &c->str_class, &c->comms_flag, &c->coll_list, &c->corr0})
+                    &c->seen_tab, &c->row_key, &c->row_first, &c->corr_zero, &c->str_class, &c->comms_flag, &c->coll_list, &c->corr0,
+                    &c->exp_keys, &c->exp_first, &c->exp_list, &c->exp_out})
     b->release();
   if (c->h_totals) cudaFreeHost(c->h_totals);
   if (c->h_counters) cudaFreeHost(c->h_counters);
@@ -476,6 +479,7 @@ k2j_status k2j_set_cupti(k2j_ctx* c, const uint8_t* bytes, uint64_t n_bytes, con
   }
   c->n_buf = (uint32_t)c->h_buf_off.size();
   c->n_chunks = (uint32_t)chunks;
+  c->guest_front_bytes = 0; c->guest_back_bytes = ~0ull; c->guests_declared = false;
   c->cupti_bytes = n_bytes;
   k2j_status st = stage(c, c->cupti, bytes, n_bytes);
   if (st) return st;
@@ -521,6 +525,8 @@ k2j_status k2j_segment(k2j_ctx* c, k2j_segment_info* info) {
   d.op_type = (const int32_t*)c->op_type.dev; d.op_name = (const uint32_t*)c->op_name.dev; d.op_flow = (const uint32_t*)c->op_flow.dev;
   d.op_flowt = (const uint8_t*)c->op_flowt.dev; d.op_mdoff = (const uint32_t*)c->op_mdoff.dev; d.md = (const MdEntry*)c->op_md.dev;
   d.counters = c->counters.as<Counters>();
+  d.guest_front = (uint32_t)(c->guest_front_bytes / 8);
+  d.guest_back = c->guest_back_bytes == ~0ull ? 0xFFFFFFFFu : (uint32_t)(c->guest_back_bytes / 8);
 
   K2J_CUDA(c, cudaMemsetAsync(c->counters.p, 0, sizeof(Counters), s));
   K2J_CUDA(c, cudaEventRecord(c->ev[0], s));
@@ -625,6 +631,79 @@ k2j_status k2j_set_global_join_rows(k2j_ctx* c, const void* ext_rows, uint64_t e
   return K2J_OK;
 }
 
+k2j_status k2j_set_guest_ranges(k2j_ctx* c, uint64_t front_end_bytes, uint64_t back_begin_bytes) {
+  if (!c) return K2J_ERR_INVALID_ARGUMENT;
+  if ((front_end_bytes & 7) || (back_begin_bytes & 7) || front_end_bytes > back_begin_bytes || back_begin_bytes > c->cupti_bytes)
+    return fail(c, K2J_ERR_INVALID_ARGUMENT, "guest ranges: not 8-byte aligned, crossing, or past the end of the CUPTI bytes");
+  for (size_t b = 0; b < c->h_buf_off.size(); b++) {  // a buffer is a guest buffer or this shard's own, never both
+    const uint64_t lo = c->h_buf_off[b], hi = lo + c->h_buf_valid[b];
+    const bool own = lo >= front_end_bytes && hi <= back_begin_bytes, guest = hi <= front_end_bytes || lo >= back_begin_bytes;
+    if (!own && !guest) return fail(c, K2J_ERR_INVALID_ARGUMENT, "guest ranges: buffer %zu straddles a boundary", b);
+  }
+  c->guest_front_bytes = front_end_bytes; c->guest_back_bytes = back_begin_bytes; c->guests_declared = true;
+  c->segmented = false;  // the next k2j_segment picks the ranges up
+  return K2J_OK;
+}
+
+k2j_status k2j_export_lookup_records(k2j_ctx* c, const void** records, uint64_t* n_bytes) {
+  if (!c) return K2J_ERR_INVALID_ARGUMENT;
+  if (!records || !n_bytes) return fail(c, K2J_ERR_INVALID_ARGUMENT, "null result pointers");
+  if (!c->segmented) return fail(c, K2J_ERR_STATE, "k2j_segment has not run");
+  if (c->guests_declared) return fail(c, K2J_ERR_STATE, "lookup records are exported from a shard's own buffers, before guests are added");
+  K2J_CUDA(c, cudaSetDevice(c->device));
+  cudaStream_t s = c->stream;
+  Dev d = c->d;
+  const uint64_t* totals = c->totals;
+  constexpr uint32_t kCtxCap = 1u << 14, kKeyCap = 1u << 16, kListCap = kCtxCap + 2 * kKeyCap;
+  K2J_CUDA(c, c->ctx_tab.reserve((size_t)kCtxCap * 8));
+  K2J_CUDA(c, c->exp_keys.reserve((size_t)kKeyCap * 8 * 2));
+  K2J_CUDA(c, c->exp_first.reserve((size_t)kKeyCap * 4 * 2 + 16));
+  K2J_CUDA(c, c->exp_list.reserve((size_t)kListCap * 8));
+  d.ctx_tab = c->ctx_tab.as<unsigned long long>(); d.ctx_mask = kCtxCap - 1;
+  unsigned long long* pair_key = c->exp_keys.as<unsigned long long>();
+  unsigned long long* sync_key = pair_key + kKeyCap;
+  uint32_t* pair_first = c->exp_first.as<uint32_t>();
+  uint32_t* sync_first = pair_first + kKeyCap;
+  uint32_t* n_list = sync_first + kKeyCap;
+  K2J_CUDA(c, cudaMemsetAsync(d.ctx_tab, 0, (size_t)kCtxCap * 8, s));
+  K2J_CUDA(c, cudaMemsetAsync(pair_key, 0, (size_t)kKeyCap * 8 * 2, s));
+  K2J_CUDA(c, cudaMemsetAsync(pair_first, 0xFF, (size_t)kKeyCap * 4 * 2, s));
+  K2J_CUDA(c, cudaMemsetAsync(n_list, 0, 16, s));
+  K2J_CUDA(c, cudaMemsetAsync(d.counters, 0, sizeof(Counters), s));
+  const uint64_t n_named = d.cls_begin[C_OVERHEAD] - d.cls_begin[C_KERNEL];
+  if (n_named) k_build_ctx<<<(uint32_t)((n_named + 255) / 256), 256, 0, s>>>(d);
+  const uint64_t n_sel = d.cls_begin[C_SYNC] + d.cls_count[C_SYNC] - d.cls_begin[C_KERNEL];
+  if (n_sel) k_export_select<<<(uint32_t)((n_sel + 255) / 256), 256, 0, s>>>(d, pair_key, pair_first, sync_key, sync_first, kKeyCap - 1);
+  k_export_list<<<(kListCap + 255) / 256, 256, 0, s>>>(d, pair_key, pair_first, sync_key, sync_first, kKeyCap - 1,
+                                                       c->exp_list.as<unsigned long long>(), n_list, kListCap);
+  K2J_CUDA(c, cudaGetLastError());
+  uint32_t n = 0;
+  K2J_CUDA(c, cudaMemcpyAsync(&n, n_list, 4, cudaMemcpyDeviceToHost, s));
+  K2J_CUDA(c, cudaMemcpyAsync(c->h_counters, d.counters, sizeof(Counters), cudaMemcpyDeviceToHost, s));
+  K2J_CUDA(c, cudaStreamSynchronize(s));
+  if (c->h_counters->device_check || n > kListCap)
+    return fail(c, K2J_ERR_DEVICE_CHECK, "more contexts or (device, stream) pairs than the export tables hold");
+  // in processing order, each record once: a record's place among the exported ones decides ties between them
+  std::vector<unsigned long long> list(n);
+  if (n) K2J_CUDA(c, cudaMemcpy(list.data(), c->exp_list.p, (size_t)n * 8, cudaMemcpyDeviceToHost));
+  std::sort(list.begin(), list.end());
+  list.erase(std::unique(list.begin(), list.end()), list.end());
+  uint64_t at = 0;
+  for (auto& e : list) { const uint32_t len = (uint32_t)e; e = (e & 0xFFFFFFFF00000000ull) | at; at += len; }
+  if (at >= (1ull << 32)) return fail(c, K2J_ERR_UNSUPPORTED, "more than 4 GiB of lookup records");
+  const uint64_t n_events = totals[C_CUDAEVENT], total = at + 56 * n_events;
+  K2J_CUDA(c, c->exp_out.reserve(std::max<uint64_t>(8, total)));
+  if (!list.empty()) K2J_CUDA(c, cudaMemcpyAsync(c->exp_list.p, list.data(), list.size() * 8, cudaMemcpyHostToDevice, s));
+  if (list.size() + n_events)
+    k_export_copy<<<(uint32_t)((list.size() + n_events + 255) / 256), 256, 0, s>>>(d, c->exp_list.as<unsigned long long>(), (uint32_t)list.size(),
+                                                                              c->exp_out.as<uint8_t>(), at);
+  K2J_CUDA(c, cudaGetLastError());
+  K2J_CUDA(c, cudaStreamSynchronize(s));  // `list` is read by the upload above; the records are complete when this returns
+  *records = c->exp_out.p;
+  *n_bytes = total;
+  return K2J_OK;
+}
+
 }  // extern "C"
 
 namespace {
@@ -688,8 +767,9 @@ k2j_status emit_core(k2j_ctx* c, k2j_result* res, const TileSink& sink) {
   const uint64_t* totals = c->totals;
   const uint64_t n_gpu_events = totals[C_EVENTS] + totals[C_WAIT];
   const uint64_t n_sync = totals[C_SYNC] + totals[C_WAIT], n_cuda_events = totals[C_CUDAEVENT];
-  if (n_sync + n_cuda_events > 0 && c->have_global_join)
-    return fail(c, K2J_ERR_UNSUPPORTED, "synchronisation and CUDA event records across shards are not implemented");
+  if (n_sync + n_cuda_events > 0 && c->have_global_join && !c->guests_declared)
+    return fail(c, K2J_ERR_UNSUPPORTED, "synchronisation and CUDA event records of a sharded trace need the other shards' lookup records "
+                                        "(k2j_export_lookup_records, k2j_set_guest_ranges)");
   K2J_CUDA(c, cudaEventRecord(c->ev[6], s));
   // every counter belongs to the emit step (segmentation counts through its scan columns): a second k2j_emit after
   // one k2j_segment starts from zero, and an earlier failed check does not fail this run
@@ -976,7 +1056,7 @@ k2j_status emit_core(k2j_ctx* c, k2j_result* res, const TileSink& sink) {
   res->out_bytes = total_bytes + ann_bytes;
   res->annotation_bytes = ann_bytes;
   res->ops_bytes = n_gpu_events ? c->h_totals[21] : total_bytes;
-  res->n_records = totals[C_EVENTS] + totals[C_WAIT] + totals[C_EXT] + totals[C_UNEXPECTED];
+  res->n_records = totals[C_EVENTS] + totals[C_WAIT] + totals[C_EXT] + totals[C_UNEXPECTED] - c->h_counters->guests;
   res->x_events = c->h_counters->x_events + (ann_bytes ? n_spans : 0);
   res->flow_events = c->h_counters->flow_events;
   res->out_of_range_events = c->h_counters->out_of_range;

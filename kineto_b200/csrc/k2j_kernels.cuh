@@ -101,7 +101,7 @@ struct DevProps {
 
 struct Counters {
   unsigned long long x_events, flow_events, out_of_range, blocklisted_runtime, invalid_external_correlation,
-      unexpected, name_bytes, device_check, n_user, n_coll;
+      unexpected, name_bytes, device_check, n_user, n_coll, guests;
 };
 
 struct MdEntry { uint32_t key, type; uint64_t value; };
@@ -178,6 +178,10 @@ struct Dev {
   uint32_t* ev_size; const uint64_t* ev_off; uint64_t n_events;
   int32_t* ev_ext;        // per event: id of the linked CPU op found by the size pass (0 = none)
   uint8_t* out; uint64_t out_cap;  // address of output byte 0 (of the whole text), bytes of the whole text
+  // Sharded traces: records in front of guest_front (a slot index) and from guest_back on are other shards' records
+  // that only feed this shard's lookups (contexts, CUDA event records, streams with GPU work, first stream syncs):
+  // they run through the size pass like any record, print nothing and are not counted.  None: 0 and 0xFFFFFFFF.
+  uint32_t guest_front, guest_back;
   uint64_t tile_begin, tile_end;   // this launch writes the events whose text starts in [tile_begin, tile_end): the whole
                                    // text, or one slab of a tiled run (then `out` points outside the slab for other bytes)
   Counters* counters;
@@ -1542,6 +1546,71 @@ __global__ void k_sync_rows(Dev d) {
   atomicMin(&d.row_first[slot], d.work_ev[i]);
 }
 
+// ---- what other shards of a trace need from this one for their synchronisation and CUDA event records ----
+// The reference fills its lookup maps from the whole trace before it logs anything (buildProcessingState,
+// CuptiActivityProfiler.cpp:256-302; seenDeviceStreams_ and the once-per-row metadata during logging).  A shard's part
+// of those maps is carried by a few of its own records, exported verbatim: per context the first kernel / copy /
+// memset record (ctxToDeviceId), per (device, stream) the first such record inside the window (seenDeviceStreams_),
+// per (context, stream) the first stream synchronisation inside the window (the row announcement), and every CUDA
+// event record (waitEventMap).  k_export_select finds the per-key first records (smallest slot), k_export_list
+// gathers their slots and sizes, the host orders them, k_export_copy writes the records.
+__global__ void k_export_select(Dev d, unsigned long long* pair_key, uint32_t* pair_first, unsigned long long* sync_key, uint32_t* sync_first,
+                                uint32_t mask) {
+  const uint64_t i = d.cls_begin[C_KERNEL] + (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= d.cls_begin[C_SYNC] + d.cls_count[C_SYNC]) return;
+  int cls = C_KERNEL;
+#pragma unroll
+  for (int c = C_MEMCPY; c <= C_SYNC; c++) if (i >= d.cls_begin[c]) cls = c;
+  if (i - d.cls_begin[cls] >= d.cls_count[cls] || (cls > C_MEMSET && cls != C_SYNC)) return;  // padding, other classes
+  const uint32_t slot = d.work_slot[i];
+  const uint32_t* r = reinterpret_cast<const uint32_t*>(d.cupti + (uint64_t)slot * 8);
+  unsigned long long key;
+  uint64_t st, en;
+  if (cls == C_SYNC) {
+    if (r[1] != 3u) return;  // stream synchronisations only
+    st = (uint64_t)r[2] | ((uint64_t)r[3] << 32); en = (uint64_t)r[4] | ((uint64_t)r[5] << 32);
+    key = dev_stream_key(r[7], r[8]);  // (context, stream): the device is only known once all shards' contexts are
+  } else {
+    st = (uint64_t)r[4] | ((uint64_t)r[5] << 32); en = (uint64_t)r[6] | ((uint64_t)r[7] << 32);
+    key = cls == C_KERNEL ? dev_stream_key(r[10], r[12]) : dev_stream_key(r[8], r[10]);  // (device, stream)
+  }
+  if (out_of_range(d, conv_ts(d, st), conv_dur(d, st, en))) return;
+  unsigned long long* keys = cls == C_SYNC ? sync_key : pair_key;
+  const uint32_t at = set64_slot(keys, mask, key, true);
+  if (at == 0xFFFFFFFFu) { atomicAdd(&d.counters->device_check, 1ull); return; }
+  atomicMin(&(cls == C_SYNC ? sync_first : pair_first)[at], slot);
+}
+// One thread per table slot of the three tables: the slot and the length of every record to export.
+__global__ void k_export_list(Dev d, const unsigned long long* pair_key, const uint32_t* pair_first, const unsigned long long* sync_key,
+                              const uint32_t* sync_first, uint32_t mask, unsigned long long* list, uint32_t* n_list, uint32_t cap) {
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  uint32_t slot = 0xFFFFFFFFu;
+  if (i <= d.ctx_mask) { const unsigned long long e = d.ctx_tab[i]; if (e != 0) slot = (uint32_t)e - 1u; }
+  else if (i - (d.ctx_mask + 1u) <= mask) { const uint32_t j = i - (d.ctx_mask + 1u); if (pair_key[j] != 0) slot = pair_first[j]; }
+  else if (i - (d.ctx_mask + 1u) - (mask + 1u) <= mask) { const uint32_t j = i - (d.ctx_mask + 1u) - (mask + 1u); if (sync_key[j] != 0) slot = sync_first[j]; }
+  if (slot == 0xFFFFFFFFu) return;
+  const uint32_t* r = reinterpret_cast<const uint32_t*>(d.cupti + (uint64_t)slot * 8);
+  const uint32_t len = (slot_code(r[0], r[1]) & 31u) * 8u;
+  const uint32_t at = atomicAdd(n_list, 1u);
+  if (at < cap) list[at] = ((unsigned long long)slot << 32) | len;
+}
+// `list`: (slot << 32 | byte offset in dst) per record, lengths from the records' kinds; then the CUDA event records.
+__global__ void k_export_copy(Dev d, const unsigned long long* list, uint32_t n_list, uint8_t* dst, uint64_t events_at) {
+  const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint64_t* src;
+  uint64_t* out;
+  if (i < n_list) {
+    src = reinterpret_cast<const uint64_t*>(d.cupti + (list[i] >> 32) * 8);
+    out = reinterpret_cast<uint64_t*>(dst + (uint32_t)list[i]);
+  } else if (i - n_list < d.cls_count[C_CUDAEVENT]) {
+    src = reinterpret_cast<const uint64_t*>(d.cupti + (uint64_t)d.work_slot[d.cls_begin[C_CUDAEVENT] + (i - n_list)] * 8);
+    out = reinterpret_cast<uint64_t*>(dst + events_at + (i - n_list) * 56u);
+  } else return;
+  const uint32_t* r = reinterpret_cast<const uint32_t*>(src);
+  const uint32_t words = slot_code(r[0], r[1]) & 31u;
+  for (uint32_t k = 0; k < words; k++) out[k] = src[k];
+}
+
 // CPU-side activity: ChromeTraceLogger::handleActivity for a GenericTraceActivity (output_json.cpp:837-963)
 __device__ __forceinline__ uint64_t gather_op(const Dev& d, uint64_t i, uint32_t* a, Tally& t) {
   const int32_t type = d.op_type[i];
@@ -2128,13 +2197,18 @@ __global__ void __launch_bounds__(kEventThreads, WRITE ? 5 : 8) k_events(Dev d) 
   }
   uint64_t ev = 0;
   const uint8_t* r = nullptr;
+  bool guest = false;
   uint32_t size = 0;
   uint64_t off = 0;
   int32_t ext = 0;
   if (cls >= 0) {
     ev = cls == C_OP ? j : d.work_ev[i];
     t.ev = ev;
-    if (cls != C_OP) r = d.cupti + (uint64_t)d.work_slot[i] * 8;
+    if (cls != C_OP) {
+      const uint32_t slot = d.work_slot[i];
+      r = d.cupti + (uint64_t)slot * 8;
+      guest = slot < d.guest_front || slot >= d.guest_back;
+    }
     if (WRITE) {
       size = d.ev_size[ev];
       if (size) {
@@ -2172,6 +2246,7 @@ __global__ void __launch_bounds__(kEventThreads, WRITE ? 5 : 8) k_events(Dev d) 
     if (!WRITE) {
       CountSink2 s;
       format_event(s, d, cls, area, j, t, &filt, &ext);
+      if (guest) { filt = 3u; t.x = 0; t.flow = 0; t.name_bytes = 0; }  // another shard's record: looked at, never written
       d.ev_size[ev] = filt ? 0u : s.n;
       if (cls != C_OP) d.ev_ext[ev] = ext;
     } else {
@@ -2185,12 +2260,14 @@ __global__ void __launch_bounds__(kEventThreads, WRITE ? 5 : 8) k_events(Dev d) 
     const uint32_t wx = __reduce_add_sync(0xffffffffu, t.x), wf = __reduce_add_sync(0xffffffffu, t.flow);
     const uint32_t wo = __reduce_add_sync(0xffffffffu, filt == 2u ? 1u : 0u), wb = __reduce_add_sync(0xffffffffu, filt == 1u ? 1u : 0u);
     const uint32_t wn = __reduce_add_sync(0xffffffffu, (uint32_t)t.name_bytes);  // a name is far shorter than 2^27 bytes
+    const uint32_t wg = __reduce_add_sync(0xffffffffu, filt == 3u ? 1u : 0u);
     if ((threadIdx.x & 31u) == 0) {
       if (wx) atomicAdd(&s_cnt[0], (unsigned long long)wx);
       if (wf) atomicAdd(&s_cnt[1], (unsigned long long)wf);
       if (wo) atomicAdd(&s_cnt[2], (unsigned long long)wo);
       if (wb) atomicAdd(&s_cnt[3], (unsigned long long)wb);
       if (wn) atomicAdd(&s_cnt[4], (unsigned long long)wn);
+      if (wg) atomicAdd(&s_cnt[5], (unsigned long long)wg);
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -2199,6 +2276,7 @@ __global__ void __launch_bounds__(kEventThreads, WRITE ? 5 : 8) k_events(Dev d) 
       if (s_cnt[2]) atomicAdd(&d.counters->out_of_range, s_cnt[2]);
       if (s_cnt[3]) atomicAdd(&d.counters->blocklisted_runtime, s_cnt[3]);
       if (s_cnt[4]) atomicAdd(&d.counters->name_bytes, s_cnt[4]);
+      if (s_cnt[5]) atomicAdd(&d.counters->guests, s_cnt[5]);
     }
   }
 }

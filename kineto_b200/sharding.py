@@ -86,6 +86,51 @@ class JoinExchange:
         return self.rows, self.ext_stride, self.ops_stride, self.counts
 
 
+def with_guest_records(own_cupti, own_buftab, blobs, rank: int):
+    """The CUPTI bytes a shard runs on when the trace has synchronisation or CUDA event records: the lookup records
+    of the lower shards (`blobs[:rank]`, uint8 device tensors from k2j_export_lookup_records) in front of the shard's
+    own bytes, those of the higher shards behind them.  Returns (bytes tensor, buffer table, front_end_bytes,
+    back_begin_bytes) for K2J.set_cupti and K2J.set_guest_ranges."""
+    import numpy as np
+    import torch
+    front = [b for b in blobs[:rank] if b.numel()]
+    back = [b for b in blobs[rank + 1:] if b.numel()]
+    n_front = sum(b.numel() for b in front)
+    n_own = own_cupti.numel()
+    whole = torch.cat(front + [own_cupti] + back) if front or back else own_cupti
+    table, at = [], 0
+    for b in front:
+        table += [at, b.numel()]
+        at += b.numel()
+    own = np.asarray(own_buftab, dtype=np.uint64).reshape(-1, 2)
+    for off, valid in own:
+        table += [n_front + int(off), int(valid)]
+    at = n_front + n_own
+    for b in back:
+        table += [at, b.numel()]
+        at += b.numel()
+    return whole, np.array(table, dtype=np.uint64), n_front, n_front + n_own
+
+
+def gather_lookup_records(ctx, rank: int, world: int, dist, device):
+    """All-gathers the shards' lookup records (K2J.export_lookup_records): one collective for the sizes (with a host
+    round trip: the buffers are laid out on the host), one for the padded records.  Returns the list of per-shard
+    uint8 device tensors for `with_guest_records`."""
+    import torch
+    from . import api
+    ptr, n = ctx.export_lookup_records()
+    sizes = torch.empty(world, dtype=torch.int64, device=device)
+    dist.all_gather_into_tensor(sizes, torch.tensor([n], dtype=torch.int64, device=device))
+    sizes = [int(v) for v in sizes.cpu()]
+    pad = max(8, max(sizes))
+    mine = torch.zeros(pad, dtype=torch.uint8, device=device)
+    if n:
+        mine[:n] = api.device_view(ptr, n, "|u1", device)
+    everyone = torch.empty(pad * world, dtype=torch.uint8, device=device)
+    dist.all_gather_into_tensor(everyone, mine)
+    return [everyone[r * pad:r * pad + sizes[r]] for r in range(world)]
+
+
 def output_bases(out_bytes: int, rank: int, world: int, dist, device):
     """All-gathers the per-shard text sizes; returns (this shard's byte offset in the whole file's
     activities section, total bytes).  CPU-op events of all shards precede GPU events in the

@@ -170,3 +170,25 @@ def with_raw_kernel_names(trace, extra_names=()):
                 k += 1
             at += size
     return raw, buf, expected
+
+
+def cut_into_shards(t, n_shards):
+    import numpy as np
+    from kineto_b200 import tracefile as tf
+    """Contiguous shards of a trace: whole buffers and a contiguous range of CPU-side activities each."""
+    bt = t.buftab.reshape(-1, 2)
+    nb, n = t.n_buffers, t.n_ops
+    cuts = [nb * i // n_shards for i in range(n_shards + 1)]
+    op_cuts = [0] + [n * (i + 1) // (n_shards + 1) for i in range(n_shards - 1)] + [n]
+    subs = []
+    for i in range(n_shards):
+        sub = tf.Trace(**{attr: getattr(t, attr) for _, attr, _ in tf._SECTIONS})
+        sub.buftab = bt[cuts[i]:cuts[i + 1]].reshape(-1).copy()
+        lo, hi = op_cuts[i], op_cuts[i + 1]
+        for col in ("op_start", "op_end", "op_id", "op_device", "op_resource", "op_thread", "op_type", "op_name", "op_flow", "op_flowt"):
+            setattr(sub, col, getattr(t, col)[lo:hi].copy())
+        mo = t.op_mdoff[lo:hi + 1]
+        sub.md = t.md[mo[0]:mo[-1]].copy()
+        sub.op_mdoff = (mo - mo[0]).astype(np.uint32)
+        subs.append(sub)
+    return subs

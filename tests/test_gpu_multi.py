@@ -90,3 +90,65 @@ def test_two_gpu_ranks_match_checker(tmp_path):
     want = b"".join(p[:m[0]] for p, m in zip(parts, metas)) + b"".join(p[m[0]:] for p, m in zip(parts, metas))
     assert metas[0][1] == len(want)
     assert open(str(tmp_path / "whole.json"), "rb").read() == want
+
+
+def _sync_rank_main(rank, port, tmp):
+    import torch.distributed as dist
+    import cases
+    from kineto_b200 import api, sharding
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(WORLD),
+                      NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    try:
+        dist.init_process_group("nccl", rank=rank, world_size=WORLD, device_id=dev, timeout=datetime.timedelta(seconds=90))
+        stream = torch.cuda.Stream(dev)
+        torch.cuda.set_stream(stream)
+        sub = helpers.cut_into_shards(cases.sync_mix_trace(40_000, seed=71), WORLD)[rank]
+        ctx = api.K2J(rank, stream.cuda_stream)
+        ctx.load(sub)
+        ctx.segment()
+        blobs = sharding.gather_lookup_records(ctx, rank, WORLD, dist, dev)
+        own = torch.from_numpy(np.ascontiguousarray(sub.cupti)).to(dev)
+        data, table, front_end, back_begin = sharding.with_guest_records(own, sub.buftab, blobs, rank)
+        torch.cuda.synchronize()
+        ctx.set_cupti(data, table)
+        ctx.set_guest_ranges(front_end, back_begin)
+        info = ctx.segment()
+        ex = sharding.JoinExchange(rank, WORLD, dist, dev)
+        rows, ext_stride, ops_stride, counts = ex.gather(api.device_view(info.external_records, int(info.n_external) * 2, "<i8", dev),
+                                                         api.device_view(info.op_ids, int(info.n_ops), "<i4", dev))
+        ctx.set_global_join_rows(rows, ext_stride, ops_stride, counts, WORLD, rank)
+        res = ctx.emit()
+        got = ctx.copy_output().tobytes()
+        total = sharding.reduce_counters(res, dist, dev)
+        np.save(os.path.join(tmp, "sync_part%d.npy" % rank), np.frombuffer(got, np.uint8))
+        open(os.path.join(tmp, "sync_meta%d" % rank), "w").write("%d %d %d" % (res["ops_bytes"], total["x_events"], total["n_records"]))
+        dist.barrier()
+    except BaseException:
+        import traceback
+        open(os.path.join(tmp, "err%d" % rank), "w").write(traceback.format_exc())
+        os._exit(1)
+    ctx.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpu_ranks_with_synchronisation_records(tmp_path):
+    """A trace with synchronisation and CUDA event records on two GPUs: the ranks all-gather their lookup records
+    (NCCL), run with the other rank's as guests, and their texts concatenate to the text of the whole trace."""
+    import torch.multiprocessing as mp
+    import cases
+    from kineto_b200 import api
+    port = 29700 + ((os.getpid() + 7) % 2000)
+    try:
+        mp.spawn(_sync_rank_main, args=(port, str(tmp_path)), nprocs=WORLD, join=True)
+    except Exception as e:  # noqa: BLE001
+        errs = [open(str(f)).read() for f in sorted(tmp_path.glob("err*"))]
+        pytest.fail("a rank failed: %s\n%s" % (e, "\n".join(errs)))
+    whole, res = api.process(cases.sync_mix_trace(40_000, seed=71))
+    parts = [np.load(str(tmp_path / ("sync_part%d.npy" % r))).tobytes() for r in range(WORLD)]
+    metas = [[int(x) for x in open(str(tmp_path / ("sync_meta%d" % r))).read().split()] for r in range(WORLD)]
+    got = b"".join(p[:m[0]] for p, m in zip(parts, metas)) + b"".join(p[m[0]:] for p, m in zip(parts, metas))
+    assert got == whole, helpers.first_diff(whole, got)
+    assert metas[0][1] == res["x_events"] and metas[0][2] == res["n_records"]

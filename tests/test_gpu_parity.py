@@ -334,6 +334,64 @@ def test_sharded_runs_concatenate_to_the_whole(n_shards):
         ctx.close()
 
 
+@pytest.mark.parametrize("n_shards,seed", [(2, 61), (3, 62), (5, 63)])
+def test_sharded_synchronisation_records_concatenate_to_the_whole(n_shards, seed):
+    """Synchronisation and CUDA event records look things up in maps the reference fills from the whole trace
+    (contexts' devices, CUDA event records, streams with GPU work, the first stream synchronisation of a row).  With
+    every shard given the other shards' lookup records as guests (k2j_export_lookup_records, k2j_set_guest_ranges)
+    the shards' texts concatenate to the text of one run over the whole trace, and the counts add up."""
+    import torch
+    from kineto_b200 import api, sharding
+    t = cases.sync_mix_trace(60_000, seed=seed)
+    whole, res = gpu_run(t)
+    subs = helpers.cut_into_shards(t, n_shards)
+    ctxs = [api.K2J(0) for _ in subs]
+    try:
+        cupti_dev = torch.from_numpy(np.ascontiguousarray(t.cupti)).to("cuda:0")
+        blobs = []
+        for c, sub in zip(ctxs, subs):
+            c.load(sub)
+            c.segment()
+            ptr, n = c.export_lookup_records()
+            blobs.append(api.device_view(ptr, n, "|u1").clone())
+        assert sum(b.numel() for b in blobs) > 0
+        torch.cuda.synchronize()
+        # without the guests a sharded run with such records is refused
+        info = ctxs[0].segment()
+        e0 = api.device_view(info.external_records, int(info.n_external) * 2, "<i8").clone()
+        o0 = api.device_view(info.op_ids, int(info.n_ops), "<i4").clone()
+        torch.cuda.synchronize()
+        ctxs[0].set_global_join(e0, e0.numel() // 2, 0, o0, o0.numel())
+        with pytest.raises(api.K2JError, match="UNSUPPORTED|lookup records"):
+            ctxs[0].emit()
+        infos = []
+        for r, (c, sub) in enumerate(zip(ctxs, subs)):
+            data, table, front_end, back_begin = sharding.with_guest_records(cupti_dev, sub.buftab, blobs, r)
+            torch.cuda.synchronize()
+            c.set_cupti(data, table)
+            c.set_guest_ranges(front_end, back_begin)
+            infos.append(c.segment())
+        ext = torch.cat([api.device_view(i.external_records, int(i.n_external) * 2, "<i8").clone() for i in infos])
+        ops = torch.cat([api.device_view(i.op_ids, int(i.n_ops), "<i4").clone() for i in infos])
+        torch.cuda.synchronize()
+        parts, results, begin = [], [], 0
+        for c, i in zip(ctxs, infos):
+            c.set_global_join(ext, ext.numel() // 2, begin, ops, ops.numel())
+            begin += int(i.n_external)
+            results.append(c.emit())
+            parts.append(c.copy_output().tobytes())
+    finally:
+        for c in ctxs:
+            c.close()
+    ops_txt = b"".join(p[:r["ops_bytes"]] for p, r in zip(parts, results))
+    gpu_txt = b"".join(p[r["ops_bytes"]:] for p, r in zip(parts, results))
+    got = ops_txt + gpu_txt
+    assert got == whole, helpers.first_diff(whole, got)
+    for k in ("x_events", "flow_events", "n_records", "out_of_range_events", "blocklisted_runtime_events",
+              "invalid_external_correlation_events", "unexpected_cuda_events"):
+        assert sum(r[k] for r in results) == res[k], k
+
+
 @pytest.mark.skipif(not helpers.have_ref(), reason="reference build (oracle/_ref) not present")
 def test_full_size_against_reference():
     """The benchmark workload at a quarter of its size, byte for byte against the unmodified reference."""
