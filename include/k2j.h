@@ -212,6 +212,14 @@ k2j_status k2j_run(k2j_ctx* ctx, k2j_result* result);
  * met them itself, print nothing and are not counted.  Then k2j_segment, the join exchange and k2j_emit as usual.
  * Without declared guest ranges a sharded run with such records is K2J_ERR_UNSUPPORTED. */
 k2j_status k2j_export_lookup_records(k2j_ctx* ctx, const void** records, uint64_t* n_bytes);
+/* Sharded traces with collectives.  A kernel launched by a record_param_comms CPU op prints that op's collective
+ * metadata (libkineto/src/output_json.cpp:718-801, :900-906), and the op may belong to another shard.  The caller
+ * appends the other shards' record_param_comms ops (id, name and metadata entries; their strings added to the pool)
+ * behind its own rows in k2j_set_ops and says how many of the last rows are such guests: guest rows are found by the
+ * kernels that need them, are never logged, extend no map and are not among the op ids k2j_segment reports.
+ * k2j_set_ops resets the count to 0.  Ids of record_param_comms ops are taken to be used by no other op of the
+ * trace (the reference would take the last op with that id, whatever its name). */
+k2j_status k2j_set_guest_ops(k2j_ctx* ctx, uint64_t n_guest_ops);
 k2j_status k2j_set_guest_ranges(k2j_ctx* ctx, uint64_t front_end_bytes, uint64_t back_begin_bytes);
 
 /* The same work in two steps, for traces sharded by contiguous record range over several GPUs (one

@@ -67,7 +67,7 @@ class SegmentInfo(C.Structure):
 EXPORTS = ["k2j_set_global_join_rows", "k2j_emit_to_host", "k2j_emit_to_fd", "k2j_exclusive_scan_u32", "k2j_exclusive_scan_u32_noalloc", "k2j_segment", "k2j_set_global_join", "k2j_emit", "k2j_create", "k2j_destroy", "k2j_last_error", "k2j_set_params", "k2j_set_strings",
            "k2j_set_cbid_names", "k2j_set_thread_map", "k2j_set_ops", "k2j_set_cupti", "k2j_run", "k2j_output",
            "k2j_copy_output", "k2j_copy_output_async", "k2j_write_output", "k2j_write_output_at", "k2j_synchronize", "k2j_version",
-           "k2j_export_lookup_records", "k2j_set_guest_ranges", "k2j_names_create", "k2j_names_destroy", "k2j_names_intern", "k2j_names_pool", "k2j_intern_kernel_names"]
+           "k2j_export_lookup_records", "k2j_set_guest_ranges", "k2j_set_guest_ops", "k2j_names_create", "k2j_names_destroy", "k2j_names_intern", "k2j_names_pool", "k2j_intern_kernel_names"]
 
 _lib = None
 
@@ -109,6 +109,7 @@ def load_library():
     lib.k2j_synchronize.argtypes = [vp]
     lib.k2j_export_lookup_records.argtypes = [vp, C.POINTER(vp), C.POINTER(C.c_uint64)]
     lib.k2j_set_guest_ranges.argtypes = [vp, C.c_uint64, C.c_uint64]
+    lib.k2j_set_guest_ops.argtypes = [vp, C.c_uint64]
     lib.k2j_names_create.argtypes = [C.POINTER(vp)]
     lib.k2j_names_destroy.argtypes = [vp]
     lib.k2j_names_destroy.restype = None
@@ -241,6 +242,9 @@ class K2J:
         self._keep["cupti"], self._keep["buftab"] = cupti, bt
         n = cupti.nbytes if isinstance(cupti, np.ndarray) else cupti.numel()
         self._check(self.lib.k2j_set_cupti(self.h, _ptr(cupti), n, _ptr(bt), bt.size // 2))
+
+    def set_guest_ops(self, n_guest_ops: int):
+        self._check(self.lib.k2j_set_guest_ops(self.h, n_guest_ops))
 
     def set_guest_ranges(self, front_end_bytes: int, back_begin_bytes: int):
         self._check(self.lib.k2j_set_guest_ranges(self.h, front_end_bytes, back_begin_bytes))

@@ -101,7 +101,8 @@ struct k2j_ctx {
   const void* g_ext = nullptr; uint64_t g_n_ext = 0, g_own_begin = 0;
   const int32_t* g_op_ids = nullptr; uint64_t g_n_ops = 0;
   uint64_t guest_front_bytes = 0, guest_back_bytes = ~0ull; bool guests_declared = false;  // k2j_set_guest_ranges
-  DevBuf exp_keys, exp_first, exp_list, exp_out;
+  DevBuf exp_keys, exp_first, exp_list, exp_out, coll_tab;
+  uint64_t n_guest_ops = 0;                                           // k2j_set_guest_ops
   uint32_t g_ext_stride = 0, g_ops_stride = 0, g_world = 1; uint64_t g_pitch = 0; const uint64_t* g_counts = nullptr;  // rows of an all-gather
 };
 
@@ -338,7 +339,7 @@ void k2j_destroy(k2j_ctx* c) {
                     &c->sort_vals[1], &c->sort_hist, &c->sort_base, &c->sort_rank, &c->tid_tab, &c->corr_tab, &c->user_tab, &c->op_tab,
                     &c->work_slot, &c->work_ev, &c->ev_size, &c->ev_off, &c->ev_ext, &c->out, &c->counters, &c->ext_local, &c->ctx_tab, &c->evt_recs,
                     &c->seen_tab, &c->row_key, &c->row_first, &c->corr_zero, &c->str_class, &c->comms_flag, &c->coll_list, &c->corr0,
-                    &c->exp_keys, &c->exp_first, &c->exp_list, &c->exp_out})
+                    &c->exp_keys, &c->exp_first, &c->exp_list, &c->exp_out, &c->coll_tab})
     b->release();
   if (c->h_totals) cudaFreeHost(c->h_totals);
   if (c->h_counters) cudaFreeHost(c->h_counters);
@@ -439,6 +440,7 @@ k2j_status k2j_set_ops(k2j_ctx* c, const k2j_ops* o) {
   K2J_CUDA(c, cudaSetDevice(c->device));
   const uint64_t n = o->n_ops;
   c->n_ops = n;
+  c->n_guest_ops = 0;  // new rows: k2j_set_guest_ops says again which of them are guests
   uint64_t n_md = 0;
   if (n > 0) {
     if (!o->md_off) return fail(c, K2J_ERR_INVALID_ARGUMENT, "null md_off");
@@ -525,6 +527,7 @@ k2j_status k2j_segment(k2j_ctx* c, k2j_segment_info* info) {
   d.op_type = (const int32_t*)c->op_type.dev; d.op_name = (const uint32_t*)c->op_name.dev; d.op_flow = (const uint32_t*)c->op_flow.dev;
   d.op_flowt = (const uint8_t*)c->op_flowt.dev; d.op_mdoff = (const uint32_t*)c->op_mdoff.dev; d.md = (const MdEntry*)c->op_md.dev;
   d.counters = c->counters.as<Counters>();
+  d.n_guest_ops = c->n_guest_ops; d.coll_tab = nullptr;
   d.guest_front = (uint32_t)(c->guest_front_bytes / 8);
   d.guest_back = c->guest_back_bytes == ~0ull ? 0xFFFFFFFFu : (uint32_t)(c->guest_back_bytes / 8);
 
@@ -590,7 +593,7 @@ k2j_status k2j_segment(k2j_ctx* c, k2j_segment_info* info) {
     info->n_records = totals[C_EVENTS] + totals[C_WAIT] + totals[C_EXT] + totals[C_UNEXPECTED];
     info->n_external = totals[C_EXT];
     info->external_records = reinterpret_cast<const k2j_external_record*>(d.ext_local);
-    info->n_ops = c->n_ops;
+    info->n_ops = c->n_ops - c->n_guest_ops;
     info->op_ids = d.op_id;
     K2J_CUDA(c, cudaStreamSynchronize(s));  // the arrays above are complete when this returns
   }
@@ -621,7 +624,7 @@ k2j_status k2j_set_global_join_rows(k2j_ctx* c, const void* ext_rows, uint64_t e
   if (!is_device_ptr(ext_rows) || !is_device_ptr(op_id_rows) || !is_device_ptr(counts))
     return fail(c, K2J_ERR_INVALID_ARGUMENT, "gathered join rows must be device memory");
   if (ext_stride == 0 || ops_stride == 0 || ext_stride * world >= 0xFFFFFFF0ull || ops_stride * world >= 0xFFFFFFF0ull ||
-      c->totals[C_EXT] > ext_stride || c->n_ops > ops_stride || (row_pitch_bytes & 7))
+      c->totals[C_EXT] > ext_stride || c->n_ops - c->n_guest_ops > ops_stride || (row_pitch_bytes & 7))
     return fail(c, K2J_ERR_INVALID_ARGUMENT, "join rows: stride smaller than this shard's share, or out of range");
   c->g_ext = ext_rows; c->g_n_ext = ext_stride * world; c->g_own_begin = ext_stride * rank;
   c->g_op_ids = op_id_rows; c->g_n_ops = ops_stride * world;
@@ -642,6 +645,14 @@ k2j_status k2j_set_guest_ranges(k2j_ctx* c, uint64_t front_end_bytes, uint64_t b
   }
   c->guest_front_bytes = front_end_bytes; c->guest_back_bytes = back_begin_bytes; c->guests_declared = true;
   c->segmented = false;  // the next k2j_segment picks the ranges up
+  return K2J_OK;
+}
+
+k2j_status k2j_set_guest_ops(k2j_ctx* c, uint64_t n_guest_ops) {
+  if (!c) return K2J_ERR_INVALID_ARGUMENT;
+  if (n_guest_ops > c->n_ops) return fail(c, K2J_ERR_INVALID_ARGUMENT, "more guest rows than CPU-side activities");
+  c->n_guest_ops = n_guest_ops;
+  c->segmented = false;
   return K2J_OK;
 }
 
@@ -784,7 +795,7 @@ k2j_status emit_core(k2j_ctx* c, k2j_result* res, const TileSink& sink) {
     own_begin = c->g_own_begin; own_end = own_begin + totals[C_EXT];
   } else {
     d.ext_all = d.ext_local; d.n_ext_all = totals[C_EXT];
-    d.join_op_ids = d.op_id; d.n_join_ops = c->n_ops;
+    d.join_op_ids = d.op_id; d.n_join_ops = c->n_ops - c->n_guest_ops;
     d.join_counts = nullptr;
   }
   K2J_CUDA(c, c->ev_size.reserve(std::max<uint64_t>(1, d.n_events) * 4));
@@ -858,12 +869,22 @@ k2j_status emit_core(k2j_ctx* c, k2j_result* res, const TileSink& sink) {
   if (c->n_ops && c->n_strings) {
     K2J_CUDA(c, c->comms_flag.reserve(16));
     K2J_CUDA(c, cudaMemsetAsync(c->comms_flag.p, 0, 4, s));
-    k_find_comms<<<(uint32_t)((c->n_ops + 255) / 256), 256, 0, s>>>(d, c->comms_flag.as<uint32_t>(), c->have_global_join ? 0 : 1);
+    k_find_comms<<<(uint32_t)((c->n_ops + 255) / 256), 256, 0, s>>>(d, c->comms_flag.as<uint32_t>(), 1);
     c->launches++;
     d.has_comms = c->comms_flag.as<uint32_t>();
+    if (c->have_global_join) {
+      // several shards: the join's table holds positions in the gathered keys, so the record_param_comms ops that carry
+      // metadata here (this shard's rows and the guest rows) get an id -> row table of their own
+      const uint32_t coll_cap = pow2_at_least(2 * c->n_ops + 16);
+      K2J_CUDA(c, c->coll_tab.reserve((size_t)coll_cap * 8));
+      d.coll_tab = c->coll_tab.as<unsigned long long>(); d.coll_mask = coll_cap - 1;
+      K2J_CUDA(c, cudaMemsetAsync(d.coll_tab, 0, (size_t)coll_cap * 8, s));
+      k_build_coll<<<(uint32_t)((c->n_ops + 255) / 256), 256, 0, s>>>(d);
+      c->launches++;
+    }
   }
   d.work_indirect = nullptr; d.n_indirect = 0; d.coll_list = nullptr;
-  if (d.has_comms && !c->have_global_join && totals[C_KERNEL]) {
+  if (d.has_comms && totals[C_KERNEL]) {
     K2J_CUDA(c, c->coll_list.reserve(totals[C_KERNEL] * 4));
     d.coll_list = c->coll_list.as<uint32_t>();
   }

@@ -182,6 +182,10 @@ struct Dev {
   // that only feed this shard's lookups (contexts, CUDA event records, streams with GPU work, first stream syncs):
   // they run through the size pass like any record, print nothing and are not counted.  None: 0 and 0xFFFFFFFF.
   uint32_t guest_front, guest_back;
+  // Sharded traces: the last n_guest_ops CPU-side activities are other shards' record_param_comms ops, present only
+  // so that kernels they launched find their collective metadata: never logged, not part of the join keys.
+  // coll_tab (sharded runs): id -> row of the record_param_comms ops among this shard's rows and the guests.
+  uint64_t n_guest_ops; unsigned long long* coll_tab; uint32_t coll_mask;
   uint64_t tile_begin, tile_end;   // this launch writes the events whose text starts in [tile_begin, tile_end): the whole
                                    // text, or one slab of a tiled run (then `out` points outside the slab for other bytes)
   Counters* counters;
@@ -584,7 +588,7 @@ __global__ void k_build_tids(Dev d) {
   if (i < d.n_tid_pairs) key = (uint32_t)d.tid_pairs[2 * i];
   else {
     const uint64_t j = i - d.n_tid_pairs;
-    if (op_pid(d, d.op_device[j]) != d.pid) return;
+    if (j >= d.n_ops - d.n_guest_ops || op_pid(d, d.op_device[j]) != d.pid) return;  // guest rows extend no map
     key = (uint32_t)d.op_thread[j];
   }
   if (!tab_insert_min(d.tid_tab, d.tid_mask, key, (uint32_t)i)) atomicAdd(&d.counters->device_check, 1ull);
@@ -624,6 +628,14 @@ __global__ void k_find_comms(Dev d, uint32_t* flag, int comms_on) {
   if (comms_on && name < d.n_strings && d.str_class[name] == 1u) atomicOr(flag, 1u);
   const int type = d.op_type[i];
   if (type == 9 || type == 17 || type == 26 || type == 28) atomicOr(flag, 2u);  // instant and counter events: written by the same extra launch
+}
+// Sharded runs: id -> row of the record_param_comms ops of this shard and of the guest rows (the last row wins).
+__global__ void k_build_coll(Dev d) {
+  const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= d.n_ops) return;
+  const uint32_t name = d.op_name[i];
+  if (name >= d.n_strings || d.str_class[name] != 1u) return;
+  if (!tab_insert(d.coll_tab, d.coll_mask, (uint32_t)d.op_id[i], (uint32_t)i)) atomicAdd(&d.counters->device_check, 1ull);
 }
 // CPU-op id -> position (last writer wins): activityMap_[id] = op, GenericActivityProfiler.cpp:262.
 __global__ void k_build_ops(Dev d) {
@@ -1386,7 +1398,9 @@ __device__ __forceinline__ uint64_t gather_kernel(const Dev& d, uint32_t* a, Tal
   if (!has_ext) p &= ~((1ull << K_EXT) | (1ull << K_EXTC));
   else if (d.has_comms != nullptr && (*d.has_comms & 1u) != 0u) {
     // a kernel launched by a record_param_comms op carries that op's collective metadata (output_json.cpp:900-906)
-    const uint32_t row = tab_find(d.op_tab, d.op_mask, (uint32_t)ext);
+    // (one shard: the op the join found; several: the join's table holds positions in the gathered keys, and the
+    // collective ops of this shard's rows and of the guest rows have a table of their own)
+    const uint32_t row = d.coll_tab != nullptr ? tab_find(d.coll_tab, d.coll_mask, (uint32_t)ext) : tab_find(d.op_tab, d.op_mask, (uint32_t)ext);
     if (row < d.n_ops && d.op_name[row] < d.n_strings && d.str_class[d.op_name[row]] == 1u) {
       p |= 1ull << K_COLL; s32(a, KS_COLLROW, row);
       if (counting && d.coll_list != nullptr) d.coll_list[atomicAdd(&d.counters->n_coll, 1ull)] = (uint32_t)t.work;  // for the extra emit launch
@@ -1613,6 +1627,7 @@ __global__ void k_export_copy(Dev d, const unsigned long long* list, uint32_t n_
 
 // CPU-side activity: ChromeTraceLogger::handleActivity for a GenericTraceActivity (output_json.cpp:837-963)
 __device__ __forceinline__ uint64_t gather_op(const Dev& d, uint64_t i, uint32_t* a, Tally& t) {
+  if (i >= d.n_ops - d.n_guest_ops) return 0;  // a guest row: looked up, never logged
   const int32_t type = d.op_type[i];
   if ((uint32_t)type >= 29u) { atomicAdd(&d.counters->device_check, 1ull); return 0; }
   if (!((d.type_mask >> type) & 1u)) return 0;  // type not selected: joins, but is not logged

@@ -10,6 +10,8 @@ in the gathered array exactly as in a single-process run.  Works with any torch.
 """
 from __future__ import annotations
 
+import numpy as np
+
 
 def gather_join_keys(ext_local, ops_local, rank: int, world: int, dist):
     """ext_local: int64 tensor with 2 words per record; ops_local: int32 tensor.
@@ -84,6 +86,62 @@ class JoinExchange:
         self.dist.all_gather_into_tensor(self.counts, self.mine)
         self.dist.all_gather_into_tensor(self.rows, self.row)
         return self.rows, self.ext_stride, self.ops_stride, self.counts
+
+
+def collective_ops(trace):
+    """The record_param_comms ops of a shard in a form that travels: (id, [(key bytes, type, value or bytes)])."""
+    from . import tracefile as tf
+    pool = trace.pool()
+    want = [i for i in range(len(pool)) if pool[i] == b"record_param_comms"]
+    if not want:
+        return []
+    out = []
+    for row in np.flatnonzero(np.isin(trace.op_name, np.array(want, dtype=np.uint32))):
+        entries = []
+        for e in trace.md[int(trace.op_mdoff[row]):int(trace.op_mdoff[row + 1])]:
+            text = e["type"] in (tf.MD_STRING, tf.MD_RAWJSON)
+            entries.append((pool[int(e["key"])], int(e["type"]), pool[int(e["value"])] if text else int(e["value"])))
+        out.append((int(trace.op_id[row]), entries))
+    return out
+
+
+def with_guest_ops(trace, guests):
+    """A copy of the shard with other shards' record_param_comms ops (`collective_ops` of those shards) appended as
+    guest rows behind its own; returns (trace, number of guest rows) for K2J.load and K2J.set_guest_ops."""
+    import copy
+    from . import tracefile as tf
+    if not guests:
+        return trace, 0
+    t = copy.copy(trace)
+    pool = trace.pool()
+    name = pool.add("record_param_comms")
+    md, mdoff = [trace.md], [trace.op_mdoff]
+    rows, at = [], int(trace.op_mdoff[-1])
+    for _, entries in guests:
+        e = np.zeros(len(entries), tf.MD_ENTRY)
+        for k, (key, typ, value) in enumerate(entries):
+            e[k] = (pool.add(key), typ, pool.add(value) if typ in (tf.MD_STRING, tf.MD_RAWJSON) else value)
+        rows.append(e)
+        at += len(entries)
+        mdoff.append(np.array([at], np.uint32))
+    n = len(guests)
+    t.md = np.concatenate(md + rows)
+    t.op_mdoff = np.concatenate(mdoff).astype(np.uint32)
+    z = lambda a, fill=0: np.concatenate([a, np.full(n, fill, a.dtype)])  # noqa: E731
+    t.op_start, t.op_end, t.op_device, t.op_resource, t.op_thread = z(trace.op_start), z(trace.op_end), z(trace.op_device), z(trace.op_resource), z(trace.op_thread)
+    t.op_type, t.op_flow, t.op_flowt = z(trace.op_type), z(trace.op_flow), z(trace.op_flowt)
+    t.op_id = np.concatenate([trace.op_id, np.array([g[0] for g in guests], trace.op_id.dtype)])
+    t.op_name = np.concatenate([trace.op_name, np.full(n, name, trace.op_name.dtype)])
+    t.set_pool(pool)
+    return t, n
+
+
+def gather_collective_ops(trace, rank: int, world: int, dist):
+    """All shards' record_param_comms ops except this shard's own, in shard order (host-side collective of pickled
+    lists: such ops are few)."""
+    everyone = [None] * world
+    dist.all_gather_object(everyone, collective_ops(trace))
+    return [g for r, ops in enumerate(everyone) if r != rank for g in ops]
 
 
 def with_guest_records(own_cupti, own_buftab, blobs, rank: int):

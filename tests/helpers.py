@@ -192,3 +192,26 @@ def cut_into_shards(t, n_shards):
         sub.op_mdoff = (mo - mo[0]).astype(np.uint32)
         subs.append(sub)
     return subs
+
+
+def rebuffer(trace, records_per_buffer):
+    """The same records in buffers of at most `records_per_buffer` records each (cut at record boundaries)."""
+    import copy
+    import numpy as np
+    from kineto_b200 import tracefile as tf
+    table = []
+    for b in range(trace.n_buffers):
+        at, end = int(trace.buftab[2 * b]), int(trace.buftab[2 * b]) + int(trace.buftab[2 * b + 1])
+        start, n = at, 0
+        while at + 8 <= end:
+            kind = int(trace.cupti[at:at + 4].view(np.uint32)[0])
+            at += (tf.RECORD_SIZE[kind] + 7) & ~7
+            n += 1
+            if n == records_per_buffer:
+                table += [start, at - start]
+                start, n = at, 0
+        if at > start:
+            table += [start, at - start]
+    t = copy.copy(trace)
+    t.buftab = np.array(table, np.uint64)
+    return t

@@ -392,6 +392,46 @@ def test_sharded_synchronisation_records_concatenate_to_the_whole(n_shards, seed
         assert sum(r[k] for r in results) == res[k], k
 
 
+@pytest.mark.parametrize("n_shards", [2, 4])
+def test_sharded_collectives_concatenate_to_the_whole(n_shards):
+    """A kernel prints the collective metadata of the record_param_comms op that launched it, and that op may belong
+    to another shard: with the other shards' collective ops appended as guest rows (k2j_set_guest_ops) the shards'
+    texts concatenate to the text of one run over the whole trace."""
+    import torch
+    from kineto_b200 import api, sharding
+    t = helpers.rebuffer(cases.collective_trace(300, seed=56), 37)
+    whole, res = gpu_run(t)
+    assert whole.count(b'"Collective name"') > 200
+    subs = helpers.cut_into_shards(t, n_shards)
+    colls = [sharding.collective_ops(sub) for sub in subs]
+    assert all(colls)
+    ctxs = [api.K2J(0) for _ in subs]
+    try:
+        infos = []
+        for r, (c, sub) in enumerate(zip(ctxs, subs)):
+            guests = [g for q, ops in enumerate(colls) if q != r for g in ops]
+            shard, n_guests = sharding.with_guest_ops(sub, guests)
+            c.load(shard)
+            c.set_guest_ops(n_guests)
+            infos.append(c.segment())
+            assert int(infos[-1].n_ops) == sub.n_ops
+        ext = torch.cat([api.device_view(i.external_records, int(i.n_external) * 2, "<i8").clone() for i in infos])
+        ops = torch.cat([api.device_view(i.op_ids, int(i.n_ops), "<i4").clone() for i in infos])
+        torch.cuda.synchronize()
+        parts, results, begin = [], [], 0
+        for c, i in zip(ctxs, infos):
+            c.set_global_join(ext, ext.numel() // 2, begin, ops, ops.numel())
+            begin += int(i.n_external)
+            results.append(c.emit())
+            parts.append(c.copy_output().tobytes())
+    finally:
+        for c in ctxs:
+            c.close()
+    got = b"".join(p[:r["ops_bytes"]] for p, r in zip(parts, results)) + b"".join(p[r["ops_bytes"]:] for p, r in zip(parts, results))
+    assert got == whole, helpers.first_diff(whole, got)
+    assert sum(r["x_events"] for r in results) == res["x_events"]
+
+
 @pytest.mark.skipif(not helpers.have_ref(), reason="reference build (oracle/_ref) not present")
 def test_full_size_against_reference():
     """The benchmark workload at a quarter of its size, byte for byte against the unmodified reference."""
