@@ -218,8 +218,29 @@ k2j_status k2j_export_lookup_records(k2j_ctx* ctx, const void** records, uint64_
  * behind its own rows in k2j_set_ops and says how many of the last rows are such guests: guest rows are found by the
  * kernels that need them, are never logged, extend no map and are not among the op ids k2j_segment reports.
  * k2j_set_ops resets the count to 0.  Ids of record_param_comms ops are taken to be used by no other op of the
- * trace (the reference would take the last op with that id, whatever its name). */
+ * trace (the reference would take the last op with that id, whatever its name).  Guest rows also serve as the
+ * named rows of k2j_append_spans below. */
 k2j_status k2j_set_guest_ops(k2j_ctx* ctx, uint64_t n_guest_ops);
+
+/* Sharded traces with user annotations.  A gpu_user_annotation span covers, per (device, stream) and annotation
+ * op, the GPU activities correlated to that op (libkineto/src/GenericActivityProfiler.cpp:292-327), wherever in the
+ * trace they are, and the reference logs the spans after every other activity.  With K2J_FLAG_USER_ANNOTATIONS a
+ * sharded run (k2j_set_global_join*) writes no spans; after k2j_emit, k2j_partial_spans returns this shard's part
+ * of every span (host memory of the context, valid until its next run; first_event is the shard's own event
+ * number; op_row is not meaningful).  The caller merges the parts of all shards - smallest start, largest end,
+ * first_event ordered by (shard, event number) - names for each span the row of its op among the LAST shard's
+ * CPU-side activities (its own or guest rows, k2j_set_guest_ops; 0xFFFFFFFF: no name), and hands the list to
+ * k2j_append_spans on the last shard's context, which appends their events, in the reference's order
+ * (libkineto/src/GenericActivityProfiler.h:341-346), to the text k2j_emit left there. */
+typedef struct {
+  int64_t start_ns, end_ns;
+  uint64_t first_event;
+  uint32_t device, stream;
+  int32_t op_id;
+  uint32_t op_row;
+} k2j_span;
+k2j_status k2j_partial_spans(k2j_ctx* ctx, const k2j_span** spans, uint64_t* n_spans);
+k2j_status k2j_append_spans(k2j_ctx* ctx, const k2j_span* spans, uint64_t n_spans, uint64_t* n_bytes);
 k2j_status k2j_set_guest_ranges(k2j_ctx* ctx, uint64_t front_end_bytes, uint64_t back_begin_bytes);
 
 /* The same work in two steps, for traces sharded by contiguous record range over several GPUs (one

@@ -64,10 +64,13 @@ class SegmentInfo(C.Structure):
                 ("n_ops", C.c_uint64), ("op_ids", C.c_void_p)]
 
 
+SPAN = np.dtype([("start_ns", "<i8"), ("end_ns", "<i8"), ("first_event", "<u8"), ("device", "<u4"), ("stream", "<u4"),
+                 ("op_id", "<i4"), ("op_row", "<u4")])  # k2j_span
+
 EXPORTS = ["k2j_set_global_join_rows", "k2j_emit_to_host", "k2j_emit_to_fd", "k2j_exclusive_scan_u32", "k2j_exclusive_scan_u32_noalloc", "k2j_segment", "k2j_set_global_join", "k2j_emit", "k2j_create", "k2j_destroy", "k2j_last_error", "k2j_set_params", "k2j_set_strings",
            "k2j_set_cbid_names", "k2j_set_thread_map", "k2j_set_ops", "k2j_set_cupti", "k2j_run", "k2j_output",
            "k2j_copy_output", "k2j_copy_output_async", "k2j_write_output", "k2j_write_output_at", "k2j_synchronize", "k2j_version",
-           "k2j_export_lookup_records", "k2j_set_guest_ranges", "k2j_set_guest_ops", "k2j_names_create", "k2j_names_destroy", "k2j_names_intern", "k2j_names_pool", "k2j_intern_kernel_names"]
+           "k2j_export_lookup_records", "k2j_set_guest_ranges", "k2j_set_guest_ops", "k2j_partial_spans", "k2j_append_spans", "k2j_names_create", "k2j_names_destroy", "k2j_names_intern", "k2j_names_pool", "k2j_intern_kernel_names"]
 
 _lib = None
 
@@ -110,6 +113,8 @@ def load_library():
     lib.k2j_export_lookup_records.argtypes = [vp, C.POINTER(vp), C.POINTER(C.c_uint64)]
     lib.k2j_set_guest_ranges.argtypes = [vp, C.c_uint64, C.c_uint64]
     lib.k2j_set_guest_ops.argtypes = [vp, C.c_uint64]
+    lib.k2j_partial_spans.argtypes = [vp, C.POINTER(vp), C.POINTER(C.c_uint64)]
+    lib.k2j_append_spans.argtypes = [vp, vp, C.c_uint64, C.POINTER(C.c_uint64)]
     lib.k2j_names_create.argtypes = [C.POINTER(vp)]
     lib.k2j_names_destroy.argtypes = [vp]
     lib.k2j_names_destroy.restype = None
@@ -242,6 +247,23 @@ class K2J:
         self._keep["cupti"], self._keep["buftab"] = cupti, bt
         n = cupti.nbytes if isinstance(cupti, np.ndarray) else cupti.numel()
         self._check(self.lib.k2j_set_cupti(self.h, _ptr(cupti), n, _ptr(bt), bt.size // 2))
+
+    def partial_spans(self) -> np.ndarray:
+        """This shard's parts of the user-annotation spans after a sharded emit (a copy; dtype SPAN)."""
+        ptr, n = C.c_void_p(), C.c_uint64()
+        self._check(self.lib.k2j_partial_spans(self.h, C.byref(ptr), C.byref(n)))
+        if n.value == 0:
+            return np.zeros(0, SPAN)
+        raw = C.string_at(ptr.value, n.value * SPAN.itemsize)
+        return np.frombuffer(raw, SPAN).copy()
+
+    def append_spans(self, spans: np.ndarray) -> int:
+        """Formats merged spans behind the text of the last emit (k2j_append_spans); returns the bytes added."""
+        a = np.ascontiguousarray(spans, dtype=SPAN)
+        n = C.c_uint64()
+        self._check(self.lib.k2j_append_spans(self.h, _ptr(a), a.size, C.byref(n)))
+        self.result["out_bytes"] += n.value
+        return n.value
 
     def set_guest_ops(self, n_guest_ops: int):
         self._check(self.lib.k2j_set_guest_ops(self.h, n_guest_ops))

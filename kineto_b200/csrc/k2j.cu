@@ -103,6 +103,7 @@ struct k2j_ctx {
   uint64_t guest_front_bytes = 0, guest_back_bytes = ~0ull; bool guests_declared = false;  // k2j_set_guest_ranges
   DevBuf exp_keys, exp_first, exp_list, exp_out, coll_tab;
   uint64_t n_guest_ops = 0;                                           // k2j_set_guest_ops
+  std::vector<SpanRec> partial_spans;                                 // sharded runs: this shard's parts of the user-annotation spans
   uint32_t g_ext_stride = 0, g_ops_stride = 0, g_world = 1; uint64_t g_pitch = 0; const uint64_t* g_counts = nullptr;  // rows of an all-gather
 };
 
@@ -250,7 +251,8 @@ k2j_status sort_gpu_events(k2j_ctx* c, uint64_t n) {
 // std::map over (device, stream), and inside it a std::unordered_map<int64_t, ...> over the op id,
 // filled in order of first use (libkineto/src/GenericActivityProfiler.h:341-346, .cpp:320-327) — and
 // sizes their events.  Host work is O(distinct annotations).
-k2j_status order_annotations(k2j_ctx* c, uint32_t span_cap, uint32_t* n_out, uint64_t* bytes_out) {
+// The span table as a list on the host (no order).
+k2j_status collect_spans(k2j_ctx* c, uint32_t span_cap, std::vector<SpanRec>* spans) {
   cudaStream_t s = c->stream;
   Dev& d = c->d;
   K2J_CUDA(c, c->span_out.reserve((size_t)span_cap * sizeof(SpanRec)));
@@ -261,11 +263,27 @@ k2j_status order_annotations(k2j_ctx* c, uint32_t span_cap, uint32_t* n_out, uin
   unsigned int n = 0;
   K2J_CUDA(c, cudaMemcpyAsync(&n, c->span_cnt.p, 4, cudaMemcpyDeviceToHost, s));
   K2J_CUDA(c, cudaStreamSynchronize(s));
+  spans->resize(n);
+  if (n == 0) return K2J_OK;
+  K2J_CUDA(c, cudaMemcpyAsync(spans->data(), c->span_out.p, (size_t)n * sizeof(SpanRec), cudaMemcpyDeviceToHost, s));
+  K2J_CUDA(c, cudaStreamSynchronize(s));
+  return K2J_OK;
+}
+k2j_status size_annotations(k2j_ctx* c, const std::vector<SpanRec>& spans, uint32_t* n_out, uint64_t* bytes_out);
+k2j_status order_annotations(k2j_ctx* c, uint32_t span_cap, uint32_t* n_out, uint64_t* bytes_out) {
+  std::vector<SpanRec> spans;
+  k2j_status st = collect_spans(c, span_cap, &spans);
+  if (st) return st;
+  return size_annotations(c, spans, n_out, bytes_out);
+}
+// Puts spans in logging order (see above), leaves them in span_out and sizes their events (ann_size, ann_off).
+k2j_status size_annotations(k2j_ctx* c, const std::vector<SpanRec>& spans, uint32_t* n_out, uint64_t* bytes_out) {
+  cudaStream_t s = c->stream;
+  Dev& d = c->d;
+  const unsigned int n = (unsigned int)spans.size();
   *n_out = n; *bytes_out = 0;
   if (n == 0) return K2J_OK;
-  std::vector<SpanRec> spans(n);
-  K2J_CUDA(c, cudaMemcpyAsync(spans.data(), c->span_out.p, (size_t)n * sizeof(SpanRec), cudaMemcpyDeviceToHost, s));
-  K2J_CUDA(c, cudaStreamSynchronize(s));
+  K2J_CUDA(c, c->span_out.reserve((size_t)n * sizeof(SpanRec)));
   std::map<std::pair<int64_t, int64_t>, std::vector<const SpanRec*>> by_stream;
   for (const SpanRec& r : spans) by_stream[{(int64_t)r.device, (int64_t)r.stream}].push_back(&r);
   std::vector<SpanRec> ordered;
@@ -648,6 +666,55 @@ k2j_status k2j_set_guest_ranges(k2j_ctx* c, uint64_t front_end_bytes, uint64_t b
   return K2J_OK;
 }
 
+k2j_status k2j_partial_spans(k2j_ctx* c, const k2j_span** spans, uint64_t* n_spans) {
+  if (!c) return K2J_ERR_INVALID_ARGUMENT;
+  if (!spans || !n_spans) return fail(c, K2J_ERR_INVALID_ARGUMENT, "null result pointers");
+  if (!c->ran && !c->streamed) return fail(c, K2J_ERR_STATE, "no completed run");
+  static_assert(sizeof(k2j_span) == sizeof(SpanRec), "k2j_span is SpanRec");
+  *spans = reinterpret_cast<const k2j_span*>(c->partial_spans.data());
+  *n_spans = c->partial_spans.size();
+  return K2J_OK;
+}
+
+k2j_status k2j_append_spans(k2j_ctx* c, const k2j_span* spans, uint64_t n_spans, uint64_t* n_bytes) {
+  if (!c) return K2J_ERR_INVALID_ARGUMENT;
+  if (!c->ran) return fail(c, K2J_ERR_STATE, "no completed run whose text is in the context");
+  if ((!spans && n_spans) || n_spans >= 0x7FFFFFF0ull) return fail(c, K2J_ERR_INVALID_ARGUMENT, "bad span list");
+  K2J_CUDA(c, cudaSetDevice(c->device));
+  cudaStream_t s = c->stream;
+  Dev& d = c->d;
+  std::vector<SpanRec> list(n_spans);
+  if (n_spans) memcpy(list.data(), spans, n_spans * sizeof(SpanRec));
+  for (const SpanRec& r : list)
+    if (r.op_row != 0xFFFFFFFFu && r.op_row >= c->n_ops) return fail(c, K2J_ERR_INVALID_ARGUMENT, "span names a row past the CPU-side activities");
+  uint32_t n = 0;
+  uint64_t ann_bytes = 0;
+  K2J_CUDA(c, cudaMemsetAsync(d.counters, 0, sizeof(Counters), s));
+  k2j_status st = size_annotations(c, list, &n, &ann_bytes);
+  if (st) return st;
+  if (ann_bytes) {
+    if (c->out.cap < c->out_bytes + ann_bytes + 64) {  // the text so far moves into a larger allocation
+      DevBuf bigger;
+      K2J_CUDA(c, bigger.reserve(c->out_bytes + ann_bytes + 64));
+      if (c->out_bytes) K2J_CUDA(c, cudaMemcpyAsync(bigger.p, c->out.p, c->out_bytes, cudaMemcpyDeviceToDevice, s));
+      K2J_CUDA(c, cudaStreamSynchronize(s));
+      c->out.release();
+      c->out = bigger;
+    }
+    d.out = c->out.as<uint8_t>(); d.out_cap = c->out_bytes + ann_bytes;
+    k_annotations<true><<<(n + kEventThreads - 1) / kEventThreads, kEventThreads, 0, s>>>(
+        d, c->span_out.as<SpanRec>(), n, c->ann_size.as<uint32_t>(), c->ann_off.as<uint64_t>(), c->out_bytes);
+    c->launches++;
+    K2J_CUDA(c, cudaGetLastError());
+  }
+  K2J_CUDA(c, cudaMemcpyAsync(c->h_counters, d.counters, sizeof(Counters), cudaMemcpyDeviceToHost, s));
+  K2J_CUDA(c, cudaStreamSynchronize(s));
+  if (c->h_counters->device_check) { c->ran = false; return fail(c, K2J_ERR_DEVICE_CHECK, "a device-side check failed while the spans were written"); }
+  c->out_bytes += ann_bytes;
+  if (n_bytes) *n_bytes = ann_bytes;
+  return K2J_OK;
+}
+
 k2j_status k2j_set_guest_ops(k2j_ctx* c, uint64_t n_guest_ops) {
   if (!c) return K2J_ERR_INVALID_ARGUMENT;
   if (n_guest_ops > c->n_ops) return fail(c, K2J_ERR_INVALID_ARGUMENT, "more guest rows than CPU-side activities");
@@ -821,7 +888,7 @@ k2j_status emit_core(k2j_ctx* c, k2j_result* res, const TileSink& sink) {
   d.corr0 = c->corr0.as<unsigned long long>();
   K2J_CUDA(c, cudaMemsetAsync(d.corr0, 0, 16, s));
   // the user-annotation table is only written and read when CUSTOM1 correlation records exist
-  if (!c->have_global_join && totals[C_USER] > 0) K2J_CUDA(c, cudaMemsetAsync(d.user_tab, 0, (size_t)corr_cap * 8, s));
+  if (totals[C_USER] > 0 || c->have_global_join) K2J_CUDA(c, cudaMemsetAsync(d.user_tab, 0, (size_t)corr_cap * 8, s));
   K2J_CUDA(c, cudaMemsetAsync(d.op_tab, 0, (size_t)op_cap * 8, s));
   const uint32_t tid_cap = std::max<uint32_t>(16384, pow2_at_least(4ull * c->n_tid));
   K2J_CUDA(c, c->tid_tab.reserve((size_t)tid_cap * 8));
@@ -829,11 +896,12 @@ k2j_status emit_core(k2j_ctx* c, k2j_result* res, const TileSink& sink) {
   K2J_CUDA(c, cudaMemsetAsync(d.tid_tab, 0, (size_t)tid_cap * 8, s));
   if (c->n_tid + c->n_ops) { k_build_tids<<<(uint32_t)((c->n_tid + c->n_ops + 255) / 256), 256, 0, s>>>(d); c->launches++; }
   // user-annotation span tables (single-shard runs only)
-  const bool spans_on = (c->params.flags & K2J_FLAG_USER_ANNOTATIONS) && !c->have_global_join && totals[C_USER] > 0;
+  // (several shards: another shard's CUSTOM1 records may name this shard's events, so the local count says nothing)
+  const bool spans_on = (c->params.flags & K2J_FLAG_USER_ANNOTATIONS) && (c->have_global_join || totals[C_USER] > 0);
   d.span_key = nullptr;
   uint32_t span_cap = 0;
   if (spans_on) {
-    span_cap = pow2_at_least(2 * totals[C_USER] + 16);
+    span_cap = pow2_at_least(2 * (c->have_global_join ? std::min<uint64_t>(c->g_n_ext, n_gpu_events) : totals[C_USER]) + 16);
     const uint32_t ds_cap = 1u << 16;
     K2J_CUDA(c, c->ds_tab.reserve((size_t)ds_cap * 8));
     K2J_CUDA(c, c->span_key.reserve((size_t)span_cap * 8));
@@ -962,7 +1030,13 @@ k2j_status emit_core(k2j_ctx* c, k2j_result* res, const TileSink& sink) {
     K2J_CUDA(c, cudaEventRecord(c->ev[4], s));
     K2J_CUDA(c, cudaStreamSynchronize(s));
     total_bytes = c->h_totals[20];
-    if (spans_on) {
+    c->partial_spans.clear();
+    if (spans_on && c->have_global_join) {
+      // several shards: this shard's part of every span waits for the caller to merge it with the other shards' parts
+      // (k2j_partial_spans, k2j_append_spans); nothing is written here
+      k2j_status st2 = collect_spans(c, span_cap, &c->partial_spans);
+      if (st2) return st2;
+    } else if (spans_on) {
       k2j_status st2 = order_annotations(c, span_cap, &n_spans, &ann_bytes);
       if (st2) return st2;
     }
@@ -1096,8 +1170,6 @@ k2j_status emit_core(k2j_ctx* c, k2j_result* res, const TileSink& sink) {
   cudaEventElapsedTime(&res->ms_emit, c->ev[7], c->ev[5]);
   res->ms_total = res->ms_segment + res->ms_join + res->ms_size + res->ms_scan + res->ms_emit;
   c->out_bytes = total_bytes + ann_bytes;
-  if ((c->params.flags & K2J_FLAG_USER_ANNOTATIONS) && c->have_global_join && c->h_counters->n_user)
-    return fail(c, K2J_ERR_UNSUPPORTED, "user-annotation spans across shards are not implemented");
   if (c->h_counters->device_check)
     return fail(c, K2J_ERR_DEVICE_CHECK, "%llu device-side checks failed (string id, table or output bound)",
                 (unsigned long long)c->h_counters->device_check);

@@ -666,7 +666,11 @@ __global__ void k_build_corr(Dev d, uint64_t own_begin, uint64_t own_end) {
     else ok = tab_insert(d.corr_tab, d.corr_mask, e.correlation_id, (uint32_t)i);
   } else if (e.external_kind == 4u) {
     atomicAdd(&d.counters->n_user, 1ull);
-    if (d.need_corr == nullptr) ok = tab_insert(d.user_tab, d.user_mask, e.correlation_id, (uint32_t)i);  // spans: single-shard runs only
+    // user-annotation spans: the same filter as above when the keys of several shards were gathered
+    if (d.need_corr == nullptr || (i >= own_begin && i < own_end) || bit_test(d.need_corr, d.need_corr_mask, e.correlation_id)) {
+      if (d.need_op != nullptr && (int64_t)e.external_id == (int64_t)(int32_t)e.external_id) bit_set(d.need_op, d.need_op_mask, (uint32_t)e.external_id);
+      ok = tab_insert(d.user_tab, d.user_mask, e.correlation_id, (uint32_t)i);
+    }
   } else if (i >= own_begin && i < own_end) atomicAdd(&d.counters->invalid_external_correlation, 1ull);
   if (!ok) atomicAdd(&d.counters->device_check, 1ull);
 }
@@ -1084,19 +1088,23 @@ __device__ __forceinline__ void linked_op(const Dev& d, uint32_t corr, unsigned 
 // Out of line (rare), with the tables it touches passed by value: a reference to the kernel's parameter block would
 // make every thread of the size pass copy that block (about 1 KB) into local memory at kernel entry.
 struct SpanArgs {
-  const unsigned long long* user_tab; uint32_t user_mask; const ExtRec* ext_all; const unsigned long long* op_tab; uint32_t op_mask;
+  const unsigned long long* user_tab; uint32_t user_mask; const ExtRec* ext_all; uint32_t ext_stride; uint64_t join_pitch;  // rows of an all-gather: see Dev
+  const unsigned long long* op_tab; uint32_t op_mask;
   unsigned long long* ds_tab; uint32_t ds_mask; unsigned long long* span_key; unsigned long long* span_nstart;
   unsigned long long* span_end; unsigned long long* span_nfirst; uint32_t* span_row; uint32_t span_mask; Counters* counters;
 };
 __device__ __forceinline__ SpanArgs span_args(const Dev& d) {
-  return SpanArgs{d.user_tab, d.user_mask, d.ext_all, d.op_tab, d.op_mask, d.ds_tab, d.ds_mask, d.span_key, d.span_nstart,
+  return SpanArgs{d.user_tab, d.user_mask, d.ext_all, d.join_counts != nullptr ? d.ext_stride : 0u, d.join_pitch, d.op_tab, d.op_mask, d.ds_tab, d.ds_mask, d.span_key, d.span_nstart,
                   d.span_end, d.span_nfirst, d.span_row, d.span_mask, d.counters};
 }
 __device__ __noinline__ void span_update(const SpanArgs d, uint32_t corr, uint32_t dev, uint32_t stream, int64_t ts,
                                          int64_t dur, uint64_t ev) {
   const uint32_t idx = tab_find(d.user_tab, d.user_mask, corr);
   if (idx == 0xFFFFFFFFu) return;
-  const int64_t ext = (int64_t)d.ext_all[idx].external_id;
+  // (the table only holds positions of records that exist, so no count is looked at here)
+  const ExtRec* rec = d.ext_stride == 0u ? d.ext_all + idx
+                                         : reinterpret_cast<const ExtRec*>(reinterpret_cast<const uint8_t*>(d.ext_all) + (uint64_t)(idx / d.ext_stride) * d.join_pitch) + idx % d.ext_stride;
+  const int64_t ext = (int64_t)rec->external_id;
   if (ext != (int64_t)(int32_t)ext) return;
   const uint32_t row = tab_find(d.op_tab, d.op_mask, (uint32_t)(int32_t)ext);
   if (row == 0xFFFFFFFFu) return;

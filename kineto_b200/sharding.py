@@ -88,8 +88,40 @@ class JoinExchange:
         return self.rows, self.ext_stride, self.ops_stride, self.counts
 
 
+USER_ANNOTATION = 1  # libkineto::ActivityType::USER_ANNOTATION
+
+
+def annotation_ops(trace):
+    """The user-annotation ops of a shard as guests that carry only their name: (id, name bytes, [])."""
+    pool = trace.pool()
+    return [(int(trace.op_id[r]), pool[int(trace.op_name[r])], []) for r in np.flatnonzero(trace.op_type == USER_ANNOTATION)]
+
+
+def merge_spans(parts, op_ids, n_own_rows=None):
+    """Merges the shards' parts of the user-annotation spans (`parts[r]`: K2J.partial_spans() of shard r): per
+    (device, stream, op id) the smallest start, the largest end and the first event in (shard, event number) order.
+    `op_ids`: the id column of the LAST shard's CPU-side activities, guest rows included; every span gets the row of
+    the last activity with its id (0xFFFFFFFF when there is none).  Returns an array for K2J.append_spans."""
+    from . import api
+    merged = {}
+    for r, part in enumerate(parts):
+        for s in part:
+            key = (int(s["device"]), int(s["stream"]), int(s["op_id"]))
+            first = (r << 40) | int(s["first_event"])
+            m = merged.get(key)
+            if m is None:
+                merged[key] = [int(s["start_ns"]), int(s["end_ns"]), first]
+            else:
+                m[0], m[1], m[2] = min(m[0], int(s["start_ns"])), max(m[1], int(s["end_ns"])), min(m[2], first)
+    row_of = {int(v): i for i, v in enumerate(np.asarray(op_ids))}   # the last row with an id stays
+    out = np.zeros(len(merged), api.SPAN)
+    for k, ((dev, stream, op_id), (start, end, first)) in enumerate(merged.items()):
+        out[k] = (start, end, first, dev, stream, op_id, row_of.get(op_id, 0xFFFFFFFF))
+    return out
+
+
 def collective_ops(trace):
-    """The record_param_comms ops of a shard in a form that travels: (id, [(key bytes, type, value or bytes)])."""
+    """The record_param_comms ops of a shard in a form that travels: (id, name, [(key bytes, type, value or bytes)])."""
     from . import tracefile as tf
     pool = trace.pool()
     want = [i for i in range(len(pool)) if pool[i] == b"record_param_comms"]
@@ -101,12 +133,12 @@ def collective_ops(trace):
         for e in trace.md[int(trace.op_mdoff[row]):int(trace.op_mdoff[row + 1])]:
             text = e["type"] in (tf.MD_STRING, tf.MD_RAWJSON)
             entries.append((pool[int(e["key"])], int(e["type"]), pool[int(e["value"])] if text else int(e["value"])))
-        out.append((int(trace.op_id[row]), entries))
+        out.append((int(trace.op_id[row]), b"record_param_comms", entries))
     return out
 
 
 def with_guest_ops(trace, guests):
-    """A copy of the shard with other shards' record_param_comms ops (`collective_ops` of those shards) appended as
+    """A copy of the shard with other shards' ops (`collective_ops`, `annotation_ops` of those shards) appended as
     guest rows behind its own; returns (trace, number of guest rows) for K2J.load and K2J.set_guest_ops."""
     import copy
     from . import tracefile as tf
@@ -114,10 +146,9 @@ def with_guest_ops(trace, guests):
         return trace, 0
     t = copy.copy(trace)
     pool = trace.pool()
-    name = pool.add("record_param_comms")
     md, mdoff = [trace.md], [trace.op_mdoff]
     rows, at = [], int(trace.op_mdoff[-1])
-    for _, entries in guests:
+    for _, _, entries in guests:
         e = np.zeros(len(entries), tf.MD_ENTRY)
         for k, (key, typ, value) in enumerate(entries):
             e[k] = (pool.add(key), typ, pool.add(value) if typ in (tf.MD_STRING, tf.MD_RAWJSON) else value)
@@ -131,16 +162,16 @@ def with_guest_ops(trace, guests):
     t.op_start, t.op_end, t.op_device, t.op_resource, t.op_thread = z(trace.op_start), z(trace.op_end), z(trace.op_device), z(trace.op_resource), z(trace.op_thread)
     t.op_type, t.op_flow, t.op_flowt = z(trace.op_type), z(trace.op_flow), z(trace.op_flowt)
     t.op_id = np.concatenate([trace.op_id, np.array([g[0] for g in guests], trace.op_id.dtype)])
-    t.op_name = np.concatenate([trace.op_name, np.full(n, name, trace.op_name.dtype)])
+    t.op_name = np.concatenate([trace.op_name, np.array([pool.add(g[1]) for g in guests], trace.op_name.dtype)])
     t.set_pool(pool)
     return t, n
 
 
-def gather_collective_ops(trace, rank: int, world: int, dist):
-    """All shards' record_param_comms ops except this shard's own, in shard order (host-side collective of pickled
-    lists: such ops are few)."""
+def gather_guest_ops(trace, rank: int, world: int, dist):
+    """All shards' record_param_comms and user-annotation ops except this shard's own, in shard order (host-side
+    collective of pickled lists: such ops are few)."""
     everyone = [None] * world
-    dist.all_gather_object(everyone, collective_ops(trace))
+    dist.all_gather_object(everyone, collective_ops(trace) + annotation_ops(trace))
     return [g for r, ops in enumerate(everyone) if r != rank for g in ops]
 
 

@@ -432,6 +432,54 @@ def test_sharded_collectives_concatenate_to_the_whole(n_shards):
     assert sum(r["x_events"] for r in results) == res["x_events"]
 
 
+@pytest.mark.parametrize("gen,n_shards", [
+    (lambda: synth.gen_kernel_launches(60_000, seed=305, pool_size=300, user_annotations=40, buffer_bytes=1 << 20), 3),
+    (lambda: helpers.rebuffer(cases.annotation_trace(), 5), 2),
+], ids=["launches", "annotation_fixture"])
+def test_sharded_user_annotations_concatenate_to_the_whole(gen, n_shards):
+    """A gpu_user_annotation span covers the GPU activities correlated to its annotation op wherever they are in the
+    trace.  Every shard reports its part of every span, the parts are merged, and the last shard writes the merged
+    spans behind its text (k2j_partial_spans, k2j_append_spans): the texts concatenate to the whole trace's text."""
+    import torch
+    from kineto_b200 import api, sharding
+    t = gen()
+    whole, res = gpu_run(t)
+    assert whole.count(b'"gpu_user_annotation"') > 3
+    subs = helpers.cut_into_shards(t, n_shards)
+    guests_of = [sharding.annotation_ops(sub) for sub in subs]
+    ctxs = [api.K2J(0) for _ in subs]
+    try:
+        infos, shards = [], []
+        for r, (c, sub) in enumerate(zip(ctxs, subs)):
+            shard, n_guests = sharding.with_guest_ops(sub, [g for q, ops in enumerate(guests_of) if q != r for g in ops])
+            shards.append(shard)
+            c.load(shard)
+            c.set_guest_ops(n_guests)
+            infos.append(c.segment())
+        ext = torch.cat([api.device_view(i.external_records, int(i.n_external) * 2, "<i8").clone() for i in infos])
+        ops = torch.cat([api.device_view(i.op_ids, int(i.n_ops), "<i4").clone() for i in infos])
+        torch.cuda.synchronize()
+        parts, results, spans, begin = [], [], [], 0
+        for c, i in zip(ctxs, infos):
+            c.set_global_join(ext, ext.numel() // 2, begin, ops, ops.numel())
+            begin += int(i.n_external)
+            results.append(c.emit())
+            spans.append(c.partial_spans())
+            parts.append(c.copy_output().tobytes())
+        assert sum(len(p) for p in spans) > 3
+        merged = sharding.merge_spans(spans, shards[-1].op_id)
+        added = ctxs[-1].append_spans(merged)
+        last = ctxs[-1].copy_output().tobytes()
+        assert len(last) == len(parts[-1]) + added and last[:len(parts[-1])] == parts[-1]
+        parts[-1] = last
+    finally:
+        for c in ctxs:
+            c.close()
+    got = b"".join(p[:r["ops_bytes"]] for p, r in zip(parts, results)) + b"".join(p[r["ops_bytes"]:] for p, r in zip(parts, results))
+    assert got == whole, helpers.first_diff(whole, got)
+    assert sum(r["x_events"] for r in results) + len(merged) == res["x_events"]
+
+
 @pytest.mark.skipif(not helpers.have_ref(), reason="reference build (oracle/_ref) not present")
 def test_full_size_against_reference():
     """The benchmark workload at a quarter of its size, byte for byte against the unmodified reference."""
