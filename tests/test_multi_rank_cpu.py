@@ -106,3 +106,67 @@ def test_join_key_exchange_with_ragged_shards(tmp_path):
     port = 31500 + (os.getpid() % 2000)
     mp.spawn(_uneven_main, args=(port, str(tmp_path)), nprocs=WORLD, join=True)
     assert all(int(np.load(str(tmp_path / ("ok%d.npy" % r)))[0]) == 1 for r in range(WORLD))
+
+
+def _guest_rank_main(rank, port, tmp):
+    """Two gloo ranks exchange what the cross-shard record families need beyond the join keys."""
+    import cases
+    from kineto_b200 import api
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(WORLD))
+    dist.init_process_group("gloo", rank=rank, world_size=WORLD)
+    try:
+        whole = helpers.rebuffer(cases.collective_trace(60, seed=57), 11)
+        sub = helpers.cut_into_shards(whole, WORLD)[rank]
+        guests = sharding.gather_guest_ops(sub, rank, WORLD, dist)
+        other = helpers.cut_into_shards(whole, WORLD)[1 - rank]
+        assert guests == sharding.collective_ops(other) + sharding.annotation_ops(other) and guests
+        shard, n = sharding.with_guest_ops(sub, guests)
+        assert n == len(guests) and shard.n_ops == sub.n_ops + n and len(shard.op_mdoff) == shard.n_ops + 1
+        pool = shard.pool()
+        for k, (op_id, name, entries) in enumerate(guests):
+            row = sub.n_ops + k
+            assert int(shard.op_id[row]) == op_id and pool[int(shard.op_name[row])] == name
+            got = shard.md[int(shard.op_mdoff[row]):int(shard.op_mdoff[row + 1])]
+            assert [(pool[int(e["key"])], int(e["type"])) for e in got] == [(key, typ) for key, typ, _ in entries]
+            for e, (_, typ, value) in zip(got, entries):
+                assert (pool[int(e["value"])] if typ in (tf.MD_STRING, tf.MD_RAWJSON) else int(e["value"])) == value
+        # the shard's own rows and strings are untouched
+        assert np.array_equal(shard.op_id[:sub.n_ops], sub.op_id) and np.array_equal(shard.md[:len(sub.md)], sub.md)
+        assert np.array_equal(shard.pool_data[:len(sub.pool_data)], sub.pool_data)
+        # spans: every rank reports parts, the merge is the same on every rank
+        part = np.zeros(2, api.SPAN)
+        part[0] = (100 + rank, 500 + 10 * rank, 7 - rank, 0, 20, 900, 0)
+        part[1] = (50, 60, 3, rank, 21, 901 + rank, 0)
+        everyone = [None] * WORLD
+        dist.all_gather_object(everyone, part)
+        merged = sharding.merge_spans(everyone, np.array([5, 900, 901, 900], np.int32))
+        by_key = {(int(m["device"]), int(m["stream"]), int(m["op_id"])): m for m in merged}
+        assert len(merged) == 3
+        m = by_key[(0, 20, 900)]
+        assert (int(m["start_ns"]), int(m["end_ns"]), int(m["first_event"]), int(m["op_row"])) == (100, 510, 7, 3)
+        assert int(by_key[(0, 21, 901)]["op_row"]) == 2 and int(by_key[(1, 21, 902)]["op_row"]) == 0xFFFFFFFF
+        assert int(by_key[(1, 21, 902)]["first_event"]) == (1 << 40) | 3
+        open(os.path.join(tmp, "guest_ok%d" % rank), "w").write("1")
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_exchange_guest_ops_and_spans(tmp_path):
+    port = 29300 + (os.getpid() % 500)
+    mp.spawn(_guest_rank_main, args=(port, str(tmp_path)), nprocs=WORLD, join=True)
+    assert all(os.path.exists(str(tmp_path / ("guest_ok%d" % r))) for r in range(WORLD))
+
+
+def test_guest_records_are_laid_out_around_the_shards_own_buffers():
+    """sharding.with_guest_records: lower shards' lookup records in front, higher shards' behind, the shard's own
+    buffers moved by the bytes in front, and the two boundaries for k2j_set_guest_ranges."""
+    own = torch.arange(64, dtype=torch.uint8)
+    blobs = [torch.full((16,), 1, dtype=torch.uint8), torch.zeros(0, dtype=torch.uint8), torch.full((8,), 3, dtype=torch.uint8),
+             torch.full((24,), 4, dtype=torch.uint8)]
+    data, table, front_end, back_begin = sharding.with_guest_records(own, np.array([8, 16, 40, 24], np.uint64), blobs, 1)
+    assert (front_end, back_begin) == (16, 80) and data.numel() == 16 + 64 + 8 + 24
+    assert table.tolist() == [0, 16, 24, 16, 56, 24, 80, 8, 88, 24]
+    assert data[:16].eq(1).all() and torch.equal(data[16:80], own) and data[80:88].eq(3).all() and data[88:].eq(4).all()
+    data, table, front_end, back_begin = sharding.with_guest_records(own, np.array([0, 64], np.uint64), [blobs[1], blobs[1]], 0)
+    assert data is own and table.tolist() == [0, 64] and (front_end, back_begin) == (0, 64)
