@@ -275,6 +275,21 @@ k2j_status k2j_set_global_join(k2j_ctx* ctx, const void* external_all, uint64_t 
 k2j_status k2j_set_global_join_rows(k2j_ctx* ctx, const void* ext_rows, uint64_t ext_stride, const int32_t* op_id_rows,
                                     uint64_t ops_stride, uint64_t row_pitch_bytes, const uint64_t* counts, uint32_t world,
                                     uint32_t rank);
+/* Sending join keys only where they can be wanted.  With k2j_set_global_join_rows a shard reads its OWN records
+ * and ids from its own arrays, never from its row, so the row a shard contributes only has to hold what other
+ * shards can want.  k2j_join_need_bits (after k2j_segment) fills `bits` (device memory, n_bits a power of two,
+ * the same on every shard; about 8 bits per GPU-side record keep false hits near 2 %) with the filter of the
+ * correlation ids this shard's events carry.  The caller all-gathers the filters; k2j_filter_join_keys then
+ * writes to `out_records` (device memory, room for `capacity` >= this shard's n_external records), in their order,
+ * those of this shard's EXTERNAL_CORRELATION records whose correlation id hits the filter of at least one OTHER
+ * shard (`need_rows`: the gathered filters, row_pitch_bytes apart), and their number to `n_out` (device memory, on
+ * the context's stream).  These records, followed by the CPU-op ids, are the row to all-gather: positions still
+ * grow along a shard's records, which is all that "the last record of a correlation id wins" needs, and counts[2 r]
+ * is the number of records row r holds.  Nothing of the result changes; the bytes a rank receives no longer grow
+ * with the number of shards times the shard size.  No reference counterpart. */
+k2j_status k2j_join_need_bits(k2j_ctx* ctx, void* bits, uint64_t n_bits);
+k2j_status k2j_filter_join_keys(k2j_ctx* ctx, const void* need_rows, uint64_t row_pitch_bytes, uint64_t n_bits, uint32_t world,
+                                uint32_t rank, void* out_records, uint64_t capacity, uint64_t* n_out);
 k2j_status k2j_emit(k2j_ctx* ctx, k2j_result* result);
 
 /* k2j_emit for traces whose text should not be held whole on the device: the text is produced in slabs of

@@ -67,7 +67,7 @@ class SegmentInfo(C.Structure):
 SPAN = np.dtype([("start_ns", "<i8"), ("end_ns", "<i8"), ("first_event", "<u8"), ("device", "<u4"), ("stream", "<u4"),
                  ("op_id", "<i4"), ("op_row", "<u4")])  # k2j_span
 
-EXPORTS = ["k2j_set_global_join_rows", "k2j_emit_to_host", "k2j_emit_to_fd", "k2j_exclusive_scan_u32", "k2j_exclusive_scan_u32_noalloc", "k2j_segment", "k2j_set_global_join", "k2j_emit", "k2j_create", "k2j_destroy", "k2j_last_error", "k2j_set_params", "k2j_set_strings",
+EXPORTS = ["k2j_set_global_join_rows", "k2j_join_need_bits", "k2j_filter_join_keys", "k2j_emit_to_host", "k2j_emit_to_fd", "k2j_exclusive_scan_u32", "k2j_exclusive_scan_u32_noalloc", "k2j_segment", "k2j_set_global_join", "k2j_emit", "k2j_create", "k2j_destroy", "k2j_last_error", "k2j_set_params", "k2j_set_strings",
            "k2j_set_cbid_names", "k2j_set_thread_map", "k2j_set_ops", "k2j_set_cupti", "k2j_run", "k2j_output",
            "k2j_copy_output", "k2j_copy_output_async", "k2j_write_output", "k2j_write_output_at", "k2j_synchronize", "k2j_version",
            "k2j_export_lookup_records", "k2j_set_guest_ranges", "k2j_set_guest_ops", "k2j_partial_spans", "k2j_append_spans", "k2j_names_create", "k2j_names_destroy", "k2j_names_intern", "k2j_names_pool", "k2j_intern_kernel_names"]
@@ -99,6 +99,8 @@ def load_library():
     lib.k2j_segment.argtypes = [vp, C.POINTER(SegmentInfo)]
     lib.k2j_set_global_join.argtypes = [vp, vp, C.c_uint64, C.c_uint64, vp, C.c_uint64]
     lib.k2j_set_global_join_rows.argtypes = [vp, vp, C.c_uint64, vp, C.c_uint64, C.c_uint64, vp, C.c_uint32, C.c_uint32]
+    lib.k2j_join_need_bits.argtypes = [vp, vp, C.c_uint64]
+    lib.k2j_filter_join_keys.argtypes = [vp, vp, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint32, vp, C.c_uint64, vp]
     lib.k2j_emit.argtypes = [vp, C.POINTER(Result)]
     lib.k2j_emit_to_host.argtypes = [vp, vp, C.c_uint64, C.c_uint64, C.POINTER(Result)]
     lib.k2j_emit_to_fd.argtypes = [vp, C.c_int, C.c_uint64, C.POINTER(Result)]
@@ -278,13 +280,26 @@ class K2J:
         self._check(self.lib.k2j_set_global_join(self.h, _ptr(ext_all), n_ext_all, own_begin, _ptr(op_ids_all),
                                                  n_ops_all))
 
-    def set_global_join_rows(self, rows, ext_stride: int, ops_stride: int, counts, world: int, rank: int):
+    def set_global_join_rows(self, rows, ext_stride: int, ops_stride: int, counts, world: int, rank: int, ext_capacity: int | None = None):
         """`rows`: the int64 device tensor an all-gather of per-shard rows produced (sharding.JoinExchange): every row
-        holds ext_stride 16-byte records followed by ops_stride ids; `counts`: int64 device tensor, 2 per shard."""
+        holds room for `ext_capacity` 16-byte records (default: ext_stride, the index stride) followed by ops_stride
+        ids; `counts`: int64 device tensor, 2 per shard."""
         self._keep["g_rows"], self._keep["g_counts"] = rows, counts
         pitch = rows.numel() * 8 // world
-        self._check(self.lib.k2j_set_global_join_rows(self.h, rows.data_ptr(), ext_stride, rows.data_ptr() + ext_stride * 16,
+        cap = ext_stride if ext_capacity is None else ext_capacity
+        self._check(self.lib.k2j_set_global_join_rows(self.h, rows.data_ptr(), ext_stride, rows.data_ptr() + cap * 16,
                                                       ops_stride, pitch, counts.data_ptr(), world, rank))
+
+    def join_need_bits(self, bits):
+        """Fills the uint8 device tensor `bits` (a power-of-two number of bits) with this shard's filter."""
+        self._check(self.lib.k2j_join_need_bits(self.h, bits.data_ptr(), bits.numel() * 8))
+
+    def filter_join_keys(self, need_rows, world: int, rank: int, out_records, n_out):
+        """`need_rows`: uint8 device tensor, the shards' filters one after the other; `out_records`: int64 device tensor
+        with room for this shard's records (2 words each); `n_out`: int64 device tensor of one element."""
+        pitch = need_rows.numel() // world
+        self._check(self.lib.k2j_filter_join_keys(self.h, need_rows.data_ptr(), pitch, pitch * 8, world, rank, out_records.data_ptr(),
+                                                  out_records.numel() // 2, n_out.data_ptr()))
 
     def emit(self) -> dict:
         r = Result()

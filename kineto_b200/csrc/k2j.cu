@@ -104,7 +104,7 @@ struct k2j_ctx {
   DevBuf exp_keys, exp_first, exp_list, exp_out, coll_tab;
   uint64_t n_guest_ops = 0;                                           // k2j_set_guest_ops
   std::vector<SpanRec> partial_spans;                                 // sharded runs: this shard's parts of the user-annotation spans
-  uint32_t g_ext_stride = 0, g_ops_stride = 0, g_world = 1; uint64_t g_pitch = 0; const uint64_t* g_counts = nullptr;  // rows of an all-gather
+  uint32_t g_ext_stride = 0, g_ops_stride = 0, g_world = 1, g_rank = 0; uint64_t g_pitch = 0; const uint64_t* g_counts = nullptr;  // rows of an all-gather
 };
 
 namespace {
@@ -629,7 +629,7 @@ k2j_status k2j_set_global_join(k2j_ctx* c, const void* ext_all, uint64_t n_ext_a
     return fail(c, K2J_ERR_INVALID_ARGUMENT, "gathered join arrays out of range");
   c->g_ext = ext_all; c->g_n_ext = n_ext_all; c->g_own_begin = own_begin;
   c->g_op_ids = op_ids_all; c->g_n_ops = n_ops_all;
-  c->g_counts = nullptr; c->g_world = 1;
+  c->g_counts = nullptr; c->g_world = 1; c->g_rank = 0;
   c->have_global_join = true;
   return K2J_OK;
 }
@@ -647,8 +647,56 @@ k2j_status k2j_set_global_join_rows(k2j_ctx* c, const void* ext_rows, uint64_t e
   c->g_ext = ext_rows; c->g_n_ext = ext_stride * world; c->g_own_begin = ext_stride * rank;
   c->g_op_ids = op_id_rows; c->g_n_ops = ops_stride * world;
   c->g_ext_stride = (uint32_t)ext_stride; c->g_ops_stride = (uint32_t)ops_stride; c->g_pitch = row_pitch_bytes;
-  c->g_counts = counts; c->g_world = world;
+  c->g_counts = counts; c->g_world = world; c->g_rank = rank;
   c->have_global_join = true;
+  return K2J_OK;
+}
+
+k2j_status k2j_join_need_bits(k2j_ctx* c, void* bits, uint64_t n_bits) {
+  if (!c) return K2J_ERR_INVALID_ARGUMENT;
+  if (!c->segmented) return fail(c, K2J_ERR_STATE, "k2j_segment has not run");
+  if (!bits || !is_device_ptr(bits) || n_bits < 1024 || (n_bits & (n_bits - 1)) || n_bits > (1ull << 32))
+    return fail(c, K2J_ERR_INVALID_ARGUMENT, "need bits: device memory and a power of two between 2^10 and 2^32 bits");
+  K2J_CUDA(c, cudaSetDevice(c->device));
+  cudaStream_t s = c->stream;
+  Dev d = c->d;
+  d.need_corr = static_cast<uint32_t*>(bits); d.need_corr_mask = (uint32_t)(n_bits - 1);
+  K2J_CUDA(c, cudaMemsetAsync(bits, 0, n_bits / 8, s));
+  if (d.ops_begin) { k_mark_corr<<<(uint32_t)((d.ops_begin + 255) / 256), 256, 0, s>>>(d); c->launches++; }
+  K2J_CUDA(c, cudaGetLastError());
+  return K2J_OK;
+}
+
+k2j_status k2j_filter_join_keys(k2j_ctx* c, const void* need_rows, uint64_t row_pitch_bytes, uint64_t n_bits, uint32_t world, uint32_t rank,
+                                void* out_records, uint64_t capacity, uint64_t* n_out) {
+  if (!c) return K2J_ERR_INVALID_ARGUMENT;
+  if (!c->segmented) return fail(c, K2J_ERR_STATE, "k2j_segment has not run");
+  const uint64_t n = c->totals[C_EXT];
+  if (!need_rows || !is_device_ptr(need_rows) || !n_out || !is_device_ptr(n_out) || world == 0 || rank >= world || n_bits < 1024 ||
+      (n_bits & (n_bits - 1)) || n_bits > (1ull << 32) || (row_pitch_bytes & 3) || row_pitch_bytes < n_bits / 8 ||
+      (n && (!out_records || !is_device_ptr(out_records))) || capacity < n)
+    return fail(c, K2J_ERR_INVALID_ARGUMENT, "filter: device memory, a power-of-two filter size, room for every record of this shard");
+  K2J_CUDA(c, cudaSetDevice(c->device));
+  cudaStream_t s = c->stream;
+  const Dev& d = c->d;
+  const uint64_t n_words = n_bits / 32;
+  K2J_CUDA(c, c->need_corr.reserve(n_bits / 8));            // scratch: the union of the other shards' filters
+  K2J_CUDA(c, c->ev_size.reserve(std::max<uint64_t>(1, n) * 4));   // scratch: marks and their scan (free between segment and emit)
+  K2J_CUDA(c, c->ev_off.reserve(std::max<uint64_t>(1, n) * 8));
+  k_union_needs<<<(uint32_t)((n_words + 255) / 256), 256, 0, s>>>(static_cast<const uint32_t*>(need_rows), row_pitch_bytes / 4, world, rank, n_words,
+                                                                c->need_corr.as<uint32_t>());
+  c->launches++;
+  if (n) {
+    k_flag_wanted<<<(uint32_t)((n + 255) / 256), 256, 0, s>>>(d, c->need_corr.as<uint32_t>(), (uint32_t)(n_bits - 1), n, c->ev_size.as<uint32_t>());
+    c->launches++;
+    K2J_CUDA(c, cudaGetLastError());
+    k2j_status st = run_scan(c, c->ev_size.as<uint32_t>(), n, 1, c->ev_off.as<uint64_t>(), c->scan_totals.as<uint64_t>() + 27, &c->launches);
+    if (st) return st;
+    k_take_wanted<<<(uint32_t)((n + 255) / 256), 256, 0, s>>>(d, c->ev_size.as<uint32_t>(), c->ev_off.as<uint64_t>(), n, static_cast<ExtRec*>(out_records));
+    c->launches++;
+    K2J_CUDA(c, cudaMemcpyAsync(n_out, c->scan_totals.as<uint64_t>() + 27, 8, cudaMemcpyDeviceToDevice, s));
+  } else K2J_CUDA(c, cudaMemsetAsync(n_out, 0, 8, s));
+  K2J_CUDA(c, cudaGetLastError());
   return K2J_OK;
 }
 
@@ -859,11 +907,12 @@ k2j_status emit_core(k2j_ctx* c, k2j_result* res, const TileSink& sink) {
     d.ext_all = (const ExtRec*)c->g_ext; d.n_ext_all = c->g_n_ext;
     d.join_op_ids = c->g_op_ids; d.n_join_ops = c->g_n_ops;
     d.join_counts = c->g_counts; d.ext_stride = c->g_ext_stride; d.ops_stride = c->g_ops_stride; d.join_pitch = c->g_pitch;
+    d.own_rank = c->g_counts ? c->g_rank : 0xFFFFFFFFu; d.own_n_ext = totals[C_EXT]; d.own_n_ops = c->n_ops - c->n_guest_ops;
     own_begin = c->g_own_begin; own_end = own_begin + totals[C_EXT];
   } else {
     d.ext_all = d.ext_local; d.n_ext_all = totals[C_EXT];
     d.join_op_ids = d.op_id; d.n_join_ops = c->n_ops - c->n_guest_ops;
-    d.join_counts = nullptr;
+    d.join_counts = nullptr; d.own_rank = 0xFFFFFFFFu;
   }
   K2J_CUDA(c, c->ev_size.reserve(std::max<uint64_t>(1, d.n_events) * 4));
   K2J_CUDA(c, c->ev_off.reserve(std::max<uint64_t>(1, d.n_events) * 8));
@@ -873,7 +922,8 @@ k2j_status emit_core(k2j_ctx* c, k2j_result* res, const TileSink& sink) {
   // are sized by the shard: its events, plus the share of foreign keys the marking lets through by chance.
   const bool filter = c->have_global_join;
   // (a filtered table holds at most the bound below, usually about half of it: 1.4 slots per possible key are enough)
-  const uint32_t corr_cap = filter ? pow2_at_least(14 * std::min<uint64_t>(d.n_ext_all, n_gpu_events + d.n_ext_all / 16 + 1024) / 10 + 2)
+  // (the shard's own records go in untested)
+  const uint32_t corr_cap = filter ? pow2_at_least(14 * std::min<uint64_t>(d.n_ext_all, totals[C_EXT] + n_gpu_events + d.n_ext_all / 16 + 1024) / 10 + 2)
                                    : pow2_at_least(2 * d.n_ext_all + 2);
   const uint32_t op_cap = filter ? pow2_at_least(14 * std::min<uint64_t>(d.n_join_ops, n_gpu_events + d.n_join_ops / 16 + 1024) / 10 + 2)
                                  : pow2_at_least(2 * d.n_join_ops + 2);

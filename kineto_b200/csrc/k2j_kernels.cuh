@@ -145,6 +145,9 @@ struct Dev {
   ExtRec* ext_local; const ExtRec* ext_all; uint64_t n_ext_all;
   const int32_t* join_op_ids; uint64_t n_join_ops;  // CPU-op ids the join sees (local or gathered)
   uint32_t ext_stride, ops_stride; uint64_t join_pitch; const uint64_t* join_counts;
+  // with rows, this shard's own records and ids are read from its own arrays (ext_local, op_id), never from its row: the
+  // rows may then hold, for every OTHER shard, only the records some shard other than their owner can want
+  uint32_t own_rank; uint64_t own_n_ext, own_n_ops;
   // sharded runs: bit sets (by hash) of the correlation ids this shard's events carry and of the CPU-op ids
   // the matching records name; keys outside them are not inserted.  nullptr: insert everything.
   uint32_t* need_corr; uint32_t need_corr_mask; uint32_t* need_op; uint32_t need_op_mask;
@@ -201,6 +204,7 @@ __device__ __forceinline__ uint64_t esc_md_pos(const Dev& d, uint32_t id) { retu
 __device__ __forceinline__ bool ext_at(const Dev& d, uint64_t i, ExtRec* out) {
   if (d.join_counts == nullptr) { *out = d.ext_all[i]; return true; }
   const uint32_t r = (uint32_t)(i / d.ext_stride), j = (uint32_t)(i - (uint64_t)r * d.ext_stride);
+  if (r == d.own_rank) { if ((uint64_t)j >= d.own_n_ext) return false; *out = d.ext_local[j]; return true; }
   if ((uint64_t)j >= d.join_counts[2 * r]) return false;
   *out = *reinterpret_cast<const ExtRec*>(reinterpret_cast<const uint8_t*>(d.ext_all) + (uint64_t)r * d.join_pitch + (uint64_t)j * sizeof(ExtRec));
   return true;
@@ -208,6 +212,7 @@ __device__ __forceinline__ bool ext_at(const Dev& d, uint64_t i, ExtRec* out) {
 __device__ __forceinline__ bool op_id_at(const Dev& d, uint64_t i, uint32_t* out) {
   if (d.join_counts == nullptr) { *out = (uint32_t)d.join_op_ids[i]; return true; }
   const uint32_t r = (uint32_t)(i / d.ops_stride), j = (uint32_t)(i - (uint64_t)r * d.ops_stride);
+  if (r == d.own_rank) { if ((uint64_t)j >= d.own_n_ops) return false; *out = (uint32_t)d.op_id[j]; return true; }
   if ((uint64_t)j >= d.join_counts[2 * r + 1]) return false;
   *out = (uint32_t)*reinterpret_cast<const int32_t*>(reinterpret_cast<const uint8_t*>(d.join_op_ids) + (uint64_t)r * d.join_pitch + (uint64_t)j * 4u);
   return true;
@@ -618,6 +623,29 @@ __global__ void k_mark_corr(Dev d) {
   const uint8_t* r = d.cupti + (uint64_t)d.work_slot[i] * 8;
   const int off = cls == C_API ? 32 : cls == C_KERNEL ? 92 : cls == C_MEMCPY2 ? 60 : cls == C_CUDAEVENT ? 4 : (cls == C_SYNC || cls == C_WAIT) ? 24 : 44;
   bit_set(d.need_corr, d.need_corr_mask, *reinterpret_cast<const uint32_t*>(r + off));
+}
+// ---- sending join keys only where they can be wanted ----
+// Every shard publishes the filter k_mark_corr fills (the correlation ids its events carry).  k_union_needs ORs the
+// other shards' filters; k_flag_wanted marks this shard's EXTERNAL_CORRELATION records (kinds the join uses) whose
+// correlation id hits that union; after a scan of the marks k_take_wanted copies them out in their order, which is
+// all that "the last record of a correlation id wins" needs: positions only have to grow along a shard's records.
+__global__ void k_union_needs(const uint32_t* rows, uint64_t pitch_words, uint32_t world, uint32_t rank, uint64_t n_words, uint32_t* out) {
+  const uint64_t w = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (w >= n_words) return;
+  uint32_t v = 0u;
+  for (uint32_t r = 0; r < world; r++) if (r != rank) v |= rows[(uint64_t)r * pitch_words + w];
+  out[w] = v;
+}
+__global__ void k_flag_wanted(Dev d, const uint32_t* wanted, uint32_t mask, uint64_t n, uint32_t* flags) {
+  const uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= n) return;
+  const ExtRec e = d.ext_local[j];
+  flags[j] = (e.external_kind == 3u || e.external_kind == 4u) && bit_test(wanted, mask, e.correlation_id) ? 1u : 0u;
+}
+__global__ void k_take_wanted(Dev d, const uint32_t* flags, const uint64_t* at, uint64_t n, ExtRec* out) {
+  const uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= n || flags[j] == 0u) return;
+  out[at[j]] = d.ext_local[j];
 }
 // Is any CPU-side activity of this run named record_param_comms (bit 0: kernel events look at their linked op's
 // name only if so), is any an instant event (bit 1)?
@@ -1089,12 +1117,13 @@ __device__ __forceinline__ void linked_op(const Dev& d, uint32_t corr, unsigned 
 // make every thread of the size pass copy that block (about 1 KB) into local memory at kernel entry.
 struct SpanArgs {
   const unsigned long long* user_tab; uint32_t user_mask; const ExtRec* ext_all; uint32_t ext_stride; uint64_t join_pitch;  // rows of an all-gather: see Dev
+  const ExtRec* ext_local; uint32_t own_rank;
   const unsigned long long* op_tab; uint32_t op_mask;
   unsigned long long* ds_tab; uint32_t ds_mask; unsigned long long* span_key; unsigned long long* span_nstart;
   unsigned long long* span_end; unsigned long long* span_nfirst; uint32_t* span_row; uint32_t span_mask; Counters* counters;
 };
 __device__ __forceinline__ SpanArgs span_args(const Dev& d) {
-  return SpanArgs{d.user_tab, d.user_mask, d.ext_all, d.join_counts != nullptr ? d.ext_stride : 0u, d.join_pitch, d.op_tab, d.op_mask, d.ds_tab, d.ds_mask, d.span_key, d.span_nstart,
+  return SpanArgs{d.user_tab, d.user_mask, d.ext_all, d.join_counts != nullptr ? d.ext_stride : 0u, d.join_pitch, d.ext_local, d.own_rank, d.op_tab, d.op_mask, d.ds_tab, d.ds_mask, d.span_key, d.span_nstart,
                   d.span_end, d.span_nfirst, d.span_row, d.span_mask, d.counters};
 }
 __device__ __noinline__ void span_update(const SpanArgs d, uint32_t corr, uint32_t dev, uint32_t stream, int64_t ts,
@@ -1103,7 +1132,8 @@ __device__ __noinline__ void span_update(const SpanArgs d, uint32_t corr, uint32
   if (idx == 0xFFFFFFFFu) return;
   // (the table only holds positions of records that exist, so no count is looked at here)
   const ExtRec* rec = d.ext_stride == 0u ? d.ext_all + idx
-                                         : reinterpret_cast<const ExtRec*>(reinterpret_cast<const uint8_t*>(d.ext_all) + (uint64_t)(idx / d.ext_stride) * d.join_pitch) + idx % d.ext_stride;
+                      : idx / d.ext_stride == d.own_rank ? d.ext_local + idx % d.ext_stride
+                      : reinterpret_cast<const ExtRec*>(reinterpret_cast<const uint8_t*>(d.ext_all) + (uint64_t)(idx / d.ext_stride) * d.join_pitch) + idx % d.ext_stride;
   const int64_t ext = (int64_t)rec->external_id;
   if (ext != (int64_t)(int32_t)ext) return;
   const uint32_t row = tab_find(d.op_tab, d.op_mask, (uint32_t)(int32_t)ext);

@@ -220,6 +220,64 @@ def gather_lookup_records(ctx, rank: int, world: int, dist, device):
     return [everyone[r * pad:r * pad + sizes[r]] for r in range(world)]
 
 
+class FilteredJoinExchange:
+    """The exchange that sends join keys only where they can be wanted.  Per step: every rank all-gathers the filter
+    of the correlation ids its events carry (K2J.join_need_bits, a few bits per event), keeps of its own
+    EXTERNAL_CORRELATION records those that hit another rank's filter (K2J.filter_join_keys, in order), and the
+    ranks all-gather rows of [kept records | CPU-op ids] sized by the largest kept count (one host round trip for
+    that count).  The library reads a rank's own records from the rank's own arrays, so nothing else is needed."""
+
+    def __init__(self, rank: int, world: int, dist, device):
+        self.rank, self.world, self.dist, self.device = rank, world, dist, device
+        self.ext_stride = 0
+        self.cap = 0
+
+    def _agree(self, n_ext: int, n_ops: int, n_records: int):
+        import torch
+        t = torch.tensor([n_ext, n_ops, n_records], dtype=torch.int64, device=self.device)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        m = t.tolist()
+        self.ext_stride = max(1, int(m[0] * 1.02) + 16)                 # index stride: room for a shard's own records
+        self.ops_stride = (max(1, int(m[1] * 1.02) + 16) + 1) & ~1
+        n_bits = 1 << 20
+        while n_bits < 8 * m[2] and n_bits < (1 << 32):
+            n_bits *= 2
+        self.bits = torch.empty(n_bits // 8, dtype=torch.uint8, device=self.device)
+        self.need = torch.empty(n_bits // 8 * self.world, dtype=torch.uint8, device=self.device)
+        self.kept = torch.empty(self.ext_stride * 2, dtype=torch.int64, device=self.device)
+        self.mine = torch.zeros(2, dtype=torch.int64, device=self.device)
+        self.counts = torch.empty(2 * self.world, dtype=torch.int64, device=self.device)
+
+    def gather(self, ctx, info):
+        """`info`: what K2J.segment() returned.  Returns (rows, ext_stride, ops_stride, counts, ext_capacity) for
+        K2J.set_global_join_rows."""
+        import torch
+        from . import api
+        n_ext, n_ops = int(info.n_external), int(info.n_ops)
+        if self.ext_stride == 0:
+            self._agree(n_ext, n_ops, int(info.n_records))
+        elif n_ext > self.ext_stride or n_ops > self.ops_stride:
+            raise ValueError("this shard outgrew the sizes the ranks agreed on: create a new FilteredJoinExchange on every rank")
+        ctx.join_need_bits(self.bits)
+        self.dist.all_gather_into_tensor(self.need, self.bits)
+        ctx.filter_join_keys(self.need, self.world, self.rank, self.kept, self.mine[:1])
+        self.mine[1] = n_ops
+        self.dist.all_gather_into_tensor(self.counts, self.mine)
+        cap = int(self.counts[0::2].max().item())                       # the one host round trip of the exchange
+        cap = max(1, cap)
+        if cap > self.cap:                                              # grow-only row buffers
+            self.cap = int(cap * 1.25) + 16
+            words = self.cap * 2 + self.ops_stride // 2
+            self.row = torch.zeros(words, dtype=torch.int64, device=self.device)
+            self.rows = torch.empty(words * self.world, dtype=torch.int64, device=self.device)
+        n_kept = int(self.counts[2 * self.rank].item())
+        self.row[:n_kept * 2] = self.kept[:n_kept * 2]
+        ops_local = api.device_view(info.op_ids, n_ops, "<i4", self.device)
+        self.row[self.cap * 2:].view(ops_local.dtype)[:n_ops] = ops_local
+        self.dist.all_gather_into_tensor(self.rows, self.row)
+        return self.rows, self.ext_stride, self.ops_stride, self.counts, self.cap
+
+
 def output_bases(out_bytes: int, rank: int, world: int, dist, device):
     """All-gathers the per-shard text sizes; returns (this shard's byte offset in the whole file's
     activities section, total bytes).  CPU-op events of all shards precede GPU events in the

@@ -323,6 +323,47 @@ def test_sharded_runs_concatenate_to_the_whole(n_shards):
                 res_rows = c.emit()
                 assert c.copy_output().tobytes() == parts[r], "rows of shard %d" % r
                 assert res_rows["invalid_external_correlation_events"] == 0
+            # and with rows that hold, per shard, only the records another shard can want (k2j_join_need_bits,
+            # k2j_filter_join_keys; sharding.FilteredJoinExchange does this with collectives)
+            n_bits = 1 << 24
+            need = torch.empty(n_bits // 8 * n_shards, dtype=torch.uint8, device="cuda:0")
+            for r, c in enumerate(ctxs):
+                c.segment()
+                c.join_need_bits(need[r * (n_bits // 8):(r + 1) * (n_bits // 8)])
+            kept, n_kept = [], []
+            for r, (c, i) in enumerate(zip(ctxs, infos)):
+                out = torch.empty(max(1, int(i.n_external)) * 2, dtype=torch.int64, device="cuda:0")
+                n_out = torch.zeros(1, dtype=torch.int64, device="cuda:0")
+                c.filter_join_keys(need, n_shards, r, out, n_out)
+                c.synchronize()
+                kept.append(out)
+                n_kept.append(int(n_out.item()))
+            assert all(0 < k <= int(i.n_external) for k, i in zip(n_kept, infos))
+            cap = max(n_kept) + 3
+            words = cap * 2 + ops_stride // 2
+            rows = torch.zeros(words * n_shards, dtype=torch.int64, device="cuda:0")
+            pos_o = 0
+            for r, i in enumerate(infos):
+                no = int(i.n_ops)
+                row = rows[r * words:(r + 1) * words]
+                row[:n_kept[r] * 2] = kept[r][:n_kept[r] * 2]
+                row[cap * 2:].view(torch.int32)[:no] = ops[pos_o:pos_o + no]
+                counts[2 * r], counts[2 * r + 1] = n_kept[r], no
+                pos_o += no
+            saved = rows[0:8].clone()
+            rows[0:8] = -1  # a shard's own row is never read: what it holds does not matter
+            torch.cuda.synchronize()
+            for r, c in enumerate(ctxs):
+                if r == 0:
+                    c.set_global_join_rows(rows, ext_stride, ops_stride, counts, n_shards, r, ext_capacity=cap)
+                    assert c.emit()["x_events"] == c.result["x_events"] and c.copy_output().tobytes() == parts[0], "filtered rows of shard 0"
+            rows[0:8] = saved
+            torch.cuda.synchronize()
+            for r, c in enumerate(ctxs):
+                if r > 0:
+                    c.set_global_join_rows(rows, ext_stride, ops_stride, counts, n_shards, r, ext_capacity=cap)
+                    c.emit()
+                    assert c.copy_output().tobytes() == parts[r], "filtered rows of shard %d" % r
         finally:
             for c in ctxs:
                 c.close()
