@@ -73,6 +73,9 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
     ap.add_argument("--no-save-e2e", action="store_true", help="skip the save() comparison through the reference's logger factory")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "wanted", "all"],
+                    help="sharded runs: all-gather only the join keys another shard can want (three small collectives and a host "
+                         "round trip: pays from four shards on, the default there), or all of them")
     ap.add_argument("--parity-full", action="store_true",
                     help="also run the reference on the WHOLE benchmark trace and compare sha256 (minutes of CPU time)")
     a = ap.parse_args()
@@ -110,7 +113,7 @@ def config(args, world, n):
             "memory_events": "memory_events: %d launches + half as many cpu_instant_event rows",
             "generic": "generic: %d GenericTraceActivity kernel records"}[args.workload] % n
     return {"workload": what, "name": args.workload, "n_per_gpu": n,
-            "sharding": ("contiguous record range, %d shard(s), join keys exchanged" % world) if args.workload in SHARDED
+            "sharding": ("contiguous record range, %d shard(s), join keys exchanged (%s)" % (world, "all" if args.exchange == "all" or (args.exchange == "auto" and world < 4) else "those another shard can want")) if args.workload in SHARDED
             else ("%d independent trace(s)" % world),
             "l2": "inputs and output of one step exceed the 126 MB L2 many times over; no flush needed", "seed": "fixed"}
 
@@ -314,11 +317,16 @@ def run_ours(args):
         ops_local = api.device_view(info.op_ids, n_ops, "<i4", dev)
         x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         x0.record(s)
-        ex = exchanges.setdefault(id(c), sharding.JoinExchange(rank, world, dist, dev))
-        rows, ext_stride, ops_stride, counts = ex.gather(ext_local, ops_local)
+        if args.exchange == "all" or (args.exchange == "auto" and world < 4):
+            ex = exchanges.setdefault(id(c), sharding.JoinExchange(rank, world, dist, dev))
+            rows, ext_stride, ops_stride, counts = ex.gather(ext_local, ops_local)
+            cap = None
+        else:  # only the records another shard can want travel
+            ex = exchanges.setdefault(id(c), sharding.FilteredJoinExchange(rank, world, dist, dev))
+            rows, ext_stride, ops_stride, counts, cap = ex.gather(c, info)
         x1.record(s)
         exchange_events.append((x0, x1))
-        c.set_global_join_rows(rows, ext_stride, ops_stride, counts, world, rank)
+        c.set_global_join_rows(rows, ext_stride, ops_stride, counts, world, rank, ext_capacity=cap)
 
     # ---- resident: inputs already in HBM, the text stays in HBM ----
     dev_arrays = api.device_arrays(trace, dev)

@@ -278,8 +278,9 @@ k2j_status k2j_set_global_join_rows(k2j_ctx* ctx, const void* ext_rows, uint64_t
 /* Sending join keys only where they can be wanted.  With k2j_set_global_join_rows a shard reads its OWN records
  * and ids from its own arrays, never from its row, so the row a shard contributes only has to hold what other
  * shards can want.  k2j_join_need_bits (after k2j_segment) fills `bits` (device memory, n_bits a power of two,
- * the same on every shard; about 8 bits per GPU-side record keep false hits near 2 %) with the filter of the
- * correlation ids this shard's events carry.  The caller all-gathers the filters; k2j_filter_join_keys then
+ * the same on every shard; about 4 bits per GPU-side record keep false hits near 2 %) with the filter of the
+ * correlation ids this shard's events carry; `bits` must stay as it is until k2j_emit has run, which tests the
+ * gathered keys against it.  The caller all-gathers the filters; k2j_filter_join_keys then
  * writes to `out_records` (device memory, room for `capacity` >= this shard's n_external records), in their order,
  * those of this shard's EXTERNAL_CORRELATION records whose correlation id hits the filter of at least one OTHER
  * shard (`need_rows`: the gathered filters, row_pitch_bytes apart), and their number to `n_out` (device memory, on

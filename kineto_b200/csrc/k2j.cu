@@ -105,6 +105,7 @@ struct k2j_ctx {
   uint64_t n_guest_ops = 0;                                           // k2j_set_guest_ops
   std::vector<SpanRec> partial_spans;                                 // sharded runs: this shard's parts of the user-annotation spans
   uint32_t g_ext_stride = 0, g_ops_stride = 0, g_world = 1, g_rank = 0; uint64_t g_pitch = 0; const uint64_t* g_counts = nullptr;  // rows of an all-gather
+  uint32_t* need_bits = nullptr; uint64_t need_n_bits = 0;             // the caller's filter from k2j_join_need_bits, valid for this segmentation
 };
 
 namespace {
@@ -518,7 +519,7 @@ k2j_status k2j_segment(k2j_ctx* c, k2j_segment_info* info) {
   if (!c) return K2J_ERR_INVALID_ARGUMENT;
   if (!c->have_params) return fail(c, K2J_ERR_STATE, "k2j_set_params has not been called");
   K2J_CUDA(c, cudaSetDevice(c->device));
-  c->ran = false; c->segmented = false; c->have_global_join = false;
+  c->ran = false; c->segmented = false; c->have_global_join = false; c->need_bits = nullptr;
   cudaStream_t s = c->stream;
   c->launches = 0;
 
@@ -664,6 +665,7 @@ k2j_status k2j_join_need_bits(k2j_ctx* c, void* bits, uint64_t n_bits) {
   K2J_CUDA(c, cudaMemsetAsync(bits, 0, n_bits / 8, s));
   if (d.ops_begin) { k_mark_corr<<<(uint32_t)((d.ops_begin + 255) / 256), 256, 0, s>>>(d); c->launches++; }
   K2J_CUDA(c, cudaGetLastError());
+  c->need_bits = static_cast<uint32_t*>(bits); c->need_n_bits = n_bits;  // k2j_emit tests the gathered keys against the same filter
   return K2J_OK;
 }
 
@@ -973,13 +975,17 @@ k2j_status emit_core(k2j_ctx* c, k2j_result* res, const TileSink& sink) {
   if (filter) {
     const uint32_t corr_bits = std::max<uint32_t>(1u << 20, pow2_at_least(8 * std::max<uint64_t>(1, n_gpu_events)));
     const uint32_t op_bits = corr_bits;
-    K2J_CUDA(c, c->need_corr.reserve(corr_bits / 8));
     K2J_CUDA(c, c->need_op.reserve(op_bits / 8));
-    d.need_corr = c->need_corr.as<uint32_t>(); d.need_corr_mask = corr_bits - 1;
     d.need_op = c->need_op.as<uint32_t>(); d.need_op_mask = op_bits - 1;
-    K2J_CUDA(c, cudaMemsetAsync(d.need_corr, 0, corr_bits / 8, s));
     K2J_CUDA(c, cudaMemsetAsync(d.need_op, 0, op_bits / 8, s));
-    if (d.ops_begin) { k_mark_corr<<<(uint32_t)((d.ops_begin + 255) / 256), 256, 0, s>>>(d); c->launches++; }
+    if (c->need_bits) {  // the filter the caller had filled for the exchange (k2j_join_need_bits): the same marks
+      d.need_corr = c->need_bits; d.need_corr_mask = (uint32_t)(c->need_n_bits - 1);
+    } else {
+      K2J_CUDA(c, c->need_corr.reserve(corr_bits / 8));
+      d.need_corr = c->need_corr.as<uint32_t>(); d.need_corr_mask = corr_bits - 1;
+      K2J_CUDA(c, cudaMemsetAsync(d.need_corr, 0, corr_bits / 8, s));
+      if (d.ops_begin) { k_mark_corr<<<(uint32_t)((d.ops_begin + 255) / 256), 256, 0, s>>>(d); c->launches++; }
+    }
   }
   // collective enrichment: kernels look at their linked op's name only if some op is a record_param_comms call;
   // ops of other shards carry no metadata here, so sharded runs do not enrich

@@ -240,7 +240,7 @@ class FilteredJoinExchange:
         self.ext_stride = max(1, int(m[0] * 1.02) + 16)                 # index stride: room for a shard's own records
         self.ops_stride = (max(1, int(m[1] * 1.02) + 16) + 1) & ~1
         n_bits = 1 << 20
-        while n_bits < 8 * m[2] and n_bits < (1 << 32):
+        while n_bits < 3 * m[2] and n_bits < (1 << 32):   # records walked, of which about three quarters own an event
             n_bits *= 2
         self.bits = torch.empty(n_bits // 8, dtype=torch.uint8, device=self.device)
         self.need = torch.empty(n_bits // 8 * self.world, dtype=torch.uint8, device=self.device)
