@@ -320,13 +320,15 @@ def run_ours(args):
         if args.exchange == "all" or (args.exchange == "auto" and world < 4):
             ex = exchanges.setdefault(id(c), sharding.JoinExchange(rank, world, dist, dev))
             rows, ext_stride, ops_stride, counts = ex.gather(ext_local, ops_local)
-            cap = None
         else:  # only the records another shard can want travel
             ex = exchanges.setdefault(id(c), sharding.FilteredJoinExchange(rank, world, dist, dev))
-            rows, ext_stride, ops_stride, counts, cap = ex.gather(c, info)
+            ex.exchange(c, info)
+            x1.record(s)
+            exchange_events.append((x0, x1))
+            return
         x1.record(s)
         exchange_events.append((x0, x1))
-        c.set_global_join_rows(rows, ext_stride, ops_stride, counts, world, rank, ext_capacity=cap)
+        c.set_global_join_rows(rows, ext_stride, ops_stride, counts, world, rank)
 
     # ---- resident: inputs already in HBM, the text stays in HBM ----
     dev_arrays = api.device_arrays(trace, dev)

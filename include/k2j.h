@@ -289,6 +289,16 @@ k2j_status k2j_set_global_join_rows(k2j_ctx* ctx, const void* ext_rows, uint64_t
  * is the number of records row r holds.  Nothing of the result changes; the bytes a rank receives no longer grow
  * with the number of shards times the shard size.  No reference counterpart. */
 k2j_status k2j_join_need_bits(k2j_ctx* ctx, void* bits, uint64_t n_bits);
+/* The CPU-op ids of the other shards as bitmaps.  The join only asks whether an activity with a given id exists
+ * anywhere in the trace (activityMap_.find, libkineto/src/GenericActivityProfiler.cpp:397-408), and the ids of a
+ * shard usually fill a narrow range: k2j_op_id_bits (after k2j_segment) sets, in `bits` (device memory, n_bits a
+ * multiple of 32), bit id - min_id for every CPU-side activity of this shard (guest rows excluded; an id outside the
+ * range is K2J_ERR_INVALID_ARGUMENT).  After k2j_set_global_join_rows, k2j_set_global_op_bits hands over the gathered
+ * bitmaps (row r of `bit_rows`, row_pitch_bytes apart, with meta[2 r] = its min_id and meta[2 r + 1] = its n_bits;
+ * device memory): the op ids of the rows given to k2j_set_global_join_rows are then not read, and only this shard's
+ * own ids enter its table.  Forgotten by the next k2j_set_global_join*. */
+k2j_status k2j_op_id_bits(k2j_ctx* ctx, int64_t min_id, uint64_t n_bits, void* bits);
+k2j_status k2j_set_global_op_bits(k2j_ctx* ctx, const void* bit_rows, uint64_t row_pitch_bytes, const int64_t* meta);
 k2j_status k2j_filter_join_keys(k2j_ctx* ctx, const void* need_rows, uint64_t row_pitch_bytes, uint64_t n_bits, uint32_t world,
                                 uint32_t rank, void* out_records, uint64_t capacity, uint64_t* n_out);
 k2j_status k2j_emit(k2j_ctx* ctx, k2j_result* result);

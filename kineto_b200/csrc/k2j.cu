@@ -105,6 +105,7 @@ struct k2j_ctx {
   uint64_t n_guest_ops = 0;                                           // k2j_set_guest_ops
   std::vector<SpanRec> partial_spans;                                 // sharded runs: this shard's parts of the user-annotation spans
   uint32_t g_ext_stride = 0, g_ops_stride = 0, g_world = 1, g_rank = 0; uint64_t g_pitch = 0; const uint64_t* g_counts = nullptr;  // rows of an all-gather
+  const uint32_t* g_op_bits = nullptr; uint64_t g_op_bits_pitch = 0; const int64_t* g_op_bits_meta = nullptr;  // k2j_set_global_op_bits
   uint32_t* need_bits = nullptr; uint64_t need_n_bits = 0;             // the caller's filter from k2j_join_need_bits, valid for this segmentation
 };
 
@@ -630,7 +631,7 @@ k2j_status k2j_set_global_join(k2j_ctx* c, const void* ext_all, uint64_t n_ext_a
     return fail(c, K2J_ERR_INVALID_ARGUMENT, "gathered join arrays out of range");
   c->g_ext = ext_all; c->g_n_ext = n_ext_all; c->g_own_begin = own_begin;
   c->g_op_ids = op_ids_all; c->g_n_ops = n_ops_all;
-  c->g_counts = nullptr; c->g_world = 1; c->g_rank = 0;
+  c->g_counts = nullptr; c->g_world = 1; c->g_rank = 0; c->g_op_bits = nullptr;
   c->have_global_join = true;
   return K2J_OK;
 }
@@ -648,8 +649,36 @@ k2j_status k2j_set_global_join_rows(k2j_ctx* c, const void* ext_rows, uint64_t e
   c->g_ext = ext_rows; c->g_n_ext = ext_stride * world; c->g_own_begin = ext_stride * rank;
   c->g_op_ids = op_id_rows; c->g_n_ops = ops_stride * world;
   c->g_ext_stride = (uint32_t)ext_stride; c->g_ops_stride = (uint32_t)ops_stride; c->g_pitch = row_pitch_bytes;
-  c->g_counts = counts; c->g_world = world; c->g_rank = rank;
+  c->g_counts = counts; c->g_world = world; c->g_rank = rank; c->g_op_bits = nullptr;
   c->have_global_join = true;
+  return K2J_OK;
+}
+
+k2j_status k2j_op_id_bits(k2j_ctx* c, int64_t min_id, uint64_t n_bits, void* bits) {
+  if (!c) return K2J_ERR_INVALID_ARGUMENT;
+  if (!c->segmented) return fail(c, K2J_ERR_STATE, "k2j_segment has not run");
+  if (!bits || !is_device_ptr(bits) || n_bits == 0 || (n_bits & 31) || n_bits > (1ull << 33))
+    return fail(c, K2J_ERR_INVALID_ARGUMENT, "op id bits: device memory, a multiple of 32 bits, at most 2^33");
+  K2J_CUDA(c, cudaSetDevice(c->device));
+  cudaStream_t s = c->stream;
+  const Dev& d = c->d;
+  K2J_CUDA(c, cudaMemsetAsync(bits, 0, n_bits / 8, s));
+  K2J_CUDA(c, cudaMemsetAsync(d.counters, 0, sizeof(Counters), s));
+  const uint64_t n = c->n_ops - c->n_guest_ops;
+  if (n) { k_op_id_bits<<<(uint32_t)((n + 255) / 256), 256, 0, s>>>(d, min_id, n_bits, static_cast<uint32_t*>(bits)); c->launches++; }
+  K2J_CUDA(c, cudaGetLastError());
+  K2J_CUDA(c, cudaMemcpyAsync(c->h_counters, d.counters, sizeof(Counters), cudaMemcpyDeviceToHost, s));
+  K2J_CUDA(c, cudaStreamSynchronize(s));
+  if (c->h_counters->device_check) return fail(c, K2J_ERR_INVALID_ARGUMENT, "op id bits: an id of this shard lies outside [min_id, min_id + n_bits)");
+  return K2J_OK;
+}
+
+k2j_status k2j_set_global_op_bits(k2j_ctx* c, const void* bit_rows, uint64_t row_pitch_bytes, const int64_t* meta) {
+  if (!c) return K2J_ERR_INVALID_ARGUMENT;
+  if (!c->have_global_join || !c->g_counts) return fail(c, K2J_ERR_STATE, "k2j_set_global_join_rows has not been called");
+  if (!bit_rows || !meta || !is_device_ptr(bit_rows) || !is_device_ptr(meta) || (row_pitch_bytes & 3))
+    return fail(c, K2J_ERR_INVALID_ARGUMENT, "op id bits: device memory, rows a multiple of 4 bytes apart");
+  c->g_op_bits = static_cast<const uint32_t*>(bit_rows); c->g_op_bits_pitch = row_pitch_bytes; c->g_op_bits_meta = meta;
   return K2J_OK;
 }
 
@@ -910,11 +939,12 @@ k2j_status emit_core(k2j_ctx* c, k2j_result* res, const TileSink& sink) {
     d.join_op_ids = c->g_op_ids; d.n_join_ops = c->g_n_ops;
     d.join_counts = c->g_counts; d.ext_stride = c->g_ext_stride; d.ops_stride = c->g_ops_stride; d.join_pitch = c->g_pitch;
     d.own_rank = c->g_counts ? c->g_rank : 0xFFFFFFFFu; d.own_n_ext = totals[C_EXT]; d.own_n_ops = c->n_ops - c->n_guest_ops;
+    d.op_bits = c->g_op_bits; d.op_bits_pitch = c->g_op_bits_pitch / 4; d.op_bits_meta = c->g_op_bits_meta; d.op_bits_world = c->g_world;
     own_begin = c->g_own_begin; own_end = own_begin + totals[C_EXT];
   } else {
     d.ext_all = d.ext_local; d.n_ext_all = totals[C_EXT];
     d.join_op_ids = d.op_id; d.n_join_ops = c->n_ops - c->n_guest_ops;
-    d.join_counts = nullptr; d.own_rank = 0xFFFFFFFFu;
+    d.join_counts = nullptr; d.own_rank = 0xFFFFFFFFu; d.op_bits = nullptr;
   }
   K2J_CUDA(c, c->ev_size.reserve(std::max<uint64_t>(1, d.n_events) * 4));
   K2J_CUDA(c, c->ev_off.reserve(std::max<uint64_t>(1, d.n_events) * 8));
@@ -1045,7 +1075,10 @@ k2j_status emit_core(k2j_ctx* c, k2j_result* res, const TileSink& sink) {
     }
   }
   if (d.n_ext_all) { k_build_corr<<<(uint32_t)((d.n_ext_all + 255) / 256), 256, 0, s>>>(d, own_begin, own_end); c->launches++; }
-  if (d.n_join_ops) { k_build_ops<<<(uint32_t)((d.n_join_ops + 255) / 256), 256, 0, s>>>(d); c->launches++; }
+  if (d.op_bits != nullptr) {  // the other shards' ids came as bitmaps: the table holds this shard's own ids only
+    const uint64_t first = (uint64_t)c->g_ops_stride * c->g_rank, last = first + d.own_n_ops;
+    if (last > first) { k_build_ops<<<(uint32_t)((last - first + 255) / 256), 256, 0, s>>>(d, first, last); c->launches++; }
+  } else if (d.n_join_ops) { k_build_ops<<<(uint32_t)((d.n_join_ops + 255) / 256), 256, 0, s>>>(d, 0, d.n_join_ops); c->launches++; }
   if (d.n_ext_all) { k_resolve_corr<<<(corr_cap + 255) / 256, 256, 0, s>>>(d); c->launches++; }
   K2J_CUDA(c, cudaGetLastError());
   K2J_CUDA(c, cudaEventRecord(c->ev[2], s));

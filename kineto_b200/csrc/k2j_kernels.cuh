@@ -148,6 +148,9 @@ struct Dev {
   // with rows, this shard's own records and ids are read from its own arrays (ext_local, op_id), never from its row: the
   // rows may then hold, for every OTHER shard, only the records some shard other than their owner can want
   uint32_t own_rank; uint64_t own_n_ext, own_n_ops;
+  // CPU-op ids of the other shards as bitmaps of their id ranges (nullptr: as lists, see join_op_ids): row r holds one
+  // bit per id from op_bits_meta[2 r] on, op_bits_meta[2 r + 1] bits; the join only asks whether an id exists
+  const uint32_t* op_bits; uint64_t op_bits_pitch; const int64_t* op_bits_meta; uint32_t op_bits_world;
   // sharded runs: bit sets (by hash) of the correlation ids this shard's events carry and of the CPU-op ids
   // the matching records name; keys outside them are not inserted.  nullptr: insert everything.
   uint32_t* need_corr; uint32_t need_corr_mask; uint32_t* need_op; uint32_t need_op_mask;
@@ -666,10 +669,10 @@ __global__ void k_build_coll(Dev d) {
   if (!tab_insert(d.coll_tab, d.coll_mask, (uint32_t)d.op_id[i], (uint32_t)i)) atomicAdd(&d.counters->device_check, 1ull);
 }
 // CPU-op id -> position (last writer wins): activityMap_[id] = op, GenericActivityProfiler.cpp:262.
-__global__ void k_build_ops(Dev d) {
-  const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+__global__ void k_build_ops(Dev d, uint64_t first, uint64_t last) {
+  const uint64_t i = first + (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   uint32_t id = 0u;
-  const bool in = i < d.n_join_ops && op_id_at(d, i, &id);
+  const bool in = i < last && op_id_at(d, i, &id);
   const bool valid = in && (d.need_op == nullptr || bit_test(d.need_op, d.need_op_mask, id));
   // Ids repeat (every memory event of a PyTorch trace carries id 0): of the lanes of a warp that hold one id only the
   // last, which is the one that must win, goes to the table, so a run of equal ids costs one atomic per warp.
@@ -1071,12 +1074,35 @@ __device__ __forceinline__ bool out_of_range(const Dev& d, int64_t ts, int64_t d
 // never match; the external id must equal a CPU-op id exactly as a 64-bit value.
 // k_resolve_corr does the two dependent lookups once per table entry and leaves the linked op's id
 // (or 0) in the entry's low half, so that an event needs a single probe.
+// Is there a CPU-side activity with this id (activityMap_.find, GenericActivityProfiler.cpp:397-408)?  The table holds
+// this shard's ids (or every shard's, as lists); the other shards' ids may come as bitmaps instead.
+struct OpBits { const uint32_t* bits; uint64_t pitch; const int64_t* meta; uint32_t world, own_rank; };
+__device__ __forceinline__ OpBits op_bits_of(const Dev& d) { return OpBits{d.op_bits, d.op_bits_pitch, d.op_bits_meta, d.op_bits_world, d.own_rank}; }
+__device__ __forceinline__ bool op_in_bitmaps(const OpBits b, int32_t id) {
+  if (b.bits == nullptr) return false;
+  for (uint32_t r = 0; r < b.world; r++) {
+    if (r == b.own_rank) continue;
+    const int64_t k = (int64_t)id - b.meta[2 * r];
+    if (k >= 0 && k < b.meta[2 * r + 1] && ((b.bits[(uint64_t)r * b.pitch + (uint64_t)(k >> 5)] >> (k & 31)) & 1u)) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ bool op_known(const Dev& d, int32_t id) {
+  return tab_find(d.op_tab, d.op_mask, (uint32_t)id) != 0xFFFFFFFFu || op_in_bitmaps(op_bits_of(d), id);
+}
+__global__ void k_op_id_bits(Dev d, int64_t min_id, uint64_t n_bits, uint32_t* bits) {
+  const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= d.n_ops - d.n_guest_ops) return;
+  const int64_t k = (int64_t)d.op_id[i] - min_id;
+  if (k < 0 || (uint64_t)k >= n_bits) { atomicAdd(&d.counters->device_check, 1ull); return; }
+  atomicOr(&bits[k >> 5], 1u << (k & 31));
+}
 __global__ void k_resolve_corr(Dev d) {
   const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i == 0u && d.corr0[0] != 0ull) {  // correlation id 0
     ExtRec z; ext_at(d, d.corr0[0] - 1ull, &z);
     const int64_t ext = (int64_t)z.external_id;
-    const bool linked = ext == (int64_t)(int32_t)ext && tab_find(d.op_tab, d.op_mask, (uint32_t)(int32_t)ext) != 0xFFFFFFFFu;
+    const bool linked = ext == (int64_t)(int32_t)ext && op_known(d, (int32_t)ext);
     d.corr0[1] = linked ? ((1ull << 33) | (unsigned long long)(uint32_t)(int32_t)ext) : 0ull;
   }
   if (i > d.corr_mask) return;
@@ -1085,7 +1111,7 @@ __global__ void k_resolve_corr(Dev d) {
   ExtRec rec; ext_at(d, (uint32_t)e - 1u, &rec);
   const int64_t ext = (int64_t)rec.external_id;
   uint32_t id = 0;
-  if (ext == (int64_t)(int32_t)ext && tab_find(d.op_tab, d.op_mask, (uint32_t)(int32_t)ext) != 0xFFFFFFFFu)
+  if (ext == (int64_t)(int32_t)ext && op_known(d, (int32_t)ext))
   {
     id = (uint32_t)(int32_t)ext;  // the linked op's correlationId() is the key it was found under
     if (id == 0u && d.corr_zero != nullptr) atomicOr(&d.corr_zero[i >> 5], 1u << (i & 31u));  // linked, to the op whose id is 0
@@ -1117,13 +1143,13 @@ __device__ __forceinline__ void linked_op(const Dev& d, uint32_t corr, unsigned 
 // make every thread of the size pass copy that block (about 1 KB) into local memory at kernel entry.
 struct SpanArgs {
   const unsigned long long* user_tab; uint32_t user_mask; const ExtRec* ext_all; uint32_t ext_stride; uint64_t join_pitch;  // rows of an all-gather: see Dev
-  const ExtRec* ext_local; uint32_t own_rank;
+  const ExtRec* ext_local; uint32_t own_rank; OpBits op_bits;
   const unsigned long long* op_tab; uint32_t op_mask;
   unsigned long long* ds_tab; uint32_t ds_mask; unsigned long long* span_key; unsigned long long* span_nstart;
   unsigned long long* span_end; unsigned long long* span_nfirst; uint32_t* span_row; uint32_t span_mask; Counters* counters;
 };
 __device__ __forceinline__ SpanArgs span_args(const Dev& d) {
-  return SpanArgs{d.user_tab, d.user_mask, d.ext_all, d.join_counts != nullptr ? d.ext_stride : 0u, d.join_pitch, d.ext_local, d.own_rank, d.op_tab, d.op_mask, d.ds_tab, d.ds_mask, d.span_key, d.span_nstart,
+  return SpanArgs{d.user_tab, d.user_mask, d.ext_all, d.join_counts != nullptr ? d.ext_stride : 0u, d.join_pitch, d.ext_local, d.own_rank, op_bits_of(d), d.op_tab, d.op_mask, d.ds_tab, d.ds_mask, d.span_key, d.span_nstart,
                   d.span_end, d.span_nfirst, d.span_row, d.span_mask, d.counters};
 }
 __device__ __noinline__ void span_update(const SpanArgs d, uint32_t corr, uint32_t dev, uint32_t stream, int64_t ts,
@@ -1137,7 +1163,7 @@ __device__ __noinline__ void span_update(const SpanArgs d, uint32_t corr, uint32
   const int64_t ext = (int64_t)rec->external_id;
   if (ext != (int64_t)(int32_t)ext) return;
   const uint32_t row = tab_find(d.op_tab, d.op_mask, (uint32_t)(int32_t)ext);
-  if (row == 0xFFFFFFFFu) return;
+  if (row == 0xFFFFFFFFu && !op_in_bitmaps(d.op_bits, (int32_t)ext)) return;  // (several shards: the row is not used, only that the op exists)
   const unsigned long long dskey = (((unsigned long long)dev << 32) | stream) + 1ull;
   uint32_t i = hash32(dev * 0x9E3779B1u ^ stream) & d.ds_mask;
   uint32_t probes = 0;

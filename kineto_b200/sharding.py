@@ -225,12 +225,15 @@ class FilteredJoinExchange:
     of the correlation ids its events carry (K2J.join_need_bits, a few bits per event), keeps of its own
     EXTERNAL_CORRELATION records those that hit another rank's filter (K2J.filter_join_keys, in order), and the
     ranks all-gather rows of [kept records | CPU-op ids] sized by the largest kept count (one host round trip for
-    that count).  The library reads a rank's own records from the rank's own arrays, so nothing else is needed."""
+    the sizes).  The CPU-op ids travel as bitmaps of the shards' id ranges when every shard's ids are dense
+    (K2J.op_id_bits: the join only asks whether an id exists), else as lists.  The library reads a rank's own records
+    and ids from the rank's own arrays, so nothing else is needed."""
 
-    def __init__(self, rank: int, world: int, dist, device):
+    def __init__(self, rank: int, world: int, dist, device, op_bitmaps: bool = True):
         self.rank, self.world, self.dist, self.device = rank, world, dist, device
+        self.op_bitmaps = op_bitmaps
         self.ext_stride = 0
-        self.cap = 0
+        self.cap = self.tail = self.row_words = 0
 
     def _agree(self, n_ext: int, n_ops: int, n_records: int):
         import torch
@@ -245,12 +248,11 @@ class FilteredJoinExchange:
         self.bits = torch.empty(n_bits // 8, dtype=torch.uint8, device=self.device)
         self.need = torch.empty(n_bits // 8 * self.world, dtype=torch.uint8, device=self.device)
         self.kept = torch.empty(self.ext_stride * 2, dtype=torch.int64, device=self.device)
-        self.mine = torch.zeros(2, dtype=torch.int64, device=self.device)
-        self.counts = torch.empty(2 * self.world, dtype=torch.int64, device=self.device)
+        self.mine = torch.zeros(4, dtype=torch.int64, device=self.device)
+        self.all4 = torch.empty(4 * self.world, dtype=torch.int64, device=self.device)
 
-    def gather(self, ctx, info):
-        """`info`: what K2J.segment() returned.  Returns (rows, ext_stride, ops_stride, counts, ext_capacity) for
-        K2J.set_global_join_rows."""
+    def exchange(self, ctx, info):
+        """`info`: what K2J.segment() returned.  Leaves the context ready for K2J.emit()."""
         import torch
         from . import api
         n_ext, n_ops = int(info.n_external), int(info.n_ops)
@@ -261,21 +263,37 @@ class FilteredJoinExchange:
         ctx.join_need_bits(self.bits)
         self.dist.all_gather_into_tensor(self.need, self.bits)
         ctx.filter_join_keys(self.need, self.world, self.rank, self.kept, self.mine[:1])
-        self.mine[1] = n_ops
-        self.dist.all_gather_into_tensor(self.counts, self.mine)
-        cap = int(self.counts[0::2].max().item())                       # the one host round trip of the exchange
-        cap = max(1, cap)
-        if cap > self.cap:                                              # grow-only row buffers
-            self.cap = int(cap * 1.25) + 16
-            words = self.cap * 2 + self.ops_stride // 2
-            self.row = torch.zeros(words, dtype=torch.int64, device=self.device)
-            self.rows = torch.empty(words * self.world, dtype=torch.int64, device=self.device)
-        n_kept = int(self.counts[2 * self.rank].item())
-        self.row[:n_kept * 2] = self.kept[:n_kept * 2]
         ops_local = api.device_view(info.op_ids, n_ops, "<i4", self.device)
-        self.row[self.cap * 2:].view(ops_local.dtype)[:n_ops] = ops_local
+        self.mine[1] = n_ops
+        if n_ops:
+            lo, hi = torch.aminmax(ops_local)
+            self.mine[2], self.mine[3] = lo, hi
+        else:
+            self.mine[2], self.mine[3] = 0, -1
+        self.dist.all_gather_into_tensor(self.all4, self.mine)
+        sizes = self.all4.cpu().view(self.world, 4)                     # the one host round trip of the exchange
+        cap = max(1, int(sizes[:, 0].max()))
+        spans = [(int(r[2]), int(r[3]) - int(r[2]) + 1, int(r[1])) for r in sizes]   # (first id, ids spanned, ids held)
+        dense = self.op_bitmaps and all(n == 0 or span <= 64 * n + 4096 for _, span, n in spans)
+        tail = max(1, max((span + 63) // 64 for _, span, _ in spans)) if dense else self.ops_stride // 2
+        if cap > self.cap or tail > self.tail:                          # grow-only row buffers
+            self.cap, self.tail = max(self.cap, int(cap * 1.25) + 16), max(self.tail, tail)
+            self.row_words = self.cap * 2 + self.tail
+            self.row = torch.zeros(self.row_words, dtype=torch.int64, device=self.device)
+            self.rows = torch.empty(self.row_words * self.world, dtype=torch.int64, device=self.device)
+        n_kept = int(sizes[self.rank, 0])
+        self.row[:n_kept * 2] = self.kept[:n_kept * 2]
+        if dense:
+            ctx.op_id_bits(spans[self.rank][0], self.row[self.cap * 2:])
+        else:
+            self.row[self.cap * 2:].view(ops_local.dtype)[:n_ops] = ops_local
         self.dist.all_gather_into_tensor(self.rows, self.row)
-        return self.rows, self.ext_stride, self.ops_stride, self.counts, self.cap
+        self.counts = self.all4.view(self.world, 4)[:, :2].contiguous().view(-1)
+        ctx.set_global_join_rows(self.rows, self.ext_stride, self.ops_stride, self.counts, self.world, self.rank, ext_capacity=self.cap)
+        if dense:
+            self.meta = torch.tensor([v for first, _, _ in spans for v in (first, self.tail * 64)], dtype=torch.int64, device=self.device)
+            ctx.set_global_op_bits(self.rows.data_ptr() + self.cap * 16, self.row_words * 8, self.meta)
+        self.kept_counts, self.dense = [int(v) for v in sizes[:, 0]], dense
 
 
 def output_bases(out_bytes: int, rank: int, world: int, dist, device):

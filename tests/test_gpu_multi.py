@@ -46,14 +46,14 @@ def _rank_main(rank, port, tmp):
         got_rows = ctx.copy_output().tobytes()
         assert got_rows == got and res_rows["x_events"] == res["x_events"] and res_rows["invalid_external_correlation_events"] == res["invalid_external_correlation_events"]
         # and with rows that hold only the records another shard can want
-        fx = sharding.FilteredJoinExchange(rank, WORLD, dist, dev)
-        for _ in range(2):
-            info3 = ctx.segment()
-            rows, ext_stride, ops_stride, counts, cap = fx.gather(ctx, info3)
-            ctx.set_global_join_rows(rows, ext_stride, ops_stride, counts, WORLD, rank, ext_capacity=cap)
-            res_f = ctx.emit()
-            assert ctx.copy_output().tobytes() == got and res_f["x_events"] == res["x_events"]
-            assert int(counts[2 * rank]) <= int(info3.n_external)
+        for bitmaps in (True, False):   # the CPU-op ids as bitmaps of the shards' id ranges, or as lists
+            fx = sharding.FilteredJoinExchange(rank, WORLD, dist, dev, op_bitmaps=bitmaps)
+            for _ in range(2):
+                info3 = ctx.segment()
+                fx.exchange(ctx, info3)
+                res_f = ctx.emit()
+                assert ctx.copy_output().tobytes() == got and res_f["x_events"] == res["x_events"]
+                assert fx.kept_counts[rank] <= int(info3.n_external) and fx.dense == bitmaps
         shard.g_ext = ext_all.cpu().numpy().view(np.uint64)
         shard.g_ops = ops_all.cpu().numpy()
         want, stats = helpers.run_port(shard)

@@ -364,6 +364,25 @@ def test_sharded_runs_concatenate_to_the_whole(n_shards):
                     c.set_global_join_rows(rows, ext_stride, ops_stride, counts, n_shards, r, ext_capacity=cap)
                     c.emit()
                     assert c.copy_output().tobytes() == parts[r], "filtered rows of shard %d" % r
+            # and with the other shards' CPU-op ids as bitmaps of their id ranges (k2j_op_id_bits, k2j_set_global_op_bits)
+            ids = [api.device_view(i.op_ids, int(i.n_ops), "<i4").clone() for i in infos]
+            firsts = [int(v.min()) for v in ids]
+            tail = max((int(v.max()) - f + 64) // 64 for v, f in zip(ids, firsts))
+            bit_rows = torch.zeros(n_shards * tail, dtype=torch.int64, device="cuda:0")
+            meta = torch.tensor([v for f in firsts for v in (f, tail * 64)], dtype=torch.int64, device="cuda:0")
+            for r, c in enumerate(ctxs):
+                c.op_id_bits(firsts[r], bit_rows[r * tail:(r + 1) * tail])
+            with pytest.raises(api.K2JError, match="outside"):
+                ctxs[0].op_id_bits(firsts[0] + 1, bit_rows[:tail].clone())
+            rows.view(torch.int32)[:] = torch.where(torch.arange(rows.numel() * 2, device="cuda:0") % (words * 2) >= cap * 4,
+                                                    torch.full((1,), 0x7FFFFFF0, dtype=torch.int32, device="cuda:0"),
+                                                    rows.view(torch.int32))   # the id lists are not read any more
+            torch.cuda.synchronize()
+            for r, c in enumerate(ctxs):
+                c.set_global_join_rows(rows, ext_stride, ops_stride, counts, n_shards, r, ext_capacity=cap)
+                c.set_global_op_bits(bit_rows.data_ptr(), tail * 8, meta)
+                c.emit()
+                assert c.copy_output().tobytes() == parts[r], "op id bitmaps, shard %d" % r
         finally:
             for c in ctxs:
                 c.close()
