@@ -232,6 +232,55 @@ def test_error_behaviour():
         ctx.close()
 
 
+def test_error_behaviour_of_the_sharding_entry_points():
+    """Call order and argument checks of the entry points for sharded traces: a status, never a fault."""
+    import torch
+    from kineto_b200 import api
+    t = synth.gen_kernel_launches(2000, seed=3, pool_size=20)
+    ctx = api.K2J(0)
+    try:
+        ctx.load(t)
+        bits = torch.zeros(1 << 17, dtype=torch.uint8, device="cuda:0")
+        torch.cuda.synchronize()
+        for call in (lambda: ctx.export_lookup_records(), lambda: ctx.join_need_bits(bits),
+                     lambda: ctx.op_id_bits(0, torch.zeros(64, dtype=torch.int64, device="cuda:0"))):
+            with pytest.raises(api.K2JError) as e:
+                call()
+            assert e.value.status == 4                     # STATE: not segmented yet
+        with pytest.raises(api.K2JError) as e:
+            ctx.partial_spans()
+        assert e.value.status == 4                         # STATE: no run yet
+        info = ctx.segment()
+        with pytest.raises(api.K2JError) as e:
+            ctx.join_need_bits(bits[:1000])                # not a power of two
+        assert e.value.status == 1
+        for front, back in ((4, len(t.cupti)), (len(t.cupti), 8), (0, len(t.cupti) + 8), (8, len(t.cupti))):
+            with pytest.raises(api.K2JError) as e:
+                ctx.set_guest_ranges(front, back)          # misaligned, crossing, past the end, through a buffer
+            assert e.value.status == 1
+        with pytest.raises(api.K2JError) as e:
+            ctx.set_guest_ops(t.n_ops + 1)
+        assert e.value.status == 1
+        with pytest.raises(api.K2JError) as e:
+            ctx.set_global_op_bits(bits.data_ptr(), 64, torch.zeros(2, dtype=torch.int64, device="cuda:0"))
+        assert e.value.status == 4                         # STATE: no gathered rows yet
+        ptr, n = ctx.export_lookup_records()               # no synchronisation records: the first writers of contexts and streams only
+        assert n > 0 and n % 8 == 0
+        with pytest.raises(api.K2JError) as e:
+            ctx.append_spans(np.zeros(0, api.SPAN))
+        assert e.value.status == 4                         # STATE: nothing emitted yet
+        ctx.emit()                                         # still one shard: k2j_run's result
+        bad = np.zeros(1, api.SPAN)
+        bad["op_row"] = t.n_ops
+        with pytest.raises(api.K2JError) as e:
+            ctx.append_spans(bad)
+        assert e.value.status == 1
+        assert ctx.append_spans(np.zeros(0, api.SPAN)) == 0
+        assert ctx.copy_output().tobytes() == helpers.run_port(t)[0] and int(info.n_ops) == t.n_ops
+    finally:
+        ctx.close()
+
+
 @pytest.mark.parametrize("n", [1, 255, 2048, 2049, 1_000_003])
 def test_exclusive_scan_entry_point(n):
     import torch
