@@ -305,6 +305,7 @@ def run_ours(args):
 
     exchange_events = []
     exchanges = {}
+    kept_fraction = [None]  # filtered exchange: the largest share of its join keys a shard had to send
 
     def prepare(c, s):
         """segment -> (all-gather join keys): everything before the emit step."""
@@ -323,6 +324,7 @@ def run_ours(args):
         else:  # only the records another shard can want travel
             ex = exchanges.setdefault(id(c), sharding.FilteredJoinExchange(rank, world, dist, dev))
             ex.exchange(c, info)
+            kept_fraction[0] = max(ex.kept_counts) / max(1, ex.ext_stride)
             x1.record(s)
             exchange_events.append((x0, x1))
             return
@@ -467,6 +469,7 @@ def run_ours(args):
                          "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at size argument 1000000, scaled by the text bytes",
                          "pipeline_frac": alg_all / (sum(stage.values()) / args.steps * 1e-3) / 1e9 / peak},
             "stage_ms_per_step": dict({k: v / args.steps for k, v in stage.items()}, ms_exchange=ms_exchange),
+            "exchange_keys_sent_fraction": kept_fraction[0],
         }
         if ms_e2e is not None:
             line["e2e"] = {"value": total_records * args.steps / (ms_e2e * 1e-3), "unit": UNIT,

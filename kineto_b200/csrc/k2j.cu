@@ -710,15 +710,11 @@ k2j_status k2j_filter_join_keys(k2j_ctx* c, const void* need_rows, uint64_t row_
   K2J_CUDA(c, cudaSetDevice(c->device));
   cudaStream_t s = c->stream;
   const Dev& d = c->d;
-  const uint64_t n_words = n_bits / 32;
-  K2J_CUDA(c, c->need_corr.reserve(n_bits / 8));            // scratch: the union of the other shards' filters
   K2J_CUDA(c, c->ev_size.reserve(std::max<uint64_t>(1, n) * 4));   // scratch: marks and their scan (free between segment and emit)
   K2J_CUDA(c, c->ev_off.reserve(std::max<uint64_t>(1, n) * 8));
-  k_union_needs<<<(uint32_t)((n_words + 255) / 256), 256, 0, s>>>(static_cast<const uint32_t*>(need_rows), row_pitch_bytes / 4, world, rank, n_words,
-                                                                c->need_corr.as<uint32_t>());
-  c->launches++;
   if (n) {
-    k_flag_wanted<<<(uint32_t)((n + 255) / 256), 256, 0, s>>>(d, c->need_corr.as<uint32_t>(), (uint32_t)(n_bits - 1), n, c->ev_size.as<uint32_t>());
+    k_flag_wanted<<<(uint32_t)((n + 255) / 256), 256, 0, s>>>(d, static_cast<const uint32_t*>(need_rows), row_pitch_bytes / 4, world, rank,
+                                                             (uint32_t)(n_bits - 1), n, c->ev_size.as<uint32_t>());
     c->launches++;
     K2J_CUDA(c, cudaGetLastError());
     k2j_status st = run_scan(c, c->ev_size.as<uint32_t>(), n, 1, c->ev_off.as<uint64_t>(), c->scan_totals.as<uint64_t>() + 27, &c->launches);

@@ -628,22 +628,21 @@ __global__ void k_mark_corr(Dev d) {
   bit_set(d.need_corr, d.need_corr_mask, *reinterpret_cast<const uint32_t*>(r + off));
 }
 // ---- sending join keys only where they can be wanted ----
-// Every shard publishes the filter k_mark_corr fills (the correlation ids its events carry).  k_union_needs ORs the
-// other shards' filters; k_flag_wanted marks this shard's EXTERNAL_CORRELATION records (kinds the join uses) whose
-// correlation id hits that union; after a scan of the marks k_take_wanted copies them out in their order, which is
-// all that "the last record of a correlation id wins" needs: positions only have to grow along a shard's records.
-__global__ void k_union_needs(const uint32_t* rows, uint64_t pitch_words, uint32_t world, uint32_t rank, uint64_t n_words, uint32_t* out) {
-  const uint64_t w = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (w >= n_words) return;
-  uint32_t v = 0u;
-  for (uint32_t r = 0; r < world; r++) if (r != rank) v |= rows[(uint64_t)r * pitch_words + w];
-  out[w] = v;
-}
-__global__ void k_flag_wanted(Dev d, const uint32_t* wanted, uint32_t mask, uint64_t n, uint32_t* flags) {
+// Every shard publishes the filter k_mark_corr fills (the correlation ids its events carry).  k_flag_wanted marks this
+// shard's EXTERNAL_CORRELATION records (kinds the join uses) whose correlation id hits the filter of at least one other
+// shard - each filter is asked on its own: their union would be so dense with many shards that half of all keys
+// passed - and after a scan of the marks k_take_wanted copies them out in their order, which is all that "the last
+// record of a correlation id wins" needs: positions only have to grow along a shard's records.
+__global__ void k_flag_wanted(Dev d, const uint32_t* filters, uint64_t pitch_words, uint32_t world, uint32_t rank, uint32_t mask, uint64_t n,
+                              uint32_t* flags) {
   const uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (j >= n) return;
   const ExtRec e = d.ext_local[j];
-  flags[j] = (e.external_kind == 3u || e.external_kind == 4u) && bit_test(wanted, mask, e.correlation_id) ? 1u : 0u;
+  bool wanted = false;
+  if (e.external_kind == 3u || e.external_kind == 4u)
+    for (uint32_t r = 0; r < world && !wanted; r++)
+      if (r != rank) wanted = bit_test(filters + (uint64_t)r * pitch_words, mask, e.correlation_id);
+  flags[j] = wanted ? 1u : 0u;
 }
 __global__ void k_take_wanted(Dev d, const uint32_t* flags, const uint64_t* at, uint64_t n, ExtRec* out) {
   const uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
