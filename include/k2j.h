@@ -232,6 +232,12 @@ k2j_status k2j_set_guest_ops(k2j_ctx* ctx, uint64_t n_guest_ops);
  * CPU-side activities (its own or guest rows, k2j_set_guest_ops; 0xFFFFFFFF: no name), and hands the list to
  * k2j_append_spans on the last shard's context, which appends their events, in the reference's order
  * (libkineto/src/GenericActivityProfiler.h:341-346), to the text k2j_emit left there. */
+/* A sharded run keeps tables for the spans whenever K2J_FLAG_USER_ANNOTATIONS is set, since another shard's CUSTOM1
+ * records may name this shard's events.  A caller that knows no shard holds such a record (the sum of
+ * n_user_external over the shards is 0) says so with k2j_set_join_user_records(ctx, 0) after k2j_set_global_join*, and
+ * the run then neither clears nor fills those tables (CUSTOM1 records that turn up all the same are ignored).
+ * Forgotten by the next k2j_set_global_join*. */
+k2j_status k2j_set_join_user_records(k2j_ctx* ctx, int any);
 typedef struct {
   int64_t start_ns, end_ns;
   uint64_t first_event;
@@ -263,6 +269,7 @@ typedef struct {
   const k2j_external_record* external_records; /* device memory, n_external entries */
   uint64_t n_ops;
   const int32_t* op_ids;                       /* device memory, n_ops entries */
+  uint64_t n_user_external;                    /* how many of the n_external records are of kind CUSTOM1 (user annotations) */
 } k2j_segment_info;
 k2j_status k2j_segment(k2j_ctx* ctx, k2j_segment_info* info);
 k2j_status k2j_set_global_join(k2j_ctx* ctx, const void* external_all, uint64_t n_external_all, uint64_t own_begin,

@@ -61,13 +61,13 @@ class Result(C.Structure):
 
 class SegmentInfo(C.Structure):
     _fields_ = [("n_records", C.c_uint64), ("n_external", C.c_uint64), ("external_records", C.c_void_p),
-                ("n_ops", C.c_uint64), ("op_ids", C.c_void_p)]
+                ("n_ops", C.c_uint64), ("op_ids", C.c_void_p), ("n_user_external", C.c_uint64)]
 
 
 SPAN = np.dtype([("start_ns", "<i8"), ("end_ns", "<i8"), ("first_event", "<u8"), ("device", "<u4"), ("stream", "<u4"),
                  ("op_id", "<i4"), ("op_row", "<u4")])  # k2j_span
 
-EXPORTS = ["k2j_set_global_join_rows", "k2j_join_need_bits", "k2j_filter_join_keys", "k2j_op_id_bits", "k2j_set_global_op_bits", "k2j_emit_to_host", "k2j_emit_to_fd", "k2j_exclusive_scan_u32", "k2j_exclusive_scan_u32_noalloc", "k2j_segment", "k2j_set_global_join", "k2j_emit", "k2j_create", "k2j_destroy", "k2j_last_error", "k2j_set_params", "k2j_set_strings",
+EXPORTS = ["k2j_set_global_join_rows", "k2j_join_need_bits", "k2j_filter_join_keys", "k2j_op_id_bits", "k2j_set_global_op_bits", "k2j_set_join_user_records", "k2j_emit_to_host", "k2j_emit_to_fd", "k2j_exclusive_scan_u32", "k2j_exclusive_scan_u32_noalloc", "k2j_segment", "k2j_set_global_join", "k2j_emit", "k2j_create", "k2j_destroy", "k2j_last_error", "k2j_set_params", "k2j_set_strings",
            "k2j_set_cbid_names", "k2j_set_thread_map", "k2j_set_ops", "k2j_set_cupti", "k2j_run", "k2j_output",
            "k2j_copy_output", "k2j_copy_output_async", "k2j_write_output", "k2j_write_output_at", "k2j_synchronize", "k2j_version",
            "k2j_export_lookup_records", "k2j_set_guest_ranges", "k2j_set_guest_ops", "k2j_partial_spans", "k2j_append_spans", "k2j_names_create", "k2j_names_destroy", "k2j_names_intern", "k2j_names_pool", "k2j_intern_kernel_names"]
@@ -102,6 +102,7 @@ def load_library():
     lib.k2j_join_need_bits.argtypes = [vp, vp, C.c_uint64]
     lib.k2j_op_id_bits.argtypes = [vp, C.c_int64, C.c_uint64, vp]
     lib.k2j_set_global_op_bits.argtypes = [vp, vp, C.c_uint64, vp]
+    lib.k2j_set_join_user_records.argtypes = [vp, C.c_int]
     lib.k2j_filter_join_keys.argtypes = [vp, vp, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint32, vp, C.c_uint64, vp]
     lib.k2j_emit.argtypes = [vp, C.POINTER(Result)]
     lib.k2j_emit_to_host.argtypes = [vp, vp, C.c_uint64, C.c_uint64, C.POINTER(Result)]
@@ -300,6 +301,10 @@ class K2J:
         """`meta`: int64 device tensor, (min_id, n_bits) per shard; `bit_rows_ptr`: address of shard 0's bitmap."""
         self._keep["g_op_meta"] = meta
         self._check(self.lib.k2j_set_global_op_bits(self.h, bit_rows_ptr, row_pitch_bytes, meta.data_ptr()))
+
+    def set_join_user_records(self, any_records: bool):
+        """Sharded runs: whether any shard holds CUSTOM1 correlation records (k2j_set_join_user_records)."""
+        self._check(self.lib.k2j_set_join_user_records(self.h, 1 if any_records else 0))
 
     def join_need_bits(self, bits):
         """Fills the uint8 device tensor `bits` (a power-of-two number of bits) with this shard's filter."""

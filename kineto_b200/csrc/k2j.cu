@@ -106,6 +106,7 @@ struct k2j_ctx {
   std::vector<SpanRec> partial_spans;                                 // sharded runs: this shard's parts of the user-annotation spans
   uint32_t g_ext_stride = 0, g_ops_stride = 0, g_world = 1, g_rank = 0; uint64_t g_pitch = 0; const uint64_t* g_counts = nullptr;  // rows of an all-gather
   const uint32_t* g_op_bits = nullptr; uint64_t g_op_bits_pitch = 0; const int64_t* g_op_bits_meta = nullptr;  // k2j_set_global_op_bits
+  int join_user_hint = -1;                                            // k2j_set_join_user_records: -1 not told
   uint32_t* need_bits = nullptr; uint64_t need_n_bits = 0;             // the caller's filter from k2j_join_need_bits, valid for this segmentation
 };
 
@@ -614,6 +615,7 @@ k2j_status k2j_segment(k2j_ctx* c, k2j_segment_info* info) {
     info->n_external = totals[C_EXT];
     info->external_records = reinterpret_cast<const k2j_external_record*>(d.ext_local);
     info->n_ops = c->n_ops - c->n_guest_ops;
+    info->n_user_external = totals[C_USER];
     info->op_ids = d.op_id;
     K2J_CUDA(c, cudaStreamSynchronize(s));  // the arrays above are complete when this returns
   }
@@ -631,7 +633,7 @@ k2j_status k2j_set_global_join(k2j_ctx* c, const void* ext_all, uint64_t n_ext_a
     return fail(c, K2J_ERR_INVALID_ARGUMENT, "gathered join arrays out of range");
   c->g_ext = ext_all; c->g_n_ext = n_ext_all; c->g_own_begin = own_begin;
   c->g_op_ids = op_ids_all; c->g_n_ops = n_ops_all;
-  c->g_counts = nullptr; c->g_world = 1; c->g_rank = 0; c->g_op_bits = nullptr;
+  c->g_counts = nullptr; c->g_world = 1; c->g_rank = 0; c->g_op_bits = nullptr; c->join_user_hint = -1;
   c->have_global_join = true;
   return K2J_OK;
 }
@@ -649,8 +651,15 @@ k2j_status k2j_set_global_join_rows(k2j_ctx* c, const void* ext_rows, uint64_t e
   c->g_ext = ext_rows; c->g_n_ext = ext_stride * world; c->g_own_begin = ext_stride * rank;
   c->g_op_ids = op_id_rows; c->g_n_ops = ops_stride * world;
   c->g_ext_stride = (uint32_t)ext_stride; c->g_ops_stride = (uint32_t)ops_stride; c->g_pitch = row_pitch_bytes;
-  c->g_counts = counts; c->g_world = world; c->g_rank = rank; c->g_op_bits = nullptr;
+  c->g_counts = counts; c->g_world = world; c->g_rank = rank; c->g_op_bits = nullptr; c->join_user_hint = -1;
   c->have_global_join = true;
+  return K2J_OK;
+}
+
+k2j_status k2j_set_join_user_records(k2j_ctx* c, int any) {
+  if (!c) return K2J_ERR_INVALID_ARGUMENT;
+  if (!c->have_global_join) return fail(c, K2J_ERR_STATE, "k2j_set_global_join has not been called");
+  c->join_user_hint = any ? 1 : 0;
   return K2J_OK;
 }
 
@@ -966,7 +975,11 @@ k2j_status emit_core(k2j_ctx* c, k2j_result* res, const TileSink& sink) {
   d.corr0 = c->corr0.as<unsigned long long>();
   K2J_CUDA(c, cudaMemsetAsync(d.corr0, 0, 16, s));
   // the user-annotation table is only written and read when CUSTOM1 correlation records exist
-  if (totals[C_USER] > 0 || c->have_global_join) K2J_CUDA(c, cudaMemsetAsync(d.user_tab, 0, (size_t)corr_cap * 8, s));
+  // (several shards: another shard's CUSTOM1 records may name this shard's events, so the local count says nothing,
+  // unless the caller has said that no shard holds any)
+  const bool user_records = c->have_global_join ? c->join_user_hint != 0 : totals[C_USER] > 0;
+  if (user_records) K2J_CUDA(c, cudaMemsetAsync(d.user_tab, 0, (size_t)corr_cap * 8, s));
+  else d.user_tab = nullptr;
   K2J_CUDA(c, cudaMemsetAsync(d.op_tab, 0, (size_t)op_cap * 8, s));
   const uint32_t tid_cap = std::max<uint32_t>(16384, pow2_at_least(4ull * c->n_tid));
   K2J_CUDA(c, c->tid_tab.reserve((size_t)tid_cap * 8));
@@ -974,8 +987,7 @@ k2j_status emit_core(k2j_ctx* c, k2j_result* res, const TileSink& sink) {
   K2J_CUDA(c, cudaMemsetAsync(d.tid_tab, 0, (size_t)tid_cap * 8, s));
   if (c->n_tid + c->n_ops) { k_build_tids<<<(uint32_t)((c->n_tid + c->n_ops + 255) / 256), 256, 0, s>>>(d); c->launches++; }
   // user-annotation span tables (single-shard runs only)
-  // (several shards: another shard's CUSTOM1 records may name this shard's events, so the local count says nothing)
-  const bool spans_on = (c->params.flags & K2J_FLAG_USER_ANNOTATIONS) && (c->have_global_join || totals[C_USER] > 0);
+  const bool spans_on = (c->params.flags & K2J_FLAG_USER_ANNOTATIONS) && user_records;
   d.span_key = nullptr;
   uint32_t span_cap = 0;
   if (spans_on) {

@@ -697,7 +697,8 @@ __global__ void k_build_corr(Dev d, uint64_t own_begin, uint64_t own_end) {
   } else if (e.external_kind == 4u) {
     atomicAdd(&d.counters->n_user, 1ull);
     // user-annotation spans: the same filter as above when the keys of several shards were gathered
-    if (d.need_corr == nullptr || (i >= own_begin && i < own_end) || bit_test(d.need_corr, d.need_corr_mask, e.correlation_id)) {
+    if (d.user_tab != nullptr &&
+        (d.need_corr == nullptr || (i >= own_begin && i < own_end) || bit_test(d.need_corr, d.need_corr_mask, e.correlation_id))) {
       if (d.need_op != nullptr && (int64_t)e.external_id == (int64_t)(int32_t)e.external_id) bit_set(d.need_op, d.need_op_mask, (uint32_t)e.external_id);
       ok = tab_insert(d.user_tab, d.user_mask, e.correlation_id, (uint32_t)i);
     }

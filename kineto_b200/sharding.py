@@ -248,8 +248,8 @@ class FilteredJoinExchange:
         self.bits = torch.empty(n_bits // 8, dtype=torch.uint8, device=self.device)
         self.need = torch.empty(n_bits // 8 * self.world, dtype=torch.uint8, device=self.device)
         self.kept = torch.empty(self.ext_stride * 2, dtype=torch.int64, device=self.device)
-        self.mine = torch.zeros(4, dtype=torch.int64, device=self.device)
-        self.all4 = torch.empty(4 * self.world, dtype=torch.int64, device=self.device)
+        self.mine = torch.zeros(5, dtype=torch.int64, device=self.device)
+        self.all5 = torch.empty(5 * self.world, dtype=torch.int64, device=self.device)
 
     def exchange(self, ctx, info):
         """`info`: what K2J.segment() returned.  Leaves the context ready for K2J.emit()."""
@@ -270,8 +270,9 @@ class FilteredJoinExchange:
             self.mine[2], self.mine[3] = lo, hi
         else:
             self.mine[2], self.mine[3] = 0, -1
-        self.dist.all_gather_into_tensor(self.all4, self.mine)
-        sizes = self.all4.cpu().view(self.world, 4)                     # the one host round trip of the exchange
+        self.mine[4] = int(info.n_user_external)
+        self.dist.all_gather_into_tensor(self.all5, self.mine)
+        sizes = self.all5.cpu().view(self.world, 5)                     # the one host round trip of the exchange
         cap = max(1, int(sizes[:, 0].max()))
         spans = [(int(r[2]), int(r[3]) - int(r[2]) + 1, int(r[1])) for r in sizes]   # (first id, ids spanned, ids held)
         dense = self.op_bitmaps and all(n == 0 or span <= 64 * n + 4096 for _, span, n in spans)
@@ -288,11 +289,12 @@ class FilteredJoinExchange:
         else:
             self.row[self.cap * 2:].view(ops_local.dtype)[:n_ops] = ops_local
         self.dist.all_gather_into_tensor(self.rows, self.row)
-        self.counts = self.all4.view(self.world, 4)[:, :2].contiguous().view(-1)
+        self.counts = self.all5.view(self.world, 5)[:, :2].contiguous().view(-1)
         ctx.set_global_join_rows(self.rows, self.ext_stride, self.ops_stride, self.counts, self.world, self.rank, ext_capacity=self.cap)
         if dense:
             self.meta = torch.tensor([v for first, _, _ in spans for v in (first, self.tail * 64)], dtype=torch.int64, device=self.device)
             ctx.set_global_op_bits(self.rows.data_ptr() + self.cap * 16, self.row_words * 8, self.meta)
+        ctx.set_join_user_records(bool(int(sizes[:, 4].sum())))         # no CUSTOM1 records anywhere: no span tables to clear
         self.kept_counts, self.dense = [int(v) for v in sizes[:, 0]], dense
 
 

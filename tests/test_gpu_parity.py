@@ -430,6 +430,7 @@ def test_sharded_runs_concatenate_to_the_whole(n_shards):
             for r, c in enumerate(ctxs):
                 c.set_global_join_rows(rows, ext_stride, ops_stride, counts, n_shards, r, ext_capacity=cap)
                 c.set_global_op_bits(bit_rows.data_ptr(), tail * 8, meta)
+                c.set_join_user_records(False)   # no shard holds CUSTOM1 records: nothing to clear or fill for spans
                 c.emit()
                 assert c.copy_output().tobytes() == parts[r], "op id bitmaps, shard %d" % r
         finally:
@@ -576,6 +577,11 @@ def test_sharded_user_annotations_concatenate_to_the_whole(gen, n_shards):
             spans.append(c.partial_spans())
             parts.append(c.copy_output().tobytes())
         assert sum(len(p) for p in spans) > 3
+        # told that no shard holds CUSTOM1 records, a run keeps no span tables: the same text, no parts
+        ctxs[0].set_global_join(ext, ext.numel() // 2, 0, ops, ops.numel())
+        ctxs[0].set_join_user_records(False)
+        assert ctxs[0].emit()["x_events"] == results[0]["x_events"] and len(ctxs[0].partial_spans()) == 0
+        assert ctxs[0].copy_output().tobytes() == parts[0]
         merged = sharding.merge_spans(spans, shards[-1].op_id)
         added = ctxs[-1].append_spans(merged)
         last = ctxs[-1].copy_output().tobytes()
