@@ -170,3 +170,82 @@ def test_guest_records_are_laid_out_around_the_shards_own_buffers():
     assert data[:16].eq(1).all() and torch.equal(data[16:80], own) and data[80:88].eq(3).all() and data[88:].eq(4).all()
     data, table, front_end, back_begin = sharding.with_guest_records(own, np.array([0, 64], np.uint64), [blobs[1], blobs[1]], 0)
     assert data is own and table.tolist() == [0, 64] and (front_end, back_begin) == (0, 64)
+
+
+class _FakeContext:
+    """Stands in for api.K2J in the exchange's control flow: records the calls, fills what the library would fill."""
+
+    def __init__(self, n_ext, kept):
+        self.n_ext, self.kept, self.calls = n_ext, kept, []
+
+    def join_need_bits(self, bits):
+        bits.zero_()
+        self.calls.append(("need", bits.numel() * 8))
+
+    def filter_join_keys(self, need, world, rank, out, n_out):
+        out[:self.kept * 2] = torch.arange(self.kept * 2, dtype=torch.int64) + 1000 * rank
+        n_out[0] = self.kept
+        self.calls.append(("filter", need.numel(), world, rank))
+
+    def op_id_bits(self, first, bits):
+        bits.zero_()
+        bits[0] = 1
+        self.calls.append(("op_bits", first, bits.numel() * 64))
+
+    def set_global_join_rows(self, rows, ext_stride, ops_stride, counts, world, rank, ext_capacity=None):
+        self.calls.append(("rows", rows.numel(), ext_stride, ops_stride, counts.tolist(), world, rank, ext_capacity))
+
+    def set_global_op_bits(self, ptr, pitch, meta):
+        self.calls.append(("op_rows", pitch, meta.tolist()))
+
+    def set_join_user_records(self, any_records):
+        self.calls.append(("user", any_records))
+
+
+def _filtered_rank_main(rank, port, tmp):
+    from kineto_b200 import api
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(WORLD))
+    dist.init_process_group("gloo", rank=rank, world_size=WORLD)
+    try:
+        ids = torch.arange(100 * rank + 5, 100 * rank + 5 + 40 + rank, dtype=torch.int32)
+        api_view = api.device_view
+        api.device_view = lambda ptr, n, typestr, device="cpu": ids[:n]       # the library's id array, on the host here
+
+        class Info:
+            n_external, n_ops, n_records, op_ids, n_user_external = 300 + rank, len(ids), 1000, 0, 3 * rank
+        for bitmaps in (True, False):
+            fx = sharding.FilteredJoinExchange(rank, WORLD, dist, "cpu", op_bitmaps=bitmaps)
+            for step in range(2):
+                ctx = _FakeContext(300 + rank, kept=20 + 7 * rank + step)
+                fx.exchange(ctx, Info)
+                names = [c[0] for c in ctx.calls]
+                assert names == (["need", "filter", "op_bits", "rows", "op_rows", "user"] if bitmaps else ["need", "filter", "rows", "user"])
+                rows = dict((c[0], c) for c in ctx.calls)["rows"]
+                assert rows[4] == [20 + step, 40, 27 + step, 41] and rows[5:7] == (WORLD, rank) and rows[7] == fx.cap >= 27 + step
+                assert rows[2] >= 301 and rows[3] >= 41 and rows[1] == fx.row_words * WORLD
+                assert dict((c[0], c) for c in ctx.calls)["user"][1] is True       # rank 1 holds CUSTOM1 records
+                assert fx.kept_counts == [20 + step, 27 + step] and fx.dense == bitmaps
+                # what travelled: every rank's kept records in front of its row, then its ids (as bits or as a list)
+                for r in range(WORLD):
+                    row = fx.rows[r * fx.row_words:(r + 1) * fx.row_words]
+                    assert row[:fx.kept_counts[r] * 2].tolist() == [1000 * r + k for k in range(fx.kept_counts[r] * 2)]
+                    if bitmaps:
+                        assert int(row[fx.cap * 2]) == 1
+                    else:
+                        assert row[fx.cap * 2:].view(torch.int32)[:40 + r].tolist() == list(range(100 * r + 5, 100 * r + 45 + r))
+                if bitmaps:
+                    meta = dict((c[0], c) for c in ctx.calls)["op_rows"]
+                    assert meta[1] == fx.row_words * 8 and meta[2][0::2] == [5, 105] and meta[2][1] == meta[2][3] >= 41
+        api.device_view = api_view
+        open(os.path.join(tmp, "filtered_ok%d" % rank), "w").write("1")
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_run_the_filtered_exchange(tmp_path):
+    """The control flow of sharding.FilteredJoinExchange over two gloo ranks with a stand-in for the context: the
+    collectives, the sizes agreed in the one host round trip, the rows' layout and the calls the library receives."""
+    port = 29400 + (os.getpid() % 500)
+    mp.spawn(_filtered_rank_main, args=(port, str(tmp_path)), nprocs=WORLD, join=True)
+    assert all(os.path.exists(str(tmp_path / ("filtered_ok%d" % r))) for r in range(WORLD))
