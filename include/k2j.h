@@ -195,60 +195,6 @@ k2j_status k2j_set_cupti(k2j_ctx* ctx, const uint8_t* bytes, uint64_t n_bytes, c
  * plus ChromeTraceLogger::handleActivity (libkineto/src/output_json.cpp:837-963) for every event. */
 k2j_status k2j_run(k2j_ctx* ctx, k2j_result* result);
 
-/* Sharded traces whose shards hold synchronisation or CUDA event records.  The reference fills the lookups
- * those records use from the WHOLE trace before it logs anything: context -> device from the first kernel, copy
- * or memset record that names the context (libkineto/src/CuptiActivityProfiler.cpp:221-239), (context, event) ->
- * CUDA event record (:241-254, :379-402), the streams that showed GPU work inside the window, which gate deferred
- * stream-wait records (:502-514), and the once-per-row announcement in front of a row's first stream
- * synchronisation (libkineto/src/output_json.cpp:917-943).  A shard's share of that knowledge is carried by a few
- * of its own records.  k2j_export_lookup_records (after k2j_segment) returns them, copied verbatim and in
- * processing order into one CUPTI buffer in device memory of the context (valid until its next call): per context
- * its first kernel / copy / memset record, per (device, stream) the first such record inside the window, per
- * (context, stream) the first stream synchronisation inside the window, and every CUDA event record.  The caller
- * all-gathers the shards' buffers and gives each shard, through k2j_set_cupti, the lower shards' buffers in front of
- * its own buffers and the higher shards' behind them, then names the two byte ranges with k2j_set_guest_ranges
- * (records below `front_end_bytes` and from `back_begin_bytes` on are guests; buffers must not straddle either
- * boundary; k2j_set_cupti forgets the ranges).  Guest records take part in every lookup exactly as if the shard had
- * met them itself, print nothing and are not counted.  Then k2j_segment, the join exchange and k2j_emit as usual.
- * Without declared guest ranges a sharded run with such records is K2J_ERR_UNSUPPORTED. */
-k2j_status k2j_export_lookup_records(k2j_ctx* ctx, const void** records, uint64_t* n_bytes);
-/* Sharded traces with collectives.  A kernel launched by a record_param_comms CPU op prints that op's collective
- * metadata (libkineto/src/output_json.cpp:718-801, :900-906), and the op may belong to another shard.  The caller
- * appends the other shards' record_param_comms ops (id, name and metadata entries; their strings added to the pool)
- * behind its own rows in k2j_set_ops and says how many of the last rows are such guests: guest rows are found by the
- * kernels that need them, are never logged, extend no map and are not among the op ids k2j_segment reports.
- * k2j_set_ops resets the count to 0.  Ids of record_param_comms ops are taken to be used by no other op of the
- * trace (the reference would take the last op with that id, whatever its name).  Guest rows also serve as the
- * named rows of k2j_append_spans below. */
-k2j_status k2j_set_guest_ops(k2j_ctx* ctx, uint64_t n_guest_ops);
-
-/* Sharded traces with user annotations.  A gpu_user_annotation span covers, per (device, stream) and annotation
- * op, the GPU activities correlated to that op (libkineto/src/GenericActivityProfiler.cpp:292-327), wherever in the
- * trace they are, and the reference logs the spans after every other activity.  With K2J_FLAG_USER_ANNOTATIONS a
- * sharded run (k2j_set_global_join*) writes no spans; after k2j_emit, k2j_partial_spans returns this shard's part
- * of every span (host memory of the context, valid until its next run; first_event is the shard's own event
- * number; op_row is not meaningful).  The caller merges the parts of all shards - smallest start, largest end,
- * first_event ordered by (shard, event number) - names for each span the row of its op among the LAST shard's
- * CPU-side activities (its own or guest rows, k2j_set_guest_ops; 0xFFFFFFFF: no name), and hands the list to
- * k2j_append_spans on the last shard's context, which appends their events, in the reference's order
- * (libkineto/src/GenericActivityProfiler.h:341-346), to the text k2j_emit left there. */
-/* A sharded run keeps tables for the spans whenever K2J_FLAG_USER_ANNOTATIONS is set, since another shard's CUSTOM1
- * records may name this shard's events.  A caller that knows no shard holds such a record (the sum of
- * n_user_external over the shards is 0) says so with k2j_set_join_user_records(ctx, 0) after k2j_set_global_join*, and
- * the run then neither clears nor fills those tables (CUSTOM1 records that turn up all the same are ignored).
- * Forgotten by the next k2j_set_global_join*. */
-k2j_status k2j_set_join_user_records(k2j_ctx* ctx, int any);
-typedef struct {
-  int64_t start_ns, end_ns;
-  uint64_t first_event;
-  uint32_t device, stream;
-  int32_t op_id;
-  uint32_t op_row;
-} k2j_span;
-k2j_status k2j_partial_spans(k2j_ctx* ctx, const k2j_span** spans, uint64_t* n_spans);
-k2j_status k2j_append_spans(k2j_ctx* ctx, const k2j_span* spans, uint64_t n_spans, uint64_t* n_bytes);
-k2j_status k2j_set_guest_ranges(k2j_ctx* ctx, uint64_t front_end_bytes, uint64_t back_begin_bytes);
-
 /* The same work in two steps, for traces sharded by contiguous record range over several GPUs (one
  * context per GPU).  k2j_segment walks this shard's buffers and compacts its EXTERNAL_CORRELATION
  * records (k2j_external_record, processing order).  The caller all-gathers those arrays and the CPU
@@ -306,6 +252,64 @@ k2j_status k2j_join_need_bits(k2j_ctx* ctx, void* bits, uint64_t n_bits);
  * own ids enter its table.  Forgotten by the next k2j_set_global_join*. */
 k2j_status k2j_op_id_bits(k2j_ctx* ctx, int64_t min_id, uint64_t n_bits, void* bits);
 k2j_status k2j_set_global_op_bits(k2j_ctx* ctx, const void* bit_rows, uint64_t row_pitch_bytes, const int64_t* meta);
+
+/* ---- sharded traces: what crosses shards besides the join keys ---- */
+
+/* Sharded traces whose shards hold synchronisation or CUDA event records.  The reference fills the lookups
+ * those records use from the WHOLE trace before it logs anything: context -> device from the first kernel, copy
+ * or memset record that names the context (libkineto/src/CuptiActivityProfiler.cpp:221-239), (context, event) ->
+ * CUDA event record (:241-254, :379-402), the streams that showed GPU work inside the window, which gate deferred
+ * stream-wait records (:502-514), and the once-per-row announcement in front of a row's first stream
+ * synchronisation (libkineto/src/output_json.cpp:917-943).  A shard's share of that knowledge is carried by a few
+ * of its own records.  k2j_export_lookup_records (after k2j_segment) returns them, copied verbatim and in
+ * processing order into one CUPTI buffer in device memory of the context (valid until its next call): per context
+ * its first kernel / copy / memset record, per (device, stream) the first such record inside the window, per
+ * (context, stream) the first stream synchronisation inside the window, and every CUDA event record.  The caller
+ * all-gathers the shards' buffers and gives each shard, through k2j_set_cupti, the lower shards' buffers in front of
+ * its own buffers and the higher shards' behind them, then names the two byte ranges with k2j_set_guest_ranges
+ * (records below `front_end_bytes` and from `back_begin_bytes` on are guests; buffers must not straddle either
+ * boundary; k2j_set_cupti forgets the ranges).  Guest records take part in every lookup exactly as if the shard had
+ * met them itself, print nothing and are not counted.  Then k2j_segment, the join exchange and k2j_emit as usual.
+ * Without declared guest ranges a sharded run with such records is K2J_ERR_UNSUPPORTED. */
+k2j_status k2j_export_lookup_records(k2j_ctx* ctx, const void** records, uint64_t* n_bytes);
+k2j_status k2j_set_guest_ranges(k2j_ctx* ctx, uint64_t front_end_bytes, uint64_t back_begin_bytes);
+
+/* Sharded traces with collectives.  A kernel launched by a record_param_comms CPU op prints that op's collective
+ * metadata (libkineto/src/output_json.cpp:718-801, :900-906), and the op may belong to another shard.  The caller
+ * appends the other shards' record_param_comms ops (id, name and metadata entries; their strings added to the pool)
+ * behind its own rows in k2j_set_ops and says how many of the last rows are such guests: guest rows are found by the
+ * kernels that need them, are never logged, extend no map and are not among the op ids k2j_segment reports.
+ * k2j_set_ops resets the count to 0.  Ids of record_param_comms ops are taken to be used by no other op of the
+ * trace (the reference would take the last op with that id, whatever its name).  Guest rows also serve as the
+ * named rows of k2j_append_spans below. */
+k2j_status k2j_set_guest_ops(k2j_ctx* ctx, uint64_t n_guest_ops);
+
+/* Sharded traces with user annotations.  A gpu_user_annotation span covers, per (device, stream) and annotation
+ * op, the GPU activities correlated to that op (libkineto/src/GenericActivityProfiler.cpp:292-327), wherever in the
+ * trace they are, and the reference logs the spans after every other activity.  With K2J_FLAG_USER_ANNOTATIONS a
+ * sharded run (k2j_set_global_join*) writes no spans; after k2j_emit, k2j_partial_spans returns this shard's part
+ * of every span (host memory of the context, valid until its next run; first_event is the shard's own event
+ * number; op_row is not meaningful).  The caller merges the parts of all shards - smallest start, largest end,
+ * first_event ordered by (shard, event number) - names for each span the row of its op among the LAST shard's
+ * CPU-side activities (its own or guest rows, k2j_set_guest_ops; 0xFFFFFFFF: no name), and hands the list to
+ * k2j_append_spans on the last shard's context, which appends their events, in the reference's order
+ * (libkineto/src/GenericActivityProfiler.h:341-346), to the text k2j_emit left there. */
+typedef struct {
+  int64_t start_ns, end_ns;
+  uint64_t first_event;
+  uint32_t device, stream;
+  int32_t op_id;
+  uint32_t op_row;
+} k2j_span;
+k2j_status k2j_partial_spans(k2j_ctx* ctx, const k2j_span** spans, uint64_t* n_spans);
+k2j_status k2j_append_spans(k2j_ctx* ctx, const k2j_span* spans, uint64_t n_spans, uint64_t* n_bytes);
+/* A sharded run keeps tables for the spans whenever K2J_FLAG_USER_ANNOTATIONS is set, since another shard's CUSTOM1
+ * records may name this shard's events.  A caller that knows no shard holds such a record (the sum of
+ * n_user_external over the shards is 0) says so with k2j_set_join_user_records(ctx, 0) after k2j_set_global_join*, and
+ * the run then neither clears nor fills those tables (CUSTOM1 records that turn up all the same are ignored).
+ * Forgotten by the next k2j_set_global_join*. */
+k2j_status k2j_set_join_user_records(k2j_ctx* ctx, int any);
+
 k2j_status k2j_filter_join_keys(k2j_ctx* ctx, const void* need_rows, uint64_t row_pitch_bytes, uint64_t n_bits, uint32_t world,
                                 uint32_t rank, void* out_records, uint64_t capacity, uint64_t* n_out);
 k2j_status k2j_emit(k2j_ctx* ctx, k2j_result* result);
