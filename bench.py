@@ -227,7 +227,7 @@ def run_reference(args):
         return
     cores = os.cpu_count() or 1
     procs = max(1, min(cores, 32))
-    sample_n = min(args.n, max(1000, args.cpu_sample // 5))
+    sample_n = min(args.n, max(1000, args.cpu_sample))   # per process: the size the cpu_baseline sample has
     trace = generate(args.workload, sample_n)
     n_rec = cupti_record_count(trace) + len(trace.op_start)
     vals, secs_all = [], []
